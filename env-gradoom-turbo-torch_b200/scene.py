@@ -1,0 +1,719 @@
+"""Host-side scene description and the seeded synthetic map generator.
+
+A :class:`Scene` is the immutable, per-device input of the renderer: map
+geometry (linedef-like walls with a front sector on the right of ``v1 -> v2``
+and an optional back sector), sector heights / lights / flats, the palette
+indexed texture atlas, PLAYPAL, COLORMAP, sprite patches with their id tables,
+psprite (weapon) patches and the status-bar patches.  Field meanings follow the
+reference's ``CompiledScenario`` (src/gradoom/scenario.py:302-401) so a scene
+can be converted to one and fed to the reference engine unchanged; the names
+and the container are this package's own.
+
+The generator stands in for the Doom assets, which are not redistributable and
+not present: it emits grid maps of rectangular rooms joined by two-sided lines
+with uniformly drawn heights, lights, textures, palette and sprite patches.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+import numpy as np
+
+# Sizes of the fixed id tables the sprite stage indexes (reference defaults:
+# src/gradoom/engine.py:922-1083).
+ENEMY_TYPES = 6
+HUD_PATCHES = 70
+WEAPON_TABLE_TICS = 52
+
+
+@dataclass(frozen=True)
+class Scene:
+    # geometry ----------------------------------------------------------
+    walls: np.ndarray            # (W,4) f32  x1,y1,x2,y2
+    wall_sectors: np.ndarray     # (W,2) i32  front, back (-1 = one sided)
+    side_textures: np.ndarray    # (W,2,3) i32 (middle, bottom, top), -1 none
+    side_offsets: np.ndarray     # (W,2,2) f32 (x, y) texel offsets
+    sector_edge_mask: np.ndarray  # (S,W) bool walls bounding each sector
+    sector_heights: np.ndarray   # (S,2) f32 floor, ceiling
+    sector_lights: np.ndarray    # (S,) i16
+    sector_floor_tex: np.ndarray  # (S,) i32
+    sector_ceil_tex: np.ndarray  # (S,) i32
+    player_starts: np.ndarray    # (P,3) f32 x,y,angle_deg; last row = player
+    # textures ----------------------------------------------------------
+    tex_atlas: np.ndarray        # (T,Hmax,Wmax) u8 palette indices
+    tex_widths: np.ndarray       # (T,) i32 (powers of two)
+    tex_heights: np.ndarray      # (T,) i32 (powers of two)
+    playpal: np.ndarray          # (256,3) u8
+    colormap: np.ndarray         # (34,256) u8
+    # sprites -----------------------------------------------------------
+    spr_atlas: np.ndarray        # (P,h,w) u8 palette indices
+    spr_opaque: np.ndarray       # (P,h,w) bool
+    spr_widths: np.ndarray       # (P,) i32
+    spr_heights: np.ndarray      # (P,) i32
+    spr_left: np.ndarray         # (P,) i32
+    spr_top: np.ndarray          # (P,) i32
+    enemy_walk_ids: np.ndarray   # (6,4,8) i32
+    enemy_attack_ids: np.ndarray  # (6,4,8) i32
+    enemy_pain_ids: np.ndarray   # (6,8) i32
+    enemy_death_ids: np.ndarray  # (6,F) i32
+    enemy_death_counts: np.ndarray     # (6,) i32
+    enemy_death_durations: np.ndarray  # (6,F) i32
+    enemy_xdeath_ids: np.ndarray
+    enemy_xdeath_counts: np.ndarray
+    enemy_xdeath_durations: np.ndarray
+    proj_flight_ids: np.ndarray  # (3,2,8) i32
+    proj_explosion_ids: np.ndarray  # (3,5) i32
+    proj_explosion_counts: np.ndarray  # (3,) i32
+    proj_explosion_durations: np.ndarray  # (3,5) i32
+    fog_ids: np.ndarray          # (12,) i32
+    puff_ids: np.ndarray         # (4,) i32
+    static_ids: np.ndarray       # (20,) i32
+    additive_luts: np.ndarray    # (2,256,256) u8 [style][dst][src]
+    translucent_lut: np.ndarray  # (256,256) u8 [dst][src]
+    # weapon (psprite) --------------------------------------------------
+    wpn_atlas: np.ndarray        # (Q,h,w) u8
+    wpn_opaque: np.ndarray       # (Q,h,w) bool
+    wpn_widths: np.ndarray
+    wpn_heights: np.ndarray
+    wpn_left: np.ndarray
+    wpn_top: np.ndarray
+    wpn_frame_ids: np.ndarray    # (8,2,52) i32
+    wpn_flash_ids: np.ndarray    # (8,2,52) i32 (-1 none)
+    wpn_flash_lights: np.ndarray  # (8,2,52) i32
+    # status bar --------------------------------------------------------
+    hud_atlas: np.ndarray        # (70,32,320) u8
+    hud_opaque: np.ndarray       # (70,32,320) bool
+    hud_widths: np.ndarray
+    hud_heights: np.ndarray
+    hud_left: np.ndarray
+    hud_top: np.ndarray
+    meta: dict = field(default_factory=dict)
+
+    @property
+    def num_walls(self) -> int:
+        return int(self.walls.shape[0])
+
+    @property
+    def num_sectors(self) -> int:
+        return int(self.sector_heights.shape[0])
+
+
+@dataclass(frozen=True)
+class GridSpec:
+    """Parameters of one seeded grid map (the synthetic-WAD stand-in)."""
+
+    rows: int = 4
+    cols: int = 4
+    room: float = 256.0
+    seed: int = 1
+    wall_textures: int = 8
+    tex_w: int = 64
+    tex_h: int = 128
+    flats: int = 4
+    floor_max: int = 64          # floors uniform in {0, 8, ..., floor_max}
+    ceil_lo: int = 128
+    ceil_hi: int = 256           # ceilings uniform in {ceil_lo, +8, ..., ceil_hi}
+    light_lo: int = 96
+    light_hi: int = 255          # lights uniform in {96, 112, ..., <=255}
+    diagonals: bool = False      # one self-referencing diagonal line per room
+    sprite_patches: int = 96
+    spr_w: int = 41
+    spr_h: int = 57
+    dolls: int = 1
+    hud: bool = True
+    weapon: bool = True
+
+
+# The five workloads of the benchmark definition, by name.
+GRID_CONFIGS = {
+    "c1": GridSpec(rows=4, cols=4, room=256.0, seed=1, wall_textures=8, flats=4,
+                   floor_max=64),
+    "c2": GridSpec(rows=8, cols=8, room=256.0, seed=2, wall_textures=16, flats=8,
+                   floor_max=128),
+    "c3": GridSpec(rows=4, cols=8, room=256.0, seed=3, wall_textures=16, flats=8,
+                   floor_max=128),
+    "c4": GridSpec(rows=16, cols=16, room=128.0, seed=4, wall_textures=64,
+                   tex_w=128, tex_h=128, flats=8, floor_max=128, diagonals=True),
+}
+
+
+def _sprite_patches(rng, count, w, h):
+    atlas = rng.integers(1, 256, size=(count, h, w), dtype=np.uint8)
+    yy, xx = np.mgrid[0:h, 0:w]
+    for i in range(count):
+        cx = (w - 1) / 2 + rng.uniform(-3, 3)
+        cy = (h - 1) / 2 + rng.uniform(-3, 3)
+        rx = w / 2 * rng.uniform(0.6, 1.0)
+        ry = h / 2 * rng.uniform(0.7, 1.0)
+        outside = ((xx - cx) / rx) ** 2 + ((yy - cy) / ry) ** 2 > 1.0
+        holes = rng.random((h, w)) < 0.04
+        atlas[i][outside | holes] = 0
+    return atlas, atlas != 0
+
+
+def make_grid_scene(spec: GridSpec) -> Scene:
+    rng = np.random.default_rng(spec.seed)
+    R, C, room = spec.rows, spec.cols, np.float32(spec.room)
+    S = R * C
+
+    def sid(r, c):
+        return r * C + c
+
+    walls, sectors, one_sided = [], [], []
+
+    def add(x1, y1, x2, y2, front, back):
+        # ``front`` must be on the right of (x1,y1)->(x2,y2); flip at random so
+        # both linedef orientations occur.
+        if back >= 0 and rng.random() < 0.5:
+            x1, y1, x2, y2, front, back = x2, y2, x1, y1, back, front
+        walls.append((x1, y1, x2, y2))
+        sectors.append((front, back))
+        one_sided.append(back < 0)
+
+    for r in range(R):
+        for c in range(C):
+            x0, y0 = c * room, r * room
+            x1, y1 = x0 + room, y0 + room
+            s = sid(r, c)
+            if r == 0:
+                add(x1, y0, x0, y0, s, -1)       # bottom edge, room above it
+            if r == R - 1:
+                add(x0, y1, x1, y1, s, -1)       # top edge
+            if c == 0:
+                add(x0, y0, x0, y1, s, -1)       # left edge
+            if c == C - 1:
+                add(x1, y1, x1, y0, s, -1)       # right edge
+            if c + 1 < C:                          # shared vertical edge
+                add(x1, y0, x1, y1, sid(r, c + 1), s)
+            if r + 1 < R:                          # shared horizontal edge
+                add(x0, y1, x1, y1, s, sid(r + 1, c))
+    if spec.diagonals:
+        for r in range(R):
+            for c in range(C):
+                x0, y0 = c * room, r * room
+                x1, y1 = x0 + room, y0 + room
+                s = sid(r, c)
+                if rng.random() < 0.5:
+                    walls.append((x0, y0, x1, y1))
+                else:
+                    walls.append((x0, y1, x1, y0))
+                sectors.append((s, s))
+                one_sided.append(False)
+
+    walls = np.asarray(walls, dtype=np.float32)
+    wall_sectors = np.asarray(sectors, dtype=np.int32)
+    W = len(walls)
+    self_ref = wall_sectors[:, 0] == wall_sectors[:, 1]
+
+    T = spec.wall_textures
+    F = spec.flats
+    hmax = max(spec.tex_h, 64)
+    wmax = max(spec.tex_w, 64)
+    tex_atlas = np.zeros((T + F, hmax, wmax), dtype=np.uint8)
+    tex_atlas[:T, : spec.tex_h, : spec.tex_w] = rng.integers(
+        0, 256, size=(T, spec.tex_h, spec.tex_w), dtype=np.uint8)
+    tex_atlas[T:, :64, :64] = rng.integers(0, 256, size=(F, 64, 64), dtype=np.uint8)
+    tex_widths = np.asarray([spec.tex_w] * T + [64] * F, dtype=np.int32)
+    tex_heights = np.asarray([spec.tex_h] * T + [64] * F, dtype=np.int32)
+
+    side_textures = np.full((W, 2, 3), -1, dtype=np.int32)
+    side_offsets = np.zeros((W, 2, 2), dtype=np.float32)
+    for w in range(W):
+        if self_ref[w]:
+            continue
+        if wall_sectors[w, 1] < 0:
+            side_textures[w, 0, 0] = rng.integers(0, T)
+        else:
+            side_textures[w, :, 1] = rng.integers(0, T, size=2)
+            side_textures[w, :, 2] = rng.integers(0, T, size=2)
+        side_offsets[w] = rng.integers(0, 64, size=(2, 2)).astype(np.float32)
+
+    sector_heights = np.stack(
+        (
+            rng.integers(0, spec.floor_max // 8 + 1, size=S) * 8,
+            spec.ceil_lo + rng.integers(0, (spec.ceil_hi - spec.ceil_lo) // 8 + 1, size=S) * 8,
+        ),
+        axis=1,
+    ).astype(np.float32)
+    light_steps = (spec.light_hi - spec.light_lo) // 16 + 1
+    sector_lights = (spec.light_lo + rng.integers(0, light_steps, size=S) * 16).astype(np.int16)
+    sector_floor_tex = (T + rng.integers(0, F, size=S)).astype(np.int32)
+    sector_ceil_tex = (T + rng.integers(0, F, size=S)).astype(np.int32)
+
+    sector_edge_mask = np.zeros((S, W), dtype=np.bool_)
+    for w in range(W):
+        if self_ref[w]:
+            continue
+        for s in wall_sectors[w]:
+            if s >= 0:
+                sector_edge_mask[s, w] = True
+
+    starts = np.zeros((spec.dolls + 1, 3), dtype=np.float32)
+    starts[:, 0] = rng.uniform(32, C * spec.room - 32, size=spec.dolls + 1).round()
+    starts[:, 1] = rng.uniform(32, R * spec.room - 32, size=spec.dolls + 1).round()
+    starts[:, 2] = rng.integers(0, 8, size=spec.dolls + 1) * 45.0
+
+    playpal = rng.integers(0, 256, size=(256, 3), dtype=np.uint8)
+    idx = np.arange(256, dtype=np.int64)
+    colormap = np.zeros((34, 256), dtype=np.uint8)
+    for row in range(32):
+        colormap[row] = (idx * (32 - row) // 32).astype(np.uint8)
+    colormap[32] = (255 - idx).astype(np.uint8)
+    colormap[33] = 0
+
+    P = spec.sprite_patches
+    spr_atlas, spr_opaque = _sprite_patches(rng, P, spec.spr_w, spec.spr_h)
+    spr_widths = np.full(P, spec.spr_w, dtype=np.int32)
+    spr_heights = np.full(P, spec.spr_h, dtype=np.int32)
+    spr_left = (spec.spr_w // 2 + rng.integers(-2, 3, size=P)).astype(np.int32)
+    spr_top = (spec.spr_h + rng.integers(-3, 1, size=P)).astype(np.int32)
+
+    def ids(*shape):
+        return rng.integers(0, P, size=shape).astype(np.int32)
+
+    death_frames = 5
+    additive = rng.integers(0, 256, size=(2, 256, 256), dtype=np.uint8)
+    translucent = rng.integers(0, 256, size=(256, 256), dtype=np.uint8)
+
+    if spec.weapon:
+        Q, wh, ww = 12, 64, 96
+        wpn_atlas = rng.integers(1, 256, size=(Q, wh, ww), dtype=np.uint8)
+        holes = rng.random((Q, wh, ww)) < 0.1
+        wpn_atlas[holes] = 0
+        wpn_opaque = wpn_atlas != 0
+        wpn_widths = rng.integers(48, ww + 1, size=Q).astype(np.int32)
+        wpn_heights = rng.integers(40, wh + 1, size=Q).astype(np.int32)
+        wpn_left = rng.integers(-160, -100, size=Q).astype(np.int32)
+        wpn_top = rng.integers(-140, -100, size=Q).astype(np.int32)
+        wpn_frame_ids = rng.integers(0, Q, size=(8, 2, WEAPON_TABLE_TICS)).astype(np.int32)
+        wpn_flash_ids = rng.integers(-1, Q, size=(8, 2, WEAPON_TABLE_TICS)).astype(np.int32)
+        wpn_flash_ids[:, :, 0] = -1
+        wpn_flash_lights = np.zeros((8, 2, WEAPON_TABLE_TICS), dtype=np.int32)
+    else:
+        Q = 8
+        wpn_atlas = np.zeros((Q, 1, 1), dtype=np.uint8)
+        wpn_opaque = np.zeros((Q, 1, 1), dtype=np.bool_)
+        wpn_widths = np.zeros(Q, dtype=np.int32)
+        wpn_heights = np.zeros(Q, dtype=np.int32)
+        wpn_left = np.zeros(Q, dtype=np.int32)
+        wpn_top = np.zeros(Q, dtype=np.int32)
+        wpn_frame_ids = np.broadcast_to(
+            np.arange(8, dtype=np.int32)[:, None, None], (8, 2, WEAPON_TABLE_TICS)).copy()
+        wpn_flash_ids = np.full((8, 2, WEAPON_TABLE_TICS), -1, dtype=np.int32)
+        wpn_flash_lights = np.zeros((8, 2, WEAPON_TABLE_TICS), dtype=np.int32)
+
+    hud_atlas = np.zeros((HUD_PATCHES, 32, 320), dtype=np.uint8)
+    hud_opaque = np.zeros((HUD_PATCHES, 32, 320), dtype=np.bool_)
+    hud_widths = np.zeros(HUD_PATCHES, dtype=np.int32)
+    hud_heights = np.zeros(HUD_PATCHES, dtype=np.int32)
+    hud_left = np.zeros(HUD_PATCHES, dtype=np.int32)
+    hud_top = np.zeros(HUD_PATCHES, dtype=np.int32)
+    if spec.hud:
+        def patch(i, w, h, hole=0.0, left=0, top=0):
+            data = rng.integers(0, 256, size=(h, w), dtype=np.uint8)
+            hud_atlas[i, :h, :w] = data
+            opaque = np.ones((h, w), dtype=np.bool_)
+            if hole > 0:
+                opaque &= rng.random((h, w)) >= hole
+            hud_opaque[i, :h, :w] = opaque
+            hud_widths[i], hud_heights[i] = w, h
+            hud_left[i], hud_top[i] = left, top
+
+        patch(0, 320, 32)                       # status bar
+        patch(1, 40, 32, hole=0.1)              # arms panel
+        for d in range(10):
+            patch(2 + d, 14, 16, hole=0.3)      # large numerals
+        patch(12, 14, 16, hole=0.3)             # percent sign
+        for i in range(13, 28):
+            patch(i, 24, 29, hole=0.1, left=-5, top=-2)   # straight faces
+        for d in range(10):
+            patch(28 + d, 4, 6, hole=0.2)       # small yellow numerals
+        for i in range(38, 44):
+            patch(i, 4, 6, hole=0.2)            # grey arms numerals
+        for i in range(44, 70):
+            patch(i, 24, 29, hole=0.1, left=-5, top=-2)   # other faces
+
+    return Scene(
+        walls=walls,
+        wall_sectors=wall_sectors,
+        side_textures=side_textures,
+        side_offsets=side_offsets,
+        sector_edge_mask=sector_edge_mask,
+        sector_heights=sector_heights,
+        sector_lights=sector_lights,
+        sector_floor_tex=sector_floor_tex,
+        sector_ceil_tex=sector_ceil_tex,
+        player_starts=starts,
+        tex_atlas=tex_atlas,
+        tex_widths=tex_widths,
+        tex_heights=tex_heights,
+        playpal=playpal,
+        colormap=colormap,
+        spr_atlas=spr_atlas,
+        spr_opaque=spr_opaque,
+        spr_widths=spr_widths,
+        spr_heights=spr_heights,
+        spr_left=spr_left,
+        spr_top=spr_top,
+        enemy_walk_ids=ids(6, 4, 8),
+        enemy_attack_ids=ids(6, 4, 8),
+        enemy_pain_ids=ids(6, 8),
+        enemy_death_ids=ids(6, death_frames),
+        enemy_death_counts=np.full(6, death_frames, dtype=np.int32),
+        enemy_death_durations=rng.integers(3, 9, size=(6, death_frames)).astype(np.int32),
+        enemy_xdeath_ids=ids(6, death_frames),
+        enemy_xdeath_counts=np.full(6, death_frames, dtype=np.int32),
+        enemy_xdeath_durations=rng.integers(3, 9, size=(6, death_frames)).astype(np.int32),
+        proj_flight_ids=ids(3, 2, 8),
+        proj_explosion_ids=ids(3, 5),
+        proj_explosion_counts=np.asarray((3, 5, 3), dtype=np.int32),
+        proj_explosion_durations=np.asarray(
+            ((8, 6, 4, 0, 0), (4, 4, 4, 4, 4), (6, 6, 6, 0, 0)), dtype=np.int32),
+        fog_ids=ids(12),
+        puff_ids=ids(4),
+        static_ids=ids(20),
+        additive_luts=additive,
+        translucent_lut=translucent,
+        wpn_atlas=wpn_atlas,
+        wpn_opaque=wpn_opaque,
+        wpn_widths=wpn_widths,
+        wpn_heights=wpn_heights,
+        wpn_left=wpn_left,
+        wpn_top=wpn_top,
+        wpn_frame_ids=wpn_frame_ids,
+        wpn_flash_ids=wpn_flash_ids,
+        wpn_flash_lights=wpn_flash_lights,
+        hud_atlas=hud_atlas,
+        hud_opaque=hud_opaque,
+        hud_widths=hud_widths,
+        hud_heights=hud_heights,
+        hud_left=hud_left,
+        hud_top=hud_top,
+        meta={"spec": spec},
+    )
+
+
+# ---------------------------------------------------------------------------
+# Packing a Scene into the device blob (layout: include/gradoom_b200_layout.h)
+# ---------------------------------------------------------------------------
+
+GD_MAGIC = 0x4744424C
+GD_VERSION = 3
+GD_HDR_WORDS = 128
+GD_HDR_SECTION0 = 48
+
+_HEADER_WORDS = (
+    "MAGIC VERSION BYTES WALLS SECTORS VERTICES TEXTURES TEX_H TEX_W SPRITES SPR_H SPR_W "
+    "WPN_PATCHES WPN_H WPN_W WPN_TICS STARTS DEATH_FRAMES XDEATH_FRAMES BLOCKING NB_DIRECT "
+    "WPN_AVAILABLE HUD_PATCHES UNSUPPORTED"
+).split()
+H = {name: i for i, name in enumerate(_HEADER_WORDS)}
+
+_SECTIONS = (
+    "WALLS WALL_SECTORS WALL_LEN SIDE_TEX SIDE_OFF WALL_VTX VTX_OFF VTX_WALLS NB_DIRECT NB_OFF "
+    "NB_IDX NB_FLAGS SB_START_OFF SB_START_IDX SB_END_OFF SB_END_IDX SECTOR_F SECTOR_I SEC_OFF "
+    "SEC_WALLS EDGE_OFF EDGE_WALLS BLOCKING TEX_INFO TEX_ATLAS PLAYPAL COLORMAP SPR_INFO "
+    "SPR_ATLAS SPR_POST ENEMY_WALK ENEMY_ATTACK ENEMY_PAIN DEATH_IDS DEATH_COUNTS DEATH_ENDS "
+    "XDEATH_IDS XDEATH_COUNTS XDEATH_ENDS PROJ_FLIGHT PROJ_EXPL_IDS PROJ_EXPL_COUNTS "
+    "PROJ_EXPL_ENDS PROJ_EXPL_TOTAL FOG_IDS PUFF_IDS STATIC_IDS ADD_LUT TRANS_LUT WPN_INFO "
+    "WPN_ATLAS WPN_OPAQUE WPN_FRAME_IDS WPN_FLASH_IDS WPN_FLASH_LIGHTS HUD_INFO HUD_ATLAS "
+    "HUD_OPAQUE FINESINE FINETAN STARTS RAY_OFFSETS RAY_COSCORR"
+).split()
+SEC = {name: i for i, name in enumerate(_SECTIONS)}
+
+FIXED_UNIT = 1 << 16
+FINE_ANGLES = 8192
+
+
+def fine_sine_table() -> np.ndarray:
+    """16.16 sine table of 8192 fine angles (definition:
+    src/gradoom/engine.py:309-320): first quadrant truncated, mirrored, negated,
+    with the two extrema forced to +-1.0."""
+
+    q = FINE_ANGLES // 4
+    first = np.trunc(np.sin(np.arange(q, dtype=np.float64) * (2.0 * np.pi / FINE_ANGLES))
+                     * FIXED_UNIT).astype(np.int64)
+    table = np.concatenate((first, first[::-1]))
+    table = np.concatenate((table, -table))
+    table[q] = FIXED_UNIT
+    table[3 * q] = -FIXED_UNIT
+    return table.astype(np.int32)
+
+
+def fine_tangent_table() -> np.ndarray:
+    """16.16 tangent table of 4096 entries (src/gradoom/engine.py:323-328)."""
+
+    half = FINE_ANGLES // 2
+    phase = (np.arange(half, dtype=np.float64) - FINE_ANGLES // 4) * (2.0 * np.pi / FINE_ANGLES)
+    phase[0] += np.pi / FINE_ANGLES
+    return np.trunc(np.tan(phase) * FIXED_UNIT + 0.5).astype(np.int64).astype(np.int32)
+
+
+def sector_at(scene: Scene, x: np.ndarray, y: np.ndarray) -> np.ndarray:
+    """First sector whose edge set has odd crossing parity for a +x ray, else 0.
+
+    float32 arithmetic in the reference's order (src/gradoom/engine.py:9598-9617).
+    """
+
+    x = np.asarray(x, dtype=np.float32).reshape(-1)
+    y = np.asarray(y, dtype=np.float32).reshape(-1)
+    e = scene.walls.astype(np.float32)
+    x1, y1, x2, y2 = e[:, 0], e[:, 1], e[:, 2], e[:, 3]
+    px, py = x[:, None], y[:, None]
+    crosses = (y1 > py) != (y2 > py)
+    dy = y2 - y1
+    safe = np.where(np.abs(dy) < np.float32(1e-6), np.float32(1), dy).astype(np.float32)
+    crossing = (x1 + ((py - y1) * (x2 - x1)).astype(np.float32) / safe).astype(np.float32)
+    hit = crosses & (px < crossing)
+    parity = (hit[:, None, :] & scene.sector_edge_mask[None, :, :]).sum(axis=2) % 2
+    return np.argmax(parity, axis=1).astype(np.int64)
+
+
+def _csr(lists):
+    off = np.zeros(len(lists) + 1, dtype=np.int32)
+    for i, l in enumerate(lists):
+        off[i + 1] = off[i] + len(l)
+    idx = np.asarray([v for l in lists for v in l], dtype=np.int32)
+    if idx.size == 0:
+        idx = np.zeros(1, dtype=np.int32)
+    return off, idx
+
+
+def ray_tables():
+    """Per-column ray angle offsets of the flat fallback and their cosines, in
+    float32 as the host framework evaluates them
+    (src/gradoom/engine.py:2050-2054, 10967)."""
+
+    import torch
+
+    columns = torch.arange(320, dtype=torch.float32) - 320 / 2.0
+    offsets = -torch.atan(columns / (320 / 2.0))
+    return offsets.numpy().copy(), torch.cos(offsets).numpy().copy()
+
+
+def pack_scene(scene: Scene, ray_table_override=None) -> np.ndarray:
+    """Serialise a Scene plus its static topology tables into one byte blob.
+
+    ``ray_table_override`` supplies ``(offsets, cosines)`` recorded elsewhere, so
+    a fixture generated on one machine replays bit-identically on another.
+    """
+
+    import torch  # deg2rad in float32 exactly as the host framework computes it
+
+    walls = np.ascontiguousarray(scene.walls, dtype=np.float32) + np.float32(0.0)
+    sectors = np.ascontiguousarray(scene.wall_sectors, dtype=np.int32)
+    W, S = len(walls), scene.num_sectors
+    one_sided = sectors[:, 1] < 0
+    unsupported = 0
+    if np.any((~one_sided) & (scene.side_textures[:, :, 0].max(axis=1) >= 0)):
+        unsupported |= 1  # two-sided middle (masked) textures are not drawn
+
+    dx = walls[:, 2] - walls[:, 0]
+    dy = walls[:, 3] - walls[:, 1]
+    wall_len = np.floor(np.sqrt(np.square(dx) + np.square(dy)) + np.float32(0.5)).astype(np.float32)
+
+    pts = walls.reshape(-1, 2)
+    verts, inverse = np.unique(pts, axis=0, return_inverse=True)
+    wall_vtx = inverse.reshape(W, 2).astype(np.int32)
+    V = len(verts)
+    vtx_lists = [[] for _ in range(V)]
+    for w in range(W):
+        for e in range(2):
+            if w not in vtx_lists[wall_vtx[w, e]]:
+                vtx_lists[wall_vtx[w, e]].append(w)
+    vtx_off, vtx_walls = _csr(vtx_lists)
+
+    same_pair = ((sectors[:, None, 0] == sectors[None, :, 0]) & (sectors[:, None, 1] == sectors[None, :, 1])) | (
+        (sectors[:, None, 0] == sectors[None, :, 1]) & (sectors[:, None, 1] == sectors[None, :, 0]))
+    v0, v1 = wall_vtx[:, 0], wall_vtx[:, 1]
+    shares_start = (v0[:, None] == v0[None, :]) | (v0[:, None] == v1[None, :])
+    shares_end = (v1[:, None] == v0[None, :]) | (v1[:, None] == v1[None, :])
+    eye = np.eye(W, dtype=np.bool_)
+    nb_mask = same_pair & (shares_start | shares_end) & ~eye
+    nb_lists, nb_flag_lists = [], []
+    for w in range(W):
+        idx = np.flatnonzero(nb_mask[w])
+        nb_lists.append(idx.tolist())
+        nb_flag_lists.append((shares_start[w, idx].astype(np.int32)
+                              + 2 * shares_end[w, idx].astype(np.int32)).tolist())
+    nb_off, nb_idx = _csr(nb_lists)
+    _, nb_flags = _csr(nb_flag_lists)
+    start_counts = np.asarray([sum(f & 1 for f in fl) for fl in nb_flag_lists])
+    end_counts = np.asarray([sum((f >> 1) & 1 for f in fl) for fl in nb_flag_lists])
+    nb_direct_ok = int(np.all(start_counts <= 1) and np.all(end_counts <= 1))
+    nb_direct = np.full((W, 4), -1, dtype=np.int32)
+    nb_direct[:, 2:] = 0
+    for w in range(W):
+        # slot of the first neighbour sharing the start / the end (0 when none),
+        # and the neighbour stored in that slot (the wall itself when the list is empty).
+        fl = nb_flag_lists[w]
+        s_slot = next((k for k, f in enumerate(fl) if f & 1), 0)
+        e_slot = next((k for k, f in enumerate(fl) if f & 2), 0)
+        nb_direct[w, 2], nb_direct[w, 3] = s_slot, e_slot
+        nb_direct[w, 0] = nb_lists[w][s_slot] if start_counts[w] > 0 else -1
+        nb_direct[w, 1] = nb_lists[w][e_slot] if end_counts[w] > 0 else -1
+
+    same_solid = sectors[:, None, 0] == sectors[None, :, 0]
+    adjacency = (shares_start | shares_end) & one_sided[:, None] & one_sided[None, :] & same_solid & ~eye
+    sel_solid = (sectors[:, None, 0] == sectors[None, :, 0]) | (sectors[:, None, 1] == sectors[None, :, 0])
+    sb_start = ((shares_start & one_sided[None, :] & sel_solid).astype(np.int32) @ adjacency.astype(np.int32)) > 0
+    sb_end = ((shares_end & one_sided[None, :] & sel_solid).astype(np.int32) @ adjacency.astype(np.int32)) > 0
+    sb_start_off, sb_start_idx = _csr([np.flatnonzero(sb_start[w]).tolist() for w in range(W)])
+    sb_end_off, sb_end_idx = _csr([np.flatnonzero(sb_end[w]).tolist() for w in range(W)])
+
+    sec_lists = [np.flatnonzero((sectors[:, 0] == s) | (sectors[:, 1] == s)).tolist() for s in range(S)]
+    sec_off, sec_walls = _csr(sec_lists)
+    edge_off, edge_walls = _csr([np.flatnonzero(scene.sector_edge_mask[s]).tolist() for s in range(S)])
+    blocking = np.flatnonzero(one_sided).astype(np.int32)
+    if blocking.size == 0:
+        blocking = np.zeros(1, dtype=np.int32)
+        unsupported |= 2
+
+    T = len(scene.tex_atlas)
+    tex_info = np.zeros((T, 4), dtype=np.int32)
+    tex_info[:, 0] = scene.tex_widths
+    tex_info[:, 1] = scene.tex_heights
+    tex_info[:, 2] = np.floor(np.log2(scene.tex_widths.astype(np.float32))).astype(np.int32)
+    tex_info[:, 3] = np.floor(np.log2(scene.tex_heights.astype(np.float32))).astype(np.int32)
+
+    P = len(scene.spr_atlas)
+    spr_info = np.stack((scene.spr_widths, scene.spr_heights, scene.spr_left, scene.spr_top),
+                        axis=1).astype(np.int32)
+    opaque = scene.spr_opaque.astype(np.bool_)
+    prior = np.concatenate((np.zeros_like(opaque[:, :1]), opaque[:, :-1]), axis=1)
+    starts_post = opaque & ~prior
+    rows = np.arange(opaque.shape[1], dtype=np.int64)[None, :, None]
+    post_top = np.maximum.accumulate(np.where(starts_post, rows, 0), axis=1)
+    if opaque.shape[1] >= 255:
+        unsupported |= 4
+    spr_post = np.where(opaque, post_top, 255).astype(np.uint8)
+
+    def ends(durations):
+        return np.cumsum(durations.astype(np.int64), axis=-1).astype(np.int32)
+
+    start_sectors = sector_at(scene, scene.player_starts[:, 0], scene.player_starts[:, 1])
+    starts = np.zeros((len(scene.player_starts), 4), dtype=np.float32)
+    starts[:, 0:2] = scene.player_starts[:, 0:2]
+    starts[:, 2] = torch.deg2rad(torch.as_tensor(scene.player_starts[:, 2].astype(np.float32))).numpy()
+    starts[:, 3] = scene.sector_heights[start_sectors, 0]
+
+    ray_offsets, ray_coscorr = ray_tables() if ray_table_override is None else ray_table_override
+    sector_i = np.zeros((S, 4), dtype=np.int32)
+    sector_i[:, 0] = scene.sector_lights
+    sector_i[:, 1] = scene.sector_floor_tex
+    sector_i[:, 2] = scene.sector_ceil_tex
+
+    def info4(a, b, c, d):
+        return np.stack((a, b, c, d), axis=1).astype(np.int32)
+
+    sections = {
+        "WALLS": walls,
+        "WALL_SECTORS": sectors,
+        "WALL_LEN": wall_len,
+        "SIDE_TEX": scene.side_textures.astype(np.int32),
+        "SIDE_OFF": scene.side_offsets.astype(np.float32),
+        "WALL_VTX": wall_vtx,
+        "VTX_OFF": vtx_off,
+        "VTX_WALLS": vtx_walls,
+        "NB_DIRECT": nb_direct,
+        "NB_OFF": nb_off,
+        "NB_IDX": nb_idx,
+        "NB_FLAGS": nb_flags,
+        "SB_START_OFF": sb_start_off,
+        "SB_START_IDX": sb_start_idx,
+        "SB_END_OFF": sb_end_off,
+        "SB_END_IDX": sb_end_idx,
+        "SECTOR_F": scene.sector_heights.astype(np.float32),
+        "SECTOR_I": sector_i,
+        "SEC_OFF": sec_off,
+        "SEC_WALLS": sec_walls,
+        "EDGE_OFF": edge_off,
+        "EDGE_WALLS": edge_walls,
+        "BLOCKING": blocking,
+        "TEX_INFO": tex_info,
+        "TEX_ATLAS": scene.tex_atlas.astype(np.uint8),
+        "PLAYPAL": scene.playpal.astype(np.uint8),
+        "COLORMAP": scene.colormap.astype(np.uint8),
+        "SPR_INFO": spr_info,
+        "SPR_ATLAS": scene.spr_atlas.astype(np.uint8),
+        "SPR_POST": spr_post,
+        "ENEMY_WALK": scene.enemy_walk_ids.astype(np.int32),
+        "ENEMY_ATTACK": scene.enemy_attack_ids.astype(np.int32),
+        "ENEMY_PAIN": scene.enemy_pain_ids.astype(np.int32),
+        "DEATH_IDS": scene.enemy_death_ids.astype(np.int32),
+        "DEATH_COUNTS": scene.enemy_death_counts.astype(np.int32),
+        "DEATH_ENDS": ends(scene.enemy_death_durations),
+        "XDEATH_IDS": scene.enemy_xdeath_ids.astype(np.int32),
+        "XDEATH_COUNTS": scene.enemy_xdeath_counts.astype(np.int32),
+        "XDEATH_ENDS": ends(scene.enemy_xdeath_durations),
+        "PROJ_FLIGHT": scene.proj_flight_ids.astype(np.int32),
+        "PROJ_EXPL_IDS": scene.proj_explosion_ids.astype(np.int32),
+        "PROJ_EXPL_COUNTS": scene.proj_explosion_counts.astype(np.int32),
+        "PROJ_EXPL_ENDS": ends(scene.proj_explosion_durations),
+        "PROJ_EXPL_TOTAL": scene.proj_explosion_durations.sum(axis=1).astype(np.int32),
+        "FOG_IDS": scene.fog_ids.astype(np.int32),
+        "PUFF_IDS": scene.puff_ids.astype(np.int32),
+        "STATIC_IDS": scene.static_ids.astype(np.int32),
+        "ADD_LUT": scene.additive_luts.astype(np.uint8),
+        "TRANS_LUT": scene.translucent_lut.astype(np.uint8),
+        "WPN_INFO": info4(scene.wpn_widths, scene.wpn_heights, scene.wpn_left, scene.wpn_top),
+        "WPN_ATLAS": scene.wpn_atlas.astype(np.uint8),
+        "WPN_OPAQUE": scene.wpn_opaque.astype(np.uint8),
+        "WPN_FRAME_IDS": scene.wpn_frame_ids.astype(np.int32),
+        "WPN_FLASH_IDS": scene.wpn_flash_ids.astype(np.int32),
+        "WPN_FLASH_LIGHTS": scene.wpn_flash_lights.astype(np.int32),
+        "HUD_INFO": info4(scene.hud_widths, scene.hud_heights, scene.hud_left, scene.hud_top),
+        "HUD_ATLAS": scene.hud_atlas.astype(np.uint8),
+        "HUD_OPAQUE": scene.hud_opaque.astype(np.uint8),
+        "FINESINE": fine_sine_table(),
+        "FINETAN": fine_tangent_table(),
+        "STARTS": starts,
+        "RAY_OFFSETS": np.asarray(ray_offsets, dtype=np.float32),
+        "RAY_COSCORR": np.asarray(ray_coscorr, dtype=np.float32),
+    }
+    assert set(sections) == set(SEC), set(SEC) ^ set(sections)
+
+    header = np.zeros(GD_HDR_WORDS, dtype=np.int32)
+    chunks = []
+    cursor = GD_HDR_WORDS * 4
+    for name in _SECTIONS:
+        data = np.ascontiguousarray(sections[name]).view(np.uint8).reshape(-1)
+        pad = (-cursor) % 16
+        if pad:
+            chunks.append(np.zeros(pad, dtype=np.uint8))
+            cursor += pad
+        header[GD_HDR_SECTION0 + SEC[name]] = cursor
+        chunks.append(data)
+        cursor += data.size
+    pad = (-cursor) % 16
+    if pad:
+        chunks.append(np.zeros(pad, dtype=np.uint8))
+        cursor += pad
+
+    header[H["MAGIC"]] = GD_MAGIC
+    header[H["VERSION"]] = GD_VERSION
+    header[H["BYTES"]] = cursor
+    header[H["WALLS"]] = W
+    header[H["SECTORS"]] = S
+    header[H["VERTICES"]] = V
+    header[H["TEXTURES"]] = T
+    header[H["TEX_H"]] = scene.tex_atlas.shape[1]
+    header[H["TEX_W"]] = scene.tex_atlas.shape[2]
+    header[H["SPRITES"]] = P
+    header[H["SPR_H"]] = scene.spr_atlas.shape[1]
+    header[H["SPR_W"]] = scene.spr_atlas.shape[2]
+    header[H["WPN_PATCHES"]] = len(scene.wpn_atlas)
+    header[H["WPN_H"]] = scene.wpn_atlas.shape[1]
+    header[H["WPN_W"]] = scene.wpn_atlas.shape[2]
+    header[H["WPN_TICS"]] = scene.wpn_frame_ids.shape[2]
+    header[H["STARTS"]] = len(scene.player_starts)
+    header[H["DEATH_FRAMES"]] = scene.enemy_death_ids.shape[1]
+    header[H["XDEATH_FRAMES"]] = scene.enemy_xdeath_ids.shape[1]
+    header[H["BLOCKING"]] = int(one_sided.sum())
+    header[H["NB_DIRECT"]] = nb_direct_ok
+    header[H["WPN_AVAILABLE"]] = int(scene.wpn_widths.max() > 0)
+    header[H["HUD_PATCHES"]] = len(scene.hud_atlas)
+    header[H["UNSUPPORTED"]] = unsupported
+    blob = np.concatenate([header.view(np.uint8)] + chunks)
+    assert blob.size == cursor
+    return blob

@@ -1,0 +1,110 @@
+"""ctypes wrapper around the CPU oracle (``gd_oracle.c``).
+
+Test infrastructure: imported only by the tests, the smoke check and the
+CPU-baseline leg of the benchmark.  ``build()`` compiles the C file with gcc;
+nothing here is reachable from the product package.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+SOURCE = os.path.join(HERE, "gd_oracle.c")
+LIBRARY = os.path.join(HERE, "_gd_oracle.so")
+
+STAGE_WALLS, STAGE_SPRITES, STAGE_WEAPON, STAGE_HUD = 1, 2, 4, 8
+STAGE_ALL = 15
+
+_lib = None
+
+
+def build(force: bool = False) -> str:
+    stale = (not os.path.exists(LIBRARY)) or os.path.getmtime(LIBRARY) < os.path.getmtime(SOURCE)
+    if force or stale:
+        subprocess.check_call(
+            ["gcc", "-O2", "-ffp-contract=off", "-fno-fast-math", "-fPIC", "-shared",
+             "-o", LIBRARY, SOURCE, "-lm"])
+    return LIBRARY
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        build()
+        _lib = ctypes.CDLL(LIBRARY)
+        _lib.gd_oracle_render.restype = ctypes.c_int
+        _lib.gd_oracle_resize.restype = ctypes.c_int
+        _lib.gd_oracle_rgb.restype = ctypes.c_int
+        _lib.gd_oracle_stack.restype = ctypes.c_int
+    return _lib
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data_as(ctypes.c_void_p)
+
+
+def render(blob, lanes, things, *, mask_hud=True, stage_mask=STAGE_ALL, depth_override=None,
+           want_stages=False):
+    """Render every lane on the CPU.
+
+    Returns a dict with ``indexed (N,240,320) u8``, ``obs (N,84,84) u8``,
+    ``unowned (N,) i32`` and, on request, ``stages (N,3,208,320) u8`` (the view
+    after walls + planes, after sprites, after the weapon).
+    """
+
+    blob = np.ascontiguousarray(blob, dtype=np.uint8)
+    lanes = np.ascontiguousarray(lanes, dtype=np.int32)
+    things = np.ascontiguousarray(things, dtype=np.int32)
+    n = lanes.shape[0]
+    k = things.shape[1]
+    indexed = np.zeros((n, 240, 320), dtype=np.uint8)
+    obs = np.zeros((n, 84, 84), dtype=np.uint8)
+    unowned = np.zeros(n, dtype=np.int32)
+    stages = np.zeros((n, 3, 208, 320), dtype=np.uint8) if want_stages else None
+    if depth_override is not None:
+        depth_override = np.ascontiguousarray(depth_override, dtype=np.float32)
+    rc = lib().gd_oracle_render(_ptr(blob), _ptr(lanes), _ptr(things), ctypes.c_int(k),
+                                _ptr(depth_override), ctypes.c_int(n), ctypes.c_int(int(mask_hud)),
+                                ctypes.c_int(stage_mask), _ptr(indexed), _ptr(obs), _ptr(stages),
+                                _ptr(unowned))
+    if rc != 0:
+        raise RuntimeError(f"oracle rejected the scene blob (code {rc})")
+    out = {"indexed": indexed, "obs": obs, "unowned": unowned}
+    if want_stages:
+        out["stages"] = stages
+    return out
+
+
+def resize(blob, indexed):
+    """Integer 320x{208,240} -> 84x84 area resize + grayscale of indexed frames."""
+
+    blob = np.ascontiguousarray(blob, dtype=np.uint8)
+    indexed = np.ascontiguousarray(indexed, dtype=np.uint8)
+    n, rows = indexed.shape[0], indexed.shape[1]
+    obs = np.zeros((n, 84, 84), dtype=np.uint8)
+    lib().gd_oracle_resize(_ptr(blob), _ptr(indexed), ctypes.c_int(n), ctypes.c_int(rows), _ptr(obs))
+    return obs
+
+
+def rgb(blob, indexed):
+    blob = np.ascontiguousarray(blob, dtype=np.uint8)
+    indexed = np.ascontiguousarray(indexed, dtype=np.uint8)
+    n, rows = indexed.shape[0], indexed.shape[1]
+    out = np.zeros((n, rows, 320, 3), dtype=np.uint8)
+    lib().gd_oracle_rgb(_ptr(blob), _ptr(indexed), ctypes.c_int(n), ctypes.c_int(rows), _ptr(out))
+    return out
+
+
+def stack_update(stack, obs, reset_mask=None):
+    """In-place frame-stack update: roll + append, or fill for reset lanes."""
+
+    assert stack.dtype == np.uint8 and stack.flags.c_contiguous
+    obs = np.ascontiguousarray(obs, dtype=np.uint8)
+    mask = None if reset_mask is None else np.ascontiguousarray(reset_mask, dtype=np.uint8)
+    lib().gd_oracle_stack(_ptr(stack), _ptr(obs), _ptr(mask), ctypes.c_int(stack.shape[0]))
+    return stack
