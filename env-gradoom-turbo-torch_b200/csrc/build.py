@@ -1,0 +1,37 @@
+"""Build recipe of the CUDA library: one nvcc call, sm_100a only, in-tree output."""
+
+from __future__ import annotations
+
+import os
+import subprocess
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+SOURCES = ["gd_render.cu"]
+HEADERS = ["gd_device.cuh", "../../include/gradoom_b200.h", "../../include/gradoom_b200_layout.h"]
+LIBRARY = os.path.join(HERE, "libgradoom_b200.so")
+
+# -fmad=false: the reference rounds every float32 multiply and add separately;
+# a fused multiply-add would change texel and ownership decisions.
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-fmad=false", "-std=c++17",
+    "-Xcompiler", "-fPIC", "-shared",
+]
+
+
+def is_stale() -> bool:
+    if not os.path.exists(LIBRARY):
+        return True
+    built = os.path.getmtime(LIBRARY)
+    return any(os.path.getmtime(os.path.join(HERE, f)) > built for f in SOURCES + HEADERS)
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    if force or is_stale():
+        cmd = ["nvcc", *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-o", LIBRARY,
+               *[os.path.join(HERE, s) for s in SOURCES]]
+        subprocess.check_call(cmd, cwd=HERE)
+    return LIBRARY
+
+
+if __name__ == "__main__":
+    print(build(force=True, verbose=True))

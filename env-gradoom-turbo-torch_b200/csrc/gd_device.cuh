@@ -1,0 +1,113 @@
+/*
+ * Device-side view of the scene blob and small exact-arithmetic helpers shared
+ * by the render kernels.  Everything is integer 16.16 / 20.12 fixed point on
+ * 64-bit integers or separately rounded float32 (the library is compiled with
+ * -fmad=false), because the results must equal the reference's
+ * (src/gradoom/engine.py:10534-15457) bit for bit.
+ */
+#pragma once
+
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include <stdint.h>
+
+#include "../../include/gradoom_b200_layout.h"
+
+typedef long long i64;
+
+#define GD_FU 65536LL
+#define GD_SW GD_SCREEN_W
+#define GD_VH GD_VIEW_H
+#define GD_ANG90 (1LL << 30)
+#define GD_FOCAL_X (160LL * GD_FU)
+#define GD_Y_ASPECT ((320LL * GD_FU * 240LL) / (200LL * 320LL))
+#define GD_FOCAL_Y (160LL * GD_Y_ASPECT)
+#define GD_FLOOR_VIS ((160LL * GD_FU * (8LL * GD_FU)) / GD_FOCAL_Y)
+#define GD_WALL_VIS (((GD_FOCAL_Y * (320LL * 600LL) / (320LL * 240LL * 3LL)) * (8LL * GD_FU)) >> 16)
+#define GD_SPRITE_MIN_DEPTH (2048LL * 4LL)
+#define GD_U32MASK 0xFFFFFFFFLL
+
+/* status bits written to the device status word */
+#define GD_STATUS_EVENT_OVERFLOW 1   /* a column produced more clip events than the scratch holds */
+#define GD_STATUS_THINGS_OVERFLOW 2  /* a lane lists more things than the configured maximum */
+#define GD_STATUS_BAD_SECTOR 4       /* a state record points outside the scene */
+
+struct GdScene {
+  int W, S, T, texH, texW, P, sprH, sprW, Q, wpnH, wpnW, wpnTics, nStarts, B, nbDirect, wpnAvailable;
+  const float *walls;
+  const int32_t *wsec;
+  const float *wlen;
+  const int32_t *sideTex;
+  const float *sideOff;
+  const int32_t *wvtx, *vtxOff, *vtxWalls;
+  const int32_t *nbDirectTab, *nbOff, *nbIdx, *nbFlags;
+  const int32_t *sbStartOff, *sbStartIdx, *sbEndOff, *sbEndIdx;
+  const float *secF;
+  const int32_t *secI;
+  const int32_t *secOff, *secWalls, *edgeOff, *edgeWalls, *blocking;
+  const int32_t *texInfo;
+  const uint8_t *texAtlas, *texAtlasCol, *playpal, *colormap;
+  const int32_t *sprInfo;
+  const uint8_t *sprAtlas, *sprPost;
+  const uint8_t *addLut, *transLut;
+  const int32_t *wpnInfo;
+  const uint8_t *wpnAtlas, *wpnOpaque;
+  const int32_t *wpnFrameIds, *wpnFlashIds, *wpnFlashLights;
+  const int32_t *hudInfo;
+  const uint8_t *hudAtlas, *hudOpaque;
+  const int32_t *fineSine, *fineTan;
+  const float *rayOffsets, *rayCosCorr;
+  const float *secBBox;
+};
+
+__device__ __forceinline__ i64 gd_min(i64 a, i64 b) { return a < b ? a : b; }
+__device__ __forceinline__ i64 gd_max(i64 a, i64 b) { return a > b ? a : b; }
+__device__ __forceinline__ i64 gd_clamp(i64 v, i64 lo, i64 hi) { return v < lo ? lo : (v > hi ? hi : v); }
+__device__ __forceinline__ i64 gd_wmul(i64 a, i64 b) { return (i64)((unsigned long long)a * (unsigned long long)b); }
+__device__ __forceinline__ i64 gd_shl(i64 a, int k) { return (i64)((unsigned long long)a << k); }
+/* float32 -> int64, round half to even */
+__device__ __forceinline__ i64 gd_rint(float v) { return (i64)rintf(v); }
+__device__ __forceinline__ i64 gd_pymod(i64 a, i64 m) {
+  i64 r = a % m;
+  return (r != 0 && ((r < 0) != (m < 0))) ? r + m : r;
+}
+
+/*
+ * Truncating signed 64-bit division.  Most quotients on this path have a
+ * divisor that fits in 32 bits; the generic operator is kept because the
+ * quotient must be exact for every operand.
+ */
+__device__ __forceinline__ i64 gd_div(i64 a, i64 b) { return a / b; }
+
+struct GdView {
+  float x, y, angle, viewZ;
+  i64 vx, vy, pitchBam;
+  i64 vsin, vcos;
+  float fcos, fsin;
+  i64 center;
+  int flashLight;
+};
+
+/* Per-wall record kept in shared memory for the lane being drawn. */
+struct __align__(8) GdWall {
+  i64 visL[2], visStep[2], visSl[2];  /* wallscan light per side */
+  i64 sl, sr;                         /* projected half-open span (unbounded when rejected) */
+  i64 dl, dr;                         /* clipped endpoint depths, 20.12 */
+  int tx[2], ty[2];                   /* view coordinates in stored endpoint order */
+  short isl, isr;                     /* span owned by the column-ray test */
+  unsigned char hasColumns, frontF, oneSided, pad;
+};
+
+/* One clip event of a column: what a drawn seg contributes to sprite clipping
+ * and to visplane ownership. Rows are 0..208 and fit a byte. */
+struct __align__(4) GdEvent {
+  float dist;
+  short wall;      /* wall whose depth clips sprites */
+  short sector;    /* sector owning the planes marked by this event, -1 none */
+  unsigned char t0a, t0b, t1a, t1b;  /* rows drawn by this event: two tier ranges */
+  unsigned char silTop, silBot;      /* silhouettes: rows < silTop and rows >= silBot */
+  unsigned char ceilA, ceilB, floorA, floorB;  /* plane marks */
+  unsigned char pad0, pad1;
+};
+
+#define GD_MAX_EVENTS 24

@@ -1,0 +1,1838 @@
+/*
+ * Fused render-to-observation kernel for sm_100a.
+ *
+ * One persistent CTA of 320 threads draws one environment lane at a time:
+ *   1. every wall of the map is projected once per lane into shared memory
+ *      (threads over walls), and its ray-owned column span is found by a warp
+ *      sweeping the 320 column rays with ballots;
+ *   2. thread x then walks column x front to back through the sector portals,
+ *      keeping the ceiling / floor clip pair in registers, drawing wall tiers
+ *      and the visplane rows they uncover straight into the palette-indexed
+ *      frame held in shared memory (aligned groups of four columns exchange
+ *      their tier bounds with warp shuffles);
+ *   3. thread x draws the depth-sorted sprites of column x against the clip
+ *      events its walk recorded;
+ *   4. the weapon and, on request, the status bar are composited;
+ *   5. the 320x240 frame is reduced to the 84x84 grayscale observation with the
+ *      exact integer area weights and written, 16 bytes per store, into the
+ *      four-frame stack; the RGB24 frame is written only when asked for.
+ * Only the lane record, the thing records and the stack slot touch HBM; the
+ * indexed frame never leaves the SM.  Tensor cores are unused: nothing here is
+ * a contraction.
+ *
+ * The arithmetic restates src/gradoom/engine.py (file:line beside each
+ * function) and must stay bit-identical to it; compile with -fmad=false.
+ */
+#include "gd_device.cuh"
+
+#define GD_THREADS 320
+#define GD_WARPS (GD_THREADS / 32)
+#define GD_INF CUDART_INF_F
+
+/* render flags */
+#define GD_F_MASK_HUD 1     /* observation sees 32 black rows instead of the status bar */
+#define GD_F_DRAW_HUD 2     /* composite the status bar (needed for RGB / unmasked obs) */
+#define GD_F_STACK_ROLL 4   /* shift the stack by one slot and append */
+#define GD_F_STACK_FILL 8   /* write all four slots of lanes whose mask byte is set */
+#define GD_F_WRITE_OBS 16   /* write plain (n,84,84) observations to obsOut */
+
+struct GdParams {
+  GdScene sc;
+  const int32_t *lanes;
+  const gd_thing *things;
+  int maxThings;
+  int n;
+  int flags;
+  uint8_t *stack;            /* n x 4 x 84 x 84 */
+  const uint8_t *resetMask;  /* n, for GD_F_STACK_FILL */
+  uint8_t *obsOut;           /* n x 84 x 84, optional */
+  uint8_t *indexedOut;       /* n x 240 x 320, optional */
+  uint8_t *rgbOut;           /* n x 240 x 320 x 3, optional */
+  uint8_t *scratch;          /* gridDim.x x GD_SCRATCH_PER_CTA */
+  int *status;
+};
+
+#define GD_SCRATCH_EVENTS_BYTES (GD_MAX_EVENTS * GD_SW * (int)sizeof(GdEvent))
+#define GD_SCRATCH_PER_CTA (GD_SCRATCH_EVENTS_BYTES + GD_SW * 4)
+
+struct GdActor {
+  float x, y, depth;
+  i64 depthFixed, xstep, yscale, topFixed, texMid, iscale;
+  int left, right;
+  int sprite, w, h;
+  short shade;
+  signed char style;
+  unsigned char alive;
+};
+
+/* ---- shared memory carve-up -------------------------------------------- */
+struct GdShared {
+  uint8_t *frame;       /* 240 x 320 */
+  uint8_t *colormap;    /* 32 x 256 */
+  uint8_t *playpal;     /* 768 */
+  unsigned *yslope;     /* 208 */
+  int32_t *lane;        /* 32 */
+  float *wallDistance;  /* 320 */
+  short *blockingWall;  /* 320 */
+  unsigned *ownerMask;  /* 10 words: boundary_has_projected_owner */
+  GdWall *walls;        /* W */
+  GdActor *actors;      /* maxThings */
+  unsigned long long *pal64;  /* 256: R | G<<20 | B<<40 */
+  uint8_t *obs;         /* 84 x 84 */
+  int *misc;            /* 4 ints: start sector, thing count */
+};
+
+__host__ __device__ inline size_t gd_align16(size_t v) { return (v + 15) & ~(size_t)15; }
+
+__host__ __device__ inline size_t gd_shared_bytes(int W, int maxThings) {
+  size_t b = 0;
+  b += gd_align16((size_t)GD_SCREEN_H * GD_SW);
+  b += gd_align16(32 * 256);
+  b += gd_align16(768);
+  b += gd_align16(GD_VH * 4);
+  b += gd_align16(GD_LANE_WORDS * 4);
+  b += gd_align16(GD_SW * 4);
+  b += gd_align16(GD_SW * 2);
+  b += gd_align16(16 * 4);
+  b += gd_align16(256 * 8);
+  b += gd_align16(GD_OBS * GD_OBS);
+  b += gd_align16(16);
+  b += gd_align16((size_t)W * sizeof(GdWall));
+  b += gd_align16((size_t)(maxThings > 0 ? maxThings : 1) * sizeof(GdActor));
+  return b;
+}
+
+__device__ inline void gd_carve(uint8_t *base, int W, int maxThings, GdShared &s) {
+  size_t o = 0;
+  s.frame = base + o; o += gd_align16((size_t)GD_SCREEN_H * GD_SW);
+  s.colormap = base + o; o += gd_align16(32 * 256);
+  s.playpal = base + o; o += gd_align16(768);
+  s.yslope = (unsigned *)(base + o); o += gd_align16(GD_VH * 4);
+  s.lane = (int32_t *)(base + o); o += gd_align16(GD_LANE_WORDS * 4);
+  s.wallDistance = (float *)(base + o); o += gd_align16(GD_SW * 4);
+  s.blockingWall = (short *)(base + o); o += gd_align16(GD_SW * 2);
+  s.ownerMask = (unsigned *)(base + o); o += gd_align16(16 * 4);
+  s.pal64 = (unsigned long long *)(base + o); o += gd_align16(256 * 8);
+  s.obs = base + o; o += gd_align16(GD_OBS * GD_OBS);
+  s.misc = (int *)(base + o); o += gd_align16(16);
+  s.walls = (GdWall *)(base + o); o += gd_align16((size_t)W * sizeof(GdWall));
+  s.actors = (GdActor *)(base + o);
+}
+
+/* ---- view (engine.py:10648-10670, 10596-10601, 14949-14967) ------------- */
+__device__ void gd_view_setup(const GdScene &sc, const int32_t *lane, GdView &v) {
+  v.x = __int_as_float(lane[GD_L_X]);
+  v.y = __int_as_float(lane[GD_L_Y]);
+  v.angle = __int_as_float(lane[GD_L_ANGLE]);
+  v.viewZ = __int_as_float(lane[GD_L_VIEW_Z]);
+  v.vx = lane[GD_L_X_FIXED];
+  v.vy = lane[GD_L_Y_FIXED];
+  i64 bam = (i64)(uint32_t)lane[GD_L_ANGLE_BAM];
+  v.pitchBam = lane[GD_L_PITCH_BAM];
+  int fine = (int)((bam >> 19) & 8191);
+  v.vsin = sc.fineSine[fine];
+  v.vcos = sc.fineSine[(fine + 2048) & 8191];
+  v.fsin = (float)v.vsin / 65536.0f;
+  v.fcos = (float)v.vcos / 65536.0f;
+  i64 ti = gd_clamp((GD_ANG90 - v.pitchBam) >> 19, 0, 4095);
+  v.center = 104 * GD_FU + ((GD_FOCAL_Y * (i64)sc.fineTan[ti]) >> 16);
+  int weapon = (int)gd_clamp(lane[GD_L_WEAPON], 0, 7);
+  int cooldown = (int)gd_clamp(lane[GD_L_WPN_COOLDOWN], 0, sc.wpnTics - 1);
+  int parity = (int)gd_pymod(lane[GD_L_WPN_FIRE_COUNT], 2);
+  if (weapon == 1 && cooldown == 0) parity = (int)gd_pymod(gd_max(lane[GD_L_WPN_READY_TICS] - 1, 0) / 4, 2);
+  v.flashLight = sc.wpnFlashLights[(weapon * 2 + parity) * sc.wpnTics + cooldown];
+}
+
+__device__ __forceinline__ void gd_ray(const GdView &v, int x, float &rx, float &ry) {
+  float c = ((float)x - 160.0f) / 160.0f;
+  rx = v.fcos + v.fsin * c;
+  ry = v.fsin - v.fcos * c;
+}
+
+/* FWallCoords (engine.py:10791-10869) */
+__device__ void gd_fwall_coords(i64 tx1, i64 ty1, i64 tx2, i64 ty2, i64 &sl, i64 &sr, i64 &dl, i64 &dr) {
+  const i64 cf = 160 * GD_FU;
+  i64 sty1 = ty1 == 0 ? 1 : ty1, sty2 = ty2 == 0 ? 1 : ty2;
+  i64 lp = (cf + gd_div(tx1 * cf, sty1)) >> 16;
+  lp += (tx1 >= 0);
+  if (tx1 >= 0) lp = gd_min(lp, GD_SW);
+  i64 rp = (cf + gd_div(tx2 * cf, sty2)) >> 16;
+  rp += (tx2 >= 0);
+  if (tx2 >= 0) rp = gd_min(rp, GD_SW);
+  i64 lden = tx1 - tx2 - ty2 + ty1, rden = ty2 - ty1 - tx2 + tx1;
+  i64 slden = lden == 0 ? 1 : lden, srden = rden == 0 ? 1 : rden;
+  bool lin = tx1 >= -ty1, rin = tx2 <= ty2;
+  i64 screenL = lin ? lp : 0, screenR = rin ? rp : GD_SW;
+  i64 depthL = lin ? ty1 : ty1 + gd_div((ty2 - ty1) * (tx1 + ty1), slden);
+  i64 depthR = rin ? ty2 : ty1 + gd_div((ty2 - ty1) * (tx1 - ty1), srden);
+  bool invL = (lin ? ((tx1 > ty1) || (ty1 == 0)) : ((tx2 < -ty2) || (lden == 0))) || (depthL < 32);
+  bool invR = (rin ? ((tx2 < -ty2) || (ty2 == 0)) : ((tx1 > ty1) || (rden == 0))) || (depthR < 32);
+  bool inv = invL || invR || (screenR <= screenL);
+  if (inv) screenR = screenL;
+  sl = screenL; sr = screenR; dl = depthL; dr = depthR;
+}
+
+/* wallscan light for one endpoint order (engine.py:11217-11291) */
+__device__ void gd_wall_visibility(i64 tx1, i64 ty1, i64 tx2, i64 ty2, i64 &visL, i64 &visStep, i64 &visSl) {
+  const i64 cf = 160 * GD_FU;
+  i64 sty1 = ty1 == 0 ? 1 : ty1, sty2 = ty2 == 0 ? 1 : ty2;
+  i64 lp = ((cf + gd_div(tx1 * cf, sty1)) >> 16) + (tx1 >= 0);
+  i64 rp = ((cf + gd_div(tx2 * cf, sty2)) >> 16) + (tx2 >= 0);
+  i64 lden = tx1 - tx2 - ty2 + ty1, rden = ty2 - ty1 - tx2 + tx1;
+  i64 slden = lden == 0 ? 1 : lden, srden = rden == 0 ? 1 : rden;
+  bool lin = tx1 >= -ty1, rin = tx2 <= ty2;
+  i64 wsl = lin ? lp : 0, wsr = rin ? rp : GD_SW;
+  i64 wdl = lin ? ty1 : ty1 + gd_div((ty2 - ty1) * (tx1 + ty1), slden);
+  i64 wdr = rin ? ty2 : ty1 + gd_div((ty2 - ty1) * (tx1 - ty1), srden);
+  i64 ll = gd_div(GD_WALL_VIS << 12, gd_max(wdl, 1));
+  i64 lr = gd_div(GD_WALL_VIS << 12, gd_max(wdr, 1));
+  visStep = gd_div(lr - ll, gd_max(wsr - wsl, 1));
+  visL = ll;
+  visSl = wsl;
+}
+
+/* Project wall w of the map for this lane (engine.py:10747-10869, 11207-11302,
+ * 11359-11427).  The ray-owned span is completed by gd_wall_span below. */
+__device__ void gd_project_wall(const GdScene &sc, const GdView &v, int w, GdWall &out) {
+  const float *wl = &sc.walls[w * 4];
+  i64 fx[2] = {gd_rint(wl[0] * 65536.0f), gd_rint(wl[2] * 65536.0f)};
+  i64 fy[2] = {gd_rint(wl[1] * 65536.0f), gd_rint(wl[3] * 65536.0f)};
+  i64 tx[2], ty[2];
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    i64 rx = fx[e] - v.vx, ry = fy[e] - v.vy;
+    tx[e] = (rx * v.vsin - ry * v.vcos) >> 20;
+    ty[e] = (rx * v.vcos + ry * v.vsin) >> 20;
+    out.tx[e] = (int)tx[e];
+    out.ty[e] = (int)ty[e];
+  }
+  i64 wvx = fx[1] - fx[0], wvy = fy[1] - fy[0];
+  i64 fsx = v.vx - fx[0], fsy = v.vy - fy[0];
+  bool ff = (wvx * fsy - wvy * fsx) < 0;
+  int a = ff ? 0 : 1, b = ff ? 1 : 0;
+  i64 sl, sr, dl, dr;
+  gd_fwall_coords(tx[a], ty[a], tx[b], ty[b], sl, sr, dl, dr);
+  out.sl = sl; out.sr = sr; out.dl = dl; out.dr = dr;
+  gd_wall_visibility(tx[0], ty[0], tx[1], ty[1], out.visL[0], out.visStep[0], out.visSl[0]);
+  gd_wall_visibility(tx[1], ty[1], tx[0], ty[0], out.visL[1], out.visStep[1], out.visSl[1]);
+  out.oneSided = sc.wsec[w * 2 + 1] < 0;
+  float sx = wl[0], sy = wl[1];
+  float segx = wl[2] - sx, segy = wl[3] - sy;
+  float vfsx = v.x - sx, vfsy = v.y - sy;
+  out.frontF = (segx * vfsy - segy * vfsx) < 0;
+}
+
+/* Column-ray test of wall w at column x (engine.py:11317-11331).  Returns the
+ * raw distance / along and the geometric-hit flag; span validity is applied by
+ * gd_hit. */
+__device__ __forceinline__ void gd_ray_test(const GdScene &sc, const GdView &v, int w, float rx, float ry,
+                                            float &distance, float &along, bool &geo, bool &positive) {
+  const float4 wl = *reinterpret_cast<const float4 *>(&sc.walls[w * 4]);
+  float sx = wl.x, sy = wl.y;
+  float segx = wl.z - sx, segy = wl.w - sy;
+  float offx = sx - v.x, offy = sy - v.y;
+  float den = rx * segy - ry * segx;
+  bool small = fabsf(den) < 1e-6f;
+  float safe = small ? 1.0f : den;
+  distance = (offx * segy - offy * segx) / safe;
+  along = (offx * ry - offy * rx) / safe;
+  positive = !small && distance > 0;
+  geo = positive && along >= 0 && along <= 1;
+}
+
+/* Same test without the divisions, for the span sweep: the comparisons of the
+ * rounded quotients with 0 and 1 depend only on signs and magnitudes. */
+__device__ __forceinline__ bool gd_ray_geo(const float4 wl, const GdView &v, float rx, float ry) {
+  float sx = wl.x, sy = wl.y;
+  float segx = wl.z - sx, segy = wl.w - sy;
+  float offx = sx - v.x, offy = sy - v.y;
+  float den = rx * segy - ry * segx;
+  bool small = fabsf(den) < 1e-6f;
+  float safe = small ? 1.0f : den;
+  float dn = offx * segy - offy * segx;
+  float an = offx * ry - offy * rx;
+  float distance = dn / safe;  /* kept: a tiny quotient may round to zero */
+  bool alongOk = (an == 0.0f) || (((an < 0) == (safe < 0)) && fabsf(an) <= fabsf(safe));
+  return !small && distance > 0 && alongOk;
+}
+
+/* ---- per (column, wall) hit -------------------------------------------- */
+struct GdHit {
+  float d;       /* ray distance, +inf when the wall does not count here */
+  float along;   /* clamped to [0,1] */
+  bool geo, proj, left;
+};
+
+/* engine.py:11440-11459 */
+__device__ __forceinline__ GdHit gd_hit(const GdScene &sc, const GdView &v, const GdWall *walls, int w, int x,
+                                        float rx, float ry) {
+  GdHit h;
+  float distance, along;
+  bool geo, positive;
+  gd_ray_test(sc, v, w, rx, ry, distance, along, geo, positive);
+  const GdWall &wv = walls[w];
+  bool screenValid = wv.hasColumns && x >= wv.isl && x < wv.isr;
+  bool pv = positive && screenValid;
+  bool valid = wv.oneSided ? (pv && wv.frontF) : (geo || pv);
+  h.d = valid ? distance : GD_INF;
+  float ac = along;
+  if (!(ac >= 0.0f)) ac = (ac != ac) ? ac : 0.0f;
+  if (ac > 1.0f) ac = 1.0f;
+  h.along = ac;
+  h.geo = geo;
+  h.proj = pv;
+  h.left = (x == wv.isl);
+  return h;
+}
+
+__device__ __forceinline__ float gd_tol(float d) { return fmaxf(fabsf(d) / 128.0f, 4.0f); }
+
+/* Endpoint owner of wall w at column x (engine.py:11589-11730). */
+__device__ void gd_endpoint_owner(const GdScene &sc, const GdView &v, const GdWall *walls, int w, int x, float rx,
+                                  float ry, const GdHit &hw, int &ownerIdx, float &ownerDist) {
+  const GdWall &wv = walls[w];
+  float d = hw.d;
+  float tol = gd_tol(d);
+  bool subpixel = (wv.sr - wv.sl <= 1) && !wv.oneSided;
+  bool usesStart = hw.along <= 0.5f;
+  int oi = w;
+  float od = d;
+  bool ownerValid = false;
+  if (sc.nbDirect) {
+    const int32_t *nd = &sc.nbDirectTab[w * 4];
+    int sIdx = nd[0] >= 0 ? nd[0] : w, eIdx = nd[1] >= 0 ? nd[1] : w;
+    bool hasS = nd[0] >= 0, hasE = nd[1] >= 0;
+    int rIdx = usesStart ? sIdx : eIdx, rSlot = usesStart ? nd[2] : nd[3];
+    bool rHas = usesStart ? hasS : hasE;
+    int oIdx = usesStart ? eIdx : sIdx, oSlot = usesStart ? nd[3] : nd[2];
+    bool oHas = usesStart ? hasE : hasS;
+    GdHit hr = (rIdx == w) ? hw : gd_hit(sc, v, walls, rIdx, x, rx, ry);
+    GdHit ho = (oIdx == w) ? hw : gd_hit(sc, v, walls, oIdx, x, rx, ry);
+    bool rOwns = rHas && hr.proj && hr.left;
+    bool oOwns = subpixel && oHas && ho.proj && ho.left && (fabsf(ho.d - d) <= tol);
+    bool useO = oOwns && (!rOwns || ho.d < hr.d || (ho.d == hr.d && oSlot < rSlot));
+    oi = useO ? oIdx : rIdx;
+    od = useO ? ho.d : hr.d;
+    ownerValid = rOwns || oOwns;
+  } else {
+    float best = GD_INF;
+    int bestSlot = 0;
+    int n0 = sc.nbOff[w], n1 = sc.nbOff[w + 1];
+    for (int k = n0; k < n1; ++k) {
+      int nb = sc.nbIdx[k], fl = sc.nbFlags[k];
+      GdHit hn = gd_hit(sc, v, walls, nb, x, rx, ry);
+      bool rayNb = usesStart ? (fl & 1) : ((fl >> 1) & 1);
+      bool sel = rayNb || (subpixel && (fabsf(hn.d - d) <= tol));
+      float cand = (hn.proj && hn.left && sel) ? hn.d : GD_INF;
+      if (cand < best) { best = cand; bestSlot = k - n0; }
+    }
+    od = best;
+    oi = (n1 > n0) ? sc.nbIdx[n0 + bestSlot] : w;
+    ownerValid = isfinite(best);
+  }
+  bool has = !hw.proj && ownerValid;
+  ownerIdx = has ? oi : w;
+  ownerDist = has ? od : d;
+}
+
+/* PrepWall for one (column, wall) (engine.py:10672-10739). */
+__device__ void gd_prep_wall(const GdScene &sc, const GdWall &wv, int w, int x, i64 &hoff, i64 &vstep) {
+  i64 tx1 = wv.tx[0], tx2 = wv.tx[1], ty1 = wv.ty[0], ty2 = wv.ty[1];
+  double uozOrigin = (double)((float)tx1 * 160.0f);
+  double uozStep = (double)(-(float)ty1);
+  double invzOrigin = (double)((float)(tx1 - tx2) * 160.0f);
+  float invzStepF = (float)(ty2 - ty1);
+  double invzStep = (double)invzStepF;
+  double col = (double)x - 160.0;
+  double top = uozOrigin + uozStep * col;
+  double bottom = invzOrigin + invzStep * col;
+  double safeBottom = bottom == 0 ? 1.0 : bottom;
+  double fraction = top / safeBottom;
+  i64 repeat = gd_rint(sc.wlen[w] * 65536.0f);
+  hoff = (i64)floor(fraction * (double)repeat + 0.5);
+  const double wms = (320 * 200.0 / 320.0 / 240) * 64.0 / (320 / 2.0);
+  double depthScale = (double)(invzStepF * (float)wms);
+  double depthOrigin = (double)((-(float)uozStep) * (float)wms);
+  vstep = (i64)floor(fraction * depthScale + depthOrigin + 0.5);
+}
+
+/* OWallMost row projection (engine.py:12294-12605), one fragment per wall. */
+__device__ int gd_project_rows(const GdView &v, const GdWall &wv, float worldZ, int x) {
+  i64 wsl = wv.sl, wsr = wv.sr;
+  i64 wdl = gd_max(wv.dl, 1), wdr = gd_max(wv.dr, 1);
+  bool owns = (wsr > wsl) && x >= wsl && x < wsr;
+  i64 relZ = gd_rint((worldZ - v.viewZ) * 65536.0f);
+  i64 pz = -(relZ >> 4);
+  i64 center = v.center;
+  i64 num = pz * GD_FOCAL_Y;
+  if (!owns) {
+    i64 ospan = gd_max(wsr - wsl, 1);
+    i64 opl = gd_div(num, wdl), opr = gd_div(num, wdr);
+    i64 ostep = gd_div(opr - opl, ospan);
+    return (int)gd_clamp((center + opl + (x - wsl) * ostep) >> 16, 0, GD_VH);
+  }
+  i64 sl = wsl, sr = wsr, dl = wdl, dr = wdr;
+  i64 upperClip = gd_div((-center) * GD_FU, GD_FOCAL_Y);
+  i64 lowerClip = gd_div((GD_VH * GD_FU - center) * GD_FU, GD_FOCAL_Y);
+  i64 ul = (upperClip * dl) >> 16, ur = (upperClip * dr) >> 16;
+  i64 ll = (lowerClip * dl) >> 16, lr = (lowerClip * dr) >> 16;
+  bool aboveL = pz < ul, aboveR = pz < ur, belowL = pz > ll, belowR = pz > lr;
+  bool entAbove = aboveL && aboveR, entBelow = belowL && belowR;
+  i64 cl = sl, cr = sr, cdl = dl, cdr = dr;
+  bool outTop = false, outBottom = false;
+  bool crossesTop = aboveL != aboveR;
+  if (crossesTop) {
+    i64 sud = (ur != ul) ? (ur - ul) : 1;
+    i64 tf = gd_div(gd_shl(pz - ul, 30), sud);
+    i64 td = dl + (((dr - dl) * tf) >> 30);
+    i64 tc = sl + gd_div(((dr * tf) >> 30) * (sr - sl), gd_max(td, 1));
+    if (aboveR && (sl <= tc)) { cr = tc; cdr = td; }
+    outTop |= aboveR && (sr > tc) && (x >= tc) && (x < sr);
+    if (aboveL && (tc <= sr)) { cl = tc; cdl = td; }
+    outTop |= aboveL && (tc > sl) && (x >= sl) && (x < tc);
+  }
+  bool crossesBottom = belowL != belowR;
+  if (crossesBottom) {
+    i64 sld = (lr != ll) ? (lr - ll) : 1;
+    i64 bf = gd_div(gd_shl(pz - ll, 30), sld);
+    i64 bd = dl + (((dr - dl) * bf) >> 30);
+    i64 bc = sl + gd_div(((dr * bf) >> 30) * (sr - sl), gd_max(bd, 1));
+    if (belowR && (sl <= bc)) { cr = bc; cdr = bd; }
+    outBottom |= belowR && (sr > bc) && (x >= bc) && (x < sr);
+    if (belowL && (bc <= sr)) { cl = bc; cdl = bd; }
+    outBottom |= belowL && (bc > sl) && (x >= sl) && (x < bc);
+  }
+  bool collapsed = (cr == cl) && (x == cl) && !(entAbove || entBelow);
+  if (entAbove || (outTop && !collapsed)) return 0;
+  if (entBelow || (outBottom && !collapsed)) return GD_VH;
+  i64 pl = gd_div(num, gd_max(cdl, 1)), pr = gd_div(num, gd_max(cdr, 1));
+  i64 span = gd_max(cr - cl, 1);
+  i64 pstep = gd_div(pr - pl, span);
+  return (int)gd_clamp((center + pl + (x - cl) * pstep) >> 16, 0, GD_VH);
+}
+
+__device__ __forceinline__ int gd_wall_shade(i64 light, i64 vis) {
+  i64 base = 64 * GD_FU - (light + 12) * (GD_FU / 4);
+  return (int)gd_clamp((base - gd_min(vis, 24 * GD_FU)) >> 16, 0, 31);
+}
+
+/* ---- static topology predicates (engine.py:399-484, 1596-1612) ---------- */
+__device__ __forceinline__ int gd_secidx(const GdScene &sc, int s) { return s < 0 ? s + sc.S : s; }
+__device__ __forceinline__ float gd_sec_floor(const GdScene &sc, int s) { return sc.secF[gd_secidx(sc, s) * 2]; }
+__device__ __forceinline__ float gd_sec_ceil(const GdScene &sc, int s) { return sc.secF[gd_secidx(sc, s) * 2 + 1]; }
+__device__ __forceinline__ int4 gd_sec_info(const GdScene &sc, int s) {
+  return *reinterpret_cast<const int4 *>(&sc.secI[gd_secidx(sc, s) * 4]);
+}
+
+__device__ __forceinline__ bool gd_same_pair(const GdScene &sc, int a, int b) {
+  int a0 = sc.wsec[a * 2], a1 = sc.wsec[a * 2 + 1], b0 = sc.wsec[b * 2], b1 = sc.wsec[b * 2 + 1];
+  return (a0 == b0 && a1 == b1) || (a0 == b1 && a1 == b0);
+}
+__device__ __forceinline__ bool gd_shares_endpoint(const GdScene &sc, int a, int b) {
+  int a0 = sc.wvtx[a * 2], a1 = sc.wvtx[a * 2 + 1], b0 = sc.wvtx[b * 2], b1 = sc.wvtx[b * 2 + 1];
+  return a0 == b0 || a0 == b1 || a1 == b0 || a1 == b1;
+}
+__device__ bool gd_opposing_pair(const GdScene &sc, int a, int b) {
+  if (!gd_same_pair(sc, a, b)) return false;
+  if (sc.wsec[a * 2 + 1] < 0 || sc.wsec[b * 2 + 1] < 0) return false;
+  if (gd_shares_endpoint(sc, a, b)) return false;
+  const float *A = &sc.walls[a * 4], *B = &sc.walls[b * 4];
+  float adx = A[2] - A[0], ady = A[3] - A[1], bdx = B[2] - B[0], bdy = B[3] - B[1];
+  float dot = adx * bdx + ady * bdy;
+  float cross = adx * bdy - ady * bdx;
+  return dot < 0 && fabsf(cross) < 1e-6f;
+}
+__device__ __forceinline__ bool gd_two_distinct(const GdScene &sc, int w) {
+  return sc.wsec[w * 2 + 1] >= 0 && sc.wsec[w * 2] != sc.wsec[w * 2 + 1];
+}
+__device__ bool gd_bridge_pair_of(const GdScene &sc, int a, int b, int &p0, int &p1) {
+  int a0 = sc.wsec[a * 2], a1 = sc.wsec[a * 2 + 1], b0 = sc.wsec[b * 2], b1 = sc.wsec[b * 2 + 1];
+  int shared = 0, sv = -2;
+  if (a0 == b0 || a0 == b1) { shared++; sv = a0; }
+  if (a1 == b0 || a1 == b1) { shared++; sv = a1; }
+  if (shared != 1) return false;
+  p0 = (a0 == sv) ? a1 : a0;
+  p1 = (b0 == sv) ? b1 : b0;
+  return true;
+}
+__device__ __forceinline__ bool gd_set_equals(const GdScene &sc, int w, int p0, int p1) {
+  int s0 = sc.wsec[w * 2], s1 = sc.wsec[w * 2 + 1];
+  if (p0 == p1) return s0 == p0 && s1 == p0;
+  return (s0 == p0 && s1 == p1) || (s0 == p1 && s1 == p0);
+}
+__device__ bool gd_unique_at_vertex(const GdScene &sc, int v, int skipA, int skipB, int p0, int p1, int &index) {
+  int count = 0, found = 0;
+  for (int k = sc.vtxOff[v]; k < sc.vtxOff[v + 1]; ++k) {
+    int c = sc.vtxWalls[k];
+    if (c == skipA || c == skipB) continue;
+    if (gd_set_equals(sc, c, p0, p1)) { count++; found = c; }
+  }
+  index = (count == 1) ? found : 0;
+  return count == 1;
+}
+__device__ bool gd_portal_bridge(const GdScene &sc, int slot, int path, int owner, int &index) {
+  index = 0;
+  if (!gd_two_distinct(sc, path) || owner == path) return false;
+  int v = sc.wvtx[path * 2 + slot];
+  if (sc.wvtx[owner * 2] != v && sc.wvtx[owner * 2 + 1] != v) return false;
+  if (!gd_two_distinct(sc, owner)) return false;
+  int p0, p1;
+  if (!gd_bridge_pair_of(sc, path, owner, p0, p1)) return false;
+  return gd_unique_at_vertex(sc, v, path, owner, p0, p1, index);
+}
+__device__ bool gd_sector_bridge(const GdScene &sc, int slot, int pending, int path, int &index) {
+  index = 0;
+  if (!gd_two_distinct(sc, pending) || path == pending || !gd_two_distinct(sc, path)) return false;
+  int p0, p1;
+  if (!gd_bridge_pair_of(sc, pending, path, p0, p1)) return false;
+  return gd_unique_at_vertex(sc, sc.wvtx[pending * 2 + slot], pending, path, p0, p1, index);
+}
+
+/* ---- phase: ray-owned spans (engine.py:11333-11438) --------------------- */
+__device__ void gd_wall_spans(const GdScene &sc, const GdView &v, GdWall *walls) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int w = warp; w < sc.W; w += GD_WARPS) {
+    const float4 wl = *reinterpret_cast<const float4 *>(&sc.walls[w * 4]);
+    int first = -1, last = -1;
+#pragma unroll 2
+    for (int chunk = 0; chunk < GD_SW / 32; ++chunk) {
+      int x = chunk * 32 + lane;
+      float rx, ry;
+      gd_ray(v, x, rx, ry);
+      unsigned m = __ballot_sync(0xffffffffu, gd_ray_geo(wl, v, rx, ry));
+      if (m) {
+        if (first < 0) first = chunk * 32 + __ffs(m) - 1;
+        last = chunk * 32 + 31 - __clz(m);
+      }
+    }
+    if (lane == 0) {
+      GdWall &wv = walls[w];
+      bool hasColumns = first >= 0;
+      i64 isl = hasColumns ? first : 0;
+      i64 isr = hasColumns ? last + 1 : GD_SW;
+      const i64 cf = 160 * GD_FU;
+      i64 ecol[2];
+      bool evis[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        i64 ty = wv.ty[e], tx = wv.tx[e];
+        i64 sty = ty == 0 ? 1 : ty;
+        i64 pf = cf + gd_div(tx * cf, sty);
+        ecol[e] = (pf >> 16) + (tx >= 0);
+        evis[e] = ty > 0 && tx >= -ty && tx <= ty && ecol[e] >= 0 && ecol[e] <= GD_SW;
+      }
+      bool fff = wv.frontF;
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        bool visible = evis[e] && hasColumns;
+        bool ownsLeft = fff ? (e == 0) : (e == 1);
+        if (visible && ownsLeft) isl = ecol[e];
+        if (visible && !ownsLeft) isr = ecol[e];
+      }
+      if (evis[0] && evis[1]) {
+        isl = ecol[fff ? 0 : 1];
+        isr = ecol[fff ? 1 : 0];
+        hasColumns = isr > isl;
+      }
+      hasColumns = hasColumns && (wv.sr > wv.sl);
+      wv.isl = (short)isl;
+      wv.isr = (short)isr;
+      wv.hasColumns = hasColumns;
+    }
+  }
+}
+
+/* ---- phase: blocking ray cast of column x (engine.py:10534-10557) ------- */
+__device__ void gd_blocking_raycast(const GdScene &sc, const GdView &v, int x, float rx, float ry, float &wallDistance,
+                                    int &blockingWall) {
+  float best = GD_INF;
+  int bestSlot = 0;
+  for (int b = 0; b < sc.B; ++b) {
+    float distance, along;
+    bool geo, positive;
+    gd_ray_test(sc, v, sc.blocking[b], rx, ry, distance, along, geo, positive);
+    float d = geo ? distance : GD_INF;
+    if (d < best) { best = d; bestSlot = b; }
+  }
+  blockingWall = sc.blocking[bestSlot];
+  wallDistance = fminf(fmaxf(best, 1.0f), 4096.0f);
+}
+
+/* ---- visplane rows (engine.py:10879-10954, 10588-10616, 13372-13405) ---- */
+struct GdPlaneSpan {
+  i64 basex, basey, pviewx, pviewy, phf, gv, shadeBase;
+  const uint8_t *tex;
+  int wbits, hbits, texW;
+};
+
+__device__ void gd_plane_setup(const GdScene &sc, const GdView &v, int sector, bool isFloor, int x, GdPlaneSpan &p) {
+  float ph = isFloor ? (v.viewZ - gd_sec_floor(sc, sector)) : (gd_sec_ceil(sc, sector) - v.viewZ);
+  int4 si = gd_sec_info(sc, sector);
+  int tex = isFloor ? si.y : si.z;
+  const int4 ti = *reinterpret_cast<const int4 *>(&sc.texInfo[tex * 4]);
+  p.wbits = ti.z; p.hbits = ti.w; p.texW = sc.texW;
+  p.tex = sc.texAtlas + (size_t)tex * sc.texH * sc.texW;
+  i64 xscale = 1LL << (32 - p.wbits), yscale = 1LL << (32 - p.hbits);
+  i64 fs = v.vsin, fc = v.vcos;
+  i64 xstep = gd_div(xscale * fs, GD_FOCAL_X), ystep = gd_div(yscale * fc, GD_FOCAL_X);
+  i64 col = (i64)x - 159;
+  p.basex = ((xscale * fc) >> 16) + col * xstep;
+  p.basey = ((yscale * -fs) >> 16) + col * ystep;
+  p.pviewx = gd_wmul(xscale, v.vx) >> 16;
+  p.pviewy = gd_wmul(yscale, -v.vy) >> 16;
+  p.phf = gd_rint(ph * 65536.0f);
+  p.gv = gd_min(gd_div(GD_FLOOR_VIS << 16, gd_max(p.phf, 1)), (1LL << 31) - 1);
+  i64 light = si.x + v.flashLight * 16;
+  p.shadeBase = 64 * GD_FU - (light + 12) * (GD_FU / 4);
+}
+
+__device__ __forceinline__ uint8_t gd_plane_pixel(const GdPlaneSpan &p, const GdView &v, const unsigned *yslope,
+                                                  const uint8_t *colormap, int y) {
+  i64 distance = gd_wmul(p.phf, (i64)yslope[y]) >> 16;
+  i64 xfrac = ((gd_wmul(distance, p.basex) >> 16) + p.pviewx) & GD_U32MASK;
+  i64 yfrac = ((gd_wmul(distance, p.basey) >> 16) + p.pviewy) & GD_U32MASK;
+  int u = (int)(xfrac >> (32 - p.wbits)), tv = (int)(yfrac >> (32 - p.hbits));
+  uint8_t texel = p.tex[tv * p.texW + u];
+  i64 rowDist = v.center - (i64)y * GD_FU;
+  if (rowDist < 0) rowDist = -rowDist;
+  i64 vis = gd_min(gd_wmul(p.gv, rowDist) >> 16, 24 * GD_FU);
+  int shade = (int)gd_clamp((p.shadeBase - vis) >> 16, 0, 31);
+  return colormap[shade * 256 + texel];
+}
+
+/* bit helpers over a 208-row column mask */
+__device__ __forceinline__ bool gd_bit(const unsigned *m, int y) { return (m[y >> 5] >> (y & 31)) & 1u; }
+__device__ __forceinline__ void gd_set(unsigned *m, int y) { m[y >> 5] |= 1u << (y & 31); }
+
+/* ---- phase: per-column portal walk (engine.py:11561-13371) -------------- */
+struct GdColState {
+  int cur;
+  int ceilClip, floorClip;
+  float prev;
+  bool pendOwnerBoundary, pendEpBoundary, pendEpBridgeBoundary, pendPortalBridge;
+  float pendOwnerEpX, pendOwnerEpY, pendEpEpX, pendEpEpY;
+  int pendEpWall, pendEpBridgeIndex, pendPortalBridgeIndex, pendPortalBridgeSector;
+  float pendPortalBridgeExit;
+};
+
+__device__ __forceinline__ bool gd_state_equal(const GdColState &a, const GdColState &b) {
+  return a.cur == b.cur && a.ceilClip == b.ceilClip && a.floorClip == b.floorClip && a.prev == b.prev &&
+         a.pendOwnerBoundary == b.pendOwnerBoundary && a.pendEpBoundary == b.pendEpBoundary &&
+         a.pendEpBridgeBoundary == b.pendEpBridgeBoundary && a.pendPortalBridge == b.pendPortalBridge &&
+         a.pendOwnerEpX == b.pendOwnerEpX && a.pendOwnerEpY == b.pendOwnerEpY && a.pendEpEpX == b.pendEpEpX &&
+         a.pendEpEpY == b.pendEpEpY && a.pendEpWall == b.pendEpWall && a.pendEpBridgeIndex == b.pendEpBridgeIndex &&
+         a.pendPortalBridgeIndex == b.pendPortalBridgeIndex &&
+         a.pendPortalBridgeSector == b.pendPortalBridgeSector && a.pendPortalBridgeExit == b.pendPortalBridgeExit;
+}
+
+/* What one iteration decided for a column; the part other columns of its
+ * aligned group of four need is exchanged with shuffles. */
+struct GdIter {
+  int wall, side;
+  bool rasterValid, valid, oneSided;
+  int renderCurrent, otherSector;
+  float distance;
+  i64 vis;
+  int ctop, cbot, cupbot, clowtop;
+  bool tier[3];
+  bool markCeil, markFloor;
+  float viewFloor, viewCeil, otherFloor, otherCeil;
+  int tex[3];
+  /* traversal */
+  bool nokpp, pskpp, usesGeo, entersOther, entersShared, endpointOnly, epb, cppb, geometric;
+  int nopOther, psOther, gpOther;
+  float nopDist, psDist, gpDist, osd;
+  bool startsOwner, continuesOwner, pendEpHasFwd;
+  float selEpX, selEpY, epEpX, epEpY;
+  int epFwdIdx, ppbIdx, psPathIndex;
+  bool psFromFront;
+};
+
+__device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWall *walls, const unsigned *ownerMask,
+                                 int x, float rx, float ry, const GdColState &c, GdIter &it) {
+  const int curSector = c.cur;
+  const int current = curSector < 0 ? 0 : curSector;
+  const float prev = c.prev;
+  const int i0 = sc.secOff[current], i1 = sc.secOff[current + 1];
+#define HIT(w) gd_hit(sc, v, walls, (w), x, rx, ry)
+  float distance = GD_INF;
+  int wallIndex = 0;
+  if (curSector >= 0) {
+    for (int k = i0; k < i1; ++k) {
+      int w = sc.secWalls[k];
+      GdHit h = HIT(w);
+      if (h.d > prev && h.d < distance) { distance = h.d; wallIndex = w; }
+    }
+    float sd = GD_INF;
+    int sw = 0;
+    for (int k = i0; k < i1; ++k) {
+      int w = sc.secWalls[k];
+      if (!walls[w].oneSided) continue;
+      GdHit h = HIT(w);
+      if (!(h.d > prev) || !isfinite(h.d)) continue;
+      if (fabsf(h.d - distance) <= 1e-3f && h.d < sd) { sd = h.d; sw = w; }
+    }
+    if (isfinite(sd)) { distance = sd; wallIndex = sw; }
+  }
+  GdHit hSel = HIT(wallIndex);
+  const float *selWall = &sc.walls[wallIndex * 4];
+  bool selUsesStart = hSel.along <= 0.5f;
+  float selEpX = selUsesStart ? selWall[0] : selWall[2], selEpY = selUsesStart ? selWall[1] : selWall[3];
+  int selVtx = sc.wvtx[wallIndex * 2 + (selUsesStart ? 0 : 1)];
+#define SHARES_SEL(w) (sc.wvtx[(w) * 2] == selVtx || sc.wvtx[(w) * 2 + 1] == selVtx)
+  bool continuesOwner = c.pendOwnerBoundary && selEpX == c.pendOwnerEpX && selEpY == c.pendOwnerEpY;
+  bool continuesEp = c.pendEpBoundary && selEpX == c.pendEpEpX && selEpY == c.pendEpEpY;
+  int selSlot = hSel.along > 0.5f;
+  int epFwdIdx = 0;
+  bool pendEpHasFwd = false;
+  if (continuesEp) {
+    bool m = gd_portal_bridge(sc, selSlot, wallIndex, c.pendEpWall, epFwdIdx);
+    pendEpHasFwd = m && (HIT(epFwdIdx).d > distance + 1e-3f);
+  } else {
+    gd_portal_bridge(sc, selSlot, wallIndex, c.pendEpWall, epFwdIdx);
+  }
+  bool completesPendEpBridge = c.pendEpBridgeBoundary && wallIndex == c.pendEpBridgeIndex;
+  bool selIsProjected = hSel.proj;
+  bool selExclRight = walls[wallIndex].sr == x;
+  float psPathDist = distance;
+  int psPathIndex = wallIndex;
+  float psd = GD_INF;
+  int psi = 0;
+  if (!selIsProjected) {
+    for (int k = i0; k < i1; ++k) {
+      int w = sc.secWalls[k];
+      if (!walls[w].oneSided || !SHARES_SEL(w)) continue;
+      GdHit h = HIT(w);
+      if (h.proj && h.left && (h.d > prev + 1e-3f) && h.d < psd) { psd = h.d; psi = w; }
+    }
+    if (selExclRight) {
+      const int32_t *off = selUsesStart ? sc.sbStartOff : sc.sbEndOff;
+      const int32_t *idx = selUsesStart ? sc.sbStartIdx : sc.sbEndIdx;
+      float sbd = GD_INF;
+      int sbi = wallIndex;
+      for (int k = off[wallIndex]; k < off[wallIndex + 1]; ++k) {
+        int b = idx[k];
+        bool inc = sc.wsec[b * 2] == current || sc.wsec[b * 2 + 1] == current;
+        if (!inc || !walls[b].oneSided) continue;
+        GdHit h = HIT(b);
+        if (h.proj && h.left && (h.d > prev + 1e-3f) && h.d < sbd) { sbd = h.d; sbi = b; }
+      }
+      if (sbd < psd) { psd = sbd; psi = sbi; }
+    }
+  }
+  bool hasProjectedSolidOwner = isfinite(psd);
+  if (hasProjectedSolidOwner) { distance = psd; wallIndex = psi; }
+  GdHit hW = (wallIndex == psPathIndex) ? hSel : HIT(wallIndex);
+  int seo;
+  float sed;
+  gd_endpoint_owner(sc, v, walls, wallIndex, x, rx, ry, hW, seo, sed);
+  bool eoPathIsGeo = hW.geo;
+  bool replaceEo = (seo != wallIndex) && (sed > prev + 1e-3f);
+  if (replaceEo) { distance = sed; wallIndex = seo; hW = HIT(wallIndex); }
+  int nopIndex = wallIndex;
+  float nopDist = distance;
+  bool nopIsGeo = replaceEo ? eoPathIsGeo : hW.geo;
+  bool nopFromFront = curSector == sc.wsec[nopIndex * 2];
+  int nopOther = nopFromFront ? sc.wsec[nopIndex * 2 + 1] : sc.wsec[nopIndex * 2];
+  bool selOwnerIsProjected = hW.proj;
+  bool selOwnerExclRight = walls[wallIndex].sr == x;
+  i64 selOwnerSpan = walls[wallIndex].sr - walls[wallIndex].sl;
+  bool selOwnerShort = sc.wlen[wallIndex] <= 32.0f;
+  float npd = GD_INF;
+  int npi = 0;
+  if (!selOwnerIsProjected) {
+    for (int k = i0; k < i1; ++k) {
+      int w = sc.secWalls[k];
+      if (walls[w].oneSided) continue;
+      GdHit h = HIT(w);
+      if (!h.proj || !(h.d > prev + 1e-3f)) continue;
+      bool topological = false;
+      if (h.left && selOwnerExclRight && selOwnerSpan <= 2) {
+        int sbIdx;
+        topological = gd_sector_bridge(sc, h.along > 0.5f, w, nopIndex, sbIdx);
+      }
+      bool a = gd_same_pair(sc, wallIndex, w) ||
+               (h.left && selOwnerExclRight && (selOwnerSpan <= 2 || (SHARES_SEL(w) && selOwnerShort)));
+      bool nearOwner = (a && (fabsf(h.d - distance) <= gd_tol(h.d))) || topological;
+      if (nearOwner && h.d < npd) { npd = h.d; npi = w; }
+    }
+  }
+  /* projected sector bridge (engine.py:12073-12164) */
+  const int pew = c.pendEpWall;
+  bool peFromCur = curSector == sc.wsec[pew * 2];
+  int peOther = peFromCur ? sc.wsec[pew * 2 + 1] : sc.wsec[pew * 2];
+  bool usePsb = false;
+  if (c.pendEpBoundary && !selOwnerIsProjected && selOwnerExclRight && nopIsGeo) {
+    bool peIncident = peFromCur || curSector == sc.wsec[pew * 2 + 1];
+    const float *peWall = &sc.walls[pew * 4];
+    int peSlot = (c.pendEpEpX == peWall[2] && c.pendEpEpY == peWall[3]) ? 1 : 0;
+    int psbIndex;
+    bool psbExists = gd_sector_bridge(sc, peSlot, pew, nopIndex, psbIndex);
+    if (psbExists && peIncident && peOther >= 0 && nopOther >= 0 && (walls[pew].sr - walls[pew].sl <= 1)) {
+      int b0 = sc.wsec[psbIndex * 2], b1 = sc.wsec[psbIndex * 2 + 1];
+      bool matches = (b0 == peOther && b1 == nopOther) || (b1 == peOther && b0 == nopOther);
+      GdHit hb = HIT(psbIndex);
+      GdHit hp = HIT(pew);
+      bool psb = matches && hb.proj && hb.left && (hb.d > prev - gd_tol(hp.d)) && (hb.d < nopDist);
+      if (psb && hb.d < npd) { usePsb = true; npd = hb.d; npi = psbIndex; }
+    }
+  }
+  bool replaceNp = isfinite(npd);
+  if (replaceNp) { distance = npd; wallIndex = npi; hW = HIT(wallIndex); }
+  bool finalIsProjected = hW.proj, finalIsGeo = hW.geo;
+  bool completesOpposing =
+      c.pendEpBoundary && finalIsProjected && !finalIsGeo && gd_opposing_pair(sc, pew, wallIndex);
+  bool valid = isfinite(distance);
+  bool boundaryHasOwner = (ownerMask[x >> 5] >> (x & 31)) & 1u;
+  bool exclTraversalOnly =
+      !selOwnerIsProjected && selOwnerExclRight && !replaceNp && selOwnerSpan <= 2 && !boundaryHasOwner;
+  bool rasterValid = valid && !exclTraversalOnly && !continuesOwner &&
+                     !((pendEpHasFwd || completesPendEpBridge) && !selIsProjected && selExclRight && !replaceNp);
+  bool geometric = replaceNp ? nopIsGeo : (replaceEo ? eoPathIsGeo : hW.geo);
+  bool nokpp = replaceNp && nopIsGeo && nopOther >= 0;
+  int front = sc.wsec[wallIndex * 2], back = sc.wsec[wallIndex * 2 + 1];
+  bool fromFront = curSector == front;
+  int otherSector = fromFront ? back : front;
+  int renderCurrent = usePsb ? peOther : (completesOpposing ? otherSector : current);
+  bool renderFromFront = renderCurrent == front;
+  int renderOther = renderFromFront ? back : front;
+  int side = renderFromFront ? 0 : 1;
+  const GdWall &wv = walls[wallIndex];
+  i64 vis = wv.visL[side] + ((i64)x - wv.visSl[side]) * wv.visStep[side];
+  bool psFromFront = curSector == sc.wsec[psPathIndex * 2];
+  int psOther = psFromFront ? sc.wsec[psPathIndex * 2 + 1] : sc.wsec[psPathIndex * 2];
+  bool pskpp = hasProjectedSolidOwner && hSel.geo && psOther >= 0;
+  int safeOther = renderOther < 0 ? 0 : renderOther;
+  float viewFloor = gd_sec_floor(sc, renderCurrent), viewCeil = gd_sec_ceil(sc, renderCurrent);
+  float otherFloor = gd_sec_floor(sc, safeOther), otherCeil = gd_sec_ceil(sc, safeOther);
+  bool oneSided = otherSector < 0;
+  const int32_t *stex = &sc.sideTex[(wallIndex * 2 + side) * 3];
+  int oneTop = gd_project_rows(v, wv, viewCeil, x), oneBottom = gd_project_rows(v, wv, viewFloor, x);
+  int lowerTop = gd_project_rows(v, wv, otherFloor, x), upperBottom = gd_project_rows(v, wv, otherCeil, x);
+  int ctop = max(oneTop, c.ceilClip), cbot = min(oneBottom, c.floorClip);
+  int cupbot = max(min(upperBottom, c.floorClip), ctop);
+  int clowtop = min(max(lowerTop, c.ceilClip), cbot);
+  int4 ri = gd_sec_info(sc, renderCurrent), oi = gd_sec_info(sc, safeOther);
+  bool lightDiff = ri.x != oi.x;
+  it.markCeil = oneSided || viewCeil != otherCeil || ri.z != oi.z || lightDiff;
+  it.markFloor = oneSided || viewFloor != otherFloor || ri.y != oi.y || lightDiff;
+  it.wall = wallIndex; it.side = side; it.rasterValid = rasterValid; it.valid = valid;
+  it.oneSided = oneSided; it.renderCurrent = renderCurrent; it.otherSector = otherSector;
+  it.distance = distance; it.vis = vis;
+  it.ctop = ctop; it.cbot = cbot; it.cupbot = cupbot; it.clowtop = clowtop;
+  it.viewFloor = viewFloor; it.viewCeil = viewCeil; it.otherFloor = otherFloor; it.otherCeil = otherCeil;
+  it.tex[0] = stex[0]; it.tex[1] = stex[1]; it.tex[2] = stex[2];
+  it.tier[0] = oneSided && rasterValid && stex[0] >= 0 && ctop < cbot;
+  it.tier[1] = !oneSided && rasterValid && (viewFloor < otherFloor) && stex[1] >= 0 && clowtop < cbot;
+  it.tier[2] = !oneSided && rasterValid && (viewCeil > otherCeil) && stex[2] >= 0 && ctop < cupbot;
+
+  /* traversal decisions (engine.py:13070-13241) */
+  bool endpointOnly = valid && !oneSided && !geometric;
+  float cnd = GD_INF, ond = GD_INF, csd = GD_INF, osd = GD_INF, gpd = GD_INF;
+  int cni = 0, oni = 0, gpi = 0;
+  const float prior = prev;
+  if (endpointOnly) {
+    for (int k = i0; k < i1; ++k) {
+      int w = sc.secWalls[k];
+      GdHit h = HIT(w);
+      bool os = walls[w].oneSided;
+      bool fut = (h.geo || (os && isfinite(h.d))) && (h.d > distance + 1e-3f);
+      if (fut && h.d < cnd) { cnd = h.d; cni = w; }
+      bool sharesEp = gd_shares_endpoint(sc, w, wallIndex);
+      bool sharedSolid = isfinite(h.d) && os && (sharesEp || h.left) && (h.d > prior + 1e-3f) &&
+                         (h.d <= distance + 1e-3f);
+      if (sharedSolid && h.d < csd) csd = h.d;
+      bool sgp = h.geo && sharesEp && !os && (h.d > prior + 1e-3f) && (fabsf(h.d - distance) <= (1.0f / 16.0f));
+      if (sgp && h.d < gpd) { gpd = h.d; gpi = w; }
+    }
+    /* endpointOnly implies otherSector >= 0 */
+    for (int k = sc.secOff[otherSector]; k < sc.secOff[otherSector + 1]; ++k) {
+      int w = sc.secWalls[k];
+      GdHit h = HIT(w);
+      bool os = walls[w].oneSided;
+      bool fut = (h.geo || (os && isfinite(h.d))) && (h.d > distance + 1e-3f);
+      if (fut && h.d < ond) { ond = h.d; oni = w; }
+      bool sharesEp = gd_shares_endpoint(sc, w, wallIndex);
+      bool sharedSolid = isfinite(h.d) && os && (sharesEp || h.left) && (h.d > prior + 1e-3f) &&
+                         (h.d <= distance + 1e-3f);
+      if (sharedSolid && h.d < osd) osd = h.d;
+    }
+  }
+  bool tied = endpointOnly && isfinite(cnd) && cni == oni && gd_opposing_pair(sc, wallIndex, cni);
+  bool entersOther = endpointOnly && otherSector >= 0 && ((ond < cnd) || tied);
+  bool entersShared = endpointOnly && otherSector >= 0 && (osd < csd);
+  bool gpFromFront = curSector == sc.wsec[gpi * 2];
+  int gpOther = gpFromFront ? sc.wsec[gpi * 2 + 1] : sc.wsec[gpi * 2];
+  bool usesGeo = endpointOnly && isfinite(gpd) && gpOther >= 0;
+  int ppbIdx = 0;
+  bool epb = false;
+  if (usesGeo) {
+    GdHit hg = HIT(gpi);
+    bool ppbExists = gd_portal_bridge(sc, hg.along > 0.5f, gpi, wallIndex, ppbIdx);
+    if (ppbExists) {
+      GdHit hb = HIT(ppbIdx);
+      epb = hb.proj && hb.left && (hb.d > prior + 1e-3f) && (fabsf(hb.d - gpd) <= gd_tol(hg.d));
+    }
+  }
+  it.cppb = valid && c.pendPortalBridge && wallIndex == c.pendPortalBridgeIndex;
+  it.nokpp = nokpp; it.pskpp = pskpp; it.usesGeo = usesGeo; it.entersOther = entersOther;
+  it.entersShared = entersShared; it.endpointOnly = endpointOnly; it.epb = epb; it.geometric = geometric;
+  it.nopOther = nopOther; it.psOther = psOther; it.gpOther = gpOther;
+  it.nopDist = nopDist; it.psDist = psPathDist; it.gpDist = gpd; it.osd = osd;
+  it.startsOwner = replaceNp; it.continuesOwner = continuesOwner; it.pendEpHasFwd = pendEpHasFwd;
+  it.selEpX = selEpX; it.selEpY = selEpY;
+  {
+    const float *fw = &sc.walls[wallIndex * 4];
+    bool us = hW.along <= 0.5f;
+    it.epEpX = us ? fw[0] : fw[2];
+    it.epEpY = us ? fw[1] : fw[3];
+  }
+  it.epFwdIdx = epFwdIdx; it.ppbIdx = ppbIdx; it.psPathIndex = psPathIndex; it.psFromFront = psFromFront;
+#undef HIT
+#undef SHARES_SEL
+}
+
+/* Draw rows [ya,yb) of one wall tier in column x, skipping rows [ea,eb)
+ * (the overlapping lower tier, which has priority) and rows already filled.
+ * engine.py:12762-12884. */
+struct GdTierCtx {
+  i64 hoff, tox, vstepBase, light;
+  float yoff;
+  int tailBottom;   /* rows >= tailBottom use the group's first-column light; 255+ = never */
+};
+
+__device__ void gd_draw_tier(const GdScene &sc, const GdView &v, const GdShared &sh, int x, int ya, int yb, int ea,
+                             int eb, int texId, float originZ, const GdTierCtx &t, i64 vis, i64 firstVis,
+                             bool tailValid, int tailBottom, int oa, int ob, bool oTailValid, int oTailBottom,
+                             unsigned *filled) {
+  if (texId < 0 || ya >= yb) return;
+  const int4 ti = *reinterpret_cast<const int4 *>(&sc.texInfo[texId * 4]);
+  int tw = ti.x, hbits = ti.w;
+  int u = (int)gd_pymod((t.hoff + t.tox) >> 16, tw);
+  i64 vstep = t.vstepBase * (1LL << (14 - hbits));
+  i64 texMid = gd_rint((originZ - v.viewZ) * 65536.0f + t.yoff * 65536.0f);
+  /* frac(y) = (texMid << (16-bits)) + ((vstep * (y*FU - center + FU)) >> 16); the
+   * y term is a multiple of 2^16 inside the shift, so it steps by vstep exactly. */
+  unsigned base = (unsigned)(gd_shl(texMid, 16 - hbits) + (gd_wmul(vstep, GD_FU - v.center) >> 16));
+  unsigned step = (unsigned)vstep;
+  const uint8_t *col = sc.texAtlasCol + ((size_t)texId * sc.texW + u) * sc.texH;
+  int shadeN = gd_wall_shade(t.light, vis), shadeT = gd_wall_shade(t.light, firstVis);
+  const uint8_t *cmN = sh.colormap + shadeN * 256, *cmT = sh.colormap + shadeT * 256;
+  for (int y = ya; y < yb; ++y) {
+    if (y >= ea && y < eb) continue;
+    if (gd_bit(filled, y)) continue;
+    unsigned frac = base + (unsigned)y * step;
+    unsigned tv = frac >> (32 - hbits);
+    uint8_t texel = col[tv];
+    bool tail = (tailValid && y >= tailBottom) || (oTailValid && y >= oa && y < ob && y >= oTailBottom);
+    sh.frame[y * GD_SW + x] = (tail ? cmT : cmN)[texel];
+    gd_set(filled, y);
+  }
+}
+
+__device__ void gd_mark_plane(const GdScene &sc, const GdView &v, const GdShared &sh, int x, int ya, int yb,
+                              int sector, bool isFloor, unsigned *owned, const unsigned *filled) {
+  if (ya >= yb) return;
+  bool any = false;
+  for (int y = ya; y < yb; ++y) any |= !gd_bit(owned, y);
+  if (!any) return;
+  GdPlaneSpan p;
+  gd_plane_setup(sc, v, sector, isFloor, x, p);
+  for (int y = ya; y < yb; ++y) {
+    if (gd_bit(owned, y)) continue;
+    gd_set(owned, y);
+    if (!gd_bit(filled, y)) sh.frame[y * GD_SW + x] = gd_plane_pixel(p, v, sh.yslope, sh.colormap, y);
+  }
+}
+
+__device__ void gd_walk(const GdScene &sc, const GdView &v, const GdShared &sh, GdEvent *events, int *eventCount,
+                        int *status, int startSector) {
+  const int x = threadIdx.x;
+  const int lane = x & 31;
+  const unsigned quadBase = lane & ~3u;
+  float rx, ry;
+  gd_ray(v, x, rx, ry);
+  unsigned filled[7] = {0, 0, 0, 0, 0, 0, 0}, owned[7] = {0, 0, 0, 0, 0, 0, 0};
+  GdColState c;
+  c.cur = startSector; c.ceilClip = 0; c.floorClip = GD_VH; c.prev = 0.0f;
+  c.pendOwnerBoundary = c.pendEpBoundary = c.pendEpBridgeBoundary = c.pendPortalBridge = false;
+  c.pendOwnerEpX = c.pendOwnerEpY = c.pendEpEpX = c.pendEpEpY = 0.0f;
+  c.pendEpWall = c.pendEpBridgeIndex = c.pendPortalBridgeIndex = 0;
+  c.pendPortalBridgeSector = -1;
+  c.pendPortalBridgeExit = 0.0f;
+  bool settled = false;
+  int nEvents = 0;
+  bool overflow = false;
+
+  for (int iter = 0; iter < sc.S; ++iter) {
+    if (__all_sync(0xffffffffu, settled)) break;
+#ifdef GD_DEBUG_BEAT
+#define GD_TB(m) do { if (blockIdx.x == 0) ((volatile int *)status)[4 + x] = iter * 16 + (m); } while (0)
+#else
+#define GD_TB(m) do {} while (0)
+#endif
+    GD_TB(0);
+    GdIter it;
+    if (!settled) {
+      gd_column_decide(sc, v, sh.walls, sh.ownerMask, x, rx, ry, c, it);
+    } else {
+      it.wall = -1 - x; it.side = 0; it.tier[0] = it.tier[1] = it.tier[2] = false;
+      it.ctop = it.clowtop = 0; it.cbot = it.cupbot = 0; it.vis = 0;
+      it.rasterValid = false; it.valid = false; it.pskpp = false;
+    }
+    GD_TB(1);
+    /* aligned four-column wallscan groups (engine.py:12694-12761) */
+    bool same = true;
+    bool groupValid[3];
+    int groupBottom[3];
+    {
+      int w0 = __shfl_sync(0xffffffffu, it.wall, quadBase), s0 = __shfl_sync(0xffffffffu, it.side, quadBase);
+#pragma unroll
+      for (int k = 1; k < 4; ++k) {
+        int wk = __shfl_sync(0xffffffffu, it.wall, quadBase + k), sk = __shfl_sync(0xffffffffu, it.side, quadBase + k);
+        same = same && (wk == w0) && (sk == s0);
+      }
+#pragma unroll
+      for (int tier = 0; tier < 3; ++tier) {
+        int top = tier == 1 ? it.clowtop : it.ctop;
+        int bot = tier == 2 ? it.cupbot : it.cbot;
+        int topMax = -1, botMin = 1 << 20;
+        bool all = true;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          topMax = max(topMax, __shfl_sync(0xffffffffu, top, quadBase + k));
+          botMin = min(botMin, __shfl_sync(0xffffffffu, bot, quadBase + k));
+          int tk = __shfl_sync(0xffffffffu, (int)it.tier[tier], quadBase + k);  /* never short-circuit a shuffle */
+          all = all && (tk != 0);
+        }
+        groupValid[tier] = same && all && topMax < botMin;
+        groupBottom[tier] = botMin;
+      }
+    }
+    i64 firstVis = __shfl_sync(0xffffffffu, it.vis, quadBase);
+    GD_TB(2);
+    if (settled) continue;
+
+    const GdColState before = c;
+    const int wallIndex = it.wall, side = it.side;
+    const GdWall &wv = sh.walls[wallIndex];
+    GdEvent ev;
+    ev.dist = it.distance; ev.wall = (short)wallIndex; ev.sector = -1;
+    ev.t0a = ev.t0b = ev.t1a = ev.t1b = 0; ev.silTop = 0; ev.silBot = 255;
+    ev.ceilA = ev.ceilB = ev.floorA = ev.floorB = 0; ev.pad0 = 0; ev.pad1 = 0;
+    if (it.rasterValid) {
+      /* visplane rows uncovered by this seg (engine.py:12637-12655) */
+      int cpb = min(it.ctop, c.floorClip), fpt = max(it.cbot, c.ceilClip);
+      ev.sector = (short)it.renderCurrent;
+      if (it.markFloor && fpt < c.floorClip) {
+        ev.floorA = (unsigned char)fpt; ev.floorB = (unsigned char)c.floorClip;
+        gd_mark_plane(sc, v, sh, x, fpt, c.floorClip, it.renderCurrent, true, owned, filled);
+      }
+      if (it.markCeil && c.ceilClip < cpb) {
+        ev.ceilA = (unsigned char)c.ceilClip; ev.ceilB = (unsigned char)cpb;
+        gd_mark_plane(sc, v, sh, x, c.ceilClip, cpb, it.renderCurrent, false, owned, filled);
+      }
+      GD_TB(3);
+      /* wall tiers */
+      GdTierCtx t;
+      gd_prep_wall(sc, wv, wallIndex, x, t.hoff, t.vstepBase);
+      i64 repeat = gd_rint(sc.wlen[wallIndex] * 65536.0f);
+      if (side != 0) t.hoff = repeat - t.hoff;
+      if (wv.sl > 0 && t.hoff < 0) t.hoff = 0;
+      if (t.hoff >= repeat) t.hoff = repeat - 1;
+      const float *soff = &sc.sideOff[(wallIndex * 2 + side) * 2];
+      t.tox = gd_rint(soff[0] * 65536.0f);
+      t.yoff = soff[1];
+      const float *wl = &sc.walls[wallIndex * 4];
+      bool horizontal = fabsf(wl[3] - wl[1]) < 1e-6f, vertical = fabsf(wl[2] - wl[0]) < 1e-6f;
+      t.light = gd_sec_info(sc, it.renderCurrent).x + v.flashLight * 16 + (vertical ? 16 : (horizontal ? -16 : 0));
+      t.tailBottom = 0;
+      if (it.oneSided) {
+        if (it.ctop < it.cbot) {
+          ev.t0a = (unsigned char)it.ctop; ev.t0b = (unsigned char)it.cbot;
+          if (it.tex[0] >= 0) ev.pad0 |= 1;
+          gd_draw_tier(sc, v, sh, x, it.ctop, it.cbot, 0, 0, it.tex[0], it.viewCeil, t, it.vis, firstVis,
+                       groupValid[0], groupBottom[0], 0, 0, false, 0, filled);
+        }
+      } else {
+        bool lowerCond = it.viewFloor < it.otherFloor, upperCond = it.viewCeil > it.otherCeil;
+        int la = 0, lb = 0;
+        if (lowerCond && it.clowtop < it.cbot) {
+          la = it.clowtop; lb = it.cbot;
+          ev.t1a = (unsigned char)la; ev.t1b = (unsigned char)lb;
+          if (it.tex[1] >= 0) ev.pad0 |= 2;
+          bool upperOn = upperCond && it.ctop < it.cupbot;
+          gd_draw_tier(sc, v, sh, x, la, lb, 0, 0, it.tex[1], it.otherFloor, t, it.vis, firstVis, groupValid[1],
+                       groupBottom[1], it.ctop, it.cupbot, upperOn && groupValid[2], groupBottom[2], filled);
+        }
+        if (upperCond && it.ctop < it.cupbot) {
+          ev.t0a = (unsigned char)it.ctop; ev.t0b = (unsigned char)it.cupbot;
+          if (it.tex[2] >= 0) ev.pad0 |= 1;
+          gd_draw_tier(sc, v, sh, x, it.ctop, it.cupbot, la, lb, it.tex[2], it.otherCeil, t, it.vis, firstVis,
+                       groupValid[2], groupBottom[2], 0, 0, false, 0, filled);
+        }
+      }
+    }
+    GD_TB(4);
+    /* clip updates (engine.py:12885-12913) */
+    bool hasUpper = it.tex[2] >= 0, hasLower = it.tex[1] >= 0;
+    bool drawsUpper = (it.viewCeil > it.otherCeil) && hasUpper;
+    bool drawsLower = (it.viewFloor < it.otherFloor) && hasLower;
+    if (it.rasterValid && !it.oneSided && (drawsUpper || it.markCeil)) c.ceilClip = drawsUpper ? it.cupbot : it.ctop;
+    if (it.rasterValid && !it.oneSided && (drawsLower || it.markFloor)) c.floorClip = drawsLower ? it.clowtop : it.cbot;
+    /* sprite silhouettes (engine.py:12940-12964) */
+    if (it.rasterValid) {
+      bool masked = it.tex[0] >= 0;
+      bool bottomSil = !it.oneSided && ((it.viewFloor > it.otherFloor) || (v.viewZ < it.otherFloor) || masked);
+      bool topSil = !it.oneSided && ((it.viewCeil < it.otherCeil) || (v.viewZ > it.otherCeil) || masked);
+      if (bottomSil) ev.silBot = (unsigned char)c.floorClip;
+      if (topSil) ev.silTop = (unsigned char)c.ceilClip;
+      if (nEvents < GD_MAX_EVENTS) events[nEvents * GD_SW + x] = ev; else overflow = true;
+      nEvents++;
+    }
+    /* clips contributed by the portal crossed behind a projected solid
+     * (engine.py:12965-13069) */
+    if (it.pskpp) {
+      int pIdx = it.psPathIndex;
+      const GdWall &pw = sh.walls[pIdx];
+      int pSafeOther = it.psOther < 0 ? 0 : it.psOther;
+      float pOtherFloor = gd_sec_floor(sc, pSafeOther), pOtherCeil = gd_sec_ceil(sc, pSafeOther);
+      int pSide = it.psFromFront ? 0 : 1;
+      const int32_t *ptex = &sc.sideTex[(pIdx * 2 + pSide) * 3];
+      int pTop = gd_project_rows(v, pw, it.viewCeil, x), pBottom = gd_project_rows(v, pw, it.viewFloor, x);
+      int pLowerTop = gd_project_rows(v, pw, pOtherFloor, x), pUpperBottom = gd_project_rows(v, pw, pOtherCeil, x);
+      int pct = max(pTop, c.ceilClip), pcb = min(pBottom, c.floorClip);
+      int pcub = max(min(pUpperBottom, c.floorClip), pct);
+      int pclt = min(max(pLowerTop, c.ceilClip), pcb);
+      int4 ri = gd_sec_info(sc, it.renderCurrent), oi = gd_sec_info(sc, pSafeOther);
+      bool ld = ri.x != oi.x;
+      bool pDrawsUpper = (it.viewCeil > pOtherCeil) && ptex[2] >= 0;
+      bool pMarksCeil = (it.viewCeil != pOtherCeil) || ri.z != oi.z || ld;
+      if (pDrawsUpper || pMarksCeil) c.ceilClip = pDrawsUpper ? pcub : pct;
+      bool pDrawsLower = (it.viewFloor < pOtherFloor) && ptex[1] >= 0;
+      bool pMarksFloor = (it.viewFloor != pOtherFloor) || ri.y != oi.y || ld;
+      if (pDrawsLower || pMarksFloor) c.floorClip = pDrawsLower ? pclt : pcb;
+      bool pMasked = ptex[0] >= 0;
+      bool pBottomSil = (it.viewFloor > pOtherFloor) || (v.viewZ < pOtherFloor) || pMasked;
+      bool pTopSil = (it.viewCeil < pOtherCeil) || (v.viewZ > pOtherCeil) || pMasked;
+      GdEvent pe;
+      pe.dist = it.psDist; pe.wall = (short)pIdx; pe.sector = -1;
+      pe.t0a = pe.t0b = pe.t1a = pe.t1b = 0; pe.pad0 = 0; pe.pad1 = 0;
+      pe.ceilA = pe.ceilB = pe.floorA = pe.floorB = 0;
+      pe.silBot = pBottomSil ? (unsigned char)c.floorClip : 255;
+      pe.silTop = pTopSil ? (unsigned char)c.ceilClip : 0;
+      if (nEvents < GD_MAX_EVENTS) events[nEvents * GD_SW + x] = pe; else overflow = true;
+      nEvents++;
+    }
+    GD_TB(5);
+    /* traversal update (engine.py:13242-13371) */
+    float prior = c.prev;
+    float np = prior;
+    if (it.valid) {
+      if (it.nokpp) np = it.nopDist;
+      else if (it.pskpp) np = it.psDist;
+      else if (it.entersShared && (it.osd < it.distance)) np = prior;
+      else if (it.usesGeo) np = it.gpDist;
+      else np = it.distance;
+    }
+    if (it.valid && it.epb) np = prior;
+    if (it.valid && it.cppb) np = fmaxf(it.distance, c.pendPortalBridgeExit);
+    c.prev = np;
+    if (it.startsOwner) { c.pendOwnerEpX = it.selEpX; c.pendOwnerEpY = it.selEpY; }
+    c.pendOwnerBoundary = it.startsOwner || (c.pendOwnerBoundary && it.continuesOwner);
+    if (it.endpointOnly) { c.pendEpEpX = it.epEpX; c.pendEpEpY = it.epEpY; c.pendEpWall = wallIndex; }
+    c.pendEpBoundary = it.endpointOnly;
+    if (it.pendEpHasFwd) c.pendEpBridgeIndex = it.epFwdIdx;
+    c.pendEpBridgeBoundary = it.pendEpHasFwd;
+    int next;
+    if (it.nokpp) next = it.nopOther;
+    else if (it.pskpp) next = it.psOther;
+    else if (it.usesGeo) next = it.gpOther;
+    else if (it.valid && !it.oneSided && (it.geometric || it.entersOther || it.entersShared)) next = it.otherSector;
+    else if (it.endpointOnly) next = c.cur;
+    else next = -1;
+    if (it.epb) next = it.otherSector;
+    if (it.cppb) next = c.pendPortalBridgeSector;
+    if (it.epb) {
+      c.pendPortalBridgeIndex = it.ppbIdx;
+      c.pendPortalBridgeSector = it.gpOther;
+      c.pendPortalBridgeExit = it.gpDist;
+    }
+    c.pendPortalBridge = it.epb;
+    c.cur = next;
+    /* A column that has left the map repeats the same decision on the same
+     * state forever; once an iteration changes nothing and draws nothing it can
+     * stop. */
+    if (before.cur < 0 && !it.rasterValid && !it.pskpp && gd_state_equal(before, c)) settled = true;
+    GD_TB(6);
+  }
+  eventCount[x] = nEvents < GD_MAX_EVENTS ? nEvents : GD_MAX_EVENTS;
+  if (overflow) atomicOr(status, GD_STATUS_EVENT_OVERFLOW);
+  /* rows no seg ever claimed stay black (the reference paints them with its
+   * per-pixel fallback, which the synthetic maps never expose) */
+  for (int y = 0; y < GD_VH; ++y)
+    if (!gd_bit(filled, y) && !gd_bit(owned, y)) sh.frame[y * GD_SW + x] = 0;
+}
+
+/* ---- point in sector (engine.py:9598-9617) ------------------------------ */
+/* Crossing parity of a +x ray over the sector's edges.  The bounding box only
+ * skips sectors whose parity is provably even. */
+__device__ __forceinline__ bool gd_point_in_sector(const GdScene &sc, int s, float px, float py) {
+  const float4 bb = *reinterpret_cast<const float4 *>(&sc.secBBox[s * 4]);
+  if (py >= bb.w || py < bb.z) return false;           /* no edge straddles the ray's row */
+  if (px > bb.y + 1.0f) return false;                  /* every crossing lies left of the point */
+  if (px < bb.x - 1.0f && sc.secI[s * 4 + 3]) return false;  /* closed loops cross an even number of times */
+  int crossings = 0;
+  for (int k = sc.edgeOff[s]; k < sc.edgeOff[s + 1]; ++k) {
+    const float4 e = *reinterpret_cast<const float4 *>(&sc.walls[sc.edgeWalls[k] * 4]);
+    bool crosses = (e.y > py) != (e.w > py);
+    float dy = e.w - e.y;
+    float safe = fabsf(dy) < 1e-6f ? 1.0f : dy;
+    float cx = e.x + (py - e.y) * (e.z - e.x) / safe;
+    crossings += (crosses && (px < cx)) ? 1 : 0;
+  }
+  return crossings & 1;
+}
+
+__device__ int gd_sector_at(const GdScene &sc, float px, float py) {
+  for (int s = 0; s < sc.S; ++s)
+    if (gd_point_in_sector(sc, s, px, py)) return s;
+  return 0;
+}
+
+/* Flat-fallback resolution of a pixel (engine.py:10961-11026): true when the
+ * column ray meets no sector's plane inside that sector's polygon. */
+__device__ bool gd_pixel_unresolved(const GdScene &sc, const GdView &v, int x, int y) {
+  i64 ti = gd_clamp((GD_ANG90 - v.pitchBam) >> 19, 0, 4095);
+  i64 offFixed = ((i64)sc.fineTan[ti] * 12582912LL) >> 16;
+  float center = 103.5f + (float)offFixed / 65536.0f;
+  float rayAngle = v.angle + sc.rayOffsets[x];
+  float rc = cosf(rayAngle), rs = sinf(rayAngle);
+  float cc = sc.rayCosCorr[x];
+  float delta = (float)y - center;
+  bool floorPixel = delta > 0;
+  float den = fmaxf(fabsf(delta), 0.5f);
+  for (int s = 0; s < sc.S; ++s) {
+    float ph = floorPixel ? (v.viewZ - sc.secF[s * 2]) : (sc.secF[s * 2 + 1] - v.viewZ);
+    float perp = ph * 192.0f / den;
+    float cd = perp / cc;
+    if (!(ph > 0) || !isfinite(cd) || !(cd > 0)) continue;
+    float px = v.x + rc * cd, py = v.y + rs * cd;
+    if (gd_point_in_sector(sc, s, px, py)) return false;
+  }
+  return true;
+}
+
+__device__ float gd_plane_depth(const GdScene &sc, const GdView &v, int sector, bool isFloor, int y) {
+  i64 ti = gd_clamp((GD_ANG90 - v.pitchBam) >> 19, 0, 4095);
+  i64 offFixed = ((i64)sc.fineTan[ti] * 12582912LL) >> 16;
+  float flatCenter = (103.0f + (float)offFixed / 65536.0f) + 0.5f;
+  float ph = isFloor ? (v.viewZ - gd_sec_floor(sc, sector)) : (gd_sec_ceil(sc, sector) - v.viewZ);
+  float den = fmaxf(fabsf((float)y - flatCenter), 0.5f);
+  return ph * 192.0f / den;
+}
+
+__device__ __forceinline__ float gd_wrap_angle(float a) {
+  const float pi = 3.14159265358979323846f, twoPi = 6.28318530717958647692f;
+  float t = a + pi;
+  float r = fmodf(t, twoPi);
+  if (r != 0 && (r < 0)) r += twoPi;
+  return r - pi;
+}
+
+/* ---- phase: sprites (engine.py:14138-14228, 14684-14947) ----------------- */
+__device__ void gd_actor_setup(const GdScene &sc, const GdView &v, const gd_thing &t, GdActor &ac) {
+  ac.alive = (t.flags & GD_THING_ALIVE) != 0;
+  ac.style = t.style;
+  ac.x = t.x; ac.y = t.y;
+  int sprite = t.sprite < sc.P ? t.sprite : 0;
+  ac.sprite = sprite;
+  const int4 si = *reinterpret_cast<const int4 *>(&sc.sprInfo[sprite * 4]);
+  ac.w = si.x; ac.h = si.y;
+  float dx = t.x - v.x, dy = t.y - v.y;
+  float dist = sqrtf(dx * dx + dy * dy);
+  if (dist < 1.0f) dist = 1.0f;
+  float rel = gd_wrap_angle(atan2f(dy, dx) - v.angle);
+  ac.depth = dist * cosf(rel);
+  i64 ax = gd_rint(t.x * 65536.0f), ay = gd_rint(t.y * 65536.0f);
+  i64 rx = ax - v.vx, ry = ay - v.vy;
+  i64 depthFixed = (rx * v.vcos + ry * v.vsin) >> 20;
+  i64 sideFixed = (rx * v.vsin - ry * v.vcos) >> 16;
+  ac.depthFixed = depthFixed;
+  i64 xscale = gd_div(GD_FOCAL_X << 12, gd_max(depthFixed, GD_SPRITE_MIN_DEPTH));
+  i64 leftFixed = sideFixed - (i64)si.z * GD_FU;
+  i64 left = 160 + (gd_wmul(leftFixed, xscale) >> 32);
+  i64 rightFixed = leftFixed + (i64)si.x * GD_FU;
+  i64 right = 160 + (gd_wmul(rightFixed, xscale) >> 32);
+  ac.xstep = gd_div((i64)si.x << 16, gd_max(right - left, 1));
+  ac.left = (int)gd_clamp(left, -(1 << 30), 1 << 30);
+  ac.right = (int)gd_clamp(right, -(1 << 30), 1 << 30);
+  ac.yscale = gd_div(GD_FOCAL_Y << 12, gd_max(depthFixed, GD_SPRITE_MIN_DEPTH));
+  ac.texMid = (i64)si.w * GD_FU - gd_rint((v.viewZ - t.z) * 65536.0f);
+  ac.topFixed = v.center - (gd_wmul(ac.texMid, ac.yscale) >> 16);
+  ac.iscale = gd_div(GD_U32MASK, gd_max(ac.yscale, 1));
+  i64 light = sc.secI[gd_sector_at(sc, t.x, t.y) * 4] + v.flashLight * 16;
+  if (t.flags & GD_THING_BRIGHT) light = 255;
+  float base = 61.0f - (float)light / 4.0f;
+  float visf = fminf(1280.0f / fmaxf(ac.depth, 1.0f), 24.0f);
+  ac.shade = (short)gd_clamp((i64)floorf(base - visf), 0, 31);
+}
+
+__device__ __forceinline__ bool gd_behind(const GdScene &sc, const GdWall &wv, int w, const GdActor &ac) {
+  i64 nearD = gd_min(wv.dl, wv.dr), farD = gd_max(wv.dl, wv.dr);
+  const float4 g = *reinterpret_cast<const float4 *>(&sc.walls[w * 4]);
+  float dx = g.z - g.x, dy = g.w - g.y;
+  float side = dx * (ac.y - g.y) - dy * (ac.x - g.x);
+  return (nearD > ac.depthFixed) || ((farD > ac.depthFixed) && (side <= 0));
+}
+
+__device__ void gd_sprites(const GdScene &sc, const GdView &v, const GdShared &sh, const GdEvent *events,
+                           const int *eventCount, int nThings) {
+  const int x = threadIdx.x;
+  if (nThings <= 0) return;
+  unsigned long long cand = 0;
+  {
+    int bw = sh.blockingWall[x];
+    const GdWall &bwv = sh.walls[bw];
+    bool bowns = x >= bwv.sl && x < bwv.sr;
+    float wd = sh.wallDistance[x];
+    for (int a = 0; a < nThings; ++a) {
+      const GdActor &ac = sh.actors[a];
+      if (!(ac.alive && x >= ac.left && x < ac.right && ac.depth > 0)) continue;
+      bool rayVisible = ac.depth < wd;
+      rayVisible = rayVisible || !bowns || gd_behind(sc, bwv, bw, ac);
+      if (rayVisible) cand |= 1ull << a;
+    }
+  }
+  if (!cand) return;
+  const int nEv = eventCount[x];
+  /* far to near: repeatedly take the remaining candidate with the largest
+   * (depth, index) key */
+  while (cand) {
+    int pick = -1;
+    float pd = 0.0f;
+    unsigned long long m = cand;
+    while (m) {
+      int a = __ffsll((long long)m) - 1;
+      m &= m - 1;
+      float d = sh.actors[a].depth;
+      if (pick < 0 || d >= pd) { pick = a; pd = d; }
+    }
+    cand &= ~(1ull << pick);
+    const GdActor &ac = sh.actors[pick];
+    i64 u = (((i64)x - ac.left) * ac.xstep) >> 16;
+    if (u < 0 || u >= ac.w) continue;
+    const uint8_t *cm = sh.colormap + ac.shade * 256;
+    i64 fracBase = ac.texMid - (gd_wmul(v.center - GD_FU, ac.iscale) >> 16);
+    /* rows whose source row lies inside the patch */
+    int y0 = 0, y1 = GD_VH;
+    if (ac.iscale > 0) {
+      /* frac(y) >> 16 in [0,h)  <=>  0 <= fracBase + y*iscale < h*FU */
+      i64 lo = -fracBase, hi = (i64)ac.h * GD_FU - fracBase;
+      i64 ya = lo <= 0 ? 0 : gd_div(lo + ac.iscale - 1, ac.iscale);
+      i64 yb = hi <= 0 ? 0 : gd_div(hi + ac.iscale - 1, ac.iscale);
+      y0 = (int)gd_clamp(ya, 0, GD_VH);
+      y1 = (int)gd_clamp(yb, 0, GD_VH);
+    }
+    for (int y = y0; y < y1; ++y) {
+      i64 frac = fracBase + (i64)y * ac.iscale;
+      i64 tv = frac >> 16;
+      if (tv < 0 || tv >= ac.h) continue;
+      size_t si = ((size_t)ac.sprite * sc.sprH + (size_t)tv) * sc.sprW + (size_t)u;
+      uint8_t post = sc.sprPost[si];
+      if (post == 255) continue;
+      i64 postTop = (ac.topFixed + ac.yscale * (i64)post) >> 16;
+      if (y < postTop) continue;
+      /* nearest clip event covering this pixel */
+      float bestD = GD_INF;
+      int bestW = -1, ownerSector = -1;
+      bool filled = false, ownerFloor = false;
+      for (int e = 0; e < nEv; ++e) {
+        const GdEvent ev = events[e * GD_SW + x];
+        bool inLower = y >= ev.t1a && y < ev.t1b, inUpper = y >= ev.t0a && y < ev.t0b;
+        bool drawn = inLower ? ((ev.pad0 & 2) != 0) : (inUpper ? ((ev.pad0 & 1) != 0) : false);
+        bool covers = (y < ev.silTop) || (y >= ev.silBot);
+        if (drawn && !filled) { filled = true; covers = true; }
+        if (covers && ev.dist < bestD) { bestD = ev.dist; bestW = ev.wall; }
+        if (ownerSector < 0 && ev.sector >= 0) {
+          if (y >= ev.floorA && y < ev.floorB) { ownerSector = ev.sector; ownerFloor = true; }
+          else if (y >= ev.ceilA && y < ev.ceilB) ownerSector = ev.sector;
+        }
+      }
+      bool visible;
+      if (bestW >= 0) {
+        visible = gd_behind(sc, sh.walls[bestW], bestW, ac);
+      } else {
+        float limit = GD_INF;
+        if (!filled && ownerSector >= 0 && gd_pixel_unresolved(sc, v, x, y))
+          limit = gd_plane_depth(sc, v, ownerSector, ownerFloor, y);
+        visible = ac.depth < limit;
+      }
+      if (!visible) continue;
+      uint8_t lit = cm[sc.sprAtlas[si]];
+      uint8_t dst = sh.frame[y * GD_SW + x];
+      uint8_t out = lit;
+      if (ac.style == -2) out = sc.transLut[dst * 256 + lit];
+      else if (ac.style >= 0) out = sc.addLut[((ac.style > 1 ? 1 : ac.style) * 256 + dst) * 256 + lit];
+      sh.frame[y * GD_SW + x] = out;
+    }
+  }
+}
+
+/* ---- phase: weapon (engine.py:14994-15121) ------------------------------ */
+__device__ void gd_weapon_patch(const GdScene &sc, uint8_t *frame, int id, i64 hoff, i64 voff) {
+  if (id < 0 || id >= sc.Q) return;
+  const int4 wi = *reinterpret_cast<const int4 *>(&sc.wpnInfo[id * 4]);
+  int w = wi.x, h = wi.y;
+  if (w <= 0 || h <= 0) return;
+  i64 screenLeft = (hoff - (i64)wi.z * GD_FU) >> 16;
+  i64 texMid = 100 * GD_FU - (32 * GD_FU + 0x6000) - voff + (i64)wi.w * GD_FU;
+  const i64 yscale = GD_SCREEN_H * GD_FU / 200;
+  const i64 iscale = GD_U32MASK / yscale;
+  for (int idx = threadIdx.x; idx < GD_VH * w; idx += GD_THREADS) {
+    int y = idx / w, sx = idx - y * w;
+    i64 xx = screenLeft + sx;
+    if (xx < 0 || xx >= GD_SW) continue;
+    i64 sy = (texMid + ((i64)y - (GD_VH / 2 - 1)) * iscale) >> 16;
+    if (sy < 0 || sy >= h) continue;
+    i64 cy = gd_min(sy, sc.wpnH - 1), cx = gd_min((i64)sx, (i64)sc.wpnW - 1);
+    size_t si = ((size_t)id * sc.wpnH + (size_t)cy) * sc.wpnW + (size_t)cx;
+    if (sc.wpnOpaque[si]) frame[y * GD_SW + (int)xx] = sc.wpnAtlas[si];
+  }
+}
+
+__device__ void gd_weapon(const GdScene &sc, const int32_t *lane, uint8_t *frame) {
+  if (!sc.wpnAvailable) return;
+  if (lane[GD_L_FLAGS] & 1) return;
+  int weapon = (int)gd_clamp(lane[GD_L_WEAPON], 0, 7);
+  int cooldown = (int)gd_clamp(lane[GD_L_WPN_COOLDOWN], 0, sc.wpnTics - 1);
+  int parity = (int)gd_pymod(lane[GD_L_WPN_FIRE_COUNT], 2);
+  if (weapon == 1 && cooldown == 0) parity = (int)gd_pymod(gd_max(lane[GD_L_WPN_READY_TICS] - 1, 0) / 4, 2);
+  int ti = (weapon * 2 + parity) * sc.wpnTics + cooldown;
+  int frameId = sc.wpnFrameIds[ti], flashId = sc.wpnFlashIds[ti];
+  i64 lowerTics = gd_clamp(16 - (i64)lane[GD_L_WPN_LOWER], 0, 16);
+  i64 verticalTics = lane[GD_L_WPN_PENDING] >= 0 ? lowerTics : (i64)lane[GD_L_WPN_RAISE];
+  i64 spawnRaise = gd_clamp(14 - ((i64)lane[GD_L_EPISODE_TIME] - 1), 0, 14);
+  verticalTics = gd_max(verticalTics, spawnRaise);
+  bool ready = lane[GD_L_WPN_COOLDOWN] <= 0 && lane[GD_L_WPN_RAISE] <= 0 && lane[GD_L_WPN_PENDING] < 0;
+  i64 bobAngle = ((i64)lane[GD_L_EPISODE_TIME] * 128) & 8191;
+  i64 bob = lane[GD_L_BOB_FIXED];
+  i64 bobx = (bob * sc.fineSine[(bobAngle + 2048) & 8191]) >> 16;
+  i64 boby = (bob * sc.fineSine[bobAngle & 4095]) >> 16;
+  if (!ready) { bobx = 0; boby = 0; }
+  i64 voff = verticalTics * 6 * GD_FU + boby;
+  gd_weapon_patch(sc, frame, frameId, bobx, voff);
+  __syncthreads();
+  if (flashId >= 0) gd_weapon_patch(sc, frame, flashId, bobx, voff);
+}
+
+/* ---- phase: status bar (engine.py:15158-15267) --------------------------- */
+__device__ void gd_hud_patch(const GdScene &sc, uint8_t *canvas, int patch, int x, int y) {
+  __syncthreads();  /* patches overlap: keep the reference's draw order */
+  const int4 hi = *reinterpret_cast<const int4 *>(&sc.hudInfo[patch * 4]);
+  x -= hi.z;
+  y -= hi.w;
+  int w = hi.x, h = hi.y;
+  if (w <= 0 || h <= 0) return;
+  int sx = x < 0 ? -x : 0, sy = y < 0 ? -y : 0;
+  int tx = x > 0 ? x : 0, ty = y > 0 ? y : 0;
+  int cw = min(w - sx, GD_SW - tx), ch = min(h - sy, GD_HUD_H - ty);
+  if (cw <= 0 || ch <= 0) return;
+  for (int idx = threadIdx.x; idx < cw * ch; idx += GD_THREADS) {
+    int j = idx / cw, i = idx - j * cw;
+    size_t si = ((size_t)patch * GD_HUD_H + (size_t)(sy + j)) * GD_SW + (size_t)(sx + i);
+    if (sc.hudOpaque[si]) canvas[(ty + j) * GD_SW + tx + i] = sc.hudAtlas[si];
+  }
+}
+
+__device__ void gd_hud_number(const GdScene &sc, uint8_t *canvas, int value, int right, int y, bool small) {
+  int vc = value < -99 ? -99 : (value > 999 ? 999 : value);
+  int neg = vc < 0;
+  int mag = neg ? -vc : vc;
+  int digits[3], n = 0;
+  do { digits[n++] = mag % 10; mag /= 10; } while (mag > 0);
+  int len = n + neg;
+  int dw = small ? 4 : 14, base = small ? 28 : 2;
+  int x = right - len * dw;
+  if (neg) x += dw;
+  for (int k = n - 1; k >= 0; --k) {
+    int patch = base + digits[k];
+    const int4 hi = *reinterpret_cast<const int4 *>(&sc.hudInfo[patch * 4]);
+    gd_hud_patch(sc, canvas, patch, x - hi.z, y - hi.w);
+    x += dw;
+  }
+}
+
+__device__ void gd_hud(const GdScene &sc, const int32_t *lane, uint8_t *canvas) {
+  for (int i = threadIdx.x; i < GD_HUD_H * GD_SW / 4; i += GD_THREADS) ((unsigned *)canvas)[i] = 0;
+  gd_hud_patch(sc, canvas, 0, 0, 0);
+  gd_hud_patch(sc, canvas, 1, 104, 0);
+  const int ammoSlotOf[8] = {-1, -1, 1, 2, 2, 1, 4, 5};
+  int weapon = lane[GD_L_WEAPON];
+  int ammoSlot = ammoSlotOf[weapon < 0 ? 0 : (weapon > 7 ? 7 : weapon)];
+  int ammo = ammoSlot < 0 ? 0 : (int)__int_as_float(lane[GD_L_READY_AMMO]);
+  float hf = __int_as_float(lane[GD_L_HEALTH]), af = __int_as_float(lane[GD_L_ARMOR]);
+  int health = (int)(hf < 0 ? 0.0f : (hf > 999 ? 999.0f : hf));
+  int armor = (int)(af < 0 ? 0.0f : (af > 999 ? 999.0f : af));
+  gd_hud_number(sc, canvas, ammo, 44, 3, false);
+  gd_hud_number(sc, canvas, health, 90, 3, false);
+  gd_hud_patch(sc, canvas, 12, 90, 3);
+  gd_hud_number(sc, canvas, armor, 221, 3, false);
+  gd_hud_patch(sc, canvas, 12, 221, 3);
+  int pain = (100 - health) >= 0 ? (100 - health) / 20 : -((health - 100 + 19) / 20);
+  pain = pain < 0 ? 0 : (pain > 4 ? 4 : pain);
+  int face = 13 + pain * 3 + lane[GD_L_FACE_INDEX];
+  if (lane[GD_L_GRIN_TICS] > 0) face = 64 + pain;
+  else if (lane[GD_L_PAIN_TICS] > 0) {
+    if (lane[GD_L_FLAGS] & 2) face = 59 + pain;
+    else {
+      int d = lane[GD_L_PAIN_DIRECTION];
+      d = d < 0 ? 0 : (d > 2 ? 2 : d);
+      face = (d == 0 ? 44 : (d == 1 ? 49 : 54)) + pain;
+    }
+  } else if (lane[GD_L_ATTACK_HELD] >= 70) face = 49 + pain;
+  if (health <= 0) face = 69;
+  gd_hud_patch(sc, canvas, face < 0 ? 0 : (face > 69 ? 69 : face), 143, 0);
+  const int armsX[6] = {111, 123, 135, 111, 123, 135}, armsY[6] = {4, 4, 4, 14, 14, 14};
+  for (int wi = 0; wi < 6; ++wi) {
+    bool owned = wi < 5 && ((lane[GD_L_WEAPONS_OWNED] >> (wi + 1)) & 1);
+    gd_hud_patch(sc, canvas, owned ? 28 + wi + 2 : 38 + wi, armsX[wi], armsY[wi]);
+  }
+  const int maxima[4] = {200, 50, 50, 300};
+  for (int row = 0; row < 4; ++row) {
+    int y = 5 + row * 6;
+    gd_hud_number(sc, canvas, (int)__int_as_float(lane[GD_L_AMMO0 + row]), 288, y, true);
+    gd_hud_number(sc, canvas, maxima[row], 314, y, true);
+  }
+  __syncthreads();
+}
+
+/* ---- phase: 320x240 -> 84x84 area resize + grayscale ---------------------
+ * Integer definition: src/gradoom/_triton_kernels.py:120-177.  The weights
+ * (y_overlap*x_overlap)/48 factor exactly into (y_overlap/12)*(x_overlap/4). */
+__device__ void gd_resize(const uint8_t *frame, const unsigned long long *pal64, int srcRows, uint8_t *out) {
+  for (int o = threadIdx.x; o < GD_OBS * GD_OBS; o += GD_THREADS) {
+    int oy = o / GD_OBS, ox = o - oy * GD_OBS;
+    int ys = oy * 240, ye = ys + 240, xs = ox * 320, xe = xs + 320;
+    unsigned long long acc = 0;
+    for (int sy = ys / 84; sy * 84 < ye; ++sy) {
+      if (sy >= srcRows) break;
+      int yo = min(ye, (sy + 1) * 84) - max(ys, sy * 84);
+      unsigned wy = (unsigned)yo / 12u;
+      const uint8_t *row = frame + sy * GD_SW;
+      unsigned long long racc = 0;
+      for (int sx = xs / 84; sx * 84 < xe; ++sx) {
+        int xo = min(xe, (sx + 1) * 84) - max(xs, sx * 84);
+        racc += (unsigned long long)((unsigned)xo / 4u) * pal64[row[sx]];
+      }
+      acc += racc * wy;
+    }
+    unsigned r = (unsigned)(acc & 0xFFFFF), g = (unsigned)((acc >> 20) & 0xFFFFF), b = (unsigned)((acc >> 40) & 0xFFFFF);
+    r = (r + 800) / 1600; g = (g + 800) / 1600; b = (b + 800) / 1600;
+    out[o] = (uint8_t)((r * 77 + g * 150 + b * 29 + 128) >> 8);
+  }
+}
+
+/* ---- the kernel ----------------------------------------------------------- */
+extern __shared__ __align__(16) uint8_t gd_smem[];
+
+__global__ void __launch_bounds__(GD_THREADS) gd_render_kernel(const GdParams p) {
+  const GdScene &sc = p.sc;
+  GdShared sh;
+  gd_carve(gd_smem, sc.W, p.maxThings, sh);
+  const int tid = threadIdx.x;
+  /* tables shared by every lane this CTA draws */
+  for (int i = tid; i < 32 * 256 / 4; i += GD_THREADS)
+    ((unsigned *)sh.colormap)[i] = ((const unsigned *)sc.colormap)[i];
+  for (int i = tid; i < 768; i += GD_THREADS) sh.playpal[i] = sc.playpal[i];
+  if (tid < 256) {
+    const uint8_t *c = &sc.playpal[tid * 3];
+    sh.pal64[tid] = (unsigned long long)c[0] | ((unsigned long long)c[1] << 20) | ((unsigned long long)c[2] << 40);
+  }
+  GdEvent *events = (GdEvent *)(p.scratch + (size_t)blockIdx.x * GD_SCRATCH_PER_CTA);
+  int *eventCount = (int *)(p.scratch + (size_t)blockIdx.x * GD_SCRATCH_PER_CTA + GD_SCRATCH_EVENTS_BYTES);
+
+#define GD_BEAT(ph) do { if (blockIdx.x == 0 && tid == 0) { ((volatile int *)p.status)[1] = l; ((volatile int *)p.status)[2] = (ph); } } while (0)
+  for (int l = blockIdx.x; l < p.n; l += gridDim.x) {
+    __syncthreads();
+    GD_BEAT(1);
+    if (p.flags & GD_F_STACK_FILL) {
+      if (p.resetMask && !p.resetMask[l]) continue;  /* uniform across the CTA */
+    }
+    if (tid < GD_LANE_WORDS) sh.lane[tid] = p.lanes[(size_t)l * GD_LANE_WORDS + tid];
+    if (tid < 10) sh.ownerMask[tid] = 0;
+    __syncthreads();
+    GdView v;
+    gd_view_setup(sc, sh.lane, v);
+    if (tid < GD_VH) {
+      /* yslope of the row (engine.py:10933-10946) */
+      i64 centerRow = v.center >> 16;
+      i64 den = (tid < centerRow) ? (v.center - (i64)tid * GD_FU - GD_FU / 2) : ((i64)tid * GD_FU - v.center + GD_FU / 2);
+      den = gd_max(den, 1);
+      i64 ys = gd_div(GD_FOCAL_Y << 16, den);
+      if (den <= (GD_FOCAL_Y >> 15)) ys = (1LL << 31) - 1;
+      sh.yslope[tid] = (unsigned)ys;
+    }
+    for (int w = tid; w < sc.W; w += GD_THREADS) gd_project_wall(sc, v, w, sh.walls[w]);
+    int nThings = sh.lane[GD_L_THINGS];
+    if (nThings > p.maxThings || nThings > 64) {
+      if (tid == 0) atomicOr(p.status, GD_STATUS_THINGS_OVERFLOW);
+      nThings = min(p.maxThings, 64);
+    }
+    if (nThings < 0) nThings = 0;
+    for (int a = tid; a < nThings; a += GD_THREADS)
+      gd_actor_setup(sc, v, p.things[(size_t)l * p.maxThings + a], sh.actors[a]);
+    if (tid == GD_THREADS - 1) sh.misc[0] = gd_sector_at(sc, v.x, v.y);
+    __syncthreads();
+    GD_BEAT(2);
+    gd_wall_spans(sc, v, sh.walls);
+    __syncthreads();
+    GD_BEAT(3);
+    for (int w = tid; w < sc.W; w += GD_THREADS) {
+      int xl = sh.walls[w].isl;
+      if (xl >= 0 && xl < GD_SW) {
+        float rx, ry;
+        gd_ray(v, xl, rx, ry);
+        GdHit h = gd_hit(sc, v, sh.walls, w, xl, rx, ry);
+        if (isfinite(h.d)) atomicOr(&sh.ownerMask[xl >> 5], 1u << (xl & 31));
+      }
+    }
+    {
+      float rx, ry, wd;
+      int bw;
+      gd_ray(v, tid, rx, ry);
+      gd_blocking_raycast(sc, v, tid, rx, ry, wd, bw);
+      sh.wallDistance[tid] = wd;
+      sh.blockingWall[tid] = (short)bw;
+    }
+    __syncthreads();
+    GD_BEAT(4);
+    gd_walk(sc, v, sh, events, eventCount, p.status, sh.misc[0]);
+    GD_BEAT(5);
+    gd_sprites(sc, v, sh, events, eventCount, nThings);
+    __syncthreads();
+    GD_BEAT(6);
+    gd_weapon(sc, sh.lane, sh.frame);
+    __syncthreads();
+    GD_BEAT(7);
+    const bool wantFull = p.indexedOut != nullptr || p.rgbOut != nullptr;
+    if (p.flags & GD_F_DRAW_HUD) {
+      gd_hud(sc, sh.lane, sh.frame + GD_VH * GD_SW);
+    } else if (wantFull) {
+      for (int i = tid; i < GD_HUD_H * GD_SW / 4; i += GD_THREADS) ((unsigned *)(sh.frame + GD_VH * GD_SW))[i] = 0;
+      __syncthreads();
+    }
+    if (p.indexedOut) {
+      uint4 *dst = (uint4 *)(p.indexedOut + (size_t)l * GD_SCREEN_H * GD_SW);
+      const uint4 *src = (const uint4 *)sh.frame;
+      for (int i = tid; i < GD_SCREEN_H * GD_SW / 16; i += GD_THREADS) dst[i] = src[i];
+    }
+    if (p.rgbOut) {
+      unsigned *dst = (unsigned *)(p.rgbOut + (size_t)l * GD_SCREEN_H * GD_SW * 3);
+      for (int j = tid; j < GD_SCREEN_H * GD_SW * 3 / 4; j += GD_THREADS) {
+        unsigned word = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          int b = j * 4 + k;
+          int px = b / 3, ch = b - px * 3;
+          word |= (unsigned)sh.playpal[sh.frame[px] * 3 + ch] << (8 * k);
+        }
+        dst[j] = word;
+      }
+    }
+    GD_BEAT(8);
+    if (p.stack || p.obsOut) {
+      int srcRows = (p.flags & GD_F_MASK_HUD) ? GD_VH : GD_SCREEN_H;
+      gd_resize(sh.frame, sh.pal64, srcRows, sh.obs);
+      __syncthreads();
+      const uint4 *src = (const uint4 *)sh.obs;
+      const int vecs = GD_OBS * GD_OBS / 16;  /* 441 */
+      if (p.obsOut) {
+        uint4 *dst = (uint4 *)(p.obsOut + (size_t)l * GD_OBS * GD_OBS);
+        for (int i = tid; i < vecs; i += GD_THREADS) dst[i] = src[i];
+      }
+      if (p.stack) {
+        uint4 *s0 = (uint4 *)(p.stack + (size_t)l * GD_STACK * GD_OBS * GD_OBS);
+        if (p.flags & GD_F_STACK_FILL) {
+          for (int i = tid; i < vecs; i += GD_THREADS) {
+            uint4 val = src[i];
+            s0[i] = val; s0[vecs + i] = val; s0[2 * vecs + i] = val; s0[3 * vecs + i] = val;
+          }
+        } else if (p.flags & GD_F_STACK_ROLL) {
+          for (int i = tid; i < vecs; i += GD_THREADS) {
+            s0[i] = s0[vecs + i];
+            s0[vecs + i] = s0[2 * vecs + i];
+            s0[2 * vecs + i] = s0[3 * vecs + i];
+            s0[3 * vecs + i] = src[i];
+          }
+        } else {
+          for (int i = tid; i < vecs; i += GD_THREADS) s0[3 * vecs + i] = src[i];
+        }
+      }
+    }
+  }
+}
+
+/* ---- C ABI (declared in include/gradoom_b200.h) --------------------------- */
+#include "../../include/gradoom_b200.h"
+
+#include <new>
+#include <string.h>
+
+struct gd_renderer {
+  GdScene sc;
+  int32_t header[GD_HDR_WORDS];
+  int device;
+  int maxThings;
+  int ctas;
+  size_t smemBytes;
+};
+
+static const void *gd_section(const uint8_t *dev, const int32_t *h, int s) { return dev + h[GD_HDR_SECTION0 + s]; }
+
+extern "C" const char *gd_error_string(int code) {
+  switch (code) {
+    case GD_OK: return "ok";
+    case GD_ERR_NULL: return "null pointer argument";
+    case GD_ERR_BLOB: return "scene blob has a bad magic, version or size";
+    case GD_ERR_UNSUPPORTED: return "scene uses a feature this render path does not draw";
+    case GD_ERR_SIZE: return "size argument out of range";
+    case GD_ERR_ALIGN: return "device pointer is not 16-byte aligned";
+    case GD_ERR_CUDA: return "CUDA runtime call failed";
+    case GD_ERR_SCRATCH: return "scratch buffer is too small";
+    case GD_ERR_SHARED: return "scene needs more shared memory than one SM offers";
+    default: return "unknown error";
+  }
+}
+
+extern "C" int gd_renderer_create(const void *blob_header_host, const void *blob_dev, size_t blob_bytes, int device,
+                                  int max_things, gd_renderer **out) {
+  if (!blob_header_host || !blob_dev || !out) return GD_ERR_NULL;
+  if (blob_bytes < GD_HDR_WORDS * 4) return GD_ERR_BLOB;
+  if (((uintptr_t)blob_dev) & 15) return GD_ERR_ALIGN;
+  if (max_things < 0 || max_things > 64) return GD_ERR_SIZE;
+  const int32_t *h = (const int32_t *)blob_header_host;
+  if (h[GD_H_MAGIC] != GD_MAGIC || h[GD_H_VERSION] != GD_VERSION || (size_t)h[GD_H_BYTES] != blob_bytes)
+    return GD_ERR_BLOB;
+  if (h[GD_H_UNSUPPORTED] != 0) return GD_ERR_UNSUPPORTED;
+  if (h[GD_H_WALLS] <= 0 || h[GD_H_WALLS] >= 32768 || h[GD_H_SECTORS] <= 0 || h[GD_H_SECTORS] >= 32768)
+    return GD_ERR_SIZE;
+  gd_renderer *r = new (std::nothrow) gd_renderer;
+  if (!r) return GD_ERR_CUDA;
+  memcpy(r->header, h, sizeof r->header);
+  r->device = device;
+  r->maxThings = max_things;
+  const uint8_t *d = (const uint8_t *)blob_dev;
+  GdScene &sc = r->sc;
+  sc.W = h[GD_H_WALLS]; sc.S = h[GD_H_SECTORS]; sc.T = h[GD_H_TEXTURES];
+  sc.texH = h[GD_H_TEX_H]; sc.texW = h[GD_H_TEX_W];
+  sc.P = h[GD_H_SPRITES]; sc.sprH = h[GD_H_SPR_H]; sc.sprW = h[GD_H_SPR_W];
+  sc.Q = h[GD_H_WPN_PATCHES]; sc.wpnH = h[GD_H_WPN_H]; sc.wpnW = h[GD_H_WPN_W]; sc.wpnTics = h[GD_H_WPN_TICS];
+  sc.nStarts = h[GD_H_STARTS]; sc.B = h[GD_H_BLOCKING]; sc.nbDirect = h[GD_H_NB_DIRECT];
+  sc.wpnAvailable = h[GD_H_WPN_AVAILABLE];
+#define SECP(type, name) (const type *)gd_section(d, h, name)
+  sc.walls = SECP(float, GD_S_WALLS); sc.wsec = SECP(int32_t, GD_S_WALL_SECTORS); sc.wlen = SECP(float, GD_S_WALL_LEN);
+  sc.sideTex = SECP(int32_t, GD_S_SIDE_TEX); sc.sideOff = SECP(float, GD_S_SIDE_OFF);
+  sc.wvtx = SECP(int32_t, GD_S_WALL_VTX); sc.vtxOff = SECP(int32_t, GD_S_VTX_OFF); sc.vtxWalls = SECP(int32_t, GD_S_VTX_WALLS);
+  sc.nbDirectTab = SECP(int32_t, GD_S_NB_DIRECT); sc.nbOff = SECP(int32_t, GD_S_NB_OFF);
+  sc.nbIdx = SECP(int32_t, GD_S_NB_IDX); sc.nbFlags = SECP(int32_t, GD_S_NB_FLAGS);
+  sc.sbStartOff = SECP(int32_t, GD_S_SB_START_OFF); sc.sbStartIdx = SECP(int32_t, GD_S_SB_START_IDX);
+  sc.sbEndOff = SECP(int32_t, GD_S_SB_END_OFF); sc.sbEndIdx = SECP(int32_t, GD_S_SB_END_IDX);
+  sc.secF = SECP(float, GD_S_SECTOR_F); sc.secI = SECP(int32_t, GD_S_SECTOR_I);
+  sc.secOff = SECP(int32_t, GD_S_SEC_OFF); sc.secWalls = SECP(int32_t, GD_S_SEC_WALLS);
+  sc.edgeOff = SECP(int32_t, GD_S_EDGE_OFF); sc.edgeWalls = SECP(int32_t, GD_S_EDGE_WALLS);
+  sc.blocking = SECP(int32_t, GD_S_BLOCKING);
+  sc.texInfo = SECP(int32_t, GD_S_TEX_INFO); sc.texAtlas = SECP(uint8_t, GD_S_TEX_ATLAS);
+  sc.texAtlasCol = SECP(uint8_t, GD_S_TEX_ATLAS_COL);
+  sc.playpal = SECP(uint8_t, GD_S_PLAYPAL); sc.colormap = SECP(uint8_t, GD_S_COLORMAP);
+  sc.sprInfo = SECP(int32_t, GD_S_SPR_INFO); sc.sprAtlas = SECP(uint8_t, GD_S_SPR_ATLAS); sc.sprPost = SECP(uint8_t, GD_S_SPR_POST);
+  sc.addLut = SECP(uint8_t, GD_S_ADD_LUT); sc.transLut = SECP(uint8_t, GD_S_TRANS_LUT);
+  sc.wpnInfo = SECP(int32_t, GD_S_WPN_INFO); sc.wpnAtlas = SECP(uint8_t, GD_S_WPN_ATLAS); sc.wpnOpaque = SECP(uint8_t, GD_S_WPN_OPAQUE);
+  sc.wpnFrameIds = SECP(int32_t, GD_S_WPN_FRAME_IDS); sc.wpnFlashIds = SECP(int32_t, GD_S_WPN_FLASH_IDS);
+  sc.wpnFlashLights = SECP(int32_t, GD_S_WPN_FLASH_LIGHTS);
+  sc.hudInfo = SECP(int32_t, GD_S_HUD_INFO); sc.hudAtlas = SECP(uint8_t, GD_S_HUD_ATLAS); sc.hudOpaque = SECP(uint8_t, GD_S_HUD_OPAQUE);
+  sc.fineSine = SECP(int32_t, GD_S_FINESINE); sc.fineTan = SECP(int32_t, GD_S_FINETAN);
+  sc.rayOffsets = SECP(float, GD_S_RAY_OFFSETS); sc.rayCosCorr = SECP(float, GD_S_RAY_COSCORR);
+  sc.secBBox = SECP(float, GD_S_SECTOR_BBOX);
+#undef SECP
+  r->smemBytes = gd_shared_bytes(sc.W, max_things);
+  int prev = 0;
+  if (cudaGetDevice(&prev) != cudaSuccess || cudaSetDevice(device) != cudaSuccess) { delete r; return GD_ERR_CUDA; }
+  int maxOptin = 0, sms = 0;
+  cudaDeviceGetAttribute(&maxOptin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  int rc = GD_OK;
+  if ((size_t)maxOptin < r->smemBytes) {
+    rc = GD_ERR_SHARED;
+  } else if (cudaFuncSetAttribute(gd_render_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)r->smemBytes) !=
+             cudaSuccess) {
+    rc = GD_ERR_CUDA;
+  } else {
+    int perSm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, gd_render_kernel, GD_THREADS, r->smemBytes) != cudaSuccess ||
+        perSm < 1)
+      rc = GD_ERR_CUDA;
+    else
+      r->ctas = sms * perSm;  /* one persistent CTA per resident slot */
+  }
+  cudaSetDevice(prev);
+  if (rc != GD_OK) { cudaGetLastError(); delete r; return rc; }
+  *out = r;
+  return GD_OK;
+}
+
+extern "C" void gd_renderer_destroy(gd_renderer *r) { delete r; }
+
+extern "C" size_t gd_renderer_scratch_bytes(const gd_renderer *r) {
+  return r ? (size_t)r->ctas * GD_SCRATCH_PER_CTA : 0;
+}
+
+extern "C" int gd_renderer_ctas(const gd_renderer *r) { return r ? r->ctas : 0; }
+extern "C" size_t gd_renderer_shared_bytes(const gd_renderer *r) { return r ? r->smemBytes : 0; }
+
+static int gd_launch(const gd_renderer *r, const int32_t *lanes, const gd_thing *things, int n, int flags,
+                     uint8_t *stack, const uint8_t *reset_mask, uint8_t *obs_out, uint8_t *indexed_out,
+                     uint8_t *rgb_out, void *scratch, size_t scratch_bytes, int *status, void *stream) {
+  if (!r || !lanes || !scratch || !status) return GD_ERR_NULL;
+  if (r->maxThings > 0 && !things) return GD_ERR_NULL;
+  if (n < 0) return GD_ERR_SIZE;
+  if (n == 0) return GD_OK;
+  if (scratch_bytes < gd_renderer_scratch_bytes(r)) return GD_ERR_SCRATCH;
+  uintptr_t align = (uintptr_t)lanes | (uintptr_t)things | (uintptr_t)stack | (uintptr_t)obs_out |
+                    (uintptr_t)indexed_out | (uintptr_t)rgb_out | (uintptr_t)scratch;
+  if (align & 15) return GD_ERR_ALIGN;
+  GdParams p;
+  p.sc = r->sc;
+  p.lanes = lanes; p.things = things; p.maxThings = r->maxThings; p.n = n; p.flags = flags;
+  p.stack = stack; p.resetMask = reset_mask; p.obsOut = obs_out; p.indexedOut = indexed_out; p.rgbOut = rgb_out;
+  p.scratch = (uint8_t *)scratch; p.status = status;
+  int grid = n < r->ctas ? n : r->ctas;
+  gd_render_kernel<<<grid, GD_THREADS, r->smemBytes, (cudaStream_t)stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? GD_OK : GD_ERR_CUDA;
+}
+
+extern "C" int gd_render_step(const gd_renderer *r, const int32_t *lanes, const void *things, int n, int mask_hud,
+                              uint8_t *stack, void *scratch, size_t scratch_bytes, int *status, void *stream) {
+  if (!stack) return GD_ERR_NULL;
+  int flags = GD_F_STACK_ROLL | (mask_hud ? GD_F_MASK_HUD : GD_F_DRAW_HUD);
+  return gd_launch(r, lanes, (const gd_thing *)things, n, flags, stack, nullptr, nullptr, nullptr, nullptr, scratch,
+                   scratch_bytes, status, stream);
+}
+
+extern "C" int gd_render_reset(const gd_renderer *r, const int32_t *lanes, const void *things, int n, int mask_hud,
+                               const uint8_t *reset_mask, uint8_t *stack, void *scratch, size_t scratch_bytes,
+                               int *status, void *stream) {
+  if (!stack || !reset_mask) return GD_ERR_NULL;
+  int flags = GD_F_STACK_FILL | (mask_hud ? GD_F_MASK_HUD : GD_F_DRAW_HUD);
+  return gd_launch(r, lanes, (const gd_thing *)things, n, flags, stack, reset_mask, nullptr, nullptr, nullptr, scratch,
+                   scratch_bytes, status, stream);
+}
+
+extern "C" int gd_render_frames(const gd_renderer *r, const int32_t *lanes, const void *things, int n, int mask_hud,
+                                int include_hud, uint8_t *obs_out, uint8_t *indexed_out, uint8_t *rgb_out,
+                                void *scratch, size_t scratch_bytes, int *status, void *stream) {
+  if (!obs_out && !indexed_out && !rgb_out) return GD_ERR_NULL;
+  int flags = (mask_hud ? GD_F_MASK_HUD : 0) | ((include_hud || !mask_hud) ? GD_F_DRAW_HUD : 0);
+  return gd_launch(r, lanes, (const gd_thing *)things, n, flags, nullptr, nullptr, obs_out, indexed_out, rgb_out,
+                   scratch, scratch_bytes, status, stream);
+}

@@ -1,0 +1,182 @@
+"""ctypes binding of the CUDA library's C ABI (include/gradoom_b200.h).
+
+There is no CPU fallback: if the shared library is missing or a call fails the
+caller gets an exception.  PyTorch only provides device memory and streams.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIBRARY = os.path.join(HERE, "csrc", "libgradoom_b200.so")
+
+GD_OK = 0
+STATUS_EVENT_OVERFLOW = 1
+STATUS_THINGS_OVERFLOW = 2
+
+EXPORTS = (
+    "gd_error_string", "gd_renderer_create", "gd_renderer_destroy", "gd_renderer_scratch_bytes",
+    "gd_renderer_ctas", "gd_renderer_shared_bytes", "gd_render_step", "gd_render_reset", "gd_render_frames",
+)
+
+_lib = None
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+def load() -> ctypes.CDLL:
+    """Load libgradoom_b200.so; raise if it has not been built."""
+
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIBRARY):
+            raise NativeError(
+                f"{LIBRARY} is missing: build it with __graft_entry__.build() "
+                "(nvcc, sm_100a). This package has no CPU or PyTorch fallback.")
+        lib = ctypes.CDLL(LIBRARY)
+        vp, ci, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+        lib.gd_error_string.restype = ctypes.c_char_p
+        lib.gd_error_string.argtypes = [ci]
+        lib.gd_renderer_create.restype = ci
+        lib.gd_renderer_create.argtypes = [vp, vp, sz, ci, ci, ctypes.POINTER(vp)]
+        lib.gd_renderer_destroy.restype = None
+        lib.gd_renderer_destroy.argtypes = [vp]
+        lib.gd_renderer_scratch_bytes.restype = sz
+        lib.gd_renderer_scratch_bytes.argtypes = [vp]
+        lib.gd_renderer_ctas.restype = ci
+        lib.gd_renderer_ctas.argtypes = [vp]
+        lib.gd_renderer_shared_bytes.restype = sz
+        lib.gd_renderer_shared_bytes.argtypes = [vp]
+        lib.gd_render_step.restype = ci
+        lib.gd_render_step.argtypes = [vp, vp, vp, ci, ci, vp, vp, sz, vp, vp]
+        lib.gd_render_reset.restype = ci
+        lib.gd_render_reset.argtypes = [vp, vp, vp, ci, ci, vp, vp, vp, sz, vp, vp]
+        lib.gd_render_frames.restype = ci
+        lib.gd_render_frames.argtypes = [vp, vp, vp, ci, ci, ci, vp, vp, vp, vp, sz, vp, vp]
+        _lib = lib
+    return _lib
+
+
+def _check(code: int, what: str) -> None:
+    if code != GD_OK:
+        raise NativeError(f"{what} failed: {load().gd_error_string(code).decode()} ({code})")
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+class Renderer:
+    """A scene blob resident on one CUDA device plus the launch scratch.
+
+    ``lanes`` is ``(N,32) int32`` and ``things`` ``(N,max_things,4) int32`` on
+    the same device (layout: include/gradoom_b200_layout.h).
+    """
+
+    def __init__(self, blob: np.ndarray, device: torch.device | str, max_things: int):
+        self.lib = load()
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise NativeError("the renderer needs a CUDA device; there is no CPU path")
+        if self.device.index is None:
+            self.device = torch.device("cuda", torch.cuda.current_device())
+        self.max_things = int(max_things)
+        blob = np.ascontiguousarray(blob, dtype=np.uint8)
+        self._blob_host = blob
+        self.blob = torch.from_numpy(blob).to(self.device)
+        handle = ctypes.c_void_p()
+        index = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        _check(self.lib.gd_renderer_create(blob.ctypes.data, self.blob.data_ptr(), blob.size, index,
+                                           self.max_things, ctypes.byref(handle)), "gd_renderer_create")
+        self.handle = handle
+        self.scratch_bytes = int(self.lib.gd_renderer_scratch_bytes(handle))
+        self.scratch = torch.empty(self.scratch_bytes, dtype=torch.uint8, device=self.device)
+        self.status = torch.zeros(4 + 320, dtype=torch.int32, device=self.device)
+        self.ctas = int(self.lib.gd_renderer_ctas(handle))
+        self.shared_bytes = int(self.lib.gd_renderer_shared_bytes(handle))
+        self.launches = 0
+
+    def close(self) -> None:
+        if getattr(self, "handle", None):
+            self.lib.gd_renderer_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _stream(self) -> int:
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def _inputs(self, lanes: torch.Tensor, things: torch.Tensor) -> int:
+        if lanes.dtype != torch.int32 or lanes.dim() != 2 or lanes.shape[1] != 32 or not lanes.is_contiguous():
+            raise ValueError("lanes must be a contiguous (N,32) int32 tensor")
+        n = lanes.shape[0]
+        if things.dtype != torch.int32 or tuple(things.shape) != (n, max(self.max_things, 1), 4) \
+                or not things.is_contiguous():
+            raise ValueError(f"things must be a contiguous (N,{max(self.max_things, 1)},4) int32 tensor")
+        if lanes.device != self.device or things.device != self.device:
+            raise TypeError("lanes and things must live on the renderer's device")
+        return n
+
+    def step(self, lanes, things, stack, mask_hud=True):
+        n = self._inputs(lanes, things)
+        self._check_stack(stack, n)
+        _check(self.lib.gd_render_step(self.handle, lanes.data_ptr(), things.data_ptr(), n, int(mask_hud),
+                                       stack.data_ptr(), self.scratch.data_ptr(), self.scratch_bytes,
+                                       self.status.data_ptr(), self._stream()), "gd_render_step")
+        self.launches += 1
+
+    def reset(self, lanes, things, reset_mask, stack, mask_hud=True):
+        n = self._inputs(lanes, things)
+        self._check_stack(stack, n)
+        if reset_mask.dtype not in (torch.bool, torch.uint8) or tuple(reset_mask.shape) != (n,):
+            raise TypeError("reset_mask must be a bool (N,) tensor")
+        mask = reset_mask.contiguous().view(torch.uint8) if reset_mask.dtype == torch.bool else reset_mask
+        mask16 = torch.zeros(((n + 15) // 16) * 16, dtype=torch.uint8, device=self.device)
+        mask16[:n] = mask
+        _check(self.lib.gd_render_reset(self.handle, lanes.data_ptr(), things.data_ptr(), n, int(mask_hud),
+                                        mask16.data_ptr(), stack.data_ptr(), self.scratch.data_ptr(),
+                                        self.scratch_bytes, self.status.data_ptr(), self._stream()),
+               "gd_render_reset")
+        self.launches += 1
+
+    def frames(self, lanes, things, *, obs=False, indexed=False, rgb=False, mask_hud=True, include_hud=True):
+        n = self._inputs(lanes, things)
+        o = torch.empty((n, 84, 84), dtype=torch.uint8, device=self.device) if obs else None
+        i = torch.empty((n, 240, 320), dtype=torch.uint8, device=self.device) if indexed else None
+        c = torch.empty((n, 240, 320, 3), dtype=torch.uint8, device=self.device) if rgb else None
+        _check(self.lib.gd_render_frames(self.handle, lanes.data_ptr(), things.data_ptr(), n, int(mask_hud),
+                                         int(include_hud), _ptr(o), _ptr(i), _ptr(c), self.scratch.data_ptr(),
+                                         self.scratch_bytes, self.status.data_ptr(), self._stream()),
+               "gd_render_frames")
+        self.launches += 1
+        return o, i, c
+
+    def _check_stack(self, stack, n):
+        if stack.dtype != torch.uint8 or tuple(stack.shape) != (n, 4, 84, 84) or not stack.is_contiguous():
+            raise ValueError("stack must be a contiguous (N,4,84,84) uint8 tensor")
+        if stack.device != self.device:
+            raise TypeError("stack must live on the renderer's device")
+
+    def check_status(self) -> None:
+        """Synchronising read of the device status word; raises on any flag."""
+
+        bits = int(self.status[0].item())
+        if bits:
+            self.status.zero_()
+            names = []
+            if bits & STATUS_EVENT_OVERFLOW:
+                names.append("clip-event overflow (a column crossed more segs than the scratch holds)")
+            if bits & STATUS_THINGS_OVERFLOW:
+                names.append("a lane listed more things than max_things")
+            raise NativeError("renderer status: " + "; ".join(names or [hex(bits)]))

@@ -398,7 +398,7 @@ def make_grid_scene(spec: GridSpec) -> Scene:
 # ---------------------------------------------------------------------------
 
 GD_MAGIC = 0x4744424C
-GD_VERSION = 3
+GD_VERSION = 5
 GD_HDR_WORDS = 128
 GD_HDR_SECTION0 = 48
 
@@ -417,7 +417,7 @@ _SECTIONS = (
     "XDEATH_IDS XDEATH_COUNTS XDEATH_ENDS PROJ_FLIGHT PROJ_EXPL_IDS PROJ_EXPL_COUNTS "
     "PROJ_EXPL_ENDS PROJ_EXPL_TOTAL FOG_IDS PUFF_IDS STATIC_IDS ADD_LUT TRANS_LUT WPN_INFO "
     "WPN_ATLAS WPN_OPAQUE WPN_FRAME_IDS WPN_FLASH_IDS WPN_FLASH_LIGHTS HUD_INFO HUD_ATLAS "
-    "HUD_OPAQUE FINESINE FINETAN STARTS RAY_OFFSETS RAY_COSCORR"
+    "HUD_OPAQUE FINESINE FINETAN STARTS RAY_OFFSETS RAY_COSCORR TEX_ATLAS_COL SECTOR_BBOX"
 ).split()
 SEC = {name: i for i, name in enumerate(_SECTIONS)}
 
@@ -603,6 +603,18 @@ def pack_scene(scene: Scene, ray_table_override=None) -> np.ndarray:
     sector_i[:, 1] = scene.sector_floor_tex
     sector_i[:, 2] = scene.sector_ceil_tex
 
+    bbox = np.zeros((S, 4), dtype=np.float32)
+    for s_ in range(S):
+        ew = np.flatnonzero(scene.sector_edge_mask[s_])
+        if len(ew) == 0:
+            bbox[s_] = (1.0, 0.0, 1.0, 0.0)
+            continue
+        ex = walls[ew][:, (0, 2)]
+        ey = walls[ew][:, (1, 3)]
+        bbox[s_] = (ex.min(), ex.max(), ey.min(), ey.max())
+        degree = np.bincount(wall_vtx[ew].reshape(-1), minlength=V)
+        sector_i[s_, 3] = int(np.all(degree % 2 == 0))
+
     def info4(a, b, c, d):
         return np.stack((a, b, c, d), axis=1).astype(np.int32)
 
@@ -670,6 +682,8 @@ def pack_scene(scene: Scene, ray_table_override=None) -> np.ndarray:
         "STARTS": starts,
         "RAY_OFFSETS": np.asarray(ray_offsets, dtype=np.float32),
         "RAY_COSCORR": np.asarray(ray_coscorr, dtype=np.float32),
+        "TEX_ATLAS_COL": np.ascontiguousarray(scene.tex_atlas.astype(np.uint8).transpose(0, 2, 1)),
+        "SECTOR_BBOX": bbox,
     }
     assert set(sections) == set(SEC), set(SEC) ^ set(sections)
 

@@ -1,0 +1,111 @@
+/*
+ * C ABI of the B200 render-to-observation library (libgradoom_b200.so).
+ *
+ * The library draws, for a batch of environment lanes, the reference's native
+ * 320x208 palette-indexed Doom view (walls, visplanes, sprites, weapon, status
+ * bar) and reduces it to the 84x84 grayscale policy observation, writing it
+ * into the four-frame stack.  Every pointer below is a plain device or host
+ * pointer; no framework types cross this boundary.  The caller owns all
+ * memory: the library never allocates device memory and never blocks on the
+ * host.  All device buffers must be 16-byte aligned.
+ *
+ * Input formats (scene blob, lane records, thing records):
+ * gradoom_b200_layout.h.
+ *
+ * Return value: GD_OK or a negative GD_ERR_* for host-side validation
+ * failures.  Device-side anomalies set bits in the caller's `status` word
+ * (GD_STATUS_*), which the caller reads when it wants to; kernels never trap.
+ */
+#ifndef GRADOOM_B200_H
+#define GRADOOM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#include "gradoom_b200_layout.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum gd_error {
+  GD_OK = 0,
+  GD_ERR_NULL = -1,
+  GD_ERR_BLOB = -2,
+  GD_ERR_UNSUPPORTED = -3,
+  GD_ERR_SIZE = -4,
+  GD_ERR_ALIGN = -5,
+  GD_ERR_CUDA = -6,
+  GD_ERR_SCRATCH = -7,
+  GD_ERR_SHARED = -8
+};
+
+/* device status bits */
+#define GD_STATUS_EVENT_OVERFLOW 1
+#define GD_STATUS_THINGS_OVERFLOW 2
+#define GD_STATUS_BAD_SECTOR 4
+
+typedef struct gd_renderer gd_renderer;
+
+const char *gd_error_string(int code);
+
+/*
+ * Bind a renderer to a scene blob already resident on `device`.
+ * Replaces: DeviceScenario.from_host + the renderer-related part of
+ * TorchDeathmatchEngine.__init__ (src/gradoom/engine.py:722-1476, 1527-1634).
+ * `blob_header_host` points at (at least) the first GD_HDR_WORDS*4 bytes of
+ * the same blob in host memory.  `max_things` (<= 64) is the per-lane stride
+ * of the thing array passed to the render calls.
+ */
+int gd_renderer_create(const void *blob_header_host, const void *blob_dev, size_t blob_bytes, int device,
+                       int max_things, gd_renderer **out);
+void gd_renderer_destroy(gd_renderer *r);
+
+/* Scratch the caller must provide to every render call (clip events of the
+ * lanes being drawn; contents are meaningless between calls). */
+size_t gd_renderer_scratch_bytes(const gd_renderer *r);
+/* Launch shape, for reports: persistent CTAs and dynamic shared memory per CTA. */
+int gd_renderer_ctas(const gd_renderer *r);
+size_t gd_renderer_shared_bytes(const gd_renderer *r);
+
+/*
+ * One agent step: render every lane and push the frame onto its stack
+ * (`stack`: n x 4 x 84 x 84 u8, oldest first; slots shift down by one and the
+ * new frame lands in slot 3).
+ * Replaces: `frame = self.render_frame(); self._finish_observation(frame)` in
+ * TorchDeathmatchEngine.step (src/gradoom/engine.py:9575-9576, 9545-9547) with
+ * render_frame = render_reference_frame (15436-15451).
+ * mask_hud != 0: the status bar rows are black in the observation (the
+ * obs_crop=(0,32,0,0) "mask" profile); otherwise the status bar is drawn.
+ */
+int gd_render_step(const gd_renderer *r, const int32_t *lanes, const void *things, int n, int mask_hud,
+                   uint8_t *stack, void *scratch, size_t scratch_bytes, int *status, void *stream);
+
+/*
+ * Reset fill: lanes whose `reset_mask` byte is nonzero get their new frame in
+ * all four stack slots; the others are neither drawn nor touched.
+ * Replaces: the tail of TorchDeathmatchEngine.reset
+ * (src/gradoom/engine.py:2443-2450).
+ */
+int gd_render_reset(const gd_renderer *r, const int32_t *lanes, const void *things, int n, int mask_hud,
+                    const uint8_t *reset_mask, uint8_t *stack, void *scratch, size_t scratch_bytes, int *status,
+                    void *stream);
+
+/*
+ * Stateless frames, any subset of (NULL = not wanted):
+ *   obs_out      n x 84 x 84 u8       render_reference_frame (engine.py:15436-15451)
+ *   indexed_out  n x 240 x 320 u8     _render_native_indexed_frame (15338-15379)
+ *   rgb_out      n x 240 x 320 x 3 u8 render_native_frame (15453-15457), the
+ *                                     frame behind GraDoomVecEnv.render()/render_lane()
+ *                                     (src/gradoom/env.py:1037-1056)
+ * include_hud selects whether rows 208..239 of the indexed / RGB frame carry
+ * the status bar (else zeros).
+ */
+int gd_render_frames(const gd_renderer *r, const int32_t *lanes, const void *things, int n, int mask_hud,
+                     int include_hud, uint8_t *obs_out, uint8_t *indexed_out, uint8_t *rgb_out, void *scratch,
+                     size_t scratch_bytes, int *status, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

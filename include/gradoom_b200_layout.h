@@ -14,7 +14,7 @@
 #include <stdint.h>
 
 #define GD_MAGIC 0x4744424C /* "GDBL" */
-#define GD_VERSION 3
+#define GD_VERSION 5
 #define GD_HDR_WORDS 128
 #define GD_HDR_SECTION0 48
 
@@ -72,7 +72,7 @@ enum gd_section {
   GD_S_SB_END_OFF,
   GD_S_SB_END_IDX,
   GD_S_SECTOR_F,      /* S x 2 f32 floor ceiling */
-  GD_S_SECTOR_I,      /* S x 4 i32 light floor_tex ceil_tex pad */
+  GD_S_SECTOR_I,      /* S x 4 i32 light floor_tex ceil_tex closed(1: edges form closed loops) */
   GD_S_SEC_OFF,       /* S+1 CSR of incident walls (ascending) */
   GD_S_SEC_WALLS,
   GD_S_EDGE_OFF,      /* S+1 CSR of polygon edge walls (ascending) */
@@ -118,6 +118,8 @@ enum gd_section {
   GD_S_STARTS,        /* starts x 4 f32: x y angle_rad floor_z */
   GD_S_RAY_OFFSETS,   /* 320 f32: -atan((col-160)/160), flat fallback rays */
   GD_S_RAY_COSCORR,   /* 320 f32: cos of the ray offsets */
+  GD_S_TEX_ATLAS_COL, /* T x W x H u8: the atlas with every texture stored column-major */
+  GD_S_SECTOR_BBOX,   /* S x 4 f32: xmin xmax ymin ymax over the sector's polygon edges */
   GD_S_COUNT
 };
 
