@@ -110,4 +110,4 @@ struct __align__(4) GdEvent {
   unsigned char pad0, pad1;
 };
 
-#define GD_MAX_EVENTS 24
+#define GD_MAX_EVENTS 48

@@ -1087,8 +1087,13 @@ __device__ void gd_walk(const GdScene &sc, const GdView &v, const GdShared &sh, 
       bool topSil = !it.oneSided && ((it.viewCeil < it.otherCeil) || (v.viewZ > it.otherCeil) || masked);
       if (bottomSil) ev.silBot = (unsigned char)c.floorClip;
       if (topSil) ev.silTop = (unsigned char)c.ceilClip;
-      if (nEvents < GD_MAX_EVENTS) events[nEvents * GD_SW + x] = ev; else overflow = true;
-      nEvents++;
+      /* a crossing that draws, marks and clips nothing leaves no trace */
+      bool empty = ev.t0a == ev.t0b && ev.t1a == ev.t1b && ev.silTop == 0 && ev.silBot == 255 &&
+                   ev.ceilA == ev.ceilB && ev.floorA == ev.floorB;
+      if (!empty) {
+        if (nEvents < GD_MAX_EVENTS) events[nEvents * GD_SW + x] = ev; else overflow = true;
+        nEvents++;
+      }
     }
     /* clips contributed by the portal crossed behind a projected solid
      * (engine.py:12965-13069) */
@@ -1121,8 +1126,10 @@ __device__ void gd_walk(const GdScene &sc, const GdView &v, const GdShared &sh, 
       pe.ceilA = pe.ceilB = pe.floorA = pe.floorB = 0;
       pe.silBot = pBottomSil ? (unsigned char)c.floorClip : 255;
       pe.silTop = pTopSil ? (unsigned char)c.ceilClip : 0;
-      if (nEvents < GD_MAX_EVENTS) events[nEvents * GD_SW + x] = pe; else overflow = true;
-      nEvents++;
+      if (pBottomSil || pTopSil) {
+        if (nEvents < GD_MAX_EVENTS) events[nEvents * GD_SW + x] = pe; else overflow = true;
+        nEvents++;
+      }
     }
     GD_TB(5);
     /* traversal update (engine.py:13242-13371) */

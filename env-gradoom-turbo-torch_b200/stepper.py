@@ -118,3 +118,158 @@ def advance(sc: gdscene.Scene, lanes: np.ndarray, seed: int, turn_bam: int = 640
     lf[:, gdstate.L_ANGLE] = bam.astype(np.float32) * np.float32(gdstate.BAM_TO_RADIANS)
     lanes[:, gdstate.L_EPISODE_TIME] += 1
     return lanes
+
+
+class LaneStepper:
+    """Device-resident state producer for throughput runs (no parity claim).
+
+    Keeps packed lane / thing records on the device and evolves them with a few
+    elementwise torch ops per step: players turn and move inside the map, the
+    view height follows the floor of the room they stand in, an ATTACK press
+    kills a thing now and then (which feeds the per-lane statistics), episodes
+    time out.  It exposes what ``GraDoomVecEnv`` needs from a producer:
+    ``reset``, ``step``, ``render_inputs``, ``signal_buffer``, ``pending_reset``.
+    """
+
+    SIGNALS = 27  # width of the reference's signal buffer (src/gradoom/engine.py:509-539)
+
+    def __init__(self, sc, num_envs, *, device, k_things=12, max_things=None, frame_skip=2,
+                 episode_timeout=4200, seed=0):
+        import torch
+
+        self.torch = torch
+        self.scene = sc
+        self.spec = sc.meta["spec"]
+        self.num_envs = num_envs
+        self.device = torch.device(device)
+        self.frame_skip = frame_skip
+        self.episode_timeout = episode_timeout
+        self.k = k_things
+        self.max_things = k_things if max_things is None else max_things
+        lanes, things = random_lanes(sc, num_envs, k_things, seed, max_things=self.max_things)
+        self.lanes = torch.from_numpy(lanes).to(self.device)
+        self.things = torch.from_numpy(things).to(self.device)
+        self.floors = torch.as_tensor(sc.sector_heights[:, 0].astype(np.float32), device=self.device)
+        self.signal_buffer = torch.zeros((num_envs, self.SIGNALS), dtype=torch.float32, device=self.device)
+        self.pending_reset = torch.zeros(num_envs, dtype=torch.bool, device=self.device)
+        self.lanes[:, gdstate.L_EPISODE_TIME] = 1
+        self._tick = 0
+
+    # deterministic per-lane pseudo random numbers in [0, 1)
+    def _uniform(self, seeds, salt):
+        torch = self.torch
+        v = (seeds.to(torch.int64) * 2654435761 + salt * 40503 + 12345) & 0xFFFFFFFF
+        v ^= v >> 15
+        v = (v * 2246822519) & 0xFFFFFFFF
+        v ^= v >> 13
+        v = (v * 3266489917) & 0xFFFFFFFF
+        v ^= v >> 16
+        return v.to(torch.float64) / float(1 << 32)
+
+    def _refresh_pose(self, x_fixed, y_fixed, bam, mask):
+        torch = self.torch
+        lanes = self.lanes
+        room = float(self.spec.room)
+        xf = x_fixed.to(torch.float32) / FIXED_UNIT
+        yf = y_fixed.to(torch.float32) / FIXED_UNIT
+        col = torch.clamp((xf / room).to(torch.int64), 0, self.spec.cols - 1)
+        row = torch.clamp((yf / room).to(torch.int64), 0, self.spec.rows - 1)
+        view_z = self.floors[row * self.spec.cols + col] + VIEW_HEIGHT
+        angle = bam.to(torch.float32) * gdstate.BAM_TO_RADIANS
+        signed_bam = torch.where(bam >= (1 << 31), bam - (1 << 32), bam)
+
+        def put(word, value):
+            lanes[:, word] = torch.where(mask, value.to(torch.int32), lanes[:, word])
+
+        put(gdstate.L_X, xf.view(torch.int32))
+        put(gdstate.L_Y, yf.view(torch.int32))
+        put(gdstate.L_ANGLE, angle.view(torch.int32))
+        put(gdstate.L_VIEW_Z, view_z.view(torch.int32))
+        put(gdstate.L_X_FIXED, x_fixed)
+        put(gdstate.L_Y_FIXED, y_fixed)
+        put(gdstate.L_ANGLE_BAM, signed_bam)
+
+    def reset(self, mask, seeds):
+        torch = self.torch
+        width = self.spec.cols * self.spec.room
+        height = self.spec.rows * self.spec.room
+        room_fixed = int(self.spec.room * FIXED_UNIT)
+        margin = 20 * FIXED_UNIT
+
+        def coordinate(extent, salt):
+            v = (self._uniform(seeds, salt) * (extent - 48.0) + 24.0) * FIXED_UNIT
+            v = v.to(torch.int64)
+            rem = v % room_fixed
+            v = v + torch.where(rem < margin, margin - rem, torch.zeros_like(rem))
+            rem = v % room_fixed
+            return v - torch.where(rem > room_fixed - margin, rem - (room_fixed - margin), torch.zeros_like(rem))
+
+        x_fixed = coordinate(width, 1)
+        y_fixed = coordinate(height, 2)
+        bam = (self._uniform(seeds, 3) * float(1 << 32)).to(torch.int64) & 0xFFFFFFFF
+        self._refresh_pose(x_fixed, y_fixed, bam, mask)
+        self.lanes[:, gdstate.L_EPISODE_TIME] = torch.where(
+            mask, torch.ones_like(self.lanes[:, gdstate.L_EPISODE_TIME]), self.lanes[:, gdstate.L_EPISODE_TIME])
+        self.lanes[:, gdstate.L_FLAGS] = torch.where(mask, torch.zeros_like(self.lanes[:, 0]),
+                                                     self.lanes[:, gdstate.L_FLAGS])
+        if self.k > 0:
+            word = self.things[:, :, 3]
+            self.things[:, :, 3] = torch.where(mask[:, None], word | (THING_ALIVE_BIT), word)
+        self.signal_buffer[mask] = 0
+        self.signal_buffer[:, 1] = torch.where(mask, torch.full_like(self.signal_buffer[:, 1], 100.0),
+                                               self.signal_buffer[:, 1])
+        self.pending_reset &= ~mask
+
+    def step(self, buttons):
+        torch = self.torch
+        lanes = self.lanes
+        everyone = torch.ones(self.num_envs, dtype=torch.bool, device=self.device)
+        self._tick += 1
+        b = buttons.to(torch.int64)
+        speed = 1 + b[:, 1]
+        forward = (b[:, 6] - b[:, 5]) * speed
+        strafe = b[:, 3] - b[:, 4]
+        turn = b[:, 8] - b[:, 7]
+        bam = lanes[:, gdstate.L_ANGLE_BAM].to(torch.int64) & 0xFFFFFFFF
+        bam = (bam + turn * (640 << 16) * self.frame_skip) & 0xFFFFFFFF
+        ang = bam.to(torch.float64) * (2.0 * np.pi / (1 << 32))
+        step_units = 6.0 * self.frame_skip * FIXED_UNIT
+        dx = (torch.cos(ang) * forward + torch.sin(ang) * strafe) * step_units
+        dy = (torch.sin(ang) * forward - torch.cos(ang) * strafe) * step_units
+        x_fixed = lanes[:, gdstate.L_X_FIXED].to(torch.int64) + dx.to(torch.int64)
+        y_fixed = lanes[:, gdstate.L_Y_FIXED].to(torch.int64) + dy.to(torch.int64)
+        lo = 20 * FIXED_UNIT
+        x_fixed = torch.clamp(x_fixed, lo, int(self.spec.cols * self.spec.room * FIXED_UNIT) - lo)
+        y_fixed = torch.clamp(y_fixed, lo, int(self.spec.rows * self.spec.room * FIXED_UNIT) - lo)
+        self._refresh_pose(x_fixed, y_fixed, bam, everyone)
+        lanes[:, gdstate.L_EPISODE_TIME] += self.frame_skip
+        moving = ((forward != 0) | (strafe != 0)).to(torch.int32)
+        lanes[:, gdstate.L_BOB_FIXED] = moving * (8 * FIXED_UNIT)
+        # an attack kills the first living thing once in a while
+        rewards = torch.zeros(self.num_envs, dtype=torch.float32, device=self.device)
+        if self.k > 0:
+            lane_ids = torch.arange(self.num_envs, device=self.device, dtype=torch.int64)
+            lucky = self._uniform(lane_ids + self._tick * 7919, 5) < 0.02
+            victim = (self._uniform(lane_ids + self._tick * 104729, 6) * self.k).to(torch.int64).clamp(0, self.k - 1)
+            word = self.things[lane_ids, victim, 3]
+            alive = (word & THING_ALIVE_BIT) != 0
+            kill = (b[:, 0] != 0) & lucky & alive
+            self.things[lane_ids, victim, 3] = torch.where(kill, word & ~THING_ALIVE_BIT, word)
+            rewards = kill.to(torch.float32)
+        time = lanes[:, gdstate.L_EPISODE_TIME]
+        truncated = time >= self.episode_timeout
+        terminated = torch.zeros_like(truncated)
+        self.pending_reset |= truncated
+        sb = self.signal_buffer
+        sb[:, 0] += rewards
+        sb[:, 26] += rewards
+        sb[:, 18] += rewards
+        sb[:, 17] = time.to(torch.float32)
+        sb[:, 20] = self.pending_reset.to(torch.float32)
+        return rewards, terminated, truncated
+
+    def render_inputs(self):
+        return self.lanes, self.things
+
+
+THING_ALIVE_BIT = gdstate.THING_ALIVE << 16

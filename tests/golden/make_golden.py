@@ -1,0 +1,158 @@
+"""Generate the golden fixtures by running the upstream CPU renderer.
+
+Run once on a machine that has the upstream sources:
+
+    python tests/golden/make_golden.py [c1 c2 c4 stack]
+
+For each seeded synthetic scene it resets the upstream engine, injects K
+monsters per lane, replays a seeded uniform action stream and, at a few
+checkpoints, stores the renderer's inputs (lane and thing records built by this
+package's packers from the engine state) together with the upstream outputs:
+the 320x240 palette-indexed frame with status bar, the 84x84 observation of the
+upstream float resize path, and the per-column ray tables.  The fixtures are
+small ``.npz`` files next to this script; tests replay them without the
+upstream sources.
+"""
+
+from __future__ import annotations
+
+import dataclasses
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, HERE)
+
+from __graft_entry__ import load_package  # noqa: E402
+
+load_package()
+from gradoom_b200 import scene as gdscene, state as gdstate  # noqa: E402
+import refbridge  # noqa: E402
+
+PLANS = {
+    # name: (config, lanes, monsters per lane, checkpoints (agent steps))
+    "c1": ("c1", 4, 4, (0, 12, 30)),
+    "c2": ("c2", 2, 12, (0, 16)),
+    "c3": ("c3", 2, 12, (0, 10)),
+    "c4": ("c4", 1, 32, (0, 3)),
+}
+ACTION_SEED = 20260813
+
+
+def action_matrix(act):
+    am = torch.zeros((len(act.DEATHMATCH_ACTIONS), len(act.DEATHMATCH_BUTTONS)), dtype=torch.bool)
+    for i, labels in enumerate(act.DEATHMATCH_ACTIONS):
+        for label in labels:
+            am[i, act.DEATHMATCH_BUTTONS.index(label)] = True
+    return am
+
+
+def make_engine(eng, scn, sc, n, k, seed):
+    cs = refbridge.scene_to_compiled(sc, scn)
+    e = eng.TorchDeathmatchEngine(cs, n, device=torch.device("cpu"), mask_hud=True)
+    e.render_frame = e.render_reference_frame
+    e.reset(torch.ones(n, dtype=torch.bool), torch.arange(n) + 1)
+    g = torch.Generator().manual_seed(seed)
+    spec = sc.meta["spec"]
+    e.enemy_x[:, :k] = torch.rand((n, k), generator=g) * (spec.cols * spec.room - 64) + 32
+    e.enemy_y[:, :k] = torch.rand((n, k), generator=g) * (spec.rows * spec.room - 64) + 32
+    sec = e._sector_at(e.enemy_x[:, :k].reshape(-1), e.enemy_y[:, :k].reshape(-1)).reshape(n, k)
+    e.enemy_z[:, :k] = e.map.sector_heights[sec, 0]
+    e.enemy_type[:, :k] = torch.randint(0, 6, (n, k), generator=g)
+    e.enemy_alive[:, :k] = True
+    e.enemy_angle[:, :k] = torch.rand((n, k), generator=g) * 6.28
+    return e, g
+
+
+def snapshot(e, tab, max_things):
+    things, counts = gdstate.gather_things(e, tab, max_things=max_things)
+    lanes = gdstate.pack_lanes(e, counts)
+    indexed = e._render_native_indexed_frame(include_hud=True).numpy()
+    obs_float = e.render_reference_frame().numpy()
+    return lanes.numpy(), things.numpy(), indexed, obs_float
+
+
+def generate(name, eng, scn, act):
+    cfg, n, k, checkpoints = PLANS[name]
+    sc = gdscene.make_grid_scene(gdscene.GRID_CONFIGS[cfg])
+    e, g = make_engine(eng, scn, sc, n, k, seed=1234)
+    tab = gdstate.SpriteTables(sc, torch.device("cpu"))
+    am = action_matrix(act)
+    ag = torch.Generator().manual_seed(ACTION_SEED)
+    max_things = 64
+    out = {"config": np.asarray(cfg), "checkpoints": np.asarray(checkpoints)}
+    offsets, coscorr = gdscene.ray_tables()
+    out["ray_offsets"], out["ray_coscorr"] = offsets, coscorr
+    step = 0
+    for ci, target in enumerate(checkpoints):
+        while step < target:
+            a = torch.randint(0, 17, (n,), generator=ag)
+            _f, _r, term, trunc = e.step(am[a])
+            done = term | trunc
+            if bool(done.any()):
+                e.reset(done, torch.arange(n) + 1000 * (step + 1))
+            step += 1
+        lanes, things, indexed, obs_float = snapshot(e, tab, max_things)
+        used = max(int(lanes[:, gdstate.L_THINGS].max()), 1)
+        out[f"lanes_{ci}"] = lanes
+        out[f"things_{ci}"] = things[:, :used].copy()
+        out[f"indexed_{ci}"] = indexed
+        out[f"obs_float_{ci}"] = obs_float
+        print(name, "checkpoint", target, "things", used, flush=True)
+    np.savez_compressed(os.path.join(HERE, f"golden_{name}.npz"), **out)
+
+
+def generate_stack(eng, scn, act):
+    """Reset + four consecutive agent steps on c1: inputs of every render and the
+    upstream four-frame stack after each of them (engine.py:9545-9548, 2443-2450)."""
+
+    n, k = 2, 4
+    sc = gdscene.make_grid_scene(gdscene.GRID_CONFIGS["c1"])
+    e, g = make_engine(eng, scn, sc, n, k, seed=77)
+    tab = gdstate.SpriteTables(sc, torch.device("cpu"))
+    am = action_matrix(act)
+    ag = torch.Generator().manual_seed(ACTION_SEED + 1)
+    offsets, coscorr = gdscene.ray_tables()
+    out = {"config": np.asarray("c1"), "ray_offsets": offsets, "ray_coscorr": coscorr}
+    # a masked reset of lane 1 only, as the reference's auto-reset does
+    mask = torch.tensor([False, True])
+    e.reset(mask, torch.tensor([5, 6]))
+    things, counts = gdstate.gather_things(e, tab, max_things=64)
+    lanes = gdstate.pack_lanes(e, counts)
+    used = [max(int(counts.max()), 1)]
+    out["reset_mask"] = mask.numpy()
+    out["lanes_reset"], out["things_reset"] = lanes.numpy(), things.numpy()
+    out["frames_reset"] = e.frames.numpy().copy()
+    for s in range(4):
+        a = torch.randint(0, 17, (n,), generator=ag)
+        e.step(am[a])
+        things, counts = gdstate.gather_things(e, tab, max_things=64)
+        lanes = gdstate.pack_lanes(e, counts)
+        used.append(max(int(counts.max()), 1))
+        out[f"lanes_{s}"], out[f"things_{s}"] = lanes.numpy(), things.numpy()
+        out[f"frames_{s}"] = e.frames.numpy().copy()
+    kmax = max(used)
+    for key in list(out):
+        if key.startswith("things_"):
+            out[key] = out[key][:, :kmax].copy()
+    np.savez_compressed(os.path.join(HERE, "golden_stack.npz"), **out)
+    print("stack fixture done", flush=True)
+
+
+def main(argv):
+    eng, scn, act = refbridge.load_reference()
+    names = argv or ["c1", "c2", "c3", "c4", "stack"]
+    for name in names:
+        if name == "stack":
+            generate_stack(eng, scn, act)
+        else:
+            generate(name, eng, scn, act)
+
+
+if __name__ == "__main__":
+    main(sys.argv[1:])

@@ -1,0 +1,114 @@
+"""The GraDoomVecEnv mirror: tensor contracts and error behaviour of the
+reference's device API (src/gradoom/env.py:851-942, 1037-1066; upstream
+tests/test_env.py:109-242, tests/test_turbo_api_contract.py:326-349, 509-519)."""
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda", 0)
+
+
+def _env(scenes, n=6, **kw):
+    from gradoom_b200 import env as gdenv
+
+    sc, _ = scenes("c1")
+    return gdenv.GraDoomVecEnv(sc, n, device=DEV, max_things=8, **kw)
+
+
+def test_reset_and_step_contracts(pkg, oracle, scenes):
+    e = _env(scenes, render_mode="rgb_array")
+    n = e.num_envs
+    lane = torch.arange(n, device=DEV)
+    obs, signals = e.reset_device(torch.ones(n, dtype=torch.bool, device=DEV), lane + 1)
+    assert obs.shape == (n, 4, 84, 84) and obs.dtype == torch.uint8 and obs.device == DEV
+    assert signals.shape == (n, 27) and signals.dtype == torch.float32
+    assert torch.equal(obs[:, 0], obs[:, 3])
+    t = e.step_device(torch.full((n,), 7, device=DEV, dtype=torch.int64))
+    assert t.observations.data_ptr() == obs.data_ptr()            # live view of the stack buffer
+    assert t.rewards.shape == (n,) and t.terminated.dtype == torch.bool and t.truncated.dtype == torch.bool
+    # what the env shows equals the oracle's rendering of the producer's state
+    lanes, things = e._producer.render_inputs()
+    from gradoom_b200 import scene as gdscene
+
+    expected = oracle.render(gdscene.pack_scene(e.scene), lanes.cpu().numpy(), things.cpu().numpy())["obs"]
+    assert np.array_equal(t.observations[:, 3].cpu().numpy(), expected)
+    a = e.step_and_reset_device(torch.zeros(n, device=DEV, dtype=torch.int32), lane + 100)
+    assert a.final_observations.data_ptr() != a.observations.data_ptr()
+    assert torch.equal(a.final_observations, a.observations)      # nobody was done: identical content
+    frame = e.render()
+    assert isinstance(frame, np.ndarray) and frame.shape == (240, 320, 3) and frame.dtype == np.uint8
+    assert len(e.get_images()) == n
+    e.check_status()
+    e.close()
+    e.close()
+    with pytest.raises(RuntimeError):
+        e.render()
+    with pytest.raises(RuntimeError):
+        e.step_device(torch.zeros(n, device=DEV, dtype=torch.int64))
+
+
+def test_masked_reset_preserves_other_lanes(pkg, scenes):
+    e = _env(scenes)
+    n = e.num_envs
+    lane = torch.arange(n, device=DEV)
+    e.reset_device(torch.ones(n, dtype=torch.bool, device=DEV), lane + 1)
+    for a in (2, 6, 2):
+        e.step_device(torch.full((n,), a, device=DEV, dtype=torch.int64))
+    before = e.step_device(torch.full((n,), 2, device=DEV, dtype=torch.int64)).observations.clone()
+    mask = torch.zeros(n, dtype=torch.bool, device=DEV)
+    mask[1] = True
+    obs, _ = e.reset_device(mask, lane + 50)
+    assert torch.equal(obs[0], before[0]) and torch.equal(obs[2:], before[2:])
+    assert torch.equal(obs[1, 0], obs[1, 3]) and not torch.equal(obs[1], before[1])
+    e.close()
+
+
+def test_timeouts_trigger_the_on_device_auto_reset(pkg, scenes):
+    e = _env(scenes, n=4, episode_timeout=7)
+    n = e.num_envs
+    lane = torch.arange(n, device=DEV)
+    e.reset_device(torch.ones(n, dtype=torch.bool, device=DEV), lane + 1)
+    done_seen = False
+    for step in range(5):
+        t = e.step_and_reset_device(torch.full((n,), 6, device=DEV, dtype=torch.int64), lane + 10 * (step + 1))
+        if bool(t.truncated.any()):
+            done_seen = True
+            assert torch.equal(t.observations[:, 0], t.observations[:, 3])      # refilled stack
+            assert not torch.equal(t.final_observations, t.observations)
+            break
+    assert done_seen
+    e.close()
+
+
+def test_validation_errors(pkg, scenes):
+    e = _env(scenes, n=4)
+    n = 4
+    good = torch.zeros(n, device=DEV, dtype=torch.int64)
+    with pytest.raises(TypeError):
+        e.step_device([0, 0, 0, 0])
+    with pytest.raises(TypeError):
+        e.step_device(good.cpu())
+    with pytest.raises(ValueError):
+        e.step_device(torch.zeros(n + 1, device=DEV, dtype=torch.int64))
+    with pytest.raises(TypeError):
+        e.step_device(torch.zeros(n, device=DEV, dtype=torch.float32))
+    with pytest.raises(TypeError):
+        e.reset_device(torch.ones(n, device=DEV, dtype=torch.uint8), good)
+    with pytest.raises(RuntimeError):
+        e.step(good)                                   # lanes were never reset
+    e.reset_device(torch.ones(n, dtype=torch.bool, device=DEV), good + 1)
+    with pytest.raises(ValueError):
+        e.step(torch.full((n,), 17, device=DEV, dtype=torch.int64))
+    assert e.render() is None                          # render_mode None
+    assert e.get_images() == [None] * n
+    with pytest.raises(TypeError):
+        e.render_lane(True)
+    with pytest.raises(IndexError):
+        e.render_lane(n)
+    hwc = _env(scenes, n=2, obs_layout="hwc")
+    obs, _ = hwc.reset_device(torch.ones(2, dtype=torch.bool, device=DEV), torch.ones(2, device=DEV, dtype=torch.int64))
+    assert obs.shape == (2, 84, 84, 4)
+    e.close()
+    hwc.close()

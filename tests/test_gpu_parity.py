@@ -1,0 +1,220 @@
+"""Parity of the CUDA path, called through the C ABI, with the CPU oracle and
+with the fixtures recorded from the upstream renderer.
+
+Bar: palette-indexed frames, RGB frames, observations and frame stacks equal
+the oracle bit for bit; against the upstream's float32 resize the observation
+is within 1 LSB (upstream tests/test_rendering.py:112-139 grants the same).
+"""
+
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import load_golden, pad_things
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def _renderer(blob, k):
+    from gradoom_b200 import native
+
+    return native.Renderer(blob, DEV, k)
+
+
+def _dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4"])
+def test_cuda_matches_upstream_fixtures(name, pkg, oracle, scenes):
+    data = load_golden(name)
+    _sc, blob = scenes(str(data["config"]), (data["ray_offsets"], data["ray_coscorr"]))
+    r = _renderer(blob, 64)
+    for ci in range(len(data["checkpoints"])):
+        lanes, things = data[f"lanes_{ci}"], pad_things(data[f"things_{ci}"], 64)
+        obs, indexed, rgb = r.frames(_dev(lanes), _dev(things), obs=True, indexed=True, rgb=True)
+        r.check_status()
+        assert np.array_equal(indexed.cpu().numpy(), data[f"indexed_{ci}"])
+        assert np.array_equal(rgb.cpu().numpy(), oracle.rgb(blob, data[f"indexed_{ci}"]))
+        expected = oracle.render(blob, lanes, things)["obs"]
+        assert np.array_equal(obs.cpu().numpy(), expected)
+        diff = np.abs(obs.cpu().numpy().astype(int) - data[f"obs_float_{ci}"].astype(int))
+        assert diff.max() <= 1
+
+
+@pytest.mark.parametrize("name,n,k,seed", [("c1", 64, 4, 1), ("c2", 96, 12, 2), ("c3", 48, 12, 3),
+                                           ("c4", 12, 32, 4), ("c2", 1, 0, 5), ("c1", 3, 1, 6)])
+def test_cuda_matches_oracle_on_seeded_lanes(name, n, k, seed, pkg, oracle, scenes):
+    from gradoom_b200 import stepper
+
+    sc, blob = scenes(name)
+    lanes, things = stepper.random_lanes(sc, n, k, seed=seed)
+    expected = oracle.render(blob, lanes, things, mask_hud=True)
+    r = _renderer(blob, k)
+    obs, indexed, _ = r.frames(_dev(lanes), _dev(things), obs=True, indexed=True)
+    r.check_status()
+    assert np.array_equal(indexed.cpu().numpy(), expected["indexed"])
+    assert np.array_equal(obs.cpu().numpy(), expected["obs"])
+
+
+def test_unmasked_observation_includes_the_status_bar(pkg, oracle, scenes):
+    from gradoom_b200 import stepper
+
+    sc, blob = scenes("c3")
+    lanes, things = stepper.random_lanes(sc, 8, 6, seed=9)
+    expected = oracle.render(blob, lanes, things, mask_hud=False)
+    r = _renderer(blob, 6)
+    obs, _, _ = r.frames(_dev(lanes), _dev(things), obs=True, mask_hud=False)
+    assert np.array_equal(obs.cpu().numpy(), expected["obs"])
+    masked, _, _ = r.frames(_dev(lanes), _dev(things), obs=True, mask_hud=True)
+    assert not np.array_equal(masked.cpu().numpy()[:, 74:], obs.cpu().numpy()[:, 74:])
+    assert masked.cpu().numpy()[:, 75:].max() == 0
+
+
+def test_frames_without_status_bar_have_black_rows(pkg, scenes):
+    from gradoom_b200 import stepper
+
+    sc, blob = scenes("c1")
+    lanes, things = stepper.random_lanes(sc, 4, 4, seed=2)
+    r = _renderer(blob, 4)
+    _, a, _ = r.frames(_dev(lanes), _dev(things), indexed=True, include_hud=False)
+    _, b, _ = r.frames(_dev(lanes), _dev(things), indexed=True, include_hud=True)
+    assert a[:, 208:].max().item() == 0
+    assert torch.equal(a[:, :208], b[:, :208]) and b[:, 208:].max().item() > 0
+
+
+def test_stack_roll_and_masked_reset_fill(pkg, oracle, scenes):
+    """engine.py:9545-9548 (roll + append) and 2443-2450 (masked fill)."""
+
+    from gradoom_b200 import stepper
+
+    sc, blob = scenes("c1")
+    n, k = 16, 4
+    r = _renderer(blob, k)
+    rng = np.random.default_rng(0)
+    stack_ref = rng.integers(0, 256, size=(n, 4, 84, 84), dtype=np.uint8)
+    stack = _dev(stack_ref)
+    lanes, things = stepper.random_lanes(sc, n, k, seed=21)
+    mask = rng.random(n) < 0.5
+    mask[0], mask[1] = True, False
+    obs = oracle.render(blob, lanes, things)["obs"]
+    oracle.stack_update(stack_ref, obs, reset_mask=mask)
+    r.reset(_dev(lanes), _dev(things), _dev(mask), stack)
+    assert np.array_equal(stack.cpu().numpy(), stack_ref)
+    for step in range(5):
+        stepper.advance(sc, lanes, seed=100 + step)
+        obs = oracle.render(blob, lanes, things)["obs"]
+        oracle.stack_update(stack_ref, obs)
+        r.step(_dev(lanes), _dev(things), stack)
+        assert np.array_equal(stack.cpu().numpy(), stack_ref), f"step {step}"
+    r.check_status()
+
+
+def test_cuda_replays_the_upstream_stack_fixture(pkg, oracle, scenes):
+    data = load_golden("stack")
+    _sc, blob = scenes("c1", (data["ray_offsets"], data["ray_coscorr"]))
+    r = _renderer(blob, 64)
+    stack = _dev(data["frames_reset"])
+    r.reset(_dev(data["lanes_reset"]), _dev(pad_things(data["things_reset"], 64)), _dev(data["reset_mask"]), stack)
+    masked = data["reset_mask"].astype(bool)
+    got = stack.cpu().numpy()
+    assert np.array_equal(got[~masked], data["frames_reset"][~masked])
+    assert np.abs(got[masked].astype(int) - data["frames_reset"][masked].astype(int)).max() <= 1
+    for s in range(4):
+        r.step(_dev(data[f"lanes_{s}"]), _dev(pad_things(data[f"things_{s}"], 64)), stack)
+        assert np.abs(stack.cpu().numpy().astype(int) - data[f"frames_{s}"].astype(int)).max() <= 1
+
+
+def test_full_size_batch_properties(pkg, oracle, scenes):
+    """4096 lanes on the 64-sector map: size-independent properties plus an
+    oracle check of a lane sample."""
+
+    from gradoom_b200 import stepper
+
+    sc, blob = scenes("c2")
+    n, k = 4096, 12
+    lanes, things = stepper.random_lanes(sc, n, k, seed=11)
+    r = _renderer(blob, k)
+    dl, dt = _dev(lanes), _dev(things)
+    stack = torch.zeros((n, 4, 84, 84), dtype=torch.uint8, device=DEV)
+    r.reset(dl, dt, torch.ones(n, dtype=torch.bool, device=DEV), stack)
+    first = stack.clone()
+    assert torch.equal(first[:, 0], first[:, 3])           # fill: all slots equal
+    r.step(dl, dt, stack)
+    assert torch.equal(stack[:, :3], first[:, 1:])          # roll moved the old slots down
+    assert torch.equal(stack[:, 3], first[:, 3])            # same state, same frame: deterministic
+    obs, _, _ = r.frames(dl, dt, obs=True)
+    assert torch.equal(obs, stack[:, 3])                    # stateless call agrees with the stack path
+    r.check_status()
+    sample = np.arange(0, n, 97)
+    expected = oracle.render(blob, lanes[sample], things[sample])["obs"]
+    assert np.array_equal(obs.cpu().numpy()[sample], expected)
+    # idempotence of a fill with an all-false mask
+    before = stack.clone()
+    r.reset(dl, dt, torch.zeros(n, dtype=torch.bool, device=DEV), stack)
+    assert torch.equal(stack, before)
+
+
+def test_known_answer_sprite_scenes(pkg):
+    import kat
+    from gradoom_b200 import scene as gdscene
+
+    sc, (lanes, things), expected = kat.transparent_case()
+    r = _renderer(gdscene.pack_scene(sc), things.shape[1])
+    _, indexed, _ = r.frames(_dev(lanes), _dev(things), indexed=True)
+    assert indexed[0, 103, 160].item() == expected
+
+
+def test_abi_argument_validation(pkg, scenes):
+    from gradoom_b200 import native, stepper
+
+    sc, blob = scenes("c1")
+    r = _renderer(blob, 4)
+    lanes, things = stepper.random_lanes(sc, 4, 4, seed=1)
+    dl, dt = _dev(lanes), _dev(things)
+    stack = torch.zeros((4, 4, 84, 84), dtype=torch.uint8, device=DEV)
+    lib = native.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    # too little scratch
+    rc = lib.gd_render_step(r.handle, dl.data_ptr(), dt.data_ptr(), 4, 1, stack.data_ptr(), r.scratch.data_ptr(),
+                            16, r.status.data_ptr(), stream)
+    assert rc == -7
+    # misaligned pointer
+    rc = lib.gd_render_step(r.handle, dl.data_ptr() + 4, dt.data_ptr(), 4, 1, stack.data_ptr(),
+                            r.scratch.data_ptr(), r.scratch_bytes, r.status.data_ptr(), stream)
+    assert rc == -5
+    # null stack, negative n, empty batch
+    assert lib.gd_render_step(r.handle, dl.data_ptr(), dt.data_ptr(), 4, 1, None, r.scratch.data_ptr(),
+                              r.scratch_bytes, r.status.data_ptr(), stream) == -1
+    assert lib.gd_render_step(r.handle, dl.data_ptr(), dt.data_ptr(), -1, 1, stack.data_ptr(),
+                              r.scratch.data_ptr(), r.scratch_bytes, r.status.data_ptr(), stream) == -4
+    assert lib.gd_render_step(r.handle, dl.data_ptr(), dt.data_ptr(), 0, 1, stack.data_ptr(),
+                              r.scratch.data_ptr(), r.scratch_bytes, r.status.data_ptr(), stream) == 0
+    # a corrupted blob header is refused
+    bad = blob.copy()
+    bad[:4] = 0
+    handle = ctypes.c_void_p()
+    assert lib.gd_renderer_create(bad.ctypes.data, r.blob.data_ptr(), bad.size, 0, 4, ctypes.byref(handle)) == -2
+    with pytest.raises(ValueError):
+        r.step(dl.to(torch.int64), dt, stack)
+    with pytest.raises(TypeError):
+        r.step(dl.cpu(), dt, stack)
+    torch.cuda.synchronize()
+
+
+def test_thing_overflow_sets_the_status_word(pkg, scenes):
+    from gradoom_b200 import native, stepper, state as gdstate
+
+    sc, blob = scenes("c1")
+    lanes, things = stepper.random_lanes(sc, 2, 4, seed=1)
+    lanes[:, gdstate.L_THINGS] = 9          # claims more records than the stride holds
+    r = _renderer(blob, 4)
+    r.frames(_dev(lanes), _dev(things), obs=True)
+    with pytest.raises(native.NativeError):
+        r.check_status()
+    r.frames(_dev(stepper.random_lanes(sc, 2, 4, seed=1)[0]), _dev(things), obs=True)
+    r.check_status()                        # cleared after being reported

@@ -1,0 +1,205 @@
+"""Host-side logic that needs no GPU: blob packing, state packing, the C ABI's
+export table, the boundary's validation errors and the lane-sharding helpers."""
+
+import ctypes
+import os
+import re
+import types
+
+import numpy as np
+import pytest
+import torch
+
+import __graft_entry__ as entry
+
+ROOT = entry.ROOT
+
+
+def test_blob_header_and_sections_are_consistent(pkg, scenes):
+    from gradoom_b200 import scene as gdscene
+
+    sc, blob = scenes("c1")
+    header = blob[: gdscene.GD_HDR_WORDS * 4].view(np.int32)
+    assert header[gdscene.H["MAGIC"]] == gdscene.GD_MAGIC
+    assert header[gdscene.H["BYTES"]] == blob.size
+    assert header[gdscene.H["WALLS"]] == sc.num_walls == 40
+    assert header[gdscene.H["SECTORS"]] == 16
+    assert header[gdscene.H["UNSUPPORTED"]] == 0
+    offsets = header[gdscene.GD_HDR_SECTION0: gdscene.GD_HDR_SECTION0 + len(gdscene.SEC)]
+    assert (offsets % 16 == 0).all() and (np.diff(offsets) > 0).all() and offsets[-1] < blob.size
+    # the layout header and the packer agree on the section list
+    text = open(os.path.join(ROOT, "include", "gradoom_b200_layout.h")).read()
+    declared = re.findall(r"^\s+GD_S_([A-Z0-9_]+)", text, flags=re.M)
+    declared = [d for d in declared if d != "COUNT"]
+    assert declared == list(gdscene._SECTIONS)
+    version = int(re.search(r"#define GD_VERSION (\d+)", text).group(1))
+    assert version == gdscene.GD_VERSION
+
+
+def test_fine_tables_have_the_doom_landmarks(pkg):
+    from gradoom_b200 import scene as gdscene
+
+    sine = gdscene.fine_sine_table()
+    assert sine[0] == 0 and sine[2048] == 65536 and sine[6144] == -65536 and sine[4096] == 0
+    assert sine[1] == 50 and sine[1024] == 46340
+    tan = gdscene.fine_tangent_table()
+    assert len(tan) == 4096 and tan[2048] == 0 and tan[3072] == 65536
+
+
+def test_generator_orientation_front_sector_on_the_right(pkg, scenes):
+    sc, _ = scenes("c2")
+    for w in range(sc.num_walls):
+        x1, y1, x2, y2 = sc.walls[w]
+        front = sc.wall_sectors[w, 0]
+        r, c = divmod(int(front), 8)
+        cx, cy = (c + 0.5) * 256.0, (r + 0.5) * 256.0
+        cross = (x2 - x1) * (cy - y1) - (y2 - y1) * (cx - x1)
+        assert cross < 0  # room centre on the right of v1 -> v2
+
+
+def _fake_engine(n=3, slots=6):
+    g = torch.Generator().manual_seed(5)
+    e = types.SimpleNamespace()
+    fixed = torch.randint(20 << 16, 900 << 16, (n,), generator=g)
+    e._x_fixed, e._y_fixed = fixed.clone(), fixed.flip(0).clone()
+    e.x, e.y = e._x_fixed.float() / 65536, e._y_fixed.float() / 65536
+    e._angle_bam = torch.randint(0, 1 << 32, (n,), generator=g)
+    e.angle = e._angle_bam.float() * (2 * np.pi / (1 << 32))
+    e._pitch_bam = torch.zeros(n, dtype=torch.int64)
+    e.view_z = torch.full((n,), 41.0)
+    e.player_dead = torch.tensor([False, True, False])
+    e.mugshot_ouch = torch.tensor([True, False, False])
+    e.episode_time = torch.tensor([1, 20, 300], dtype=torch.int32)
+    e._player_bob_fixed = torch.tensor([0, 1 << 16, 5], dtype=torch.int64)
+    e.selected_weapon = torch.tensor([1, 3, 6])
+    e.selected_weapon_variant = torch.tensor([True, True, False])
+    for name in ("weapon_state_cooldown", "weapon_fire_count", "weapon_ready_tics", "weapon_raise_cooldown",
+                 "weapon_lower_cooldown", "mugshot_pain_tics", "mugshot_grin_tics", "attack_held_tics"):
+        setattr(e, name, torch.arange(n, dtype=torch.int32))
+    e.pending_weapon = torch.tensor([-1, 2, -1])
+    e.health, e.armor = torch.tensor([100.0, 0.0, 55.5]), torch.tensor([0.0, 200.0, 1.0])
+    e.hud_ready_ammo = torch.tensor([50.0, 7.0, 0.0])
+    e.hud_ammo_counts = torch.arange(n * 4, dtype=torch.float32).reshape(n, 4)
+    e.weapons = torch.tensor([[1, 1, 0, 0, 0, 0], [1, 1, 1, 0, 0, 1], [1, 0, 0, 0, 0, 0]], dtype=torch.float32)
+    e.mugshot_face_index = torch.tensor([0, 1, 2])
+    e.mugshot_pain_direction = torch.tensor([1, 0, 2])
+    return e
+
+
+def test_pack_lanes_fields(pkg):
+    from gradoom_b200 import state as gdstate
+
+    e = _fake_engine()
+    lanes = gdstate.pack_lanes(e, torch.tensor([4, 5, 6])).numpy()
+    assert lanes.shape == (3, 32) and lanes.dtype == np.int32
+    assert np.array_equal(lanes[:, gdstate.L_X].view(np.float32), e.x.numpy())
+    assert np.array_equal(lanes[:, gdstate.L_X_FIXED], e._x_fixed.numpy())
+    assert np.array_equal(lanes[:, gdstate.L_ANGLE_BAM].view(np.uint32), e._angle_bam.numpy().astype(np.uint32))
+    assert lanes[:, gdstate.L_FLAGS].tolist() == [2, 1, 0]
+    assert lanes[:, gdstate.L_THINGS].tolist() == [4, 5, 6]
+    # slot 1 + variant -> chainsaw (1); slot 3 + variant -> super shotgun (4); slot 6 -> plasma (7)
+    assert lanes[:, gdstate.L_WEAPON].tolist() == [1, 4, 7]
+    assert lanes[:, gdstate.L_WEAPONS_OWNED].tolist() == [3, 0b100111, 1]
+    # an overridden public coordinate wins over the retained fixed value
+    e.x = e.x + 1.0
+    lanes2 = gdstate.pack_lanes(e).numpy()
+    assert np.array_equal(lanes2[:, gdstate.L_X_FIXED], np.round(e.x.numpy() * 65536).astype(np.int32))
+
+
+def test_sprite_rotation_known_answers(pkg):
+    """Upstream tests/test_rendering.py:31-52."""
+
+    import math
+    from gradoom_b200 import state as gdstate
+
+    viewer = torch.tensor((0.0, math.pi / 2, math.pi, -math.pi / 2))
+    assert gdstate.sprite_rotation(viewer, torch.zeros_like(viewer)).tolist() == [0, 2, 4, 6]
+    boundary = torch.tensor(-math.pi / 8, dtype=torch.float32)
+    below = torch.nextafter(boundary, torch.tensor(float("-inf")))
+    assert gdstate.sprite_rotation(below, torch.zeros_like(below)).item() == 0
+
+
+def test_pack_things_roundtrip(pkg):
+    from gradoom_b200 import state as gdstate
+
+    x = torch.tensor([[1.5, -2.0]]); y = torch.tensor([[3.0, 4.0]]); z = torch.tensor([[0.0, 8.0]])
+    things = gdstate.pack_things(x, y, z, torch.tensor([[7, 300]]), torch.tensor([[True, False]]),
+                                 torch.tensor([[False, True]]), torch.tensor([[-2, 1]]), pad_to=4).numpy()
+    assert things.shape == (1, 4, 4)
+    assert things[0, 0, 0].view(np.float32) == np.float32(1.5)
+    word = things[0, :2, 3].view(np.uint32)
+    assert (word & 0xFFFF).tolist() == [7, 300]
+    assert ((word >> 16) & 0xFF).tolist() == [1, 2]
+    assert (word >> 24).astype(np.uint8).view(np.int8).tolist() == [-2, 1]
+
+
+def test_library_exports_every_declared_symbol(pkg):
+    from gradoom_b200 import native
+
+    header = open(os.path.join(ROOT, "include", "gradoom_b200.h")).read()
+    declared = set(re.findall(r"\b(gd_[a-z_]+)\s*\(", header))
+    assert declared == set(native.EXPORTS)
+    if not os.path.exists(native.LIBRARY):
+        entry.build()
+    lib = ctypes.CDLL(native.LIBRARY)
+    for name in declared:
+        assert getattr(lib, name) is not None
+    lib.gd_error_string.restype = ctypes.c_char_p
+    assert lib.gd_error_string(0) == b"ok"
+    assert b"scratch" in lib.gd_error_string(-7)
+
+
+def test_renderer_refuses_cpu_devices(pkg, scenes):
+    from gradoom_b200 import native
+
+    _sc, blob = scenes("c1")
+    with pytest.raises(native.NativeError):
+        native.Renderer(blob, "cpu", 4)
+
+
+def test_boundary_validation_raises_the_reference_exception_types(pkg):
+    from gradoom_b200 import env
+
+    dev = torch.device("cpu")
+    ok = torch.zeros(4, dtype=torch.int64)
+    assert env.require_device_tensor(ok, "actions", device=dev, shape=(4,), dtypes=(torch.int64,)) is ok
+    with pytest.raises(TypeError):
+        env.require_device_tensor([0, 1, 2, 3], "actions", device=dev, shape=(4,), dtypes=(torch.int64,))
+    with pytest.raises(ValueError):
+        env.require_device_tensor(torch.zeros(3, dtype=torch.int64), "actions", device=dev, shape=(4,),
+                                  dtypes=(torch.int64,))
+    with pytest.raises(TypeError):
+        env.require_device_tensor(torch.zeros(4), "actions", device=dev, shape=(4,), dtypes=(torch.int64,))
+    with pytest.raises(TypeError):
+        env.check_lane_index(True, 4)      # upstream tests/test_turbo_api_contract.py:509-519
+    with pytest.raises(IndexError):
+        env.check_lane_index(4, 4)
+    assert env.check_lane_index(np.int64(2), 4) == 2
+    m = env.action_matrix(dev)
+    assert m.shape == (17, 20) and m[0].sum() == 0 and m[8].tolist().count(True) == 2
+
+
+def test_lane_slices_partition_the_global_lanes(pkg):
+    from gradoom_b200 import stats
+
+    lanes = [i for r in range(8) for i in stats.lane_slice(r, 8, 8192)]
+    assert lanes == list(range(65536))
+    with pytest.raises(ValueError):
+        stats.lane_slice(8, 8, 4)
+    sb = torch.arange(3 * 27, dtype=torch.float32).reshape(3, 27)
+    block = stats.local_stats(sb)
+    assert block.shape == (3, 4) and block[1].tolist() == [27.0, 44.0, 45.0, 53.0]
+    assert torch.equal(stats.gather_lane_stats(sb), block)
+
+
+def test_random_lanes_are_valid_and_deterministic(pkg, scenes):
+    from gradoom_b200 import stepper, state as gdstate
+
+    sc, _ = scenes("c2")
+    a = stepper.random_lanes(sc, 16, 12, seed=3)
+    b = stepper.random_lanes(sc, 16, 12, seed=3)
+    assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+    lanes = a[0]
+    x = lanes[:, gdstate.L_X].view(np.float32)
+    assert ((x > 0) & (x < 2048)).all()
+    assert (lanes[:, gdstate.L_THINGS] == 12).all()

@@ -1,0 +1,107 @@
+"""The CPU oracle against fixtures recorded from the upstream renderer.
+
+Bar: the palette-indexed 320x240 frame (view + status bar) is bit-exact; the
+84x84 observation equals the upstream *integer* definition exactly and is within
+1 LSB of the upstream float32 matmul path (the tolerance the upstream's own
+test grants: tests/test_rendering.py:112-139).
+"""
+
+import numpy as np
+import pytest
+
+from conftest import load_golden
+
+
+@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4"])
+def test_oracle_matches_upstream_indexed_frames(name, pkg, oracle, scenes):
+    data = load_golden(name)
+    _sc, blob = scenes(str(data["config"]), (data["ray_offsets"], data["ray_coscorr"]))
+    for ci in range(len(data["checkpoints"])):
+        lanes, things = data[f"lanes_{ci}"], data[f"things_{ci}"]
+        out = oracle.render(blob, lanes, things, mask_hud=True)
+        assert np.array_equal(out["indexed"], data[f"indexed_{ci}"]), f"{name} checkpoint {ci}"
+        diff = np.abs(out["obs"].astype(np.int32) - data[f"obs_float_{ci}"].astype(np.int32))
+        assert diff.max() <= 1
+        assert diff.mean() < 0.01
+
+
+def test_oracle_stack_follows_upstream_roll_and_reset_fill(pkg, oracle, scenes):
+    data = load_golden("stack")
+    _sc, blob = scenes("c1", (data["ray_offsets"], data["ray_coscorr"]))
+    n = data["lanes_reset"].shape[0]
+    # start from the upstream stack before the masked reset is unknown: rebuild the
+    # sequence from the reset on, lane by lane, and compare with +-1 (float resize).
+    stack = data["frames_reset"].copy()
+    obs = oracle.render(blob, data["lanes_reset"], data["things_reset"])["obs"]
+    oracle.stack_update(stack, obs, reset_mask=data["reset_mask"])
+    masked = data["reset_mask"].astype(bool)
+    assert np.abs(stack[masked].astype(int) - data["frames_reset"][masked].astype(int)).max() <= 1
+    assert np.array_equal(stack[~masked], data["frames_reset"][~masked])
+    for s in range(4):
+        obs = oracle.render(blob, data[f"lanes_{s}"], data[f"things_{s}"])["obs"]
+        oracle.stack_update(stack, obs)
+        ref = data[f"frames_{s}"]
+        assert np.abs(stack.astype(int) - ref.astype(int)).max() <= 1
+    assert stack.shape == (n, 4, 84, 84)
+
+
+def _area_axis(source, output):
+    w = np.zeros((output, source), dtype=np.float32)
+    for o in range(output):
+        start, end = o * source, (o + 1) * source
+        for s in range(start // output, min((end + output - 1) // output, source)):
+            w[o, s] = (min(end, (s + 1) * output) - max(start, s * output)) / source
+    return w
+
+
+def test_integer_resize_is_within_one_lsb_of_the_float_definition(pkg, oracle, scenes):
+    """Known-answer shape of upstream tests/test_rendering.py:112-139: random
+    indexed frames and palette, float area weights vs the integer kernel."""
+
+    rng = np.random.default_rng(20260813)
+    indexed = rng.integers(0, 256, size=(2, 208, 320), dtype=np.uint8)
+    sc, blob = scenes("c1")
+    rgb = sc.playpal[indexed].astype(np.float32)
+    rgb = np.concatenate((rgb, np.zeros((2, 32, 320, 3), dtype=np.float32)), axis=1)
+    wy, wx = _area_axis(240, 84), _area_axis(320, 84)
+    pooled = np.einsum("oy,nyxc->noxc", wy, rgb)
+    pooled = np.einsum("px,noxc->nopc", wx, pooled)
+    rounded = np.floor(pooled + 0.5).astype(np.int32)
+    expected = (rounded[..., 0] * 77 + rounded[..., 1] * 150 + rounded[..., 2] * 29 + 128) >> 8
+    actual = oracle.resize(blob, indexed).astype(np.int32)
+    assert np.abs(expected - actual).max() <= 1
+    assert np.abs(expected - actual).mean() < 0.001
+    # footprints: every output row / column sums to one with at most 4 / 5 taps
+    assert np.allclose(wy.sum(1), 1) and np.allclose(wx.sum(1), 1)
+    assert (np.count_nonzero(wy, axis=1) <= 4).all() and (np.count_nonzero(wx, axis=1) <= 5).all()
+
+
+def test_transparent_sprites_reveal_the_fifth_actor(pkg, oracle):
+    """Upstream tests/test_rendering.py:2649-2694: pixel (103,160) shows value 20."""
+
+    import kat
+    from gradoom_b200 import scene as gdscene
+
+    sc, (lanes, things), expected = kat.transparent_case()
+    out = oracle.render(gdscene.pack_scene(sc), lanes, things)
+    assert out["indexed"][0, 103, 160] == expected
+
+
+def test_teleport_fog_animation_frames(pkg, oracle):
+    """Upstream tests/test_rendering.py:2844-2887: pixels 10/10/11/12/21 and nothing at 0 tics."""
+
+    import kat
+    from gradoom_b200 import scene as gdscene
+
+    background = None
+    for tics, value in ((71, 10), (67, 10), (66, 11), (60, 12), (1, 21), (0, None)):
+        sc, (lanes, things), expected = kat.fog_case(tics)
+        sc = __import__("dataclasses").replace(
+            sc, additive_luts=np.broadcast_to(np.arange(256, dtype=np.uint8)[None, None, :], (2, 256, 256)).copy())
+        px = oracle.render(gdscene.pack_scene(sc), lanes, things)["indexed"][0, 103, 160]
+        if value is None:
+            background = px
+            assert expected is None
+        else:
+            assert px == value == expected
+    assert background is not None and background not in (10, 11, 12, 21)
