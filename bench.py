@@ -1,0 +1,330 @@
+"""Benchmark of the render-to-observation path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One step = one pass of the hot path over one batch of lanes: every lane of the
+rank is rendered (walls, visplanes, sprites, weapon, area resize) and its 84x84
+frame is pushed onto the four-frame stack.  Workload at every N: 4096 lanes per
+GPU on the seeded 64-sector map with 12 things per lane (the configuration the
+headline metric is quoted on); lane states are synthetic, resident in HBM, and
+advanced between steps by the built-in lane stepper outside the timed region.
+With N>1 (torchrun, one rank per GPU) every rank owns its own 4096 lanes (weak
+scaling, no collective on the render path; the per-lane statistics are
+all-gathered every 100 steps).
+
+Prints one JSON line; see DESIGN.md for the meaning of every field.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import threading
+import time
+from concurrent.futures import ThreadPoolExecutor
+
+import numpy as np
+
+import __graft_entry__ as entry
+
+LANES_PER_GPU = 4096
+THINGS = 12
+WORKLOAD = "c2"
+METRIC = "rendered env-frames/sec at 4096 lanes/GPU"
+UNIT = "frames/s"
+# algorithmic HBM bytes per env-frame: newest 84x84 slot + 64 B lane scalars + 16 B per thing
+BYTES_PER_FRAME = 84 * 84 + 64 + 16 * THINGS
+
+
+def measured_peaks():
+    path = os.path.join(entry.ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle samples while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.rows = []
+        self.proc = None
+        self.gpu_index = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        inside = [r for t, r in self.rows if t0 <= t <= t1] or [r for _, r in self.rows]
+        sm, reasons, sm_max = [], set(), None
+        for r in inside:
+            try:
+                sm.append(float(r[1]))
+                sm_max = float(r[2])
+            except (ValueError, IndexError):
+                continue
+            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7),
+                              ("sw_power_cap", 8)):
+                if len(r) > col and r[col].lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": sm_max, "reasons": sorted(reasons),
+                "samples": len(inside)}
+
+
+def cpu_baseline(blob, lanes, things, oracle, seconds=12.0, threads=1):
+    """Time the CPU port of the path on a bounded sample of the same workload."""
+
+    chunk = 32
+    done = 0
+    t0 = time.perf_counter()
+
+    def work(i):
+        sl = slice(i * chunk, (i + 1) * chunk)
+        oracle.render(blob, lanes[sl], things[sl], mask_hud=True, stage_mask=oracle.STAGE_WALLS
+                      | oracle.STAGE_SPRITES | oracle.STAGE_WEAPON)
+        return chunk
+
+    n_chunks = lanes.shape[0] // chunk
+    with ThreadPoolExecutor(max_workers=threads) as pool:
+        i = 0
+        while i < n_chunks and time.perf_counter() - t0 < seconds:
+            batch = list(range(i, min(i + threads, n_chunks)))
+            done += sum(pool.map(work, batch))
+            i += len(batch)
+    dt = time.perf_counter() - t0
+    return done / dt, done, dt
+
+
+def run_reference(args):
+    """The reference arm: the CPU implementation of the path (the oracle port of
+    the upstream renderer; the upstream itself is Python and is not on this
+    machine) on all host threads, on a bounded sample of the same workload."""
+
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    entry.load_package()
+    from gradoom_b200 import scene as gdscene, stepper
+
+    oracle = entry.load_oracle()
+    sc = gdscene.make_grid_scene(gdscene.GRID_CONFIGS[WORKLOAD])
+    blob = gdscene.pack_scene(sc)
+    cores = len(os.sched_getaffinity(0))
+    sample = 64 * cores
+    lanes, things = stepper.random_lanes(sc, sample, THINGS, seed=11)
+    times = []
+    for step in range(args.warmup + args.steps):
+        stepper.advance(sc, lanes, seed=step)
+        t0 = time.perf_counter()
+        chunk = max(sample // cores, 1)
+        with ThreadPoolExecutor(max_workers=cores) as pool:
+            list(pool.map(lambda i: oracle.render(blob, lanes[i:i + chunk], things[i:i + chunk], mask_hud=True,
+                                                  stage_mask=7), range(0, sample, chunk)))
+        if step >= args.warmup:
+            times.append(time.perf_counter() - t0)
+    total = sum(times)
+    value = sample * len(times) / total
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * total / len(times),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "i64+f32", "data": "synthetic",
+        "config": {"workload": f"{WORKLOAD}: {sample} of {LANES_PER_GPU} lanes, 64-sector map, {THINGS} things/lane",
+                   "l2": "n/a (CPU)"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"{sample} lanes per step x {len(times)} steps of the {WORKLOAD} workload"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    entry.load_package()
+    from gradoom_b200 import native, scene as gdscene, stats, stepper
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    if args.gpus != world and rank == 0 and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} does not match WORLD_SIZE {world}")
+
+    sc = gdscene.make_grid_scene(gdscene.GRID_CONFIGS[WORKLOAD])
+    blob = gdscene.pack_scene(sc)
+    n = args.lanes
+    producer = stepper.LaneStepper(sc, n, device=device, k_things=THINGS, max_things=THINGS, seed=1000 + rank)
+    renderer = native.Renderer(blob, device, THINGS)
+    stack = torch.zeros((n, 4, 84, 84), dtype=torch.uint8, device=device)
+    everyone = torch.ones(n, dtype=torch.bool, device=device)
+    lane_ids = torch.arange(n, device=device, dtype=torch.int64) + rank * n
+    producer.reset(everyone, lane_ids + 1)
+    lanes, things = producer.render_inputs()
+    renderer.reset(lanes, things, everyone, stack)
+    actions = torch.randint(0, 17, (args.warmup + 2 * args.steps + 8, n), device=device,
+                            generator=torch.Generator(device=device).manual_seed(20260813 + rank))
+    from gradoom_b200.env import action_matrix
+
+    buttons = action_matrix(device)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)   # > 126 MB L2
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    step_index = 0
+
+    def advance():
+        nonlocal step_index
+        producer.step(buttons[actions[step_index % actions.shape[0]]])
+        step_index += 1
+
+    for _ in range(args.warmup):
+        advance()
+        renderer.step(lanes, things, stack)
+    barrier()
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    time.sleep(0.3)
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    gathered = None
+    barrier()
+    wall0 = time.time()
+    launches0 = renderer.launches
+    for k in range(args.steps):
+        advance()
+        flush.fill_(k & 0xFF)                 # evict the previous step's stack and records from L2
+        starts[k].record()
+        renderer.step(lanes, things, stack)
+        ends[k].record()
+        if (k + 1) % 100 == 0:
+            gathered = stats.gather_lane_stats(producer.signal_buffer)
+    barrier()
+    wall1 = time.time()
+    kernel_ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
+    launches = renderer.launches - launches0
+    renderer.check_status()
+    clocks = sampler.stop(wall0, wall1)
+    elapsed_ms = torch.tensor([sum(kernel_ms)], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(elapsed_ms, op=dist.ReduceOp.MAX)
+    total_ms = float(elapsed_ms.item())
+    value = world * n * args.steps / (total_ms / 1000.0)
+
+    # end to end through the host-buffer entry point: pinned records in, newest frames out
+    host_lanes = torch.empty(lanes.shape, dtype=torch.int32).pin_memory()
+    host_things = torch.empty(things.shape, dtype=torch.int32).pin_memory()
+    host_obs = torch.empty((n, 84, 84), dtype=torch.uint8).pin_memory()
+    dev_lanes, dev_things = torch.empty_like(lanes), torch.empty_like(things)
+    pool = []
+    for _ in range(4):
+        advance()
+        pool.append((lanes.cpu().clone(), things.cpu().clone()))
+    e2e_steps = max(args.steps, 3)
+    for w in range(2):
+        host_lanes.copy_(pool[w % 4][0]); host_things.copy_(pool[w % 4][1])
+        renderer.step_host(host_lanes, host_things, dev_lanes, dev_things, stack, host_obs)
+    barrier()
+    t0 = time.perf_counter()
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s0.record()
+    for k in range(e2e_steps):
+        host_lanes.copy_(pool[k % 4][0]); host_things.copy_(pool[k % 4][1])
+        renderer.step_host(host_lanes, host_things, dev_lanes, dev_things, stack, host_obs)
+        torch.cuda.current_stream(device).synchronize()     # the caller reads host_obs here
+    s1.record()
+    barrier()
+    e2e_ms = torch.tensor([s0.elapsed_time(s1)], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    e2e_value = world * n * e2e_steps / (float(e2e_ms.item()) / 1000.0)
+    renderer.check_status()
+
+    if rank == 0:
+        oracle = entry.load_oracle()
+        peak, peak_kind = measured_peaks()
+        avg_ms = statistics.mean(kernel_ms)
+        achieved = BYTES_PER_FRAME * n / (avg_ms / 1000.0) / 1e9
+        cpu_lanes, cpu_things = stepper.random_lanes(sc, 2048, THINGS, seed=11)
+        cpu_value, cpu_done, cpu_dt = cpu_baseline(blob, cpu_lanes, cpu_things, oracle,
+                                                   seconds=0.5 if args.skip_cpu else 12.0, threads=1)
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "i64+f32", "data": "synthetic",
+            "config": {"workload": f"{WORKLOAD}: {n} lanes/GPU, 64-sector 8x8 map, {THINGS} things/lane, obs only",
+                       "lanes_per_gpu": n, "l2": "flushed with a 256 MiB write between timed steps",
+                       "ctas": renderer.ctas, "shared_bytes_per_cta": renderer.shared_bytes,
+                       "stack_policy": "roll (read 3 + write 4 slots per lane)"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_source": peak_kind,
+                         "algorithmic_bytes_per_launch": BYTES_PER_FRAME * n,
+                         "kernel_ms": avg_ms, "pixels_per_s": 320 * 208 * n / (avg_ms / 1000.0)},
+            "cpu_baseline": {"value": cpu_value, "unit": UNIT, "cores": 1, "kind": "port",
+                             "sample": f"{cpu_done} lanes of the {WORKLOAD} workload in {cpu_dt:.1f} s, one thread"},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(host_lanes.numel() * 4
+                                                                                 + host_things.numel() * 4),
+                    "d2h_bytes_per_step": int(host_obs.numel()), "steps": e2e_steps},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "stats_gather": None if gathered is None else list(gathered.shape),
+            "wall_s": wall1 - wall0,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--lanes", type=int, default=LANES_PER_GPU, help="lanes per GPU (profiling captures use fewer)")
+    ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg (profiling captures)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

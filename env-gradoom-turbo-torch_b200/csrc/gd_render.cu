@@ -1843,3 +1843,31 @@ extern "C" int gd_render_frames(const gd_renderer *r, const int32_t *lanes, cons
   return gd_launch(r, lanes, (const gd_thing *)things, n, flags, nullptr, nullptr, obs_out, indexed_out, rgb_out,
                    scratch, scratch_bytes, status, stream);
 }
+
+/* Host-buffer variant of gd_render_step: copies the lane and thing records to
+ * the caller's device staging buffers, renders, and copies the newest frame of
+ * every lane (stack slot 3) back to `obs_host`.  Everything is queued on
+ * `stream`; pinned host memory keeps the copies asynchronous. */
+extern "C" int gd_render_step_host(const gd_renderer *r, const int32_t *lanes_host, const void *things_host, int n,
+                                   int mask_hud, int32_t *lanes_dev, void *things_dev, uint8_t *stack,
+                                   uint8_t *obs_host, void *scratch, size_t scratch_bytes, int *status,
+                                   void *stream) {
+  if (!r || !lanes_host || !lanes_dev || !stack || !obs_host) return GD_ERR_NULL;
+  if (r->maxThings > 0 && (!things_host || !things_dev)) return GD_ERR_NULL;
+  if (n < 0) return GD_ERR_SIZE;
+  if (n == 0) return GD_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  size_t thingStride = (size_t)(r->maxThings > 0 ? r->maxThings : 1) * sizeof(gd_thing);
+  if (cudaMemcpyAsync(lanes_dev, lanes_host, (size_t)n * GD_LANE_WORDS * 4, cudaMemcpyHostToDevice, s) != cudaSuccess)
+    return GD_ERR_CUDA;
+  if (things_host &&
+      cudaMemcpyAsync(things_dev, things_host, (size_t)n * thingStride, cudaMemcpyHostToDevice, s) != cudaSuccess)
+    return GD_ERR_CUDA;
+  int rc = gd_render_step(r, lanes_dev, things_dev, n, mask_hud, stack, scratch, scratch_bytes, status, stream);
+  if (rc != GD_OK) return rc;
+  const size_t frame = (size_t)GD_OBS * GD_OBS;
+  if (cudaMemcpy2DAsync(obs_host, frame, stack + (GD_STACK - 1) * frame, GD_STACK * frame, frame, (size_t)n,
+                        cudaMemcpyDeviceToHost, s) != cudaSuccess)
+    return GD_ERR_CUDA;
+  return GD_OK;
+}

@@ -22,6 +22,7 @@ STATUS_THINGS_OVERFLOW = 2
 EXPORTS = (
     "gd_error_string", "gd_renderer_create", "gd_renderer_destroy", "gd_renderer_scratch_bytes",
     "gd_renderer_ctas", "gd_renderer_shared_bytes", "gd_render_step", "gd_render_reset", "gd_render_frames",
+    "gd_render_step_host",
 )
 
 _lib = None
@@ -60,6 +61,8 @@ def load() -> ctypes.CDLL:
         lib.gd_render_reset.argtypes = [vp, vp, vp, ci, ci, vp, vp, vp, sz, vp, vp]
         lib.gd_render_frames.restype = ci
         lib.gd_render_frames.argtypes = [vp, vp, vp, ci, ci, ci, vp, vp, vp, vp, sz, vp, vp]
+        lib.gd_render_step_host.restype = ci
+        lib.gd_render_step_host.argtypes = [vp, vp, vp, ci, ci, vp, vp, vp, vp, vp, sz, vp, vp]
         _lib = lib
     return _lib
 
@@ -134,6 +137,26 @@ class Renderer:
         _check(self.lib.gd_render_step(self.handle, lanes.data_ptr(), things.data_ptr(), n, int(mask_hud),
                                        stack.data_ptr(), self.scratch.data_ptr(), self.scratch_bytes,
                                        self.status.data_ptr(), self._stream()), "gd_render_step")
+        self.launches += 1
+
+    def step_host(self, lanes_host, things_host, lanes_dev, things_dev, stack, obs_host, mask_hud=True):
+        """Host-buffer step: pinned ``lanes_host``/``things_host`` in, pinned
+        ``obs_host (N,84,84) uint8`` out, all queued on the current stream."""
+
+        n = self._inputs(lanes_dev, things_dev)
+        self._check_stack(stack, n)
+        for t in (lanes_host, things_host, obs_host):
+            if t.device.type != "cpu" or not t.is_contiguous():
+                raise TypeError("host buffers must be contiguous CPU tensors")
+        if tuple(lanes_host.shape) != tuple(lanes_dev.shape) or tuple(things_host.shape) != tuple(things_dev.shape):
+            raise ValueError("host and device record buffers must have the same shape")
+        if tuple(obs_host.shape) != (n, 84, 84) or obs_host.dtype != torch.uint8:
+            raise ValueError("obs_host must be (N,84,84) uint8")
+        _check(self.lib.gd_render_step_host(self.handle, lanes_host.data_ptr(), things_host.data_ptr(), n,
+                                            int(mask_hud), lanes_dev.data_ptr(), things_dev.data_ptr(),
+                                            stack.data_ptr(), obs_host.data_ptr(), self.scratch.data_ptr(),
+                                            self.scratch_bytes, self.status.data_ptr(), self._stream()),
+               "gd_render_step_host")
         self.launches += 1
 
     def reset(self, lanes, things, reset_mask, stack, mask_hud=True):

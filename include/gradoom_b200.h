@@ -105,6 +105,19 @@ int gd_render_frames(const gd_renderer *r, const int32_t *lanes, const void *thi
                      int include_hud, uint8_t *obs_out, uint8_t *indexed_out, uint8_t *rgb_out, void *scratch,
                      size_t scratch_bytes, int *status, void *stream);
 
+/*
+ * gd_render_step for callers that keep their state in host memory: queues the
+ * host->device copies of the records into the caller's staging buffers
+ * (`lanes_dev`, `things_dev`), the render, and the device->host copy of the
+ * newest 84x84 frame of every lane into `obs_host` (n x 84 x 84 u8).  Use
+ * pinned host buffers to keep the call asynchronous.  Same reference call site
+ * as gd_render_step (src/gradoom/engine.py:9575-9576), plus the
+ * `.to("cpu")` a host-side learner performs on the observation.
+ */
+int gd_render_step_host(const gd_renderer *r, const int32_t *lanes_host, const void *things_host, int n,
+                        int mask_hud, int32_t *lanes_dev, void *things_dev, uint8_t *stack, uint8_t *obs_host,
+                        void *scratch, size_t scratch_bytes, int *status, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

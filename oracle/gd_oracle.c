@@ -712,7 +712,7 @@ static void wall_pass(const Scene *sc, const View *v, const LaneGeom *g, LaneBuf
       int pendEpHasFwd, epFwdIdx, ppbIdx;
       int psPathIndex, psFromFront;
     } Trav;
-    static Trav trav[SW];
+    Trav *trav = calloc(SW, sizeof(Trav));
     for (int x = 0; x < SW; ++x) {
       ColState *c = &cs[x];
       ColIter *it = &ci[x];
@@ -1099,6 +1099,7 @@ static void wall_pass(const Scene *sc, const View *v, const LaneGeom *g, LaneBuf
         c->cur = next;
       }
     }
+    free(trav);
   }
   free(cs);
   free(ci);
