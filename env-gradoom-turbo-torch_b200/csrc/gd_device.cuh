@@ -73,11 +73,23 @@ __device__ __forceinline__ i64 gd_pymod(i64 a, i64 m) {
 }
 
 /*
- * Truncating signed 64-bit division.  Most quotients on this path have a
- * divisor that fits in 32 bits; the generic operator is kept because the
- * quotient must be exact for every operand.
+ * Truncating signed 64-bit division.  The generic 64-bit divide is a long
+ * software routine on the GPU; nearly every quotient on this path has operands
+ * below 2^52, where a double-precision divide is within one of the exact
+ * quotient and an integer remainder check makes it exact.
  */
-__device__ __forceinline__ i64 gd_div(i64 a, i64 b) { return a / b; }
+__device__ __noinline__ i64 gd_div_generic(i64 a, i64 b) { return a / b; }
+
+__device__ __forceinline__ i64 gd_div(i64 a, i64 b) {
+  unsigned long long ua = a < 0 ? 0ull - (unsigned long long)a : (unsigned long long)a;
+  unsigned long long ub = b < 0 ? 0ull - (unsigned long long)b : (unsigned long long)b;
+  if (((ua | ub) >> 52) != 0 || ub == 0) return gd_div_generic(a, b);
+  i64 q = (i64)__ddiv_rn((double)ua, (double)ub);
+  i64 r = (i64)ua - q * (i64)ub;
+  if (r < 0) q -= 1;
+  else if (r >= (i64)ub) q += 1;
+  return ((a ^ b) < 0) ? -q : q;
+}
 
 struct GdView {
   float x, y, angle, viewZ;
@@ -85,6 +97,7 @@ struct GdView {
   i64 vsin, vcos;
   float fcos, fsin;
   i64 center;
+  i64 upperClip, lowerClip;  /* view frustum top / bottom slopes used by the row projection */
   int flashLight;
 };
 
@@ -111,3 +124,15 @@ struct __align__(4) GdEvent {
 };
 
 #define GD_MAX_EVENTS 48
+
+/* Row projection of one (wall, plane height) pair: everything of the OWallMost
+ * replay that does not depend on the screen column. */
+struct __align__(8) GdRowProj {
+  i64 pl, pstep, cl;     /* clipped-edge projection: center + pl + (x - cl) * pstep */
+  i64 opl, ostep;        /* whole-wall projection for columns outside the seg's span */
+  short topA, topB;      /* columns forced to row 0 (above the view frustum) */
+  short botA, botB;      /* columns forced to the bottom row */
+  short collapsedX;      /* the one column exempt from both, or -1 */
+  unsigned char entAbove, entBelow;
+  short pad;
+};

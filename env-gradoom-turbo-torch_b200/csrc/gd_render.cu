@@ -48,12 +48,16 @@ struct GdParams {
   uint8_t *obsOut;           /* n x 84 x 84, optional */
   uint8_t *indexedOut;       /* n x 240 x 320, optional */
   uint8_t *rgbOut;           /* n x 240 x 320 x 3, optional */
-  uint8_t *scratch;          /* gridDim.x x GD_SCRATCH_PER_CTA */
+  uint8_t *scratch;          /* ctas x gd_scratch_per_cta(W), then the lane queue (2 words, zero between launches) */
+  size_t queueOffset;
   int *status;
 };
 
 #define GD_SCRATCH_EVENTS_BYTES (GD_MAX_EVENTS * GD_SW * (int)sizeof(GdEvent))
-#define GD_SCRATCH_PER_CTA (GD_SCRATCH_EVENTS_BYTES + GD_SW * 4)
+#define GD_SCRATCH_FIXED (GD_SCRATCH_EVENTS_BYTES + GD_SW * 4)
+__host__ __device__ inline size_t gd_scratch_per_cta(int W) {
+  return (GD_SCRATCH_FIXED + (size_t)W * 4 * sizeof(GdRowProj) + 15) & ~(size_t)15;
+}
 
 struct GdActor {
   float x, y, depth;
@@ -136,6 +140,8 @@ __device__ void gd_view_setup(const GdScene &sc, const int32_t *lane, GdView &v)
   v.fcos = (float)v.vcos / 65536.0f;
   i64 ti = gd_clamp((GD_ANG90 - v.pitchBam) >> 19, 0, 4095);
   v.center = 104 * GD_FU + ((GD_FOCAL_Y * (i64)sc.fineTan[ti]) >> 16);
+  v.upperClip = gd_div((-v.center) * GD_FU, GD_FOCAL_Y);
+  v.lowerClip = gd_div((GD_VH * GD_FU - v.center) * GD_FU, GD_FOCAL_Y);
   int weapon = (int)gd_clamp(lane[GD_L_WEAPON], 0, 7);
   int cooldown = (int)gd_clamp(lane[GD_L_WPN_COOLDOWN], 0, sc.wpnTics - 1);
   int parity = (int)gd_pymod(lane[GD_L_WPN_FIRE_COUNT], 2);
@@ -193,7 +199,7 @@ __device__ void gd_wall_visibility(i64 tx1, i64 ty1, i64 tx2, i64 ty2, i64 &visL
 
 /* Project wall w of the map for this lane (engine.py:10747-10869, 11207-11302,
  * 11359-11427).  The ray-owned span is completed by gd_wall_span below. */
-__device__ void gd_project_wall(const GdScene &sc, const GdView &v, int w, GdWall &out) {
+__device__ __noinline__ void gd_project_wall(const GdScene &sc, const GdView &v, int w, GdWall &out) {
   const float *wl = &sc.walls[w * 4];
   i64 fx[2] = {gd_rint(wl[0] * 65536.0f), gd_rint(wl[2] * 65536.0f)};
   i64 fy[2] = {gd_rint(wl[1] * 65536.0f), gd_rint(wl[3] * 65536.0f)};
@@ -251,9 +257,11 @@ __device__ __forceinline__ bool gd_ray_geo(const float4 wl, const GdView &v, flo
   float safe = small ? 1.0f : den;
   float dn = offx * segy - offy * segx;
   float an = offx * ry - offy * rx;
-  float distance = dn / safe;  /* kept: a tiny quotient may round to zero */
+  /* dn / safe > 0: both are differences of products of map-scale numbers, so a
+   * nonzero dn is far too large for the quotient to underflow to zero */
+  bool positive = (dn != 0.0f) && ((dn < 0) == (safe < 0));
   bool alongOk = (an == 0.0f) || (((an < 0) == (safe < 0)) && fabsf(an) <= fabsf(safe));
-  return !small && distance > 0 && alongOk;
+  return !small && positive && alongOk;
 }
 
 /* ---- per (column, wall) hit -------------------------------------------- */
@@ -288,7 +296,7 @@ __device__ __forceinline__ GdHit gd_hit(const GdScene &sc, const GdView &v, cons
 __device__ __forceinline__ float gd_tol(float d) { return fmaxf(fabsf(d) / 128.0f, 4.0f); }
 
 /* Endpoint owner of wall w at column x (engine.py:11589-11730). */
-__device__ void gd_endpoint_owner(const GdScene &sc, const GdView &v, const GdWall *walls, int w, int x, float rx,
+__device__ __noinline__ void gd_endpoint_owner(const GdScene &sc, const GdView &v, const GdWall *walls, int w, int x, float rx,
                                   float ry, const GdHit &hw, int &ownerIdx, float &ownerDist) {
   const GdWall &wv = walls[w];
   float d = hw.d;
@@ -336,7 +344,7 @@ __device__ void gd_endpoint_owner(const GdScene &sc, const GdView &v, const GdWa
 }
 
 /* PrepWall for one (column, wall) (engine.py:10672-10739). */
-__device__ void gd_prep_wall(const GdScene &sc, const GdWall &wv, int w, int x, i64 &hoff, i64 &vstep) {
+__device__ __noinline__ void gd_prep_wall(const GdScene &sc, const GdWall &wv, int w, int x, i64 &hoff, i64 &vstep) {
   i64 tx1 = wv.tx[0], tx2 = wv.tx[1], ty1 = wv.ty[0], ty2 = wv.ty[1];
   double uozOrigin = (double)((float)tx1 * 160.0f);
   double uozStep = (double)(-(float)ty1);
@@ -357,7 +365,7 @@ __device__ void gd_prep_wall(const GdScene &sc, const GdWall &wv, int w, int x, 
 }
 
 /* OWallMost row projection (engine.py:12294-12605), one fragment per wall. */
-__device__ int gd_project_rows(const GdView &v, const GdWall &wv, float worldZ, int x) {
+__device__ __noinline__ int gd_project_rows(const GdView &v, const GdWall &wv, float worldZ, int x) {
   i64 wsl = wv.sl, wsr = wv.sr;
   i64 wdl = gd_max(wv.dl, 1), wdr = gd_max(wv.dr, 1);
   bool owns = (wsr > wsl) && x >= wsl && x < wsr;
@@ -372,8 +380,7 @@ __device__ int gd_project_rows(const GdView &v, const GdWall &wv, float worldZ, 
     return (int)gd_clamp((center + opl + (x - wsl) * ostep) >> 16, 0, GD_VH);
   }
   i64 sl = wsl, sr = wsr, dl = wdl, dr = wdr;
-  i64 upperClip = gd_div((-center) * GD_FU, GD_FOCAL_Y);
-  i64 lowerClip = gd_div((GD_VH * GD_FU - center) * GD_FU, GD_FOCAL_Y);
+  i64 upperClip = v.upperClip, lowerClip = v.lowerClip;
   i64 ul = (upperClip * dl) >> 16, ur = (upperClip * dr) >> 16;
   i64 ll = (lowerClip * dl) >> 16, lr = (lowerClip * dr) >> 16;
   bool aboveL = pz < ul, aboveR = pz < ur, belowL = pz > ll, belowR = pz > lr;
@@ -411,6 +418,69 @@ __device__ int gd_project_rows(const GdView &v, const GdWall &wv, float worldZ, 
   return (int)gd_clamp((center + pl + (x - cl) * pstep) >> 16, 0, GD_VH);
 }
 
+/* Column-independent part of gd_project_rows for one (wall, height). */
+__device__ __noinline__ void gd_rowproj_setup(const GdView &v, const GdWall &wv, float worldZ, GdRowProj &o) {
+  i64 wsl = wv.sl, wsr = wv.sr;
+  i64 wdl = gd_max(wv.dl, 1), wdr = gd_max(wv.dr, 1);
+  i64 relZ = gd_rint((worldZ - v.viewZ) * 65536.0f);
+  i64 pz = -(relZ >> 4);
+  i64 num = pz * GD_FOCAL_Y;
+  {
+    i64 ospan = gd_max(wsr - wsl, 1);
+    i64 opl = gd_div(num, wdl), opr = gd_div(num, wdr);
+    o.opl = opl;
+    o.ostep = gd_div(opr - opl, ospan);
+  }
+  i64 sl = wsl, sr = wsr, dl = wdl, dr = wdr;
+  i64 upperClip = v.upperClip, lowerClip = v.lowerClip;
+  i64 ul = (upperClip * dl) >> 16, ur = (upperClip * dr) >> 16;
+  i64 ll = (lowerClip * dl) >> 16, lr = (lowerClip * dr) >> 16;
+  bool aboveL = pz < ul, aboveR = pz < ur, belowL = pz > ll, belowR = pz > lr;
+  bool entAbove = aboveL && aboveR, entBelow = belowL && belowR;
+  i64 cl = sl, cr = sr, cdl = dl, cdr = dr;
+  i64 topA = 0, topB = 0, botA = 0, botB = 0;
+  if (aboveL != aboveR) {
+    i64 sud = (ur != ul) ? (ur - ul) : 1;
+    i64 tf = gd_div(gd_shl(pz - ul, 30), sud);
+    i64 td = dl + (((dr - dl) * tf) >> 30);
+    i64 tc = sl + gd_div(((dr * tf) >> 30) * (sr - sl), gd_max(td, 1));
+    if (aboveR && (sl <= tc)) { cr = tc; cdr = td; }
+    if (aboveR && (sr > tc)) { topA = tc; topB = sr; }
+    if (aboveL && (tc <= sr)) { cl = tc; cdl = td; }
+    if (aboveL && (tc > sl)) { topA = sl; topB = tc; }
+  }
+  if (belowL != belowR) {
+    i64 sld = (lr != ll) ? (lr - ll) : 1;
+    i64 bf = gd_div(gd_shl(pz - ll, 30), sld);
+    i64 bd = dl + (((dr - dl) * bf) >> 30);
+    i64 bc = sl + gd_div(((dr * bf) >> 30) * (sr - sl), gd_max(bd, 1));
+    if (belowR && (sl <= bc)) { cr = bc; cdr = bd; }
+    if (belowR && (sr > bc)) { botA = bc; botB = sr; }
+    if (belowL && (bc <= sr)) { cl = bc; cdl = bd; }
+    if (belowL && (bc > sl)) { botA = sl; botB = bc; }
+  }
+  bool collapsed = (cr == cl) && !(entAbove || entBelow);
+  o.collapsedX = (short)((collapsed && cl >= 0 && cl < GD_SW) ? cl : -1);
+  o.entAbove = entAbove; o.entBelow = entBelow;
+  o.topA = (short)gd_clamp(topA, -1, GD_SW + 1); o.topB = (short)gd_clamp(topB, -1, GD_SW + 1);
+  o.botA = (short)gd_clamp(botA, -1, GD_SW + 1); o.botB = (short)gd_clamp(botB, -1, GD_SW + 1);
+  i64 pl = gd_div(num, gd_max(cdl, 1)), pr = gd_div(num, gd_max(cdr, 1));
+  o.pl = pl;
+  o.pstep = gd_div(pr - pl, gd_max(cr - cl, 1));
+  o.cl = cl;
+  o.pad = 0;
+}
+
+__device__ __forceinline__ int gd_rowproj_eval(const GdView &v, const GdWall &wv, const GdRowProj &o, int x) {
+  bool owns = (wv.sr > wv.sl) && x >= wv.sl && x < wv.sr;
+  if (!owns) return (int)gd_clamp((v.center + o.opl + (x - wv.sl) * o.ostep) >> 16, 0, GD_VH);
+  bool collapsed = x == o.collapsedX;
+  bool outTop = x >= o.topA && x < o.topB, outBottom = x >= o.botA && x < o.botB;
+  if (o.entAbove || (outTop && !collapsed)) return 0;
+  if (o.entBelow || (outBottom && !collapsed)) return GD_VH;
+  return (int)gd_clamp((v.center + o.pl + (x - o.cl) * o.pstep) >> 16, 0, GD_VH);
+}
+
 __device__ __forceinline__ int gd_wall_shade(i64 light, i64 vis) {
   i64 base = 64 * GD_FU - (light + 12) * (GD_FU / 4);
   return (int)gd_clamp((base - gd_min(vis, 24 * GD_FU)) >> 16, 0, 31);
@@ -432,7 +502,7 @@ __device__ __forceinline__ bool gd_shares_endpoint(const GdScene &sc, int a, int
   int a0 = sc.wvtx[a * 2], a1 = sc.wvtx[a * 2 + 1], b0 = sc.wvtx[b * 2], b1 = sc.wvtx[b * 2 + 1];
   return a0 == b0 || a0 == b1 || a1 == b0 || a1 == b1;
 }
-__device__ bool gd_opposing_pair(const GdScene &sc, int a, int b) {
+__device__ __noinline__ bool gd_opposing_pair(const GdScene &sc, int a, int b) {
   if (!gd_same_pair(sc, a, b)) return false;
   if (sc.wsec[a * 2 + 1] < 0 || sc.wsec[b * 2 + 1] < 0) return false;
   if (gd_shares_endpoint(sc, a, b)) return false;
@@ -470,7 +540,7 @@ __device__ bool gd_unique_at_vertex(const GdScene &sc, int v, int skipA, int ski
   index = (count == 1) ? found : 0;
   return count == 1;
 }
-__device__ bool gd_portal_bridge(const GdScene &sc, int slot, int path, int owner, int &index) {
+__device__ __noinline__ bool gd_portal_bridge(const GdScene &sc, int slot, int path, int owner, int &index) {
   index = 0;
   if (!gd_two_distinct(sc, path) || owner == path) return false;
   int v = sc.wvtx[path * 2 + slot];
@@ -480,7 +550,7 @@ __device__ bool gd_portal_bridge(const GdScene &sc, int slot, int path, int owne
   if (!gd_bridge_pair_of(sc, path, owner, p0, p1)) return false;
   return gd_unique_at_vertex(sc, v, path, owner, p0, p1, index);
 }
-__device__ bool gd_sector_bridge(const GdScene &sc, int slot, int pending, int path, int &index) {
+__device__ __noinline__ bool gd_sector_bridge(const GdScene &sc, int slot, int pending, int path, int &index) {
   index = 0;
   if (!gd_two_distinct(sc, pending) || path == pending || !gd_two_distinct(sc, path)) return false;
   int p0, p1;
@@ -491,15 +561,15 @@ __device__ bool gd_sector_bridge(const GdScene &sc, int slot, int pending, int p
 /* ---- phase: ray-owned spans (engine.py:11333-11438) --------------------- */
 __device__ void gd_wall_spans(const GdScene &sc, const GdView &v, GdWall *walls) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float rxs[GD_SW / 32], rys[GD_SW / 32];
+#pragma unroll
+  for (int chunk = 0; chunk < GD_SW / 32; ++chunk) gd_ray(v, chunk * 32 + lane, rxs[chunk], rys[chunk]);
   for (int w = warp; w < sc.W; w += GD_WARPS) {
     const float4 wl = *reinterpret_cast<const float4 *>(&sc.walls[w * 4]);
     int first = -1, last = -1;
-#pragma unroll 2
+#pragma unroll
     for (int chunk = 0; chunk < GD_SW / 32; ++chunk) {
-      int x = chunk * 32 + lane;
-      float rx, ry;
-      gd_ray(v, x, rx, ry);
-      unsigned m = __ballot_sync(0xffffffffu, gd_ray_geo(wl, v, rx, ry));
+      unsigned m = __ballot_sync(0xffffffffu, gd_ray_geo(wl, v, rxs[chunk], rys[chunk]));
       if (m) {
         if (first < 0) first = chunk * 32 + __ffs(m) - 1;
         last = chunk * 32 + 31 - __clz(m);
@@ -649,18 +719,34 @@ struct GdIter {
 };
 
 __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWall *walls, const unsigned *ownerMask,
-                                 int x, float rx, float ry, const GdColState &c, GdIter &it) {
+                                 const GdRowProj *rowproj, int x, float rx, float ry, const GdColState &c,
+                                 GdIter &it) {
   const int curSector = c.cur;
   const int current = curSector < 0 ? 0 : curSector;
   const float prev = c.prev;
   const int i0 = sc.secOff[current], i1 = sc.secOff[current + 1];
-#define HIT(w) gd_hit(sc, v, walls, (w), x, rx, ry)
+  /* every rule below looks at the walls of the current sector: test each once */
+  constexpr int kCache = 8;
+  GdHit cache[kCache];
+  int cacheWall[kCache];
+  const int nCache = min(i1 - i0, kCache);
+  for (int k = 0; k < nCache; ++k) {
+    cacheWall[k] = sc.secWalls[i0 + k];
+    cache[k] = gd_hit(sc, v, walls, cacheWall[k], x, rx, ry);
+  }
+  auto cachedHit = [&](int w) -> GdHit {
+    for (int k = 0; k < nCache; ++k)
+      if (cacheWall[k] == w) return cache[k];
+    return gd_hit(sc, v, walls, w, x, rx, ry);
+  };
+#define HIT(w) cachedHit(w)
+#define HITK(k) (((k) - i0) < nCache ? cache[(k) - i0] : gd_hit(sc, v, walls, sc.secWalls[k], x, rx, ry))
   float distance = GD_INF;
   int wallIndex = 0;
   if (curSector >= 0) {
     for (int k = i0; k < i1; ++k) {
       int w = sc.secWalls[k];
-      GdHit h = HIT(w);
+      GdHit h = HITK(k);
       if (h.d > prev && h.d < distance) { distance = h.d; wallIndex = w; }
     }
     float sd = GD_INF;
@@ -668,7 +754,7 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
     for (int k = i0; k < i1; ++k) {
       int w = sc.secWalls[k];
       if (!walls[w].oneSided) continue;
-      GdHit h = HIT(w);
+      GdHit h = HITK(k);
       if (!(h.d > prev) || !isfinite(h.d)) continue;
       if (fabsf(h.d - distance) <= 1e-3f && h.d < sd) { sd = h.d; sw = w; }
     }
@@ -688,8 +774,6 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
   if (continuesEp) {
     bool m = gd_portal_bridge(sc, selSlot, wallIndex, c.pendEpWall, epFwdIdx);
     pendEpHasFwd = m && (HIT(epFwdIdx).d > distance + 1e-3f);
-  } else {
-    gd_portal_bridge(sc, selSlot, wallIndex, c.pendEpWall, epFwdIdx);
   }
   bool completesPendEpBridge = c.pendEpBridgeBoundary && wallIndex == c.pendEpBridgeIndex;
   bool selIsProjected = hSel.proj;
@@ -702,7 +786,7 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
     for (int k = i0; k < i1; ++k) {
       int w = sc.secWalls[k];
       if (!walls[w].oneSided || !SHARES_SEL(w)) continue;
-      GdHit h = HIT(w);
+      GdHit h = HITK(k);
       if (h.proj && h.left && (h.d > prev + 1e-3f) && h.d < psd) { psd = h.d; psi = w; }
     }
     if (selExclRight) {
@@ -723,9 +807,9 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
   bool hasProjectedSolidOwner = isfinite(psd);
   if (hasProjectedSolidOwner) { distance = psd; wallIndex = psi; }
   GdHit hW = (wallIndex == psPathIndex) ? hSel : HIT(wallIndex);
-  int seo;
-  float sed;
-  gd_endpoint_owner(sc, v, walls, wallIndex, x, rx, ry, hW, seo, sed);
+  int seo = wallIndex;
+  float sed = hW.d;
+  if (!hW.proj) gd_endpoint_owner(sc, v, walls, wallIndex, x, rx, ry, hW, seo, sed);
   bool eoPathIsGeo = hW.geo;
   bool replaceEo = (seo != wallIndex) && (sed > prev + 1e-3f);
   if (replaceEo) { distance = sed; wallIndex = seo; hW = HIT(wallIndex); }
@@ -744,7 +828,7 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
     for (int k = i0; k < i1; ++k) {
       int w = sc.secWalls[k];
       if (walls[w].oneSided) continue;
-      GdHit h = HIT(w);
+      GdHit h = HITK(k);
       if (!h.proj || !(h.d > prev + 1e-3f)) continue;
       bool topological = false;
       if (h.left && selOwnerExclRight && selOwnerSpan <= 2) {
@@ -807,8 +891,29 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
   float otherFloor = gd_sec_floor(sc, safeOther), otherCeil = gd_sec_ceil(sc, safeOther);
   bool oneSided = otherSector < 0;
   const int32_t *stex = &sc.sideTex[(wallIndex * 2 + side) * 3];
-  int oneTop = gd_project_rows(v, wv, viewCeil, x), oneBottom = gd_project_rows(v, wv, viewFloor, x);
-  int lowerTop = gd_project_rows(v, wv, otherFloor, x), upperBottom = gd_project_rows(v, wv, otherCeil, x);
+  /* Row bounds: per (wall, sector height) tables built once per lane cover the
+   * usual case of heights taken from the wall's own two sectors. */
+  const GdRowProj *rp = rowproj + wallIndex * 4;
+  int slotCur = (renderCurrent == front) ? 0 : ((renderCurrent == back && back >= 0) ? 2 : -1);
+  int oneTop, oneBottom;
+  if (slotCur >= 0) {
+    oneBottom = gd_rowproj_eval(v, wv, rp[slotCur], x);
+    oneTop = gd_rowproj_eval(v, wv, rp[slotCur + 1], x);
+  } else {
+    oneTop = gd_project_rows(v, wv, viewCeil, x);
+    oneBottom = gd_project_rows(v, wv, viewFloor, x);
+  }
+  int lowerTop = 0, upperBottom = 0;
+  if (!oneSided) {  /* the tiers and clips below use them only for two-sided lines */
+    int slotOther = (renderOther >= 0 && renderOther == back) ? 2 : ((renderOther >= 0 && renderOther == front) ? 0 : -1);
+    if (slotOther >= 0) {
+      lowerTop = gd_rowproj_eval(v, wv, rp[slotOther], x);
+      upperBottom = gd_rowproj_eval(v, wv, rp[slotOther + 1], x);
+    } else {
+      lowerTop = gd_project_rows(v, wv, otherFloor, x);
+      upperBottom = gd_project_rows(v, wv, otherCeil, x);
+    }
+  }
   int ctop = max(oneTop, c.ceilClip), cbot = min(oneBottom, c.floorClip);
   int cupbot = max(min(upperBottom, c.floorClip), ctop);
   int clowtop = min(max(lowerTop, c.ceilClip), cbot);
@@ -834,7 +939,7 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
   if (endpointOnly) {
     for (int k = i0; k < i1; ++k) {
       int w = sc.secWalls[k];
-      GdHit h = HIT(w);
+      GdHit h = HITK(k);
       bool os = walls[w].oneSided;
       bool fut = (h.geo || (os && isfinite(h.d))) && (h.d > distance + 1e-3f);
       if (fut && h.d < cnd) { cnd = h.d; cni = w; }
@@ -889,6 +994,7 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
   }
   it.epFwdIdx = epFwdIdx; it.ppbIdx = ppbIdx; it.psPathIndex = psPathIndex; it.psFromFront = psFromFront;
 #undef HIT
+#undef HITK
 #undef SHARES_SEL
 }
 
@@ -901,7 +1007,7 @@ struct GdTierCtx {
   int tailBottom;   /* rows >= tailBottom use the group's first-column light; 255+ = never */
 };
 
-__device__ void gd_draw_tier(const GdScene &sc, const GdView &v, const GdShared &sh, int x, int ya, int yb, int ea,
+__device__ __noinline__ void gd_draw_tier(const GdScene &sc, const GdView &v, const GdShared &sh, int x, int ya, int yb, int ea,
                              int eb, int texId, float originZ, const GdTierCtx &t, i64 vis, i64 firstVis,
                              bool tailValid, int tailBottom, int oa, int ob, bool oTailValid, int oTailBottom,
                              unsigned *filled) {
@@ -930,7 +1036,7 @@ __device__ void gd_draw_tier(const GdScene &sc, const GdView &v, const GdShared 
   }
 }
 
-__device__ void gd_mark_plane(const GdScene &sc, const GdView &v, const GdShared &sh, int x, int ya, int yb,
+__device__ __noinline__ void gd_mark_plane(const GdScene &sc, const GdView &v, const GdShared &sh, int x, int ya, int yb,
                               int sector, bool isFloor, unsigned *owned, const unsigned *filled) {
   if (ya >= yb) return;
   bool any = false;
@@ -946,7 +1052,7 @@ __device__ void gd_mark_plane(const GdScene &sc, const GdView &v, const GdShared
 }
 
 __device__ void gd_walk(const GdScene &sc, const GdView &v, const GdShared &sh, GdEvent *events, int *eventCount,
-                        int *status, int startSector) {
+                        const GdRowProj *rowproj, int *status, int startSector) {
   const int x = threadIdx.x;
   const int lane = x & 31;
   const unsigned quadBase = lane & ~3u;
@@ -961,20 +1067,23 @@ __device__ void gd_walk(const GdScene &sc, const GdView &v, const GdShared &sh, 
   c.pendPortalBridgeSector = -1;
   c.pendPortalBridgeExit = 0.0f;
   bool settled = false;
+#ifdef GD_PROFILE_PHASES
+  long long gdW0 = clock64();
+#endif
   int nEvents = 0;
   bool overflow = false;
 
   for (int iter = 0; iter < sc.S; ++iter) {
     if (__all_sync(0xffffffffu, settled)) break;
-#ifdef GD_DEBUG_BEAT
-#define GD_TB(m) do { if (blockIdx.x == 0) ((volatile int *)status)[4 + x] = iter * 16 + (m); } while (0)
+#ifdef GD_PROFILE_PHASES
+#define GD_TB(m) do { if ((x & 31) == 0) { long long t = clock64(); atomicAdd((unsigned long long *)(status + 8) + 16 + (m), (unsigned long long)(t - gdW0)); gdW0 = t; } } while (0)
 #else
 #define GD_TB(m) do {} while (0)
 #endif
     GD_TB(0);
     GdIter it;
     if (!settled) {
-      gd_column_decide(sc, v, sh.walls, sh.ownerMask, x, rx, ry, c, it);
+      gd_column_decide(sc, v, sh.walls, sh.ownerMask, rowproj, x, rx, ry, c, it);
     } else {
       it.wall = -1 - x; it.side = 0; it.tier[0] = it.tier[1] = it.tier[2] = false;
       it.ctop = it.clowtop = 0; it.cbot = it.cupbot = 0; it.vis = 0;
@@ -1209,12 +1318,10 @@ __device__ int gd_sector_at(const GdScene &sc, float px, float py) {
 
 /* Flat-fallback resolution of a pixel (engine.py:10961-11026): true when the
  * column ray meets no sector's plane inside that sector's polygon. */
-__device__ bool gd_pixel_unresolved(const GdScene &sc, const GdView &v, int x, int y) {
+__device__ __noinline__ bool gd_pixel_unresolved(const GdScene &sc, const GdView &v, int x, int y, float rc, float rs) {
   i64 ti = gd_clamp((GD_ANG90 - v.pitchBam) >> 19, 0, 4095);
   i64 offFixed = ((i64)sc.fineTan[ti] * 12582912LL) >> 16;
   float center = 103.5f + (float)offFixed / 65536.0f;
-  float rayAngle = v.angle + sc.rayOffsets[x];
-  float rc = cosf(rayAngle), rs = sinf(rayAngle);
   float cc = sc.rayCosCorr[x];
   float delta = (float)y - center;
   bool floorPixel = delta > 0;
@@ -1248,7 +1355,7 @@ __device__ __forceinline__ float gd_wrap_angle(float a) {
 }
 
 /* ---- phase: sprites (engine.py:14138-14228, 14684-14947) ----------------- */
-__device__ void gd_actor_setup(const GdScene &sc, const GdView &v, const gd_thing &t, GdActor &ac) {
+__device__ __noinline__ void gd_actor_setup(const GdScene &sc, const GdView &v, const gd_thing &t, GdActor &ac) {
   ac.alive = (t.flags & GD_THING_ALIVE) != 0;
   ac.style = t.style;
   ac.x = t.x; ac.y = t.y;
@@ -1313,6 +1420,8 @@ __device__ void gd_sprites(const GdScene &sc, const GdView &v, const GdShared &s
   }
   if (!cand) return;
   const int nEv = eventCount[x];
+  const float rayAngle = v.angle + sc.rayOffsets[x];
+  const float rayCos = cosf(rayAngle), raySin = sinf(rayAngle);
   /* far to near: repeatedly take the remaining candidate with the largest
    * (depth, index) key */
   while (cand) {
@@ -1371,7 +1480,7 @@ __device__ void gd_sprites(const GdScene &sc, const GdView &v, const GdShared &s
         visible = gd_behind(sc, sh.walls[bestW], bestW, ac);
       } else {
         float limit = GD_INF;
-        if (!filled && ownerSector >= 0 && gd_pixel_unresolved(sc, v, x, y))
+        if (!filled && ownerSector >= 0 && gd_pixel_unresolved(sc, v, x, y, rayCos, raySin))
           limit = gd_plane_depth(sc, v, ownerSector, ownerFloor, y);
         visible = ac.depth < limit;
       }
@@ -1387,7 +1496,7 @@ __device__ void gd_sprites(const GdScene &sc, const GdView &v, const GdShared &s
 }
 
 /* ---- phase: weapon (engine.py:14994-15121) ------------------------------ */
-__device__ void gd_weapon_patch(const GdScene &sc, uint8_t *frame, int id, i64 hoff, i64 voff) {
+__device__ __noinline__ void gd_weapon_patch(const GdScene &sc, uint8_t *frame, int id, i64 hoff, i64 voff) {
   if (id < 0 || id >= sc.Q) return;
   const int4 wi = *reinterpret_cast<const int4 *>(&sc.wpnInfo[id * 4]);
   int w = wi.x, h = wi.y;
@@ -1434,7 +1543,7 @@ __device__ void gd_weapon(const GdScene &sc, const int32_t *lane, uint8_t *frame
 }
 
 /* ---- phase: status bar (engine.py:15158-15267) --------------------------- */
-__device__ void gd_hud_patch(const GdScene &sc, uint8_t *canvas, int patch, int x, int y) {
+__device__ __noinline__ void gd_hud_patch(const GdScene &sc, uint8_t *canvas, int patch, int x, int y) {
   __syncthreads();  /* patches overlap: keep the reference's draw order */
   const int4 hi = *reinterpret_cast<const int4 *>(&sc.hudInfo[patch * 4]);
   x -= hi.z;
@@ -1556,12 +1665,32 @@ __global__ void __launch_bounds__(GD_THREADS) gd_render_kernel(const GdParams p)
     const uint8_t *c = &sc.playpal[tid * 3];
     sh.pal64[tid] = (unsigned long long)c[0] | ((unsigned long long)c[1] << 20) | ((unsigned long long)c[2] << 40);
   }
-  GdEvent *events = (GdEvent *)(p.scratch + (size_t)blockIdx.x * GD_SCRATCH_PER_CTA);
-  int *eventCount = (int *)(p.scratch + (size_t)blockIdx.x * GD_SCRATCH_PER_CTA + GD_SCRATCH_EVENTS_BYTES);
+  uint8_t *myScratch = p.scratch + (size_t)blockIdx.x * gd_scratch_per_cta(sc.W);
+  GdEvent *events = (GdEvent *)myScratch;
+  int *eventCount = (int *)(myScratch + GD_SCRATCH_EVENTS_BYTES);
+  GdRowProj *rowproj = (GdRowProj *)(myScratch + GD_SCRATCH_FIXED);
 
-#define GD_BEAT(ph) do { if (blockIdx.x == 0 && tid == 0) { ((volatile int *)p.status)[1] = l; ((volatile int *)p.status)[2] = (ph); } } while (0)
-  for (int l = blockIdx.x; l < p.n; l += gridDim.x) {
+#ifdef GD_PROFILE_PHASES
+  long long gdT0 = clock64();
+  const long long gdStartClock = gdT0;
+  unsigned long long gdStartNs;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gdStartNs));
+#define GD_BEAT(ph) do { __syncthreads(); if (tid == 0) { long long t = clock64(); atomicAdd((unsigned long long *)(p.status + 8) + (ph), (unsigned long long)(t - gdT0)); gdT0 = t; } } while (0)
+#else
+#define GD_BEAT(ph) do {} while (0)
+#endif
+  /* Lanes differ a lot in cost (a long corridor crosses many sectors), so the
+   * persistent CTAs take lanes from a shared counter instead of a fixed stride.
+   * The counter pair lives behind the event scratch and is left at zero by the
+   * last CTA to finish. */
+  unsigned *queue = (unsigned *)(p.scratch + (size_t)p.queueOffset);
+  __shared__ int nextLane;
+  for (;;) {
     __syncthreads();
+    if (tid == 0) nextLane = (int)atomicAdd(&queue[0], 1u);
+    __syncthreads();
+    const int l = nextLane;
+    if (l >= p.n) break;
     GD_BEAT(1);
     if (p.flags & GD_F_STACK_FILL) {
       if (p.resetMask && !p.resetMask[l]) continue;  /* uniform across the CTA */
@@ -1593,6 +1722,11 @@ __global__ void __launch_bounds__(GD_THREADS) gd_render_kernel(const GdParams p)
     __syncthreads();
     GD_BEAT(2);
     gd_wall_spans(sc, v, sh.walls);
+    for (int idx = tid; idx < sc.W * 4; idx += GD_THREADS) {
+      int w = idx >> 2, slot = idx & 3;
+      int sector = sc.wsec[w * 2 + (slot >> 1)];
+      if (sector >= 0) gd_rowproj_setup(v, sh.walls[w], sc.secF[sector * 2 + (slot & 1)], rowproj[idx]);
+    }
     __syncthreads();
     GD_BEAT(3);
     for (int w = tid; w < sc.W; w += GD_THREADS) {
@@ -1614,7 +1748,7 @@ __global__ void __launch_bounds__(GD_THREADS) gd_render_kernel(const GdParams p)
     }
     __syncthreads();
     GD_BEAT(4);
-    gd_walk(sc, v, sh, events, eventCount, p.status, sh.misc[0]);
+    gd_walk(sc, v, sh, events, eventCount, rowproj, p.status, sh.misc[0]);
     GD_BEAT(5);
     gd_sprites(sc, v, sh, events, eventCount, nThings);
     __syncthreads();
@@ -1676,6 +1810,22 @@ __global__ void __launch_bounds__(GD_THREADS) gd_render_kernel(const GdParams p)
           for (int i = tid; i < vecs; i += GD_THREADS) s0[3 * vecs + i] = src[i];
         }
       }
+    }
+  }
+#ifdef GD_PROFILE_PHASES
+  if (tid == 0) {
+    unsigned long long ns;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
+    atomicAdd((unsigned long long *)(p.status + 8) + 12, ns - gdStartNs);
+    atomicAdd((unsigned long long *)(p.status + 8) + 13, (unsigned long long)(clock64() - gdStartClock));
+  }
+#endif
+  if (tid == 0) {
+    __threadfence();
+    if (atomicAdd(&queue[1], 1u) == gridDim.x - 1) {
+      queue[0] = 0;
+      queue[1] = 0;
+      __threadfence();
     }
   }
 }
@@ -1791,7 +1941,7 @@ extern "C" int gd_renderer_create(const void *blob_header_host, const void *blob
 extern "C" void gd_renderer_destroy(gd_renderer *r) { delete r; }
 
 extern "C" size_t gd_renderer_scratch_bytes(const gd_renderer *r) {
-  return r ? (size_t)r->ctas * GD_SCRATCH_PER_CTA : 0;
+  return r ? (size_t)r->ctas * gd_scratch_per_cta(r->sc.W) + 16 : 0;
 }
 
 extern "C" int gd_renderer_ctas(const gd_renderer *r) { return r ? r->ctas : 0; }
@@ -1813,6 +1963,7 @@ static int gd_launch(const gd_renderer *r, const int32_t *lanes, const gd_thing 
   p.lanes = lanes; p.things = things; p.maxThings = r->maxThings; p.n = n; p.flags = flags;
   p.stack = stack; p.resetMask = reset_mask; p.obsOut = obs_out; p.indexedOut = indexed_out; p.rgbOut = rgb_out;
   p.scratch = (uint8_t *)scratch; p.status = status;
+  p.queueOffset = (size_t)r->ctas * gd_scratch_per_cta(r->sc.W);
   int grid = n < r->ctas ? n : r->ctas;
   gd_render_kernel<<<grid, GD_THREADS, r->smemBytes, (cudaStream_t)stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? GD_OK : GD_ERR_CUDA;

@@ -100,7 +100,8 @@ class Renderer:
                                            self.max_things, ctypes.byref(handle)), "gd_renderer_create")
         self.handle = handle
         self.scratch_bytes = int(self.lib.gd_renderer_scratch_bytes(handle))
-        self.scratch = torch.empty(self.scratch_bytes, dtype=torch.uint8, device=self.device)
+        # zero-initialised: the tail holds the kernel's lane queue, which every launch leaves at zero
+        self.scratch = torch.zeros(self.scratch_bytes, dtype=torch.uint8, device=self.device)
         self.status = torch.zeros(4 + 320, dtype=torch.int32, device=self.device)
         self.ctas = int(self.lib.gd_renderer_ctas(handle))
         self.shared_bytes = int(self.lib.gd_renderer_shared_bytes(handle))

@@ -61,8 +61,10 @@ int gd_renderer_create(const void *blob_header_host, const void *blob_dev, size_
                        int max_things, gd_renderer **out);
 void gd_renderer_destroy(gd_renderer *r);
 
-/* Scratch the caller must provide to every render call (clip events of the
- * lanes being drawn; contents are meaningless between calls). */
+/* Scratch the caller must provide to every render call: clip events of the
+ * lanes being drawn plus, in its last 16 bytes, the kernel's lane queue.  Zero
+ * the buffer once after allocating it; every launch leaves the queue at zero.
+ * Launches that share a scratch buffer must not overlap on the device. */
 size_t gd_renderer_scratch_bytes(const gd_renderer *r);
 /* Launch shape, for reports: persistent CTAs and dynamic shared memory per CTA. */
 int gd_renderer_ctas(const gd_renderer *r);
