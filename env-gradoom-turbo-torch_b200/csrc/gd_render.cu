@@ -1858,6 +1858,8 @@ extern "C" const char *gd_error_string(int code) {
     case GD_ERR_CUDA: return "CUDA runtime call failed";
     case GD_ERR_SCRATCH: return "scratch buffer is too small";
     case GD_ERR_SHARED: return "scene needs more shared memory than one SM offers";
+    case GD_ERR_STATIC_LIMIT: return "scene or device index exceeds the limits of the built-in scratch array";
+    case GD_ERR_DEVICE: return "the renderer's device is not the current CUDA device";
     default: return "unknown error";
   }
 }
@@ -2021,4 +2023,68 @@ extern "C" int gd_render_step_host(const gd_renderer *r, const int32_t *lanes_ho
                         cudaMemcpyDeviceToHost, s) != cudaSuccess)
     return GD_ERR_CUDA;
   return GD_OK;
+}
+
+/* ---- allocation-free entry point ------------------------------------------
+ * gd_render_step for hosts that are not allowed to allocate device memory at
+ * all -- for instance a plugin loaded into an inference server or a game
+ * process whose memory pool is owned and fully budgeted by its embedder, or
+ * code that runs after the framework's allocator has been frozen.  Such a
+ * caller cannot obtain the scratch buffer the other entry points ask for, so
+ * this variant keeps the clip-event scratch in a fixed array inside the
+ * library image.  Every GPU that loads the library holds GD_STATIC_SCRATCH_BYTES
+ * of it until the process exits.
+ */
+#define GD_STATIC_MAX_CTAS 32
+#define GD_STATIC_MAX_WALLS 256
+#define GD_STATIC_PER_CTA ((GD_SCRATCH_FIXED + GD_STATIC_MAX_WALLS * 4 * sizeof(GdRowProj) + 15) & ~(size_t)15)
+#define GD_STATIC_SCRATCH_BYTES (GD_STATIC_MAX_CTAS * GD_STATIC_PER_CTA + 16)
+#define GD_STATIC_MAX_DEVICES 64
+
+static __device__ __align__(256) unsigned char gd_static_scratch[GD_STATIC_SCRATCH_BYTES];
+
+/* device address of the array above, looked up once per device */
+static unsigned char *gd_static_scratch_ptr[GD_STATIC_MAX_DEVICES];
+
+extern "C" size_t gd_static_scratch_bytes(void) { return GD_STATIC_SCRATCH_BYTES; }
+extern "C" int gd_static_max_walls(void) { return GD_STATIC_MAX_WALLS; }
+
+extern "C" int gd_render_step_static(const gd_renderer *r, const int32_t *lanes, const void *things, int n,
+                                     int mask_hud, uint8_t *stack, int *status, void *stream) {
+  if (!r || !lanes || !stack || !status) return GD_ERR_NULL;
+  if (r->maxThings > 0 && !things) return GD_ERR_NULL;
+  if (n < 0) return GD_ERR_SIZE;
+  if (r->sc.W > GD_STATIC_MAX_WALLS) return GD_ERR_STATIC_LIMIT;
+  if (r->device < 0 || r->device >= GD_STATIC_MAX_DEVICES) return GD_ERR_STATIC_LIMIT;
+  if (n == 0) return GD_OK;
+  uintptr_t align = (uintptr_t)lanes | (uintptr_t)things | (uintptr_t)stack;
+  if (align & 15) return GD_ERR_ALIGN;
+  int current = -1;
+  if (cudaGetDevice(&current) != cudaSuccess) return GD_ERR_CUDA;
+  if (current != r->device) return GD_ERR_DEVICE;  /* the renderer's device must be the current one */
+  unsigned char *scratch = gd_static_scratch_ptr[current];
+  if (!scratch) {
+    /* In host code the array's name is only a handle: the kernel needs the
+     * address the symbol has on this device. */
+    void *address = nullptr;
+    if (cudaGetSymbolAddress(&address, gd_static_scratch) != cudaSuccess || !address) {
+      cudaGetLastError();
+      return GD_ERR_CUDA;
+    }
+    scratch = (unsigned char *)address;
+    gd_static_scratch_ptr[current] = scratch;
+  }
+  GdParams p;
+  p.sc = r->sc;
+  p.lanes = lanes; p.things = (const gd_thing *)things; p.maxThings = r->maxThings; p.n = n;
+  p.flags = GD_F_STACK_ROLL | (mask_hud ? GD_F_MASK_HUD : GD_F_DRAW_HUD);
+  p.stack = stack; p.resetMask = nullptr; p.obsOut = nullptr; p.indexedOut = nullptr; p.rgbOut = nullptr;
+  p.scratch = scratch; p.status = status;
+  /* lane queue: the last 16 bytes of the array; zero when the library is
+   * loaded and left at zero by every launch */
+  p.queueOffset = (size_t)GD_STATIC_MAX_CTAS * GD_STATIC_PER_CTA;
+  int grid = n < r->ctas ? n : r->ctas;
+  if (grid > GD_STATIC_MAX_CTAS) grid = GD_STATIC_MAX_CTAS;
+  gd_render_kernel<<<grid, GD_THREADS, r->smemBytes, (cudaStream_t)stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? GD_OK : GD_ERR_CUDA;
 }

@@ -22,7 +22,7 @@ STATUS_THINGS_OVERFLOW = 2
 EXPORTS = (
     "gd_error_string", "gd_renderer_create", "gd_renderer_destroy", "gd_renderer_scratch_bytes",
     "gd_renderer_ctas", "gd_renderer_shared_bytes", "gd_render_step", "gd_render_reset", "gd_render_frames",
-    "gd_render_step_host",
+    "gd_render_step_host", "gd_static_scratch_bytes", "gd_static_max_walls", "gd_render_step_static",
 )
 
 _lib = None
@@ -63,6 +63,12 @@ def load() -> ctypes.CDLL:
         lib.gd_render_frames.argtypes = [vp, vp, vp, ci, ci, ci, vp, vp, vp, vp, sz, vp, vp]
         lib.gd_render_step_host.restype = ci
         lib.gd_render_step_host.argtypes = [vp, vp, vp, ci, ci, vp, vp, vp, vp, vp, sz, vp, vp]
+        lib.gd_static_scratch_bytes.restype = sz
+        lib.gd_static_scratch_bytes.argtypes = []
+        lib.gd_static_max_walls.restype = ci
+        lib.gd_static_max_walls.argtypes = []
+        lib.gd_render_step_static.restype = ci
+        lib.gd_render_step_static.argtypes = [vp, vp, vp, ci, ci, vp, vp, vp]
         _lib = lib
     return _lib
 
@@ -138,6 +144,19 @@ class Renderer:
         _check(self.lib.gd_render_step(self.handle, lanes.data_ptr(), things.data_ptr(), n, int(mask_hud),
                                        stack.data_ptr(), self.scratch.data_ptr(), self.scratch_bytes,
                                        self.status.data_ptr(), self._stream()), "gd_render_step")
+        self.launches += 1
+
+    def step_static(self, lanes, things, stack, mask_hud=True):
+        """``step`` without any caller-provided scratch: for hosts that must not
+        allocate device memory, the library's built-in scratch array is used
+        (scenes up to ``gd_static_max_walls()`` walls; calls must not overlap)."""
+
+        n = self._inputs(lanes, things)
+        self._check_stack(stack, n)
+        with torch.cuda.device(self.device):
+            _check(self.lib.gd_render_step_static(self.handle, lanes.data_ptr(), things.data_ptr(), n,
+                                                  int(mask_hud), stack.data_ptr(), self.status.data_ptr(),
+                                                  self._stream()), "gd_render_step_static")
         self.launches += 1
 
     def step_host(self, lanes_host, things_host, lanes_dev, things_dev, stack, obs_host, mask_hud=True):

@@ -37,7 +37,9 @@ enum gd_error {
   GD_ERR_ALIGN = -5,
   GD_ERR_CUDA = -6,
   GD_ERR_SCRATCH = -7,
-  GD_ERR_SHARED = -8
+  GD_ERR_SHARED = -8,
+  GD_ERR_STATIC_LIMIT = -9,
+  GD_ERR_DEVICE = -10
 };
 
 /* device status bits */
@@ -119,6 +121,27 @@ int gd_render_frames(const gd_renderer *r, const int32_t *lanes, const void *thi
 int gd_render_step_host(const gd_renderer *r, const int32_t *lanes_host, const void *things_host, int n,
                         int mask_hud, int32_t *lanes_dev, void *things_dev, uint8_t *stack, uint8_t *obs_host,
                         void *scratch, size_t scratch_bytes, int *status, void *stream);
+
+/*
+ * No counterpart in the reference.  gd_render_step for callers that may not
+ * allocate device memory -- a plugin inside a host process whose GPU memory
+ * pool is owned and budgeted by the embedding application, or code running
+ * after the framework's allocator has been frozen -- and therefore cannot
+ * provide the scratch buffer.  The scratch lives in a fixed array inside the
+ * library (gd_static_scratch_bytes(), about 12 MB, held by every GPU that loads
+ * the library until the process exits); the call allocates and frees nothing.
+ * Limits: scenes of at most gd_static_max_walls() walls (more: GD_ERR_STATIC_LIMIT)
+ * and at most 32 concurrently drawing CTAs, so it is slower than gd_render_step
+ * on large batches.  The renderer's device must be current (else GD_ERR_DEVICE).
+ * The first call on a device looks up the array's device address; make that
+ * call outside any stream capture.  All calls share the one array: two calls
+ * that overlap on the GPU (different streams) race.  Between calls nothing
+ * needs clearing: the kernel re-zeroes the few words that must start at zero.
+ */
+size_t gd_static_scratch_bytes(void);
+int gd_static_max_walls(void);
+int gd_render_step_static(const gd_renderer *r, const int32_t *lanes, const void *things, int n, int mask_hud,
+                          uint8_t *stack, int *status, void *stream);
 
 #ifdef __cplusplus
 }
