@@ -50,6 +50,8 @@ struct GdParams {
   uint8_t *rgbOut;           /* n x 240 x 320 x 3, optional */
   uint8_t *scratch;          /* ctas x gd_scratch_per_cta(W), then the lane queue (2 words, zero between launches) */
   size_t queueOffset;
+  int stageMask;             /* which scene tables each CTA copies into shared memory */
+  int secWallsN, vtxWallsN, V;
   int *status;
 };
 
@@ -84,6 +86,9 @@ struct GdShared {
   unsigned long long *pal64;  /* 256: R | G<<20 | B<<40 */
   uint8_t *obs;         /* 84 x 84 */
   int *misc;            /* 4 ints: start sector, thing count */
+  unsigned *masks;      /* 14 x 320: per-column filled / plane-owned row bitmasks */
+  float *hitD, *hitA;   /* 8 x 320 each: per-column cache of this iteration's wall hits */
+  uint8_t *hitF;        /* 8 x 320 */
 };
 
 __host__ __device__ inline size_t gd_align16(size_t v) { return (v + 15) & ~(size_t)15; }
@@ -101,6 +106,8 @@ __host__ __device__ inline size_t gd_shared_bytes(int W, int maxThings) {
   b += gd_align16(256 * 8);
   b += gd_align16(GD_OBS * GD_OBS);
   b += gd_align16(16);
+  b += gd_align16(14 * GD_SW * 4);
+  b += 2 * gd_align16(8 * GD_SW * 4) + gd_align16(8 * GD_SW);
   b += gd_align16((size_t)W * sizeof(GdWall));
   b += gd_align16((size_t)(maxThings > 0 ? maxThings : 1) * sizeof(GdActor));
   return b;
@@ -119,6 +126,10 @@ __device__ inline void gd_carve(uint8_t *base, int W, int maxThings, GdShared &s
   s.pal64 = (unsigned long long *)(base + o); o += gd_align16(256 * 8);
   s.obs = base + o; o += gd_align16(GD_OBS * GD_OBS);
   s.misc = (int *)(base + o); o += gd_align16(16);
+  s.masks = (unsigned *)(base + o); o += gd_align16(14 * GD_SW * 4);
+  s.hitD = (float *)(base + o); o += gd_align16(8 * GD_SW * 4);
+  s.hitA = (float *)(base + o); o += gd_align16(8 * GD_SW * 4);
+  s.hitF = base + o; o += gd_align16(8 * GD_SW);
   s.walls = (GdWall *)(base + o); o += gd_align16((size_t)W * sizeof(GdWall));
   s.actors = (GdActor *)(base + o);
 }
@@ -671,8 +682,9 @@ __device__ __forceinline__ uint8_t gd_plane_pixel(const GdPlaneSpan &p, const Gd
 }
 
 /* bit helpers over a 208-row column mask */
-__device__ __forceinline__ bool gd_bit(const unsigned *m, int y) { return (m[y >> 5] >> (y & 31)) & 1u; }
-__device__ __forceinline__ void gd_set(unsigned *m, int y) { m[y >> 5] |= 1u << (y & 31); }
+/* the masks live in shared memory, one word column per screen column */
+__device__ __forceinline__ bool gd_bit(const unsigned *m, int y) { return (m[(y >> 5) * GD_SW] >> (y & 31)) & 1u; }
+__device__ __forceinline__ void gd_set(unsigned *m, int y) { m[(y >> 5) * GD_SW] |= 1u << (y & 31); }
 
 /* ---- phase: per-column portal walk (engine.py:11561-13371) -------------- */
 struct GdColState {
@@ -719,28 +731,37 @@ struct GdIter {
 };
 
 __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWall *walls, const unsigned *ownerMask,
-                                 const GdRowProj *rowproj, int x, float rx, float ry, const GdColState &c,
-                                 GdIter &it) {
+                                 const GdRowProj *rowproj, float *hitD, float *hitA, uint8_t *hitF, int x, float rx,
+                                 float ry, const GdColState &c, GdIter &it) {
   const int curSector = c.cur;
   const int current = curSector < 0 ? 0 : curSector;
   const float prev = c.prev;
   const int i0 = sc.secOff[current], i1 = sc.secOff[current + 1];
-  /* every rule below looks at the walls of the current sector: test each once */
+  /* every rule below looks at the walls of the current sector: test each once
+   * and keep the results in this column's slice of shared memory */
   constexpr int kCache = 8;
-  GdHit cache[kCache];
-  int cacheWall[kCache];
   const int nCache = min(i1 - i0, kCache);
   for (int k = 0; k < nCache; ++k) {
-    cacheWall[k] = sc.secWalls[i0 + k];
-    cache[k] = gd_hit(sc, v, walls, cacheWall[k], x, rx, ry);
+    GdHit h = gd_hit(sc, v, walls, sc.secWalls[i0 + k], x, rx, ry);
+    hitD[k * GD_SW + x] = h.d;
+    hitA[k * GD_SW + x] = h.along;
+    hitF[k * GD_SW + x] = (uint8_t)((h.geo ? 1 : 0) | (h.proj ? 2 : 0) | (h.left ? 4 : 0));
   }
+  auto loadHit = [&](int k) -> GdHit {
+    GdHit h;
+    h.d = hitD[k * GD_SW + x];
+    h.along = hitA[k * GD_SW + x];
+    uint8_t f = hitF[k * GD_SW + x];
+    h.geo = f & 1; h.proj = (f & 2) != 0; h.left = (f & 4) != 0;
+    return h;
+  };
   auto cachedHit = [&](int w) -> GdHit {
     for (int k = 0; k < nCache; ++k)
-      if (cacheWall[k] == w) return cache[k];
+      if (sc.secWalls[i0 + k] == w) return loadHit(k);
     return gd_hit(sc, v, walls, w, x, rx, ry);
   };
 #define HIT(w) cachedHit(w)
-#define HITK(k) (((k) - i0) < nCache ? cache[(k) - i0] : gd_hit(sc, v, walls, sc.secWalls[k], x, rx, ry))
+#define HITK(k) (((k) - i0) < nCache ? loadHit((k) - i0) : gd_hit(sc, v, walls, sc.secWalls[k], x, rx, ry))
   float distance = GD_INF;
   int wallIndex = 0;
   if (curSector >= 0) {
@@ -1058,7 +1079,9 @@ __device__ void gd_walk(const GdScene &sc, const GdView &v, const GdShared &sh, 
   const unsigned quadBase = lane & ~3u;
   float rx, ry;
   gd_ray(v, x, rx, ry);
-  unsigned filled[7] = {0, 0, 0, 0, 0, 0, 0}, owned[7] = {0, 0, 0, 0, 0, 0, 0};
+  unsigned *filled = sh.masks + x, *owned = sh.masks + 7 * GD_SW + x;
+#pragma unroll
+  for (int k = 0; k < 7; ++k) { filled[k * GD_SW] = 0; owned[k * GD_SW] = 0; }
   GdColState c;
   c.cur = startSector; c.ceilClip = 0; c.floorClip = GD_VH; c.prev = 0.0f;
   c.pendOwnerBoundary = c.pendEpBoundary = c.pendEpBridgeBoundary = c.pendPortalBridge = false;
@@ -1081,9 +1104,14 @@ __device__ void gd_walk(const GdScene &sc, const GdView &v, const GdShared &sh, 
 #define GD_TB(m) do {} while (0)
 #endif
     GD_TB(0);
+#ifdef GD_PROFILE_PHASES
+    if ((x & 31) == 0) atomicAdd((unsigned long long *)(status + 8) + 24, 1ull);
+    if (!settled) atomicAdd((unsigned long long *)(status + 8) + 25, 1ull);
+    if (!settled && c.cur >= 0) atomicAdd((unsigned long long *)(status + 8) + 26, 1ull);
+#endif
     GdIter it;
     if (!settled) {
-      gd_column_decide(sc, v, sh.walls, sh.ownerMask, rowproj, x, rx, ry, c, it);
+      gd_column_decide(sc, v, sh.walls, sh.ownerMask, rowproj, sh.hitD, sh.hitA, sh.hitF, x, rx, ry, c, it);
     } else {
       it.wall = -1 - x; it.side = 0; it.tier[0] = it.tier[1] = it.tier[2] = false;
       it.ctop = it.clowtop = 0; it.cbot = it.cupbot = 0; it.vis = 0;
@@ -1649,14 +1677,84 @@ __device__ void gd_resize(const uint8_t *frame, const unsigned long long *pal64,
   }
 }
 
+/* ---- scene tables staged in shared memory ----------------------------------
+ * The column walk chases small topology tables (wall endpoints, sector lists,
+ * heights) through long dependent chains; from global memory every link costs
+ * an L1/L2 round trip.  Each CTA therefore copies the tables that fit into its
+ * shared memory once per launch, in this priority order, and redirects the
+ * scene's pointers to the copies. */
+enum {
+  GD_STAGE_WALLS = 1, GD_STAGE_WSEC = 2, GD_STAGE_SECLIST = 4, GD_STAGE_SECTORS = 8, GD_STAGE_WVTX = 16,
+  GD_STAGE_WLEN = 32, GD_STAGE_SIDETEX = 64, GD_STAGE_SIDEOFF = 128, GD_STAGE_VTXLIST = 256, GD_STAGE_ROWPROJ = 512
+};
+
+__host__ __device__ inline size_t gd_stage_bytes(int bit, int W, int S, int V, int secWallsN, int vtxWallsN) {
+  switch (bit) {
+    case GD_STAGE_WALLS: return gd_align16((size_t)W * 16);
+    case GD_STAGE_WSEC: return gd_align16((size_t)W * 8);
+    case GD_STAGE_SECLIST: return gd_align16((size_t)(S + 1) * 4) + gd_align16((size_t)(secWallsN > 0 ? secWallsN : 1) * 4);
+    case GD_STAGE_SECTORS: return gd_align16((size_t)S * 8) + gd_align16((size_t)S * 16);
+    case GD_STAGE_WVTX: return gd_align16((size_t)W * 8);
+    case GD_STAGE_WLEN: return gd_align16((size_t)W * 4);
+    case GD_STAGE_SIDETEX: return gd_align16((size_t)W * 24);
+    case GD_STAGE_SIDEOFF: return gd_align16((size_t)W * 16);
+    case GD_STAGE_VTXLIST: return gd_align16((size_t)(V + 1) * 4) + gd_align16((size_t)(vtxWallsN > 0 ? vtxWallsN : 1) * 4);
+    case GD_STAGE_ROWPROJ: return gd_align16((size_t)W * 4 * sizeof(GdRowProj));
+  }
+  return 0;
+}
+
+__device__ inline const void *gd_stage_copy(uint8_t *&cursor, const void *src, size_t bytes) {
+  uint8_t *dst = cursor;
+  const unsigned *s4 = (const unsigned *)src;
+  unsigned *d4 = (unsigned *)dst;
+  for (size_t i = threadIdx.x; i < bytes / 4; i += GD_THREADS) d4[i] = s4[i];
+  cursor += gd_align16(bytes);
+  return dst;
+}
+
 /* ---- the kernel ----------------------------------------------------------- */
 extern __shared__ __align__(16) uint8_t gd_smem[];
 
 __global__ void __launch_bounds__(GD_THREADS) gd_render_kernel(const GdParams p) {
-  const GdScene &sc = p.sc;
-  GdShared sh;
-  gd_carve(gd_smem, sc.W, p.maxThings, sh);
+  /* The scene descriptor, the shared-memory map and the lane's view are read by
+   * every helper through references; keeping them in shared memory (one copy
+   * per CTA) keeps those reads off the per-thread stack. */
+  __shared__ GdScene sScene;
+  __shared__ GdShared sShared;
+  __shared__ GdView sView;
   const int tid = threadIdx.x;
+  GdRowProj *stagedRowproj = nullptr;
+  {
+    GdScene sc = p.sc;
+    GdShared sh;
+    gd_carve(gd_smem, sc.W, p.maxThings, sh);
+    uint8_t *cursor = gd_smem + gd_shared_bytes(sc.W, p.maxThings);
+    const int m = p.stageMask;
+    if (m & GD_STAGE_WALLS) sc.walls = (const float *)gd_stage_copy(cursor, sc.walls, (size_t)sc.W * 16);
+    if (m & GD_STAGE_WSEC) sc.wsec = (const int32_t *)gd_stage_copy(cursor, sc.wsec, (size_t)sc.W * 8);
+    if (m & GD_STAGE_SECLIST) {
+      sc.secOff = (const int32_t *)gd_stage_copy(cursor, sc.secOff, (size_t)(sc.S + 1) * 4);
+      sc.secWalls = (const int32_t *)gd_stage_copy(cursor, sc.secWalls, (size_t)(p.secWallsN > 0 ? p.secWallsN : 1) * 4);
+    }
+    if (m & GD_STAGE_SECTORS) {
+      sc.secF = (const float *)gd_stage_copy(cursor, sc.secF, (size_t)sc.S * 8);
+      sc.secI = (const int32_t *)gd_stage_copy(cursor, sc.secI, (size_t)sc.S * 16);
+    }
+    if (m & GD_STAGE_WVTX) sc.wvtx = (const int32_t *)gd_stage_copy(cursor, sc.wvtx, (size_t)sc.W * 8);
+    if (m & GD_STAGE_WLEN) sc.wlen = (const float *)gd_stage_copy(cursor, sc.wlen, (size_t)sc.W * 4);
+    if (m & GD_STAGE_SIDETEX) sc.sideTex = (const int32_t *)gd_stage_copy(cursor, sc.sideTex, (size_t)sc.W * 24);
+    if (m & GD_STAGE_SIDEOFF) sc.sideOff = (const float *)gd_stage_copy(cursor, sc.sideOff, (size_t)sc.W * 16);
+    if (m & GD_STAGE_VTXLIST) {
+      sc.vtxOff = (const int32_t *)gd_stage_copy(cursor, sc.vtxOff, (size_t)(p.V + 1) * 4);
+      sc.vtxWalls = (const int32_t *)gd_stage_copy(cursor, sc.vtxWalls, (size_t)(p.vtxWallsN > 0 ? p.vtxWallsN : 1) * 4);
+    }
+    if (m & GD_STAGE_ROWPROJ) { stagedRowproj = (GdRowProj *)cursor; cursor += gd_align16((size_t)sc.W * 4 * sizeof(GdRowProj)); }
+    if (tid == 0) { sScene = sc; sShared = sh; }
+  }
+  __syncthreads();
+  const GdScene &sc = sScene;
+  const GdShared &sh = sShared;
   /* tables shared by every lane this CTA draws */
   for (int i = tid; i < 32 * 256 / 4; i += GD_THREADS)
     ((unsigned *)sh.colormap)[i] = ((const unsigned *)sc.colormap)[i];
@@ -1668,7 +1766,7 @@ __global__ void __launch_bounds__(GD_THREADS) gd_render_kernel(const GdParams p)
   uint8_t *myScratch = p.scratch + (size_t)blockIdx.x * gd_scratch_per_cta(sc.W);
   GdEvent *events = (GdEvent *)myScratch;
   int *eventCount = (int *)(myScratch + GD_SCRATCH_EVENTS_BYTES);
-  GdRowProj *rowproj = (GdRowProj *)(myScratch + GD_SCRATCH_FIXED);
+  GdRowProj *rowproj = stagedRowproj ? stagedRowproj : (GdRowProj *)(myScratch + GD_SCRATCH_FIXED);
 
 #ifdef GD_PROFILE_PHASES
   long long gdT0 = clock64();
@@ -1698,8 +1796,9 @@ __global__ void __launch_bounds__(GD_THREADS) gd_render_kernel(const GdParams p)
     if (tid < GD_LANE_WORDS) sh.lane[tid] = p.lanes[(size_t)l * GD_LANE_WORDS + tid];
     if (tid < 10) sh.ownerMask[tid] = 0;
     __syncthreads();
-    GdView v;
-    gd_view_setup(sc, sh.lane, v);
+    if (tid == 0) gd_view_setup(sc, sh.lane, sView);
+    __syncthreads();
+    const GdView &v = sView;
     if (tid < GD_VH) {
       /* yslope of the row (engine.py:10933-10946) */
       i64 centerRow = v.center >> 16;
@@ -1843,6 +1942,8 @@ struct gd_renderer {
   int maxThings;
   int ctas;
   size_t smemBytes;
+  int stageMask;
+  int secWallsN, vtxWallsN, V;
 };
 
 static const void *gd_section(const uint8_t *dev, const int32_t *h, int s) { return dev + h[GD_HDR_SECTION0 + s]; }
@@ -1915,11 +2016,18 @@ extern "C" int gd_renderer_create(const void *blob_header_host, const void *blob
   sc.secBBox = SECP(float, GD_S_SECTOR_BBOX);
 #undef SECP
   r->smemBytes = gd_shared_bytes(sc.W, max_things);
+  r->secWallsN = h[GD_H_SEC_WALLS_N]; r->vtxWallsN = h[GD_H_VTX_WALLS_N]; r->V = h[GD_H_VERTICES];
+  r->stageMask = 0;
   int prev = 0;
   if (cudaGetDevice(&prev) != cudaSuccess || cudaSetDevice(device) != cudaSuccess) { delete r; return GD_ERR_CUDA; }
   int maxOptin = 0, sms = 0;
   cudaDeviceGetAttribute(&maxOptin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  /* stage as many topology tables as the SM's shared memory still holds */
+  for (int bit = 1; bit <= GD_STAGE_ROWPROJ; bit <<= 1) {
+    size_t extra = gd_stage_bytes(bit, sc.W, sc.S, r->V, r->secWallsN, r->vtxWallsN);
+    if (r->smemBytes + extra + 1024 <= (size_t)maxOptin) { r->smemBytes += extra; r->stageMask |= bit; }
+  }
   int rc = GD_OK;
   if ((size_t)maxOptin < r->smemBytes) {
     rc = GD_ERR_SHARED;
@@ -1966,6 +2074,7 @@ static int gd_launch(const gd_renderer *r, const int32_t *lanes, const gd_thing 
   p.stack = stack; p.resetMask = reset_mask; p.obsOut = obs_out; p.indexedOut = indexed_out; p.rgbOut = rgb_out;
   p.scratch = (uint8_t *)scratch; p.status = status;
   p.queueOffset = (size_t)r->ctas * gd_scratch_per_cta(r->sc.W);
+  p.stageMask = r->stageMask; p.secWallsN = r->secWallsN; p.vtxWallsN = r->vtxWallsN; p.V = r->V;
   int grid = n < r->ctas ? n : r->ctas;
   gd_render_kernel<<<grid, GD_THREADS, r->smemBytes, (cudaStream_t)stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? GD_OK : GD_ERR_CUDA;
@@ -2083,6 +2192,7 @@ extern "C" int gd_render_step_static(const gd_renderer *r, const int32_t *lanes,
   /* lane queue: the last 16 bytes of the array; zero when the library is
    * loaded and left at zero by every launch */
   p.queueOffset = (size_t)GD_STATIC_MAX_CTAS * GD_STATIC_PER_CTA;
+  p.stageMask = r->stageMask; p.secWallsN = r->secWallsN; p.vtxWallsN = r->vtxWallsN; p.V = r->V;
   int grid = n < r->ctas ? n : r->ctas;
   if (grid > GD_STATIC_MAX_CTAS) grid = GD_STATIC_MAX_CTAS;
   gd_render_kernel<<<grid, GD_THREADS, r->smemBytes, (cudaStream_t)stream>>>(p);

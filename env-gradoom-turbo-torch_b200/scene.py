@@ -398,14 +398,14 @@ def make_grid_scene(spec: GridSpec) -> Scene:
 # ---------------------------------------------------------------------------
 
 GD_MAGIC = 0x4744424C
-GD_VERSION = 5
+GD_VERSION = 6
 GD_HDR_WORDS = 128
 GD_HDR_SECTION0 = 48
 
 _HEADER_WORDS = (
     "MAGIC VERSION BYTES WALLS SECTORS VERTICES TEXTURES TEX_H TEX_W SPRITES SPR_H SPR_W "
     "WPN_PATCHES WPN_H WPN_W WPN_TICS STARTS DEATH_FRAMES XDEATH_FRAMES BLOCKING NB_DIRECT "
-    "WPN_AVAILABLE HUD_PATCHES UNSUPPORTED"
+    "WPN_AVAILABLE HUD_PATCHES UNSUPPORTED SEC_WALLS_N VTX_WALLS_N"
 ).split()
 H = {name: i for i, name in enumerate(_HEADER_WORDS)}
 
@@ -728,6 +728,8 @@ def pack_scene(scene: Scene, ray_table_override=None) -> np.ndarray:
     header[H["WPN_AVAILABLE"]] = int(scene.wpn_widths.max() > 0)
     header[H["HUD_PATCHES"]] = len(scene.hud_atlas)
     header[H["UNSUPPORTED"]] = unsupported
+    header[H["SEC_WALLS_N"]] = int(sec_off[-1])
+    header[H["VTX_WALLS_N"]] = int(vtx_off[-1])
     blob = np.concatenate([header.view(np.uint8)] + chunks)
     assert blob.size == cursor
     return blob

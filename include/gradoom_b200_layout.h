@@ -14,7 +14,7 @@
 #include <stdint.h>
 
 #define GD_MAGIC 0x4744424C /* "GDBL" */
-#define GD_VERSION 5
+#define GD_VERSION 6
 #define GD_HDR_WORDS 128
 #define GD_HDR_SECTION0 48
 
@@ -51,6 +51,8 @@ enum gd_header_word {
   GD_H_WPN_AVAILABLE,
   GD_H_HUD_PATCHES,
   GD_H_UNSUPPORTED,  /* nonzero: scene uses a feature outside this path */
+  GD_H_SEC_WALLS_N,  /* entries of GD_S_SEC_WALLS */
+  GD_H_VTX_WALLS_N,  /* entries of GD_S_VTX_WALLS */
   GD_H_COUNT
 };
 

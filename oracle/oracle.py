@@ -24,7 +24,9 @@ _lib = None
 
 
 def build(force: bool = False) -> str:
-    stale = (not os.path.exists(LIBRARY)) or os.path.getmtime(LIBRARY) < os.path.getmtime(SOURCE)
+    header = os.path.join(HERE, "..", "include", "gradoom_b200_layout.h")
+    stale = (not os.path.exists(LIBRARY)) or os.path.getmtime(LIBRARY) < max(
+        os.path.getmtime(SOURCE), os.path.getmtime(header))
     if force or stale:
         subprocess.check_call(
             ["gcc", "-O2", "-ffp-contract=off", "-fno-fast-math", "-fPIC", "-shared",
