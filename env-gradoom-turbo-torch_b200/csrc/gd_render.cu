@@ -85,7 +85,7 @@ struct GdShared {
   GdActor *actors;      /* maxThings */
   unsigned long long *pal64;  /* 256: R | G<<20 | B<<40 */
   uint8_t *obs;         /* 84 x 84 */
-  int *misc;            /* 4 ints: start sector, thing count */
+  int *misc;            /* 16 ints: start sector, fallback queue length, its unresolved rows' range, GdFlatBounds */
   unsigned *masks;      /* 14 x 320: per-column filled / plane-owned row bitmasks */
   float *hitD, *hitA;   /* 8 x 320 each: per-column cache of this iteration's wall hits */
   uint8_t *hitF;        /* 8 x 320 */
@@ -105,7 +105,7 @@ __host__ __device__ inline size_t gd_shared_bytes(int W, int maxThings) {
   b += gd_align16(16 * 4);
   b += gd_align16(256 * 8);
   b += gd_align16(GD_OBS * GD_OBS);
-  b += gd_align16(16);
+  b += gd_align16(64);
   b += gd_align16(14 * GD_SW * 4);
   b += 2 * gd_align16(8 * GD_SW * 4) + gd_align16(8 * GD_SW);
   b += gd_align16((size_t)W * sizeof(GdWall));
@@ -125,7 +125,7 @@ __device__ inline void gd_carve(uint8_t *base, int W, int maxThings, GdShared &s
   s.ownerMask = (unsigned *)(base + o); o += gd_align16(16 * 4);
   s.pal64 = (unsigned long long *)(base + o); o += gd_align16(256 * 8);
   s.obs = base + o; o += gd_align16(GD_OBS * GD_OBS);
-  s.misc = (int *)(base + o); o += gd_align16(16);
+  s.misc = (int *)(base + o); o += gd_align16(64);
   s.masks = (unsigned *)(base + o); o += gd_align16(14 * GD_SW * 4);
   s.hitD = (float *)(base + o); o += gd_align16(8 * GD_SW * 4);
   s.hitA = (float *)(base + o); o += gd_align16(8 * GD_SW * 4);
@@ -1389,109 +1389,226 @@ __device__ __forceinline__ float gd_wrap_angle(float a) {
  * pixels those repairs would read for the one pixel asked for. */
 struct GdFlatProbe { bool unresolved, isFloor; int sector; };
 
-__device__ __noinline__ GdFlatProbe gd_flat_resolve(const GdScene &sc, const GdView &v, int x, int y, int currentSector) {
+/* the part of a probe that depends on the column only */
+struct GdFlatRay { float rc, rs, cc, center; };
+
+/* Per-lane bounds that let a probe prove "no sector" without visiting any:
+ * the smallest positive plane height of either orientation (the nearest plane
+ * point of every sector lies at least that far along the ray) and the box
+ * outside which gd_point_in_sector rejects every sector. */
+struct GdFlatBounds { float phFloor, phCeil, xHi, xLo, yHi, yLo; int allClosed; };
+
+__device__ __forceinline__ GdFlatBounds gd_flat_bounds_load(const int *misc) {
+  GdFlatBounds b;
+  b.phFloor = __int_as_float(misc[4]); b.phCeil = __int_as_float(misc[5]);
+  b.xHi = __int_as_float(misc[6]); b.xLo = __int_as_float(misc[7]);
+  b.yHi = __int_as_float(misc[8]); b.yLo = __int_as_float(misc[9]);
+  b.allClosed = misc[10];
+  return b;
+}
+
+/* warp 0 fills misc[4..10] */
+__device__ void gd_flat_bounds_setup(const GdScene &sc, const GdView &v, int *misc) {
+  const int lane = threadIdx.x & 31;
+  float phF = GD_INF, phC = GD_INF, xHi = -GD_INF, xLo = GD_INF, yHi = -GD_INF, yLo = GD_INF;
+  int closed = 1;
+  for (int s = lane; s < sc.S; s += 32) {
+    float f = v.viewZ - sc.secF[s * 2], c = sc.secF[s * 2 + 1] - v.viewZ;
+    if (f > 0) phF = fminf(phF, f);
+    if (c > 0) phC = fminf(phC, c);
+    const float4 bb = *reinterpret_cast<const float4 *>(&sc.secBBox[s * 4]);
+    xHi = fmaxf(xHi, bb.y + 1.0f);
+    xLo = fminf(xLo, bb.x - 1.0f);
+    yHi = fmaxf(yHi, bb.w);
+    yLo = fminf(yLo, bb.z);
+    closed &= sc.secI[s * 4 + 3] != 0;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    phF = fminf(phF, __shfl_xor_sync(0xffffffffu, phF, o));
+    phC = fminf(phC, __shfl_xor_sync(0xffffffffu, phC, o));
+    xHi = fmaxf(xHi, __shfl_xor_sync(0xffffffffu, xHi, o));
+    xLo = fminf(xLo, __shfl_xor_sync(0xffffffffu, xLo, o));
+    yHi = fmaxf(yHi, __shfl_xor_sync(0xffffffffu, yHi, o));
+    yLo = fminf(yLo, __shfl_xor_sync(0xffffffffu, yLo, o));
+    closed &= __shfl_xor_sync(0xffffffffu, closed, o);
+  }
+  if (lane == 0) {
+    misc[4] = __float_as_int(phF); misc[5] = __float_as_int(phC);
+    misc[6] = __float_as_int(xHi); misc[7] = __float_as_int(xLo);
+    misc[8] = __float_as_int(yHi); misc[9] = __float_as_int(yLo);
+    misc[10] = closed;
+  }
+}
+
+__device__ __forceinline__ GdFlatRay gd_flat_ray(const GdScene &sc, const GdView &v, int x) {
   i64 ti = gd_clamp((GD_ANG90 - v.pitchBam) >> 19, 0, 4095);
   i64 offFixed = ((i64)sc.fineTan[ti] * 12582912LL) >> 16;
-  float center = 103.5f + (float)offFixed / 65536.0f;
+  GdFlatRay r;
+  r.center = 103.5f + (float)offFixed / 65536.0f;
   float rayAngle = v.angle + sc.rayOffsets[x];
-  float rc = cosf(rayAngle), rs = sinf(rayAngle);
-  float cc = sc.rayCosCorr[x];
-  float delta = (float)y - center;
+  r.rc = cosf(rayAngle);
+  r.rs = sinf(rayAngle);
+  r.cc = sc.rayCosCorr[x];
+  return r;
+}
+
+__device__ __noinline__ GdFlatProbe gd_flat_probe(const GdScene &sc, const GdView &v, const GdFlatRay &r,
+                                                  const GdFlatBounds &b, int y, int currentSector) {
+  float delta = (float)y - r.center;
   GdFlatProbe out;
   out.isFloor = delta > 0;
   float den = fmaxf(fabsf(delta), 0.5f);
-  float best = GD_INF;
   out.sector = currentSector;
+  out.unresolved = true;
+  {
+    /* Every sector's plane point lies at cd >= cd0 along the ray, and each
+     * coordinate moves monotonically with cd (the roundings are monotone too):
+     * once the nearest candidate is past the box on the side the ray is
+     * heading to, every sector rejects every candidate. */
+    float ph0 = out.isFloor ? b.phFloor : b.phCeil;
+    float cd0 = ph0 * 192.0f / den / r.cc;
+    if (!isfinite(cd0)) return out;
+    if (cd0 > 0) {
+      float px0 = v.x + r.rc * cd0, py0 = v.y + r.rs * cd0;
+      if (r.rc > 0 && px0 > b.xHi) return out;
+      if (r.rc < 0 && b.allClosed && px0 < b.xLo) return out;
+      if (r.rs > 0 && py0 >= b.yHi) return out;
+      if (r.rs < 0 && py0 < b.yLo) return out;
+    }
+  }
+  float best = GD_INF;
   for (int s = 0; s < sc.S; ++s) {
     float ph = out.isFloor ? (v.viewZ - sc.secF[s * 2]) : (sc.secF[s * 2 + 1] - v.viewZ);
     float perp = ph * 192.0f / den;
-    float cd = perp / cc;
+    float cd = perp / r.cc;
     if (!(ph > 0) || !isfinite(cd) || !(cd > 0) || !(cd < best)) continue;
-    float px = v.x + rc * cd, py = v.y + rs * cd;
+    float px = v.x + r.rc * cd, py = v.y + r.rs * cd;
     if (gd_point_in_sector(sc, s, px, py)) { best = cd; out.sector = s; }
   }
   out.unresolved = !isfinite(best);
   return out;
 }
 
-/* sector of pixel (x,y) after the vertical repair; `anchor` tells whether the
- * pixel anchors horizontal spans */
-__device__ int gd_flat_vertical(const GdScene &sc, const GdView &v, int x, int y, int currentSector, bool &anchor,
-                                bool &unresolved, bool &isFloor) {
-  GdFlatProbe p = gd_flat_resolve(sc, v, x, y, currentSector);
-  unresolved = p.unresolved;
-  isFloor = p.isFloor;
-  if (!p.unresolved) { anchor = true; return p.sector; }
-  for (int yy = y + 1; yy < GD_VH; ++yy) {
-    GdFlatProbe q = gd_flat_resolve(sc, v, x, yy, currentSector);
-    if (q.isFloor != p.isFloor) break;  /* orientation flips once, at the view centre */
-    if (!q.unresolved) { anchor = q.sector != currentSector; return q.sector; }
+/* Sector of pixel (x,y) after the vertical repair, computed by a whole warp
+ * (32 rows per step); `anchor` tells whether the pixel anchors horizontal
+ * spans.  Every lane passes the same arguments and gets the same result. */
+__device__ int gd_flat_vertical_warp(const GdScene &sc, const GdView &v, const GdFlatBounds &b, int x, int y,
+                                     int currentSector, bool &anchor, bool &unresolved, bool &isFloor) {
+  const int lane = threadIdx.x & 31;
+  const GdFlatRay r = gd_flat_ray(sc, v, x);
+  GdFlatProbe own = gd_flat_probe(sc, v, r, b, y, currentSector);
+  unresolved = own.unresolved;
+  isFloor = own.isFloor;
+  anchor = !own.unresolved;
+  int sector = own.sector;
+  if (!own.unresolved) return sector;
+  for (int base = y + 1; base < GD_VH; base += 32) {
+    int yy = base + lane;
+    bool valid = yy < GD_VH;
+    GdFlatProbe q;
+    q.unresolved = true; q.isFloor = isFloor; q.sector = 0;
+    if (valid) q = gd_flat_probe(sc, v, r, b, yy, currentSector);
+    unsigned flip = __ballot_sync(0xffffffffu, valid && q.isFloor != isFloor);
+    unsigned hit = __ballot_sync(0xffffffffu, valid && q.isFloor == isFloor && !q.unresolved);
+    /* the orientation flips once, at the view centre: only rows before it count */
+    if (flip) hit &= (1u << (__ffs(flip) - 1)) - 1u;
+    int found = __shfl_sync(0xffffffffu, q.sector, hit ? __ffs(hit) - 1 : 0);
+    if (hit) {
+      anchor = found != currentSector;
+      return found;
+    }
+    if (flip) break;
   }
-  anchor = false;
-  return p.sector;
+  return sector;
 }
 
-/* Pass over the queued pixels, one warp per pixel.  A resolved pixel needs
- * nothing but its own probe.  An unresolved one needs the nearest anchors of
- * its row: the warp probes 32 columns at a time outwards, left then right. */
+/* Pass over the queued pixels.
+ *   A  one thread per queued pixel probes it; a resolved pixel is drawn at
+ *      once and leaves the queue.
+ *   B  only when unresolved pixels remain, in rows minY..maxY: one thread per
+ *      column first looks below maxY for the nearest resolved row, then sweeps
+ *      maxY..minY bottom-up carrying the nearest resolved row below, and
+ *      records in a bit per pixel whether the vertically repaired pixel is an
+ *      anchor.
+ *   C  one warp per remaining pixel: nearest anchors left and right in the
+ *      pixel's row from those bits, their sectors by a vertical repair each. */
 __device__ void gd_fallback_pass(const GdScene &sc, const GdView &v, const GdShared &sh, int currentSector) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int count = min(sh.misc[1], GD_FALLBACK_MAX);
-  const int *queue = (const int *)sh.hitD;
-  for (int i = warp; i < count; i += GD_WARPS) {
+  int *queue = (int *)sh.hitD;
+  unsigned *anchors = (unsigned *)sh.hitA;           /* [row][GD_WARPS] column bits */
+  if (tid == 0) { sh.misc[2] = GD_VH; sh.misc[3] = -1; }
+  if (warp == 0) gd_flat_bounds_setup(sc, v, sh.misc);
+  __syncthreads();
+  const GdFlatBounds b = gd_flat_bounds_load(sh.misc);
+  for (int i = tid; i < count; i += GD_THREADS) {
     const int px = queue[i] & 0xFFFF, py = queue[i] >> 16;
-    /* the pixel's own probe and vertical repair, 32 rows per step */
-    bool anchor = false, unresolved = false, isFloor = false;
-    int sector = 0;
-    {
-      GdFlatProbe own = gd_flat_resolve(sc, v, px, py, currentSector);   /* all lanes: same pixel */
-      unresolved = own.unresolved; isFloor = own.isFloor; sector = own.sector;
-      anchor = !unresolved;
-      if (unresolved) {
-        bool done = false;
-        for (int base = py + 1; base < GD_VH && !done; base += 32) {
-          int yy = base + lane;
-          bool valid = yy < GD_VH;
-          GdFlatProbe q;
-          q.unresolved = true; q.isFloor = isFloor; q.sector = 0;
-          if (valid) q = gd_flat_resolve(sc, v, px, yy, currentSector);
-          unsigned flip = __ballot_sync(0xffffffffu, valid && q.isFloor != isFloor);
-          unsigned hit = __ballot_sync(0xffffffffu, valid && q.isFloor == isFloor && !q.unresolved);
-          /* only rows before the orientation flips count */
-          if (flip) hit &= (1u << (__ffs(flip) - 1)) - 1u;
-          if (hit) {
-            int src = __ffs(hit) - 1;
-            int found = __shfl_sync(0xffffffffu, q.sector, src);
-            sector = found;
-            anchor = found != currentSector;
-            done = true;
-          } else if (flip) {
-            done = true;
-          }
-        }
+    const GdFlatRay r = gd_flat_ray(sc, v, px);
+    GdFlatProbe own = gd_flat_probe(sc, v, r, b, py, currentSector);
+    if (!own.unresolved) {
+      GdPlaneSpan p;
+      gd_plane_setup(sc, v, own.sector, own.isFloor, px, p);
+      sh.frame[py * GD_SW + px] = gd_plane_pixel(p, v, sh.yslope, sh.colormap, py);
+      queue[i] = -1;
+    } else {
+      atomicMin(&sh.misc[2], py);
+      atomicMax(&sh.misc[3], py);
+    }
+  }
+  __syncthreads();
+  const int minY = sh.misc[2], maxY = sh.misc[3];
+  if (maxY < 0) return;                               /* block-uniform */
+  {
+    const GdFlatRay r = gd_flat_ray(sc, v, tid);
+    const int flipRow = gd_clamp((int)floorf(r.center) + 1, 0, GD_VH);   /* first floor row */
+    /* nearest resolved row below maxY, of maxY's orientation */
+    bool haveBelow = false, belowFloor = false;
+    int belowSector = 0;
+    const int limit = maxY < flipRow ? flipRow : GD_VH;
+    for (int y = maxY + 1; y < limit; ++y) {
+      GdFlatProbe q = gd_flat_probe(sc, v, r, b, y, currentSector);
+      if (!q.unresolved) { haveBelow = true; belowFloor = q.isFloor; belowSector = q.sector; break; }
+    }
+    __syncwarp();
+    for (int y = maxY; y >= minY; --y) {
+      GdFlatProbe q = gd_flat_probe(sc, v, r, b, y, currentSector);
+      bool anchor;
+      if (!q.unresolved) {
+        anchor = true;
+        haveBelow = true; belowFloor = q.isFloor; belowSector = q.sector;
+      } else {
+        anchor = haveBelow && belowFloor == q.isFloor && belowSector != currentSector;
+      }
+      unsigned m = __ballot_sync(0xffffffffu, anchor);
+      if (lane == 0) anchors[y * GD_WARPS + warp] = m;
+    }
+  }
+  __syncthreads();
+  for (int i = warp; i < count; i += GD_WARPS) {
+    if (queue[i] < 0) continue;                       /* warp-uniform */
+    const int px = queue[i] & 0xFFFF, py = queue[i] >> 16;
+    bool anchor, unresolved, isFloor;
+    int sector = gd_flat_vertical_warp(sc, v, b, px, py, currentSector, anchor, unresolved, isFloor);
+    /* nearest anchor at or left of px, at or right of px */
+    int left = -1, right = -1;
+    for (int w = 0; w < GD_WARPS; ++w) {
+      unsigned bits = anchors[py * GD_WARPS + w];
+      int base = w * 32;
+      if (base <= px) {
+        unsigned lo = px - base >= 31 ? bits : (bits & ((2u << (px - base)) - 1u));
+        if (lo) left = base + 31 - __clz(lo);
+      }
+      if (base + 31 >= px && right < 0) {
+        unsigned hi = px - base <= 0 ? bits : (bits & ~((1u << (px - base)) - 1u));
+        if (hi) right = base + __ffs(hi) - 1;
       }
     }
-    if (unresolved) {
-      int side[2] = {-1, -1};
-#pragma unroll
-      for (int dir = 0; dir < 2; ++dir) {
-        if (dir == 1 && side[0] < 0) break;
-        for (int base = 0; base < GD_SW && side[dir] < 0; base += 32) {
-          int xx = dir == 0 ? px - base - lane : px + base + lane;
-          bool valid = xx >= 0 && xx < GD_SW;
-          bool a = false, u, f;
-          int sct = -1;
-          if (valid) {
-            if (xx == px) { a = anchor; sct = sector; }
-            else sct = gd_flat_vertical(sc, v, xx, py, currentSector, a, u, f);
-          }
-          unsigned m = __ballot_sync(0xffffffffu, valid && a);
-          unsigned any = __ballot_sync(0xffffffffu, valid);
-          if (m) side[dir] = __shfl_sync(0xffffffffu, sct, __ffs(m) - 1);
-          if (!any) break;
-        }
-      }
-      if (side[0] >= 0 && side[1] >= 0 && side[0] == side[1]) sector = side[0];
+    if (left >= 0 && right >= 0) {
+      bool a, u, f;
+      int sl = left == px ? sector : gd_flat_vertical_warp(sc, v, b, left, py, currentSector, a, u, f);
+      int sr = right == px ? sector : gd_flat_vertical_warp(sc, v, b, right, py, currentSector, a, u, f);
+      if (sl == sr) sector = sl;
     }
     if (lane == 0) {
       GdPlaneSpan p;

@@ -235,3 +235,32 @@ def test_unclaimed_pixels_show_the_flat_fallback(pkg, oracle, scenes):
     _, indexed, _ = r.frames(_dev(lanes[chosen]), _dev(things[chosen]), indexed=True)
     r.check_status()
     assert np.array_equal(indexed.cpu().numpy(), expected["indexed"][chosen])
+
+
+@pytest.mark.gpu
+def test_flat_fallback_after_free_movement(pkg, oracle, scenes):
+    """Players that have walked freely stand on or next to portal lines now and
+    then; their frames need the fallback's vertical and horizontal repairs."""
+
+    import torch
+
+    from gradoom_b200 import stepper
+    from gradoom_b200.env import action_matrix
+
+    sc, blob = scenes("c2")
+    n = 512
+    producer = stepper.LaneStepper(sc, n, device="cpu", k_things=12, max_things=12, seed=1000)
+    producer.reset(torch.ones(n, dtype=torch.bool), torch.arange(n) + 1)
+    table = action_matrix("cpu")
+    g = torch.Generator().manual_seed(20260813)
+    for _ in range(8):
+        producer.step(table[torch.randint(0, table.shape[0], (n,), generator=g)])
+    lanes_t, things_t = producer.render_inputs()
+    lanes, things = lanes_t.numpy().copy(), things_t.numpy().copy()
+    expected = oracle.render(blob, lanes, things)
+    chosen = np.flatnonzero(expected["unowned"] > 0)
+    assert len(chosen) >= 4, "the seeded batch is expected to contain such lanes"
+    r = _renderer(blob, 12)
+    _, indexed, _ = r.frames(_dev(lanes[chosen]), _dev(things[chosen]), indexed=True)
+    r.check_status()
+    assert np.array_equal(indexed.cpu().numpy(), expected["indexed"][chosen])
