@@ -1953,7 +1953,7 @@ __device__ inline const void *gd_stage_copy(uint8_t *&cursor, const void *src, s
 /* ---- the kernel ----------------------------------------------------------- */
 extern __shared__ __align__(16) uint8_t gd_smem[];
 
-__global__ void __launch_bounds__(GD_THREADS) gd_render_kernel(const GdParams p) {
+__global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams p) {
   /* The scene descriptor, the shared-memory map and the lane's view are read by
    * every helper through references; keeping them in shared memory (one copy
    * per CTA) keeps those reads off the per-thread stack. */
