@@ -37,6 +37,9 @@ METRIC = "rendered env-frames/sec at 4096 lanes/GPU"
 UNIT = "frames/s"
 # algorithmic HBM bytes per env-frame: newest 84x84 slot + 64 B lane scalars + 16 B per thing
 BYTES_PER_FRAME = 84 * 84 + 64 + 16 * THINGS
+# dram__bytes_read.sum + dram__bytes_write.sum of one render launch at 4096 lanes (a one-pass ncu
+# capture of this file's default command), per lane; mostly the oldest-first roll of the frame stack
+DRAM_TRAFFIC_PER_LANE = 168.3e6 / 4096
 
 
 def measured_peaks():
@@ -292,7 +295,8 @@ def run_ours(args):
                        "ctas": renderer.ctas, "shared_bytes_per_cta": renderer.shared_bytes,
                        "stack_policy": "roll (read 3 + write 4 slots per lane)"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": peak_kind,
+                         "traffic": DRAM_TRAFFIC_PER_LANE * n if n == 4096 else None,
+                         "traffic_source": "ncu capture of this command at 4096 lanes/GPU", "peak_source": peak_kind,
                          "algorithmic_bytes_per_launch": BYTES_PER_FRAME * n,
                          "kernel_ms": avg_ms, "pixels_per_s": 320 * 208 * n / (avg_ms / 1000.0)},
             "cpu_baseline": {"value": cpu_value, "unit": UNIT, "cores": 1, "kind": "port",
