@@ -681,10 +681,15 @@ __device__ __forceinline__ uint8_t gd_plane_pixel(const GdPlaneSpan &p, const Gd
   return colormap[shade * 256 + texel];
 }
 
-/* bit helpers over a 208-row column mask */
-/* the masks live in shared memory, one word column per screen column */
-__device__ __forceinline__ bool gd_bit(const unsigned *m, int y) { return (m[(y >> 5) * GD_SW] >> (y & 31)) & 1u; }
-__device__ __forceinline__ void gd_set(unsigned *m, int y) { m[(y >> 5) * GD_SW] |= 1u << (y & 31); }
+/* The 208-row column masks live in shared memory, one word column per screen
+ * column: word k of column x is m[k * GD_SW]. */
+/* bits of mask word k (rows 32k..32k+31) that lie in rows [a,b) */
+__device__ __forceinline__ unsigned gd_range_word(int k, int a, int b) {
+  int lo = max(a - (k << 5), 0), hi = min(b - (k << 5), 32);
+  if (lo >= hi) return 0u;
+  unsigned upto = hi == 32 ? 0xffffffffu : ((1u << hi) - 1u);
+  return upto & ~((1u << lo) - 1u);
+}
 
 /* ---- phase: per-column portal walk (engine.py:11561-13371) -------------- */
 struct GdColState {
@@ -1045,30 +1050,60 @@ __device__ __noinline__ void gd_draw_tier(const GdScene &sc, const GdView &v, co
   const uint8_t *col = sc.texAtlasCol + ((size_t)texId * sc.texW + u) * sc.texH;
   int shadeN = gd_wall_shade(t.light, vis), shadeT = gd_wall_shade(t.light, firstVis);
   const uint8_t *cmN = sh.colormap + shadeN * 256, *cmT = sh.colormap + shadeT * 256;
-  for (int y = ya; y < yb; ++y) {
-    if (y >= ea && y < eb) continue;
-    if (gd_bit(filled, y)) continue;
-    unsigned frac = base + (unsigned)y * step;
-    unsigned tv = frac >> (32 - hbits);
-    uint8_t texel = col[tv];
-    bool tail = (tailValid && y >= tailBottom) || (oTailValid && y >= oa && y < ob && y >= oTailBottom);
-    sh.frame[y * GD_SW + x] = (tail ? cmT : cmN)[texel];
-    gd_set(filled, y);
+  /* rows lit with the group's first-column light */
+  const int tailA = tailValid ? tailBottom : GD_VH, oTailA = oTailValid ? max(oa, oTailBottom) : 0,
+            oTailB = oTailValid ? ob : 0;
+  const int shift = 32 - hbits;
+  uint8_t *dst = sh.frame + x;
+  for (int k = ya >> 5; k <= (yb - 1) >> 5; ++k) {
+    unsigned have = filled[k * GD_SW];
+    unsigned m = gd_range_word(k, ya, yb) & ~gd_range_word(k, ea, eb) & ~have;
+    if (!m) continue;
+    filled[k * GD_SW] = have | m;
+    const unsigned tailM = gd_range_word(k, tailA, GD_VH) | gd_range_word(k, oTailA, oTailB);
+    const int y0 = k << 5;
+    /* two rows per trip; an odd last row is simply drawn twice */
+    while (m) {
+      int b0 = __ffs(m) - 1;
+      m &= m - 1;
+      int b1 = m ? __ffs(m) - 1 : b0;
+      m &= m - 1;
+      unsigned f0 = base + (unsigned)(y0 + b0) * step, f1 = base + (unsigned)(y0 + b1) * step;
+      uint8_t t0 = col[f0 >> shift], t1 = col[f1 >> shift];
+      uint8_t p0 = ((tailM >> b0) & 1u ? cmT : cmN)[t0], p1 = ((tailM >> b1) & 1u ? cmT : cmN)[t1];
+      dst[(y0 + b0) * GD_SW] = p0;
+      dst[(y0 + b1) * GD_SW] = p1;
+    }
   }
 }
 
 __device__ __noinline__ void gd_mark_plane(const GdScene &sc, const GdView &v, const GdShared &sh, int x, int ya, int yb,
                               int sector, bool isFloor, unsigned *owned, const unsigned *filled) {
   if (ya >= yb) return;
-  bool any = false;
-  for (int y = ya; y < yb; ++y) any |= !gd_bit(owned, y);
+  const int k0 = ya >> 5, k1 = (yb - 1) >> 5;
+  unsigned any = 0;
+  for (int k = k0; k <= k1; ++k) any |= gd_range_word(k, ya, yb) & ~owned[k * GD_SW];
   if (!any) return;
   GdPlaneSpan p;
   gd_plane_setup(sc, v, sector, isFloor, x, p);
-  for (int y = ya; y < yb; ++y) {
-    if (gd_bit(owned, y)) continue;
-    gd_set(owned, y);
-    if (!gd_bit(filled, y)) sh.frame[y * GD_SW + x] = gd_plane_pixel(p, v, sh.yslope, sh.colormap, y);
+  uint8_t *dst = sh.frame + x;
+  for (int k = k0; k <= k1; ++k) {
+    unsigned have = owned[k * GD_SW];
+    unsigned fresh = gd_range_word(k, ya, yb) & ~have;
+    if (!fresh) continue;
+    owned[k * GD_SW] = have | fresh;
+    unsigned m = fresh & ~filled[k * GD_SW];
+    const int y0 = k << 5;
+    while (m) {
+      int b0 = __ffs(m) - 1;
+      m &= m - 1;
+      int b1 = m ? __ffs(m) - 1 : b0;
+      m &= m - 1;
+      uint8_t p0 = gd_plane_pixel(p, v, sh.yslope, sh.colormap, y0 + b0);
+      uint8_t p1 = gd_plane_pixel(p, v, sh.yslope, sh.colormap, y0 + b1);
+      dst[(y0 + b0) * GD_SW] = p0;
+      dst[(y0 + b1) * GD_SW] = p1;
+    }
   }
 }
 
@@ -2091,12 +2126,16 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
       /* rows no seg ever claimed show the per-pixel flat fallback: queue them
        * (the hit cache is free once every column has finished its walk) */
       const unsigned *filled = sh.masks + tid, *owned = sh.masks + 7 * GD_SW + tid;
-      for (int y = 0; y < GD_VH; ++y)
-        if (!gd_bit(filled, y) && !gd_bit(owned, y)) {
+      for (int k = 0; k < 7; ++k) {
+        unsigned m = gd_range_word(k, 0, GD_VH) & ~filled[k * GD_SW] & ~owned[k * GD_SW];
+        while (m) {
+          int y = (k << 5) + __ffs(m) - 1;
+          m &= m - 1;
           sh.frame[y * GD_SW + tid] = 0;
           int slot = atomicAdd(&sh.misc[1], 1);
           if (slot < GD_FALLBACK_MAX) ((int *)sh.hitD)[slot] = (y << 16) | tid;
         }
+      }
     }
     __syncthreads();
     if (sh.misc[1] > 0) {
