@@ -1380,7 +1380,8 @@ __device__ int gd_sector_at(const GdScene &sc, float px, float py) {
 
 /* Flat-fallback resolution of a pixel (engine.py:10961-11026): true when the
  * column ray meets no sector's plane inside that sector's polygon. */
-__device__ __noinline__ bool gd_pixel_unresolved(const GdScene &sc, const GdView &v, int x, int y, float rc, float rs) {
+__device__ __noinline__ bool gd_pixel_unresolved(const GdScene &sc, const GdView &v, int x, int y, float rc, float rs,
+                                                 int hint) {
   i64 ti = gd_clamp((GD_ANG90 - v.pitchBam) >> 19, 0, 4095);
   i64 offFixed = ((i64)sc.fineTan[ti] * 12582912LL) >> 16;
   float center = 103.5f + (float)offFixed / 65536.0f;
@@ -1388,7 +1389,11 @@ __device__ __noinline__ bool gd_pixel_unresolved(const GdScene &sc, const GdView
   float delta = (float)y - center;
   bool floorPixel = delta > 0;
   float den = fmaxf(fabsf(delta), 0.5f);
-  for (int s = 0; s < sc.S; ++s) {
+  /* An existence test, so the order is free: `hint` (the sector whose plane
+   * was marked on this pixel) is nearly always the one that answers it. */
+  for (int k = -1; k < sc.S; ++k) {
+    int s = k < 0 ? hint : k;
+    if (k >= 0 && s == hint) continue;
     float ph = floorPixel ? (v.viewZ - sc.secF[s * 2]) : (sc.secF[s * 2 + 1] - v.viewZ);
     float perp = ph * 192.0f / den;
     float cd = perp / cc;
@@ -1780,7 +1785,7 @@ __device__ void gd_sprites(const GdScene &sc, const GdView &v, const GdShared &s
         visible = gd_behind(sc, sh.walls[bestW], bestW, ac);
       } else {
         float limit = GD_INF;
-        if (!filled && ownerSector >= 0 && gd_pixel_unresolved(sc, v, x, y, rayCos, raySin))
+        if (!filled && ownerSector >= 0 && gd_pixel_unresolved(sc, v, x, y, rayCos, raySin, ownerSector))
           limit = gd_plane_depth(sc, v, ownerSector, ownerFloor, y);
         visible = ac.depth < limit;
       }
@@ -1930,17 +1935,29 @@ __device__ void gd_resize(const uint8_t *frame, const unsigned long long *pal64,
   for (int o = threadIdx.x; o < GD_OBS * GD_OBS; o += GD_THREADS) {
     int oy = o / GD_OBS, ox = o - oy * GD_OBS;
     int ys = oy * 240, ye = ys + 240, xs = ox * 320, xe = xs + 320;
+    /* An output pixel overlaps at most 4 source rows and 5 source columns; taps
+     * past the overlap get weight zero, so the tap loops have fixed trip counts
+     * and their loads are independent. */
+    const int sy0 = ys / 84, sx0 = xs / 84;
+    unsigned wx[5];
+    int cx[5];
+#pragma unroll
+    for (int j = 0; j < 5; ++j) {
+      int sx = sx0 + j;
+      int xo = min(xe, (sx + 1) * 84) - max(xs, sx * 84);
+      wx[j] = xo > 0 ? (unsigned)xo / 4u : 0u;
+      cx[j] = min(sx, GD_SW - 1);
+    }
     unsigned long long acc = 0;
-    for (int sy = ys / 84; sy * 84 < ye; ++sy) {
-      if (sy >= srcRows) break;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      int sy = sy0 + i;
       int yo = min(ye, (sy + 1) * 84) - max(ys, sy * 84);
-      unsigned wy = (unsigned)yo / 12u;
-      const uint8_t *row = frame + sy * GD_SW;
+      unsigned wy = (yo > 0 && sy < srcRows) ? (unsigned)yo / 12u : 0u;
+      const uint8_t *row = frame + min(sy, GD_SCREEN_H - 1) * GD_SW;
       unsigned long long racc = 0;
-      for (int sx = xs / 84; sx * 84 < xe; ++sx) {
-        int xo = min(xe, (sx + 1) * 84) - max(xs, sx * 84);
-        racc += (unsigned long long)((unsigned)xo / 4u) * pal64[row[sx]];
-      }
+#pragma unroll
+      for (int j = 0; j < 5; ++j) racc += (unsigned long long)wx[j] * pal64[row[cx[j]]];
       acc += racc * wy;
     }
     unsigned r = (unsigned)(acc & 0xFFFFF), g = (unsigned)((acc >> 20) & 0xFFFFF), b = (unsigned)((acc >> 40) & 0xFFFFF);
