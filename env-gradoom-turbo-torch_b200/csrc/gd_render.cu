@@ -570,12 +570,42 @@ __device__ __noinline__ bool gd_sector_bridge(const GdScene &sc, int slot, int p
 }
 
 /* ---- phase: ray-owned spans (engine.py:11333-11438) --------------------- */
-__device__ void gd_wall_spans(const GdScene &sc, const GdView &v, GdWall *walls) {
+/* A wall whose two endpoints lie behind the viewer, or both beyond the same
+ * edge of the 90-degree frustum, is crossed by no column ray at a positive
+ * distance.  The two-unit margin is four orders of magnitude above the float
+ * error of these dot products at map scale, so the test only ever drops walls
+ * for which the exact sweep below finds no column. */
+__device__ __forceinline__ bool gd_wall_in_frustum(const float4 wl, const GdView &v) {
+  float ax = wl.x - v.x, ay = wl.y - v.y, bx = wl.z - v.x, by = wl.w - v.y;
+  float fa = ax * v.fcos + ay * v.fsin, fb = bx * v.fcos + by * v.fsin;      /* forward */
+  float sa = ax * v.fsin - ay * v.fcos, sb = bx * v.fsin - by * v.fcos;      /* to the right */
+  const float m = -2.0f;
+  if (fa < m && fb < m) return false;
+  if (fa + sa < m && fb + sb < m) return false;
+  if (fa - sa < m && fb - sb < m) return false;
+  return true;
+}
+
+__device__ void gd_wall_spans(const GdScene &sc, const GdView &v, const GdShared &sh) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  GdWall *walls = sh.walls;
+  short *list = (short *)sh.hitD;           /* walls that need the sweep */
+  if (threadIdx.x == 0) sh.misc[2] = 0;
+  __syncthreads();
+  for (int w = threadIdx.x; w < sc.W; w += GD_THREADS) {
+    const float4 wl = *reinterpret_cast<const float4 *>(&sc.walls[w * 4]);
+    walls[w].isl = -1;
+    walls[w].isr = -1;
+    if (gd_wall_in_frustum(wl, v)) list[atomicAdd(&sh.misc[2], 1)] = (short)w;
+  }
+  __syncthreads();
+  const int n = sh.misc[2];
   float rxs[GD_SW / 32], rys[GD_SW / 32];
 #pragma unroll
   for (int chunk = 0; chunk < GD_SW / 32; ++chunk) gd_ray(v, chunk * 32 + lane, rxs[chunk], rys[chunk]);
-  for (int w = warp; w < sc.W; w += GD_WARPS) {
+  /* first and last column whose ray crosses the wall, kept in isl / isr */
+  for (int i = warp; i < n; i += GD_WARPS) {
+    const int w = list[i];
     const float4 wl = *reinterpret_cast<const float4 *>(&sc.walls[w * 4]);
     int first = -1, last = -1;
 #pragma unroll
@@ -586,40 +616,43 @@ __device__ void gd_wall_spans(const GdScene &sc, const GdView &v, GdWall *walls)
         last = chunk * 32 + 31 - __clz(m);
       }
     }
-    if (lane == 0) {
-      GdWall &wv = walls[w];
-      bool hasColumns = first >= 0;
-      i64 isl = hasColumns ? first : 0;
-      i64 isr = hasColumns ? last + 1 : GD_SW;
-      const i64 cf = 160 * GD_FU;
-      i64 ecol[2];
-      bool evis[2];
+    if (lane == 0) { walls[w].isl = (short)first; walls[w].isr = (short)last; }
+  }
+  __syncthreads();
+  for (int w = threadIdx.x; w < sc.W; w += GD_THREADS) {
+    GdWall &wv = walls[w];
+    const int first = wv.isl, last = wv.isr;
+    bool hasColumns = first >= 0;
+    i64 isl = hasColumns ? first : 0;
+    i64 isr = hasColumns ? last + 1 : GD_SW;
+    const i64 cf = 160 * GD_FU;
+    i64 ecol[2];
+    bool evis[2];
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        i64 ty = wv.ty[e], tx = wv.tx[e];
-        i64 sty = ty == 0 ? 1 : ty;
-        i64 pf = cf + gd_div(tx * cf, sty);
-        ecol[e] = (pf >> 16) + (tx >= 0);
-        evis[e] = ty > 0 && tx >= -ty && tx <= ty && ecol[e] >= 0 && ecol[e] <= GD_SW;
-      }
-      bool fff = wv.frontF;
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        bool visible = evis[e] && hasColumns;
-        bool ownsLeft = fff ? (e == 0) : (e == 1);
-        if (visible && ownsLeft) isl = ecol[e];
-        if (visible && !ownsLeft) isr = ecol[e];
-      }
-      if (evis[0] && evis[1]) {
-        isl = ecol[fff ? 0 : 1];
-        isr = ecol[fff ? 1 : 0];
-        hasColumns = isr > isl;
-      }
-      hasColumns = hasColumns && (wv.sr > wv.sl);
-      wv.isl = (short)isl;
-      wv.isr = (short)isr;
-      wv.hasColumns = hasColumns;
+    for (int e = 0; e < 2; ++e) {
+      i64 ty = wv.ty[e], tx = wv.tx[e];
+      i64 sty = ty == 0 ? 1 : ty;
+      i64 pf = cf + gd_div(tx * cf, sty);
+      ecol[e] = (pf >> 16) + (tx >= 0);
+      evis[e] = ty > 0 && tx >= -ty && tx <= ty && ecol[e] >= 0 && ecol[e] <= GD_SW;
     }
+    bool fff = wv.frontF;
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      bool visible = evis[e] && hasColumns;
+      bool ownsLeft = fff ? (e == 0) : (e == 1);
+      if (visible && ownsLeft) isl = ecol[e];
+      if (visible && !ownsLeft) isr = ecol[e];
+    }
+    if (evis[0] && evis[1]) {
+      isl = ecol[fff ? 0 : 1];
+      isr = ecol[fff ? 1 : 0];
+      hasColumns = isr > isl;
+    }
+    hasColumns = hasColumns && (wv.sr > wv.sl);
+    wv.isl = (short)isl;
+    wv.isr = (short)isr;
+    wv.hasColumns = hasColumns;
   }
 }
 
@@ -2110,7 +2143,7 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
     if (tid == GD_THREADS - 1) sh.misc[0] = gd_sector_at(sc, v.x, v.y);
     __syncthreads();
     GD_BEAT(2);
-    gd_wall_spans(sc, v, sh.walls);
+    gd_wall_spans(sc, v, sh);
     for (int idx = tid; idx < sc.W * 4; idx += GD_THREADS) {
       int w = idx >> 2, slot = idx & 3;
       int sector = sc.wsec[w * 2 + (slot >> 1)];
