@@ -1405,12 +1405,6 @@ __device__ __forceinline__ bool gd_point_in_sector(const GdScene &sc, int s, flo
   return crossings & 1;
 }
 
-__device__ int gd_sector_at(const GdScene &sc, float px, float py) {
-  for (int s = 0; s < sc.S; ++s)
-    if (gd_point_in_sector(sc, s, px, py)) return s;
-  return 0;
-}
-
 /* Flat-fallback resolution of a pixel (engine.py:10961-11026): true when the
  * column ray meets no sector's plane inside that sector's polygon. */
 __device__ __noinline__ bool gd_pixel_unresolved(const GdScene &sc, const GdView &v, int x, int y, float rc, float rs,
@@ -1693,7 +1687,8 @@ __device__ void gd_fallback_pass(const GdScene &sc, const GdView &v, const GdSha
 }
 
 /* ---- phase: sprites (engine.py:14138-14228, 14684-14947) ----------------- */
-__device__ __noinline__ void gd_actor_setup(const GdScene &sc, const GdView &v, const gd_thing &t, GdActor &ac) {
+__device__ __noinline__ void gd_actor_setup(const GdScene &sc, const GdView &v, const gd_thing &t, int sector,
+                                            GdActor &ac) {
   ac.alive = (t.flags & GD_THING_ALIVE) != 0;
   ac.style = t.style;
   ac.x = t.x; ac.y = t.y;
@@ -1723,7 +1718,7 @@ __device__ __noinline__ void gd_actor_setup(const GdScene &sc, const GdView &v, 
   ac.texMid = (i64)si.w * GD_FU - gd_rint((v.viewZ - t.z) * 65536.0f);
   ac.topFixed = v.center - (gd_wmul(ac.texMid, ac.yscale) >> 16);
   ac.iscale = gd_div(GD_U32MASK, gd_max(ac.yscale, 1));
-  i64 light = sc.secI[gd_sector_at(sc, t.x, t.y) * 4] + v.flashLight * 16;
+  i64 light = sc.secI[sector * 4] + v.flashLight * 16;
   if (t.flags & GD_THING_BRIGHT) light = 255;
   float base = 61.0f - (float)light / 4.0f;
   float visf = fminf(1280.0f / fmaxf(ac.depth, 1.0f), 24.0f);
@@ -2118,8 +2113,35 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
     if (tid < GD_LANE_WORDS) sh.lane[tid] = p.lanes[(size_t)l * GD_LANE_WORDS + tid];
     if (tid < 10) sh.ownerMask[tid] = 0;
     if (tid == 0) sh.misc[1] = 0;
+    /* sector of every thing and of the player (slot 64): lowest index that
+     * contains the point (engine.py:9598-9617), found by all threads together
+     * while thread 0 sets up the view */
+    int *pointSector = (int *)sh.hitA;
+    if (tid <= 64) pointSector[tid] = 0x7fffffff;
     __syncthreads();
-    if (tid == 0) gd_view_setup(sc, sh.lane, sView);
+    int nThings = sh.lane[GD_L_THINGS];
+    if (nThings > p.maxThings || nThings > 64) {
+      if (tid == 0) atomicOr(p.status, GD_STATUS_THINGS_OVERFLOW);
+      nThings = min(p.maxThings, 64);
+    }
+    if (nThings < 0) nThings = 0;
+    if (tid == 0) {
+      gd_view_setup(sc, sh.lane, sView);
+    } else if (tid >= 32) {
+      const int pairs = (nThings + 1) * sc.S;
+      for (int i = tid - 32; i < pairs; i += GD_THREADS - 32) {
+        int t = i / sc.S, s = i - t * sc.S;
+        float px, py;
+        if (t < nThings) {
+          const gd_thing &th = p.things[(size_t)l * p.maxThings + t];
+          px = th.x; py = th.y;
+        } else {
+          px = __int_as_float(sh.lane[GD_L_X]); py = __int_as_float(sh.lane[GD_L_Y]);
+          t = 64;
+        }
+        if (gd_point_in_sector(sc, s, px, py)) atomicMin(&pointSector[t], s);
+      }
+    }
     __syncthreads();
     const GdView &v = sView;
     if (tid < GD_VH) {
@@ -2132,22 +2154,20 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
       sh.yslope[tid] = (unsigned)ys;
     }
     for (int w = tid; w < sc.W; w += GD_THREADS) gd_project_wall(sc, v, w, sh.walls[w]);
-    int nThings = sh.lane[GD_L_THINGS];
-    if (nThings > p.maxThings || nThings > 64) {
-      if (tid == 0) atomicOr(p.status, GD_STATUS_THINGS_OVERFLOW);
-      nThings = min(p.maxThings, 64);
+    for (int a = tid; a < nThings; a += GD_THREADS) {
+      int sector = pointSector[a] == 0x7fffffff ? 0 : pointSector[a];
+      gd_actor_setup(sc, v, p.things[(size_t)l * p.maxThings + a], sector, sh.actors[a]);
     }
-    if (nThings < 0) nThings = 0;
-    for (int a = tid; a < nThings; a += GD_THREADS)
-      gd_actor_setup(sc, v, p.things[(size_t)l * p.maxThings + a], sh.actors[a]);
-    if (tid == GD_THREADS - 1) sh.misc[0] = gd_sector_at(sc, v.x, v.y);
+    if (tid == GD_THREADS - 1) sh.misc[0] = pointSector[64] == 0x7fffffff ? 0 : pointSector[64];
     __syncthreads();
     GD_BEAT(2);
     gd_wall_spans(sc, v, sh);
-    for (int idx = tid; idx < sc.W * 4; idx += GD_THREADS) {
-      int w = idx >> 2, slot = idx & 3;
+    /* row projection tables, for the walls that passed the frustum test (the
+     * walk selects no other wall) */
+    for (int idx = tid; idx < sh.misc[2] * 4; idx += GD_THREADS) {
+      int w = ((const short *)sh.hitD)[idx >> 2], slot = idx & 3;
       int sector = sc.wsec[w * 2 + (slot >> 1)];
-      if (sector >= 0) gd_rowproj_setup(v, sh.walls[w], sc.secF[sector * 2 + (slot & 1)], rowproj[idx]);
+      if (sector >= 0) gd_rowproj_setup(v, sh.walls[w], sc.secF[sector * 2 + (slot & 1)], rowproj[w * 4 + slot]);
     }
     __syncthreads();
     GD_BEAT(3);
