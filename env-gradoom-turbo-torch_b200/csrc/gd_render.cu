@@ -1733,98 +1733,120 @@ __device__ __forceinline__ bool gd_behind(const GdScene &sc, const GdWall &wv, i
   return (nearD > ac.depthFixed) || ((farD > ac.depthFixed) && (side <= 0));
 }
 
+/* Sprites cluster in a few screen columns, so the drawing is spread by rows:
+ * every column thread first lists its visible candidates; then the warps take
+ * the listed columns from a counter and draw each candidate's rows 32 at a
+ * time, far to near. */
 __device__ void gd_sprites(const GdScene &sc, const GdView &v, const GdShared &sh, const GdEvent *events,
                            const int *eventCount, int nThings) {
-  const int x = threadIdx.x;
-  if (nThings <= 0) return;
-  unsigned long long cand = 0;
+  const int x0 = threadIdx.x, lane = threadIdx.x & 31;
+  if (nThings <= 0) return;                          /* block-uniform */
+  unsigned long long *candOf = (unsigned long long *)sh.hitD;       /* per column */
+  short *list = (short *)sh.hitA;
+  int *counters = &sh.misc[2];                       /* [0] listed columns, [1] next to draw */
+  if (x0 == 0) { counters[0] = 0; counters[1] = 0; }
+  __syncthreads();
   {
-    int bw = sh.blockingWall[x];
+    unsigned long long cand = 0;
+    int bw = sh.blockingWall[x0];
     const GdWall &bwv = sh.walls[bw];
-    bool bowns = x >= bwv.sl && x < bwv.sr;
-    float wd = sh.wallDistance[x];
+    bool bowns = x0 >= bwv.sl && x0 < bwv.sr;
+    float wd = sh.wallDistance[x0];
     for (int a = 0; a < nThings; ++a) {
       const GdActor &ac = sh.actors[a];
-      if (!(ac.alive && x >= ac.left && x < ac.right && ac.depth > 0)) continue;
+      if (!(ac.alive && x0 >= ac.left && x0 < ac.right && ac.depth > 0)) continue;
       bool rayVisible = ac.depth < wd;
       rayVisible = rayVisible || !bowns || gd_behind(sc, bwv, bw, ac);
       if (rayVisible) cand |= 1ull << a;
     }
+    candOf[x0] = cand;
+    if (cand) list[atomicAdd(&counters[0], 1)] = (short)x0;
   }
-  if (!cand) return;
-  const int nEv = eventCount[x];
-  const float rayAngle = v.angle + sc.rayOffsets[x];
-  const float rayCos = cosf(rayAngle), raySin = sinf(rayAngle);
-  /* far to near: repeatedly take the remaining candidate with the largest
-   * (depth, index) key */
-  while (cand) {
-    int pick = -1;
-    float pd = 0.0f;
-    unsigned long long m = cand;
-    while (m) {
-      int a = __ffsll((long long)m) - 1;
-      m &= m - 1;
-      float d = sh.actors[a].depth;
-      if (pick < 0 || d >= pd) { pick = a; pd = d; }
-    }
-    cand &= ~(1ull << pick);
-    const GdActor &ac = sh.actors[pick];
-    i64 u = (((i64)x - ac.left) * ac.xstep) >> 16;
-    if (u < 0 || u >= ac.w) continue;
-    const uint8_t *cm = sh.colormap + ac.shade * 256;
-    i64 fracBase = ac.texMid - (gd_wmul(v.center - GD_FU, ac.iscale) >> 16);
-    /* rows whose source row lies inside the patch */
-    int y0 = 0, y1 = GD_VH;
-    if (ac.iscale > 0) {
-      /* frac(y) >> 16 in [0,h)  <=>  0 <= fracBase + y*iscale < h*FU */
-      i64 lo = -fracBase, hi = (i64)ac.h * GD_FU - fracBase;
-      i64 ya = lo <= 0 ? 0 : gd_div(lo + ac.iscale - 1, ac.iscale);
-      i64 yb = hi <= 0 ? 0 : gd_div(hi + ac.iscale - 1, ac.iscale);
-      y0 = (int)gd_clamp(ya, 0, GD_VH);
-      y1 = (int)gd_clamp(yb, 0, GD_VH);
-    }
-    for (int y = y0; y < y1; ++y) {
-      i64 frac = fracBase + (i64)y * ac.iscale;
-      i64 tv = frac >> 16;
-      if (tv < 0 || tv >= ac.h) continue;
-      size_t si = ((size_t)ac.sprite * sc.sprH + (size_t)tv) * sc.sprW + (size_t)u;
-      uint8_t post = sc.sprPost[si];
-      if (post == 255) continue;
-      i64 postTop = (ac.topFixed + ac.yscale * (i64)post) >> 16;
-      if (y < postTop) continue;
-      /* nearest clip event covering this pixel */
-      float bestD = GD_INF;
-      int bestW = -1, ownerSector = -1;
-      bool filled = false, ownerFloor = false;
-      for (int e = 0; e < nEv; ++e) {
-        const GdEvent ev = events[e * GD_SW + x];
-        bool inLower = y >= ev.t1a && y < ev.t1b, inUpper = y >= ev.t0a && y < ev.t0b;
-        bool drawn = inLower ? ((ev.pad0 & 2) != 0) : (inUpper ? ((ev.pad0 & 1) != 0) : false);
-        bool covers = (y < ev.silTop) || (y >= ev.silBot);
-        if (drawn && !filled) { filled = true; covers = true; }
-        if (covers && ev.dist < bestD) { bestD = ev.dist; bestW = ev.wall; }
-        if (ownerSector < 0 && ev.sector >= 0) {
-          if (y >= ev.floorA && y < ev.floorB) { ownerSector = ev.sector; ownerFloor = true; }
-          else if (y >= ev.ceilA && y < ev.ceilB) ownerSector = ev.sector;
+  __syncthreads();
+  const int listed = counters[0];
+  for (;;) {
+    int slot = 0;
+    if (lane == 0) slot = atomicAdd(&counters[1], 1);
+    slot = __shfl_sync(0xffffffffu, slot, 0);
+    if (slot >= listed) break;
+    const int x = list[slot];
+    unsigned long long cand = candOf[x];
+    const int nEv = eventCount[x];
+    const float rayAngle = v.angle + sc.rayOffsets[x];
+    const float rayCos = cosf(rayAngle), raySin = sinf(rayAngle);
+    /* far to near: repeatedly take the remaining candidate with the largest
+     * (depth, index) key */
+    while (cand) {
+      int pick = -1;
+      float pd = 0.0f;
+      unsigned long long m = cand;
+      while (m) {
+        int a = __ffsll((long long)m) - 1;
+        m &= m - 1;
+        float d = sh.actors[a].depth;
+        if (pick < 0 || d >= pd) { pick = a; pd = d; }
+      }
+      cand &= ~(1ull << pick);
+      const GdActor &ac = sh.actors[pick];
+      i64 u = (((i64)x - ac.left) * ac.xstep) >> 16;
+      if (u < 0 || u >= ac.w) continue;
+      const uint8_t *cm = sh.colormap + ac.shade * 256;
+      i64 fracBase = ac.texMid - (gd_wmul(v.center - GD_FU, ac.iscale) >> 16);
+      /* rows whose source row lies inside the patch */
+      int y0 = 0, y1 = GD_VH;
+      if (ac.iscale > 0) {
+        /* frac(y) >> 16 in [0,h)  <=>  0 <= fracBase + y*iscale < h*FU */
+        i64 lo = -fracBase, hi = (i64)ac.h * GD_FU - fracBase;
+        i64 ya = lo <= 0 ? 0 : gd_div(lo + ac.iscale - 1, ac.iscale);
+        i64 yb = hi <= 0 ? 0 : gd_div(hi + ac.iscale - 1, ac.iscale);
+        y0 = (int)gd_clamp(ya, 0, GD_VH);
+        y1 = (int)gd_clamp(yb, 0, GD_VH);
+      }
+      __syncwarp();                                  /* the farther sprite's pixels are in place */
+      for (int y = y0 + lane; y < y1; y += 32) {
+        i64 frac = fracBase + (i64)y * ac.iscale;
+        i64 tv = frac >> 16;
+        if (tv < 0 || tv >= ac.h) continue;
+        size_t si = ((size_t)ac.sprite * sc.sprH + (size_t)tv) * sc.sprW + (size_t)u;
+        uint8_t post = sc.sprPost[si];
+        if (post == 255) continue;
+        i64 postTop = (ac.topFixed + ac.yscale * (i64)post) >> 16;
+        if (y < postTop) continue;
+        /* nearest clip event covering this pixel */
+        float bestD = GD_INF;
+        int bestW = -1, ownerSector = -1;
+        bool filled = false, ownerFloor = false;
+        for (int e = 0; e < nEv; ++e) {
+          const GdEvent ev = events[e * GD_SW + x];
+          bool inLower = y >= ev.t1a && y < ev.t1b, inUpper = y >= ev.t0a && y < ev.t0b;
+          bool drawn = inLower ? ((ev.pad0 & 2) != 0) : (inUpper ? ((ev.pad0 & 1) != 0) : false);
+          bool covers = (y < ev.silTop) || (y >= ev.silBot);
+          if (drawn && !filled) { filled = true; covers = true; }
+          if (covers && ev.dist < bestD) { bestD = ev.dist; bestW = ev.wall; }
+          if (ownerSector < 0 && ev.sector >= 0) {
+            if (y >= ev.floorA && y < ev.floorB) { ownerSector = ev.sector; ownerFloor = true; }
+            else if (y >= ev.ceilA && y < ev.ceilB) ownerSector = ev.sector;
+          }
         }
+        bool visible;
+        if (bestW >= 0) {
+          visible = gd_behind(sc, sh.walls[bestW], bestW, ac);
+        } else {
+          float limit = GD_INF;
+          if (!filled && ownerSector >= 0 && gd_pixel_unresolved(sc, v, x, y, rayCos, raySin, ownerSector))
+            limit = gd_plane_depth(sc, v, ownerSector, ownerFloor, y);
+          visible = ac.depth < limit;
+        }
+        if (!visible) continue;
+        uint8_t lit = cm[sc.sprAtlas[si]];
+        uint8_t dst = sh.frame[y * GD_SW + x];
+        uint8_t out = lit;
+        if (ac.style == -2) out = sc.transLut[dst * 256 + lit];
+        else if (ac.style >= 0) out = sc.addLut[((ac.style > 1 ? 1 : ac.style) * 256 + dst) * 256 + lit];
+        sh.frame[y * GD_SW + x] = out;
       }
-      bool visible;
-      if (bestW >= 0) {
-        visible = gd_behind(sc, sh.walls[bestW], bestW, ac);
-      } else {
-        float limit = GD_INF;
-        if (!filled && ownerSector >= 0 && gd_pixel_unresolved(sc, v, x, y, rayCos, raySin, ownerSector))
-          limit = gd_plane_depth(sc, v, ownerSector, ownerFloor, y);
-        visible = ac.depth < limit;
-      }
-      if (!visible) continue;
-      uint8_t lit = cm[sc.sprAtlas[si]];
-      uint8_t dst = sh.frame[y * GD_SW + x];
-      uint8_t out = lit;
-      if (ac.style == -2) out = sc.transLut[dst * 256 + lit];
-      else if (ac.style >= 0) out = sc.addLut[((ac.style > 1 ? 1 : ac.style) * 256 + dst) * 256 + lit];
-      sh.frame[y * GD_SW + x] = out;
     }
+    __syncwarp();
   }
 }
 
