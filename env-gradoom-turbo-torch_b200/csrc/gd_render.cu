@@ -768,6 +768,13 @@ struct GdIter {
   bool psFromFront;
 };
 
+#ifdef GD_PROFILE_PHASES
+__device__ unsigned long long *gdProfile;   /* decide-phase cycle counters */
+#define GD_TD(m) do { if ((x & 31) == 0) { long long t = clock64(); atomicAdd(gdProfile + 32 + (m), (unsigned long long)(t - gdD0)); gdD0 = t; } } while (0)
+#else
+#define GD_TD(m) do {} while (0)
+#endif
+
 __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWall *walls, const unsigned *ownerMask,
                                  const GdRowProj *rowproj, float *hitD, float *hitA, uint8_t *hitF, int x, float rx,
                                  float ry, const GdColState &c, GdIter &it) {
@@ -775,6 +782,9 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
   const int current = curSector < 0 ? 0 : curSector;
   const float prev = c.prev;
   const int i0 = sc.secOff[current], i1 = sc.secOff[current + 1];
+#ifdef GD_PROFILE_PHASES
+  long long gdD0 = clock64();
+#endif
   /* every rule below looks at the walls of the current sector: test each once
    * and keep the results in this column's slice of shared memory */
   constexpr int kCache = 8;
@@ -800,6 +810,7 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
   };
 #define HIT(w) cachedHit(w)
 #define HITK(k) (((k) - i0) < nCache ? loadHit((k) - i0) : gd_hit(sc, v, walls, sc.secWalls[k], x, rx, ry))
+  GD_TD(0);
   float distance = GD_INF;
   int wallIndex = 0;
   if (curSector >= 0) {
@@ -819,6 +830,7 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
     }
     if (isfinite(sd)) { distance = sd; wallIndex = sw; }
   }
+  GD_TD(1);
   GdHit hSel = HIT(wallIndex);
   const float *selWall = &sc.walls[wallIndex * 4];
   bool selUsesStart = hSel.along <= 0.5f;
@@ -863,6 +875,7 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
       if (sbd < psd) { psd = sbd; psi = sbi; }
     }
   }
+  GD_TD(2);
   bool hasProjectedSolidOwner = isfinite(psd);
   if (hasProjectedSolidOwner) { distance = psd; wallIndex = psi; }
   GdHit hW = (wallIndex == psPathIndex) ? hSel : HIT(wallIndex);
@@ -872,6 +885,7 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
   bool eoPathIsGeo = hW.geo;
   bool replaceEo = (seo != wallIndex) && (sed > prev + 1e-3f);
   if (replaceEo) { distance = sed; wallIndex = seo; hW = HIT(wallIndex); }
+  GD_TD(3);
   int nopIndex = wallIndex;
   float nopDist = distance;
   bool nopIsGeo = replaceEo ? eoPathIsGeo : hW.geo;
@@ -920,6 +934,7 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
       if (psb && hb.d < npd) { usePsb = true; npd = hb.d; npi = psbIndex; }
     }
   }
+  GD_TD(4);
   bool replaceNp = isfinite(npd);
   if (replaceNp) { distance = npd; wallIndex = npi; hW = HIT(wallIndex); }
   bool finalIsProjected = hW.proj, finalIsGeo = hW.geo;
@@ -950,12 +965,16 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
   float otherFloor = gd_sec_floor(sc, safeOther), otherCeil = gd_sec_ceil(sc, safeOther);
   bool oneSided = otherSector < 0;
   const int32_t *stex = &sc.sideTex[(wallIndex * 2 + side) * 3];
+  GD_TD(5);
   /* Row bounds: per (wall, sector height) tables built once per lane cover the
    * usual case of heights taken from the wall's own two sectors. */
   const GdRowProj *rp = rowproj + wallIndex * 4;
   int slotCur = (renderCurrent == front) ? 0 : ((renderCurrent == back && back >= 0) ? 2 : -1);
-  int oneTop, oneBottom;
-  if (slotCur >= 0) {
+  int oneTop = 0, oneBottom = 0;
+  /* the row bounds feed tiers, marks, clips and events, all of which need a
+   * raster-valid crossing */
+  if (!rasterValid) {
+  } else if (slotCur >= 0) {
     oneBottom = gd_rowproj_eval(v, wv, rp[slotCur], x);
     oneTop = gd_rowproj_eval(v, wv, rp[slotCur + 1], x);
   } else {
@@ -963,7 +982,7 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
     oneBottom = gd_project_rows(v, wv, viewFloor, x);
   }
   int lowerTop = 0, upperBottom = 0;
-  if (!oneSided) {  /* the tiers and clips below use them only for two-sided lines */
+  if (!oneSided && rasterValid) {  /* the tiers and clips below use them only for two-sided lines */
     int slotOther = (renderOther >= 0 && renderOther == back) ? 2 : ((renderOther >= 0 && renderOther == front) ? 0 : -1);
     if (slotOther >= 0) {
       lowerTop = gd_rowproj_eval(v, wv, rp[slotOther], x);
@@ -990,6 +1009,7 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
   it.tier[1] = !oneSided && rasterValid && (viewFloor < otherFloor) && stex[1] >= 0 && clowtop < cbot;
   it.tier[2] = !oneSided && rasterValid && (viewCeil > otherCeil) && stex[2] >= 0 && ctop < cupbot;
 
+  GD_TD(6);
   /* traversal decisions (engine.py:13070-13241) */
   bool endpointOnly = valid && !oneSided && !geometric;
   float cnd = GD_INF, ond = GD_INF, csd = GD_INF, osd = GD_INF, gpd = GD_INF;
@@ -1052,6 +1072,7 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
     it.epEpY = us ? fw[1] : fw[3];
   }
   it.epFwdIdx = epFwdIdx; it.ppbIdx = ppbIdx; it.psPathIndex = psPathIndex; it.psFromFront = psFromFront;
+  GD_TD(7);
 #undef HIT
 #undef HITK
 #undef SHARES_SEL
@@ -2108,6 +2129,7 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
   GdRowProj *rowproj = stagedRowproj ? stagedRowproj : (GdRowProj *)(myScratch + GD_SCRATCH_FIXED);
 
 #ifdef GD_PROFILE_PHASES
+  if (tid == 0 && blockIdx.x == 0) gdProfile = (unsigned long long *)(p.status + 8);
   long long gdT0 = clock64();
   const long long gdStartClock = gdT0;
   unsigned long long gdStartNs;
