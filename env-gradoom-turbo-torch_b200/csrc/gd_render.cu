@@ -304,6 +304,11 @@ __device__ __forceinline__ GdHit gd_hit(const GdScene &sc, const GdView &v, cons
   return h;
 }
 
+__device__ __noinline__ GdHit gd_hit_slow(const GdScene &sc, const GdView &v, const GdWall *walls, int w, int x,
+                                          float rx, float ry) {
+  return gd_hit(sc, v, walls, w, x, rx, ry);
+}
+
 __device__ __forceinline__ float gd_tol(float d) { return fmaxf(fabsf(d) / 128.0f, 4.0f); }
 
 /* Endpoint owner of wall w at column x (engine.py:11589-11730). */
@@ -803,14 +808,14 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
     h.geo = f & 1; h.proj = (f & 2) != 0; h.left = (f & 4) != 0;
     return h;
   };
+  /* one out-of-line copy of the uncached test serves every rule below */
   auto cachedHit = [&](int w) -> GdHit {
     for (int k = 0; k < nCache; ++k)
       if (sc.secWalls[i0 + k] == w) return loadHit(k);
-    return gd_hit(sc, v, walls, w, x, rx, ry);
+    return gd_hit_slow(sc, v, walls, w, x, rx, ry);
   };
 #define HIT(w) cachedHit(w)
-#define HITK(k) (((k) - i0) < nCache ? loadHit((k) - i0) : gd_hit(sc, v, walls, sc.secWalls[k], x, rx, ry))
-  GD_TD(0);
+#define HITK(k) (((k) - i0) < nCache ? loadHit((k) - i0) : gd_hit_slow(sc, v, walls, sc.secWalls[k], x, rx, ry))
   float distance = GD_INF;
   int wallIndex = 0;
   if (curSector >= 0) {
