@@ -37,6 +37,14 @@ METRIC = "rendered env-frames/sec at 4096 lanes/GPU"
 UNIT = "frames/s"
 # algorithmic HBM bytes per env-frame: newest 84x84 slot + 64 B lane scalars + 16 B per thing
 BYTES_PER_FRAME = 84 * 84 + 64 + 16 * THINGS
+# The headline workload is c2.  --workload selects the other GPU configurations of the benchmark
+# definition: c3 also streams the 320x240 RGB24 frame of every lane every step, c4 is the 256-sector
+# map with diagonal lines at 8192 lanes and 32 things per lane.
+WORKLOADS = {
+    "c2": {"lanes": 4096, "things": 12, "rgb": False, "map": "64-sector 8x8 map"},
+    "c3": {"lanes": 1024, "things": 12, "rgb": True, "map": "32-sector 4x8 map"},
+    "c4": {"lanes": 8192, "things": 32, "rgb": False, "map": "256-sector 16x16 map with diagonals"},
+}
 # dram__bytes_read.sum + dram__bytes_write.sum of one render launch at 4096 lanes (a one-pass ncu
 # capture of this file's default command), per lane; mostly the oldest-first roll of the frame stack
 DRAM_TRAFFIC_PER_LANE = 168.3e6 / 4096
@@ -137,7 +145,9 @@ def run_reference(args):
     from gradoom_b200 import scene as gdscene, stepper
 
     oracle = entry.load_oracle()
-    sc = gdscene.make_grid_scene(gdscene.GRID_CONFIGS[WORKLOAD])
+    workload = args.workload
+    THINGS = WORKLOADS[workload]["things"]
+    sc = gdscene.make_grid_scene(gdscene.GRID_CONFIGS[workload])
     blob = gdscene.pack_scene(sc)
     cores = len(os.sched_getaffinity(0))
     sample = 64 * cores
@@ -155,13 +165,15 @@ def run_reference(args):
     total = sum(times)
     value = sample * len(times) / total
     line = {
-        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "impl": "reference", "metric": METRIC if workload == WORKLOAD else
+        f"rendered env-frames/sec at {WORKLOADS[workload]['lanes']} lanes/GPU ({workload})", "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * total / len(times),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "i64+f32", "data": "synthetic",
-        "config": {"workload": f"{WORKLOAD}: {sample} of {LANES_PER_GPU} lanes, 64-sector map, {THINGS} things/lane",
+        "config": {"workload": f"{workload}: {sample} of {WORKLOADS[workload]['lanes']} lanes, "
+                               f"{WORKLOADS[workload]['map']}, {THINGS} things/lane",
                    "l2": "n/a (CPU)"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": f"{sample} lanes per step x {len(times)} steps of the {WORKLOAD} workload"},
+                         "sample": f"{sample} lanes per step x {len(times)} steps of the {workload} workload"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -185,12 +197,23 @@ def run_ours(args):
     if args.gpus != world and rank == 0 and world > 1:
         raise SystemExit(f"--gpus {args.gpus} does not match WORLD_SIZE {world}")
 
-    sc = gdscene.make_grid_scene(gdscene.GRID_CONFIGS[WORKLOAD])
+    workload = args.workload
+    spec = WORKLOADS[workload]
+    THINGS = spec["things"]
+    sc = gdscene.make_grid_scene(gdscene.GRID_CONFIGS[workload])
     blob = gdscene.pack_scene(sc)
-    n = args.lanes
+    n = args.lanes if args.lanes else spec["lanes"]
     producer = stepper.LaneStepper(sc, n, device=device, k_things=THINGS, max_things=THINGS, seed=1000 + rank)
     renderer = native.Renderer(blob, device, THINGS)
     stack = torch.zeros((n, 4, 84, 84), dtype=torch.uint8, device=device)
+    rgb = torch.empty((n, 240, 320, 3), dtype=torch.uint8, device=device) if spec["rgb"] else None
+
+    def render_step():
+        if rgb is None:
+            renderer.step(lanes, things, stack)
+        else:
+            renderer.step_frames(lanes, things, stack, rgb=rgb)
+
     everyone = torch.ones(n, dtype=torch.bool, device=device)
     lane_ids = torch.arange(n, device=device, dtype=torch.int64) + rank * n
     producer.reset(everyone, lane_ids + 1)
@@ -217,7 +240,7 @@ def run_ours(args):
 
     for _ in range(args.warmup):
         advance()
-        renderer.step(lanes, things, stack)
+        render_step()
     barrier()
 
     sampler = ClockSampler(local_rank)
@@ -233,7 +256,7 @@ def run_ours(args):
         advance()
         flush.fill_(k & 0xFF)                 # evict the previous step's stack and records from L2
         starts[k].record()
-        renderer.step(lanes, things, stack)
+        render_step()
         ends[k].record()
         if (k + 1) % 100 == 0:
             gathered = stats.gather_lane_stats(producer.signal_buffer)
@@ -282,25 +305,29 @@ def run_ours(args):
         oracle = entry.load_oracle()
         peak, peak_kind = measured_peaks()
         avg_ms = statistics.mean(kernel_ms)
-        achieved = BYTES_PER_FRAME * n / (avg_ms / 1000.0) / 1e9
+        bytes_per_frame = 84 * 84 + 64 + 16 * THINGS + (240 * 320 * 3 if rgb is not None else 0)
+        achieved = bytes_per_frame * n / (avg_ms / 1000.0) / 1e9
         cpu_lanes, cpu_things = stepper.random_lanes(sc, 2048, THINGS, seed=11)
         cpu_value, cpu_done, cpu_dt = cpu_baseline(blob, cpu_lanes, cpu_things, oracle,
                                                    seconds=0.5 if args.skip_cpu else 12.0, threads=1)
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "metric": METRIC if (workload, n) == (WORKLOAD, LANES_PER_GPU) else
+            f"rendered env-frames/sec at {n} lanes/GPU ({workload})",
+            "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "i64+f32", "data": "synthetic",
-            "config": {"workload": f"{WORKLOAD}: {n} lanes/GPU, 64-sector 8x8 map, {THINGS} things/lane, obs only",
+            "config": {"workload": f"{workload}: {n} lanes/GPU, {spec['map']}, {THINGS} things/lane, "
+                                   + ("obs and RGB24 frame every step" if rgb is not None else "obs only"),
                        "lanes_per_gpu": n, "l2": "flushed with a 256 MiB write between timed steps",
                        "ctas": renderer.ctas, "shared_bytes_per_cta": renderer.shared_bytes,
                        "stack_policy": "roll (read 3 + write 4 slots per lane)"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": DRAM_TRAFFIC_PER_LANE * n if n == 4096 else None,
+                         "traffic": DRAM_TRAFFIC_PER_LANE * n if (workload, n) == (WORKLOAD, 4096) else None,
                          "traffic_source": "ncu capture of this command at 4096 lanes/GPU", "peak_source": peak_kind,
-                         "algorithmic_bytes_per_launch": BYTES_PER_FRAME * n,
+                         "algorithmic_bytes_per_launch": bytes_per_frame * n,
                          "kernel_ms": avg_ms, "pixels_per_s": 320 * 208 * n / (avg_ms / 1000.0)},
             "cpu_baseline": {"value": cpu_value, "unit": UNIT, "cores": 1, "kind": "port",
-                             "sample": f"{cpu_done} lanes of the {WORKLOAD} workload in {cpu_dt:.1f} s, one thread"},
+                             "sample": f"{cpu_done} lanes of the {workload} workload in {cpu_dt:.1f} s, one thread"},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(host_lanes.numel() * 4
                                                                                  + host_things.numel() * 4),
                     "d2h_bytes_per_step": int(host_obs.numel()), "steps": e2e_steps},
@@ -320,7 +347,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--lanes", type=int, default=LANES_PER_GPU, help="lanes per GPU (profiling captures use fewer)")
+    ap.add_argument("--workload", default=WORKLOAD, choices=sorted(WORKLOADS),
+                    help="benchmark configuration (default: the headline one)")
+    ap.add_argument("--lanes", type=int, default=0, help="lanes per GPU (default: the workload's own count)")
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg (profiling captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

@@ -1631,6 +1631,7 @@ __device__ void gd_fallback_pass(const GdScene &sc, const GdView &v, const GdSha
   const int count = min(sh.misc[1], GD_FALLBACK_MAX);
   int *queue = (int *)sh.hitD;
   unsigned *anchors = (unsigned *)sh.hitA;           /* [row][GD_WARPS] column bits */
+  unsigned *owned = sh.masks + 7 * GD_SW;            /* drawn pixels are marked owned */
   if (tid == 0) { sh.misc[2] = GD_VH; sh.misc[3] = -1; }
   if (warp == 0) gd_flat_bounds_setup(sc, v, sh.misc);
   __syncthreads();
@@ -1643,6 +1644,7 @@ __device__ void gd_fallback_pass(const GdScene &sc, const GdView &v, const GdSha
       GdPlaneSpan p;
       gd_plane_setup(sc, v, own.sector, own.isFloor, px, p);
       sh.frame[py * GD_SW + px] = gd_plane_pixel(p, v, sh.yslope, sh.colormap, py);
+      atomicOr(&owned[(py >> 5) * GD_SW + px], 1u << (py & 31));
       queue[i] = -1;
     } else {
       atomicMin(&sh.misc[2], py);
@@ -1707,6 +1709,7 @@ __device__ void gd_fallback_pass(const GdScene &sc, const GdView &v, const GdSha
       GdPlaneSpan p;
       gd_plane_setup(sc, v, sector, isFloor, px, p);
       sh.frame[py * GD_SW + px] = gd_plane_pixel(p, v, sh.yslope, sh.colormap, py);
+      atomicOr(&owned[(py >> 5) * GD_SW + px], 1u << (py & 31));
     }
   }
   __syncthreads();
@@ -2241,25 +2244,28 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
     GD_BEAT(4);
     gd_walk(sc, v, sh, events, eventCount, rowproj, p.status, sh.misc[0]);
     __syncthreads();
-    {
-      /* rows no seg ever claimed show the per-pixel flat fallback: queue them
-       * (the hit cache is free once every column has finished its walk) */
+    /* Rows no seg ever claimed show the per-pixel flat fallback.  They are
+     * queued (the hit cache is free once every column has finished its walk)
+     * and resolved; a frame with more such pixels than the queue holds takes
+     * several rounds, each pass marking what it drew as owned. */
+    for (;;) {
       const unsigned *filled = sh.masks + tid, *owned = sh.masks + 7 * GD_SW + tid;
       for (int k = 0; k < 7; ++k) {
         unsigned m = gd_range_word(k, 0, GD_VH) & ~filled[k * GD_SW] & ~owned[k * GD_SW];
         while (m) {
           int y = (k << 5) + __ffs(m) - 1;
           m &= m - 1;
-          sh.frame[y * GD_SW + tid] = 0;
           int slot = atomicAdd(&sh.misc[1], 1);
           if (slot < GD_FALLBACK_MAX) ((int *)sh.hitD)[slot] = (y << 16) | tid;
         }
       }
-    }
-    __syncthreads();
-    if (sh.misc[1] > 0) {
-      if (sh.misc[1] > GD_FALLBACK_MAX && tid == 0) atomicOr(p.status, GD_STATUS_FALLBACK_OVERFLOW);
+      __syncthreads();
+      const int queued = sh.misc[1];
+      if (queued == 0) break;                        /* block-uniform */
       gd_fallback_pass(sc, v, sh, sh.misc[0]);
+      if (queued <= GD_FALLBACK_MAX) break;
+      if (tid == 0) sh.misc[1] = 0;
+      __syncthreads();
     }
     GD_BEAT(5);
     gd_sprites(sc, v, sh, events, eventCount, nThings);
@@ -2516,6 +2522,16 @@ extern "C" int gd_render_frames(const gd_renderer *r, const int32_t *lanes, cons
   if (!obs_out && !indexed_out && !rgb_out) return GD_ERR_NULL;
   int flags = (mask_hud ? GD_F_MASK_HUD : 0) | ((include_hud || !mask_hud) ? GD_F_DRAW_HUD : 0);
   return gd_launch(r, lanes, (const gd_thing *)things, n, flags, nullptr, nullptr, obs_out, indexed_out, rgb_out,
+                   scratch, scratch_bytes, status, stream);
+}
+
+extern "C" int gd_render_step_frames(const gd_renderer *r, const int32_t *lanes, const void *things, int n,
+                                     int mask_hud, int include_hud, uint8_t *stack, uint8_t *indexed_out,
+                                     uint8_t *rgb_out, void *scratch, size_t scratch_bytes, int *status,
+                                     void *stream) {
+  if (!stack || (!indexed_out && !rgb_out)) return GD_ERR_NULL;
+  int flags = GD_F_STACK_ROLL | (mask_hud ? GD_F_MASK_HUD : 0) | ((include_hud || !mask_hud) ? GD_F_DRAW_HUD : 0);
+  return gd_launch(r, lanes, (const gd_thing *)things, n, flags, stack, nullptr, nullptr, indexed_out, rgb_out,
                    scratch, scratch_bytes, status, stream);
 }
 

@@ -22,7 +22,7 @@ STATUS_THINGS_OVERFLOW = 2
 EXPORTS = (
     "gd_error_string", "gd_renderer_create", "gd_renderer_destroy", "gd_renderer_scratch_bytes",
     "gd_renderer_ctas", "gd_renderer_shared_bytes", "gd_render_step", "gd_render_reset", "gd_render_frames",
-    "gd_render_step_host", "gd_static_scratch_bytes", "gd_static_max_walls", "gd_render_step_static",
+    "gd_render_step_frames", "gd_render_step_host", "gd_static_scratch_bytes", "gd_static_max_walls", "gd_render_step_static",
 )
 
 _lib = None
@@ -61,6 +61,8 @@ def load() -> ctypes.CDLL:
         lib.gd_render_reset.argtypes = [vp, vp, vp, ci, ci, vp, vp, vp, sz, vp, vp]
         lib.gd_render_frames.restype = ci
         lib.gd_render_frames.argtypes = [vp, vp, vp, ci, ci, ci, vp, vp, vp, vp, sz, vp, vp]
+        lib.gd_render_step_frames.restype = ci
+        lib.gd_render_step_frames.argtypes = [vp, vp, vp, ci, ci, ci, vp, vp, vp, vp, sz, vp, vp]
         lib.gd_render_step_host.restype = ci
         lib.gd_render_step_host.argtypes = [vp, vp, vp, ci, ci, vp, vp, vp, vp, vp, sz, vp, vp]
         lib.gd_static_scratch_bytes.restype = sz
@@ -205,6 +207,23 @@ class Renderer:
         self.launches += 1
         return o, i, c
 
+    def step_frames(self, lanes, things, stack, *, indexed=None, rgb=None, mask_hud=True, include_hud=True):
+        """One step (stack push) that also writes the full frame(s) of the same
+        drawing pass into the caller's ``indexed (N,240,320)`` / ``rgb
+        (N,240,320,3)`` uint8 tensors."""
+
+        n = self._inputs(lanes, things)
+        self._check_stack(stack, n)
+        for t, shape in ((indexed, (n, 240, 320)), (rgb, (n, 240, 320, 3))):
+            if t is not None and (t.dtype != torch.uint8 or tuple(t.shape) != shape or not t.is_contiguous()
+                                  or t.device != self.device):
+                raise ValueError(f"frame output must be a contiguous uint8 tensor of shape {shape} on the device")
+        _check(self.lib.gd_render_step_frames(self.handle, lanes.data_ptr(), things.data_ptr(), n, int(mask_hud),
+                                              int(include_hud), stack.data_ptr(), _ptr(indexed), _ptr(rgb),
+                                              self.scratch.data_ptr(), self.scratch_bytes, self.status.data_ptr(),
+                                              self._stream()), "gd_render_step_frames")
+        self.launches += 1
+
     def _check_stack(self, stack, n):
         if stack.dtype != torch.uint8 or tuple(stack.shape) != (n, 4, 84, 84) or not stack.is_contiguous():
             raise ValueError("stack must be a contiguous (N,4,84,84) uint8 tensor")
@@ -222,6 +241,4 @@ class Renderer:
                 names.append("clip-event overflow (a column crossed more segs than the scratch holds)")
             if bits & STATUS_THINGS_OVERFLOW:
                 names.append("a lane listed more things than max_things")
-            if bits & 8:
-                names.append("more unclaimed pixels in a frame than the fallback queue holds")
             raise NativeError("renderer status: " + "; ".join(names or [hex(bits)]))

@@ -46,7 +46,7 @@ enum gd_error {
 #define GD_STATUS_EVENT_OVERFLOW 1
 #define GD_STATUS_THINGS_OVERFLOW 2
 #define GD_STATUS_BAD_SECTOR 4
-#define GD_STATUS_FALLBACK_OVERFLOW 8
+#define GD_STATUS_FALLBACK_OVERFLOW 8   /* reserved; never set (the fallback takes as many rounds as it needs) */
 
 typedef struct gd_renderer gd_renderer;
 
@@ -109,6 +109,19 @@ int gd_render_reset(const gd_renderer *r, const int32_t *lanes, const void *thin
 int gd_render_frames(const gd_renderer *r, const int32_t *lanes, const void *things, int n, int mask_hud,
                      int include_hud, uint8_t *obs_out, uint8_t *indexed_out, uint8_t *rgb_out, void *scratch,
                      size_t scratch_bytes, int *status, void *stream);
+
+/*
+ * One agent step that also hands out the full frame it was reduced from:
+ * gd_render_step plus the indexed and/or RGB24 frame of gd_render_frames from
+ * the same drawing pass.  Replaces the pair the reference runs when a caller
+ * asks for images every step: the observation render inside
+ * TorchDeathmatchEngine.step (src/gradoom/engine.py:9575-9576) followed by
+ * render_native_frame (15453-15457) behind GraDoomVecEnv.render()
+ * (src/gradoom/env.py:1055); both draw the same state, so one pass serves both.
+ */
+int gd_render_step_frames(const gd_renderer *r, const int32_t *lanes, const void *things, int n, int mask_hud,
+                          int include_hud, uint8_t *stack, uint8_t *indexed_out, uint8_t *rgb_out, void *scratch,
+                          size_t scratch_bytes, int *status, void *stream);
 
 /*
  * gd_render_step for callers that keep their state in host memory: queues the

@@ -264,3 +264,28 @@ def test_flat_fallback_after_free_movement(pkg, oracle, scenes):
     _, indexed, _ = r.frames(_dev(lanes[chosen]), _dev(things[chosen]), indexed=True)
     r.check_status()
     assert np.array_equal(indexed.cpu().numpy(), expected["indexed"][chosen])
+
+
+@pytest.mark.gpu
+def test_step_with_frames_equals_step_plus_frames(pkg, scenes):
+    """The fused entry point pushes the same stack as gd_render_step and writes
+    the same frames as gd_render_frames."""
+
+    import torch
+
+    from gradoom_b200 import stepper
+
+    sc, blob = scenes("c3")
+    lanes, things = stepper.random_lanes(sc, 96, 12, seed=5)
+    r = _renderer(blob, 12)
+    dl, dt = _dev(lanes), _dev(things)
+    base = torch.randint(0, 256, (96, 4, 84, 84), dtype=torch.uint8, device="cuda")
+    a, b = base.clone(), base.clone()
+    r.step(dl, dt, a)
+    _, indexed, rgb = r.frames(dl, dt, indexed=True, rgb=True)
+    indexed2, rgb2 = torch.empty_like(indexed), torch.empty_like(rgb)
+    r.step_frames(dl, dt, b, indexed=indexed2, rgb=rgb2)
+    r.check_status()
+    assert torch.equal(a, b)
+    assert torch.equal(indexed, indexed2)
+    assert torch.equal(rgb, rgb2)
