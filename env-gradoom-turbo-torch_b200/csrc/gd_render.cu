@@ -794,6 +794,7 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
    * and keep the results in this column's slice of shared memory */
   constexpr int kCache = 8;
   const int nCache = min(i1 - i0, kCache);
+#pragma unroll 1
   for (int k = 0; k < nCache; ++k) {
     GdHit h = gd_hit(sc, v, walls, sc.secWalls[i0 + k], x, rx, ry);
     hitD[k * GD_SW + x] = h.d;
@@ -810,6 +811,7 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
   };
   /* one out-of-line copy of the uncached test serves every rule below */
   auto cachedHit = [&](int w) -> GdHit {
+#pragma unroll 1
     for (int k = 0; k < nCache; ++k)
       if (sc.secWalls[i0 + k] == w) return loadHit(k);
     return gd_hit_slow(sc, v, walls, w, x, rx, ry);
@@ -819,6 +821,7 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
   float distance = GD_INF;
   int wallIndex = 0;
   if (curSector >= 0) {
+#pragma unroll 1
     for (int k = i0; k < i1; ++k) {
       int w = sc.secWalls[k];
       GdHit h = HITK(k);
@@ -826,6 +829,7 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
     }
     float sd = GD_INF;
     int sw = 0;
+#pragma unroll 1
     for (int k = i0; k < i1; ++k) {
       int w = sc.secWalls[k];
       if (!walls[w].oneSided) continue;
@@ -859,6 +863,7 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
   float psd = GD_INF;
   int psi = 0;
   if (!selIsProjected) {
+#pragma unroll 1
     for (int k = i0; k < i1; ++k) {
       int w = sc.secWalls[k];
       if (!walls[w].oneSided || !SHARES_SEL(w)) continue;
@@ -870,6 +875,7 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
       const int32_t *idx = selUsesStart ? sc.sbStartIdx : sc.sbEndIdx;
       float sbd = GD_INF;
       int sbi = wallIndex;
+#pragma unroll 1
       for (int k = off[wallIndex]; k < off[wallIndex + 1]; ++k) {
         int b = idx[k];
         bool inc = sc.wsec[b * 2] == current || sc.wsec[b * 2 + 1] == current;
@@ -903,6 +909,7 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
   float npd = GD_INF;
   int npi = 0;
   if (!selOwnerIsProjected) {
+#pragma unroll 1
     for (int k = i0; k < i1; ++k) {
       int w = sc.secWalls[k];
       if (walls[w].oneSided) continue;
@@ -1021,6 +1028,7 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
   int cni = 0, oni = 0, gpi = 0;
   const float prior = prev;
   if (endpointOnly) {
+#pragma unroll 1
     for (int k = i0; k < i1; ++k) {
       int w = sc.secWalls[k];
       GdHit h = HITK(k);
@@ -1035,6 +1043,7 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
       if (sgp && h.d < gpd) { gpd = h.d; gpi = w; }
     }
     /* endpointOnly implies otherSector >= 0 */
+#pragma unroll 1
     for (int k = sc.secOff[otherSector]; k < sc.secOff[otherSector + 1]; ++k) {
       int w = sc.secWalls[k];
       GdHit h = HIT(w);
