@@ -81,7 +81,7 @@ __device__ __forceinline__ i64 gd_pymod(i64 a, i64 m) {
  */
 __device__ __noinline__ i64 gd_div_generic(i64 a, i64 b) { return a / b; }
 
-__device__ __forceinline__ i64 gd_div(i64 a, i64 b) {
+__device__ __noinline__ i64 gd_div(i64 a, i64 b) {
   unsigned long long ua = a < 0 ? 0ull - (unsigned long long)a : (unsigned long long)a;
   unsigned long long ub = b < 0 ? 0ull - (unsigned long long)b : (unsigned long long)b;
   if (((ua | ub) >> 52) != 0 || ub == 0) return gd_div_generic(a, b);

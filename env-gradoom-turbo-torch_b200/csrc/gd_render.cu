@@ -342,6 +342,7 @@ __device__ __noinline__ void gd_endpoint_owner(const GdScene &sc, const GdView &
     float best = GD_INF;
     int bestSlot = 0;
     int n0 = sc.nbOff[w], n1 = sc.nbOff[w + 1];
+#pragma unroll 1
     for (int k = n0; k < n1; ++k) {
       int nb = sc.nbIdx[k], fl = sc.nbFlags[k];
       GdHit hn = gd_hit(sc, v, walls, nb, x, rx, ry);
@@ -548,6 +549,7 @@ __device__ __forceinline__ bool gd_set_equals(const GdScene &sc, int w, int p0, 
 }
 __device__ bool gd_unique_at_vertex(const GdScene &sc, int v, int skipA, int skipB, int p0, int p1, int &index) {
   int count = 0, found = 0;
+#pragma unroll 1
   for (int k = sc.vtxOff[v]; k < sc.vtxOff[v + 1]; ++k) {
     int c = sc.vtxWalls[k];
     if (c == skipA || c == skipB) continue;
@@ -1123,6 +1125,7 @@ __device__ __noinline__ void gd_draw_tier(const GdScene &sc, const GdView &v, co
             oTailB = oTailValid ? ob : 0;
   const int shift = 32 - hbits;
   uint8_t *dst = sh.frame + x;
+#pragma unroll 1
   for (int k = ya >> 5; k <= (yb - 1) >> 5; ++k) {
     unsigned have = filled[k * GD_SW];
     unsigned m = gd_range_word(k, ya, yb) & ~gd_range_word(k, ea, eb) & ~have;
@@ -1131,6 +1134,7 @@ __device__ __noinline__ void gd_draw_tier(const GdScene &sc, const GdView &v, co
     const unsigned tailM = gd_range_word(k, tailA, GD_VH) | gd_range_word(k, oTailA, oTailB);
     const int y0 = k << 5;
     /* two rows per trip; an odd last row is simply drawn twice */
+#pragma unroll 1
     while (m) {
       int b0 = __ffs(m) - 1;
       m &= m - 1;
@@ -1150,11 +1154,13 @@ __device__ __noinline__ void gd_mark_plane(const GdScene &sc, const GdView &v, c
   if (ya >= yb) return;
   const int k0 = ya >> 5, k1 = (yb - 1) >> 5;
   unsigned any = 0;
+#pragma unroll 1
   for (int k = k0; k <= k1; ++k) any |= gd_range_word(k, ya, yb) & ~owned[k * GD_SW];
   if (!any) return;
   GdPlaneSpan p;
   gd_plane_setup(sc, v, sector, isFloor, x, p);
   uint8_t *dst = sh.frame + x;
+#pragma unroll 1
   for (int k = k0; k <= k1; ++k) {
     unsigned have = owned[k * GD_SW];
     unsigned fresh = gd_range_word(k, ya, yb) & ~have;
@@ -1162,6 +1168,7 @@ __device__ __noinline__ void gd_mark_plane(const GdScene &sc, const GdView &v, c
     owned[k * GD_SW] = have | fresh;
     unsigned m = fresh & ~filled[k * GD_SW];
     const int y0 = k << 5;
+#pragma unroll 1
     while (m) {
       int b0 = __ffs(m) - 1;
       m &= m - 1;
@@ -1429,6 +1436,7 @@ __device__ __forceinline__ bool gd_point_in_sector(const GdScene &sc, int s, flo
   if (px > bb.y + 1.0f) return false;                  /* every crossing lies left of the point */
   if (px < bb.x - 1.0f && sc.secI[s * 4 + 3]) return false;  /* closed loops cross an even number of times */
   int crossings = 0;
+#pragma unroll 1
   for (int k = sc.edgeOff[s]; k < sc.edgeOff[s + 1]; ++k) {
     const float4 e = *reinterpret_cast<const float4 *>(&sc.walls[sc.edgeWalls[k] * 4]);
     bool crosses = (e.y > py) != (e.w > py);
@@ -1453,6 +1461,7 @@ __device__ __noinline__ bool gd_pixel_unresolved(const GdScene &sc, const GdView
   float den = fmaxf(fabsf(delta), 0.5f);
   /* An existence test, so the order is free: `hint` (the sector whose plane
    * was marked on this pixel) is nearly always the one that answers it. */
+#pragma unroll 1
   for (int k = -1; k < sc.S; ++k) {
     int s = k < 0 ? hint : k;
     if (k >= 0 && s == hint) continue;
@@ -1543,7 +1552,7 @@ __device__ void gd_flat_bounds_setup(const GdScene &sc, const GdView &v, int *mi
   }
 }
 
-__device__ __forceinline__ GdFlatRay gd_flat_ray(const GdScene &sc, const GdView &v, int x) {
+__device__ __noinline__ GdFlatRay gd_flat_ray(const GdScene &sc, const GdView &v, int x) {
   i64 ti = gd_clamp((GD_ANG90 - v.pitchBam) >> 19, 0, 4095);
   i64 offFixed = ((i64)sc.fineTan[ti] * 12582912LL) >> 16;
   GdFlatRay r;
@@ -1580,6 +1589,7 @@ __device__ __noinline__ GdFlatProbe gd_flat_probe(const GdScene &sc, const GdVie
     }
   }
   float best = GD_INF;
+#pragma unroll 1
   for (int s = 0; s < sc.S; ++s) {
     float ph = out.isFloor ? (v.viewZ - sc.secF[s * 2]) : (sc.secF[s * 2 + 1] - v.viewZ);
     float perp = ph * 192.0f / den;
@@ -1841,6 +1851,7 @@ __device__ void gd_sprites(const GdScene &sc, const GdView &v, const GdShared &s
         y1 = (int)gd_clamp(yb, 0, GD_VH);
       }
       __syncwarp();                                  /* the farther sprite's pixels are in place */
+#pragma unroll 1
       for (int y = y0 + lane; y < y1; y += 32) {
         i64 frac = fracBase + (i64)y * ac.iscale;
         i64 tv = frac >> 16;
@@ -1854,6 +1865,7 @@ __device__ void gd_sprites(const GdScene &sc, const GdView &v, const GdShared &s
         float bestD = GD_INF;
         int bestW = -1, ownerSector = -1;
         bool filled = false, ownerFloor = false;
+#pragma unroll 1
         for (int e = 0; e < nEv; ++e) {
           const GdEvent ev = events[e * GD_SW + x];
           bool inLower = y >= ev.t1a && y < ev.t1b, inUpper = y >= ev.t0a && y < ev.t0b;
