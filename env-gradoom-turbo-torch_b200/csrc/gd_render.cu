@@ -1910,11 +1910,16 @@ __device__ __noinline__ void gd_weapon_patch(const GdScene &sc, uint8_t *frame, 
   i64 texMid = 100 * GD_FU - (32 * GD_FU + 0x6000) - voff + (i64)wi.w * GD_FU;
   const i64 yscale = GD_SCREEN_H * GD_FU / 200;
   const i64 iscale = GD_U32MASK / yscale;
-  for (int idx = threadIdx.x; idx < GD_VH * w; idx += GD_THREADS) {
-    int y = idx / w, sx = idx - y * w;
+  /* rows whose source row lies inside the patch: 0 <= base + y*iscale < h*FU */
+  const i64 base = texMid - (i64)(GD_VH / 2 - 1) * iscale;
+  const i64 lo = -base, hi = (i64)h * GD_FU - base;
+  const int y0 = (int)gd_clamp(lo <= 0 ? 0 : gd_div(lo + iscale - 1, iscale), 0, GD_VH);
+  const int y1 = (int)gd_clamp(hi <= 0 ? 0 : gd_div(hi + iscale - 1, iscale), 0, GD_VH);
+  for (int idx = threadIdx.x; idx < (y1 - y0) * w; idx += GD_THREADS) {
+    int y = y0 + idx / w, sx = idx - (y - y0) * w;
     i64 xx = screenLeft + sx;
     if (xx < 0 || xx >= GD_SW) continue;
-    i64 sy = (texMid + ((i64)y - (GD_VH / 2 - 1)) * iscale) >> 16;
+    i64 sy = (base + (i64)y * iscale) >> 16;
     if (sy < 0 || sy >= h) continue;
     i64 cy = gd_min(sy, sc.wpnH - 1), cx = gd_min((i64)sx, (i64)sc.wpnW - 1);
     size_t si = ((size_t)id * sc.wpnH + (size_t)cy) * sc.wpnW + (size_t)cx;
