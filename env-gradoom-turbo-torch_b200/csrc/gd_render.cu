@@ -2380,6 +2380,8 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
 #include <new>
 #include <string.h>
 
+#define GD_HOST_CHUNKS 4
+
 struct gd_renderer {
   GdScene sc;
   int32_t header[GD_HDR_WORDS];
@@ -2389,6 +2391,10 @@ struct gd_renderer {
   size_t smemBytes;
   int stageMask;
   int secWallsN, vtxWallsN, V;
+  /* gd_render_step_host overlaps the device->host copy of one lane chunk with
+   * the drawing of the next on this side stream */
+  cudaStream_t copyStream;
+  cudaEvent_t chunkDone[GD_HOST_CHUNKS], copiesDone;
 };
 
 static const void *gd_section(const uint8_t *dev, const int32_t *h, int s) { return dev + h[GD_HDR_SECTION0 + s]; }
@@ -2424,6 +2430,9 @@ extern "C" int gd_renderer_create(const void *blob_header_host, const void *blob
     return GD_ERR_SIZE;
   gd_renderer *r = new (std::nothrow) gd_renderer;
   if (!r) return GD_ERR_CUDA;
+  r->copyStream = nullptr;
+  r->copiesDone = nullptr;
+  for (int c = 0; c < GD_HOST_CHUNKS; ++c) r->chunkDone[c] = nullptr;
   memcpy(r->header, h, sizeof r->header);
   r->device = device;
   r->maxThings = max_things;
@@ -2487,13 +2496,33 @@ extern "C" int gd_renderer_create(const void *blob_header_host, const void *blob
     else
       r->ctas = sms * perSm;  /* one persistent CTA per resident slot */
   }
+  r->copyStream = nullptr;
+  r->copiesDone = nullptr;
+  for (int c = 0; c < GD_HOST_CHUNKS; ++c) r->chunkDone[c] = nullptr;
+  if (rc == GD_OK) {
+    bool ok = cudaStreamCreateWithFlags(&r->copyStream, cudaStreamNonBlocking) == cudaSuccess &&
+              cudaEventCreateWithFlags(&r->copiesDone, cudaEventDisableTiming) == cudaSuccess;
+    for (int c = 0; ok && c < GD_HOST_CHUNKS; ++c)
+      ok = cudaEventCreateWithFlags(&r->chunkDone[c], cudaEventDisableTiming) == cudaSuccess;
+    if (!ok) rc = GD_ERR_CUDA;
+  }
   cudaSetDevice(prev);
-  if (rc != GD_OK) { cudaGetLastError(); delete r; return rc; }
+  if (rc != GD_OK) { cudaGetLastError(); gd_renderer_destroy(r); return rc; }
   *out = r;
   return GD_OK;
 }
 
-extern "C" void gd_renderer_destroy(gd_renderer *r) { delete r; }
+extern "C" void gd_renderer_destroy(gd_renderer *r) {
+  if (!r) return;
+  int prev = 0;
+  bool switched = cudaGetDevice(&prev) == cudaSuccess && cudaSetDevice(r->device) == cudaSuccess;
+  for (int c = 0; c < GD_HOST_CHUNKS; ++c)
+    if (r->chunkDone[c]) cudaEventDestroy(r->chunkDone[c]);
+  if (r->copiesDone) cudaEventDestroy(r->copiesDone);
+  if (r->copyStream) cudaStreamDestroy(r->copyStream);
+  if (switched) cudaSetDevice(prev);
+  delete r;
+}
 
 extern "C" size_t gd_renderer_scratch_bytes(const gd_renderer *r) {
   return r ? (size_t)r->ctas * gd_scratch_per_cta(r->sc.W) + 16 : 0;
@@ -2580,12 +2609,49 @@ extern "C" int gd_render_step_host(const gd_renderer *r, const int32_t *lanes_ho
   if (things_host &&
       cudaMemcpyAsync(things_dev, things_host, (size_t)n * thingStride, cudaMemcpyHostToDevice, s) != cudaSuccess)
     return GD_ERR_CUDA;
-  int rc = gd_render_step(r, lanes_dev, things_dev, n, mask_hud, stack, scratch, scratch_bytes, status, stream);
-  if (rc != GD_OK) return rc;
+  /* Pinned (or registered) host memory is mapped into the device's address
+   * space: the kernel then writes every lane's newest frame straight into it
+   * while it draws the following lanes, and no copy is left to wait for. */
+  {
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, obs_host) == cudaSuccess && attr.type == cudaMemoryTypeHost &&
+        attr.devicePointer != nullptr && (((uintptr_t)attr.devicePointer) & 15) == 0) {
+      int flags = GD_F_STACK_ROLL | (mask_hud ? GD_F_MASK_HUD : GD_F_DRAW_HUD);
+      return gd_launch(r, lanes_dev, (const gd_thing *)things_dev, n, flags, stack, nullptr,
+                       (uint8_t *)attr.devicePointer, nullptr, nullptr, scratch, scratch_bytes, status, stream);
+    }
+    cudaGetLastError();
+  }
+  /* Pageable host memory: lanes are drawn in chunks; each chunk's newest frames travel to the host
+   * on the side stream while the next chunk is drawn.  The caller's stream
+   * waits for the last copy, so synchronising it covers the whole call. */
   const size_t frame = (size_t)GD_OBS * GD_OBS;
-  if (cudaMemcpy2DAsync(obs_host, frame, stack + (GD_STACK - 1) * frame, GD_STACK * frame, frame, (size_t)n,
-                        cudaMemcpyDeviceToHost, s) != cudaSuccess)
-    return GD_ERR_CUDA;
+  const int chunks = n >= 512 * GD_HOST_CHUNKS ? GD_HOST_CHUNKS : 1;
+  const int per = (n + chunks - 1) / chunks;
+  for (int c = 0; c < chunks; ++c) {
+    const int n0 = c * per, nc = (n0 + per <= n ? per : n - n0);
+    if (nc <= 0) break;
+    const gd_thing *th = things_dev ? (const gd_thing *)things_dev + (size_t)n0 * (r->maxThings > 0 ? r->maxThings : 1)
+                                    : nullptr;
+    uint8_t *st = stack + (size_t)n0 * GD_STACK * frame;
+    int rc = gd_render_step(r, lanes_dev + (size_t)n0 * GD_LANE_WORDS, th, nc, mask_hud, st, scratch, scratch_bytes,
+                            status, stream);
+    if (rc != GD_OK) return rc;
+    cudaStream_t cs = s;
+    if (chunks > 1) {
+      cs = r->copyStream;
+      if (cudaEventRecord(r->chunkDone[c], s) != cudaSuccess || cudaStreamWaitEvent(cs, r->chunkDone[c], 0) != cudaSuccess)
+        return GD_ERR_CUDA;
+    }
+    if (cudaMemcpy2DAsync(obs_host + (size_t)n0 * frame, frame, st + (GD_STACK - 1) * frame, GD_STACK * frame, frame,
+                          (size_t)nc, cudaMemcpyDeviceToHost, cs) != cudaSuccess)
+      return GD_ERR_CUDA;
+  }
+  if (chunks > 1) {
+    if (cudaEventRecord(r->copiesDone, r->copyStream) != cudaSuccess ||
+        cudaStreamWaitEvent(s, r->copiesDone, 0) != cudaSuccess)
+      return GD_ERR_CUDA;
+  }
   return GD_OK;
 }
 

@@ -128,7 +128,11 @@ int gd_render_step_frames(const gd_renderer *r, const int32_t *lanes, const void
  * host->device copies of the records into the caller's staging buffers
  * (`lanes_dev`, `things_dev`), the render, and the device->host copy of the
  * newest 84x84 frame of every lane into `obs_host` (n x 84 x 84 u8).  Use
- * pinned host buffers to keep the call asynchronous.  Same reference call site
+ * pinned host buffers to keep the call asynchronous: a pinned (or registered,
+ * 16-byte aligned) `obs_host` is written by the kernel itself as each lane
+ * finishes, so no copy remains after the drawing; a pageable one is filled by
+ * chunked copies that overlap the drawing of the following chunk.  Either way
+ * the result is complete once `stream` has been synchronised.  Same reference call site
  * as gd_render_step (src/gradoom/engine.py:9575-9576), plus the
  * `.to("cpu")` a host-side learner performs on the observation.
  */

@@ -289,3 +289,32 @@ def test_step_with_frames_equals_step_plus_frames(pkg, scenes):
     assert torch.equal(a, b)
     assert torch.equal(indexed, indexed2)
     assert torch.equal(rgb, rgb2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("pinned", [True, False])
+def test_host_buffer_step_matches_device_step(pkg, scenes, pinned):
+    """gd_render_step_host, with a pinned result buffer (written by the kernel
+    itself) and with a pageable one (chunked copies), against gd_render_step."""
+
+    import torch
+
+    from gradoom_b200 import stepper
+
+    sc, blob = scenes("c1")
+    n = 2304                                   # enough lanes for the chunked path, not a multiple of the chunk size
+    lanes, things = stepper.random_lanes(sc, n, 4, seed=21)
+    r = _renderer(blob, 4)
+    dl, dt = _dev(lanes), _dev(things)
+    base = torch.randint(0, 256, (n, 4, 84, 84), dtype=torch.uint8, device="cuda")
+    expect, got = base.clone(), base.clone()
+    r.step(dl, dt, expect)
+    host_lanes, host_things = torch.from_numpy(lanes), torch.from_numpy(things)
+    host_obs = torch.zeros((n, 84, 84), dtype=torch.uint8)
+    if pinned:
+        host_lanes, host_things, host_obs = host_lanes.pin_memory(), host_things.pin_memory(), host_obs.pin_memory()
+    r.step_host(host_lanes, host_things, torch.empty_like(dl), torch.empty_like(dt), got, host_obs)
+    torch.cuda.synchronize()
+    r.check_status()
+    assert torch.equal(expect, got)
+    assert torch.equal(host_obs, expect[:, 3].cpu())
