@@ -2044,6 +2044,7 @@ __device__ void gd_resize(const uint8_t *frame, const unsigned long long *pal64,
      * past the overlap get weight zero, so the tap loops have fixed trip counts
      * and their loads are independent. */
     const int sy0 = ys / 84, sx0 = xs / 84;
+    if (sy0 >= srcRows) { out[o] = 0; continue; }    /* only masked status-bar rows: black */
     unsigned wx[5];
     int cx[5];
 #pragma unroll
