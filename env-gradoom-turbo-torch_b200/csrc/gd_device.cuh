@@ -59,6 +59,8 @@ struct GdScene {
   const int32_t *fineSine, *fineTan;
   const float *rayOffsets, *rayCosCorr;
   const float *secBBox;
+  const int32_t *maskedWalls;   /* M two-sided walls that carry a middle texture */
+  int M;
 };
 
 __device__ __forceinline__ i64 gd_min(i64 a, i64 b) { return a < b ? a : b; }

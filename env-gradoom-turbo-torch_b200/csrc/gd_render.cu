@@ -87,6 +87,8 @@ struct GdShared {
   uint8_t *obs;         /* 84 x 84 */
   int *misc;            /* 16 ints: start sector, fallback queue length, its unresolved rows' range, GdFlatBounds */
   unsigned *masks;      /* 14 x 320: per-column filled / plane-owned row bitmasks */
+  float *maskedDist;    /* 320: nearest masked drawseg of the column ... */
+  unsigned *maskedInfo; /* ... its wall << 16 | ceiling clip << 8 | floor clip; 0xFFFF0000 | .. = none */
   float *hitD, *hitA;   /* 8 x 320 each: per-column cache of this iteration's wall hits */
   uint8_t *hitF;        /* 8 x 320 */
 };
@@ -107,6 +109,7 @@ __host__ __device__ inline size_t gd_shared_bytes(int W, int maxThings) {
   b += gd_align16(GD_OBS * GD_OBS);
   b += gd_align16(64);
   b += gd_align16(14 * GD_SW * 4);
+  b += 2 * gd_align16(GD_SW * 4);
   b += 2 * gd_align16(8 * GD_SW * 4) + gd_align16(8 * GD_SW);
   b += gd_align16((size_t)W * sizeof(GdWall));
   b += gd_align16((size_t)(maxThings > 0 ? maxThings : 1) * sizeof(GdActor));
@@ -127,6 +130,8 @@ __device__ inline void gd_carve(uint8_t *base, int W, int maxThings, GdShared &s
   s.obs = base + o; o += gd_align16(GD_OBS * GD_OBS);
   s.misc = (int *)(base + o); o += gd_align16(64);
   s.masks = (unsigned *)(base + o); o += gd_align16(14 * GD_SW * 4);
+  s.maskedDist = (float *)(base + o); o += gd_align16(GD_SW * 4);
+  s.maskedInfo = (unsigned *)(base + o); o += gd_align16(GD_SW * 4);
   s.hitD = (float *)(base + o); o += gd_align16(8 * GD_SW * 4);
   s.hitA = (float *)(base + o); o += gd_align16(8 * GD_SW * 4);
   s.hitF = base + o; o += gd_align16(8 * GD_SW);
@@ -1182,6 +1187,89 @@ __device__ __noinline__ void gd_mark_plane(const GdScene &sc, const GdView &v, c
   }
 }
 
+/* ---- two-sided middle textures (engine.py:13424-13745) -----------------------
+ * Replayed after the planes: per column the nearest projected crossing of a
+ * line that carries a middle texture on the viewer's side, clipped by the
+ * drawseg snapshot the walk left for that column. */
+__device__ __forceinline__ i64 gd_masked_iscale(i64 swall) {
+  i64 s = (swall * GD_FU) >> 18;
+  if (s >= 0 && s < 3) return 3;
+  if (s > -3 && s < 0) return -3;
+  return s;
+}
+
+__device__ __noinline__ void gd_masked_pass(const GdScene &sc, const GdView &v, const GdShared &sh) {
+  const int x = threadIdx.x;
+  float rx, ry;
+  gd_ray(v, x, rx, ry);
+  float best = GD_INF;
+  int w = -1, side = 0, texId = -1;
+  bool leftEdge = false;
+#pragma unroll 1
+  for (int i = 0; i < sc.M; ++i) {
+    const int k = sc.maskedWalls[i];
+    const int sd = sh.walls[k].frontF ? 0 : 1;
+    const int t = sc.sideTex[(k * 2 + sd) * 3];
+    if (t < 0) continue;
+    GdHit h = gd_hit_slow(sc, v, sh.walls, k, x, rx, ry);
+    if (h.proj && h.d < best) { best = h.d; w = k; side = sd; texId = t; leftEdge = h.left; }
+  }
+  if (!isfinite(best)) return;
+  const GdWall &wv = sh.walls[w];
+  const int front = sc.wsec[w * 2], back = sc.wsec[w * 2 + 1] < 0 ? 0 : sc.wsec[w * 2 + 1];
+  const int lightSector = side == 0 ? front : back;
+  const float worldTop = fminf(gd_sec_ceil(sc, front), gd_sec_ceil(sc, back));
+  const int4 ti = *reinterpret_cast<const int4 *>(&sc.texInfo[texId * 4]);
+  const int tw = ti.x, th = ti.y, hbits = ti.w;
+  const i64 owallTop = gd_project_rows(v, wv, worldTop, x);
+  const i64 owallBottom = gd_project_rows(v, wv, worldTop - (float)th, x);
+  const unsigned info = sh.maskedInfo[x];
+  const bool hasSaved = (int)(info >> 16) == w;
+  const i64 ceilClip = gd_max(owallTop, hasSaved ? (i64)((info >> 8) & 0xFF) : 0);
+  const i64 floorClip = gd_min(owallBottom, hasSaved ? (i64)(info & 0xFF) : GD_VH);
+  const float *soff = &sc.sideOff[(w * 2 + side) * 2];
+  i64 hoff, vstepBase;
+  gd_prep_wall(sc, wv, w, x, hoff, vstepBase);
+  const i64 repeat = gd_rint(sc.wlen[w] * 65536.0f);
+  if (side != 0) hoff = repeat - hoff;
+  if (wv.sl > 0 && hoff < 0) hoff = 0;
+  if (hoff >= repeat) hoff = repeat - 1;
+  const int u = (int)gd_pymod((hoff + gd_rint(soff[0] * 65536.0f)) >> 16, tw);
+  const i64 vstep = vstepBase * (1LL << (14 - hbits));
+  const i64 texMid = gd_rint((worldTop - v.viewZ) * 65536.0f + soff[1] * 65536.0f);
+  /* R_DrawMaskedColumn: post rows from the drawseg's interpolated scale */
+  const i64 sLeft = gd_clamp(wv.sl, 0, GD_SW - 1), sLast = gd_clamp(wv.sr - 1, 0, GD_SW - 1);
+  i64 unused, startSwall, endSwall;
+  gd_prep_wall(sc, wv, w, (int)sLeft, unused, startSwall);
+  gd_prep_wall(sc, wv, w, (int)sLast, unused, endSwall);
+  const i64 startScale = gd_div(1LL << 32, gd_masked_iscale(startSwall));
+  const i64 endScale = gd_div(1LL << 32, gd_masked_iscale(endSwall));
+  const i64 scaleStep = gd_div(endScale - startScale, gd_max(wv.sr - wv.sl, 1));
+  const i64 spriteScale = startScale + gd_wmul(scaleStep, (i64)x - wv.sl);
+  const i64 topScreen = v.center - (gd_wmul(texMid, spriteScale) >> 16);
+  const i64 postTop = topScreen >> 16;
+  const i64 postBottom = ((topScreen + gd_wmul(spriteScale, th) - GD_FU) >> 16) + 1;
+  const i64 clippedTop = gd_max(postTop, ceilClip);
+  i64 clippedBottom = gd_min(postBottom, floorClip);
+  const i64 dcIscale = (vstepBase * GD_FU) >> 18;
+  const i64 fracStart = texMid + gd_wmul(clippedTop, dcIscale) - (gd_wmul(v.center - GD_FU, dcIscale) >> 16);
+  const i64 fracEnd = fracStart + gd_wmul(clippedBottom - clippedTop - 1, dcIscale);
+  if (clippedTop < clippedBottom && clippedBottom < floorClip && fracEnd < (i64)th * GD_FU - dcIscale)
+    clippedBottom += 1;
+  if (!(hasSaved || leftEdge)) return;
+  const float *wl = &sc.walls[w * 4];
+  const bool horizontal = fabsf(wl[3] - wl[1]) < 1e-6f, vertical = fabsf(wl[2] - wl[0]) < 1e-6f;
+  const i64 light = gd_sec_info(sc, lightSector).x + v.flashLight * 16 + (vertical ? 16 : (horizontal ? -16 : 0));
+  const i64 vis = wv.visL[side] + ((i64)x - wv.visSl[side]) * wv.visStep[side];
+  const uint8_t *cm = sh.colormap + gd_wall_shade(light, vis) * 256;
+  const uint8_t *col = sc.texAtlasCol + ((size_t)texId * sc.texW + u) * sc.texH;
+  const unsigned base = (unsigned)(gd_shl(texMid, 16 - hbits) + (gd_wmul(vstep, GD_FU - v.center) >> 16));
+  const unsigned step = (unsigned)vstep;
+#pragma unroll 1
+  for (int y = (int)gd_max(clippedTop, 0); y < (int)gd_min(clippedBottom, GD_VH); ++y)
+    sh.frame[y * GD_SW + x] = cm[col[(base + (unsigned)y * step) >> (32 - hbits)]];
+}
+
 #define GD_FALLBACK_MAX (8 * GD_SW)
 
 __device__ void gd_walk(const GdScene &sc, const GdView &v, const GdShared &sh, GdEvent *events, int *eventCount,
@@ -1194,6 +1282,7 @@ __device__ void gd_walk(const GdScene &sc, const GdView &v, const GdShared &sh, 
   unsigned *filled = sh.masks + x, *owned = sh.masks + 7 * GD_SW + x;
 #pragma unroll
   for (int k = 0; k < 7; ++k) { filled[k * GD_SW] = 0; owned[k * GD_SW] = 0; }
+  if (sc.M > 0) { sh.maskedDist[x] = GD_INF; sh.maskedInfo[x] = 0xFFFF0000u | GD_VH; }
   GdColState c;
   c.cur = startSector; c.ceilClip = 0; c.floorClip = GD_VH; c.prev = 0.0f;
   c.pendOwnerBoundary = c.pendEpBoundary = c.pendEpBridgeBoundary = c.pendPortalBridge = false;
@@ -1329,6 +1418,11 @@ __device__ void gd_walk(const GdScene &sc, const GdView &v, const GdShared &sh, 
     bool drawsLower = (it.viewFloor < it.otherFloor) && hasLower;
     if (it.rasterValid && !it.oneSided && (drawsUpper || it.markCeil)) c.ceilClip = drawsUpper ? it.cupbot : it.ctop;
     if (it.rasterValid && !it.oneSided && (drawsLower || it.markFloor)) c.floorClip = drawsLower ? it.clowtop : it.cbot;
+    /* masked drawseg snapshot (engine.py:12914-12939) */
+    if (sc.M > 0 && it.rasterValid && !it.oneSided && it.tex[0] >= 0 && it.distance < sh.maskedDist[x]) {
+      sh.maskedDist[x] = it.distance;
+      sh.maskedInfo[x] = ((unsigned)wallIndex << 16) | ((unsigned)c.ceilClip << 8) | (unsigned)c.floorClip;
+    }
     /* sprite silhouettes (engine.py:12940-12964) */
     if (it.rasterValid) {
       bool masked = it.tex[0] >= 0;
@@ -2294,6 +2388,10 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
       if (tid == 0) sh.misc[1] = 0;
       __syncthreads();
     }
+    if (sc.M > 0) {
+      gd_masked_pass(sc, v, sh);
+      __syncthreads();
+    }
     GD_BEAT(5);
     gd_sprites(sc, v, sh, events, eventCount, nThings);
     __syncthreads();
@@ -2469,6 +2567,8 @@ extern "C" int gd_renderer_create(const void *blob_header_host, const void *blob
   sc.fineSine = SECP(int32_t, GD_S_FINESINE); sc.fineTan = SECP(int32_t, GD_S_FINETAN);
   sc.rayOffsets = SECP(float, GD_S_RAY_OFFSETS); sc.rayCosCorr = SECP(float, GD_S_RAY_COSCORR);
   sc.secBBox = SECP(float, GD_S_SECTOR_BBOX);
+  sc.maskedWalls = SECP(int32_t, GD_S_MASKED_WALLS);
+  sc.M = h[GD_H_MASKED_WALLS_N];
 #undef SECP
   r->smemBytes = gd_shared_bytes(sc.W, max_things);
   r->secWallsN = h[GD_H_SEC_WALLS_N]; r->vtxWallsN = h[GD_H_VTX_WALLS_N]; r->V = h[GD_H_VERTICES];

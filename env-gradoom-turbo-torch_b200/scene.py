@@ -116,6 +116,7 @@ class GridSpec:
     light_lo: int = 96
     light_hi: int = 255          # lights uniform in {96, 112, ..., <=255}
     diagonals: bool = False      # one self-referencing diagonal line per room
+    mid_textures: float = 0.0    # share of two-sided lines that carry a masked middle texture
     sprite_patches: int = 96
     spr_w: int = 41
     spr_h: int = 57
@@ -134,6 +135,10 @@ GRID_CONFIGS = {
                    floor_max=128),
     "c4": GridSpec(rows=16, cols=16, room=128.0, seed=4, wall_textures=64,
                    tex_w=128, tex_h=128, flats=8, floor_max=128, diagonals=True),
+    # not a benchmark configuration: c1's shape with masked middle textures on half of the
+    # two-sided lines, for the parity tests of that part of the renderer
+    "c1m": GridSpec(rows=4, cols=4, room=256.0, seed=5, wall_textures=8, flats=4,
+                    floor_max=64, mid_textures=0.5),
 }
 
 
@@ -227,6 +232,16 @@ def make_grid_scene(spec: GridSpec) -> Scene:
             side_textures[w, :, 1] = rng.integers(0, T, size=2)
             side_textures[w, :, 2] = rng.integers(0, T, size=2)
         side_offsets[w] = rng.integers(0, 64, size=(2, 2)).astype(np.float32)
+
+    if spec.mid_textures > 0:
+        # drawn from a generator of their own so the other tables of a seed do not move
+        mid_rng = np.random.default_rng(spec.seed + 1000)
+        for w in range(W):
+            if self_ref[w] or wall_sectors[w, 1] < 0:
+                continue
+            for side in range(2):
+                if mid_rng.random() < spec.mid_textures:
+                    side_textures[w, side, 0] = mid_rng.integers(0, T)
 
     sector_heights = np.stack(
         (
@@ -398,14 +413,14 @@ def make_grid_scene(spec: GridSpec) -> Scene:
 # ---------------------------------------------------------------------------
 
 GD_MAGIC = 0x4744424C
-GD_VERSION = 6
+GD_VERSION = 7
 GD_HDR_WORDS = 128
 GD_HDR_SECTION0 = 48
 
 _HEADER_WORDS = (
     "MAGIC VERSION BYTES WALLS SECTORS VERTICES TEXTURES TEX_H TEX_W SPRITES SPR_H SPR_W "
     "WPN_PATCHES WPN_H WPN_W WPN_TICS STARTS DEATH_FRAMES XDEATH_FRAMES BLOCKING NB_DIRECT "
-    "WPN_AVAILABLE HUD_PATCHES UNSUPPORTED SEC_WALLS_N VTX_WALLS_N"
+    "WPN_AVAILABLE HUD_PATCHES UNSUPPORTED SEC_WALLS_N VTX_WALLS_N MASKED_WALLS_N"
 ).split()
 H = {name: i for i, name in enumerate(_HEADER_WORDS)}
 
@@ -417,7 +432,8 @@ _SECTIONS = (
     "XDEATH_IDS XDEATH_COUNTS XDEATH_ENDS PROJ_FLIGHT PROJ_EXPL_IDS PROJ_EXPL_COUNTS "
     "PROJ_EXPL_ENDS PROJ_EXPL_TOTAL FOG_IDS PUFF_IDS STATIC_IDS ADD_LUT TRANS_LUT WPN_INFO "
     "WPN_ATLAS WPN_OPAQUE WPN_FRAME_IDS WPN_FLASH_IDS WPN_FLASH_LIGHTS HUD_INFO HUD_ATLAS "
-    "HUD_OPAQUE FINESINE FINETAN STARTS RAY_OFFSETS RAY_COSCORR TEX_ATLAS_COL SECTOR_BBOX"
+    "HUD_OPAQUE FINESINE FINETAN STARTS RAY_OFFSETS RAY_COSCORR TEX_ATLAS_COL SECTOR_BBOX "
+    "MASKED_WALLS"
 ).split()
 SEC = {name: i for i, name in enumerate(_SECTIONS)}
 
@@ -505,8 +521,8 @@ def pack_scene(scene: Scene, ray_table_override=None) -> np.ndarray:
     W, S = len(walls), scene.num_sectors
     one_sided = sectors[:, 1] < 0
     unsupported = 0
-    if np.any((~one_sided) & (scene.side_textures[:, :, 0].max(axis=1) >= 0)):
-        unsupported |= 1  # two-sided middle (masked) textures are not drawn
+    # two-sided lines with a middle (masked) texture on either side, ascending
+    masked_walls = np.flatnonzero((~one_sided) & (scene.side_textures[:, :, 0].max(axis=1) >= 0)).astype(np.int32)
 
     dx = walls[:, 2] - walls[:, 0]
     dy = walls[:, 3] - walls[:, 1]
@@ -684,6 +700,7 @@ def pack_scene(scene: Scene, ray_table_override=None) -> np.ndarray:
         "RAY_COSCORR": np.asarray(ray_coscorr, dtype=np.float32),
         "TEX_ATLAS_COL": np.ascontiguousarray(scene.tex_atlas.astype(np.uint8).transpose(0, 2, 1)),
         "SECTOR_BBOX": bbox,
+        "MASKED_WALLS": masked_walls if masked_walls.size else np.zeros(1, dtype=np.int32),
     }
     assert set(sections) == set(SEC), set(SEC) ^ set(sections)
 
@@ -730,6 +747,7 @@ def pack_scene(scene: Scene, ray_table_override=None) -> np.ndarray:
     header[H["UNSUPPORTED"]] = unsupported
     header[H["SEC_WALLS_N"]] = int(sec_off[-1])
     header[H["VTX_WALLS_N"]] = int(vtx_off[-1])
+    header[H["MASKED_WALLS_N"]] = int(masked_walls.size)
     blob = np.concatenate([header.view(np.uint8)] + chunks)
     assert blob.size == cursor
     return blob

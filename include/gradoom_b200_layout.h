@@ -14,7 +14,7 @@
 #include <stdint.h>
 
 #define GD_MAGIC 0x4744424C /* "GDBL" */
-#define GD_VERSION 6
+#define GD_VERSION 7
 #define GD_HDR_WORDS 128
 #define GD_HDR_SECTION0 48
 
@@ -53,6 +53,7 @@ enum gd_header_word {
   GD_H_UNSUPPORTED,  /* nonzero: scene uses a feature outside this path */
   GD_H_SEC_WALLS_N,  /* entries of GD_S_SEC_WALLS */
   GD_H_VTX_WALLS_N,  /* entries of GD_S_VTX_WALLS */
+  GD_H_MASKED_WALLS_N, /* entries of GD_S_MASKED_WALLS */
   GD_H_COUNT
 };
 
@@ -122,6 +123,7 @@ enum gd_section {
   GD_S_RAY_COSCORR,   /* 320 f32: cos of the ray offsets */
   GD_S_TEX_ATLAS_COL, /* T x W x H u8: the atlas with every texture stored column-major */
   GD_S_SECTOR_BBOX,   /* S x 4 f32: xmin xmax ymin ymax over the sector's polygon edges */
+  GD_S_MASKED_WALLS,  /* i32, ascending: two-sided walls with a middle texture on either side */
   GD_S_COUNT
 };
 

@@ -660,6 +660,11 @@ typedef struct {
   int16_t planeSector[VH * SW];
   uint8_t planeIsFloor[VH * SW];
   SpriteClip clip;
+  /* nearest raster-valid two-sided crossing with a middle texture, per column
+   * (engine.py:11573-11579, 12914-12939) */
+  int maskedWall[SW];
+  i64 maskedCeil[SW], maskedFloor[SW];
+  float maskedDist[SW];
 } LaneBuffers;
 
 static void wall_pass(const Scene *sc, const View *v, const LaneGeom *g, LaneBuffers *lb) {
@@ -691,6 +696,10 @@ static void wall_pass(const Scene *sc, const View *v, const LaneGeom *g, LaneBuf
     }
   }
   for (int x = 0; x < SW; ++x) {
+    lb->maskedWall[x] = -1;
+    lb->maskedCeil[x] = 0;
+    lb->maskedFloor[x] = VH;
+    lb->maskedDist[x] = INFINITY;
     cs[x].cur = startSector;
     cs[x].ceilClip = 0;
     cs[x].floorClip = VH;
@@ -1017,6 +1026,13 @@ static void wall_pass(const Scene *sc, const View *v, const LaneGeom *g, LaneBuf
         int drawsLower = (it->viewFloor < it->otherFloor) && hasLower;
         if (it->rasterValid && !it->oneSided && (drawsUpper || it->markCeil)) c->ceilClip = drawsUpper ? it->cupbot : it->ctop;
         if (it->rasterValid && !it->oneSided && (drawsLower || it->markFloor)) c->floorClip = drawsLower ? it->clowtop : it->cbot;
+        /* masked drawseg snapshot (engine.py:12914-12939) */
+        if (it->rasterValid && !it->oneSided && it->tex[0] >= 0 && it->distance < lb->maskedDist[x]) {
+          lb->maskedCeil[x] = c->ceilClip;
+          lb->maskedFloor[x] = c->floorClip;
+          lb->maskedDist[x] = it->distance;
+          lb->maskedWall[x] = wallIndex;
+        }
         /* sprite silhouettes (engine.py:12940-12964) */
         int masked = it->tex[0] >= 0;
         int bottomSil = !it->oneSided && ((it->viewFloor > it->otherFloor) || (v->viewZ < it->otherFloor) || masked);
@@ -1258,6 +1274,88 @@ static void plane_pass(const Scene *sc, const View *v, LaneBuffers *lb, int *uno
     free(fl);
   }
   if (unownedPixels) *unownedPixels = unowned;
+}
+
+/* Two-sided middle textures, replayed after the planes (engine.py:13424-13745):
+ * per column the nearest projected crossing of a line that carries a middle
+ * texture on the viewer's side, clipped by the drawseg snapshot of the walk. */
+static inline i64 trunc_div(i64 a, i64 b) { return a / b; }
+
+static inline i64 masked_iscale(i64 swall) {
+  i64 s = (swall * FU) >> 18;
+  if (s >= 0 && s < 3) return 3;
+  if (s > -3 && s < 0) return -3;
+  return s;
+}
+
+static void masked_pass(const Scene *sc, const View *v, const LaneGeom *g, LaneBuffers *lb) {
+  const int W = sc->W;
+  for (int x = 0; x < SW; ++x) {
+    float best = INFINITY;
+    int w = -1, side = 0, texId = -1;
+    for (int k = 0; k < W; ++k) {
+      if (sc->wsec[k * 2 + 1] < 0) continue;
+      int sd = g->wv[k].frontFacingF ? 0 : 1;
+      int t = sc->sideTex[(k * 2 + sd) * 3];
+      if (t < 0 || !g->proj[(size_t)x * W + k]) continue;
+      float d = g->dist[(size_t)x * W + k];
+      if (d < best) { best = d; w = k; side = sd; texId = t; }
+    }
+    if (!isfinite(best)) continue;
+    const WallView *wv = &g->wv[w];
+    int front = sc->wsec[w * 2], back = sc->wsec[w * 2 + 1] < 0 ? 0 : sc->wsec[w * 2 + 1];
+    int lightSector = side == 0 ? front : back;
+    float worldTop = fminf(sec_ceil(sc, front), sec_ceil(sc, back));
+    const int32_t *ti = &sc->texInfo[texId * 4];
+    int tw = ti[0], th = ti[1], hbits = ti[3];
+    i64 owallTop = project_rows(v, wv, worldTop, x);
+    i64 owallBottom = project_rows(v, wv, worldTop - (float)th, x);
+    int hasSaved = lb->maskedWall[x] == w;
+    i64 ceilClip = imax(owallTop, hasSaved ? lb->maskedCeil[x] : 0);
+    i64 floorClip = imin(owallBottom, hasSaved ? lb->maskedFloor[x] : VH);
+    const float *soff = &sc->sideOff[(w * 2 + side) * 2];
+    i64 hoff, vstepBase;
+    prep_wall(sc, wv, w, x, &hoff, &vstepBase);
+    i64 repeat = rint_f(sc->wlen[w] * 65536.0f);
+    if (side != 0) hoff = repeat - hoff;
+    if (wv->sl > 0 && hoff < 0) hoff = 0;
+    if (hoff >= repeat) hoff = repeat - 1;
+    i64 u = pymod((hoff + rint_f(soff[0] * 65536.0f)) >> 16, tw);
+    i64 vstep = vstepBase * (1LL << (14 - hbits));
+    i64 texMid = rint_f((worldTop - v->viewZ) * 65536.0f + soff[1] * 65536.0f);
+    /* R_DrawMaskedColumn: post rows from the drawseg's interpolated scale */
+    i64 sLeft = iclamp(wv->sl, 0, SW - 1), sLast = iclamp(wv->sr - 1, 0, SW - 1);
+    i64 dummy, startSwall, endSwall;
+    prep_wall(sc, wv, w, (int)sLeft, &dummy, &startSwall);
+    prep_wall(sc, wv, w, (int)sLast, &dummy, &endSwall);
+    i64 startScale = trunc_div(1LL << 32, masked_iscale(startSwall));
+    i64 endScale = trunc_div(1LL << 32, masked_iscale(endSwall));
+    i64 span = imax(wv->sr - wv->sl, 1);
+    i64 scaleStep = trunc_div(endScale - startScale, span);
+    i64 spriteScale = startScale + wrap_mul(scaleStep, (i64)x - wv->sl);
+    i64 topScreen = v->center - (wrap_mul(texMid, spriteScale) >> 16);
+    i64 postTop = topScreen >> 16;
+    i64 postBottom = ((topScreen + wrap_mul(spriteScale, th) - FU) >> 16) + 1;
+    i64 clippedTop = imax(postTop, ceilClip), clippedBottom = imin(postBottom, floorClip);
+    i64 dcIscale = (vstepBase * FU) >> 18;
+    int initialPost = clippedTop < clippedBottom;
+    i64 fracStart = texMid + wrap_mul(clippedTop, dcIscale) - (wrap_mul(v->center - FU, dcIscale) >> 16);
+    i64 fracEnd = fracStart + wrap_mul(clippedBottom - clippedTop - 1, dcIscale);
+    if (initialPost && clippedBottom < floorClip && fracEnd < (i64)th * FU - dcIscale) clippedBottom += 1;
+    if (!(hasSaved || g->left[(size_t)x * W + w])) continue;
+    const float *wl = &sc->walls[w * 4];
+    int horizontal = fabsf(wl[3] - wl[1]) < 1e-6f, vertical = fabsf(wl[2] - wl[0]) < 1e-6f;
+    i64 light = sec_light(sc, lightSector) + v->flashLight * 16 + (vertical ? 16 : (horizontal ? -16 : 0));
+    i64 vis = wv->visL[side] + ((i64)x - wv->visSl[side]) * wv->visStep[side];
+    int shade = wall_shade(light, vis);
+    for (i64 y = imax(clippedTop, 0); y < imin(clippedBottom, VH); ++y) {
+      i64 screenDelta = y * FU - v->center + FU;
+      i64 frac = shl(texMid, 16 - hbits) + (wrap_mul(vstep, screenDelta) >> 16);
+      i64 tv = (frac & U32MASK) >> (32 - hbits);
+      uint8_t texel = sc->texAtlas[((size_t)texId * sc->texH + tv) * sc->texW + u];
+      lb->frame[y * SW + x] = sc->colormap[shade * 256 + texel];
+    }
+  }
 }
 
 /* point-in-sector for actors (engine.py:9598-9617) */
@@ -1667,6 +1765,7 @@ int gd_oracle_render(const uint8_t *blob, const int32_t *lanes, const gd_thing *
     if (stage_mask & 1) {
       wall_pass(&c->sc, &v, &c->g, c->lb);
       plane_pass(&c->sc, &v, c->lb, &un);
+      masked_pass(&c->sc, &v, &c->g, c->lb);
     } else {
       for (int i = 0; i < VH * SW; ++i) { c->lb->clip.depth[i] = INFINITY; c->lb->clip.wall[i] = -1; }
     }

@@ -2,7 +2,7 @@
 
 Run once on a machine that has the upstream sources:
 
-    python tests/golden/make_golden.py [c1 c2 c4 stack]
+    python tests/golden/make_golden.py [c1 c2 c3 c4 c1m stack]
 
 For each seeded synthetic scene it resets the upstream engine, injects K
 monsters per lane, replays a seeded uniform action stream and, at a few
@@ -40,6 +40,7 @@ PLANS = {
     "c2": ("c2", 2, 12, (0, 16)),
     "c3": ("c3", 2, 12, (0, 10)),
     "c4": ("c4", 1, 32, (0, 3)),
+    "c1m": ("c1m", 4, 4, (0, 12, 30)),
 }
 ACTION_SEED = 20260813
 
@@ -146,7 +147,7 @@ def generate_stack(eng, scn, act):
 
 def main(argv):
     eng, scn, act = refbridge.load_reference()
-    names = argv or ["c1", "c2", "c3", "c4", "stack"]
+    names = argv or ["c1", "c2", "c3", "c4", "c1m", "stack"]
     for name in names:
         if name == "stack":
             generate_stack(eng, scn, act)
