@@ -301,6 +301,29 @@ def run_ours(args):
     e2e_value = world * n * e2e_steps / (float(e2e_ms.item()) / 1000.0)
     renderer.check_status()
 
+    # context: the whole device step through the environment API (state producer + render + the
+    # reset launch of the auto-reset), no host synchronisation between steps
+    from gradoom_b200.env import GraDoomVecEnv
+
+    env = GraDoomVecEnv(sc, n, device=device, max_things=THINGS, producer_seed=2000 + rank)
+    env.reset_device(everyone, lane_ids + 1)
+    api_steps = max(args.steps, 3)
+    for k in range(3):
+        env.step_and_reset_device(actions[k % actions.shape[0]], lane_ids + 7)
+    barrier()
+    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a0.record()
+    for k in range(api_steps):
+        env.step_and_reset_device(actions[k % actions.shape[0]], lane_ids + 11 * (k + 1))
+    a1.record()
+    barrier()
+    api_ms = torch.tensor([a0.elapsed_time(a1)], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(api_ms, op=dist.ReduceOp.MAX)
+    api_value = world * n * api_steps / (float(api_ms.item()) / 1000.0)
+    env.check_status()
+    env.close()
+
     if rank == 0:
         oracle = entry.load_oracle()
         peak, peak_kind = measured_peaks()
@@ -331,6 +354,9 @@ def run_ours(args):
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(host_lanes.numel() * 4
                                                                                  + host_things.numel() * 4),
                     "d2h_bytes_per_step": int(host_obs.numel()), "steps": e2e_steps},
+            "whole_step": {"value": api_value, "unit": UNIT, "steps": api_steps,
+                           "api": "GraDoomVecEnv.step_and_reset_device, device tensors, no host sync",
+                           "producer": "synthetic lane stepper (torch elementwise ops)"},
             "gpu_launches": launches,
             "clocks": clocks,
             "stats_gather": None if gathered is None else list(gathered.shape),
