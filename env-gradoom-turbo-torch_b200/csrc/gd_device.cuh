@@ -60,6 +60,7 @@ struct GdScene {
   const float *rayOffsets, *rayCosCorr;
   const float *secBBox;
   const int32_t *maskedWalls;   /* M two-sided walls that carry a middle texture */
+  const float *damageAlpha;     /* 114: damage count -> red flash alpha */
   int M;
 };
 

@@ -2202,6 +2202,37 @@ __device__ inline const void *gd_stage_copy(uint8_t *&cursor, const void *src, s
   return dst;
 }
 
+/* PLAYPAL of the lane in shared memory, as bytes and as packed 3 x 20-bit
+ * words for the resize: the scene's palette, or its bonus / damage blends when
+ * the lane's flags ask for screen flashes (engine.py:15381-15398; float32,
+ * separately rounded, truncating conversion). */
+__device__ void gd_lane_palette(const GdScene &sc, const GdShared &sh, int flags) {
+  const int i = threadIdx.x;
+  if (i >= 256) return;
+  float bonus = 0.0f, flash = 0.0f;
+  const bool blend = (flags & 4) != 0;
+  if (blend) {
+    int damage = min((flags >> 8) & 0xFF, 113), bonusCount = (flags >> 16) & 0xFF;
+    bonus = fminf((float)bonusCount * 8.0f, 128.0f) / 255.0f;
+    flash = sc.damageAlpha[damage] / 255.0f;
+  }
+  const float gold[3] = {215.0f, 186.0f, 69.0f}, red[3] = {255.0f, 0.0f, 0.0f};
+  unsigned ch[3];
+#pragma unroll
+  for (int c = 0; c < 3; ++c) {
+    unsigned v = sc.playpal[i * 3 + c];
+    if (blend) {
+      float rgb = (float)v * (1.0f - bonus) + gold[c] * bonus;
+      float out = rgb * (1.0f - flash) + red[c] * flash;
+      out = fminf(fmaxf(out, 0.0f), 255.0f);
+      v = (unsigned)out;
+    }
+    ch[c] = v;
+    sh.playpal[i * 3 + c] = (uint8_t)v;
+  }
+  sh.pal64[i] = (unsigned long long)ch[0] | ((unsigned long long)ch[1] << 20) | ((unsigned long long)ch[2] << 40);
+}
+
 /* ---- the kernel ----------------------------------------------------------- */
 extern __shared__ __align__(16) uint8_t gd_smem[];
 
@@ -2247,11 +2278,8 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
   /* tables shared by every lane this CTA draws */
   for (int i = tid; i < 32 * 256 / 4; i += GD_THREADS)
     ((unsigned *)sh.colormap)[i] = ((const unsigned *)sc.colormap)[i];
-  for (int i = tid; i < 768; i += GD_THREADS) sh.playpal[i] = sc.playpal[i];
-  if (tid < 256) {
-    const uint8_t *c = &sc.playpal[tid * 3];
-    sh.pal64[tid] = (unsigned long long)c[0] | ((unsigned long long)c[1] << 20) | ((unsigned long long)c[2] << 40);
-  }
+  gd_lane_palette(sc, sh, 0);
+  bool paletteBlended = false;    /* CTA-uniform: the shared palette holds a lane's screen-flash blend */
   uint8_t *myScratch = p.scratch + (size_t)blockIdx.x * gd_scratch_per_cta(sc.W);
   GdEvent *events = (GdEvent *)myScratch;
   int *eventCount = (int *)(myScratch + GD_SCRATCH_EVENTS_BYTES);
@@ -2292,6 +2320,12 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
     int *pointSector = (int *)sh.hitA;
     if (tid <= 64) pointSector[tid] = 0x7fffffff;
     __syncthreads();
+    {
+      const int laneFlags = sh.lane[GD_L_FLAGS];
+      const bool wantBlend = (laneFlags & 4) != 0;
+      if (wantBlend || paletteBlended) gd_lane_palette(sc, sh, laneFlags);   /* read again after later barriers */
+      paletteBlended = wantBlend;
+    }
     int nThings = sh.lane[GD_L_THINGS];
     if (nThings > p.maxThings || nThings > 64) {
       if (tid == 0) atomicOr(p.status, GD_STATUS_THINGS_OVERFLOW);
@@ -2568,6 +2602,7 @@ extern "C" int gd_renderer_create(const void *blob_header_host, const void *blob
   sc.rayOffsets = SECP(float, GD_S_RAY_OFFSETS); sc.rayCosCorr = SECP(float, GD_S_RAY_COSCORR);
   sc.secBBox = SECP(float, GD_S_SECTOR_BBOX);
   sc.maskedWalls = SECP(int32_t, GD_S_MASKED_WALLS);
+  sc.damageAlpha = SECP(float, GD_S_DAMAGE_ALPHA);
   sc.M = h[GD_H_MASKED_WALLS_N];
 #undef SECP
   r->smemBytes = gd_shared_bytes(sc.W, max_things);

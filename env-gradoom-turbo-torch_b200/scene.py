@@ -413,7 +413,7 @@ def make_grid_scene(spec: GridSpec) -> Scene:
 # ---------------------------------------------------------------------------
 
 GD_MAGIC = 0x4744424C
-GD_VERSION = 7
+GD_VERSION = 8
 GD_HDR_WORDS = 128
 GD_HDR_SECTION0 = 48
 
@@ -433,7 +433,7 @@ _SECTIONS = (
     "PROJ_EXPL_ENDS PROJ_EXPL_TOTAL FOG_IDS PUFF_IDS STATIC_IDS ADD_LUT TRANS_LUT WPN_INFO "
     "WPN_ATLAS WPN_OPAQUE WPN_FRAME_IDS WPN_FLASH_IDS WPN_FLASH_LIGHTS HUD_INFO HUD_ATLAS "
     "HUD_OPAQUE FINESINE FINETAN STARTS RAY_OFFSETS RAY_COSCORR TEX_ATLAS_COL SECTOR_BBOX "
-    "MASKED_WALLS"
+    "MASKED_WALLS DAMAGE_ALPHA"
 ).split()
 SEC = {name: i for i, name in enumerate(_SECTIONS)}
 
@@ -521,6 +521,11 @@ def pack_scene(scene: Scene, ray_table_override=None) -> np.ndarray:
     W, S = len(walls), scene.num_sectors
     one_sided = sectors[:, 1] < 0
     unsupported = 0
+    # red-flash alpha per damage count (src/gradoom/engine.py:2016, 15393); a scene built from an
+    # engine carries the engine's table in meta["damage_alpha"], synthetic scenes use a plain ramp
+    damage_alpha = np.asarray(scene.meta.get("damage_alpha", np.minimum(np.arange(114) * 2.0, 226.0)),
+                              dtype=np.float32)
+    assert damage_alpha.shape == (114,)
     # two-sided lines with a middle (masked) texture on either side, ascending
     masked_walls = np.flatnonzero((~one_sided) & (scene.side_textures[:, :, 0].max(axis=1) >= 0)).astype(np.int32)
 
@@ -701,6 +706,7 @@ def pack_scene(scene: Scene, ray_table_override=None) -> np.ndarray:
         "TEX_ATLAS_COL": np.ascontiguousarray(scene.tex_atlas.astype(np.uint8).transpose(0, 2, 1)),
         "SECTOR_BBOX": bbox,
         "MASKED_WALLS": masked_walls if masked_walls.size else np.zeros(1, dtype=np.int32),
+        "DAMAGE_ALPHA": damage_alpha,
     }
     assert set(sections) == set(SEC), set(SEC) ^ set(sections)
 

@@ -80,6 +80,9 @@ def _u32_as_i32(t: torch.Tensor) -> torch.Tensor:
     return torch.where(t >= (1 << 31), t - (1 << 32), t).to(torch.int32)
 
 
+FLAG_SCREEN_FLASHES = 4
+
+
 def pack_lanes(src, thing_counts: torch.Tensor | None = None) -> torch.Tensor:
     """Build the ``(N, 32) int32`` lane records from engine-shaped tensors."""
 
@@ -94,7 +97,12 @@ def pack_lanes(src, thing_counts: torch.Tensor | None = None) -> torch.Tensor:
     out[:, L_Y_FIXED] = _public_or_retained(src.y, src._y_fixed).to(torch.int32)
     out[:, L_ANGLE_BAM] = _u32_as_i32(view_angle_bam(src.angle, src._angle_bam))
     out[:, L_PITCH_BAM] = src._pitch_bam.to(torch.int32)
-    out[:, L_FLAGS] = src.player_dead.to(torch.int32) | (src.mugshot_ouch.to(torch.int32) << 1)
+    flags = src.player_dead.to(torch.int32) | (src.mugshot_ouch.to(torch.int32) << 1)
+    if getattr(src, "render_screen_flashes", False):
+        # damage / bonus screen blends (src/gradoom/engine.py:15385-15397)
+        flags = (flags | FLAG_SCREEN_FLASHES | (src.damage_count.to(torch.int32).clamp(0, 113) << 8)
+                 | (src.bonus_count.to(torch.int32).clamp(0, 255) << 16))
+    out[:, L_FLAGS] = flags
     out[:, L_EPISODE_TIME] = src.episode_time.to(torch.int32)
     out[:, L_BOB_FIXED] = src._player_bob_fixed.to(torch.int32)
     if thing_counts is not None:

@@ -14,7 +14,7 @@
 #include <stdint.h>
 
 #define GD_MAGIC 0x4744424C /* "GDBL" */
-#define GD_VERSION 7
+#define GD_VERSION 8
 #define GD_HDR_WORDS 128
 #define GD_HDR_SECTION0 48
 
@@ -124,6 +124,7 @@ enum gd_section {
   GD_S_TEX_ATLAS_COL, /* T x W x H u8: the atlas with every texture stored column-major */
   GD_S_SECTOR_BBOX,   /* S x 4 f32: xmin xmax ymin ymax over the sector's polygon edges */
   GD_S_MASKED_WALLS,  /* i32, ascending: two-sided walls with a middle texture on either side */
+  GD_S_DAMAGE_ALPHA,  /* 114 f32: damage count -> red flash alpha (0..255), screen flashes */
   GD_S_COUNT
 };
 
@@ -142,7 +143,8 @@ enum gd_lane_word {
   GD_L_Y_FIXED,        /* i32 16.16 */
   GD_L_ANGLE_BAM,      /* u32 view angle BAM (public value if overridden) */
   GD_L_PITCH_BAM,      /* i32 */
-  GD_L_FLAGS,          /* bit0 player dead, bit1 mugshot ouch */
+  GD_L_FLAGS,          /* bit0 player dead, bit1 mugshot ouch, bit2 screen flashes on;
+                          bits 8-15 damage count (0..113), bits 16-23 bonus count (0..255) */
   GD_L_EPISODE_TIME,   /* i32 */
   GD_L_BOB_FIXED,      /* i32 16.16 */
   GD_L_THINGS,         /* i32 number of thing records of this lane */

@@ -66,6 +66,7 @@ typedef struct {
   const int32_t *secI;
   const int32_t *secOff, *secWalls, *edgeOff, *edgeWalls, *blocking;
   const int32_t *texInfo;
+  const float *damageAlpha;
   const uint8_t *texAtlas, *playpal, *colormap;
   const int32_t *sprInfo;
   const uint8_t *sprAtlas, *sprPost;
@@ -136,6 +137,7 @@ static int scene_open(Scene *sc, const uint8_t *blob) {
   sc->edgeWalls = sec_ptr(blob, GD_S_EDGE_WALLS);
   sc->blocking = sec_ptr(blob, GD_S_BLOCKING);
   sc->texInfo = sec_ptr(blob, GD_S_TEX_INFO);
+  sc->damageAlpha = sec_ptr(blob, GD_S_DAMAGE_ALPHA);
   sc->texAtlas = sec_ptr(blob, GD_S_TEX_ATLAS);
   sc->playpal = sec_ptr(blob, GD_S_PLAYPAL);
   sc->colormap = sec_ptr(blob, GD_S_COLORMAP);
@@ -1690,7 +1692,32 @@ static void hud_pass(const Scene *sc, const int32_t *lane, uint8_t *canvas) {
 
 /* integer 320x240 -> 84x84 area resize and grayscale
  * (src/gradoom/_triton_kernels.py:120-177).  Rows >= srcRows read as black. */
-static void area_resize(const Scene *sc, const uint8_t *indexed, int srcRows, uint8_t *out) {
+/* PLAYPAL of one lane: the plain palette, or its bonus / damage blends when the
+ * lane asks for screen flashes (engine.py:15381-15398; float32, separately
+ * rounded operations, truncating conversion). */
+static void lane_palette(const Scene *sc, const int32_t *lane, uint8_t *pal) {
+  memcpy(pal, sc->playpal, 768);
+  int flags = lane ? lane[GD_L_FLAGS] : 0;
+  if (!(flags & 4)) return;
+  int damage = (flags >> 8) & 0xFF, bonusCount = (flags >> 16) & 0xFF;
+  if (damage > 113) damage = 113;
+  float bonus = fminf((float)bonusCount * 8.0f, 128.0f) / 255.0f;
+  float flash = sc->damageAlpha[damage] / 255.0f;
+  static const float gold[3] = {215.0f, 186.0f, 69.0f}, red[3] = {255.0f, 0.0f, 0.0f};
+  for (int i = 0; i < 256; ++i)
+    for (int c = 0; c < 3; ++c) {
+      float a = (float)sc->playpal[i * 3 + c] * (1.0f - bonus);
+      float b = gold[c] * bonus;
+      float rgb = a + b;
+      float d = rgb * (1.0f - flash);
+      float e = red[c] * flash;
+      float out = d + e;
+      out = out < 0.0f ? 0.0f : (out > 255.0f ? 255.0f : out);
+      pal[i * 3 + c] = (uint8_t)out;
+    }
+}
+
+static void area_resize(const uint8_t *playpal, const uint8_t *indexed, int srcRows, uint8_t *out) {
   for (int oy = 0; oy < GD_OBS; ++oy)
     for (int ox = 0; ox < GD_OBS; ++ox) {
       int ys = oy * 240, ye = (oy + 1) * 240, xs = ox * 320, xe = (ox + 1) * 320;
@@ -1703,7 +1730,7 @@ static void area_resize(const Scene *sc, const uint8_t *indexed, int srcRows, ui
           if (xo <= 0) continue;
           int wgt = (yo * xo) / 48;
           if (sy >= srcRows) continue;
-          const uint8_t *rgb = &sc->playpal[indexed[sy * SW + sx] * 3];
+          const uint8_t *rgb = &playpal[indexed[sy * SW + sx] * 3];
           sum[0] += rgb[0] * wgt; sum[1] += rgb[1] * wgt; sum[2] += rgb[2] * wgt;
         }
       }
@@ -1783,19 +1810,28 @@ int gd_oracle_render(const uint8_t *blob, const int32_t *lanes, const gd_thing *
     if (stage_mask & 8) hud_pass(&c->sc, lane, full + (size_t)VH * SW);
     else memset(full + (size_t)VH * SW, 0, (size_t)GD_HUD_H * SW);
     if (indexed) memcpy(&indexed[(size_t)l * GD_SCREEN_H * SW], full, (size_t)GD_SCREEN_H * SW);
-    if (obs) area_resize(&c->sc, full, mask_hud ? VH : GD_SCREEN_H, &obs[(size_t)l * GD_OBS * GD_OBS]);
+    if (obs) {
+      uint8_t pal[768];
+      lane_palette(&c->sc, lane, pal);
+      area_resize(pal, full, mask_hud ? VH : GD_SCREEN_H, &obs[(size_t)l * GD_OBS * GD_OBS]);
+    }
   }
   free(full);
   ctx_free(c);
   return 0;
 }
 
-/* PLAYPAL expansion of an indexed frame (engine.py:15381-15384). */
-int gd_oracle_rgb(const uint8_t *blob, const uint8_t *indexed, int n, int rows, uint8_t *rgb) {
+/* PLAYPAL expansion of indexed frames (engine.py:15381-15398); `lanes` (n x 32
+ * words, may be NULL) supplies the per-lane screen-flash state. */
+int gd_oracle_rgb(const uint8_t *blob, const int32_t *lanes, const uint8_t *indexed, int n, int rows, uint8_t *rgb) {
   Scene sc;
   if (scene_open(&sc, blob) != 0) return -1;
-  size_t count = (size_t)n * rows * SW;
-  for (size_t i = 0; i < count; ++i) memcpy(&rgb[i * 3], &sc.playpal[indexed[i] * 3], 3);
+  for (int l = 0; l < n; ++l) {
+    uint8_t pal[768];
+    lane_palette(&sc, lanes ? &lanes[(size_t)l * GD_LANE_WORDS] : NULL, pal);
+    size_t count = (size_t)rows * SW, base = (size_t)l * count;
+    for (size_t i = 0; i < count; ++i) memcpy(&rgb[(base + i) * 3], &pal[indexed[base + i] * 3], 3);
+  }
   return 0;
 }
 
@@ -1804,7 +1840,7 @@ int gd_oracle_resize(const uint8_t *blob, const uint8_t *indexed, int n, int row
   Scene sc;
   if (scene_open(&sc, blob) != 0) return -1;
   for (int l = 0; l < n; ++l)
-    area_resize(&sc, &indexed[(size_t)l * rows * SW], rows, &obs[(size_t)l * GD_OBS * GD_OBS]);
+    area_resize(sc.playpal, &indexed[(size_t)l * rows * SW], rows, &obs[(size_t)l * GD_OBS * GD_OBS]);
   return 0;
 }
 

@@ -93,12 +93,16 @@ def resize(blob, indexed):
     return obs
 
 
-def rgb(blob, indexed):
+def rgb(blob, indexed, lanes=None):
+    """PLAYPAL expansion; ``lanes`` carries the per-lane screen-flash state."""
+
     blob = np.ascontiguousarray(blob, dtype=np.uint8)
     indexed = np.ascontiguousarray(indexed, dtype=np.uint8)
+    if lanes is not None:
+        lanes = np.ascontiguousarray(lanes, dtype=np.int32)
     n, rows = indexed.shape[0], indexed.shape[1]
     out = np.zeros((n, rows, 320, 3), dtype=np.uint8)
-    lib().gd_oracle_rgb(_ptr(blob), _ptr(indexed), ctypes.c_int(n), ctypes.c_int(rows), _ptr(out))
+    lib().gd_oracle_rgb(_ptr(blob), _ptr(lanes), _ptr(indexed), ctypes.c_int(n), ctypes.c_int(rows), _ptr(out))
     return out
 
 

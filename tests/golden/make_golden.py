@@ -2,7 +2,7 @@
 
 Run once on a machine that has the upstream sources:
 
-    python tests/golden/make_golden.py [c1 c2 c3 c4 c1m stack]
+    python tests/golden/make_golden.py [c1 c2 c3 c4 c1m stack flashes]
 
 For each seeded synthetic scene it resets the upstream engine, injects K
 monsters per lane, replays a seeded uniform action stream and, at a few
@@ -53,9 +53,10 @@ def action_matrix(act):
     return am
 
 
-def make_engine(eng, scn, sc, n, k, seed):
+def make_engine(eng, scn, sc, n, k, seed, flashes=False):
     cs = refbridge.scene_to_compiled(sc, scn)
-    e = eng.TorchDeathmatchEngine(cs, n, device=torch.device("cpu"), mask_hud=True)
+    e = eng.TorchDeathmatchEngine(cs, n, device=torch.device("cpu"), mask_hud=True,
+                                  render_screen_flashes=flashes)
     e.render_frame = e.render_reference_frame
     e.reset(torch.ones(n, dtype=torch.bool), torch.arange(n) + 1)
     g = torch.Generator().manual_seed(seed)
@@ -145,12 +146,44 @@ def generate_stack(eng, scn, act):
     print("stack fixture done", flush=True)
 
 
+def generate_flashes(eng, scn, act):
+    """c1 with the damage / bonus screen blends switched on (engine.py:15385-15397):
+    inputs, the blended RGB24 frame and the observation derived from it."""
+
+    n, k = 4, 4
+    sc = gdscene.make_grid_scene(gdscene.GRID_CONFIGS["c1"])
+    e, g = make_engine(eng, scn, sc, n, k, seed=4321, flashes=True)
+    tab = gdstate.SpriteTables(sc, torch.device("cpu"))
+    am = action_matrix(act)
+    ag = torch.Generator().manual_seed(ACTION_SEED + 2)
+    for _ in range(6):
+        e.step(am[torch.randint(0, 17, (n,), generator=ag)])
+    offsets, coscorr = gdscene.ray_tables()
+    out = {"config": np.asarray("c1"), "ray_offsets": offsets, "ray_coscorr": coscorr,
+           "damage_alpha": e._damage_to_alpha.numpy().astype(np.float32)}
+    cases = [((0, 0, 0, 0), (0, 0, 0, 0)), ((7, 40, 100, 113), (0, 3, 6, 20)), ((1, 0, 63, 30), (16, 1, 0, 9))]
+    for ci, (damage, bonus) in enumerate(cases):
+        e.damage_count.copy_(torch.tensor(damage, dtype=torch.int32))
+        e.bonus_count.copy_(torch.tensor(bonus, dtype=torch.int32))
+        things, counts = gdstate.gather_things(e, tab, max_things=64)
+        lanes = gdstate.pack_lanes(e, counts)
+        used = max(int(counts.max()), 1)
+        out[f"lanes_{ci}"] = lanes.numpy()
+        out[f"things_{ci}"] = things.numpy()[:, :used].copy()
+        out[f"rgb_{ci}"] = e.render_native_frame(include_hud=True).numpy()
+        out[f"obs_float_{ci}"] = e.render_reference_frame().numpy()
+    np.savez_compressed(os.path.join(HERE, "golden_flashes.npz"), **out)
+    print("flash fixture done", flush=True)
+
+
 def main(argv):
     eng, scn, act = refbridge.load_reference()
-    names = argv or ["c1", "c2", "c3", "c4", "c1m", "stack"]
+    names = argv or ["c1", "c2", "c3", "c4", "c1m", "stack", "flashes"]
     for name in names:
         if name == "stack":
             generate_stack(eng, scn, act)
+        elif name == "flashes":
+            generate_flashes(eng, scn, act)
         else:
             generate(name, eng, scn, act)
 

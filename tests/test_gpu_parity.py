@@ -319,3 +319,38 @@ def test_host_buffer_step_matches_device_step(pkg, scenes, pinned):
     r.check_status()
     assert torch.equal(expect, got)
     assert torch.equal(host_obs, expect[:, 3].cpu())
+
+
+@pytest.mark.gpu
+def test_screen_flashes_blend_rgb_and_observation(pkg, oracle):
+    """Lanes that ask for the damage / bonus screen blends (engine.py:15385-15397):
+    RGB24 bit-exact against the upstream fixture, observation equal to the oracle's
+    and within 1 LSB of the upstream float path; plain lanes drawn afterwards by
+    the same CTAs get the plain palette back."""
+
+    import torch
+
+    from gradoom_b200 import scene as gdscene
+
+    data = load_golden("flashes")
+    sc = gdscene.make_grid_scene(gdscene.GRID_CONFIGS["c1"])
+    sc.meta["damage_alpha"] = data["damage_alpha"]
+    blob = gdscene.pack_scene(sc, ray_table_override=(data["ray_offsets"], data["ray_coscorr"]))
+    k = max(data[f"things_{ci}"].shape[1] for ci in range(3))
+    r = _renderer(blob, k)
+    for ci in range(3):
+        lanes, things = data[f"lanes_{ci}"], pad_things(data[f"things_{ci}"], k)
+        expected = oracle.render(blob, lanes, things, mask_hud=True)
+        obs, _, rgb = r.frames(_dev(lanes), _dev(things), obs=True, rgb=True)
+        r.check_status()
+        assert np.array_equal(rgb.cpu().numpy(), data[f"rgb_{ci}"])
+        assert np.array_equal(obs.cpu().numpy(), expected["obs"])
+        assert np.abs(obs.cpu().numpy().astype(int) - data[f"obs_float_{ci}"].astype(int)).max() <= 1
+    # blended and plain lanes interleaved in one launch
+    lanes = np.concatenate([data["lanes_2"], data["lanes_2"]])
+    lanes[4:, 8] &= 3
+    things = np.concatenate([pad_things(data["things_2"], k)] * 2)
+    order = np.array([0, 4, 1, 5, 2, 6, 3, 7] * 40)
+    _, _, rgb = r.frames(_dev(lanes[order]), _dev(things[order]), rgb=True)
+    want = oracle.rgb(blob, oracle.render(blob, lanes, things)["indexed"], lanes)[order]
+    assert np.array_equal(rgb.cpu().numpy(), want)

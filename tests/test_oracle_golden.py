@@ -118,3 +118,26 @@ def test_fallback_layer_is_deterministic_and_total(pkg, oracle, scenes):
     lanes, _ = stepper.random_lanes(sc, 2, 0, seed=5)
     a, b = oracle.flats(blob, lanes), oracle.flats(blob, lanes)
     assert a.shape == (2, 208, 320) and np.array_equal(a, b)
+
+
+def _flash_scene(pkg, data):
+    from gradoom_b200 import scene as gdscene
+
+    sc = gdscene.make_grid_scene(gdscene.GRID_CONFIGS["c1"])
+    sc.meta["damage_alpha"] = data["damage_alpha"]
+    return gdscene.pack_scene(sc, ray_table_override=(data["ray_offsets"], data["ray_coscorr"]))
+
+
+def test_oracle_screen_flashes_match_upstream_rgb(pkg, oracle):
+    """Damage / bonus blends (engine.py:15385-15397): blended RGB24 bit-exact, the
+    observation derived from it within 1 LSB of the upstream float path."""
+
+    data = load_golden("flashes")
+    blob = _flash_scene(pkg, data)
+    for ci in range(3):
+        lanes, things = data[f"lanes_{ci}"], data[f"things_{ci}"]
+        out = oracle.render(blob, lanes, things, mask_hud=True)
+        assert np.array_equal(oracle.rgb(blob, out["indexed"], lanes), data[f"rgb_{ci}"])
+        assert np.abs(out["obs"].astype(int) - data[f"obs_float_{ci}"].astype(int)).max() <= 1
+    plain = oracle.rgb(blob, out["indexed"])
+    assert not np.array_equal(plain, data["rgb_2"]), "the last case blends every lane"
