@@ -267,7 +267,11 @@ def run_ours(args):
     renderer.check_status()
     clocks = sampler.stop(wall0, wall1)
     elapsed_ms = torch.tensor([sum(kernel_ms)], dtype=torch.float64, device=device)
+    per_rank_ms = [float(elapsed_ms.item()) / args.steps]
     if world > 1:
+        every = [torch.zeros_like(elapsed_ms) for _ in range(world)]
+        dist.all_gather(every, elapsed_ms)
+        per_rank_ms = [float(t.item()) / args.steps for t in every]
         dist.all_reduce(elapsed_ms, op=dist.ReduceOp.MAX)
     total_ms = float(elapsed_ms.item())
     value = world * n * args.steps / (total_ms / 1000.0)
@@ -357,6 +361,7 @@ def run_ours(args):
             "whole_step": {"value": api_value, "unit": UNIT, "steps": api_steps,
                            "api": "GraDoomVecEnv.step_and_reset_device, device tensors, no host sync",
                            "producer": "synthetic lane stepper (torch elementwise ops)"},
+            "per_rank_ms_per_step": per_rank_ms, "host_cores": len(os.sched_getaffinity(0)),
             "gpu_launches": launches,
             "clocks": clocks,
             "stats_gather": None if gathered is None else list(gathered.shape),

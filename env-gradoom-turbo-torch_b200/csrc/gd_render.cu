@@ -56,7 +56,8 @@ struct GdParams {
 };
 
 #define GD_SCRATCH_EVENTS_BYTES (GD_MAX_EVENTS * GD_SW * (int)sizeof(GdEvent))
-#define GD_SCRATCH_FIXED (GD_SCRATCH_EVENTS_BYTES + GD_SW * 4)
+#define GD_SCRATCH_VSEC_BYTES (GD_VH * GD_SW * 2)   /* flat fallback: vertically repaired sector per pixel */
+#define GD_SCRATCH_FIXED (GD_SCRATCH_EVENTS_BYTES + GD_SW * 4 + GD_SCRATCH_VSEC_BYTES)
 __host__ __device__ inline size_t gd_scratch_per_cta(int W) {
   return (GD_SCRATCH_FIXED + (size_t)W * 4 * sizeof(GdRowProj) + 15) & ~(size_t)15;
 }
@@ -1696,56 +1697,25 @@ __device__ __noinline__ GdFlatProbe gd_flat_probe(const GdScene &sc, const GdVie
   return out;
 }
 
-/* Sector of pixel (x,y) after the vertical repair, computed by a whole warp
- * (32 rows per step); `anchor` tells whether the pixel anchors horizontal
- * spans.  Every lane passes the same arguments and gets the same result. */
-__device__ int gd_flat_vertical_warp(const GdScene &sc, const GdView &v, const GdFlatBounds &b, int x, int y,
-                                     int currentSector, bool &anchor, bool &unresolved, bool &isFloor) {
-  const int lane = threadIdx.x & 31;
-  const GdFlatRay r = gd_flat_ray(sc, v, x);
-  GdFlatProbe own = gd_flat_probe(sc, v, r, b, y, currentSector);
-  unresolved = own.unresolved;
-  isFloor = own.isFloor;
-  anchor = !own.unresolved;
-  int sector = own.sector;
-  if (!own.unresolved) return sector;
-  for (int base = y + 1; base < GD_VH; base += 32) {
-    int yy = base + lane;
-    bool valid = yy < GD_VH;
-    GdFlatProbe q;
-    q.unresolved = true; q.isFloor = isFloor; q.sector = 0;
-    if (valid) q = gd_flat_probe(sc, v, r, b, yy, currentSector);
-    unsigned flip = __ballot_sync(0xffffffffu, valid && q.isFloor != isFloor);
-    unsigned hit = __ballot_sync(0xffffffffu, valid && q.isFloor == isFloor && !q.unresolved);
-    /* the orientation flips once, at the view centre: only rows before it count */
-    if (flip) hit &= (1u << (__ffs(flip) - 1)) - 1u;
-    int found = __shfl_sync(0xffffffffu, q.sector, hit ? __ffs(hit) - 1 : 0);
-    if (hit) {
-      anchor = found != currentSector;
-      return found;
-    }
-    if (flip) break;
-  }
-  return sector;
-}
-
 /* Pass over the queued pixels.
  *   A  one thread per queued pixel probes it; a resolved pixel is drawn at
  *      once and leaves the queue.
- *   B  only when unresolved pixels remain, in rows minY..maxY: one thread per
- *      column first looks below maxY for the nearest resolved row, then sweeps
- *      maxY..minY bottom-up carrying the nearest resolved row below, and
- *      records in a bit per pixel whether the vertically repaired pixel is an
- *      anchor.
- *   C  one warp per remaining pixel: nearest anchors left and right in the
- *      pixel's row from those bits, their sectors by a vertical repair each. */
-__device__ void gd_fallback_pass(const GdScene &sc, const GdView &v, const GdShared &sh, int currentSector) {
+ *   B  only when unresolved pixels remain, once per lane: over the rows of
+ *      every pixel that is still unclaimed, one thread per column first looks
+ *      below the last of those rows for the nearest resolved row, then sweeps
+ *      the rows bottom-up carrying the nearest resolved row below.  It writes
+ *      the vertically repaired sector of every pixel of those rows to `vsec`
+ *      and one bit per pixel telling whether it anchors horizontal spans.
+ *   C  one thread per remaining queued pixel: its own repaired sector, or the
+ *      one its nearest anchors left and right agree on. */
+__device__ void gd_fallback_pass(const GdScene &sc, const GdView &v, const GdShared &sh, int currentSector,
+                                 unsigned short *vsec, bool &sweepDone) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int count = min(sh.misc[1], GD_FALLBACK_MAX);
   int *queue = (int *)sh.hitD;
   unsigned *anchors = (unsigned *)sh.hitA;           /* [row][GD_WARPS] column bits */
   unsigned *owned = sh.masks + 7 * GD_SW;            /* drawn pixels are marked owned */
-  if (tid == 0) { sh.misc[2] = GD_VH; sh.misc[3] = -1; }
+  if (tid == 0) { sh.misc[2] = GD_VH; sh.misc[3] = -1; sh.misc[11] = 0; }
   if (warp == 0) gd_flat_bounds_setup(sc, v, sh.misc);
   __syncthreads();
   const GdFlatBounds b = gd_flat_bounds_load(sh.misc);
@@ -1760,46 +1730,64 @@ __device__ void gd_fallback_pass(const GdScene &sc, const GdView &v, const GdSha
       atomicOr(&owned[(py >> 5) * GD_SW + px], 1u << (py & 31));
       queue[i] = -1;
     } else {
-      atomicMin(&sh.misc[2], py);
-      atomicMax(&sh.misc[3], py);
+      sh.misc[11] = 1;
     }
   }
   __syncthreads();
-  const int minY = sh.misc[2], maxY = sh.misc[3];
-  if (maxY < 0) return;                               /* block-uniform */
-  {
+  if (sh.misc[11] == 0) return;                       /* block-uniform: nothing unresolved */
+  if (!sweepDone) {
+    {
+      const unsigned *filled = sh.masks + tid, *own = owned + tid;
+      int lo = GD_VH, hi = -1;
+      for (int k = 0; k < 7; ++k) {
+        unsigned m = gd_range_word(k, 0, GD_VH) & ~filled[k * GD_SW] & ~own[k * GD_SW];
+        if (m) { lo = min(lo, (k << 5) + __ffs(m) - 1); hi = max(hi, (k << 5) + 31 - __clz(m)); }
+      }
+      if (hi >= 0) { atomicMin(&sh.misc[2], lo); atomicMax(&sh.misc[3], hi); }
+    }
+    __syncthreads();
+    const int minY = sh.misc[2], maxY = sh.misc[3];
     const GdFlatRay r = gd_flat_ray(sc, v, tid);
     const int flipRow = gd_clamp((int)floorf(r.center) + 1, 0, GD_VH);   /* first floor row */
     /* nearest resolved row below maxY, of maxY's orientation */
     bool haveBelow = false, belowFloor = false;
     int belowSector = 0;
     const int limit = maxY < flipRow ? flipRow : GD_VH;
+#pragma unroll 1
     for (int y = maxY + 1; y < limit; ++y) {
       GdFlatProbe q = gd_flat_probe(sc, v, r, b, y, currentSector);
       if (!q.unresolved) { haveBelow = true; belowFloor = q.isFloor; belowSector = q.sector; break; }
     }
     __syncwarp();
+#pragma unroll 1
     for (int y = maxY; y >= minY; --y) {
       GdFlatProbe q = gd_flat_probe(sc, v, r, b, y, currentSector);
       bool anchor;
+      int repaired;
       if (!q.unresolved) {
         anchor = true;
+        repaired = q.sector;
         haveBelow = true; belowFloor = q.isFloor; belowSector = q.sector;
       } else {
-        anchor = haveBelow && belowFloor == q.isFloor && belowSector != currentSector;
+        bool spans = haveBelow && belowFloor == q.isFloor;
+        repaired = spans ? belowSector : currentSector;
+        anchor = spans && belowSector != currentSector;
       }
+      vsec[y * GD_SW + tid] = (unsigned short)repaired;
       unsigned m = __ballot_sync(0xffffffffu, anchor);
       if (lane == 0) anchors[y * GD_WARPS + warp] = m;
     }
+    sweepDone = true;
+    __threadfence_block();
+    __syncthreads();
   }
-  __syncthreads();
-  for (int i = warp; i < count; i += GD_WARPS) {
-    if (queue[i] < 0) continue;                       /* warp-uniform */
+  for (int i = tid; i < count; i += GD_THREADS) {
+    if (queue[i] < 0) continue;
     const int px = queue[i] & 0xFFFF, py = queue[i] >> 16;
-    bool anchor, unresolved, isFloor;
-    int sector = gd_flat_vertical_warp(sc, v, b, px, py, currentSector, anchor, unresolved, isFloor);
+    int sector = vsec[py * GD_SW + px];
     /* nearest anchor at or left of px, at or right of px */
     int left = -1, right = -1;
+#pragma unroll 1
     for (int w = 0; w < GD_WARPS; ++w) {
       unsigned bits = anchors[py * GD_WARPS + w];
       int base = w * 32;
@@ -1813,17 +1801,14 @@ __device__ void gd_fallback_pass(const GdScene &sc, const GdView &v, const GdSha
       }
     }
     if (left >= 0 && right >= 0) {
-      bool a, u, f;
-      int sl = left == px ? sector : gd_flat_vertical_warp(sc, v, b, left, py, currentSector, a, u, f);
-      int sr = right == px ? sector : gd_flat_vertical_warp(sc, v, b, right, py, currentSector, a, u, f);
+      int sl = vsec[py * GD_SW + left], sr = vsec[py * GD_SW + right];
       if (sl == sr) sector = sl;
     }
-    if (lane == 0) {
-      GdPlaneSpan p;
-      gd_plane_setup(sc, v, sector, isFloor, px, p);
-      sh.frame[py * GD_SW + px] = gd_plane_pixel(p, v, sh.yslope, sh.colormap, py);
-      atomicOr(&owned[(py >> 5) * GD_SW + px], 1u << (py & 31));
-    }
+    const bool isFloor = ((float)py - gd_flat_ray(sc, v, px).center) > 0;
+    GdPlaneSpan p;
+    gd_plane_setup(sc, v, sector, isFloor, px, p);
+    sh.frame[py * GD_SW + px] = gd_plane_pixel(p, v, sh.yslope, sh.colormap, py);
+    atomicOr(&owned[(py >> 5) * GD_SW + px], 1u << (py & 31));
   }
   __syncthreads();
 }
@@ -2283,6 +2268,7 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
   uint8_t *myScratch = p.scratch + (size_t)blockIdx.x * gd_scratch_per_cta(sc.W);
   GdEvent *events = (GdEvent *)myScratch;
   int *eventCount = (int *)(myScratch + GD_SCRATCH_EVENTS_BYTES);
+  unsigned short *vsec = (unsigned short *)(myScratch + GD_SCRATCH_EVENTS_BYTES + GD_SW * 4);
   GdRowProj *rowproj = stagedRowproj ? stagedRowproj : (GdRowProj *)(myScratch + GD_SCRATCH_FIXED);
 
 #ifdef GD_PROFILE_PHASES
@@ -2403,6 +2389,7 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
      * queued (the hit cache is free once every column has finished its walk)
      * and resolved; a frame with more such pixels than the queue holds takes
      * several rounds, each pass marking what it drew as owned. */
+    bool sweepDone = false;                          /* CTA-uniform */
     for (;;) {
       const unsigned *filled = sh.masks + tid, *owned = sh.masks + 7 * GD_SW + tid;
       for (int k = 0; k < 7; ++k) {
@@ -2417,7 +2404,7 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
       __syncthreads();
       const int queued = sh.misc[1];
       if (queued == 0) break;                        /* block-uniform */
-      gd_fallback_pass(sc, v, sh, sh.misc[0]);
+      gd_fallback_pass(sc, v, sh, sh.misc[0], vsec, sweepDone);
       if (queued <= GD_FALLBACK_MAX) break;
       if (tid == 0) sh.misc[1] = 0;
       __syncthreads();
