@@ -61,6 +61,10 @@ struct GdScene {
   const float *secBBox;
   const int32_t *maskedWalls;   /* M two-sided walls that carry a middle texture */
   const float *damageAlpha;     /* 114: damage count -> red flash alpha */
+  /* sectors grouped by floor / ceiling height, nearest plane first */
+  const float *groupH[2];       /* [0] ceilings ascending, [1] floors descending */
+  const int32_t *groupOff[2], *groupSec[2];
+  int groups[2];
   int M;
 };
 

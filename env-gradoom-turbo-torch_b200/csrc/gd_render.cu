@@ -1555,17 +1555,26 @@ __device__ __noinline__ bool gd_pixel_unresolved(const GdScene &sc, const GdView
   bool floorPixel = delta > 0;
   float den = fmaxf(fabsf(delta), 0.5f);
   /* An existence test, so the order is free: `hint` (the sector whose plane
-   * was marked on this pixel) is nearly always the one that answers it. */
+   * was marked on this pixel) is nearly always the one that answers it; the
+   * others are visited by plane height, one plane point per distinct height. */
+  {
+    float ph = floorPixel ? (v.viewZ - sc.secF[hint * 2]) : (sc.secF[hint * 2 + 1] - v.viewZ);
+    float cd = ph * 192.0f / den / cc;
+    if (ph > 0 && isfinite(cd) && cd > 0 && gd_point_in_sector(sc, hint, v.x + rc * cd, v.y + rs * cd)) return false;
+  }
+  const int f = floorPixel ? 1 : 0;
+  const float *gh = sc.groupH[f];
+  const int32_t *goff = sc.groupOff[f], *gsec = sc.groupSec[f];
 #pragma unroll 1
-  for (int k = -1; k < sc.S; ++k) {
-    int s = k < 0 ? hint : k;
-    if (k >= 0 && s == hint) continue;
-    float ph = floorPixel ? (v.viewZ - sc.secF[s * 2]) : (sc.secF[s * 2 + 1] - v.viewZ);
+  for (int g = 0; g < sc.groups[f]; ++g) {
+    float ph = floorPixel ? (v.viewZ - gh[g]) : (gh[g] - v.viewZ);
     float perp = ph * 192.0f / den;
     float cd = perp / cc;
     if (!(ph > 0) || !isfinite(cd) || !(cd > 0)) continue;
     float px = v.x + rc * cd, py = v.y + rs * cd;
-    if (gd_point_in_sector(sc, s, px, py)) return false;
+#pragma unroll 1
+    for (int k = goff[g]; k < goff[g + 1]; ++k)
+      if (gd_point_in_sector(sc, gsec[k], px, py)) return false;
   }
   return true;
 }
@@ -1683,15 +1692,29 @@ __device__ __noinline__ GdFlatProbe gd_flat_probe(const GdScene &sc, const GdVie
       if (r.rs < 0 && py0 < b.yLo) return out;
     }
   }
+  /* Sectors are visited by plane height, nearest plane first, so the distance
+   * along the ray never decreases from group to group: the first group with a
+   * sector that contains its plane point holds the answer, except that a later
+   * group whose distance rounds to the same value may still own it with a lower
+   * sector index (the reference keeps the first index among equal distances). */
   float best = GD_INF;
+  const int f = out.isFloor ? 1 : 0;
+  const float *gh = sc.groupH[f];
+  const int32_t *goff = sc.groupOff[f], *gsec = sc.groupSec[f];
 #pragma unroll 1
-  for (int s = 0; s < sc.S; ++s) {
-    float ph = out.isFloor ? (v.viewZ - sc.secF[s * 2]) : (sc.secF[s * 2 + 1] - v.viewZ);
+  for (int g = 0; g < sc.groups[f]; ++g) {
+    float ph = out.isFloor ? (v.viewZ - gh[g]) : (gh[g] - v.viewZ);
     float perp = ph * 192.0f / den;
     float cd = perp / r.cc;
-    if (!(ph > 0) || !isfinite(cd) || !(cd > 0) || !(cd < best)) continue;
+    if (!(ph > 0) || !isfinite(cd) || !(cd > 0)) continue;
+    if (cd > best) break;
     float px = v.x + r.rc * cd, py = v.y + r.rs * cd;
-    if (gd_point_in_sector(sc, s, px, py)) { best = cd; out.sector = s; }
+#pragma unroll 1
+    for (int k = goff[g]; k < goff[g + 1]; ++k) {
+      int s = gsec[k];
+      if (cd == best && s > out.sector) break;
+      if (gd_point_in_sector(sc, s, px, py)) { best = cd; out.sector = s; break; }
+    }
   }
   out.unresolved = !isfinite(best);
   return out;
@@ -2590,6 +2613,10 @@ extern "C" int gd_renderer_create(const void *blob_header_host, const void *blob
   sc.secBBox = SECP(float, GD_S_SECTOR_BBOX);
   sc.maskedWalls = SECP(int32_t, GD_S_MASKED_WALLS);
   sc.damageAlpha = SECP(float, GD_S_DAMAGE_ALPHA);
+  sc.groupH[1] = SECP(float, GD_S_FLOOR_GROUP_H); sc.groupOff[1] = SECP(int32_t, GD_S_FLOOR_GROUP_OFF);
+  sc.groupSec[1] = SECP(int32_t, GD_S_FLOOR_GROUP_SEC); sc.groups[1] = h[GD_H_FLOOR_GROUPS];
+  sc.groupH[0] = SECP(float, GD_S_CEIL_GROUP_H); sc.groupOff[0] = SECP(int32_t, GD_S_CEIL_GROUP_OFF);
+  sc.groupSec[0] = SECP(int32_t, GD_S_CEIL_GROUP_SEC); sc.groups[0] = h[GD_H_CEIL_GROUPS];
   sc.M = h[GD_H_MASKED_WALLS_N];
 #undef SECP
   r->smemBytes = gd_shared_bytes(sc.W, max_things);

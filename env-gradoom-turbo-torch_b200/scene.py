@@ -413,14 +413,14 @@ def make_grid_scene(spec: GridSpec) -> Scene:
 # ---------------------------------------------------------------------------
 
 GD_MAGIC = 0x4744424C
-GD_VERSION = 8
+GD_VERSION = 9
 GD_HDR_WORDS = 128
 GD_HDR_SECTION0 = 48
 
 _HEADER_WORDS = (
     "MAGIC VERSION BYTES WALLS SECTORS VERTICES TEXTURES TEX_H TEX_W SPRITES SPR_H SPR_W "
     "WPN_PATCHES WPN_H WPN_W WPN_TICS STARTS DEATH_FRAMES XDEATH_FRAMES BLOCKING NB_DIRECT "
-    "WPN_AVAILABLE HUD_PATCHES UNSUPPORTED SEC_WALLS_N VTX_WALLS_N MASKED_WALLS_N"
+    "WPN_AVAILABLE HUD_PATCHES UNSUPPORTED SEC_WALLS_N VTX_WALLS_N MASKED_WALLS_N FLOOR_GROUPS CEIL_GROUPS"
 ).split()
 H = {name: i for i, name in enumerate(_HEADER_WORDS)}
 
@@ -433,7 +433,8 @@ _SECTIONS = (
     "PROJ_EXPL_ENDS PROJ_EXPL_TOTAL FOG_IDS PUFF_IDS STATIC_IDS ADD_LUT TRANS_LUT WPN_INFO "
     "WPN_ATLAS WPN_OPAQUE WPN_FRAME_IDS WPN_FLASH_IDS WPN_FLASH_LIGHTS HUD_INFO HUD_ATLAS "
     "HUD_OPAQUE FINESINE FINETAN STARTS RAY_OFFSETS RAY_COSCORR TEX_ATLAS_COL SECTOR_BBOX "
-    "MASKED_WALLS DAMAGE_ALPHA"
+    "MASKED_WALLS DAMAGE_ALPHA FLOOR_GROUP_H FLOOR_GROUP_OFF FLOOR_GROUP_SEC CEIL_GROUP_H CEIL_GROUP_OFF "
+    "CEIL_GROUP_SEC"
 ).split()
 SEC = {name: i for i, name in enumerate(_SECTIONS)}
 
@@ -521,6 +522,21 @@ def pack_scene(scene: Scene, ray_table_override=None) -> np.ndarray:
     W, S = len(walls), scene.num_sectors
     one_sided = sectors[:, 1] < 0
     unsupported = 0
+
+    def height_groups(values, descending):
+        """Sectors grouped by plane height, nearest plane first for a viewer between
+        the planes: (heights, CSR offsets, sector indices ascending inside a group)."""
+
+        values = np.asarray(values, dtype=np.float32)
+        heights = np.unique(values)
+        if descending:
+            heights = heights[::-1]
+        members = [np.flatnonzero(values == h).astype(np.int32) for h in heights]
+        offsets = np.concatenate(([0], np.cumsum([len(m) for m in members]))).astype(np.int32)
+        return np.ascontiguousarray(heights, dtype=np.float32), offsets, np.concatenate(members).astype(np.int32)
+
+    floor_groups = height_groups(scene.sector_heights[:, 0], descending=True)
+    ceil_groups = height_groups(scene.sector_heights[:, 1], descending=False)
     # red-flash alpha per damage count (src/gradoom/engine.py:2016, 15393); a scene built from an
     # engine carries the engine's table in meta["damage_alpha"], synthetic scenes use a plain ramp
     damage_alpha = np.asarray(scene.meta.get("damage_alpha", np.minimum(np.arange(114) * 2.0, 226.0)),
@@ -707,6 +723,8 @@ def pack_scene(scene: Scene, ray_table_override=None) -> np.ndarray:
         "SECTOR_BBOX": bbox,
         "MASKED_WALLS": masked_walls if masked_walls.size else np.zeros(1, dtype=np.int32),
         "DAMAGE_ALPHA": damage_alpha,
+        "FLOOR_GROUP_H": floor_groups[0], "FLOOR_GROUP_OFF": floor_groups[1], "FLOOR_GROUP_SEC": floor_groups[2],
+        "CEIL_GROUP_H": ceil_groups[0], "CEIL_GROUP_OFF": ceil_groups[1], "CEIL_GROUP_SEC": ceil_groups[2],
     }
     assert set(sections) == set(SEC), set(SEC) ^ set(sections)
 
@@ -754,6 +772,8 @@ def pack_scene(scene: Scene, ray_table_override=None) -> np.ndarray:
     header[H["SEC_WALLS_N"]] = int(sec_off[-1])
     header[H["VTX_WALLS_N"]] = int(vtx_off[-1])
     header[H["MASKED_WALLS_N"]] = int(masked_walls.size)
+    header[H["FLOOR_GROUPS"]] = int(floor_groups[0].size)
+    header[H["CEIL_GROUPS"]] = int(ceil_groups[0].size)
     blob = np.concatenate([header.view(np.uint8)] + chunks)
     assert blob.size == cursor
     return blob

@@ -14,7 +14,7 @@
 #include <stdint.h>
 
 #define GD_MAGIC 0x4744424C /* "GDBL" */
-#define GD_VERSION 8
+#define GD_VERSION 9
 #define GD_HDR_WORDS 128
 #define GD_HDR_SECTION0 48
 
@@ -54,6 +54,8 @@ enum gd_header_word {
   GD_H_SEC_WALLS_N,  /* entries of GD_S_SEC_WALLS */
   GD_H_VTX_WALLS_N,  /* entries of GD_S_VTX_WALLS */
   GD_H_MASKED_WALLS_N, /* entries of GD_S_MASKED_WALLS */
+  GD_H_FLOOR_GROUPS, /* distinct floor heights */
+  GD_H_CEIL_GROUPS,  /* distinct ceiling heights */
   GD_H_COUNT
 };
 
@@ -125,6 +127,12 @@ enum gd_section {
   GD_S_SECTOR_BBOX,   /* S x 4 f32: xmin xmax ymin ymax over the sector's polygon edges */
   GD_S_MASKED_WALLS,  /* i32, ascending: two-sided walls with a middle texture on either side */
   GD_S_DAMAGE_ALPHA,  /* 114 f32: damage count -> red flash alpha (0..255), screen flashes */
+  GD_S_FLOOR_GROUP_H,   /* distinct floor heights, descending (f32) */
+  GD_S_FLOOR_GROUP_OFF, /* groups + 1 i32: CSR offsets into GD_S_FLOOR_GROUP_SEC */
+  GD_S_FLOOR_GROUP_SEC, /* S i32: sectors of each floor height, ascending inside a group */
+  GD_S_CEIL_GROUP_H,    /* distinct ceiling heights, ascending (f32) */
+  GD_S_CEIL_GROUP_OFF,
+  GD_S_CEIL_GROUP_SEC,
   GD_S_COUNT
 };
 
