@@ -146,7 +146,7 @@ int gd_render_step_host(const gd_renderer *r, const int32_t *lanes_host, const v
  * pool is owned and budgeted by the embedding application, or code running
  * after the framework's allocator has been frozen -- and therefore cannot
  * provide the scratch buffer.  The scratch lives in a fixed array inside the
- * library (gd_static_scratch_bytes(), about 12 MB, held by every GPU that loads
+ * library (gd_static_scratch_bytes(), about 16 MB, held by every GPU that loads
  * the library until the process exits); the call allocates and frees nothing.
  * Limits: scenes of at most gd_static_max_walls() walls (more: GD_ERR_STATIC_LIMIT)
  * and at most 32 concurrently drawing CTAs, so it is slower than gd_render_step
