@@ -12,7 +12,12 @@ With N>1 (torchrun, one rank per GPU) every rank owns its own 4096 lanes (weak
 scaling, no collective on the render path; the per-lane statistics are
 all-gathered every 100 steps).
 
-Prints one JSON line; see DESIGN.md for the meaning of every field.
+Prints one JSON line: `value` is whole-job frames/s with inputs resident on the
+device; `e2e` is the same through the host-buffer entry point (host records in,
+newest frames out, stream synchronised every step); `roofline` relates the
+algorithmic bytes of one launch to its measured duration and to the measured
+copy bandwidth of the GPU; `cpu_baseline` times the CPU port on a bounded
+sample; `whole_step` drives the lanes through the environment API for context.
 """
 
 from __future__ import annotations

@@ -2,7 +2,7 @@
 
 Run once on a machine that has the upstream sources:
 
-    python tests/golden/make_golden.py [c1 c2 c3 c4 c1m stack flashes]
+    GRADOOM_REFERENCE_SRC=<upstream checkout>/src/gradoom python tests/golden/make_golden.py [c1 c2 c3 c4 c1m stack flashes]
 
 For each seeded synthetic scene it resets the upstream engine, injects K
 monsters per lane, replays a seeded uniform action stream and, at a few

@@ -16,7 +16,7 @@ import types
 
 import numpy as np
 
-REFERENCE_SRC = os.environ.get("GRADOOM_REFERENCE_SRC", "/root/reference/src/gradoom")
+REFERENCE_SRC = os.environ.get("GRADOOM_REFERENCE_SRC", "")   # <upstream checkout>/src/gradoom
 
 
 def load_reference():
@@ -26,6 +26,8 @@ def load_reference():
     engine module itself only needs numpy and torch.
     """
 
+    if not os.path.isdir(REFERENCE_SRC):
+        raise SystemExit("set GRADOOM_REFERENCE_SRC to the upstream checkout's src/gradoom directory")
     if "gradoom" not in sys.modules:
         pkg = types.ModuleType("gradoom")
         pkg.__path__ = [REFERENCE_SRC]
