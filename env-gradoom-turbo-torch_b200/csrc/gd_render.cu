@@ -58,8 +58,10 @@ struct GdParams {
 #define GD_SCRATCH_EVENTS_BYTES (GD_MAX_EVENTS * GD_SW * (int)sizeof(GdEvent))
 #define GD_SCRATCH_VSEC_BYTES (GD_VH * GD_SW * 2)   /* flat fallback: vertically repaired sector per pixel */
 #define GD_SCRATCH_FIXED (GD_SCRATCH_EVENTS_BYTES + GD_SW * 4 + GD_SCRATCH_VSEC_BYTES)
-__host__ __device__ inline size_t gd_scratch_per_cta(int W) {
-  return (GD_SCRATCH_FIXED + (size_t)W * 4 * sizeof(GdRowProj) + 15) & ~(size_t)15;
+#define GD_PLANE_ENTRY_BYTES 88          /* sizeof(GdPlaneEntry), checked below */
+__host__ __device__ inline size_t gd_scratch_plane_bytes(int S) { return ((size_t)S * 2 * GD_PLANE_ENTRY_BYTES + 15) & ~(size_t)15; }
+__host__ __device__ inline size_t gd_scratch_per_cta(int W, int S) {
+  return (GD_SCRATCH_FIXED + gd_scratch_plane_bytes(S) + (size_t)W * 4 * sizeof(GdRowProj) + 15) & ~(size_t)15;
 }
 
 struct GdActor {
@@ -73,7 +75,10 @@ struct GdActor {
 };
 
 /* ---- shared memory carve-up -------------------------------------------- */
+struct GdPlaneEntry;
+
 struct GdShared {
+  GdPlaneEntry *planeTab; /* scratch: per (sector, floor/ceiling) span setup of the lane being drawn */
   uint8_t *frame;       /* 240 x 320 */
   uint8_t *colormap;    /* 32 x 256 */
   uint8_t *playpal;     /* 768 */
@@ -692,25 +697,52 @@ struct GdPlaneSpan {
   int wbits, hbits, texW;
 };
 
-__device__ void gd_plane_setup(const GdScene &sc, const GdView &v, int sector, bool isFloor, int x, GdPlaneSpan &p) {
+/* Column-independent part of a span setup, one entry per (sector, floor or
+ * ceiling), rebuilt for every lane: the three divisions of R_DrawSpan's setup
+ * leave the per-crossing path. */
+struct GdPlaneEntry {
+  i64 phf, gv, shadeBase, xstep, ystep, bx0, by0, pviewx, pviewy;
+  const uint8_t *tex;
+  int wbits, hbits;
+};
+
+static_assert(sizeof(GdPlaneEntry) == GD_PLANE_ENTRY_BYTES, "scratch layout");
+
+__device__ __noinline__ void gd_plane_entry_setup(const GdScene &sc, const GdView &v, int sector, bool isFloor,
+                                                  GdPlaneEntry &e) {
   float ph = isFloor ? (v.viewZ - gd_sec_floor(sc, sector)) : (gd_sec_ceil(sc, sector) - v.viewZ);
   int4 si = gd_sec_info(sc, sector);
   int tex = isFloor ? si.y : si.z;
   const int4 ti = *reinterpret_cast<const int4 *>(&sc.texInfo[tex * 4]);
-  p.wbits = ti.z; p.hbits = ti.w; p.texW = sc.texW;
-  p.tex = sc.texAtlas + (size_t)tex * sc.texH * sc.texW;
-  i64 xscale = 1LL << (32 - p.wbits), yscale = 1LL << (32 - p.hbits);
+  e.wbits = ti.z; e.hbits = ti.w;
+  e.tex = sc.texAtlas + (size_t)tex * sc.texH * sc.texW;
+  i64 xscale = 1LL << (32 - e.wbits), yscale = 1LL << (32 - e.hbits);
   i64 fs = v.vsin, fc = v.vcos;
-  i64 xstep = gd_div(xscale * fs, GD_FOCAL_X), ystep = gd_div(yscale * fc, GD_FOCAL_X);
-  i64 col = (i64)x - 159;
-  p.basex = ((xscale * fc) >> 16) + col * xstep;
-  p.basey = ((yscale * -fs) >> 16) + col * ystep;
-  p.pviewx = gd_wmul(xscale, v.vx) >> 16;
-  p.pviewy = gd_wmul(yscale, -v.vy) >> 16;
-  p.phf = gd_rint(ph * 65536.0f);
-  p.gv = gd_min(gd_div(GD_FLOOR_VIS << 16, gd_max(p.phf, 1)), (1LL << 31) - 1);
+  e.xstep = gd_div(xscale * fs, GD_FOCAL_X);
+  e.ystep = gd_div(yscale * fc, GD_FOCAL_X);
+  e.bx0 = (xscale * fc) >> 16;
+  e.by0 = (yscale * -fs) >> 16;
+  e.pviewx = gd_wmul(xscale, v.vx) >> 16;
+  e.pviewy = gd_wmul(yscale, -v.vy) >> 16;
+  e.phf = gd_rint(ph * 65536.0f);
+  e.gv = gd_min(gd_div(GD_FLOOR_VIS << 16, gd_max(e.phf, 1)), (1LL << 31) - 1);
   i64 light = si.x + v.flashLight * 16;
-  p.shadeBase = 64 * GD_FU - (light + 12) * (GD_FU / 4);
+  e.shadeBase = 64 * GD_FU - (light + 12) * (GD_FU / 4);
+}
+
+__device__ __forceinline__ void gd_plane_setup(const GdScene &sc, const GdPlaneEntry *table, int sector, bool isFloor,
+                                               int x, GdPlaneSpan &p) {
+  const GdPlaneEntry &e = table[gd_secidx(sc, sector) * 2 + (isFloor ? 1 : 0)];
+  i64 col = (i64)x - 159;
+  p.wbits = e.wbits; p.hbits = e.hbits; p.texW = sc.texW;
+  p.tex = e.tex;
+  p.basex = e.bx0 + col * e.xstep;
+  p.basey = e.by0 + col * e.ystep;
+  p.pviewx = e.pviewx;
+  p.pviewy = e.pviewy;
+  p.phf = e.phf;
+  p.gv = e.gv;
+  p.shadeBase = e.shadeBase;
 }
 
 __device__ __forceinline__ uint8_t gd_plane_pixel(const GdPlaneSpan &p, const GdView &v, const unsigned *yslope,
@@ -1164,7 +1196,7 @@ __device__ __noinline__ void gd_mark_plane(const GdScene &sc, const GdView &v, c
   for (int k = k0; k <= k1; ++k) any |= gd_range_word(k, ya, yb) & ~owned[k * GD_SW];
   if (!any) return;
   GdPlaneSpan p;
-  gd_plane_setup(sc, v, sector, isFloor, x, p);
+  gd_plane_setup(sc, sh.planeTab, sector, isFloor, x, p);
   uint8_t *dst = sh.frame + x;
 #pragma unroll 1
   for (int k = k0; k <= k1; ++k) {
@@ -1748,7 +1780,7 @@ __device__ void gd_fallback_pass(const GdScene &sc, const GdView &v, const GdSha
     GdFlatProbe own = gd_flat_probe(sc, v, r, b, py, currentSector);
     if (!own.unresolved) {
       GdPlaneSpan p;
-      gd_plane_setup(sc, v, own.sector, own.isFloor, px, p);
+      gd_plane_setup(sc, sh.planeTab, own.sector, own.isFloor, px, p);
       sh.frame[py * GD_SW + px] = gd_plane_pixel(p, v, sh.yslope, sh.colormap, py);
       atomicOr(&owned[(py >> 5) * GD_SW + px], 1u << (py & 31));
       queue[i] = -1;
@@ -1829,7 +1861,7 @@ __device__ void gd_fallback_pass(const GdScene &sc, const GdView &v, const GdSha
     }
     const bool isFloor = ((float)py - gd_flat_ray(sc, v, px).center) > 0;
     GdPlaneSpan p;
-    gd_plane_setup(sc, v, sector, isFloor, px, p);
+    gd_plane_setup(sc, sh.planeTab, sector, isFloor, px, p);
     sh.frame[py * GD_SW + px] = gd_plane_pixel(p, v, sh.yslope, sh.colormap, py);
     atomicOr(&owned[(py >> 5) * GD_SW + px], 1u << (py & 31));
   }
@@ -2278,6 +2310,7 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
       sc.vtxWalls = (const int32_t *)gd_stage_copy(cursor, sc.vtxWalls, (size_t)(p.vtxWallsN > 0 ? p.vtxWallsN : 1) * 4);
     }
     if (m & GD_STAGE_ROWPROJ) { stagedRowproj = (GdRowProj *)cursor; cursor += gd_align16((size_t)sc.W * 4 * sizeof(GdRowProj)); }
+    sh.planeTab = (GdPlaneEntry *)(p.scratch + (size_t)blockIdx.x * gd_scratch_per_cta(sc.W, sc.S) + GD_SCRATCH_FIXED);
     if (tid == 0) { sScene = sc; sShared = sh; }
   }
   __syncthreads();
@@ -2288,11 +2321,12 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
     ((unsigned *)sh.colormap)[i] = ((const unsigned *)sc.colormap)[i];
   gd_lane_palette(sc, sh, 0);
   bool paletteBlended = false;    /* CTA-uniform: the shared palette holds a lane's screen-flash blend */
-  uint8_t *myScratch = p.scratch + (size_t)blockIdx.x * gd_scratch_per_cta(sc.W);
+  uint8_t *myScratch = p.scratch + (size_t)blockIdx.x * gd_scratch_per_cta(sc.W, sc.S);
   GdEvent *events = (GdEvent *)myScratch;
   int *eventCount = (int *)(myScratch + GD_SCRATCH_EVENTS_BYTES);
   unsigned short *vsec = (unsigned short *)(myScratch + GD_SCRATCH_EVENTS_BYTES + GD_SW * 4);
-  GdRowProj *rowproj = stagedRowproj ? stagedRowproj : (GdRowProj *)(myScratch + GD_SCRATCH_FIXED);
+  GdRowProj *rowproj = stagedRowproj ? stagedRowproj
+                                     : (GdRowProj *)(myScratch + GD_SCRATCH_FIXED + gd_scratch_plane_bytes(sc.S));
 
 #ifdef GD_PROFILE_PHASES
   if (tid == 0 && blockIdx.x == 0) gdProfile = (unsigned long long *)(p.status + 8);
@@ -2370,6 +2404,8 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
       sh.yslope[tid] = (unsigned)ys;
     }
     for (int w = tid; w < sc.W; w += GD_THREADS) gd_project_wall(sc, v, w, sh.walls[w]);
+    for (int idx = GD_THREADS - 1 - tid; idx < sc.S * 2; idx += GD_THREADS)   /* the threads the walls leave idle */
+      gd_plane_entry_setup(sc, v, idx >> 1, (idx & 1) != 0, sh.planeTab[idx]);
     for (int a = tid; a < nThings; a += GD_THREADS) {
       int sector = pointSector[a] == 0x7fffffff ? 0 : pointSector[a];
       gd_actor_setup(sc, v, p.things[(size_t)l * p.maxThings + a], sector, sh.actors[a]);
@@ -2675,7 +2711,7 @@ extern "C" void gd_renderer_destroy(gd_renderer *r) {
 }
 
 extern "C" size_t gd_renderer_scratch_bytes(const gd_renderer *r) {
-  return r ? (size_t)r->ctas * gd_scratch_per_cta(r->sc.W) + 16 : 0;
+  return r ? (size_t)r->ctas * gd_scratch_per_cta(r->sc.W, r->sc.S) + 16 : 0;
 }
 
 extern "C" int gd_renderer_ctas(const gd_renderer *r) { return r ? r->ctas : 0; }
@@ -2697,7 +2733,7 @@ static int gd_launch(const gd_renderer *r, const int32_t *lanes, const gd_thing 
   p.lanes = lanes; p.things = things; p.maxThings = r->maxThings; p.n = n; p.flags = flags;
   p.stack = stack; p.resetMask = reset_mask; p.obsOut = obs_out; p.indexedOut = indexed_out; p.rgbOut = rgb_out;
   p.scratch = (uint8_t *)scratch; p.status = status;
-  p.queueOffset = (size_t)r->ctas * gd_scratch_per_cta(r->sc.W);
+  p.queueOffset = (size_t)r->ctas * gd_scratch_per_cta(r->sc.W, r->sc.S);
   p.stageMask = r->stageMask; p.secWallsN = r->secWallsN; p.vtxWallsN = r->vtxWallsN; p.V = r->V;
   int grid = n < r->ctas ? n : r->ctas;
   gd_render_kernel<<<grid, GD_THREADS, r->smemBytes, (cudaStream_t)stream>>>(p);
@@ -2817,7 +2853,9 @@ extern "C" int gd_render_step_host(const gd_renderer *r, const int32_t *lanes_ho
  */
 #define GD_STATIC_MAX_CTAS 32
 #define GD_STATIC_MAX_WALLS 256
-#define GD_STATIC_PER_CTA ((GD_SCRATCH_FIXED + GD_STATIC_MAX_WALLS * 4 * sizeof(GdRowProj) + 15) & ~(size_t)15)
+/* a scene of W walls has fewer than W sectors (three walls bound a sector, a wall bounds two) */
+#define GD_STATIC_PER_CTA ((GD_SCRATCH_FIXED + GD_STATIC_MAX_WALLS * 2 * GD_PLANE_ENTRY_BYTES + \
+                            GD_STATIC_MAX_WALLS * 4 * sizeof(GdRowProj) + 31) & ~(size_t)15)
 #define GD_STATIC_SCRATCH_BYTES (GD_STATIC_MAX_CTAS * GD_STATIC_PER_CTA + 16)
 #define GD_STATIC_MAX_DEVICES 64
 
@@ -2834,7 +2872,7 @@ extern "C" int gd_render_step_static(const gd_renderer *r, const int32_t *lanes,
   if (!r || !lanes || !stack || !status) return GD_ERR_NULL;
   if (r->maxThings > 0 && !things) return GD_ERR_NULL;
   if (n < 0) return GD_ERR_SIZE;
-  if (r->sc.W > GD_STATIC_MAX_WALLS) return GD_ERR_STATIC_LIMIT;
+  if (r->sc.W > GD_STATIC_MAX_WALLS || r->sc.S > GD_STATIC_MAX_WALLS) return GD_ERR_STATIC_LIMIT;
   if (r->device < 0 || r->device >= GD_STATIC_MAX_DEVICES) return GD_ERR_STATIC_LIMIT;
   if (n == 0) return GD_OK;
   uintptr_t align = (uintptr_t)lanes | (uintptr_t)things | (uintptr_t)stack;
