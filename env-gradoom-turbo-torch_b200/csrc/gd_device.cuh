@@ -79,6 +79,11 @@ __device__ __forceinline__ i64 gd_pymod(i64 a, i64 m) {
   i64 r = a % m;
   return (r != 0 && ((r < 0) != (m < 0))) ? r + m : r;
 }
+/* the same for a texture width: a power of two needs no division */
+__device__ __forceinline__ int gd_pymod_width(i64 a, int w) {
+  if (w > 0 && (w & (w - 1)) == 0) return (int)(a & (i64)(w - 1));
+  return (int)gd_pymod(a, w);
+}
 
 /*
  * Truncating signed 64-bit division.  The generic 64-bit divide is a long

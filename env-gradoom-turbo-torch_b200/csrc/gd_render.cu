@@ -1148,7 +1148,7 @@ __device__ __noinline__ void gd_draw_tier(const GdScene &sc, const GdView &v, co
   if (texId < 0 || ya >= yb) return;
   const int4 ti = *reinterpret_cast<const int4 *>(&sc.texInfo[texId * 4]);
   int tw = ti.x, hbits = ti.w;
-  int u = (int)gd_pymod((t.hoff + t.tox) >> 16, tw);
+  int u = gd_pymod_width((t.hoff + t.tox) >> 16, tw);
   i64 vstep = t.vstepBase * (1LL << (14 - hbits));
   i64 texMid = gd_rint((originZ - v.viewZ) * 65536.0f + t.yoff * 65536.0f);
   /* frac(y) = (texMid << (16-bits)) + ((vstep * (y*FU - center + FU)) >> 16); the
@@ -1267,7 +1267,7 @@ __device__ __noinline__ void gd_masked_pass(const GdScene &sc, const GdView &v, 
   if (side != 0) hoff = repeat - hoff;
   if (wv.sl > 0 && hoff < 0) hoff = 0;
   if (hoff >= repeat) hoff = repeat - 1;
-  const int u = (int)gd_pymod((hoff + gd_rint(soff[0] * 65536.0f)) >> 16, tw);
+  const int u = gd_pymod_width((hoff + gd_rint(soff[0] * 65536.0f)) >> 16, tw);
   const i64 vstep = vstepBase * (1LL << (14 - hbits));
   const i64 texMid = gd_rint((worldTop - v.viewZ) * 65536.0f + soff[1] * 65536.0f);
   /* R_DrawMaskedColumn: post rows from the drawseg's interpolated scale */
