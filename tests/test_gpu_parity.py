@@ -7,6 +7,7 @@ is within 1 LSB (upstream tests/test_rendering.py:112-139 grants the same).
 """
 
 import ctypes
+import os
 
 import numpy as np
 import pytest
@@ -354,3 +355,21 @@ def test_screen_flashes_blend_rgb_and_observation(pkg, oracle):
     _, _, rgb = r.frames(_dev(lanes[order]), _dev(things[order]), rgb=True)
     want = oracle.rgb(blob, oracle.render(blob, lanes, things)["indexed"], lanes)[order]
     assert np.array_equal(rgb.cpu().numpy(), want)
+
+
+@pytest.mark.gpu
+def test_player_exactly_on_a_portal_line(pkg, oracle, scenes):
+    """A recorded c2 lane whose player stands on a room boundary (x = 1792 - 2^-15):
+    no seg claims 84 % of the view, so the frame is mostly flat fallback and the
+    pixel queue is refilled many times."""
+
+    data = np.load(os.path.join(os.path.dirname(__file__), "golden", "lane_on_portal_line.npz"))
+    sc, blob = scenes("c2")
+    lanes, things = data["lanes"], data["things"]
+    expected = oracle.render(blob, lanes, things)
+    assert expected["unowned"][0] > 50000
+    r = _renderer(blob, things.shape[1])
+    obs, indexed, _ = r.frames(_dev(lanes), _dev(things), obs=True, indexed=True)
+    r.check_status()
+    assert np.array_equal(indexed.cpu().numpy(), expected["indexed"])
+    assert np.array_equal(obs.cpu().numpy(), expected["obs"])
