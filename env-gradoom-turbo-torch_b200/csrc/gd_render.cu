@@ -675,18 +675,27 @@ __device__ void gd_wall_spans(const GdScene &sc, const GdView &v, const GdShared
 }
 
 /* ---- phase: blocking ray cast of column x (engine.py:10534-10557) ------- */
-__device__ void gd_blocking_raycast(const GdScene &sc, const GdView &v, int x, float rx, float ry, float &wallDistance,
-                                    int &blockingWall) {
+/* Nearest one-sided wall the column ray crosses; among equal distances the
+ * lowest wall index, as the reference's first-minimum over its ascending
+ * blocking list.  Only walls that passed the frustum test can be crossed, and
+ * the division is spent only on walls the sign test says are crossed. */
+__device__ void gd_blocking_raycast(const GdScene &sc, const GdView &v, const GdShared &sh, const short *list, int listed,
+                                    float rx, float ry, float &wallDistance, int &blockingWall) {
   float best = GD_INF;
-  int bestSlot = 0;
-  for (int b = 0; b < sc.B; ++b) {
+  int bestWall = sc.blocking[0];
+#pragma unroll 1
+  for (int i = 0; i < listed; ++i) {
+    const int w = list[i];
+    if (!sh.walls[w].oneSided) continue;
+    const float4 wl = *reinterpret_cast<const float4 *>(&sc.walls[w * 4]);
+    if (!gd_ray_geo(wl, v, rx, ry)) continue;
     float distance, along;
     bool geo, positive;
-    gd_ray_test(sc, v, sc.blocking[b], rx, ry, distance, along, geo, positive);
+    gd_ray_test(sc, v, w, rx, ry, distance, along, geo, positive);
     float d = geo ? distance : GD_INF;
-    if (d < best) { best = d; bestSlot = b; }
+    if (d < best || (d == best && w < bestWall && isfinite(d))) { best = d; bestWall = w; }
   }
-  blockingWall = sc.blocking[bestSlot];
+  blockingWall = bestWall;
   wallDistance = fminf(fmaxf(best, 1.0f), 4096.0f);
 }
 
@@ -2423,7 +2432,10 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
     }
     __syncthreads();
     GD_BEAT(3);
-    for (int w = tid; w < sc.W; w += GD_THREADS) {
+    const short *frustumList = (const short *)sh.hitD;
+    const int frustumListed = sh.misc[2];
+    for (int i = tid; i < frustumListed; i += GD_THREADS) {   /* walls outside the frustum own no column */
+      const int w = frustumList[i];
       int xl = sh.walls[w].isl;
       if (xl >= 0 && xl < GD_SW) {
         float rx, ry;
@@ -2436,7 +2448,7 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
       float rx, ry, wd;
       int bw;
       gd_ray(v, tid, rx, ry);
-      gd_blocking_raycast(sc, v, tid, rx, ry, wd, bw);
+      gd_blocking_raycast(sc, v, sh, frustumList, frustumListed, rx, ry, wd, bw);
       sh.wallDistance[tid] = wd;
       sh.blockingWall[tid] = (short)bw;
     }
