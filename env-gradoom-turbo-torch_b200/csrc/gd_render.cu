@@ -93,6 +93,7 @@ struct GdShared {
   uint8_t *obs;         /* 84 x 84 */
   int *misc;            /* 16 ints: start sector, fallback queue length, its unresolved rows' range, GdFlatBounds */
   unsigned *masks;      /* 14 x 320: per-column filled / plane-owned row bitmasks */
+  unsigned *pal32;      /* 256: the lane's palette as r | g << 8 | b << 16, for the RGB24 output */
   float *maskedDist;    /* 320: nearest masked drawseg of the column ... */
   unsigned *maskedInfo; /* ... its wall << 16 | ceiling clip << 8 | floor clip; 0xFFFF0000 | .. = none */
   float *hitD, *hitA;   /* 8 x 320 each: per-column cache of this iteration's wall hits */
@@ -116,6 +117,7 @@ __host__ __device__ inline size_t gd_shared_bytes(int W, int maxThings) {
   b += gd_align16(64);
   b += gd_align16(14 * GD_SW * 4);
   b += 2 * gd_align16(GD_SW * 4);
+  b += gd_align16(256 * 4);
   b += 2 * gd_align16(8 * GD_SW * 4) + gd_align16(8 * GD_SW);
   b += gd_align16((size_t)W * sizeof(GdWall));
   b += gd_align16((size_t)(maxThings > 0 ? maxThings : 1) * sizeof(GdActor));
@@ -138,6 +140,7 @@ __device__ inline void gd_carve(uint8_t *base, int W, int maxThings, GdShared &s
   s.masks = (unsigned *)(base + o); o += gd_align16(14 * GD_SW * 4);
   s.maskedDist = (float *)(base + o); o += gd_align16(GD_SW * 4);
   s.maskedInfo = (unsigned *)(base + o); o += gd_align16(GD_SW * 4);
+  s.pal32 = (unsigned *)(base + o); o += gd_align16(256 * 4);
   s.hitD = (float *)(base + o); o += gd_align16(8 * GD_SW * 4);
   s.hitA = (float *)(base + o); o += gd_align16(8 * GD_SW * 4);
   s.hitF = base + o; o += gd_align16(8 * GD_SW);
@@ -2280,6 +2283,7 @@ __device__ void gd_lane_palette(const GdScene &sc, const GdShared &sh, int flags
     sh.playpal[i * 3 + c] = (uint8_t)v;
   }
   sh.pal64[i] = (unsigned long long)ch[0] | ((unsigned long long)ch[1] << 20) | ((unsigned long long)ch[2] << 40);
+  sh.pal32[i] = ch[0] | (ch[1] << 8) | (ch[2] << 16);
 }
 
 /* ---- the kernel ----------------------------------------------------------- */
@@ -2504,16 +2508,16 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
       for (int i = tid; i < GD_SCREEN_H * GD_SW / 16; i += GD_THREADS) dst[i] = src[i];
     }
     if (p.rgbOut) {
+      /* four pixels (one word of indices) become three words of RGB24 */
       unsigned *dst = (unsigned *)(p.rgbOut + (size_t)l * GD_SCREEN_H * GD_SW * 3);
-      for (int j = tid; j < GD_SCREEN_H * GD_SW * 3 / 4; j += GD_THREADS) {
-        unsigned word = 0;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          int b = j * 4 + k;
-          int px = b / 3, ch = b - px * 3;
-          word |= (unsigned)sh.playpal[sh.frame[px] * 3 + ch] << (8 * k);
-        }
-        dst[j] = word;
+      const unsigned *src = (const unsigned *)sh.frame;
+      for (int q = tid; q < GD_SCREEN_H * GD_SW / 4; q += GD_THREADS) {
+        const unsigned idx = src[q];
+        const unsigned p0 = sh.pal32[idx & 0xFF], p1 = sh.pal32[(idx >> 8) & 0xFF];
+        const unsigned p2 = sh.pal32[(idx >> 16) & 0xFF], p3 = sh.pal32[idx >> 24];
+        dst[q * 3 + 0] = p0 | (p1 << 24);
+        dst[q * 3 + 1] = (p1 >> 8) | (p2 << 16);
+        dst[q * 3 + 2] = (p2 >> 16) | (p3 << 8);
       }
     }
     GD_BEAT(8);
