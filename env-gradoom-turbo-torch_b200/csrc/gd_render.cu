@@ -2099,25 +2099,20 @@ __device__ void gd_weapon(const GdScene &sc, const int32_t *lane, uint8_t *frame
 }
 
 /* ---- phase: status bar (engine.py:15158-15267) --------------------------- */
-__device__ __noinline__ void gd_hud_patch(const GdScene &sc, uint8_t *canvas, int patch, int x, int y) {
-  __syncthreads();  /* patches overlap: keep the reference's draw order */
-  const int4 hi = *reinterpret_cast<const int4 *>(&sc.hudInfo[patch * 4]);
-  x -= hi.z;
-  y -= hi.w;
-  int w = hi.x, h = hi.y;
-  if (w <= 0 || h <= 0) return;
-  int sx = x < 0 ? -x : 0, sy = y < 0 ? -y : 0;
-  int tx = x > 0 ? x : 0, ty = y > 0 ? y : 0;
-  int cw = min(w - sx, GD_SW - tx), ch = min(h - sy, GD_HUD_H - ty);
-  if (cw <= 0 || ch <= 0) return;
-  for (int idx = threadIdx.x; idx < cw * ch; idx += GD_THREADS) {
-    int j = idx / cw, i = idx - j * cw;
-    size_t si = ((size_t)patch * GD_HUD_H + (size_t)(sy + j)) * GD_SW + (size_t)(sx + i);
-    if (sc.hudOpaque[si]) canvas[(ty + j) * GD_SW + tx + i] = sc.hudAtlas[si];
-  }
+/* The status bar is a list of up to GD_HUD_MAX_PATCHES opaque-masked blits drawn
+ * in a fixed order, later ones on top.  Thread 0 lists (patch, x, y), one thread
+ * per entry clips it against the canvas, and then every column thread resolves
+ * its 32 pixels from the entries that cross its column, topmost first. */
+#define GD_HUD_MAX_PATCHES 48
+
+struct GdHudList { int4 *entries; int *count; };
+
+__device__ __forceinline__ void gd_hud_push(const GdHudList &hl, int patch, int x, int y) {
+  int n = *hl.count;
+  if (n < GD_HUD_MAX_PATCHES) { hl.entries[n] = make_int4(patch, x, y, 0); *hl.count = n + 1; }
 }
 
-__device__ void gd_hud_number(const GdScene &sc, uint8_t *canvas, int value, int right, int y, bool small) {
+__device__ void gd_hud_number(const GdScene &sc, const GdHudList &hl, int value, int right, int y, bool small) {
   int vc = value < -99 ? -99 : (value > 999 ? 999 : value);
   int neg = vc < 0;
   int mag = neg ? -vc : vc;
@@ -2130,51 +2125,92 @@ __device__ void gd_hud_number(const GdScene &sc, uint8_t *canvas, int value, int
   for (int k = n - 1; k >= 0; --k) {
     int patch = base + digits[k];
     const int4 hi = *reinterpret_cast<const int4 *>(&sc.hudInfo[patch * 4]);
-    gd_hud_patch(sc, canvas, patch, x - hi.z, y - hi.w);
+    gd_hud_push(hl, patch, x - hi.z, y - hi.w);   /* the blit subtracts the glyph offsets once more */
     x += dw;
   }
 }
 
-__device__ void gd_hud(const GdScene &sc, const int32_t *lane, uint8_t *canvas) {
-  for (int i = threadIdx.x; i < GD_HUD_H * GD_SW / 4; i += GD_THREADS) ((unsigned *)canvas)[i] = 0;
-  gd_hud_patch(sc, canvas, 0, 0, 0);
-  gd_hud_patch(sc, canvas, 1, 104, 0);
-  const int ammoSlotOf[8] = {-1, -1, 1, 2, 2, 1, 4, 5};
-  int weapon = lane[GD_L_WEAPON];
-  int ammoSlot = ammoSlotOf[weapon < 0 ? 0 : (weapon > 7 ? 7 : weapon)];
-  int ammo = ammoSlot < 0 ? 0 : (int)__int_as_float(lane[GD_L_READY_AMMO]);
-  float hf = __int_as_float(lane[GD_L_HEALTH]), af = __int_as_float(lane[GD_L_ARMOR]);
-  int health = (int)(hf < 0 ? 0.0f : (hf > 999 ? 999.0f : hf));
-  int armor = (int)(af < 0 ? 0.0f : (af > 999 ? 999.0f : af));
-  gd_hud_number(sc, canvas, ammo, 44, 3, false);
-  gd_hud_number(sc, canvas, health, 90, 3, false);
-  gd_hud_patch(sc, canvas, 12, 90, 3);
-  gd_hud_number(sc, canvas, armor, 221, 3, false);
-  gd_hud_patch(sc, canvas, 12, 221, 3);
-  int pain = (100 - health) >= 0 ? (100 - health) / 20 : -((health - 100 + 19) / 20);
-  pain = pain < 0 ? 0 : (pain > 4 ? 4 : pain);
-  int face = 13 + pain * 3 + lane[GD_L_FACE_INDEX];
-  if (lane[GD_L_GRIN_TICS] > 0) face = 64 + pain;
-  else if (lane[GD_L_PAIN_TICS] > 0) {
-    if (lane[GD_L_FLAGS] & 2) face = 59 + pain;
-    else {
-      int d = lane[GD_L_PAIN_DIRECTION];
-      d = d < 0 ? 0 : (d > 2 ? 2 : d);
-      face = (d == 0 ? 44 : (d == 1 ? 49 : 54)) + pain;
+__device__ __noinline__ void gd_hud(const GdScene &sc, const GdShared &sh, const int32_t *lane, uint8_t *canvas) {
+  GdHudList hl;
+  hl.entries = (int4 *)sh.obs;                       /* free until the resize */
+  hl.count = (int *)(sh.obs + GD_HUD_MAX_PATCHES * sizeof(int4));
+  if (threadIdx.x == 0) {
+    *hl.count = 0;
+    gd_hud_push(hl, 0, 0, 0);
+    gd_hud_push(hl, 1, 104, 0);
+    int weapon = lane[GD_L_WEAPON];
+    int ammoSlot = weapon < 2 ? -1 : (int)((0x54122100u >> (4 * (weapon > 7 ? 7 : weapon))) & 0xF);   /* -,-,1,2,2,1,4,5 */
+    int ammo = ammoSlot < 0 ? 0 : (int)__int_as_float(lane[GD_L_READY_AMMO]);
+    float hf = __int_as_float(lane[GD_L_HEALTH]), af = __int_as_float(lane[GD_L_ARMOR]);
+    int health = (int)(hf < 0 ? 0.0f : (hf > 999 ? 999.0f : hf));
+    int armor = (int)(af < 0 ? 0.0f : (af > 999 ? 999.0f : af));
+    gd_hud_number(sc, hl, ammo, 44, 3, false);
+    gd_hud_number(sc, hl, health, 90, 3, false);
+    gd_hud_push(hl, 12, 90, 3);
+    gd_hud_number(sc, hl, armor, 221, 3, false);
+    gd_hud_push(hl, 12, 221, 3);
+    int pain = (100 - health) >= 0 ? (100 - health) / 20 : -((health - 100 + 19) / 20);
+    pain = pain < 0 ? 0 : (pain > 4 ? 4 : pain);
+    int face = 13 + pain * 3 + lane[GD_L_FACE_INDEX];
+    if (lane[GD_L_GRIN_TICS] > 0) face = 64 + pain;
+    else if (lane[GD_L_PAIN_TICS] > 0) {
+      if (lane[GD_L_FLAGS] & 2) face = 59 + pain;
+      else {
+        int d = lane[GD_L_PAIN_DIRECTION];
+        d = d < 0 ? 0 : (d > 2 ? 2 : d);
+        face = (d == 0 ? 44 : (d == 1 ? 49 : 54)) + pain;
+      }
+    } else if (lane[GD_L_ATTACK_HELD] >= 70) face = 49 + pain;
+    if (health <= 0) face = 69;
+    gd_hud_push(hl, face < 0 ? 0 : (face > 69 ? 69 : face), 143, 0);
+    for (int wi = 0; wi < 6; ++wi) {
+      bool owned = wi < 5 && ((lane[GD_L_WEAPONS_OWNED] >> (wi + 1)) & 1);
+      gd_hud_push(hl, owned ? 28 + wi + 2 : 38 + wi, 111 + 12 * (wi % 3), wi < 3 ? 4 : 14);
     }
-  } else if (lane[GD_L_ATTACK_HELD] >= 70) face = 49 + pain;
-  if (health <= 0) face = 69;
-  gd_hud_patch(sc, canvas, face < 0 ? 0 : (face > 69 ? 69 : face), 143, 0);
-  const int armsX[6] = {111, 123, 135, 111, 123, 135}, armsY[6] = {4, 4, 4, 14, 14, 14};
-  for (int wi = 0; wi < 6; ++wi) {
-    bool owned = wi < 5 && ((lane[GD_L_WEAPONS_OWNED] >> (wi + 1)) & 1);
-    gd_hud_patch(sc, canvas, owned ? 28 + wi + 2 : 38 + wi, armsX[wi], armsY[wi]);
+    for (int row = 0; row < 4; ++row) {
+      int y = 5 + row * 6;
+      gd_hud_number(sc, hl, (int)__int_as_float(lane[GD_L_AMMO0 + row]), 288, y, true);
+      gd_hud_number(sc, hl, row == 0 ? 200 : (row == 3 ? 300 : 50), 314, y, true);   /* ammo maxima */
+    }
   }
-  const int maxima[4] = {200, 50, 50, 300};
-  for (int row = 0; row < 4; ++row) {
-    int y = 5 + row * 6;
-    gd_hud_number(sc, canvas, (int)__int_as_float(lane[GD_L_AMMO0 + row]), 288, y, true);
-    gd_hud_number(sc, canvas, maxima[row], 314, y, true);
+  __syncthreads();
+  const int n = *hl.count;
+  if (threadIdx.x < n) {
+    /* clip against the canvas: (tx | ty << 16, cw | ch << 16, sx | sy << 16, patch); cw = 0 when nothing is left */
+    int4 e = hl.entries[threadIdx.x];
+    const int patch = e.x;
+    const int4 hi = *reinterpret_cast<const int4 *>(&sc.hudInfo[patch * 4]);
+    int x = e.y - hi.z, y = e.z - hi.w;
+    int w = hi.x, h = hi.y;
+    int sx = x < 0 ? -x : 0, sy = y < 0 ? -y : 0;
+    int tx = x > 0 ? x : 0, ty = y > 0 ? y : 0;
+    int cw = min(w - sx, GD_SW - tx), ch = min(h - sy, GD_HUD_H - ty);
+    if (w <= 0 || h <= 0 || cw <= 0 || ch <= 0) { cw = 0; ch = 0; }
+    hl.entries[threadIdx.x] = make_int4(tx | (ty << 16), cw | (ch << 16), sx | (sy << 16), patch);
+  }
+  __syncthreads();
+  {
+    const int x = threadIdx.x;
+    unsigned long long mine = 0;                       /* entries that cross this column */
+    for (int k = 0; k < n; ++k) {
+      int4 e = hl.entries[k];
+      int tx = e.x & 0xFFFF, cw = e.y & 0xFFFF;
+      if (x >= tx && x < tx + cw) mine |= 1ull << k;
+    }
+    for (int y = 0; y < GD_HUD_H; ++y) {
+      uint8_t value = 0;
+      unsigned long long m = mine;
+      while (m) {
+        int k = 63 - __clzll((long long)m);            /* topmost remaining entry */
+        m &= ~(1ull << k);
+        int4 e = hl.entries[k];
+        int tx = e.x & 0xFFFF, ty = e.x >> 16, ch = e.y >> 16, sx = e.z & 0xFFFF, sy = e.z >> 16;
+        if (y < ty || y >= ty + ch) continue;
+        size_t si = ((size_t)e.w * GD_HUD_H + (size_t)(sy + y - ty)) * GD_SW + (size_t)(sx + x - tx);
+        if (sc.hudOpaque[si]) { value = sc.hudAtlas[si]; break; }
+      }
+      canvas[y * GD_SW + x] = value;
+    }
   }
   __syncthreads();
 }
@@ -2497,7 +2533,7 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
     GD_BEAT(7);
     const bool wantFull = p.indexedOut != nullptr || p.rgbOut != nullptr;
     if (p.flags & GD_F_DRAW_HUD) {
-      gd_hud(sc, sh.lane, sh.frame + GD_VH * GD_SW);
+      gd_hud(sc, sh, sh.lane, sh.frame + GD_VH * GD_SW);
     } else if (wantFull) {
       for (int i = tid; i < GD_HUD_H * GD_SW / 4; i += GD_THREADS) ((unsigned *)(sh.frame + GD_VH * GD_SW))[i] = 0;
       __syncthreads();
