@@ -52,7 +52,7 @@ WORKLOADS = {
 }
 # dram__bytes_read.sum + dram__bytes_write.sum of one render launch at 4096 lanes (a one-pass ncu
 # capture of this file's default command), per lane; mostly the oldest-first roll of the frame stack
-DRAM_TRAFFIC_PER_LANE = 167.8e6 / 4096
+DRAM_TRAFFIC_PER_LANE = 170.5e6 / 4096
 
 
 def measured_peaks():
