@@ -2,7 +2,7 @@
 
 Run once on a machine that has the upstream sources:
 
-    GRADOOM_REFERENCE_SRC=<upstream checkout>/src/gradoom python tests/golden/make_golden.py [c1 c2 c3 c4 c1m stack flashes]
+    GRADOOM_REFERENCE_SRC=<upstream checkout>/src/gradoom python tests/golden/make_golden.py [c1 c2 c3 c4 c1m stack flashes pitch]
 
 For each seeded synthetic scene it resets the upstream engine, injects K
 monsters per lane, replays a seeded uniform action stream and, at a few
@@ -146,6 +146,37 @@ def generate_stack(eng, scn, act):
     print("stack fixture done", flush=True)
 
 
+def generate_pitch(eng, scn, act):
+    """c1 with the view pitched up and down (engine.py:9622-9631 and every use of the
+    pitched view centre): inputs, indexed frames and observations."""
+
+    n, k = 4, 4
+    sc = gdscene.make_grid_scene(gdscene.GRID_CONFIGS["c1"])
+    e, g = make_engine(eng, scn, sc, n, k, seed=2468)
+    tab = gdstate.SpriteTables(sc, torch.device("cpu"))
+    am = action_matrix(act)
+    ag = torch.Generator().manual_seed(ACTION_SEED + 3)
+    for _ in range(9):
+        e.step(am[torch.randint(0, 17, (n,), generator=ag)])
+    offsets, coscorr = gdscene.ray_tables()
+    out = {"config": np.asarray("c1"), "ray_offsets": offsets, "ray_coscorr": coscorr,
+           "checkpoints": np.asarray([0, 1, 2])}
+    # BAM pitches: +-4, +-11, +-20, +-28 degrees and two odd values
+    degrees = [(4.0, -4.0, 11.0, -11.0), (20.0, -20.0, 28.0, -28.0), (0.37, -7.77, 15.5, -1.0)]
+    for ci, row in enumerate(degrees):
+        bam = torch.tensor([int(round(d / 360.0 * (1 << 32))) for d in row], dtype=torch.int64)
+        e._pitch_bam.copy_(bam)
+        e.pitch.copy_(bam.to(torch.float32) * (2.0 * np.pi / (1 << 32)))
+        lanes, things, indexed, obs_float = snapshot(e, tab, 64)
+        used = max(int(lanes[:, gdstate.L_THINGS].max()), 1)
+        out[f"lanes_{ci}"] = lanes
+        out[f"things_{ci}"] = things[:, :used].copy()
+        out[f"indexed_{ci}"] = indexed
+        out[f"obs_float_{ci}"] = obs_float
+    np.savez_compressed(os.path.join(HERE, "golden_pitch.npz"), **out)
+    print("pitch fixture done", flush=True)
+
+
 def generate_flashes(eng, scn, act):
     """c1 with the damage / bonus screen blends switched on (engine.py:15385-15397):
     inputs, the blended RGB24 frame and the observation derived from it."""
@@ -178,12 +209,14 @@ def generate_flashes(eng, scn, act):
 
 def main(argv):
     eng, scn, act = refbridge.load_reference()
-    names = argv or ["c1", "c2", "c3", "c4", "c1m", "stack", "flashes"]
+    names = argv or ["c1", "c2", "c3", "c4", "c1m", "stack", "flashes", "pitch"]
     for name in names:
         if name == "stack":
             generate_stack(eng, scn, act)
         elif name == "flashes":
             generate_flashes(eng, scn, act)
+        elif name == "pitch":
+            generate_pitch(eng, scn, act)
         else:
             generate(name, eng, scn, act)
 

@@ -30,7 +30,7 @@ def _dev(a):
     return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
 
 
-@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4", "c1m"])
+@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4", "c1m", "pitch"])
 def test_cuda_matches_upstream_fixtures(name, pkg, oracle, scenes):
     data = load_golden(name)
     _sc, blob = scenes(str(data["config"]), (data["ray_offsets"], data["ray_coscorr"]))

@@ -12,7 +12,7 @@ import pytest
 from conftest import load_golden
 
 
-@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4", "c1m"])
+@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4", "c1m", "pitch"])
 def test_oracle_matches_upstream_indexed_frames(name, pkg, oracle, scenes):
     data = load_golden(name)
     _sc, blob = scenes(str(data["config"]), (data["ray_offsets"], data["ray_coscorr"]))
