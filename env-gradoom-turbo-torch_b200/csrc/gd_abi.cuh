@@ -192,6 +192,7 @@ static int gd_launch(const gd_renderer *r, const int32_t *lanes, const gd_thing 
 
 extern "C" int gd_render_step(const gd_renderer *r, const int32_t *lanes, const void *things, int n, int mask_hud,
                               uint8_t *stack, void *scratch, size_t scratch_bytes, int *status, void *stream) {
+  if (r && n == 0) return GD_OK;   /* an empty batch needs no buffers */
   if (!stack) return GD_ERR_NULL;
   int flags = GD_F_STACK_ROLL | (mask_hud ? GD_F_MASK_HUD : GD_F_DRAW_HUD);
   return gd_launch(r, lanes, (const gd_thing *)things, n, flags, stack, nullptr, nullptr, nullptr, nullptr, scratch,
@@ -201,6 +202,7 @@ extern "C" int gd_render_step(const gd_renderer *r, const int32_t *lanes, const 
 extern "C" int gd_render_reset(const gd_renderer *r, const int32_t *lanes, const void *things, int n, int mask_hud,
                                const uint8_t *reset_mask, uint8_t *stack, void *scratch, size_t scratch_bytes,
                                int *status, void *stream) {
+  if (r && n == 0) return GD_OK;   /* an empty batch needs no buffers */
   if (!stack || !reset_mask) return GD_ERR_NULL;
   int flags = GD_F_STACK_FILL | (mask_hud ? GD_F_MASK_HUD : GD_F_DRAW_HUD);
   return gd_launch(r, lanes, (const gd_thing *)things, n, flags, stack, reset_mask, nullptr, nullptr, nullptr, scratch,
@@ -210,6 +212,7 @@ extern "C" int gd_render_reset(const gd_renderer *r, const int32_t *lanes, const
 extern "C" int gd_render_frames(const gd_renderer *r, const int32_t *lanes, const void *things, int n, int mask_hud,
                                 int include_hud, uint8_t *obs_out, uint8_t *indexed_out, uint8_t *rgb_out,
                                 void *scratch, size_t scratch_bytes, int *status, void *stream) {
+  if (r && n == 0) return GD_OK;   /* an empty batch needs no buffers */
   if (!obs_out && !indexed_out && !rgb_out) return GD_ERR_NULL;
   int flags = (mask_hud ? GD_F_MASK_HUD : 0) | ((include_hud || !mask_hud) ? GD_F_DRAW_HUD : 0);
   return gd_launch(r, lanes, (const gd_thing *)things, n, flags, nullptr, nullptr, obs_out, indexed_out, rgb_out,
@@ -220,6 +223,7 @@ extern "C" int gd_render_step_frames(const gd_renderer *r, const int32_t *lanes,
                                      int mask_hud, int include_hud, uint8_t *stack, uint8_t *indexed_out,
                                      uint8_t *rgb_out, void *scratch, size_t scratch_bytes, int *status,
                                      void *stream) {
+  if (r && n == 0) return GD_OK;   /* an empty batch needs no buffers */
   if (!stack || (!indexed_out && !rgb_out)) return GD_ERR_NULL;
   int flags = GD_F_STACK_ROLL | (mask_hud ? GD_F_MASK_HUD : 0) | ((include_hud || !mask_hud) ? GD_F_DRAW_HUD : 0);
   return gd_launch(r, lanes, (const gd_thing *)things, n, flags, stack, nullptr, nullptr, indexed_out, rgb_out,
@@ -234,6 +238,7 @@ extern "C" int gd_render_step_host(const gd_renderer *r, const int32_t *lanes_ho
                                    int mask_hud, int32_t *lanes_dev, void *things_dev, uint8_t *stack,
                                    uint8_t *obs_host, void *scratch, size_t scratch_bytes, int *status,
                                    void *stream) {
+  if (r && n == 0) return GD_OK;   /* an empty batch needs no buffers */
   if (!r || !lanes_host || !lanes_dev || !stack || !obs_host) return GD_ERR_NULL;
   if (r->maxThings > 0 && (!things_host || !things_dev)) return GD_ERR_NULL;
   if (n < 0) return GD_ERR_SIZE;
@@ -319,6 +324,7 @@ extern "C" int gd_static_max_walls(void) { return GD_STATIC_MAX_WALLS; }
 
 extern "C" int gd_render_step_static(const gd_renderer *r, const int32_t *lanes, const void *things, int n,
                                      int mask_hud, uint8_t *stack, int *status, void *stream) {
+  if (r && n == 0) return GD_OK;   /* an empty batch needs no buffers */
   if (!r || !lanes || !stack || !status) return GD_ERR_NULL;
   if (r->maxThings > 0 && !things) return GD_ERR_NULL;
   if (n < 0) return GD_ERR_SIZE;

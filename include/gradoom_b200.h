@@ -13,7 +13,8 @@
  * gradoom_b200_layout.h.
  *
  * Return value: GD_OK or a negative GD_ERR_* for host-side validation
- * failures.  Device-side anomalies set bits in the caller's `status` word
+ * failures.  A call over n = 0 lanes returns GD_OK without looking at its
+ * buffers.  Device-side anomalies set bits in the caller's `status` word
  * (GD_STATUS_*), which the caller reads when it wants to; kernels never trap.
  */
 #ifndef GRADOOM_B200_H

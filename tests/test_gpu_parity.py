@@ -373,3 +373,32 @@ def test_player_exactly_on_a_portal_line(pkg, oracle, scenes):
     r.check_status()
     assert np.array_equal(indexed.cpu().numpy(), expected["indexed"])
     assert np.array_equal(obs.cpu().numpy(), expected["obs"])
+
+
+@pytest.mark.gpu
+def test_sixty_four_things_per_lane_and_empty_batches(pkg, oracle, scenes):
+    """The per-column candidate mask is 64 bits wide: lanes with exactly 64 things,
+    most of them crowded into one room so that many overlap in a column; and a
+    launch over zero lanes touches nothing."""
+
+    import torch
+
+    from gradoom_b200 import stepper
+
+    sc, blob = scenes("c1")
+    lanes, things = stepper.random_lanes(sc, 24, 64, seed=31)
+    tf = things.view(np.float32)
+    room = float(sc.meta["spec"].room)
+    tf[:, 8:, 0] = tf[:, 8:, 0] % room + room       # things 8..63 share the second room of the first row
+    tf[:, 8:, 1] = tf[:, 8:, 1] % room
+    floor = sc.sector_heights[1, 0]
+    tf[:, 8:, 2] = floor
+    expected = oracle.render(blob, lanes, things)
+    r = _renderer(blob, 64)
+    obs, indexed, _ = r.frames(_dev(lanes), _dev(things), obs=True, indexed=True)
+    r.check_status()
+    assert np.array_equal(indexed.cpu().numpy(), expected["indexed"])
+    assert np.array_equal(obs.cpu().numpy(), expected["obs"])
+    stack = torch.full((0, 4, 84, 84), 7, dtype=torch.uint8, device="cuda")
+    r.step(_dev(lanes[:0]), _dev(things[:0]), stack)
+    r.check_status()
