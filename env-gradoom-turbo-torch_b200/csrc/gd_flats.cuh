@@ -81,8 +81,9 @@ __device__ __forceinline__ float gd_wrap_angle(float a) {
  * Only pixels that no seg and no visplane claimed show this layer, so it is
  * evaluated lazily for exactly those pixels.  The reference resolves every
  * pixel, repairs unresolved ones from the next resolved row below and then
- * from the nearest anchors left and right; the scans below visit only the
- * pixels those repairs would read for the one pixel asked for. */
+ * from the nearest anchors left and right; here a pixel that resolves by
+ * itself costs one probe, and only when some do not is the repair state built,
+ * once per lane and only for the rows that still hold unclaimed pixels. */
 struct GdFlatProbe { bool unresolved, isFloor; int sector; };
 
 /* the part of a probe that depends on the column only */
