@@ -195,6 +195,7 @@ class GraDoomVecEnv:
         self._initialized = torch.zeros(self.num_envs, dtype=torch.bool, device=self.device)
         self._action_matrix = action_matrix(self.device)
         self._info_history = torch.zeros((self.num_envs, 0, 4), dtype=torch.float32, device=self.device)
+        self._state_indices = torch.zeros(self.num_envs, dtype=torch.int32, device=self.device)
         self.action_table = DEATHMATCH_ACTIONS
         self.buttons = DEATHMATCH_BUTTONS
 
@@ -263,6 +264,12 @@ class GraDoomVecEnv:
 
     def device_info_histories(self) -> torch.Tensor:
         return self._info_history
+
+    def active_state_indices(self) -> torch.Tensor:
+        """Index of the scenario state every lane runs (src/gradoom/env.py:392-394, 1034): one
+        scenario, so all zeros."""
+
+        return self._state_indices
 
     # -- diagnostic RGB --------------------------------------------------
     def _render_rgb(self, first: int, count: int) -> np.ndarray:
