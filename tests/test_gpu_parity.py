@@ -402,3 +402,38 @@ def test_sixty_four_things_per_lane_and_empty_batches(pkg, oracle, scenes):
     stack = torch.full((0, 4, 84, 84), 7, dtype=torch.uint8, device="cuda")
     r.step(_dev(lanes[:0]), _dev(things[:0]), stack)
     r.check_status()
+
+
+@pytest.mark.gpu
+def test_render_step_captures_into_a_cuda_graph(pkg, scenes):
+    """The entry points allocate nothing and never synchronise, so a step can be
+    captured once and replayed on new records written into the same buffers."""
+
+    import torch
+
+    from gradoom_b200 import stepper
+
+    sc, blob = scenes("c1")
+    la, ta = stepper.random_lanes(sc, 300, 4, seed=41)
+    lb, tb = stepper.random_lanes(sc, 300, 4, seed=42)
+    r = _renderer(blob, 4)
+    lanes, things = _dev(la), _dev(ta)
+    stack = torch.zeros((300, 4, 84, 84), dtype=torch.uint8, device="cuda")
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        r.step(lanes, things, stack)                 # warm-up outside the capture
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        r.step(lanes, things, stack)
+    stack.zero_()
+    expect = torch.zeros_like(stack)
+    for records in ((la, ta), (lb, tb), (la, ta)):
+        lanes.copy_(_dev(records[0])); things.copy_(_dev(records[1]))
+        graph.replay()
+        r.step(_dev(records[0]), _dev(records[1]), expect)
+    torch.cuda.synchronize()
+    r.check_status()
+    assert torch.equal(stack, expect)
+    assert not torch.equal(stack[:, 3], stack[:, 2])
