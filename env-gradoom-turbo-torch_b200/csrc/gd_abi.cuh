@@ -169,7 +169,8 @@ extern "C" size_t gd_renderer_shared_bytes(const gd_renderer *r) { return r ? r-
 
 static int gd_launch(const gd_renderer *r, const int32_t *lanes, const gd_thing *things, int n, int flags,
                      uint8_t *stack, const uint8_t *reset_mask, uint8_t *obs_out, uint8_t *indexed_out,
-                     uint8_t *rgb_out, void *scratch, size_t scratch_bytes, int *status, void *stream) {
+                     uint8_t *rgb_out, void *scratch, size_t scratch_bytes, int *status, void *stream,
+                     int ring_head = 0) {
   if (!r || !lanes || !scratch || !status) return GD_ERR_NULL;
   if (r->maxThings > 0 && !things) return GD_ERR_NULL;
   if (n < 0) return GD_ERR_SIZE;
@@ -181,7 +182,7 @@ static int gd_launch(const gd_renderer *r, const int32_t *lanes, const gd_thing 
   GdParams p;
   p.sc = r->sc;
   p.lanes = lanes; p.things = things; p.maxThings = r->maxThings; p.n = n; p.flags = flags;
-  p.stack = stack; p.resetMask = reset_mask; p.obsOut = obs_out; p.indexedOut = indexed_out; p.rgbOut = rgb_out;
+  p.stack = stack; p.ringHead = ring_head; p.resetMask = reset_mask; p.obsOut = obs_out; p.indexedOut = indexed_out; p.rgbOut = rgb_out;
   p.scratch = (uint8_t *)scratch; p.status = status;
   p.queueOffset = (size_t)r->ctas * gd_scratch_per_cta(r->sc.W, r->sc.S);
   p.stageMask = r->stageMask; p.secWallsN = r->secWallsN; p.vtxWallsN = r->vtxWallsN; p.V = r->V;
@@ -196,6 +197,27 @@ extern "C" int gd_render_step(const gd_renderer *r, const int32_t *lanes, const 
   if (!stack) return GD_ERR_NULL;
   int flags = GD_F_STACK_ROLL | (mask_hud ? GD_F_MASK_HUD : GD_F_DRAW_HUD);
   return gd_launch(r, lanes, (const gd_thing *)things, n, flags, stack, nullptr, nullptr, nullptr, nullptr, scratch,
+                   scratch_bytes, status, stream);
+}
+
+extern "C" int gd_render_step_ring(const gd_renderer *r, const int32_t *lanes, const void *things, int n,
+                                   int mask_hud, uint8_t *ring, int head, void *scratch, size_t scratch_bytes,
+                                   int *status, void *stream) {
+  if (r && n == 0) return GD_OK;   /* an empty batch needs no buffers */
+  if (!ring) return GD_ERR_NULL;
+  if (head < 0 || head >= GD_STACK) return GD_ERR_SIZE;
+  int flags = GD_F_STACK_RING | (mask_hud ? GD_F_MASK_HUD : GD_F_DRAW_HUD);
+  return gd_launch(r, lanes, (const gd_thing *)things, n, flags, ring, nullptr, nullptr, nullptr, nullptr, scratch,
+                   scratch_bytes, status, stream, head);
+}
+
+extern "C" int gd_render_reset_ring(const gd_renderer *r, const int32_t *lanes, const void *things, int n,
+                                    int mask_hud, const uint8_t *reset_mask, uint8_t *ring, void *scratch,
+                                    size_t scratch_bytes, int *status, void *stream) {
+  if (r && n == 0) return GD_OK;   /* an empty batch needs no buffers */
+  if (!ring || !reset_mask) return GD_ERR_NULL;
+  int flags = GD_F_STACK_RING | GD_F_STACK_FILL | (mask_hud ? GD_F_MASK_HUD : GD_F_DRAW_HUD);
+  return gd_launch(r, lanes, (const gd_thing *)things, n, flags, ring, reset_mask, nullptr, nullptr, nullptr, scratch,
                    scratch_bytes, status, stream);
 }
 

@@ -35,6 +35,7 @@
 #define GD_F_STACK_ROLL 4   /* shift the stack by one slot and append */
 #define GD_F_STACK_FILL 8   /* write all four slots of lanes whose mask byte is set */
 #define GD_F_WRITE_OBS 16   /* write plain (n,84,84) observations to obsOut */
+#define GD_F_STACK_RING 32  /* the stack is a mirrored ring of eight slots per lane (see gd_render_step_ring) */
 
 struct GdParams {
   GdScene sc;
@@ -43,7 +44,8 @@ struct GdParams {
   int maxThings;
   int n;
   int flags;
-  uint8_t *stack;            /* n x 4 x 84 x 84 */
+  uint8_t *stack;            /* n x 4 x 84 x 84, or n x 8 x 84 x 84 with GD_F_STACK_RING */
+  int ringHead;              /* GD_F_STACK_RING: slot 0..3 that takes the new frame (and slot + 4) */
   const uint8_t *resetMask;  /* n, for GD_F_STACK_FILL */
   uint8_t *obsOut;           /* n x 84 x 84, optional */
   uint8_t *indexedOut;       /* n x 240 x 320, optional */
@@ -399,7 +401,23 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
         uint4 *dst = (uint4 *)(p.obsOut + (size_t)l * GD_OBS * GD_OBS);
         for (int i = tid; i < vecs; i += GD_THREADS) dst[i] = src[i];
       }
-      if (p.stack) {
+      if (p.stack && (p.flags & GD_F_STACK_RING)) {
+        /* mirrored ring: no old slot is read or moved */
+        uint4 *s0 = (uint4 *)(p.stack + (size_t)l * 2 * GD_STACK * GD_OBS * GD_OBS);
+        if (p.flags & GD_F_STACK_FILL) {
+          for (int i = tid; i < vecs; i += GD_THREADS) {
+            uint4 val = src[i];
+#pragma unroll
+            for (int k = 0; k < 2 * GD_STACK; ++k) s0[k * vecs + i] = val;
+          }
+        } else {
+          for (int i = tid; i < vecs; i += GD_THREADS) {
+            uint4 val = src[i];
+            s0[p.ringHead * vecs + i] = val;
+            s0[(p.ringHead + GD_STACK) * vecs + i] = val;
+          }
+        }
+      } else if (p.stack) {
         uint4 *s0 = (uint4 *)(p.stack + (size_t)l * GD_STACK * GD_OBS * GD_OBS);
         if (p.flags & GD_F_STACK_FILL) {
           for (int i = tid; i < vecs; i += GD_THREADS) {

@@ -162,13 +162,15 @@ class GraDoomVecEnv:
     def __init__(self, sc: gdscene.Scene, num_envs: int, *, device, producer=None, max_things: int = 16,
                  frame_skip: int = 2, render_mode: str | None = None, obs_crop=(0, 32, 0, 0),
                  obs_crop_mode: str = "mask", obs_layout: str = "chw", episode_timeout: int = 4200,
-                 producer_seed: int = 0):
+                 producer_seed: int = 0, stack_policy: str = "roll"):
         if num_envs <= 0:
             raise ValueError("num_envs must be positive")
         if render_mode not in (None, "rgb_array"):
             raise ValueError("render_mode must be None or 'rgb_array'")
         if obs_layout not in ("chw", "hwc"):
             raise ValueError("obs_layout must be 'chw' or 'hwc'")
+        if stack_policy not in ("roll", "ring"):
+            raise ValueError("stack_policy must be 'roll' or 'ring'")
         if obs_crop not in (None, (0, 32, 0, 0)) or (obs_crop is not None and obs_crop_mode != "mask"):
             raise ValueError("only obs_crop=None or obs_crop=(0, 32, 0, 0) with obs_crop_mode='mask' is supported")
         self.device = torch.device(device)
@@ -191,7 +193,13 @@ class GraDoomVecEnv:
                                    max_things=max_things, frame_skip=frame_skip, episode_timeout=episode_timeout,
                                    seed=producer_seed)
         self._producer = producer
-        self._frames = torch.zeros((self.num_envs, 4, 84, 84), dtype=torch.uint8, device=self.device)
+        # "roll": the reference's contiguous oldest-first stack, shifted every step.  "ring": eight
+        # slots per lane written twice and never moved; observations are then a strided (N,4,84,84)
+        # view of the same four frames (valid until the next step, like the reference's).
+        self.stack_policy = stack_policy
+        self._ring_head = 3
+        slots = 4 if stack_policy == "roll" else 8
+        self._frames = torch.zeros((self.num_envs, slots, 84, 84), dtype=torch.uint8, device=self.device)
         self._initialized = torch.zeros(self.num_envs, dtype=torch.bool, device=self.device)
         self._action_matrix = action_matrix(self.device)
         self._info_history = torch.zeros((self.num_envs, 0, 4), dtype=torch.float32, device=self.device)
@@ -201,7 +209,10 @@ class GraDoomVecEnv:
 
     # -- helpers ---------------------------------------------------------
     def _device_observations(self) -> torch.Tensor:
-        return self._frames if self.obs_layout == "chw" else self._frames.permute(0, 2, 3, 1)
+        frames = self._frames
+        if self.stack_policy == "ring":
+            frames = frames[:, self._ring_head + 1:self._ring_head + 5]
+        return frames if self.obs_layout == "chw" else frames.permute(0, 2, 3, 1)
 
     def _require_open(self, what: str) -> None:
         if self.closed:
@@ -215,7 +226,10 @@ class GraDoomVecEnv:
                                       dtypes=_ACTION_DTYPES).to(torch.int64)
         self._producer.reset(mask, seeds)
         lanes, things = self._producer.render_inputs()
-        self._renderer.reset(lanes, things, mask, self._frames, mask_hud=self.mask_hud)
+        if self.stack_policy == "ring":
+            self._renderer.reset_ring(lanes, things, mask, self._frames, mask_hud=self.mask_hud)
+        else:
+            self._renderer.reset(lanes, things, mask, self._frames, mask_hud=self.mask_hud)
         self._initialized |= mask
         return self._device_observations(), self._producer.signal_buffer
 
@@ -226,7 +240,11 @@ class GraDoomVecEnv:
         buttons = self._action_matrix[indices]
         rewards, terminated, truncated = self._producer.step(buttons)
         lanes, things = self._producer.render_inputs()
-        self._renderer.step(lanes, things, self._frames, mask_hud=self.mask_hud)
+        if self.stack_policy == "ring":
+            self._ring_head = (self._ring_head + 1) & 3
+            self._renderer.step_ring(lanes, things, self._frames, self._ring_head, mask_hud=self.mask_hud)
+        else:
+            self._renderer.step(lanes, things, self._frames, mask_hud=self.mask_hud)
         return DeviceTransition(self._device_observations(), rewards, terminated, truncated,
                                 self._producer.signal_buffer, self._info_history)
 

@@ -22,7 +22,7 @@ STATUS_THINGS_OVERFLOW = 2
 EXPORTS = (
     "gd_error_string", "gd_renderer_create", "gd_renderer_destroy", "gd_renderer_scratch_bytes",
     "gd_renderer_ctas", "gd_renderer_shared_bytes", "gd_render_step", "gd_render_reset", "gd_render_frames",
-    "gd_render_step_frames", "gd_render_step_host", "gd_static_scratch_bytes", "gd_static_max_walls", "gd_render_step_static",
+    "gd_render_step_frames", "gd_render_step_host", "gd_render_step_ring", "gd_render_reset_ring", "gd_static_scratch_bytes", "gd_static_max_walls", "gd_render_step_static",
 )
 
 _lib = None
@@ -63,6 +63,10 @@ def load() -> ctypes.CDLL:
         lib.gd_render_frames.argtypes = [vp, vp, vp, ci, ci, ci, vp, vp, vp, vp, sz, vp, vp]
         lib.gd_render_step_frames.restype = ci
         lib.gd_render_step_frames.argtypes = [vp, vp, vp, ci, ci, ci, vp, vp, vp, vp, sz, vp, vp]
+        lib.gd_render_step_ring.restype = ci
+        lib.gd_render_step_ring.argtypes = [vp, vp, vp, ci, ci, vp, ci, vp, sz, vp, vp]
+        lib.gd_render_reset_ring.restype = ci
+        lib.gd_render_reset_ring.argtypes = [vp, vp, vp, ci, ci, vp, vp, vp, sz, vp, vp]
         lib.gd_render_step_host.restype = ci
         lib.gd_render_step_host.argtypes = [vp, vp, vp, ci, ci, vp, vp, vp, vp, vp, sz, vp, vp]
         lib.gd_static_scratch_bytes.restype = sz
@@ -222,6 +226,35 @@ class Renderer:
                                               int(include_hud), stack.data_ptr(), _ptr(indexed), _ptr(rgb),
                                               self.scratch.data_ptr(), self.scratch_bytes, self.status.data_ptr(),
                                               self._stream()), "gd_render_step_frames")
+        self.launches += 1
+
+    def _check_ring(self, ring, n):
+        if ring.dtype != torch.uint8 or tuple(ring.shape) != (n, 8, 84, 84) or not ring.is_contiguous():
+            raise ValueError("ring must be a contiguous (N,8,84,84) uint8 tensor")
+        if ring.device != self.device:
+            raise TypeError("ring must live on the renderer's device")
+
+    def step_ring(self, lanes, things, ring, head, mask_hud=True):
+        """One step on the mirrored ring: the new frame goes to slots ``head`` and
+        ``head + 4``; ``ring[:, head + 1:head + 5]`` is then the four-frame window."""
+
+        n = self._inputs(lanes, things)
+        self._check_ring(ring, n)
+        _check(self.lib.gd_render_step_ring(self.handle, lanes.data_ptr(), things.data_ptr(), n, int(mask_hud),
+                                            ring.data_ptr(), int(head), self.scratch.data_ptr(), self.scratch_bytes,
+                                            self.status.data_ptr(), self._stream()), "gd_render_step_ring")
+        self.launches += 1
+
+    def reset_ring(self, lanes, things, reset_mask, ring, mask_hud=True):
+        n = self._inputs(lanes, things)
+        self._check_ring(ring, n)
+        if reset_mask.dtype not in (torch.bool, torch.uint8) or tuple(reset_mask.shape) != (n,):
+            raise TypeError("reset_mask must be a bool (N,) tensor")
+        mask = reset_mask.contiguous().view(torch.uint8) if reset_mask.dtype == torch.bool else reset_mask
+        _check(self.lib.gd_render_reset_ring(self.handle, lanes.data_ptr(), things.data_ptr(), n, int(mask_hud),
+                                             mask.data_ptr(), ring.data_ptr(), self.scratch.data_ptr(),
+                                             self.scratch_bytes, self.status.data_ptr(), self._stream()),
+               "gd_render_reset_ring")
         self.launches += 1
 
     def _check_stack(self, stack, n):

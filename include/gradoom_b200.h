@@ -98,6 +98,24 @@ int gd_render_reset(const gd_renderer *r, const int32_t *lanes, const void *thin
                     void *stream);
 
 /*
+ * gd_render_step / gd_render_reset on a mirrored ring instead of the reference's
+ * oldest-first stack, for callers that accept a strided view: `ring` is
+ * n x 8 x 84 x 84 u8, the new frame goes to slots `head` and `head + 4`
+ * (head = step count mod 4, 0..3), and slots head+1 .. head+4 of every lane are
+ * then its last four frames, oldest first -- the same (n,4,84,84) window the
+ * reference keeps (src/gradoom/engine.py:9545-9547), with a lane stride of eight
+ * slots.  No old slot is read or moved: 14 KB written per lane instead of 21 KB
+ * read + 28 KB written.  The reset variant writes all eight slots of the masked
+ * lanes (src/gradoom/engine.py:2443-2450), so their window is the reset frame
+ * four times whatever `head` is.
+ */
+int gd_render_step_ring(const gd_renderer *r, const int32_t *lanes, const void *things, int n, int mask_hud,
+                        uint8_t *ring, int head, void *scratch, size_t scratch_bytes, int *status, void *stream);
+int gd_render_reset_ring(const gd_renderer *r, const int32_t *lanes, const void *things, int n, int mask_hud,
+                         const uint8_t *reset_mask, uint8_t *ring, void *scratch, size_t scratch_bytes,
+                         int *status, void *stream);
+
+/*
  * Stateless frames, any subset of (NULL = not wanted):
  *   obs_out      n x 84 x 84 u8       render_reference_frame (engine.py:15436-15451)
  *   indexed_out  n x 240 x 320 u8     _render_native_indexed_frame (15338-15379)

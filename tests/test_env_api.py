@@ -112,3 +112,37 @@ def test_validation_errors(pkg, scenes):
     assert obs.shape == (2, 84, 84, 4)
     e.close()
     hwc.close()
+
+
+@pytest.mark.gpu
+def test_ring_stack_policy_shows_the_same_windows_as_the_rolled_stack(pkg, scenes):
+    """Two environments with the same seeds, one keeping the reference's rolled stack and one the
+    mirrored ring: observations equal after every reset and step, including masked auto-resets."""
+
+    import torch
+
+    from gradoom_b200.env import GraDoomVecEnv
+
+    sc, _ = scenes("c1")
+    n = 96
+    envs = [GraDoomVecEnv(sc, n, device="cuda", max_things=8, episode_timeout=10, producer_seed=3, stack_policy=p)
+            for p in ("roll", "ring")]
+    everyone = torch.ones(n, dtype=torch.bool, device="cuda")
+    seeds = torch.arange(n, device="cuda") + 1
+    first = [e.reset_device(everyone, seeds)[0] for e in envs]
+    assert torch.equal(first[0], first[1]) and tuple(first[1].shape) == (n, 4, 84, 84)
+    g = torch.Generator(device="cuda").manual_seed(4)
+    for step in range(11):
+        actions = torch.randint(0, 17, (n,), device="cuda", generator=g)
+        if step == 5:                        # a masked reset of a third of the lanes between steps
+            mask = (torch.arange(n, device="cuda") % 3) == 0
+            partial = [e.reset_device(mask, seeds + 100)[0] for e in envs]
+            assert torch.equal(partial[0], partial[1])
+        out = [e.step_and_reset_device(actions, seeds + 1000 * (step + 1)) for e in envs]
+        assert torch.equal(out[0].observations, out[1].observations), step
+        assert torch.equal(out[0].final_observations, out[1].final_observations), step
+    hwc = GraDoomVecEnv(sc, 4, device="cuda", max_things=8, obs_layout="hwc", stack_policy="ring")
+    assert tuple(hwc.reset_device(torch.ones(4, dtype=torch.bool, device="cuda"), seeds[:4])[0].shape) == (4, 84, 84, 4)
+    for e in envs + [hwc]:
+        e.check_status()
+        e.close()
