@@ -50,9 +50,10 @@ WORKLOADS = {
     "c3": {"lanes": 1024, "things": 12, "rgb": True, "map": "32-sector 4x8 map"},
     "c4": {"lanes": 8192, "things": 32, "rgb": False, "map": "256-sector 16x16 map with diagonals"},
 }
-# dram__bytes_read.sum + dram__bytes_write.sum of one render launch at 4096 lanes (a one-pass ncu
-# capture of this file's default command), per lane; mostly the oldest-first roll of the frame stack
-DRAM_TRAFFIC_PER_LANE = 170.5e6 / 4096
+# dram__bytes_read.sum + dram__bytes_write.sum of one render launch at 4096 lanes (one-pass ncu captures
+# of this file's default command and of --stack-policy roll), per lane; the rolled stack moves three old
+# slots per step, the ring only writes (and part of what it writes is still in L2 when the kernel ends)
+DRAM_TRAFFIC_PER_LANE = {"roll": 170.5e6 / 4096, "ring": 27.3e6 / 4096}
 
 
 def measured_peaks():
@@ -212,9 +213,18 @@ def run_ours(args):
     renderer = native.Renderer(blob, device, THINGS)
     stack = torch.zeros((n, 4, 84, 84), dtype=torch.uint8, device=device)
     rgb = torch.empty((n, 240, 320, 3), dtype=torch.uint8, device=device) if spec["rgb"] else None
+    # timed leg: the mirrored eight-slot ring (no old frame is moved) unless --stack-policy roll asks for
+    # the reference's contiguous rolled stack; the RGB workload and the host-buffer leg use the rolled one
+    use_ring = args.stack_policy == "ring" and rgb is None
+    ring = torch.zeros((n, 8, 84, 84), dtype=torch.uint8, device=device) if use_ring else None
+    ring_head = 3
 
     def render_step():
-        if rgb is None:
+        nonlocal ring_head
+        if use_ring:
+            ring_head = (ring_head + 1) & 3
+            renderer.step_ring(lanes, things, ring, ring_head)
+        elif rgb is None:
             renderer.step(lanes, things, stack)
         else:
             renderer.step_frames(lanes, things, stack, rgb=rgb)
@@ -224,6 +234,8 @@ def run_ours(args):
     producer.reset(everyone, lane_ids + 1)
     lanes, things = producer.render_inputs()
     renderer.reset(lanes, things, everyone, stack)
+    if use_ring:
+        renderer.reset_ring(lanes, things, everyone, ring)
     actions = torch.randint(0, 17, (args.warmup + 2 * args.steps + 8, n), device=device,
                             generator=torch.Generator(device=device).manual_seed(20260813 + rank))
     from gradoom_b200.env import action_matrix
@@ -352,9 +364,11 @@ def run_ours(args):
                                    + ("obs and RGB24 frame every step" if rgb is not None else "obs only"),
                        "lanes_per_gpu": n, "l2": "flushed with a 256 MiB write between timed steps",
                        "ctas": renderer.ctas, "shared_bytes_per_cta": renderer.shared_bytes,
-                       "stack_policy": "roll (read 3 + write 4 slots per lane)"},
+                       "stack_policy": "mirrored ring (write 2 of 8 slots per lane, no reads)" if use_ring
+                       else "roll (read 3 + write 4 slots per lane)"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": DRAM_TRAFFIC_PER_LANE * n if (workload, n) == (WORKLOAD, 4096) else None,
+                         "traffic": DRAM_TRAFFIC_PER_LANE[args.stack_policy] * n
+                         if (workload, n) == (WORKLOAD, 4096) else None,
                          "traffic_source": "ncu capture of this command at 4096 lanes/GPU", "peak_source": peak_kind,
                          "algorithmic_bytes_per_launch": bytes_per_frame * n,
                          "kernel_ms": avg_ms, "pixels_per_s": 320 * 208 * n / (avg_ms / 1000.0),
@@ -506,6 +520,8 @@ def main():
                     help="benchmark configuration (default: the headline one)")
     ap.add_argument("--lanes", type=int, default=0, help="lanes per GPU (default: the workload's own count)")
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg (profiling captures)")
+    ap.add_argument("--stack-policy", default="ring", choices=["ring", "roll"],
+                    help="frame stack of the timed leg: mirrored eight-slot ring, or the reference's rolled stack")
     ap.add_argument("--no-graph", action="store_true", help="c5 only: launch the rollout eagerly instead of as a CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
