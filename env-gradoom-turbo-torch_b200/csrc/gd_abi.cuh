@@ -45,6 +45,17 @@ extern "C" const char *gd_error_string(int code) {
   }
 }
 
+/* The dynamic shared-memory limit belongs to the kernel on a device, not to one
+ * renderer: every renderer raises it to the most the device allows beside the
+ * kernel's static shared memory, so renderers of different scenes can live side
+ * by side. */
+static bool gd_raise_shared_limit(int maxOptin) {
+  cudaFuncAttributes fa;
+  if (cudaFuncGetAttributes(&fa, gd_render_kernel) != cudaSuccess) return false;
+  return cudaFuncSetAttribute(gd_render_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              maxOptin - (int)fa.sharedSizeBytes) == cudaSuccess;
+}
+
 extern "C" int gd_renderer_create(const void *blob_header_host, const void *blob_dev, size_t blob_bytes, int device,
                                   int max_things, gd_renderer **out) {
   if (!blob_header_host || !blob_dev || !out) return GD_ERR_NULL;
@@ -121,8 +132,7 @@ extern "C" int gd_renderer_create(const void *blob_header_host, const void *blob
   int rc = GD_OK;
   if ((size_t)maxOptin < r->smemBytes) {
     rc = GD_ERR_SHARED;
-  } else if (cudaFuncSetAttribute(gd_render_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)r->smemBytes) !=
-             cudaSuccess) {
+  } else if (!gd_raise_shared_limit(maxOptin)) {
     rc = GD_ERR_CUDA;
   } else {
     int perSm = 0;
@@ -175,6 +185,9 @@ static int gd_launch(const gd_renderer *r, const int32_t *lanes, const gd_thing 
   if (r->maxThings > 0 && !things) return GD_ERR_NULL;
   if (n < 0) return GD_ERR_SIZE;
   if (n == 0) return GD_OK;
+  int current = -1;
+  if (cudaGetDevice(&current) != cudaSuccess) return GD_ERR_CUDA;
+  if (current != r->device) return GD_ERR_DEVICE;   /* the launch goes to the current device */
   if (scratch_bytes < gd_renderer_scratch_bytes(r)) return GD_ERR_SCRATCH;
   uintptr_t align = (uintptr_t)lanes | (uintptr_t)things | (uintptr_t)stack | (uintptr_t)obs_out |
                     (uintptr_t)indexed_out | (uintptr_t)rgb_out | (uintptr_t)scratch;
@@ -265,6 +278,15 @@ extern "C" int gd_render_step_host(const gd_renderer *r, const int32_t *lanes_ho
   if (r->maxThings > 0 && (!things_host || !things_dev)) return GD_ERR_NULL;
   if (n < 0) return GD_ERR_SIZE;
   if (n == 0) return GD_OK;
+  /* every argument is checked before the first copy is queued */
+  if (!scratch || !status) return GD_ERR_NULL;
+  if (scratch_bytes < gd_renderer_scratch_bytes(r)) return GD_ERR_SCRATCH;
+  if (((uintptr_t)lanes_dev | (uintptr_t)things_dev | (uintptr_t)stack | (uintptr_t)scratch) & 15) return GD_ERR_ALIGN;
+  {
+    int current = -1;
+    if (cudaGetDevice(&current) != cudaSuccess) return GD_ERR_CUDA;
+    if (current != r->device) return GD_ERR_DEVICE;
+  }
   cudaStream_t s = (cudaStream_t)stream;
   size_t thingStride = (size_t)(r->maxThings > 0 ? r->maxThings : 1) * sizeof(gd_thing);
   if (cudaMemcpyAsync(lanes_dev, lanes_host, (size_t)n * GD_LANE_WORDS * 4, cudaMemcpyHostToDevice, s) != cudaSuccess)
@@ -374,7 +396,7 @@ extern "C" int gd_render_step_static(const gd_renderer *r, const int32_t *lanes,
   p.sc = r->sc;
   p.lanes = lanes; p.things = (const gd_thing *)things; p.maxThings = r->maxThings; p.n = n;
   p.flags = GD_F_STACK_ROLL | (mask_hud ? GD_F_MASK_HUD : GD_F_DRAW_HUD);
-  p.stack = stack; p.resetMask = nullptr; p.obsOut = nullptr; p.indexedOut = nullptr; p.rgbOut = nullptr;
+  p.stack = stack; p.ringHead = 0; p.resetMask = nullptr; p.obsOut = nullptr; p.indexedOut = nullptr; p.rgbOut = nullptr;
   p.scratch = scratch; p.status = status;
   /* lane queue: the last 16 bytes of the array; zero when the library is
    * loaded and left at zero by every launch */

@@ -31,7 +31,6 @@ typedef long long i64;
 #define GD_STATUS_EVENT_OVERFLOW 1   /* a column produced more clip events than the scratch holds */
 #define GD_STATUS_THINGS_OVERFLOW 2  /* a lane lists more things than the configured maximum */
 #define GD_STATUS_BAD_SECTOR 4       /* a state record points outside the scene */
-#define GD_STATUS_FALLBACK_OVERFLOW 8 /* more unclaimed pixels than the fallback queue holds */
 
 struct GdScene {
   int W, S, T, texH, texW, P, sprH, sprW, Q, wpnH, wpnW, wpnTics, nStarts, B, nbDirect, wpnAvailable;

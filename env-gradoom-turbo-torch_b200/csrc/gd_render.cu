@@ -211,16 +211,6 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
   GdRowProj *rowproj = stagedRowproj ? stagedRowproj
                                      : (GdRowProj *)(myScratch + GD_SCRATCH_FIXED + gd_scratch_plane_bytes(sc.S));
 
-#ifdef GD_PROFILE_PHASES
-  if (tid == 0 && blockIdx.x == 0) gdProfile = (unsigned long long *)(p.status + 8);
-  long long gdT0 = clock64();
-  const long long gdStartClock = gdT0;
-  unsigned long long gdStartNs;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gdStartNs));
-#define GD_BEAT(ph) do { __syncthreads(); if (tid == 0) { long long t = clock64(); atomicAdd((unsigned long long *)(p.status + 8) + (ph), (unsigned long long)(t - gdT0)); gdT0 = t; } } while (0)
-#else
-#define GD_BEAT(ph) do {} while (0)
-#endif
   /* Lanes differ a lot in cost (a long corridor crosses many sectors), so the
    * persistent CTAs take lanes from a shared counter instead of a fixed stride.
    * The counter pair lives behind the event scratch and is left at zero by the
@@ -233,7 +223,6 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
     __syncthreads();
     const int l = nextLane;
     if (l >= p.n) break;
-    GD_BEAT(1);
     if (p.flags & GD_F_STACK_FILL) {
       if (p.resetMask && !p.resetMask[l]) continue;  /* uniform across the CTA */
     }
@@ -295,7 +284,6 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
     }
     if (tid == GD_THREADS - 1) sh.misc[0] = pointSector[64] == 0x7fffffff ? 0 : pointSector[64];
     __syncthreads();
-    GD_BEAT(2);
     gd_wall_spans(sc, v, sh);
     /* row projection tables, for the walls that passed the frustum test (the
      * walk selects no other wall) */
@@ -305,7 +293,6 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
       if (sector >= 0) gd_rowproj_setup(v, sh.walls[w], sc.secF[sector * 2 + (slot & 1)], rowproj[w * 4 + slot]);
     }
     __syncthreads();
-    GD_BEAT(3);
     const short *frustumList = (const short *)sh.hitD;
     const int frustumListed = sh.misc[2];
     for (int i = tid; i < frustumListed; i += GD_THREADS) {   /* walls outside the frustum own no column */
@@ -327,7 +314,6 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
       sh.blockingWall[tid] = (short)bw;
     }
     __syncthreads();
-    GD_BEAT(4);
     gd_walk(sc, v, sh, events, eventCount, rowproj, p.status, sh.misc[0]);
     __syncthreads();
     /* Rows no seg ever claimed show the per-pixel flat fallback.  They are
@@ -358,13 +344,10 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
       gd_masked_pass(sc, v, sh);
       __syncthreads();
     }
-    GD_BEAT(5);
     gd_sprites(sc, v, sh, events, eventCount, nThings);
     __syncthreads();
-    GD_BEAT(6);
     gd_weapon(sc, sh.lane, sh.frame);
     __syncthreads();
-    GD_BEAT(7);
     const bool wantFull = p.indexedOut != nullptr || p.rgbOut != nullptr;
     if (p.flags & GD_F_DRAW_HUD) {
       gd_hud(sc, sh, sh.lane, sh.frame + GD_VH * GD_SW);
@@ -390,7 +373,6 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
         dst[q * 3 + 2] = (p2 >> 16) | (p3 << 8);
       }
     }
-    GD_BEAT(8);
     if (p.stack || p.obsOut) {
       int srcRows = (p.flags & GD_F_MASK_HUD) ? GD_VH : GD_SCREEN_H;
       gd_resize(sh.frame, sh.pal64, srcRows, sh.obs);
@@ -437,14 +419,6 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
       }
     }
   }
-#ifdef GD_PROFILE_PHASES
-  if (tid == 0) {
-    unsigned long long ns;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
-    atomicAdd((unsigned long long *)(p.status + 8) + 12, ns - gdStartNs);
-    atomicAdd((unsigned long long *)(p.status + 8) + 13, (unsigned long long)(clock64() - gdStartClock));
-  }
-#endif
   if (tid == 0) {
     __threadfence();
     if (atomicAdd(&queue[1], 1u) == gridDim.x - 1) {

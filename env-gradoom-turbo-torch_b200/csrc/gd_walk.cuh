@@ -126,13 +126,6 @@ struct GdIter {
   bool psFromFront;
 };
 
-#ifdef GD_PROFILE_PHASES
-__device__ unsigned long long *gdProfile;   /* decide-phase cycle counters */
-#define GD_TD(m) do { if ((x & 31) == 0) { long long t = clock64(); atomicAdd(gdProfile + 32 + (m), (unsigned long long)(t - gdD0)); gdD0 = t; } } while (0)
-#else
-#define GD_TD(m) do {} while (0)
-#endif
-
 __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWall *walls, const unsigned *ownerMask,
                                  const GdRowProj *rowproj, float *hitD, float *hitA, uint8_t *hitF, int x, float rx,
                                  float ry, const GdColState &c, GdIter &it) {
@@ -140,9 +133,6 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
   const int current = curSector < 0 ? 0 : curSector;
   const float prev = c.prev;
   const int i0 = sc.secOff[current], i1 = sc.secOff[current + 1];
-#ifdef GD_PROFILE_PHASES
-  long long gdD0 = clock64();
-#endif
   /* every rule below looks at the walls of the current sector: test each once
    * and keep the results in this column's slice of shared memory */
   constexpr int kCache = 8;
@@ -192,7 +182,6 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
     }
     if (isfinite(sd)) { distance = sd; wallIndex = sw; }
   }
-  GD_TD(1);
   GdHit hSel = HIT(wallIndex);
   const float *selWall = &sc.walls[wallIndex * 4];
   bool selUsesStart = hSel.along <= 0.5f;
@@ -239,7 +228,6 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
       if (sbd < psd) { psd = sbd; psi = sbi; }
     }
   }
-  GD_TD(2);
   bool hasProjectedSolidOwner = isfinite(psd);
   if (hasProjectedSolidOwner) { distance = psd; wallIndex = psi; }
   GdHit hW = (wallIndex == psPathIndex) ? hSel : HIT(wallIndex);
@@ -249,7 +237,6 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
   bool eoPathIsGeo = hW.geo;
   bool replaceEo = (seo != wallIndex) && (sed > prev + 1e-3f);
   if (replaceEo) { distance = sed; wallIndex = seo; hW = HIT(wallIndex); }
-  GD_TD(3);
   int nopIndex = wallIndex;
   float nopDist = distance;
   bool nopIsGeo = replaceEo ? eoPathIsGeo : hW.geo;
@@ -299,7 +286,6 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
       if (psb && hb.d < npd) { usePsb = true; npd = hb.d; npi = psbIndex; }
     }
   }
-  GD_TD(4);
   bool replaceNp = isfinite(npd);
   if (replaceNp) { distance = npd; wallIndex = npi; hW = HIT(wallIndex); }
   bool finalIsProjected = hW.proj, finalIsGeo = hW.geo;
@@ -330,7 +316,6 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
   float otherFloor = gd_sec_floor(sc, safeOther), otherCeil = gd_sec_ceil(sc, safeOther);
   bool oneSided = otherSector < 0;
   const int32_t *stex = &sc.sideTex[(wallIndex * 2 + side) * 3];
-  GD_TD(5);
   /* Row bounds: per (wall, sector height) tables built once per lane cover the
    * usual case of heights taken from the wall's own two sectors. */
   const GdRowProj *rp = rowproj + wallIndex * 4;
@@ -374,7 +359,6 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
   it.tier[1] = !oneSided && rasterValid && (viewFloor < otherFloor) && stex[1] >= 0 && clowtop < cbot;
   it.tier[2] = !oneSided && rasterValid && (viewCeil > otherCeil) && stex[2] >= 0 && ctop < cupbot;
 
-  GD_TD(6);
   /* traversal decisions (engine.py:13070-13241) */
   bool endpointOnly = valid && !oneSided && !geometric;
   float cnd = GD_INF, ond = GD_INF, csd = GD_INF, osd = GD_INF, gpd = GD_INF;
@@ -439,7 +423,6 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
     it.epEpY = us ? fw[1] : fw[3];
   }
   it.epFwdIdx = epFwdIdx; it.ppbIdx = ppbIdx; it.psPathIndex = psPathIndex; it.psFromFront = psFromFront;
-  GD_TD(7);
 #undef HIT
 #undef HITK
 #undef SHARES_SEL
@@ -637,25 +620,11 @@ __device__ void gd_walk(const GdScene &sc, const GdView &v, const GdShared &sh, 
   c.pendPortalBridgeSector = -1;
   c.pendPortalBridgeExit = 0.0f;
   bool settled = false;
-#ifdef GD_PROFILE_PHASES
-  long long gdW0 = clock64();
-#endif
   int nEvents = 0;
   bool overflow = false;
 
   for (int iter = 0; iter < sc.S; ++iter) {
     if (__all_sync(0xffffffffu, settled)) break;
-#ifdef GD_PROFILE_PHASES
-#define GD_TB(m) do { if ((x & 31) == 0) { long long t = clock64(); atomicAdd((unsigned long long *)(status + 8) + 16 + (m), (unsigned long long)(t - gdW0)); gdW0 = t; } } while (0)
-#else
-#define GD_TB(m) do {} while (0)
-#endif
-    GD_TB(0);
-#ifdef GD_PROFILE_PHASES
-    if ((x & 31) == 0) atomicAdd((unsigned long long *)(status + 8) + 24, 1ull);
-    if (!settled) atomicAdd((unsigned long long *)(status + 8) + 25, 1ull);
-    if (!settled && c.cur >= 0) atomicAdd((unsigned long long *)(status + 8) + 26, 1ull);
-#endif
     GdIter it;
     if (!settled) {
       gd_column_decide(sc, v, sh.walls, sh.ownerMask, rowproj, sh.hitD, sh.hitA, sh.hitF, x, rx, ry, c, it);
@@ -664,7 +633,6 @@ __device__ void gd_walk(const GdScene &sc, const GdView &v, const GdShared &sh, 
       it.ctop = it.clowtop = 0; it.cbot = it.cupbot = 0; it.vis = 0;
       it.rasterValid = false; it.valid = false; it.pskpp = false;
     }
-    GD_TB(1);
     /* aligned four-column wallscan groups (engine.py:12694-12761) */
     bool same = true;
     bool groupValid[3];
@@ -694,7 +662,6 @@ __device__ void gd_walk(const GdScene &sc, const GdView &v, const GdShared &sh, 
       }
     }
     i64 firstVis = __shfl_sync(0xffffffffu, it.vis, quadBase);
-    GD_TB(2);
     if (settled) continue;
 
     const GdColState before = c;
@@ -716,7 +683,6 @@ __device__ void gd_walk(const GdScene &sc, const GdView &v, const GdShared &sh, 
         ev.ceilA = (unsigned char)c.ceilClip; ev.ceilB = (unsigned char)cpb;
         gd_mark_plane(sc, v, sh, x, c.ceilClip, cpb, it.renderCurrent, false, owned, filled);
       }
-      GD_TB(3);
       /* wall tiers */
       GdTierCtx t;
       gd_prep_wall(sc, wv, wallIndex, x, t.hoff, t.vstepBase);
@@ -757,7 +723,6 @@ __device__ void gd_walk(const GdScene &sc, const GdView &v, const GdShared &sh, 
         }
       }
     }
-    GD_TB(4);
     /* clip updates (engine.py:12885-12913) */
     bool hasUpper = it.tex[2] >= 0, hasLower = it.tex[1] >= 0;
     bool drawsUpper = (it.viewCeil > it.otherCeil) && hasUpper;
@@ -820,7 +785,6 @@ __device__ void gd_walk(const GdScene &sc, const GdView &v, const GdShared &sh, 
         nEvents++;
       }
     }
-    GD_TB(5);
     /* traversal update (engine.py:13242-13371) */
     float prior = c.prev;
     float np = prior;
@@ -860,7 +824,6 @@ __device__ void gd_walk(const GdScene &sc, const GdView &v, const GdShared &sh, 
      * state forever; once an iteration changes nothing and draws nothing it can
      * stop. */
     if (before.cur < 0 && !it.rasterValid && !it.pskpp && gd_state_equal(before, c)) settled = true;
-    GD_TB(6);
   }
   eventCount[x] = nEvents < GD_MAX_EVENTS ? nEvents : GD_MAX_EVENTS;
   if (overflow) atomicOr(status, GD_STATUS_EVENT_OVERFLOW);

@@ -114,7 +114,7 @@ class Renderer:
         self.scratch_bytes = int(self.lib.gd_renderer_scratch_bytes(handle))
         # zero-initialised: the tail holds the kernel's lane queue, which every launch leaves at zero
         self.scratch = torch.zeros(self.scratch_bytes, dtype=torch.uint8, device=self.device)
-        self.status = torch.zeros(4 + 320, dtype=torch.int32, device=self.device)
+        self.status = torch.zeros(4, dtype=torch.int32, device=self.device)   # word 0 is the status word
         self.ctas = int(self.lib.gd_renderer_ctas(handle))
         self.shared_bytes = int(self.lib.gd_renderer_shared_bytes(handle))
         self.launches = 0

@@ -47,7 +47,6 @@ enum gd_error {
 #define GD_STATUS_EVENT_OVERFLOW 1
 #define GD_STATUS_THINGS_OVERFLOW 2
 #define GD_STATUS_BAD_SECTOR 4
-#define GD_STATUS_FALLBACK_OVERFLOW 8   /* reserved; never set (the fallback takes as many rounds as it needs) */
 
 typedef struct gd_renderer gd_renderer;
 
@@ -108,6 +107,10 @@ int gd_render_reset(const gd_renderer *r, const int32_t *lanes, const void *thin
  * read + 28 KB written.  The reset variant writes all eight slots of the masked
  * lanes (src/gradoom/engine.py:2443-2450), so their window is the reset frame
  * four times whatever `head` is.
+ * `head` is a launch parameter and the window is a host-side slice: a CUDA
+ * graph that captures ring steps bakes both in, so capture them only in groups
+ * of four consecutive steps starting at head 0 (a replay then advances the ring
+ * exactly once around), and derive the window from the step count after the replay.
  */
 int gd_render_step_ring(const gd_renderer *r, const int32_t *lanes, const void *things, int n, int mask_hud,
                         uint8_t *ring, int head, void *scratch, size_t scratch_bytes, int *status, void *stream);
@@ -151,7 +154,9 @@ int gd_render_step_frames(const gd_renderer *r, const int32_t *lanes, const void
  * 16-byte aligned) `obs_host` is written by the kernel itself as each lane
  * finishes, so no copy remains after the drawing; a pageable one is filled by
  * chunked copies that overlap the drawing of the following chunk.  Either way
- * the result is complete once `stream` has been synchronised.  Same reference call site
+ * the result is complete once `stream` has been synchronised.  Calls on one
+ * renderer share its side stream and events: do not overlap two of them on
+ * different streams.  Same reference call site
  * as gd_render_step (src/gradoom/engine.py:9575-9576), plus the
  * `.to("cpu")` a host-side learner performs on the observation.
  */

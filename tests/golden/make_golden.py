@@ -2,7 +2,8 @@
 
 Run once on a machine that has the upstream sources:
 
-    GRADOOM_REFERENCE_SRC=<upstream checkout>/src/gradoom python tests/golden/make_golden.py [c1 c2 c3 c4 c1m stack flashes pitch]
+    GRADOOM_REFERENCE_SRC=<upstream checkout>/src/gradoom python tests/golden/make_golden.py \
+        [c1 c2 c3 c4 c1m stack flashes pitch fallback c2d c4d c1k]
 
 For each seeded synthetic scene it resets the upstream engine, injects K
 monsters per lane, replays a seeded uniform action stream and, at a few
@@ -25,6 +26,7 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
+OUT = os.environ.get("GRADOOM_GOLDEN_OUT", HERE)    # where the .npz files are written
 sys.path.insert(0, ROOT)
 sys.path.insert(0, HERE)
 
@@ -41,7 +43,14 @@ PLANS = {
     "c3": ("c3", 2, 12, (0, 10)),
     "c4": ("c4", 1, 32, (0, 3)),
     "c1m": ("c1m", 4, 4, (0, 12, 30)),
+    # deeper action streams on the two benchmark maps
+    "c2d": ("c2", 8, 12, (0, 50, 150)),
+    "c4d": ("c4", 4, 32, (0, 20, 60)),
 }
+# Plans whose skipped steps run with the upstream default (fast) observation renderer: the
+# game dynamics never read a rendered frame, so the state at a checkpoint is the same
+# (generate("c1") under both settings gives identical records).
+FAST_STEPPING = {"c2d", "c4d"} | set(filter(None, os.environ.get("GRADOOM_GOLDEN_FAST", "").split(",")))
 ACTION_SEED = 20260813
 
 
@@ -91,6 +100,8 @@ def generate(name, eng, scn, act):
     offsets, coscorr = gdscene.ray_tables()
     out["ray_offsets"], out["ray_coscorr"] = offsets, coscorr
     step = 0
+    if name in FAST_STEPPING:
+        del e.render_frame          # back to the class default while stepping
     for ci, target in enumerate(checkpoints):
         while step < target:
             a = torch.randint(0, 17, (n,), generator=ag)
@@ -106,7 +117,7 @@ def generate(name, eng, scn, act):
         out[f"indexed_{ci}"] = indexed
         out[f"obs_float_{ci}"] = obs_float
         print(name, "checkpoint", target, "things", used, flush=True)
-    np.savez_compressed(os.path.join(HERE, f"golden_{name}.npz"), **out)
+    np.savez_compressed(os.path.join(OUT, f"golden_{name}.npz"), **out)
 
 
 def generate_stack(eng, scn, act):
@@ -142,8 +153,95 @@ def generate_stack(eng, scn, act):
     for key in list(out):
         if key.startswith("things_"):
             out[key] = out[key][:, :kmax].copy()
-    np.savez_compressed(os.path.join(HERE, "golden_stack.npz"), **out)
+    np.savez_compressed(os.path.join(OUT, "golden_stack.npz"), **out)
     print("stack fixture done", flush=True)
+
+
+def generate_fallback(eng, scn, act):
+    """Poses that leave most of the view to the per-pixel flat fallback
+    (engine.py:10956-11171) on the 64-sector map: a player exactly on a portal
+    line, exactly on a vertex, 2**-15 beside a line, and on a line looking along it
+    (standing in the doorway between two rooms).  The pose is written after the reset,
+    public floats and retained fixed-point coordinates together."""
+
+    n, k = 6, 12
+    sc = gdscene.make_grid_scene(gdscene.GRID_CONFIGS["c2"])
+    e, g = make_engine(eng, scn, sc, n, k, seed=97)
+    tab = gdstate.SpriteTables(sc, torch.device("cpu"))
+    poses = [  # x, y, angle (degrees)
+        (512.0, 600.0, 170.0),                # on the portal line x = 512, looking across it
+        (768.0, 1024.0, 200.0),               # on the vertex shared by four rooms
+        (1280.0 + 2.0 ** -15, 700.0, 95.0),   # two fixed-point steps beside a line
+        (900.0, 1536.0, 0.0),                 # on the line y = 1536, looking along it
+        (600.0, 512.0, 200.0),                # on a horizontal portal line
+        (512.0, 600.0, 100.0),                # on the line x = 512, looking almost along it
+    ]
+    x = torch.tensor([p[0] for p in poses], dtype=torch.float32)
+    y = torch.tensor([p[1] for p in poses], dtype=torch.float32)
+    bam = torch.tensor([int(round(p[2] / 360.0 * (1 << 32))) & 0xFFFFFFFF for p in poses], dtype=torch.int64)
+    e.x.copy_(x)
+    e.y.copy_(y)
+    e._x_fixed.copy_(torch.round(x.to(torch.float64) * 65536.0).to(torch.int64))
+    e._y_fixed.copy_(torch.round(y.to(torch.float64) * 65536.0).to(torch.int64))
+    e._angle_bam.copy_(bam)
+    e.angle.copy_(bam.to(torch.float32) * gdstate.BAM_TO_RADIANS)
+    offsets, coscorr = gdscene.ray_tables()
+    out = {"config": np.asarray("c2"), "ray_offsets": offsets, "ray_coscorr": coscorr,
+           "checkpoints": np.asarray([0])}
+    lanes, things, indexed, obs_float = snapshot(e, tab, 64)
+    used = max(int(lanes[:, gdstate.L_THINGS].max()), 1)
+    out["lanes_0"], out["things_0"] = lanes, things[:, :used].copy()
+    out["indexed_0"], out["obs_float_0"] = indexed, obs_float
+    np.savez_compressed(os.path.join(OUT, "golden_fallback.npz"), **out)
+    print("fallback fixture done", flush=True)
+
+
+def generate_c1k(eng, scn, act):
+    """The CPU configuration of the benchmark definition taken literally: c1, 4 lanes,
+    uniform actions, a checkpoint after 1000 agent steps: the renderer's inputs, the
+    indexed frame, and the four-frame stack (engine.py:9545-9548) together with the
+    inputs of the four renders that filled it."""
+
+    n, k, total = 4, 4, 1000
+    sc = gdscene.make_grid_scene(gdscene.GRID_CONFIGS["c1"])
+    e, g = make_engine(eng, scn, sc, n, k, seed=1234)
+    tab = gdstate.SpriteTables(sc, torch.device("cpu"))
+    am = action_matrix(act)
+    ag = torch.Generator().manual_seed(ACTION_SEED)
+    offsets, coscorr = gdscene.ray_tables()
+    out = {"config": np.asarray("c1"), "ray_offsets": offsets, "ray_coscorr": coscorr,
+           "checkpoints": np.asarray([total])}
+    reference_frame = e.render_frame
+    del e.render_frame              # fast default renderer while skipping (see FAST_STEPPING)
+    resets = 0
+    for step in range(total):
+        if step == total - 8:
+            e.render_frame = reference_frame
+        a = torch.randint(0, 17, (n,), generator=ag)
+        _f, _r, term, trunc = e.step(am[a])
+        done = term | trunc
+        if bool(done.any()):
+            e.reset(done, torch.arange(n) + 1000 * (step + 1))
+            resets += int(done.sum())
+        if step >= total - 4:
+            things, counts = gdstate.gather_things(e, tab, max_things=64)
+            lanes = gdstate.pack_lanes(e, counts)
+            s = step - (total - 4)
+            out[f"stack_lanes_{s}"], out[f"stack_things_{s}"] = lanes.numpy(), things.numpy()
+            out[f"stack_done_{s}"] = done.numpy()
+        if step % 100 == 0:
+            print("c1k step", step, flush=True)
+    lanes, things, indexed, obs_float = snapshot(e, tab, 64)
+    used = max(int(lanes[:, gdstate.L_THINGS].max()), 1)
+    kmax = max(used, *(int(out[f"stack_lanes_{s}"][:, gdstate.L_THINGS].max()) for s in range(4)))
+    for s in range(4):
+        out[f"stack_things_{s}"] = out[f"stack_things_{s}"][:, :kmax].copy()
+    out["lanes_0"], out["things_0"] = lanes, things[:, :used].copy()
+    out["indexed_0"], out["obs_float_0"] = indexed, obs_float
+    out["frames"] = e.frames.numpy().copy()
+    out["resets"] = np.asarray(resets)
+    np.savez_compressed(os.path.join(OUT, "golden_c1k.npz"), **out)
+    print("c1k fixture done; lane resets along the way:", resets, flush=True)
 
 
 def generate_pitch(eng, scn, act):
@@ -173,7 +271,7 @@ def generate_pitch(eng, scn, act):
         out[f"things_{ci}"] = things[:, :used].copy()
         out[f"indexed_{ci}"] = indexed
         out[f"obs_float_{ci}"] = obs_float
-    np.savez_compressed(os.path.join(HERE, "golden_pitch.npz"), **out)
+    np.savez_compressed(os.path.join(OUT, "golden_pitch.npz"), **out)
     print("pitch fixture done", flush=True)
 
 
@@ -203,7 +301,7 @@ def generate_flashes(eng, scn, act):
         out[f"things_{ci}"] = things.numpy()[:, :used].copy()
         out[f"rgb_{ci}"] = e.render_native_frame(include_hud=True).numpy()
         out[f"obs_float_{ci}"] = e.render_reference_frame().numpy()
-    np.savez_compressed(os.path.join(HERE, "golden_flashes.npz"), **out)
+    np.savez_compressed(os.path.join(OUT, "golden_flashes.npz"), **out)
     print("flash fixture done", flush=True)
 
 
@@ -217,6 +315,10 @@ def main(argv):
             generate_flashes(eng, scn, act)
         elif name == "pitch":
             generate_pitch(eng, scn, act)
+        elif name == "fallback":
+            generate_fallback(eng, scn, act)
+        elif name == "c1k":
+            generate_c1k(eng, scn, act)
         else:
             generate(name, eng, scn, act)
 

@@ -30,7 +30,7 @@ def _dev(a):
     return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
 
 
-@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4", "c1m", "pitch"])
+@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4", "c1m", "pitch", "fallback", "c2d", "c4d", "c1k"])
 def test_cuda_matches_upstream_fixtures(name, pkg, oracle, scenes):
     data = load_golden(name)
     _sc, blob = scenes(str(data["config"]), (data["ray_offsets"], data["ray_coscorr"]))
@@ -131,6 +131,69 @@ def test_cuda_replays_the_upstream_stack_fixture(pkg, oracle, scenes):
         assert np.abs(stack.cpu().numpy().astype(int) - data[f"frames_{s}"].astype(int)).max() <= 1
 
 
+def test_fallback_fixture_is_mostly_unclaimed_pixels(pkg, oracle, scenes):
+    """Players on portal lines and vertices (engine.py:10956-11171): the frames of the
+    upstream renderer, most of whose pixels come from the per-pixel flat fallback."""
+
+    data = load_golden("fallback")
+    _sc, blob = scenes("c2", (data["ray_offsets"], data["ray_coscorr"]))
+    unowned = oracle.render(blob, data["lanes_0"], data["things_0"])["unowned"]
+    assert int(unowned.max()) > 50000 and int(unowned.sum()) > 200000
+    r = _renderer(blob, 64)
+    _, indexed, _ = r.frames(_dev(data["lanes_0"]), _dev(pad_things(data["things_0"], 64)), indexed=True)
+    r.check_status()
+    assert np.array_equal(indexed.cpu().numpy(), data["indexed_0"])
+
+
+def test_cuda_replays_the_thousand_step_stack(pkg, scenes):
+    """c1, 4 lanes, after 1000 agent steps of the upstream engine: the last four
+    renders rebuild the upstream four-frame stack (engine.py:9545-9548, 2443-2450)
+    within the 1 LSB of its float resize."""
+
+    data = load_golden("c1k")
+    _sc, blob = scenes("c1", (data["ray_offsets"], data["ray_coscorr"]))
+    r = _renderer(blob, 64)
+    n = data["frames"].shape[0]
+    stack = torch.zeros((n, 4, 84, 84), dtype=torch.uint8, device=DEV)
+    for s in range(4):
+        lanes, things = _dev(data[f"stack_lanes_{s}"]), _dev(pad_things(data[f"stack_things_{s}"], 64))
+        r.step(lanes, things, stack)
+        done = data[f"stack_done_{s}"].astype(bool)
+        if done.any():
+            r.reset(lanes, things, _dev(done), stack)
+    r.check_status()
+    assert np.abs(stack.cpu().numpy().astype(int) - data["frames"].astype(int)).max() <= 1
+
+
+def test_two_renderers_of_different_scenes_side_by_side(pkg, oracle, scenes):
+    """A large and a small scene alive on one device, stepped in turns: each keeps
+    its own shared-memory size and scratch."""
+
+    from gradoom_b200 import stepper
+
+    sc4, blob4 = scenes("c4")
+    sc1, blob1 = scenes("c1")
+    big = _renderer(blob4, 8)
+    small = _renderer(blob1, 4)
+    assert big.shared_bytes != small.shared_bytes
+    l4, t4 = stepper.random_lanes(sc4, 6, 8, seed=31)
+    l1, t1 = stepper.random_lanes(sc1, 6, 4, seed=32)
+    e4, e1 = oracle.render(blob4, l4, t4)["obs"], oracle.render(blob1, l1, t1)["obs"]
+    s4 = torch.zeros((6, 4, 84, 84), dtype=torch.uint8, device=DEV)
+    s1 = torch.zeros((6, 4, 84, 84), dtype=torch.uint8, device=DEV)
+    for _ in range(2):
+        big.step(_dev(l4), _dev(t4), s4)
+        small.step(_dev(l1), _dev(t1), s1)
+    third = _renderer(blob1, 4)          # created after the large one was used
+    big.step(_dev(l4), _dev(t4), s4)
+    third.step(_dev(l1), _dev(t1), s1)
+    torch.cuda.synchronize()
+    for r in (big, small, third):
+        r.check_status()
+    assert np.array_equal(s4[:, 3].cpu().numpy(), e4) and np.array_equal(s4[:, 1].cpu().numpy(), e4)
+    assert np.array_equal(s1[:, 3].cpu().numpy(), e1) and np.array_equal(s1[:, 1].cpu().numpy(), e1)
+
+
 def test_full_size_batch_properties(pkg, oracle, scenes):
     """4096 lanes on the 64-sector map: size-independent properties plus an
     oracle check of a lane sample."""
@@ -196,6 +259,11 @@ def test_abi_argument_validation(pkg, scenes):
                               r.scratch.data_ptr(), r.scratch_bytes, r.status.data_ptr(), stream) == -4
     assert lib.gd_render_step(r.handle, dl.data_ptr(), dt.data_ptr(), 0, 1, stack.data_ptr(),
                               r.scratch.data_ptr(), r.scratch_bytes, r.status.data_ptr(), stream) == 0
+    # a renderer bound to another device than the current one
+    if torch.cuda.device_count() > 1:
+        with torch.cuda.device(1):
+            assert lib.gd_render_step(r.handle, dl.data_ptr(), dt.data_ptr(), 4, 1, stack.data_ptr(),
+                                      r.scratch.data_ptr(), r.scratch_bytes, r.status.data_ptr(), stream) == -10
     # a corrupted blob header is refused
     bad = blob.copy()
     bad[:4] = 0

@@ -12,7 +12,7 @@ import pytest
 from conftest import load_golden
 
 
-@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4", "c1m", "pitch"])
+@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4", "c1m", "pitch", "fallback", "c2d", "c4d", "c1k"])
 def test_oracle_matches_upstream_indexed_frames(name, pkg, oracle, scenes):
     data = load_golden(name)
     _sc, blob = scenes(str(data["config"]), (data["ray_offsets"], data["ray_coscorr"]))
@@ -43,6 +43,42 @@ def test_oracle_stack_follows_upstream_roll_and_reset_fill(pkg, oracle, scenes):
         ref = data[f"frames_{s}"]
         assert np.abs(stack.astype(int) - ref.astype(int)).max() <= 1
     assert stack.shape == (n, 4, 84, 84)
+
+
+def test_fallback_fixture_pins_the_flat_fallback_layer(pkg, oracle, scenes):
+    """Poses on portal lines and vertices (engine.py:10956-11171): most of each view
+    is claimed by no seg and no visplane, and the upstream frame is still met bit for bit."""
+
+    data = load_golden("fallback")
+    _sc, blob = scenes("c2", (data["ray_offsets"], data["ray_coscorr"]))
+    out = oracle.render(blob, data["lanes_0"], data["things_0"], mask_hud=True)
+    assert int(out["unowned"].max()) > 50000 and int(out["unowned"].sum()) > 200000
+    assert np.array_equal(out["indexed"], data["indexed_0"])
+
+
+def test_oracle_replays_the_thousand_step_stack(pkg, oracle, scenes):
+    """The CPU configuration of the benchmark definition (c1, 4 lanes) after 1000
+    agent steps: the upstream four-frame stack (engine.py:9545-9548) is the last
+    four renders, oldest first, within the 1 LSB of the float resize; lanes reset in
+    one of those steps carry the reset frame in every older slot (2443-2450)."""
+
+    data = load_golden("c1k")
+    _sc, blob = scenes("c1", (data["ray_offsets"], data["ray_coscorr"]))
+    n = data["frames"].shape[0]
+    stack = np.zeros((n, 4, 84, 84), dtype=np.uint8)
+    known = np.zeros((n, 4), dtype=bool)
+    for s in range(4):
+        obs = oracle.render(blob, data[f"stack_lanes_{s}"], data[f"stack_things_{s}"])["obs"]
+        oracle.stack_update(stack, obs)
+        known[:, :-1] = known[:, 1:]
+        known[:, -1] = True
+        done = data[f"stack_done_{s}"].astype(bool)
+        if done.any():
+            oracle.stack_update(stack, obs, reset_mask=done)
+            known[done] = True
+    assert known.all()
+    assert np.abs(stack.astype(int) - data["frames"].astype(int)).max() <= 1
+    assert int(data["checkpoints"][0]) == 1000
 
 
 def _area_axis(source, output):
