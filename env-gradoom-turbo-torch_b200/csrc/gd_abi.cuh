@@ -14,6 +14,7 @@
 struct gd_renderer {
   GdScene sc;
   int32_t header[GD_HDR_WORDS];
+  const void *blobDev;
   int device;
   int maxThings;
   int ctas;
@@ -48,12 +49,13 @@ extern "C" const char *gd_error_string(int code) {
 /* The dynamic shared-memory limit belongs to the kernel on a device, not to one
  * renderer: every renderer raises it to the most the device allows beside the
  * kernel's static shared memory, so renderers of different scenes can live side
- * by side. */
-static bool gd_raise_shared_limit(int maxOptin) {
+ * by side.  Returns that limit, or -1. */
+static int gd_raise_shared_limit(int maxOptin) {
   cudaFuncAttributes fa;
-  if (cudaFuncGetAttributes(&fa, gd_render_kernel) != cudaSuccess) return false;
-  return cudaFuncSetAttribute(gd_render_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              maxOptin - (int)fa.sharedSizeBytes) == cudaSuccess;
+  if (cudaFuncGetAttributes(&fa, gd_render_kernel) != cudaSuccess) return -1;
+  const int limit = maxOptin - (int)fa.sharedSizeBytes;
+  if (cudaFuncSetAttribute(gd_render_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, limit) != cudaSuccess) return -1;
+  return limit;
 }
 
 extern "C" int gd_renderer_create(const void *blob_header_host, const void *blob_dev, size_t blob_bytes, int device,
@@ -75,6 +77,7 @@ extern "C" int gd_renderer_create(const void *blob_header_host, const void *blob
   for (int c = 0; c < GD_HOST_CHUNKS; ++c) r->chunkDone[c] = nullptr;
   memcpy(r->header, h, sizeof r->header);
   r->device = device;
+  r->blobDev = blob_dev;
   r->maxThings = max_things;
   const uint8_t *d = (const uint8_t *)blob_dev;
   GdScene &sc = r->sc;
@@ -124,17 +127,18 @@ extern "C" int gd_renderer_create(const void *blob_header_host, const void *blob
   int maxOptin = 0, sms = 0;
   cudaDeviceGetAttribute(&maxOptin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-  /* stage as many topology tables as the SM's shared memory still holds */
-  for (int bit = 1; bit <= GD_STAGE_ROWPROJ; bit <<= 1) {
-    size_t extra = gd_stage_bytes(bit, sc.W, sc.S, r->V, r->secWallsN, r->vtxWallsN);
-    if (r->smemBytes + extra + 1024 <= (size_t)maxOptin) { r->smemBytes += extra; r->stageMask |= bit; }
-  }
   int rc = GD_OK;
-  if ((size_t)maxOptin < r->smemBytes) {
-    rc = GD_ERR_SHARED;
-  } else if (!gd_raise_shared_limit(maxOptin)) {
+  const int limit = gd_raise_shared_limit(maxOptin);
+  if (limit < 0) {
     rc = GD_ERR_CUDA;
+  } else if ((size_t)limit < r->smemBytes) {
+    rc = GD_ERR_SHARED;
   } else {
+    /* stage as many topology tables as the SM's shared memory still holds */
+    for (int bit = 1; bit <= GD_STAGE_ROWPROJ; bit <<= 1) {
+      size_t extra = gd_stage_bytes(bit, sc.W, sc.S, r->V, r->secWallsN, r->vtxWallsN);
+      if (r->smemBytes + extra <= (size_t)limit) { r->smemBytes += extra; r->stageMask |= bit; }
+    }
     int perSm = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, gd_render_kernel, GD_THREADS, r->smemBytes) != cudaSuccess ||
         perSm < 1)

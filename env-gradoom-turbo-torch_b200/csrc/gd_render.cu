@@ -26,6 +26,7 @@
 #include "gd_device.cuh"
 
 #define GD_THREADS 320
+#define GD_HUD_MAX_PATCHES 48
 #define GD_WARPS (GD_THREADS / 32)
 #define GD_INF CUDART_INF_F
 
@@ -92,7 +93,7 @@ struct GdShared {
   GdWall *walls;        /* W */
   GdActor *actors;      /* maxThings */
   unsigned long long *pal64;  /* 256: R | G<<20 | B<<40 */
-  uint8_t *obs;         /* 84 x 84 */
+  uint8_t *obs;         /* 84 x 84; shares the memory of hitD, which is free once the sprites are drawn */
   int *misc;            /* 16 ints: start sector, fallback queue length, its unresolved rows' range, GdFlatBounds */
   unsigned *masks;      /* 14 x 320: per-column filled / plane-owned row bitmasks */
   unsigned *pal32;      /* 256: the lane's palette as r | g << 8 | b << 16, for the RGB24 output */
@@ -115,7 +116,6 @@ __host__ __device__ inline size_t gd_shared_bytes(int W, int maxThings) {
   b += gd_align16(GD_SW * 2);
   b += gd_align16(16 * 4);
   b += gd_align16(256 * 8);
-  b += gd_align16(GD_OBS * GD_OBS);
   b += gd_align16(64);
   b += gd_align16(14 * GD_SW * 4);
   b += 2 * gd_align16(GD_SW * 4);
@@ -137,7 +137,6 @@ __device__ inline void gd_carve(uint8_t *base, int W, int maxThings, GdShared &s
   s.blockingWall = (short *)(base + o); o += gd_align16(GD_SW * 2);
   s.ownerMask = (unsigned *)(base + o); o += gd_align16(16 * 4);
   s.pal64 = (unsigned long long *)(base + o); o += gd_align16(256 * 8);
-  s.obs = base + o; o += gd_align16(GD_OBS * GD_OBS);
   s.misc = (int *)(base + o); o += gd_align16(64);
   s.masks = (unsigned *)(base + o); o += gd_align16(14 * GD_SW * 4);
   s.maskedDist = (float *)(base + o); o += gd_align16(GD_SW * 4);
@@ -146,6 +145,8 @@ __device__ inline void gd_carve(uint8_t *base, int W, int maxThings, GdShared &s
   s.hitD = (float *)(base + o); o += gd_align16(8 * GD_SW * 4);
   s.hitA = (float *)(base + o); o += gd_align16(8 * GD_SW * 4);
   s.hitF = base + o; o += gd_align16(8 * GD_SW);
+  s.obs = (uint8_t *)s.hitD;
+  static_assert(8 * GD_SW * 4 >= GD_OBS * GD_OBS && 8 * GD_SW * 4 >= (GD_HUD_MAX_PATCHES + 1) * 16, "obs aliases hitD");
   s.walls = (GdWall *)(base + o); o += gd_align16((size_t)W * sizeof(GdWall));
   s.actors = (GdActor *)(base + o);
 }
@@ -430,3 +431,5 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
 }
 
 #include "gd_abi.cuh"
+#include "gd_state.cuh"
+#include "gd_state_abi.cuh"

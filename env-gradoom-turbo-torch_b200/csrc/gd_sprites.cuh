@@ -226,7 +226,6 @@ __device__ void gd_weapon(const GdScene &sc, const int32_t *lane, uint8_t *frame
  * in a fixed order, later ones on top.  Thread 0 lists (patch, x, y), one thread
  * per entry clips it against the canvas, and then every column thread resolves
  * its 32 pixels from the entries that cross its column, topmost first. */
-#define GD_HUD_MAX_PATCHES 48
 
 struct GdHudList { int4 *entries; int *count; };
 

@@ -112,9 +112,11 @@ class EngineStateProducer:
 
     def __init__(self, engine, sc: gdscene.Scene, max_things: int):
         self.engine = engine
-        self.tables = gdstate.SpriteTables(sc, engine.x.device)
+        self.state = gdstate.EngineState(engine)
         self.max_things = max_things
         self.num_envs = engine.x.shape[0]
+        self.renderer = None            # bound by the environment once it owns one
+        self._lanes = self._things = None
 
     @property
     def signal_buffer(self):
@@ -143,9 +145,20 @@ class EngineStateProducer:
             self.engine.render_frame = render_frame
         return rewards, terminated, truncated
 
+    def bind_renderer(self, renderer):
+        self.renderer = renderer
+        dev = renderer.device
+        self._lanes = torch.zeros((self.num_envs, gdstate.LANE_WORDS), dtype=torch.int32, device=dev)
+        self._things = torch.zeros((self.num_envs, max(self.max_things, 1), 4), dtype=torch.int32, device=dev)
+
     def render_inputs(self):
-        things, counts = gdstate.gather_things(self.engine, self.tables, max_things=self.max_things)
-        return gdstate.pack_lanes(self.engine, counts), things
+        """Lane and thing records of the engine's present state, packed on the
+        device by the library (gd_pack_state)."""
+
+        if self.renderer is None:
+            raise RuntimeError("bind_renderer() must be called before render_inputs()")
+        self.renderer.pack_state(self.state.refresh(), self._lanes, self._things)
+        return self._lanes, self._things
 
 
 class GraDoomVecEnv:
@@ -193,6 +206,8 @@ class GraDoomVecEnv:
                                    max_things=max_things, frame_skip=frame_skip, episode_timeout=episode_timeout,
                                    seed=producer_seed)
         self._producer = producer
+        if hasattr(producer, "bind_renderer"):
+            producer.bind_renderer(self._renderer)
         # "roll": the reference's contiguous oldest-first stack, shifted every step.  "ring": eight
         # slots per lane written twice and never moved; observations are then a strided (N,4,84,84)
         # view of the same four frames (valid until the next step, like the reference's).

@@ -23,6 +23,7 @@ EXPORTS = (
     "gd_error_string", "gd_renderer_create", "gd_renderer_destroy", "gd_renderer_scratch_bytes",
     "gd_renderer_ctas", "gd_renderer_shared_bytes", "gd_render_step", "gd_render_reset", "gd_render_frames",
     "gd_render_step_frames", "gd_render_step_host", "gd_render_step_ring", "gd_render_reset_ring", "gd_static_scratch_bytes", "gd_static_max_walls", "gd_render_step_static",
+    "gd_pack_state_scratch_bytes", "gd_pack_state",
 )
 
 _lib = None
@@ -75,6 +76,10 @@ def load() -> ctypes.CDLL:
         lib.gd_static_max_walls.argtypes = []
         lib.gd_render_step_static.restype = ci
         lib.gd_render_step_static.argtypes = [vp, vp, vp, ci, ci, vp, vp, vp]
+        lib.gd_pack_state_scratch_bytes.restype = sz
+        lib.gd_pack_state_scratch_bytes.argtypes = []
+        lib.gd_pack_state.restype = ci
+        lib.gd_pack_state.argtypes = [vp, vp, vp, vp, vp, sz, vp, vp]
         _lib = lib
     return _lib
 
@@ -115,6 +120,8 @@ class Renderer:
         # zero-initialised: the tail holds the kernel's lane queue, which every launch leaves at zero
         self.scratch = torch.zeros(self.scratch_bytes, dtype=torch.uint8, device=self.device)
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)   # word 0 is the status word
+        self.flags_scratch = torch.zeros(int(self.lib.gd_pack_state_scratch_bytes()), dtype=torch.uint8,
+                                         device=self.device)
         self.ctas = int(self.lib.gd_renderer_ctas(handle))
         self.shared_bytes = int(self.lib.gd_renderer_shared_bytes(handle))
         self.launches = 0
@@ -143,6 +150,23 @@ class Renderer:
         if lanes.device != self.device or things.device != self.device:
             raise TypeError("lanes and things must live on the renderer's device")
         return n
+
+    def pack_state(self, engine_state, lanes, things):
+        """Fill ``lanes`` / ``things`` from engine-shaped tensors on the device
+        (``engine_state``: a ``state.EngineState``); two small launches on the
+        current stream, no host synchronisation."""
+
+        n = self._inputs(lanes, things)
+        if engine_state.n != n:
+            raise ValueError(f"the state has {engine_state.n} lanes, the record buffers {n}")
+        if engine_state.device != self.device:
+            raise TypeError("the state tensors must live on the renderer's device")
+        with torch.cuda.device(self.device):
+            _check(self.lib.gd_pack_state(self.handle, ctypes.byref(engine_state.struct), lanes.data_ptr(),
+                                          things.data_ptr(), self.flags_scratch.data_ptr(),
+                                          self.flags_scratch.numel(), self.status.data_ptr(), self._stream()),
+                   "gd_pack_state")
+        self.launches += 2
 
     def step(self, lanes, things, stack, mask_hud=True):
         n = self._inputs(lanes, things)

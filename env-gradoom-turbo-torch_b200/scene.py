@@ -123,6 +123,7 @@ class GridSpec:
     dolls: int = 1
     hud: bool = True
     weapon: bool = True
+    items: int = 0               # map items (pickups) at seeded positions, cycling through the animated kinds
 
 
 # The five workloads of the benchmark definition, by name.
@@ -139,7 +140,16 @@ GRID_CONFIGS = {
     # two-sided lines, for the parity tests of that part of the renderer
     "c1m": GridSpec(rows=4, cols=4, room=256.0, seed=5, wall_textures=8, flats=4,
                     floor_max=64, mid_textures=0.5),
+    # c1 with twelve map items, for the parity tests of the state packer
+    "c1i": GridSpec(rows=4, cols=4, room=256.0, seed=1, wall_textures=8, flats=4,
+                    floor_max=64, items=12),
 }
+
+
+# editor type id of a map item -> index of its resting sprite in the static sprite list, counted
+# from 6 as the reference does (src/gradoom/engine.py:490-508, 1084-1088)
+ITEM_SPRITE_INDEX = {2011: 6, 2012: 7, 2014: 8, 2015: 9, 2018: 10, 2019: 11, 2007: 12, 2048: 13, 2049: 14,
+                     2046: 15, 17: 16, 2005: 17, 2001: 18, 82: 19, 2002: 20, 2003: 21, 2004: 22}
 
 
 def _sprite_patches(rng, count, w, h):
@@ -154,6 +164,23 @@ def _sprite_patches(rng, count, w, h):
         holes = rng.random((h, w)) < 0.04
         atlas[i][outside | holes] = 0
     return atlas, atlas != 0
+
+
+_ITEM_KINDS = (2014, 2015, 2018, 2019, 2011, 2012, 2007, 2001)   # both bonuses, both armours, four still pickups
+
+
+def _scene_meta(spec: GridSpec, static_ids, patches) -> dict:
+    meta = {"spec": spec}
+    if spec.items > 0:
+        # a generator of its own, so the other tables of a seed do not move
+        rng = np.random.default_rng(spec.seed + 2000)
+        spawns = np.zeros((spec.items, 3), dtype=np.float32)
+        spawns[:, 0] = rng.uniform(24, spec.cols * spec.room - 24, size=spec.items).round()
+        spawns[:, 1] = rng.uniform(24, spec.rows * spec.room - 24, size=spec.items).round()
+        types = np.asarray([_ITEM_KINDS[i % len(_ITEM_KINDS)] for i in range(spec.items)], dtype=np.int32)
+        meta["items"] = {"spawns": spawns, "types": types,
+                         "anim_ids": rng.integers(0, patches, size=8).astype(np.int32)}
+    return meta
 
 
 def make_grid_scene(spec: GridSpec) -> Scene:
@@ -404,7 +431,7 @@ def make_grid_scene(spec: GridSpec) -> Scene:
         hud_heights=hud_heights,
         hud_left=hud_left,
         hud_top=hud_top,
-        meta={"spec": spec},
+        meta=_scene_meta(spec, None, P),
     )
 
 
@@ -413,14 +440,14 @@ def make_grid_scene(spec: GridSpec) -> Scene:
 # ---------------------------------------------------------------------------
 
 GD_MAGIC = 0x4744424C
-GD_VERSION = 9
+GD_VERSION = 10
 GD_HDR_WORDS = 128
 GD_HDR_SECTION0 = 48
 
 _HEADER_WORDS = (
     "MAGIC VERSION BYTES WALLS SECTORS VERTICES TEXTURES TEX_H TEX_W SPRITES SPR_H SPR_W "
     "WPN_PATCHES WPN_H WPN_W WPN_TICS STARTS DEATH_FRAMES XDEATH_FRAMES BLOCKING NB_DIRECT "
-    "WPN_AVAILABLE HUD_PATCHES UNSUPPORTED SEC_WALLS_N VTX_WALLS_N MASKED_WALLS_N FLOOR_GROUPS CEIL_GROUPS"
+    "WPN_AVAILABLE HUD_PATCHES UNSUPPORTED SEC_WALLS_N VTX_WALLS_N MASKED_WALLS_N FLOOR_GROUPS CEIL_GROUPS ITEMS"
 ).split()
 H = {name: i for i, name in enumerate(_HEADER_WORDS)}
 
@@ -434,7 +461,7 @@ _SECTIONS = (
     "WPN_ATLAS WPN_OPAQUE WPN_FRAME_IDS WPN_FLASH_IDS WPN_FLASH_LIGHTS HUD_INFO HUD_ATLAS "
     "HUD_OPAQUE FINESINE FINETAN STARTS RAY_OFFSETS RAY_COSCORR TEX_ATLAS_COL SECTOR_BBOX "
     "MASKED_WALLS DAMAGE_ALPHA FLOOR_GROUP_H FLOOR_GROUP_OFF FLOOR_GROUP_SEC CEIL_GROUP_H CEIL_GROUP_OFF "
-    "CEIL_GROUP_SEC"
+    "CEIL_GROUP_SEC ITEM_POS ITEM_INFO ITEM_ANIM"
 ).split()
 SEC = {name: i for i, name in enumerate(_SECTIONS)}
 
@@ -655,6 +682,25 @@ def pack_scene(scene: Scene, ray_table_override=None) -> np.ndarray:
     def info4(a, b, c, d):
         return np.stack((a, b, c, d), axis=1).astype(np.int32)
 
+    # Map items (pickups placed by the map; src/gradoom/engine.py:1084-1088, 2077-2081): an optional
+    # meta["items"] = {"spawns": (I,3) x y z-above-floor, "types": (I,) editor ids, "anim_ids": (8,)}.
+    items = scene.meta.get("items")
+    n_items = 0 if items is None else len(items["types"])
+    item_pos = np.zeros((max(n_items, 1), 4), dtype=np.float32)
+    item_info = np.zeros((max(n_items, 1), 2), dtype=np.int32)
+    item_anim = np.zeros(8, dtype=np.int32)
+    if n_items:
+        spawns = np.asarray(items["spawns"], dtype=np.float32)
+        types = np.asarray(items["types"], dtype=np.int32)
+        item_pos[:, 0:2] = spawns[:, 0:2]
+        item_pos[:, 2] = scene.sector_heights[sector_at(scene, spawns[:, 0], spawns[:, 1]), 0] + spawns[:, 2]
+        item_info[:, 0] = types
+        for i, t in enumerate(types.tolist()):
+            if t not in ITEM_SPRITE_INDEX:
+                raise ValueError(f"unsupported item type {t}")
+            item_info[i, 1] = scene.static_ids[ITEM_SPRITE_INDEX[t] - 6]
+        item_anim[:] = np.asarray(items.get("anim_ids", np.zeros(8)), dtype=np.int32)
+
     sections = {
         "WALLS": walls,
         "WALL_SECTORS": sectors,
@@ -725,6 +771,7 @@ def pack_scene(scene: Scene, ray_table_override=None) -> np.ndarray:
         "DAMAGE_ALPHA": damage_alpha,
         "FLOOR_GROUP_H": floor_groups[0], "FLOOR_GROUP_OFF": floor_groups[1], "FLOOR_GROUP_SEC": floor_groups[2],
         "CEIL_GROUP_H": ceil_groups[0], "CEIL_GROUP_OFF": ceil_groups[1], "CEIL_GROUP_SEC": ceil_groups[2],
+        "ITEM_POS": item_pos, "ITEM_INFO": item_info, "ITEM_ANIM": item_anim,
     }
     assert set(sections) == set(SEC), set(SEC) ^ set(sections)
 
@@ -774,6 +821,7 @@ def pack_scene(scene: Scene, ray_table_override=None) -> np.ndarray:
     header[H["MASKED_WALLS_N"]] = int(masked_walls.size)
     header[H["FLOOR_GROUPS"]] = int(floor_groups[0].size)
     header[H["CEIL_GROUPS"]] = int(ceil_groups[0].size)
+    header[H["ITEMS"]] = n_items
     blob = np.concatenate([header.view(np.uint8)] + chunks)
     assert blob.size == cursor
     return blob

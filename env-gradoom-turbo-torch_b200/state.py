@@ -1,4 +1,4 @@
-"""Per-lane render state: packing engine tensors into the C-ABI records.
+"""Per-lane render state: record layouts and the binding of engine-shaped tensors.
 
 The renderer reads two arrays per call (layout: include/gradoom_b200_layout.h):
 
@@ -6,15 +6,19 @@ The renderer reads two arrays per call (layout: include/gradoom_b200_layout.h):
 * ``things`` ``(N, K, 4) int32`` viewed as 16-byte records -- one drawable actor
   each: position, sprite patch, alive / full-bright flags and blend style.
 
-``pack_lanes`` and ``gather_things`` build them from any object that carries
-the reference engine's lane tensors under the reference's attribute names
-(src/gradoom/engine.py:1653-1934), which is how the environment class adapts a
-state producer to the renderer.  Everything here is elementwise torch code on
-the producer's device; the drawing itself happens in the CUDA library.
+``EngineState`` collects, from any object that carries the reference engine's
+lane tensors under the reference's attribute names and dtypes
+(src/gradoom/engine.py:1653-1934), the table of device pointers
+``gd_engine_state`` that the CUDA library's ``gd_pack_state`` turns into those
+records (sprite-id selection, actor order and view-pose selection of
+src/gradoom/engine.py:13994-14136, 14258-14317, 14328-14682, 2122-2133,
+10648-10658 happen in that kernel, not here).  ``pack_things`` assembles thing
+records from per-actor arrays for synthetic states and tests.
 """
 
 from __future__ import annotations
 
+import ctypes
 import math
 
 import numpy as np
@@ -34,303 +38,129 @@ BAM_TO_RADIANS = 2.0 * math.pi / float(1 << 32)
 
 THING_ALIVE = 1
 THING_BRIGHT = 2
+FLAG_SCREEN_FLASHES = 4
 
-_SLOT_BASE_WEAPON = (0, 0, 2, 3, 5, 6, 7)
-_ENEMY_WALK_FRAME_TICS = (8, 6, 4, 6, 4, 6)
-_ENEMY_IDLE_FRAME_TICS = (10, 10, 8, 10, 10, 10)
-_ENEMY_ATTACK_RECOVERY = (16, 20, 4, 4, 8, 8)
-_TELEPORT_FOG_TOTAL_TICS = 72
-_BULLET_PUFF_FRAME_TICS = 4
+_F32, _I64, _I32, _U8 = torch.float32, torch.int64, torch.int32, torch.uint8
+
+# struct gd_engine_state (include/gradoom_b200.h): (field, engine attribute, dtype, trailing shape key)
+# in declaration order.  Shape keys: None = (n,), an int = (n, that many), a string = (n, that slot count).
+ENGINE_STATE_COUNTS = ("n", "enemy_slots", "projectile_slots", "enemy_projectile_slots", "puff_slots", "items",
+                       "render_screen_flashes", "reserved")
+ENGINE_STATE_POINTERS = (
+    *[(f, f, _F32, None) for f in ("x", "y", "angle", "view_z", "health", "armor", "hud_ready_ammo")],
+    ("x_fixed", "_x_fixed", _I64, None), ("y_fixed", "_y_fixed", _I64, None),
+    ("angle_bam", "_angle_bam", _I64, None), ("pitch_bam", "_pitch_bam", _I64, None),
+    ("player_bob_fixed", "_player_bob_fixed", _I64, None),
+    *[(f, f, _I64, None) for f in ("selected_weapon", "pending_weapon", "mugshot_face_index",
+                                   "mugshot_pain_direction")],
+    *[(f, f, _I32, None) for f in ("episode_time", "weapon_state_cooldown", "weapon_fire_count", "weapon_ready_tics",
+                                   "weapon_raise_cooldown", "weapon_lower_cooldown", "mugshot_pain_tics",
+                                   "mugshot_grin_tics", "attack_held_tics", "damage_count", "bonus_count")],
+    *[(f, f, _U8, None) for f in ("player_dead", "selected_weapon_variant", "mugshot_ouch")],
+    ("hud_ammo_counts", "hud_ammo_counts", _F32, 4), ("weapons", "weapons", _F32, 6),
+    *[(f, f, _F32, "enemy_slots") for f in ("enemy_x", "enemy_y", "enemy_z", "enemy_angle")],
+    *[(f, f, _I64, "enemy_slots") for f in ("enemy_type", "enemy_target_slot", "enemy_death_type")],
+    *[(f, f, _I32, "enemy_slots") for f in ("enemy_animation_tics", "enemy_attack_phase", "enemy_cooldown",
+                                            "enemy_pain_tics", "enemy_death_tics", "enemy_death_elapsed")],
+    *[(f, f, _U8, "enemy_slots") for f in ("enemy_alive", "enemy_death_extreme")],
+    *[(f, f, _F32, "enemy_slots") for f in ("teleport_fog_x", "teleport_fog_y", "teleport_fog_z")],
+    ("teleport_fog_tics", "teleport_fog_tics", _I32, "enemy_slots"),
+    *[(f, f, _F32, "enemy_slots") for f in ("drop_x", "drop_y", "drop_z")],
+    ("drop_type", "drop_type", _I64, "enemy_slots"), ("drop_spawned", "drop_spawned", _U8, "enemy_slots"),
+    *[(f, f, _F32, "projectile_slots") for f in ("projectile_x", "projectile_y", "projectile_z",
+                                                 "projectile_velocity_x", "projectile_velocity_y")],
+    *[(f, f, _I64, "projectile_slots") for f in ("projectile_type", "projectile_impact_type")],
+    *[(f, f, _I32, "projectile_slots") for f in ("projectile_age", "projectile_impact_tics")],
+    ("projectile_alive", "projectile_alive", _U8, "projectile_slots"),
+    *[(f, f, _F32, "enemy_projectile_slots") for f in ("enemy_projectile_x", "enemy_projectile_y",
+                                                       "enemy_projectile_z", "enemy_projectile_velocity_x",
+                                                       "enemy_projectile_velocity_y")],
+    *[(f, f, _I32, "enemy_projectile_slots") for f in ("enemy_projectile_age", "enemy_projectile_impact_tics")],
+    ("enemy_projectile_alive", "enemy_projectile_alive", _U8, "enemy_projectile_slots"),
+    *[(f, f, _F32, "puff_slots") for f in ("hitscan_puff_x", "hitscan_puff_y", "hitscan_puff_z")],
+    ("hitscan_puff_tics", "hitscan_puff_tics", _I32, "puff_slots"),
+    ("item_available", "item_available", _U8, "items"),
+    ("item_animation_initial_tics", "item_animation_initial_tics", _I32, "items"),
+)
+_OPTIONAL = {"damage_count", "bonus_count"}
+_SLOT_SOURCES = {"enemy_slots": "enemy_x", "projectile_slots": "projectile_x",
+                 "enemy_projectile_slots": "enemy_projectile_x", "puff_slots": "hitscan_puff_x",
+                 "items": "item_available"}
+
+
+class EngineStateStruct(ctypes.Structure):
+    """ctypes mirror of ``struct gd_engine_state``."""
+
+    _fields_ = [(name, ctypes.c_int32) for name in ENGINE_STATE_COUNTS] + \
+               [(field, ctypes.c_void_p) for field, _a, _d, _s in ENGINE_STATE_POINTERS]
+
+
+def _as_dtype(t: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    if dtype == _U8 and t.dtype == torch.bool:
+        return t.contiguous().view(torch.uint8)      # same bytes, no copy
+    if t.dtype != dtype:
+        t = t.to(dtype)                              # a producer with other dtypes pays one cast
+    return t.contiguous()
+
+
+class EngineState:
+    """The pointer table of one engine-shaped state object.
+
+    The tensors are looked up once per call of ``refresh`` (their storage may be
+    replaced by the producer between steps); tensors whose dtype already matches
+    the reference's are passed without a copy.  ``keep`` holds whatever had to be
+    cast so the pointers stay valid until the launch has been queued.
+    """
+
+    def __init__(self, src, *, render_screen_flashes: bool | None = None):
+        self.src = src
+        self.flashes = bool(getattr(src, "render_screen_flashes", False)) if render_screen_flashes is None \
+            else bool(render_screen_flashes)
+        self.struct = EngineStateStruct()
+        self.keep: list[torch.Tensor] = []
+        self.refresh()
+
+    def refresh(self) -> "EngineState":
+        src, st = self.src, self.struct
+        self.keep = []
+        n = int(src.x.shape[0])
+        self.device = src.x.device
+        st.n = n
+        for count, attr in _SLOT_SOURCES.items():
+            t = getattr(src, attr, None)
+            setattr(st, count, 0 if t is None else int(t.shape[1]))
+        st.render_screen_flashes = int(self.flashes)
+        st.reserved = 0
+        for field, attr, dtype, shape in ENGINE_STATE_POINTERS:
+            t = getattr(src, attr, None)
+            slots = shape if isinstance(shape, int) or shape is None else getattr(st, shape)
+            if t is None or (isinstance(shape, str) and slots == 0):
+                if t is None and field not in _OPTIONAL and not (isinstance(shape, str) and slots == 0):
+                    raise AttributeError(f"the state producer has no tensor {attr!r}")
+                setattr(st, field, None)
+                continue
+            want = (n,) if slots is None else (n, slots)
+            if tuple(t.shape) != want:
+                raise ValueError(f"{attr} has shape {tuple(t.shape)}, expected {want}")
+            if t.device != self.device:
+                raise TypeError(f"{attr} lives on {t.device}, the state on {self.device}")
+            c = _as_dtype(t, dtype)
+            self.keep.append(c)
+            setattr(st, field, c.data_ptr())
+        return self
+
+    @property
+    def n(self) -> int:
+        return int(self.struct.n)
 
 
 def _f32_bits(t: torch.Tensor) -> torch.Tensor:
     return t.to(torch.float32).contiguous().view(torch.int32)
 
 
-def _public_or_retained(public: torch.Tensor, retained: torch.Tensor) -> torch.Tensor:
-    """Fixed-point coordinate the renderer uses: the retained 16.16 value unless
-    the public float was changed behind it (src/gradoom/engine.py:2122-2133)."""
-
-    visible = retained.to(torch.float32) / FIXED_UNIT
-    return torch.where(public != visible, torch.round(public * FIXED_UNIT).to(torch.int64), retained)
-
-
-def view_angle_bam(angle: torch.Tensor, angle_bam: torch.Tensor) -> torch.Tensor:
-    """Unsigned view BAM, honouring an overridden public angle
-    (src/gradoom/engine.py:10648-10658)."""
-
-    visible = angle_bam.to(torch.float32) * BAM_TO_RADIANS
-    public = torch.bitwise_and(
-        torch.round(torch.remainder(angle, 2.0 * math.pi) / BAM_TO_RADIANS).to(torch.int64),
-        0xFFFFFFFF,
-    )
-    return torch.where(angle != visible, public, angle_bam)
-
-
-def active_weapon(selected_weapon: torch.Tensor, variant: torch.Tensor) -> torch.Tensor:
-    """Internal weapon id 0..7 from the selected slot (src/gradoom/engine.py:4673-4676)."""
-
-    base = torch.as_tensor(_SLOT_BASE_WEAPON, device=selected_weapon.device, dtype=torch.int64)
-    alternate = (selected_weapon == 1) | (selected_weapon == 3)
-    return base[selected_weapon] + (alternate & variant).to(torch.int64)
-
-
 def _u32_as_i32(t: torch.Tensor) -> torch.Tensor:
     t = t.to(torch.int64) & 0xFFFFFFFF
     return torch.where(t >= (1 << 31), t - (1 << 32), t).to(torch.int32)
-
-
-FLAG_SCREEN_FLASHES = 4
-
-
-def pack_lanes(src, thing_counts: torch.Tensor | None = None) -> torch.Tensor:
-    """Build the ``(N, 32) int32`` lane records from engine-shaped tensors."""
-
-    n = src.x.shape[0]
-    dev = src.x.device
-    out = torch.zeros((n, LANE_WORDS), dtype=torch.int32, device=dev)
-    out[:, L_X] = _f32_bits(src.x)
-    out[:, L_Y] = _f32_bits(src.y)
-    out[:, L_ANGLE] = _f32_bits(src.angle)
-    out[:, L_VIEW_Z] = _f32_bits(src.view_z)
-    out[:, L_X_FIXED] = _public_or_retained(src.x, src._x_fixed).to(torch.int32)
-    out[:, L_Y_FIXED] = _public_or_retained(src.y, src._y_fixed).to(torch.int32)
-    out[:, L_ANGLE_BAM] = _u32_as_i32(view_angle_bam(src.angle, src._angle_bam))
-    out[:, L_PITCH_BAM] = src._pitch_bam.to(torch.int32)
-    flags = src.player_dead.to(torch.int32) | (src.mugshot_ouch.to(torch.int32) << 1)
-    if getattr(src, "render_screen_flashes", False):
-        # damage / bonus screen blends (src/gradoom/engine.py:15385-15397)
-        flags = (flags | FLAG_SCREEN_FLASHES | (src.damage_count.to(torch.int32).clamp(0, 113) << 8)
-                 | (src.bonus_count.to(torch.int32).clamp(0, 255) << 16))
-    out[:, L_FLAGS] = flags
-    out[:, L_EPISODE_TIME] = src.episode_time.to(torch.int32)
-    out[:, L_BOB_FIXED] = src._player_bob_fixed.to(torch.int32)
-    if thing_counts is not None:
-        out[:, L_THINGS] = thing_counts.to(torch.int32)
-    out[:, L_WEAPON] = active_weapon(src.selected_weapon, src.selected_weapon_variant).to(torch.int32)
-    out[:, L_WPN_COOLDOWN] = src.weapon_state_cooldown.to(torch.int32)
-    out[:, L_WPN_FIRE_COUNT] = src.weapon_fire_count.to(torch.int32)
-    out[:, L_WPN_READY_TICS] = src.weapon_ready_tics.to(torch.int32)
-    out[:, L_WPN_RAISE] = src.weapon_raise_cooldown.to(torch.int32)
-    out[:, L_WPN_LOWER] = src.weapon_lower_cooldown.to(torch.int32)
-    out[:, L_WPN_PENDING] = src.pending_weapon.to(torch.int32)
-    out[:, L_HEALTH] = _f32_bits(src.health)
-    out[:, L_ARMOR] = _f32_bits(src.armor)
-    out[:, L_READY_AMMO] = _f32_bits(src.hud_ready_ammo)
-    out[:, L_AMMO0:L_AMMO3 + 1] = _f32_bits(src.hud_ammo_counts)
-    owned = (src.weapons != 0).to(torch.int32)
-    shifts = torch.arange(owned.shape[1], device=dev, dtype=torch.int32)
-    out[:, L_WEAPONS_OWNED] = (owned << shifts[None, :]).sum(dim=1).to(torch.int32)
-    out[:, L_FACE_INDEX] = src.mugshot_face_index.to(torch.int32)
-    out[:, L_PAIN_DIRECTION] = src.mugshot_pain_direction.to(torch.int32)
-    out[:, L_PAIN_TICS] = src.mugshot_pain_tics.to(torch.int32)
-    out[:, L_GRIN_TICS] = src.mugshot_grin_tics.to(torch.int32)
-    out[:, L_ATTACK_HELD] = src.attack_held_tics.to(torch.int32)
-    return out
-
-
-def sprite_rotation(viewer_angle: torch.Tensor, actor_angle: torch.Tensor) -> torch.Tensor:
-    """Zero-based clockwise Doom sprite rotation (src/gradoom/engine.py:13994-14009)."""
-
-    relative = torch.remainder(viewer_angle - actor_angle + math.pi / 8, 2 * math.pi)
-    return torch.remainder(torch.floor(relative / (math.pi / 4)).to(torch.int64), 8)
-
-
-def _frame_from_ends(elapsed: torch.Tensor, ends: torch.Tensor, counts: torch.Tensor) -> torch.Tensor:
-    frame = torch.sum(elapsed[..., None] >= ends, dim=-1)
-    return torch.minimum(frame, counts - 1)
-
-
-class SpriteTables:
-    """Device copies of the sprite id tables a Scene carries."""
-
-    def __init__(self, scene, device):
-        def t(a):
-            return torch.as_tensor(np.ascontiguousarray(a), device=device, dtype=torch.int64)
-
-        self.walk = t(scene.enemy_walk_ids)
-        self.attack = t(scene.enemy_attack_ids)
-        self.pain = t(scene.enemy_pain_ids)
-        self.death = t(scene.enemy_death_ids)
-        self.death_counts = t(scene.enemy_death_counts)
-        self.death_ends = torch.cumsum(t(scene.enemy_death_durations), dim=1)
-        self.xdeath = t(scene.enemy_xdeath_ids)
-        self.xdeath_counts = t(scene.enemy_xdeath_counts)
-        self.xdeath_ends = torch.cumsum(t(scene.enemy_xdeath_durations), dim=1)
-        self.flight = t(scene.proj_flight_ids)
-        self.explosion = t(scene.proj_explosion_ids)
-        self.explosion_counts = t(scene.proj_explosion_counts)
-        self.explosion_ends = torch.cumsum(t(scene.proj_explosion_durations), dim=1)
-        self.explosion_total = t(scene.proj_explosion_durations).sum(dim=1)
-        self.fog = t(scene.fog_ids)
-        self.puff = t(scene.puff_ids)
-        self.static = t(scene.static_ids)
-        self.starts = torch.as_tensor(scene.player_starts, device=device, dtype=torch.float32)
-        self.walk_tics = t(_ENEMY_WALK_FRAME_TICS)
-        self.idle_tics = t(_ENEMY_IDLE_FRAME_TICS)
-        self.recovery = t(_ENEMY_ATTACK_RECOVERY)
-
-
-def enemy_sprite_ids(src, tab: SpriteTables) -> torch.Tensor:
-    """Walk / attack / pain sprite of every enemy slot
-    (src/gradoom/engine.py:14011-14077)."""
-
-    etype = src.enemy_type.clamp(0, 5)
-    viewer = torch.atan2(src.y[:, None] - src.enemy_y, src.x[:, None] - src.enemy_x)
-    rot = sprite_rotation(viewer, src.enemy_angle)
-    tics = src.enemy_animation_tics
-    walk = torch.remainder(tics // tab.walk_tics[etype], 4).to(torch.int64)
-    idle = torch.remainder(tics // tab.idle_tics[etype], 2).to(torch.int64)
-    idle = torch.where(etype == 2, torch.zeros_like(idle), idle)
-    walk = torch.where(src.enemy_target_slot < -1, idle, walk)
-    phase, cooldown = src.enemy_attack_phase, src.enemy_cooldown
-    recovering = (cooldown > (tab.recovery[etype] // 2)).to(torch.int64)
-    zero = torch.zeros_like(etype)
-    attack = torch.where((etype == 0) | (etype == 1), torch.where(phase == 2, recovering, zero), zero)
-    heavy = (etype == 4) | (etype == 5)
-    attack = torch.where(heavy & (phase == 1), (cooldown <= 8).to(torch.int64), attack)
-    attack = torch.where(heavy & (phase == 2), torch.full_like(attack, 2), attack)
-    attack = torch.where((etype == 3) & ((phase == 4) | (phase == 2)), torch.ones_like(attack), attack)
-    attack = torch.where((etype == 3) & (phase == 3), torch.full_like(attack, 2), attack)
-    animated = torch.where(phase > 0, tab.attack[etype, attack, rot], tab.walk[etype, walk, rot])
-    return torch.where(src.enemy_pain_tics > 0, tab.pain[etype, rot], animated)
-
-
-def gather_things(src, tab: SpriteTables, max_things: int | None = None):
-    """Collect every drawable actor of every lane, in the reference's order.
-
-    Returns ``(things (N,K,4) int32, counts (N,) int32)``.  Columns of inactive
-    slots across all lanes are dropped like the reference does
-    (src/gradoom/engine.py:14328-14682); per lane the record count is K and dead
-    records simply carry a cleared alive flag.
-    """
-
-    dev = src.x.device
-    n = src.x.shape[0]
-    xs, ys, zs, alive, sprite, bright, style = [], [], [], [], [], [], []
-
-    def emit(x, y, z, a, s, b, st, used):
-        slots = torch.nonzero(torch.any(used, dim=0)).flatten()
-        if slots.numel() == 0:
-            return
-        xs.append(x[:, slots]); ys.append(y[:, slots]); zs.append(z[:, slots])
-        alive.append(a[:, slots]); sprite.append(s[:, slots].to(torch.int64))
-        bright.append(b[:, slots])
-        style.append(st[:, slots].to(torch.int64))
-
-    # living enemies -------------------------------------------------------
-    etype = src.enemy_type.clamp(0, 5)
-    recovery = tab.recovery[etype]
-    muzzle = ((etype == 1) & (src.enemy_attack_phase == 2) & (src.enemy_cooldown > (recovery // 2))) | (
-        (etype == 3) & ((src.enemy_attack_phase == 2) | (src.enemy_attack_phase == 3)))
-    eslots = torch.nonzero(torch.any(src.enemy_alive, dim=0)).flatten()
-    esprite = enemy_sprite_ids(src, tab)
-    xs.append(src.enemy_x[:, eslots]); ys.append(src.enemy_y[:, eslots]); zs.append(src.enemy_z[:, eslots])
-    alive.append(src.enemy_alive[:, eslots]); sprite.append(esprite[:, eslots])
-    bright.append(muzzle[:, eslots]); style.append(torch.full_like(esprite[:, eslots], -1))
-
-    # voodoo dolls at the unused player starts ----------------------------------
-    dolls = tab.starts[:-1]
-    if len(dolls):
-        dx = dolls[None, :, 0].expand(n, -1)
-        dy = dolls[None, :, 1].expand(n, -1)
-        dang = torch.deg2rad(dolls[None, :, 2]).expand(n, -1)
-        viewer = torch.atan2(src.y[:, None] - dy, src.x[:, None] - dx)
-        dspr = tab.walk[2, 0, sprite_rotation(viewer, dang)]
-        xs.append(dx); ys.append(dy)
-        zs.append(src._player_start_z[:-1][None, :].expand(n, -1))
-        alive.append((~src.player_dead)[:, None].expand(-1, len(dolls)))
-        sprite.append(dspr)
-        bright.append(torch.zeros_like(dspr, dtype=torch.bool))
-        style.append(torch.full_like(dspr, -1))
-
-    # corpses ------------------------------------------------------------------
-    dtype_ = src.enemy_death_type.clamp(0, 5)
-    elapsed = src.enemy_death_elapsed.to(torch.int64)
-    dframe = _frame_from_ends(elapsed, tab.death_ends[dtype_], tab.death_counts[dtype_])
-    xframe = _frame_from_ends(elapsed, tab.xdeath_ends[dtype_], tab.xdeath_counts[dtype_])
-    dspr = torch.where(src.enemy_death_extreme, tab.xdeath[dtype_, xframe], tab.death[dtype_, dframe])
-    dying = src.enemy_death_tics > 0
-    no = torch.zeros_like(dying)
-    emit(src.enemy_x, src.enemy_y, src.enemy_z, dying, dspr, no, torch.full_like(dspr, -1), dying)
-
-    # player projectiles in flight ---------------------------------------------
-    ptype = src.projectile_type.clamp(0, 1)
-    pang = torch.atan2(src.projectile_velocity_y, src.projectile_velocity_x)
-    pview = torch.atan2(src.y[:, None] - src.projectile_y, src.x[:, None] - src.projectile_x)
-    prot = sprite_rotation(pview, pang)
-    pframe = torch.where(ptype == 1, torch.remainder(src.projectile_age // 6, 2).to(torch.int64),
-                         torch.zeros_like(ptype))
-    pspr = tab.flight[ptype, pframe, prot]
-    palive = src.projectile_alive
-    emit(src.projectile_x, src.projectile_y, src.projectile_z, palive, pspr, palive,
-         torch.where(ptype == 1, torch.zeros_like(ptype), torch.full_like(ptype, -1)), palive)
-
-    # enemy projectiles in flight ------------------------------------------------
-    eang = torch.atan2(src.enemy_projectile_velocity_y, src.enemy_projectile_velocity_x)
-    eview = torch.atan2(src.y[:, None] - src.enemy_projectile_y, src.x[:, None] - src.enemy_projectile_x)
-    erot = sprite_rotation(eview, eang)
-    eframe = torch.remainder(src.enemy_projectile_age // 4, 2).to(torch.int64)
-    espr = tab.flight[2, eframe, erot]
-    ealive = src.enemy_projectile_alive
-    emit(src.enemy_projectile_x, src.enemy_projectile_y, src.enemy_projectile_z, ealive, espr, ealive,
-         torch.ones_like(eframe), ealive)
-
-    # impacts -----------------------------------------------------------------------
-    def explosion(kind, remaining):
-        safe = kind.clamp(0, 2)
-        el = tab.explosion_total[safe] - remaining.to(torch.int64)
-        frame = _frame_from_ends(el, tab.explosion_ends[safe], tab.explosion_counts[safe])
-        return tab.explosion[safe, frame]
-
-    pi_alive = src.projectile_impact_tics > 0
-    pi_type = src.projectile_impact_type
-    emit(src.projectile_x, src.projectile_y, src.projectile_z, pi_alive,
-         explosion(pi_type, src.projectile_impact_tics), pi_alive,
-         torch.where(pi_type == 1, torch.zeros_like(pi_type), torch.full_like(pi_type, -1)), pi_alive)
-    ei_alive = src.enemy_projectile_impact_tics > 0
-    ei_type = torch.full_like(src.enemy_projectile_age, 2, dtype=torch.int64)
-    emit(src.enemy_projectile_x, src.enemy_projectile_y, src.enemy_projectile_z, ei_alive,
-         explosion(ei_type, src.enemy_projectile_impact_tics), ei_alive, torch.ones_like(ei_type), ei_alive)
-
-    # teleport fog ----------------------------------------------------------------------
-    fog_alive = src.teleport_fog_tics > 0
-    fog_frame = torch.clamp((_TELEPORT_FOG_TOTAL_TICS - src.teleport_fog_tics.to(torch.int64)) // 6, max=11)
-    fog_spr = tab.fog[fog_frame]
-    emit(src.teleport_fog_x, src.teleport_fog_y, src.teleport_fog_z, fog_alive, fog_spr, fog_alive,
-         torch.ones_like(fog_spr), fog_alive)
-
-    # bullet puffs ----------------------------------------------------------------------
-    ptics = src.hitscan_puff_tics
-    pf = torch.where(ptics > 3 * _BULLET_PUFF_FRAME_TICS, 0,
-                     torch.where(ptics > 2 * _BULLET_PUFF_FRAME_TICS, 1,
-                                 torch.where(ptics > _BULLET_PUFF_FRAME_TICS, 2, 3))).to(torch.int64)
-    puff_spr = tab.puff[pf]
-    emit(src.hitscan_puff_x, src.hitscan_puff_y, src.hitscan_puff_z, ptics > 0, puff_spr, pf == 0,
-         torch.full_like(puff_spr, -2), ptics > 0)
-
-    # map items are not generated by the synthetic scenes; dropped items ------------------
-    drop_visible = (src.drop_type >= 0) & src.drop_spawned
-    drop_spr = tab.static[12].expand_as(src.drop_type)
-    drop_spr = torch.where(src.drop_type == 2007, tab.static[6], drop_spr)
-    drop_spr = torch.where(src.drop_type == 2002, tab.static[14], drop_spr)
-    emit(src.drop_x, src.drop_y, src.drop_z, drop_visible, drop_spr, torch.zeros_like(drop_visible),
-         torch.full_like(drop_spr, -1), drop_visible)
-
-    ax = torch.cat(xs, dim=1).to(torch.float32)
-    ay = torch.cat(ys, dim=1).to(torch.float32)
-    az = torch.cat(zs, dim=1).to(torch.float32)
-    aalive = torch.cat(alive, dim=1)
-    aspr = torch.cat(sprite, dim=1)
-    abright = torch.cat(bright, dim=1)
-    astyle = torch.cat(style, dim=1)
-    k = ax.shape[1]
-    if max_things is not None:
-        if k > max_things:
-            raise ValueError(f"{k} drawable actors exceed the configured maximum of {max_things}")
-    things = pack_things(ax, ay, az, aspr, aalive, abright, astyle, pad_to=max_things)
-    counts = torch.full((n,), k, dtype=torch.int32, device=dev)
-    return things, counts
 
 
 def pack_things(x, y, z, sprite, alive, bright, style, pad_to: int | None = None) -> torch.Tensor:

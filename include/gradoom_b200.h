@@ -165,6 +165,88 @@ int gd_render_step_host(const gd_renderer *r, const int32_t *lanes_host, const v
                         void *scratch, size_t scratch_bytes, int *status, void *stream);
 
 /*
+ * Engine-shaped lane state -> render records, on the device.
+ *
+ * `gd_engine_state` is a table of device pointers to the reference engine's own
+ * per-lane tensors, each under the reference's attribute name and in the
+ * reference's dtype (src/gradoom/engine.py:1653-1934: torch.bool as uint8_t,
+ * torch.int64 as int64_t, torch.int32 as int32_t, float32 as float), row-major
+ * with leading dimension n.  gd_pack_state turns them into the lane records and
+ * the thing records the render calls read, in two small launches and without any
+ * host synchronisation:
+ *   lanes   n x 32 i32            the fields of src/gradoom/engine.py:1658-1739 the
+ *                                 renderer reads (layout: gradoom_b200_layout.h)
+ *   things  n x max_things x 16 B every drawable actor in the order the reference
+ *                                 concatenates them
+ * Replaces: the actor gathering at the head of _native_render_sprites
+ * (src/gradoom/engine.py:14328-14682) with _native_enemy_sprite_ids (14011-14077),
+ * _native_enemy_death_sprite_ids (14079-14104),
+ * _native_projectile_explosion_sprite_ids (14106-14122), _native_enemy_fullbright
+ * (14124-14136), _doom_sprite_rotation (13994-14009) and _native_item_sprite_ids
+ * (14258-14317), and the view-pose selection of _native_view_fixed /
+ * _native_view_angle_bam (2122-2133, 10648-10658).
+ * Like the reference, a slot of an actor class is dropped only when no lane of
+ * the batch uses it; every lane therefore gets the same number K of records
+ * (lanes where the slot is idle carry a record with the alive flag cleared), K is
+ * written to word GD_L_THINGS of every lane record, and K > max_things sets
+ * GD_STATUS_THINGS_OVERFLOW (the records beyond max_things are not written).
+ * `flags_scratch` is gd_pack_state_scratch_bytes() of device memory (cleared by
+ * the call itself).  Pointers of an actor class whose slot count is 0 may be NULL.
+ */
+typedef struct gd_engine_state {
+  int32_t n;
+  int32_t enemy_slots;              /* enemies, corpses, teleport fog and drops share it (64) */
+  int32_t projectile_slots;         /* player projectiles and their impacts (32) */
+  int32_t enemy_projectile_slots;   /* (64) */
+  int32_t puff_slots;               /* bullet puffs (20) */
+  int32_t items;                    /* map items of the scene blob (GD_H_ITEMS) */
+  int32_t render_screen_flashes;    /* nonzero: pass damage_count / bonus_count on to the renderer */
+  int32_t reserved;
+  /* player: n */
+  const float *x, *y, *angle, *view_z, *health, *armor, *hud_ready_ammo;
+  const int64_t *x_fixed, *y_fixed, *angle_bam, *pitch_bam, *player_bob_fixed;      /* _x_fixed ... */
+  const int64_t *selected_weapon, *pending_weapon, *mugshot_face_index, *mugshot_pain_direction;
+  const int32_t *episode_time, *weapon_state_cooldown, *weapon_fire_count, *weapon_ready_tics,
+      *weapon_raise_cooldown, *weapon_lower_cooldown, *mugshot_pain_tics, *mugshot_grin_tics, *attack_held_tics,
+      *damage_count, *bonus_count;                                                   /* the last two may be NULL */
+  const uint8_t *player_dead, *selected_weapon_variant, *mugshot_ouch;
+  const float *hud_ammo_counts;     /* n x 4 */
+  const float *weapons;             /* n x 6 */
+  /* enemies: n x enemy_slots */
+  const float *enemy_x, *enemy_y, *enemy_z, *enemy_angle;
+  const int64_t *enemy_type, *enemy_target_slot, *enemy_death_type;
+  const int32_t *enemy_animation_tics, *enemy_attack_phase, *enemy_cooldown, *enemy_pain_tics, *enemy_death_tics,
+      *enemy_death_elapsed;
+  const uint8_t *enemy_alive, *enemy_death_extreme;
+  /* teleport fog and dropped items: n x enemy_slots */
+  const float *teleport_fog_x, *teleport_fog_y, *teleport_fog_z;
+  const int32_t *teleport_fog_tics;
+  const float *drop_x, *drop_y, *drop_z;
+  const int64_t *drop_type;
+  const uint8_t *drop_spawned;
+  /* player projectiles: n x projectile_slots */
+  const float *projectile_x, *projectile_y, *projectile_z, *projectile_velocity_x, *projectile_velocity_y;
+  const int64_t *projectile_type, *projectile_impact_type;
+  const int32_t *projectile_age, *projectile_impact_tics;
+  const uint8_t *projectile_alive;
+  /* enemy projectiles: n x enemy_projectile_slots */
+  const float *enemy_projectile_x, *enemy_projectile_y, *enemy_projectile_z, *enemy_projectile_velocity_x,
+      *enemy_projectile_velocity_y;
+  const int32_t *enemy_projectile_age, *enemy_projectile_impact_tics;
+  const uint8_t *enemy_projectile_alive;
+  /* bullet puffs: n x puff_slots */
+  const float *hitscan_puff_x, *hitscan_puff_y, *hitscan_puff_z;
+  const int32_t *hitscan_puff_tics;
+  /* map items: n x items */
+  const uint8_t *item_available;
+  const int32_t *item_animation_initial_tics;
+} gd_engine_state;
+
+size_t gd_pack_state_scratch_bytes(void);
+int gd_pack_state(const gd_renderer *r, const gd_engine_state *state, int32_t *lanes, void *things,
+                  void *flags_scratch, size_t flags_scratch_bytes, int *status, void *stream);
+
+/*
  * No counterpart in the reference.  gd_render_step for callers that may not
  * allocate device memory -- a plugin inside a host process whose GPU memory
  * pool is owned and budgeted by the embedding application, or code running

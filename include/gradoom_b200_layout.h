@@ -14,7 +14,7 @@
 #include <stdint.h>
 
 #define GD_MAGIC 0x4744424C /* "GDBL" */
-#define GD_VERSION 9
+#define GD_VERSION 10
 #define GD_HDR_WORDS 128
 #define GD_HDR_SECTION0 48
 
@@ -56,6 +56,7 @@ enum gd_header_word {
   GD_H_MASKED_WALLS_N, /* entries of GD_S_MASKED_WALLS */
   GD_H_FLOOR_GROUPS, /* distinct floor heights */
   GD_H_CEIL_GROUPS,  /* distinct ceiling heights */
+  GD_H_ITEMS,        /* map items (pickups placed by the map) */
   GD_H_COUNT
 };
 
@@ -133,6 +134,9 @@ enum gd_section {
   GD_S_CEIL_GROUP_H,    /* distinct ceiling heights, ascending (f32) */
   GD_S_CEIL_GROUP_OFF,
   GD_S_CEIL_GROUP_SEC,
+  GD_S_ITEM_POS,        /* items x 4 f32: x y z (floor of its sector + spawn height) 0 */
+  GD_S_ITEM_INFO,       /* items x 2 i32: editor type id, sprite patch of its resting frame */
+  GD_S_ITEM_ANIM,       /* 8 i32: bonus / armour animation frames (src/gradoom/engine.py:14258-14317) */
   GD_S_COUNT
 };
 

@@ -15,6 +15,7 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 SOURCE = os.path.join(HERE, "gd_oracle.c")
+STATE_SOURCE = os.path.join(HERE, "gd_oracle_state.c")
 LIBRARY = os.path.join(HERE, "_gd_oracle.so")
 
 STAGE_WALLS, STAGE_SPRITES, STAGE_WEAPON, STAGE_HUD = 1, 2, 4, 8
@@ -24,13 +25,13 @@ _lib = None
 
 
 def build(force: bool = False) -> str:
-    header = os.path.join(HERE, "..", "include", "gradoom_b200_layout.h")
+    headers = [os.path.join(HERE, "..", "include", h) for h in ("gradoom_b200_layout.h", "gradoom_b200.h")]
     stale = (not os.path.exists(LIBRARY)) or os.path.getmtime(LIBRARY) < max(
-        os.path.getmtime(SOURCE), os.path.getmtime(header))
+        os.path.getmtime(f) for f in (SOURCE, STATE_SOURCE, *headers))
     if force or stale:
         subprocess.check_call(
             ["gcc", "-O2", "-ffp-contract=off", "-fno-fast-math", "-fPIC", "-shared",
-             "-o", LIBRARY, SOURCE, "-lm"])
+             "-o", LIBRARY, SOURCE, STATE_SOURCE, "-lm"])
     return LIBRARY
 
 
@@ -43,6 +44,7 @@ def lib():
         _lib.gd_oracle_resize.restype = ctypes.c_int
         _lib.gd_oracle_rgb.restype = ctypes.c_int
         _lib.gd_oracle_stack.restype = ctypes.c_int
+        _lib.gd_oracle_pack_state.restype = ctypes.c_int
     return _lib
 
 
@@ -124,3 +126,26 @@ def flats(blob, lanes):
     out = np.zeros((lanes.shape[0], 208, 320), dtype=np.uint8)
     lib().gd_oracle_flats(_ptr(blob), _ptr(lanes), ctypes.c_int(lanes.shape[0]), _ptr(out))
     return out
+
+
+def pack_state(blob, src, max_things, *, render_screen_flashes=None):
+    """Lane and thing records from an object that carries the reference engine's
+    lane tensors on the CPU (the checker of the CUDA library's ``gd_pack_state``).
+
+    Returns ``(lanes (N,32) i32, things (N,max_things,4) i32, K)``.
+    """
+
+    from gradoom_b200 import state as gdstate      # the struct layout is shared with the product binding
+
+    es = gdstate.EngineState(src, render_screen_flashes=render_screen_flashes)
+    if es.device.type != "cpu":
+        raise TypeError("the oracle packs CPU tensors")
+    blob = np.ascontiguousarray(blob, dtype=np.uint8)
+    n = es.n
+    lanes = np.zeros((n, 32), dtype=np.int32)
+    things = np.zeros((n, max(max_things, 1), 4), dtype=np.int32)
+    k = lib().gd_oracle_pack_state(_ptr(blob), ctypes.byref(es.struct), ctypes.c_int(max_things), _ptr(lanes),
+                                   _ptr(things))
+    if k < 0:
+        raise RuntimeError(f"oracle rejected the state or the blob (code {k})")
+    return lanes, things, int(k)

@@ -3,7 +3,7 @@
 Run once on a machine that has the upstream sources:
 
     GRADOOM_REFERENCE_SRC=<upstream checkout>/src/gradoom python tests/golden/make_golden.py \
-        [c1 c2 c3 c4 c1m stack flashes pitch fallback c2d c4d c1k]
+        [c1 c2 c3 c4 c1m stack flashes pitch fallback c2d c4d c1k state]
 
 For each seeded synthetic scene it resets the upstream engine, injects K
 monsters per lane, replays a seeded uniform action stream and, at a few
@@ -30,9 +30,10 @@ OUT = os.environ.get("GRADOOM_GOLDEN_OUT", HERE)    # where the .npz files are w
 sys.path.insert(0, ROOT)
 sys.path.insert(0, HERE)
 
-from __graft_entry__ import load_package  # noqa: E402
+from __graft_entry__ import load_oracle, load_package  # noqa: E402
 
 load_package()
+oracle = load_oracle()
 from gradoom_b200 import scene as gdscene, state as gdstate  # noqa: E402
 import refbridge  # noqa: E402
 
@@ -80,19 +81,27 @@ def make_engine(eng, scn, sc, n, k, seed, flashes=False):
     return e, g
 
 
-def snapshot(e, tab, max_things):
-    things, counts = gdstate.gather_things(e, tab, max_things=max_things)
-    lanes = gdstate.pack_lanes(e, counts)
+def pack(e, blob, max_things=64):
+    """The renderer's inputs for the engine's present state (CPU packer of the oracle)."""
+
+    lanes, things, k = oracle.pack_state(blob, e, max_things)
+    if k > max_things:
+        raise ValueError(f"{k} drawable actors exceed the configured maximum of {max_things}")
+    return lanes, things
+
+
+def snapshot(e, blob, max_things):
+    lanes, things = pack(e, blob, max_things)
     indexed = e._render_native_indexed_frame(include_hud=True).numpy()
     obs_float = e.render_reference_frame().numpy()
-    return lanes.numpy(), things.numpy(), indexed, obs_float
+    return lanes, things, indexed, obs_float
 
 
 def generate(name, eng, scn, act):
     cfg, n, k, checkpoints = PLANS[name]
     sc = gdscene.make_grid_scene(gdscene.GRID_CONFIGS[cfg])
     e, g = make_engine(eng, scn, sc, n, k, seed=1234)
-    tab = gdstate.SpriteTables(sc, torch.device("cpu"))
+    blob = gdscene.pack_scene(sc)
     am = action_matrix(act)
     ag = torch.Generator().manual_seed(ACTION_SEED)
     max_things = 64
@@ -110,7 +119,7 @@ def generate(name, eng, scn, act):
             if bool(done.any()):
                 e.reset(done, torch.arange(n) + 1000 * (step + 1))
             step += 1
-        lanes, things, indexed, obs_float = snapshot(e, tab, max_things)
+        lanes, things, indexed, obs_float = snapshot(e, blob, max_things)
         used = max(int(lanes[:, gdstate.L_THINGS].max()), 1)
         out[f"lanes_{ci}"] = lanes
         out[f"things_{ci}"] = things[:, :used].copy()
@@ -127,7 +136,7 @@ def generate_stack(eng, scn, act):
     n, k = 2, 4
     sc = gdscene.make_grid_scene(gdscene.GRID_CONFIGS["c1"])
     e, g = make_engine(eng, scn, sc, n, k, seed=77)
-    tab = gdstate.SpriteTables(sc, torch.device("cpu"))
+    blob = gdscene.pack_scene(sc)
     am = action_matrix(act)
     ag = torch.Generator().manual_seed(ACTION_SEED + 1)
     offsets, coscorr = gdscene.ray_tables()
@@ -135,19 +144,17 @@ def generate_stack(eng, scn, act):
     # a masked reset of lane 1 only, as the reference's auto-reset does
     mask = torch.tensor([False, True])
     e.reset(mask, torch.tensor([5, 6]))
-    things, counts = gdstate.gather_things(e, tab, max_things=64)
-    lanes = gdstate.pack_lanes(e, counts)
-    used = [max(int(counts.max()), 1)]
+    lanes, things = pack(e, blob)
+    used = [max(int(lanes[:, gdstate.L_THINGS].max()), 1)]
     out["reset_mask"] = mask.numpy()
-    out["lanes_reset"], out["things_reset"] = lanes.numpy(), things.numpy()
+    out["lanes_reset"], out["things_reset"] = lanes, things
     out["frames_reset"] = e.frames.numpy().copy()
     for s in range(4):
         a = torch.randint(0, 17, (n,), generator=ag)
         e.step(am[a])
-        things, counts = gdstate.gather_things(e, tab, max_things=64)
-        lanes = gdstate.pack_lanes(e, counts)
-        used.append(max(int(counts.max()), 1))
-        out[f"lanes_{s}"], out[f"things_{s}"] = lanes.numpy(), things.numpy()
+        lanes, things = pack(e, blob)
+        used.append(max(int(lanes[:, gdstate.L_THINGS].max()), 1))
+        out[f"lanes_{s}"], out[f"things_{s}"] = lanes, things
         out[f"frames_{s}"] = e.frames.numpy().copy()
     kmax = max(used)
     for key in list(out):
@@ -167,7 +174,7 @@ def generate_fallback(eng, scn, act):
     n, k = 6, 12
     sc = gdscene.make_grid_scene(gdscene.GRID_CONFIGS["c2"])
     e, g = make_engine(eng, scn, sc, n, k, seed=97)
-    tab = gdstate.SpriteTables(sc, torch.device("cpu"))
+    blob = gdscene.pack_scene(sc)
     poses = [  # x, y, angle (degrees)
         (512.0, 600.0, 170.0),                # on the portal line x = 512, looking across it
         (768.0, 1024.0, 200.0),               # on the vertex shared by four rooms
@@ -188,7 +195,7 @@ def generate_fallback(eng, scn, act):
     offsets, coscorr = gdscene.ray_tables()
     out = {"config": np.asarray("c2"), "ray_offsets": offsets, "ray_coscorr": coscorr,
            "checkpoints": np.asarray([0])}
-    lanes, things, indexed, obs_float = snapshot(e, tab, 64)
+    lanes, things, indexed, obs_float = snapshot(e, blob, 64)
     used = max(int(lanes[:, gdstate.L_THINGS].max()), 1)
     out["lanes_0"], out["things_0"] = lanes, things[:, :used].copy()
     out["indexed_0"], out["obs_float_0"] = indexed, obs_float
@@ -205,7 +212,7 @@ def generate_c1k(eng, scn, act):
     n, k, total = 4, 4, 1000
     sc = gdscene.make_grid_scene(gdscene.GRID_CONFIGS["c1"])
     e, g = make_engine(eng, scn, sc, n, k, seed=1234)
-    tab = gdstate.SpriteTables(sc, torch.device("cpu"))
+    blob = gdscene.pack_scene(sc)
     am = action_matrix(act)
     ag = torch.Generator().manual_seed(ACTION_SEED)
     offsets, coscorr = gdscene.ray_tables()
@@ -224,14 +231,13 @@ def generate_c1k(eng, scn, act):
             e.reset(done, torch.arange(n) + 1000 * (step + 1))
             resets += int(done.sum())
         if step >= total - 4:
-            things, counts = gdstate.gather_things(e, tab, max_things=64)
-            lanes = gdstate.pack_lanes(e, counts)
+            lanes, things = pack(e, blob)
             s = step - (total - 4)
-            out[f"stack_lanes_{s}"], out[f"stack_things_{s}"] = lanes.numpy(), things.numpy()
+            out[f"stack_lanes_{s}"], out[f"stack_things_{s}"] = lanes, things
             out[f"stack_done_{s}"] = done.numpy()
         if step % 100 == 0:
             print("c1k step", step, flush=True)
-    lanes, things, indexed, obs_float = snapshot(e, tab, 64)
+    lanes, things, indexed, obs_float = snapshot(e, blob, 64)
     used = max(int(lanes[:, gdstate.L_THINGS].max()), 1)
     kmax = max(used, *(int(out[f"stack_lanes_{s}"][:, gdstate.L_THINGS].max()) for s in range(4)))
     for s in range(4):
@@ -244,6 +250,92 @@ def generate_c1k(eng, scn, act):
     print("c1k fixture done; lane resets along the way:", resets, flush=True)
 
 
+def generate_state(eng, scn, act):
+    """The engine's own lane tensors with every actor class in use, and the frame the
+    upstream renderer draws from them: c1 with twelve map items, 6 lanes, 40 agent steps
+    of the uniform action stream, then effects written into a few slots of every class
+    (the way the upstream tests set state).  Pins the state packer: tensors in, records
+    out, frame equal."""
+
+    n, k = 6, 4
+    sc = gdscene.make_grid_scene(gdscene.GRID_CONFIGS["c1i"])
+    blob = gdscene.pack_scene(sc)
+    e, g = make_engine(eng, scn, sc, n, k, seed=555)
+    am = action_matrix(act)
+    ag = torch.Generator().manual_seed(ACTION_SEED + 7)
+    del e.render_frame
+    for step in range(40):
+        _f, _r, term, trunc = e.step(am[torch.randint(0, 17, (n,), generator=ag)])
+        done = term | trunc
+        if bool(done.any()):
+            e.reset(done, torch.arange(n) + 1000 * (step + 1))
+    spec = sc.meta["spec"]
+    span_x, span_y = spec.cols * spec.room - 64, spec.rows * spec.room - 64
+
+    def place(count):
+        x = torch.rand((n, count), generator=g) * span_x + 32
+        y = torch.rand((n, count), generator=g) * span_y + 32
+        sec = e._sector_at(x.reshape(-1), y.reshape(-1)).reshape(n, count)
+        return x, y, e.map.sector_heights[sec, 0] + 24.0
+
+    lanes_with = lambda p: torch.rand((n, 1), generator=g) < p          # noqa: E731
+    # corpses: slots 10..13, both death kinds, several stages
+    e.enemy_x[:, 10:14], e.enemy_y[:, 10:14], z = place(4)
+    e.enemy_z[:, 10:14] = z - 24.0
+    e.enemy_death_type[:, 10:14] = torch.randint(0, 6, (n, 4), generator=g)
+    e.enemy_death_extreme[:, 10:14] = torch.rand((n, 4), generator=g) < 0.4
+    e.enemy_death_elapsed[:, 10:14] = torch.randint(0, 60, (n, 4), generator=g).to(torch.int32)
+    e.enemy_death_tics[:, 10:14] = (torch.randint(0, 30, (n, 4), generator=g) * lanes_with(0.7)).to(torch.int32)
+    # living monsters in every animation state
+    e.enemy_attack_phase[:, :k] = torch.randint(0, 5, (n, k), generator=g).to(torch.int32)
+    e.enemy_cooldown[:, :k] = torch.randint(0, 24, (n, k), generator=g).to(torch.int32)
+    e.enemy_pain_tics[:, :k] = (torch.randint(0, 6, (n, k), generator=g) * (torch.rand((n, k), generator=g) < 0.3)).to(torch.int32)
+    e.enemy_animation_tics[:, :k] = torch.randint(0, 200, (n, k), generator=g).to(torch.int32)
+    e.enemy_target_slot[:, :k] = torch.randint(-2, 3, (n, k), generator=g)
+    # player projectiles: flights in slots 0..2, impacts in slots 3..4
+    e.projectile_x[:, 0:5], e.projectile_y[:, 0:5], e.projectile_z[:, 0:5] = place(5)
+    e.projectile_velocity_x[:, 0:5] = torch.randn((n, 5), generator=g) * 10
+    e.projectile_velocity_y[:, 0:5] = torch.randn((n, 5), generator=g) * 10
+    e.projectile_type[:, 0:5] = torch.randint(0, 2, (n, 5), generator=g)
+    e.projectile_age[:, 0:5] = torch.randint(0, 40, (n, 5), generator=g).to(torch.int32)
+    e.projectile_alive[:, 0:3] = torch.rand((n, 3), generator=g) < 0.6
+    e.projectile_impact_type[:, 3:5] = torch.randint(0, 3, (n, 2), generator=g)
+    e.projectile_impact_tics[:, 3:5] = torch.randint(0, 16, (n, 2), generator=g).to(torch.int32)
+    # enemy projectiles: flights 0..1, impacts 2..3
+    e.enemy_projectile_x[:, 0:4], e.enemy_projectile_y[:, 0:4], e.enemy_projectile_z[:, 0:4] = place(4)
+    e.enemy_projectile_velocity_x[:, 0:4] = torch.randn((n, 4), generator=g) * 10
+    e.enemy_projectile_velocity_y[:, 0:4] = torch.randn((n, 4), generator=g) * 10
+    e.enemy_projectile_age[:, 0:4] = torch.randint(0, 40, (n, 4), generator=g).to(torch.int32)
+    e.enemy_projectile_alive[:, 0:2] = torch.rand((n, 2), generator=g) < 0.6
+    e.enemy_projectile_impact_tics[:, 2:4] = torch.randint(0, 12, (n, 2), generator=g).to(torch.int32)
+    # teleport fog, bullet puffs, dropped items
+    e.teleport_fog_x[:, 5:8], e.teleport_fog_y[:, 5:8], e.teleport_fog_z[:, 5:8] = place(3)
+    e.teleport_fog_tics[:, 5:8] = torch.randint(0, 73, (n, 3), generator=g).to(torch.int32)
+    e.hitscan_puff_x[:, 0:4], e.hitscan_puff_y[:, 0:4], e.hitscan_puff_z[:, 0:4] = place(4)
+    e.hitscan_puff_tics[:, 0:4] = torch.randint(0, 17, (n, 4), generator=g).to(torch.int32)
+    e.drop_x[:, 20:23], e.drop_y[:, 20:23], z = place(3)
+    e.drop_z[:, 20:23] = z - 24.0
+    e.drop_type[:, 20:23] = torch.tensor([2007, 2002, 2001])[torch.randint(0, 3, (n, 3), generator=g)]
+    e.drop_spawned[:, 20:23] = torch.rand((n, 3), generator=g) < 0.7
+    # map items: some picked up, animation offsets spread
+    e.item_available.copy_(torch.rand(e.item_available.shape, generator=g) < 0.8)
+    e.item_animation_initial_tics.copy_(torch.randint(1, 7, e.item_animation_initial_tics.shape, generator=g).to(torch.int32))
+    e.episode_time.copy_(torch.randint(1, 500, (n,), generator=g).to(torch.int32))
+    e.player_dead[1] = True
+
+    offsets, coscorr = gdscene.ray_tables()
+    out = {"config": np.asarray("c1i"), "ray_offsets": offsets, "ray_coscorr": coscorr,
+           "checkpoints": np.asarray([0])}
+    for _field, attr, _dtype, _shape in gdstate.ENGINE_STATE_POINTERS:
+        out["state_" + attr] = getattr(e, attr).numpy().copy()
+    lanes, things, indexed, obs_float = snapshot(e, blob, 64)
+    used = max(int(lanes[:, gdstate.L_THINGS].max()), 1)
+    out["lanes_0"], out["things_0"] = lanes, things[:, :used].copy()
+    out["indexed_0"], out["obs_float_0"] = indexed, obs_float
+    np.savez_compressed(os.path.join(OUT, "golden_state.npz"), **out)
+    print("state fixture done; records per lane:", used, flush=True)
+
+
 def generate_pitch(eng, scn, act):
     """c1 with the view pitched up and down (engine.py:9622-9631 and every use of the
     pitched view centre): inputs, indexed frames and observations."""
@@ -251,7 +343,7 @@ def generate_pitch(eng, scn, act):
     n, k = 4, 4
     sc = gdscene.make_grid_scene(gdscene.GRID_CONFIGS["c1"])
     e, g = make_engine(eng, scn, sc, n, k, seed=2468)
-    tab = gdstate.SpriteTables(sc, torch.device("cpu"))
+    blob = gdscene.pack_scene(sc)
     am = action_matrix(act)
     ag = torch.Generator().manual_seed(ACTION_SEED + 3)
     for _ in range(9):
@@ -265,7 +357,7 @@ def generate_pitch(eng, scn, act):
         bam = torch.tensor([int(round(d / 360.0 * (1 << 32))) for d in row], dtype=torch.int64)
         e._pitch_bam.copy_(bam)
         e.pitch.copy_(bam.to(torch.float32) * (2.0 * np.pi / (1 << 32)))
-        lanes, things, indexed, obs_float = snapshot(e, tab, 64)
+        lanes, things, indexed, obs_float = snapshot(e, blob, 64)
         used = max(int(lanes[:, gdstate.L_THINGS].max()), 1)
         out[f"lanes_{ci}"] = lanes
         out[f"things_{ci}"] = things[:, :used].copy()
@@ -282,7 +374,7 @@ def generate_flashes(eng, scn, act):
     n, k = 4, 4
     sc = gdscene.make_grid_scene(gdscene.GRID_CONFIGS["c1"])
     e, g = make_engine(eng, scn, sc, n, k, seed=4321, flashes=True)
-    tab = gdstate.SpriteTables(sc, torch.device("cpu"))
+    blob = gdscene.pack_scene(sc)
     am = action_matrix(act)
     ag = torch.Generator().manual_seed(ACTION_SEED + 2)
     for _ in range(6):
@@ -294,11 +386,10 @@ def generate_flashes(eng, scn, act):
     for ci, (damage, bonus) in enumerate(cases):
         e.damage_count.copy_(torch.tensor(damage, dtype=torch.int32))
         e.bonus_count.copy_(torch.tensor(bonus, dtype=torch.int32))
-        things, counts = gdstate.gather_things(e, tab, max_things=64)
-        lanes = gdstate.pack_lanes(e, counts)
-        used = max(int(counts.max()), 1)
-        out[f"lanes_{ci}"] = lanes.numpy()
-        out[f"things_{ci}"] = things.numpy()[:, :used].copy()
+        lanes, things = pack(e, blob)
+        used = max(int(lanes[:, gdstate.L_THINGS].max()), 1)
+        out[f"lanes_{ci}"] = lanes
+        out[f"things_{ci}"] = things[:, :used].copy()
         out[f"rgb_{ci}"] = e.render_native_frame(include_hud=True).numpy()
         out[f"obs_float_{ci}"] = e.render_reference_frame().numpy()
     np.savez_compressed(os.path.join(OUT, "golden_flashes.npz"), **out)
@@ -315,6 +406,8 @@ def main(argv):
             generate_flashes(eng, scn, act)
         elif name == "pitch":
             generate_pitch(eng, scn, act)
+        elif name == "state":
+            generate_state(eng, scn, act)
         elif name == "fallback":
             generate_fallback(eng, scn, act)
         elif name == "c1k":

@@ -53,6 +53,7 @@ def scene_to_compiled(scene, scenario_module):
     gray = gray.astype(np.uint8)
     W = len(walls)
     middle = scene.side_textures[:, 0, 0]
+    items = scene.meta.get("items")
     return scenario_module.CompiledScenario(
         scenario_sha256="0" * 64,
         iwad_sha256="1" * 64,
@@ -72,8 +73,9 @@ def scene_to_compiled(scene, scenario_module):
         sector_floor_texture_ids=scene.sector_floor_tex.astype(np.int32),
         sector_ceiling_texture_ids=scene.sector_ceil_tex.astype(np.int32),
         player_starts=scene.player_starts.astype(np.float32),
-        item_spawns=np.empty((0, 3), dtype=np.float32),
-        item_types=np.empty((0,), dtype=np.int32),
+        item_spawns=np.empty((0, 3), dtype=np.float32) if items is None else items["spawns"].astype(np.float32),
+        item_types=np.empty((0,), dtype=np.int32) if items is None else items["types"].astype(np.int32),
+        raw_item_animation_sprite_ids=None if items is None else items["anim_ids"].astype(np.int32),
         playpal=scene.playpal,
         texture_names=tuple(f"T{i}" for i in range(len(scene.tex_atlas))),
         texture_atlas=gray[scene.tex_atlas],

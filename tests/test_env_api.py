@@ -146,3 +146,50 @@ def test_ring_stack_policy_shows_the_same_windows_as_the_rolled_stack(pkg, scene
     for e in envs + [hwc]:
         e.check_status()
         e.close()
+
+
+@pytest.mark.gpu
+def test_engine_state_producer_packs_on_the_device(pkg, oracle, scenes):
+    """``EngineStateProducer`` around an object with the reference engine's tensors and
+    methods: the environment's observations are the oracle's render of the oracle-packed
+    state, after reset and after a step that changes the state."""
+
+    from conftest import fake_engine
+    from gradoom_b200 import env as gdenv
+
+    sc, blob = scenes("c1")
+    n = 5
+
+    class Engine:
+        """The slice of the reference engine's interface the producer drives."""
+
+        def __init__(self):
+            self.__dict__.update(vars(fake_engine(n, seed=21, device="cuda:0")))
+            self.signal_buffer = torch.zeros((n, 27), device="cuda:0")
+            self.pending_reset = torch.zeros(n, dtype=torch.bool, device="cuda:0")
+            self.render_frame = None
+            self.steps = 0
+
+        def reset(self, mask, seeds):
+            self.render_frame(mask)
+
+        def step(self, buttons):
+            self.render_frame()
+            self.steps += 1
+            self.__dict__.update(vars(fake_engine(n, seed=21 + self.steps, device="cuda:0")))
+            zeros = torch.zeros(n, device="cuda:0")
+            return None, zeros, zeros.bool(), zeros.bool()
+
+    engine = Engine()
+    producer = gdenv.EngineStateProducer(engine, sc, 64)
+    e = gdenv.GraDoomVecEnv(sc, n, device="cuda:0", producer=producer, max_things=64)
+    obs, _signals = e.reset_device(torch.ones(n, dtype=torch.bool, device="cuda:0"),
+                                   torch.arange(n, device="cuda:0"))
+    lanes, things, _k = oracle.pack_state(blob, fake_engine(n, seed=21), 64)
+    want = oracle.render(blob, lanes, things)["obs"]
+    assert np.array_equal(obs[:, 3].cpu().numpy(), want) and np.array_equal(obs[:, 0].cpu().numpy(), want)
+    t = e.step_device(torch.zeros(n, dtype=torch.int64, device="cuda:0"))
+    lanes, things, _k = oracle.pack_state(blob, fake_engine(n, seed=22), 64)
+    assert np.array_equal(t.observations[:, 3].cpu().numpy(), oracle.render(blob, lanes, things)["obs"])
+    assert np.array_equal(t.observations[:, 2].cpu().numpy(), want)
+    e.close()

@@ -13,7 +13,7 @@ import numpy as np
 import pytest
 import torch
 
-from conftest import load_golden, pad_things
+from conftest import engine_from_fixture, fake_engine, load_golden, pad_things
 
 pytestmark = pytest.mark.gpu
 
@@ -192,6 +192,66 @@ def test_two_renderers_of_different_scenes_side_by_side(pkg, oracle, scenes):
         r.check_status()
     assert np.array_equal(s4[:, 3].cpu().numpy(), e4) and np.array_equal(s4[:, 1].cpu().numpy(), e4)
     assert np.array_equal(s1[:, 3].cpu().numpy(), e1) and np.array_equal(s1[:, 1].cpu().numpy(), e1)
+
+
+def test_state_packer_kernel_matches_the_fixture_and_the_upstream_frame(pkg, oracle, scenes):
+    """gd_pack_state on the engine tensors recorded from the upstream engine (every actor
+    class in use, map items included): records equal the fixture's bit for bit, and the
+    frame drawn from them is the upstream renderer's (engine.py:14328-14682)."""
+
+    from gradoom_b200 import state as gdstate
+
+    data = load_golden("state")
+    _sc, blob = scenes("c1i", (data["ray_offsets"], data["ray_coscorr"]))
+    r = _renderer(blob, 64)
+    src = engine_from_fixture(data, DEV)
+    n = data["lanes_0"].shape[0]
+    lanes = torch.zeros((n, 32), dtype=torch.int32, device=DEV)
+    things = torch.zeros((n, 64, 4), dtype=torch.int32, device=DEV)
+    r.pack_state(gdstate.EngineState(src), lanes, things)
+    k = data["things_0"].shape[1]
+    assert np.array_equal(lanes.cpu().numpy(), data["lanes_0"])
+    assert np.array_equal(things[:, :k].cpu().numpy(), data["things_0"])
+    _, indexed, _ = r.frames(lanes, things, indexed=True)
+    r.check_status()
+    assert np.array_equal(indexed.cpu().numpy(), data["indexed_0"])
+
+
+@pytest.mark.parametrize("n,seed,items", [(1, 1, 0), (257, 2, 12), (1024, 3, 12)])
+def test_state_packer_kernel_matches_the_oracle_packer(n, seed, items, pkg, oracle, scenes):
+    """Random engine-shaped states, all classes active: lane and thing records of the
+    kernel equal the CPU packer's, twice in a row (the slot-use flags are cleared per call)."""
+
+    from gradoom_b200 import state as gdstate
+
+    _sc, blob = scenes("c1i" if items else "c1")
+    r = _renderer(blob, 64)
+    lanes = torch.zeros((n, 32), dtype=torch.int32, device=DEV)
+    things = torch.zeros((n, 64, 4), dtype=torch.int32, device=DEV)
+    for round_ in range(2):
+        src = fake_engine(n, seed=seed + 10 * round_, items=items)
+        want_lanes, want_things, k = oracle.pack_state(blob, src, 64)
+        assert 0 < k <= 64
+        dev = fake_engine(n, seed=seed + 10 * round_, items=items, device=DEV)
+        things.zero_()
+        r.pack_state(gdstate.EngineState(dev), lanes, things)
+        r.check_status()
+        assert np.array_equal(lanes.cpu().numpy(), want_lanes)
+        assert np.array_equal(things.cpu().numpy(), want_things)
+
+
+def test_state_packer_reports_more_records_than_the_stride(pkg, scenes):
+    from gradoom_b200 import native, state as gdstate
+
+    _sc, blob = scenes("c1")
+    r = _renderer(blob, 8)
+    dev = fake_engine(4, seed=3, device=DEV)
+    lanes = torch.zeros((4, 32), dtype=torch.int32, device=DEV)
+    things = torch.zeros((4, 8, 4), dtype=torch.int32, device=DEV)
+    r.pack_state(gdstate.EngineState(dev), lanes, things)
+    assert int(lanes[0, gdstate.L_THINGS]) > 8
+    with pytest.raises(native.NativeError):
+        r.check_status()
 
 
 def test_full_size_batch_properties(pkg, oracle, scenes):

@@ -57,66 +57,92 @@ def test_generator_orientation_front_sector_on_the_right(pkg, scenes):
         assert cross < 0  # room centre on the right of v1 -> v2
 
 
-def _fake_engine(n=3, slots=6):
-    g = torch.Generator().manual_seed(5)
-    e = types.SimpleNamespace()
-    fixed = torch.randint(20 << 16, 900 << 16, (n,), generator=g)
-    e._x_fixed, e._y_fixed = fixed.clone(), fixed.flip(0).clone()
-    e.x, e.y = e._x_fixed.float() / 65536, e._y_fixed.float() / 65536
-    e._angle_bam = torch.randint(0, 1 << 32, (n,), generator=g)
-    e.angle = e._angle_bam.float() * (2 * np.pi / (1 << 32))
-    e._pitch_bam = torch.zeros(n, dtype=torch.int64)
-    e.view_z = torch.full((n,), 41.0)
-    e.player_dead = torch.tensor([False, True, False])
-    e.mugshot_ouch = torch.tensor([True, False, False])
-    e.episode_time = torch.tensor([1, 20, 300], dtype=torch.int32)
-    e._player_bob_fixed = torch.tensor([0, 1 << 16, 5], dtype=torch.int64)
-    e.selected_weapon = torch.tensor([1, 3, 6])
-    e.selected_weapon_variant = torch.tensor([True, True, False])
-    for name in ("weapon_state_cooldown", "weapon_fire_count", "weapon_ready_tics", "weapon_raise_cooldown",
-                 "weapon_lower_cooldown", "mugshot_pain_tics", "mugshot_grin_tics", "attack_held_tics"):
-        setattr(e, name, torch.arange(n, dtype=torch.int32))
-    e.pending_weapon = torch.tensor([-1, 2, -1])
-    e.health, e.armor = torch.tensor([100.0, 0.0, 55.5]), torch.tensor([0.0, 200.0, 1.0])
-    e.hud_ready_ammo = torch.tensor([50.0, 7.0, 0.0])
-    e.hud_ammo_counts = torch.arange(n * 4, dtype=torch.float32).reshape(n, 4)
-    e.weapons = torch.tensor([[1, 1, 0, 0, 0, 0], [1, 1, 1, 0, 0, 1], [1, 0, 0, 0, 0, 0]], dtype=torch.float32)
-    e.mugshot_face_index = torch.tensor([0, 1, 2])
-    e.mugshot_pain_direction = torch.tensor([1, 0, 2])
-    return e
+def test_state_packer_lane_fields(pkg, oracle, scenes):
+    """Lane records from engine-shaped tensors (src/gradoom/engine.py:1658-1739, 2122-2133,
+    4673-4676, 10648-10658), through the CPU packer that checks the library's kernel."""
 
-
-def test_pack_lanes_fields(pkg):
+    from conftest import fake_engine
     from gradoom_b200 import state as gdstate
 
-    e = _fake_engine()
-    lanes = gdstate.pack_lanes(e, torch.tensor([4, 5, 6])).numpy()
-    assert lanes.shape == (3, 32) and lanes.dtype == np.int32
+    _sc, blob = scenes("c1")
+    e = fake_engine(3, seed=5)
+    e.player_dead = torch.tensor([False, True, False])
+    e.mugshot_ouch = torch.tensor([True, False, False])
+    e.selected_weapon = torch.tensor([1, 3, 6])
+    e.selected_weapon_variant = torch.tensor([True, True, False])
+    e.weapons = torch.tensor([[1, 1, 0, 0, 0, 0], [1, 1, 1, 0, 0, 1], [1, 0, 0, 0, 0, 0]], dtype=torch.float32)
+    lanes, things, k = oracle.pack_state(blob, e, 64)
+    assert lanes.shape == (3, 32) and lanes.dtype == np.int32 and things.shape == (3, 64, 4)
     assert np.array_equal(lanes[:, gdstate.L_X].view(np.float32), e.x.numpy())
     assert np.array_equal(lanes[:, gdstate.L_X_FIXED], e._x_fixed.numpy())
     assert np.array_equal(lanes[:, gdstate.L_ANGLE_BAM].view(np.uint32), e._angle_bam.numpy().astype(np.uint32))
     assert lanes[:, gdstate.L_FLAGS].tolist() == [2, 1, 0]
-    assert lanes[:, gdstate.L_THINGS].tolist() == [4, 5, 6]
+    assert lanes[:, gdstate.L_THINGS].tolist() == [k, k, k] and 0 < k <= 64
     # slot 1 + variant -> chainsaw (1); slot 3 + variant -> super shotgun (4); slot 6 -> plasma (7)
     assert lanes[:, gdstate.L_WEAPON].tolist() == [1, 4, 7]
     assert lanes[:, gdstate.L_WEAPONS_OWNED].tolist() == [3, 0b100111, 1]
     # an overridden public coordinate wins over the retained fixed value
     e.x = e.x + 1.0
-    lanes2 = gdstate.pack_lanes(e).numpy()
+    lanes2, _, _ = oracle.pack_state(blob, e, 64)
     assert np.array_equal(lanes2[:, gdstate.L_X_FIXED], np.round(e.x.numpy() * 65536).astype(np.int32))
+    # screen flashes travel in the flag word only when asked for
+    e.damage_count = torch.tensor([7, 200, 0], dtype=torch.int32)
+    e.bonus_count = torch.tensor([1, 2, 300], dtype=torch.int32)
+    lanes3, _, _ = oracle.pack_state(blob, e, 64, render_screen_flashes=True)
+    assert ((lanes3[:, gdstate.L_FLAGS] >> 8) & 0xFF).tolist() == [7, 113, 0]
+    assert ((lanes3[:, gdstate.L_FLAGS] >> 16) & 0xFF).tolist() == [1, 2, 255]
+    assert (lanes3[:, gdstate.L_FLAGS] & 4).tolist() == [4, 4, 4]
 
 
-def test_sprite_rotation_known_answers(pkg):
-    """Upstream tests/test_rendering.py:31-52."""
+def test_sprite_rotation_known_answers(pkg, oracle, scenes):
+    """Upstream tests/test_rendering.py:31-52: a viewer east / north / west / south of an
+    actor that faces east sees rotations 0, 2, 4, 6; just below the -pi/8 boundary is 0."""
 
     import math
-    from gradoom_b200 import state as gdstate
 
-    viewer = torch.tensor((0.0, math.pi / 2, math.pi, -math.pi / 2))
-    assert gdstate.sprite_rotation(viewer, torch.zeros_like(viewer)).tolist() == [0, 2, 4, 6]
+    from conftest import fake_engine
+
+    sc, blob = scenes("c1")
+    e = fake_engine(5, seed=9)
+    for name in ("enemy_alive", "enemy_death_tics", "teleport_fog_tics", "drop_spawned", "projectile_alive",
+                 "projectile_impact_tics", "enemy_projectile_alive", "enemy_projectile_impact_tics",
+                 "hitscan_puff_tics", "enemy_pain_tics", "enemy_attack_phase", "enemy_animation_tics"):
+        getattr(e, name).zero_()
+    e.enemy_alive[:, 0] = True
+    e.enemy_type[:, 0] = 4
+    e.enemy_target_slot[:, 0] = -1
+    e.enemy_x[:, 0], e.enemy_y[:, 0], e.enemy_angle[:, 0] = 500.0, 500.0, 0.0
     boundary = torch.tensor(-math.pi / 8, dtype=torch.float32)
     below = torch.nextafter(boundary, torch.tensor(float("-inf")))
-    assert gdstate.sprite_rotation(below, torch.zeros_like(below)).item() == 0
+    viewer = torch.tensor((0.0, math.pi / 2, math.pi, -math.pi / 2, float(below)))
+    e.x = 500.0 + 100.0 * torch.cos(viewer)
+    e.y = 500.0 + 100.0 * torch.sin(viewer)
+    e._x_fixed = torch.round(e.x * 65536).to(torch.int64)
+    e._y_fixed = torch.round(e.y * 65536).to(torch.int64)
+    _lanes, things, k = oracle.pack_state(blob, e, 8)
+    sprites = things[:, 0, 3] & 0xFFFF
+    assert k == 1 + (len(sc.player_starts) - 1)
+    assert sprites[:4].tolist() == [int(sc.enemy_walk_ids[4, 0, r]) for r in (0, 2, 4, 6)]
+    assert sprites[4] in (int(sc.enemy_walk_ids[4, 0, 0]), int(sc.enemy_walk_ids[4, 0, 7]))
+
+
+def test_engine_state_struct_matches_the_header(pkg):
+    """The ctypes mirror lists the fields of ``struct gd_engine_state`` in the header's order."""
+
+    from gradoom_b200 import state as gdstate
+
+    text = open(os.path.join(entry.ROOT, "include", "gradoom_b200.h")).read()
+    body = text[text.index("typedef struct gd_engine_state {"):text.index("} gd_engine_state;")]
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    names = []
+    for decl in body.split("{", 1)[1].split(";"):
+        decl = decl.strip()
+        if not decl:
+            continue
+        tail = re.sub(r"^(const\s+)?\w+\s+", "", decl)
+        names += [part.strip().lstrip("*").strip() for part in tail.split(",")]
+    mirror = [name for name, _ in gdstate.EngineStateStruct._fields_]
+    assert names == mirror
 
 
 def test_pack_things_roundtrip(pkg):

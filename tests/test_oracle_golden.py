@@ -9,7 +9,7 @@ test grants: tests/test_rendering.py:112-139).
 import numpy as np
 import pytest
 
-from conftest import load_golden
+from conftest import engine_from_fixture, load_golden
 
 
 @pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4", "c1m", "pitch", "fallback", "c2d", "c4d", "c1k"])
@@ -79,6 +79,25 @@ def test_oracle_replays_the_thousand_step_stack(pkg, oracle, scenes):
     assert known.all()
     assert np.abs(stack.astype(int) - data["frames"].astype(int)).max() <= 1
     assert int(data["checkpoints"][0]) == 1000
+
+
+def test_state_packer_feeds_the_upstream_frame(pkg, oracle, scenes):
+    """Engine tensors with every actor class in use (living monsters in all animation
+    states, voodoo doll, corpses, both kinds of projectiles and impacts, teleport fog,
+    puffs, map items, drops): packed by the oracle, drawn by the oracle, equal to the frame
+    the upstream renderer drew from the same tensors (engine.py:14328-14682, 14011-14136,
+    14258-14317)."""
+
+    data = load_golden("state")
+    _sc, blob = scenes("c1i", (data["ray_offsets"], data["ray_coscorr"]))
+    lanes, things, k = oracle.pack_state(blob, engine_from_fixture(data), 64)
+    assert k == data["things_0"].shape[1] and k >= 30
+    assert np.array_equal(lanes, data["lanes_0"]) and np.array_equal(things[:, :k], data["things_0"])
+    # every class contributes records
+    styles = things[:, :k, 3] >> 24
+    assert (styles == -2).any() and (styles == 0).any() and (styles == 1).any() and (styles == -1).any()
+    out = oracle.render(blob, lanes, things, mask_hud=True)
+    assert np.array_equal(out["indexed"], data["indexed_0"])
 
 
 def _area_axis(source, output):
