@@ -50,10 +50,32 @@ WORKLOADS = {
     "c3": {"lanes": 1024, "things": 12, "rgb": True, "map": "32-sector 4x8 map"},
     "c4": {"lanes": 8192, "things": 32, "rgb": False, "map": "256-sector 16x16 map with diagonals"},
 }
-# dram__bytes_read.sum + dram__bytes_write.sum of one render launch at 4096 lanes (one-pass ncu captures
-# of this file's default command and of --stack-policy roll), per lane; the rolled stack moves three old
-# slots per step, the ring only writes (and part of what it writes is still in L2 when the kernel ends)
-DRAM_TRAFFIC_PER_LANE = {"roll": 170.5e6 / 4096, "ring": 27.3e6 / 4096}
+PROFILE_FACTS = os.path.join(entry.ROOT, "profiles", "gd_render_kernel_c2_counters.json")
+
+
+def kernel_sources_hash():
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("gd_build", os.path.join(entry.PACKAGE_DIR, "csrc", "build.py"))
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    return module.sources_hash()
+
+
+def recorded_counters(stack_policy):
+    """ncu counters of one 4096-lane launch recorded under profiles/ (DRAM bytes per launch, L2 hit
+    rate), or Nones when the record was taken on other kernel sources than the ones in the tree."""
+
+    try:
+        with open(PROFILE_FACTS) as f:
+            facts = json.load(f)
+    except (OSError, ValueError):
+        return None, None, "no record under profiles/"
+    if facts.get("sources_sha256") != kernel_sources_hash():
+        return None, None, "the record under profiles/ was taken on other kernel sources"
+    entry_ = facts.get(stack_policy, {})
+    return entry_.get("dram_bytes_per_launch_4096_lanes"), facts.get("l2_hit_rate"), \
+        "profiles/" + os.path.basename(PROFILE_FACTS)
 
 
 def measured_peaks():
@@ -139,10 +161,97 @@ def cpu_baseline(blob, lanes, things, oracle, seconds=12.0, threads=1):
     return done / dt, done, dt
 
 
+def median_rate(call, units, warmup, repeats, steps):
+    """Median of `repeats` samples of units/s, each over `steps` calls, after `warmup` calls."""
+
+    for _ in range(warmup):
+        call()
+    samples = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            call()
+        samples.append(units * steps / (time.perf_counter() - t0))
+    return statistics.median(samples), samples
+
+
+def upstream_cpu_numbers(cores, workload, lanes_sample, steps, warmup):
+    """The upstream Torch engine on the host cores (installed under oracle/_ref by build()):
+    the five figures of the CPU configuration (16-sector map, 4 lanes, uniform actions) with a
+    shortened warm-up / median protocol, and the render of `lanes_sample` lanes of `workload`."""
+
+    import sys
+
+    import torch
+
+    sys.path.insert(0, os.path.join(entry.ROOT, "oracle"))
+    sys.path.insert(0, os.path.join(entry.ROOT, "tests", "golden"))
+    import ref_engine
+
+    if ref_engine.source_dir() is None:
+        return None
+    import make_golden
+
+    eng, scn, act = ref_engine.load_reference()
+    from gradoom_b200 import scene as gdscene
+
+    torch.set_num_threads(cores)
+    am = make_golden.action_matrix(act)
+    out = {"cores": cores, "torch": torch.__version__,
+           "protocol": "3 warm-up calls, median of 3 samples x 5 calls (the upstream tool uses 20 + 5 x 100)"}
+
+    def note(text):
+        print(f"[reference arm] {text}", file=sys.stderr, flush=True)
+
+    def engine(config, n, k, renderer):
+        note(f"upstream engine: {config}, {n} lanes, {renderer} renderer")
+        sc = gdscene.make_grid_scene(gdscene.GRID_CONFIGS[config])
+        e, _g = make_golden.make_engine(eng, scn, sc, n, k, seed=1234)
+        if renderer == "approximate":
+            del e.render_frame                  # the constructor default of the upstream environment
+        return e
+
+    g = torch.Generator().manual_seed(make_golden.ACTION_SEED)
+    for renderer in ("approximate", "reference"):
+        e = engine("c1", 4, 4, renderer)
+        n = 4
+
+        def step():
+            _f, _r, term, trunc = e.step(am[torch.randint(0, 17, (n,), generator=g)])
+            done = term | trunc
+            if bool(done.any()):
+                e.reset(done, torch.arange(n) + 77)
+
+        rate, samples = median_rate(step, n, 3, 3, 5)
+        note(f"step loop: {rate:.2f} frames/s")
+        out[f"c1_step_loop_{renderer}"] = {"frames_per_s": rate, "samples": samples}
+        if renderer == "approximate":
+            rate, samples = median_rate(lambda: type(e).render_frame(e), n, 3, 3, 5)
+            out["c1_render_frame_approximate"] = {"frames_per_s": rate, "samples": samples}
+        else:
+            rate, samples = median_rate(e.render_reference_frame, n, 1, 3, 3)
+            out["c1_render_reference_frame"] = {"frames_per_s": rate, "samples": samples}
+            rate, samples = median_rate(lambda: e.render_native_frame(include_hud=True), n, 1, 3, 3)
+            out["c1_render_native_frame_hud"] = {"frames_per_s": rate, "samples": samples}
+    e = engine(workload, lanes_sample, WORKLOADS[workload]["things"], "reference")
+    times = []
+    for k in range(warmup + steps):
+        t0 = time.perf_counter()
+        e.render_reference_frame()
+        if k >= warmup:
+            times.append(time.perf_counter() - t0)
+    out["headline"] = {"frames_per_s": lanes_sample * len(times) / sum(times), "lanes": lanes_sample,
+                       "calls": len(times), "seconds": sum(times)}
+    return out
+
+
 def run_reference(args):
-    """The reference arm: the CPU implementation of the path (the oracle port of
-    the upstream renderer; the upstream itself is Python and is not on this
-    machine) on all host threads, on a bounded sample of the same workload."""
+    """The reference arm: the upstream's own CPU implementation of the path on all host
+    threads.  `value` is the upstream Torch engine's render_reference_frame on a bounded
+    sample of the workload's lanes (oracle/_ref, installed by build()); beside it the C
+    restatement of the same pipeline (the oracle) over all lanes of the workload, and the
+    five figures of the upstream's CPU configuration.  Without an installed upstream the
+    C restatement is the value."""
 
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -152,36 +261,51 @@ def run_reference(args):
 
     oracle = entry.load_oracle()
     workload = args.workload
-    THINGS = WORKLOADS[workload]["things"]
+    spec = WORKLOADS[workload]
+    THINGS = spec["things"]
     sc = gdscene.make_grid_scene(gdscene.GRID_CONFIGS[workload])
     blob = gdscene.pack_scene(sc)
     cores = len(os.sched_getaffinity(0))
-    sample = 64 * cores
+    # the C restatement over the lanes of one full step of the workload
+    sample = min(spec["lanes"], 4096)
     lanes, things = stepper.random_lanes(sc, sample, THINGS, seed=11)
+    port_steps = max(min(args.steps, 3), 1)
     times = []
-    for step in range(args.warmup + args.steps):
+    for step in range(1 + port_steps):
         stepper.advance(sc, lanes, seed=step)
         t0 = time.perf_counter()
-        chunk = max(sample // cores, 1)
+        chunk = 16
         with ThreadPoolExecutor(max_workers=cores) as pool:
             list(pool.map(lambda i: oracle.render(blob, lanes[i:i + chunk], things[i:i + chunk], mask_hud=True,
                                                   stage_mask=7), range(0, sample, chunk)))
-        if step >= args.warmup:
+        if step >= 1:
             times.append(time.perf_counter() - t0)
-    total = sum(times)
-    value = sample * len(times) / total
+    port_value = sample * len(times) / sum(times)
+    port = {"value": port_value, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"all {sample} lanes of a {workload} step x {len(times)} steps, {cores} threads"}
+    upstream = None if args.skip_upstream else upstream_cpu_numbers(cores, workload, 4, max(min(args.steps, 8), 1),
+                                                                     min(args.warmup, 1))
+    if upstream is not None:
+        value = upstream["headline"]["frames_per_s"]
+        ms_per_step = 1000.0 * upstream["headline"]["seconds"] / upstream["headline"]["calls"]
+        baseline = {"value": value, "unit": UNIT, "cores": cores, "kind": "reference",
+                    "sample": f"upstream render_reference_frame (torch {upstream['torch']}, device=cpu), 4 lanes of the "
+                              f"{workload} map per call x {upstream['headline']['calls']} calls"}
+        sample_text = f"4 of {spec['lanes']} lanes per step"
+    else:
+        value, ms_per_step, baseline = port_value, 1000.0 * sum(times) / len(times), port
+        sample_text = f"{sample} of {spec['lanes']} lanes per step"
     line = {
         "impl": "reference", "metric": METRIC if workload == WORKLOAD else
-        f"rendered env-frames/sec at {WORKLOADS[workload]['lanes']} lanes/GPU ({workload})", "value": value, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * total / len(times),
+        f"rendered env-frames/sec at {spec['lanes']} lanes/GPU ({workload})", "value": value, "unit": UNIT,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "i64+f32", "data": "synthetic",
-        "config": {"workload": f"{workload}: {sample} of {WORKLOADS[workload]['lanes']} lanes, "
-                               f"{WORKLOADS[workload]['map']}, {THINGS} things/lane",
-                   "l2": "n/a (CPU)"},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": f"{sample} lanes per step x {len(times)} steps of the {workload} workload"},
+        "config": {"workload": f"{workload}: {spec['lanes']} lanes/GPU, {spec['map']}, {THINGS} things/lane, "
+                               + ("obs and RGB24 frame every step" if spec["rgb"] else "obs only"),
+                   "lanes_per_gpu": spec["lanes"], "sample": sample_text, "l2": "n/a (CPU)"},
+        "cpu_baseline": baseline, "cpu_port": port, "upstream_cpu": upstream,
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
+        "gpu_launches": 0, "host_cores": cores,
     }
     print(json.dumps(line), flush=True)
 
@@ -209,12 +333,14 @@ def run_ours(args):
     sc = gdscene.make_grid_scene(gdscene.GRID_CONFIGS[workload])
     blob = gdscene.pack_scene(sc)
     n = args.lanes if args.lanes else spec["lanes"]
-    producer = stepper.LaneStepper(sc, n, device=device, k_things=THINGS, max_things=THINGS, seed=1000 + rank)
+    # every rank draws the same seeded lane population (its lanes differ only in their global ids), so
+    # that the ranks' times measure the machine and not the seeds
+    producer = stepper.LaneStepper(sc, n, device=device, k_things=THINGS, max_things=THINGS, seed=1000)
     renderer = native.Renderer(blob, device, THINGS)
     stack = torch.zeros((n, 4, 84, 84), dtype=torch.uint8, device=device)
     rgb = torch.empty((n, 240, 320, 3), dtype=torch.uint8, device=device) if spec["rgb"] else None
-    # timed leg: the mirrored eight-slot ring (no old frame is moved) unless --stack-policy roll asks for
-    # the reference's contiguous rolled stack; the RGB workload and the host-buffer leg use the rolled one
+    # timed leg: the reference's contiguous rolled stack (what GraDoomVecEnv hands out by default);
+    # --stack-policy ring times the mirrored eight-slot ring (no old frame is moved) instead
     use_ring = args.stack_policy == "ring" and rgb is None
     ring = torch.zeros((n, 8, 84, 84), dtype=torch.uint8, device=device) if use_ring else None
     ring_head = 3
@@ -237,7 +363,7 @@ def run_ours(args):
     if use_ring:
         renderer.reset_ring(lanes, things, everyone, ring)
     actions = torch.randint(0, 17, (args.warmup + 2 * args.steps + 8, n), device=device,
-                            generator=torch.Generator(device=device).manual_seed(20260813 + rank))
+                            generator=torch.Generator(device=device).manual_seed(20260813))
     from gradoom_b200.env import action_matrix
 
     buttons = action_matrix(device)
@@ -266,6 +392,9 @@ def run_ours(args):
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     gathered = None
+    gather_every = min(100, args.steps)        # the statistics collective, once per 100 steps (or per run)
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    gather_us = None
     barrier()
     wall0 = time.time()
     launches0 = renderer.launches
@@ -275,10 +404,14 @@ def run_ours(args):
         starts[k].record()
         render_step()
         ends[k].record()
-        if (k + 1) % 100 == 0:
+        if (k + 1) % gather_every == 0:
+            g0.record()
             gathered = stats.gather_lane_stats(producer.signal_buffer)
+            g1.record()
     barrier()
     wall1 = time.time()
+    if gathered is not None:
+        gather_us = 1000.0 * g0.elapsed_time(g1)
     kernel_ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
     launches = renderer.launches - launches0
     renderer.check_status()
@@ -292,6 +425,7 @@ def run_ours(args):
         dist.all_reduce(elapsed_ms, op=dist.ReduceOp.MAX)
     total_ms = float(elapsed_ms.item())
     value = world * n * args.steps / (total_ms / 1000.0)
+    sum_of_rank_rates = sum(n / (ms / 1000.0) for ms in per_rank_ms)
 
     # end to end through the host-buffer entry point: pinned records in, newest frames out
     host_lanes = torch.empty(lanes.shape, dtype=torch.int32).pin_memory()
@@ -349,6 +483,9 @@ def run_ours(args):
         oracle = entry.load_oracle()
         peak, peak_kind = measured_peaks()
         avg_ms = statistics.mean(kernel_ms)
+        policy = "ring" if use_ring else "roll"
+        traffic, l2_hit, counters_source = recorded_counters(policy)
+        sm_hz = (clocks.get("sm_mhz") or 0) * 1e6 or None
         bytes_per_frame = 84 * 84 + 64 + 16 * THINGS + (240 * 320 * 3 if rgb is not None else 0)
         achieved = bytes_per_frame * n / (avg_ms / 1000.0) / 1e9
         cpu_lanes, cpu_things = stepper.random_lanes(sc, 2048, THINGS, seed=11)
@@ -367,17 +504,18 @@ def run_ours(args):
                        "stack_policy": "mirrored ring (write 2 of 8 slots per lane, no reads)" if use_ring
                        else "roll (read 3 + write 4 slots per lane)"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": DRAM_TRAFFIC_PER_LANE[args.stack_policy] * n
-                         if (workload, n) == (WORKLOAD, 4096) else None,
-                         "traffic_source": "ncu capture of this command at 4096 lanes/GPU", "peak_source": peak_kind,
+                         "traffic": traffic if (workload, n, rgb) == (WORKLOAD, 4096, None) else None,
+                         "traffic_source": counters_source + " (ncu capture of this command, recorded; not "
+                         "measured by this run)", "peak_source": peak_kind,
                          "algorithmic_bytes_per_launch": bytes_per_frame * n,
                          "kernel_ms": avg_ms, "pixels_per_s": 320 * 208 * n / (avg_ms / 1000.0),
                          # the path is bound on chip, not by HBM: >= 5 B of shared-memory / L2 gathers per
                          # shaded pixel (texel, colormap, frame byte, masks) against 128 B/clk/SM of shared memory
+                         # at the SM clock sampled during this run
                          "onchip": {"bytes_per_s": 5 * 320 * 208 * n / (avg_ms / 1000.0),
-                                    "peak_bytes_per_s": 148 * 128 * 1.965e9,
-                                    "frac": 5 * 320 * 208 * n / (avg_ms / 1000.0) / (148 * 128 * 1.965e9),
-                                    "l2_hit_rate_ncu": 0.857}},
+                                    "peak_bytes_per_s": 148 * 128 * sm_hz if sm_hz else None,
+                                    "frac": 5 * 320 * 208 * n / (avg_ms / 1000.0) / (148 * 128 * sm_hz) if sm_hz else None,
+                                    "l2_hit_rate_recorded": l2_hit}},
             "cpu_baseline": {"value": cpu_value, "unit": UNIT, "cores": 1, "kind": "port",
                              "sample": f"{cpu_done} lanes of the {workload} workload in {cpu_dt:.1f} s, one thread"},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(host_lanes.numel() * 4
@@ -386,10 +524,13 @@ def run_ours(args):
             "whole_step": {"value": api_value, "unit": UNIT, "steps": api_steps,
                            "api": "GraDoomVecEnv.step_and_reset_device, device tensors, no host sync",
                            "producer": "synthetic lane stepper (torch elementwise ops)"},
-            "per_rank_ms_per_step": per_rank_ms, "host_cores": len(os.sched_getaffinity(0)),
+            "per_rank_ms_per_step": per_rank_ms, "sum_of_rank_rates": sum_of_rank_rates,
+            "host_cores": len(os.sched_getaffinity(0)),
             "gpu_launches": launches,
             "clocks": clocks,
-            "stats_gather": None if gathered is None else list(gathered.shape),
+            "stats_gather": None if gathered is None else {
+                "shape": list(gathered.shape), "every_steps": gather_every, "collective_us": gather_us,
+                "backend": "nccl all_gather_into_tensor" if world > 1 else "single rank (no collective)"},
             "wall_s": wall1 - wall0,
         }
         print(json.dumps(line), flush=True)
@@ -520,8 +661,11 @@ def main():
                     help="benchmark configuration (default: the headline one)")
     ap.add_argument("--lanes", type=int, default=0, help="lanes per GPU (default: the workload's own count)")
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg (profiling captures)")
-    ap.add_argument("--stack-policy", default="ring", choices=["ring", "roll"],
-                    help="frame stack of the timed leg: mirrored eight-slot ring, or the reference's rolled stack")
+    ap.add_argument("--stack-policy", default="roll", choices=["roll", "ring"],
+                    help="frame stack of the timed leg: the reference's contiguous rolled stack (the drop-in "
+                         "contract), or the mirrored eight-slot ring")
+    ap.add_argument("--skip-upstream", action="store_true",
+                    help="reference arm: time only the C restatement, not the upstream Torch engine")
     ap.add_argument("--no-graph", action="store_true", help="c5 only: launch the rollout eagerly instead of as a CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

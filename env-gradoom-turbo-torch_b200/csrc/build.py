@@ -19,6 +19,19 @@ NVCC_FLAGS = [
 ]
 
 
+def sources_hash() -> str:
+    """SHA-256 over the kernel sources and the two headers, in a fixed order: profile
+    summaries are stamped with it so that a figure measured on other code is not quoted."""
+
+    import hashlib
+
+    digest = hashlib.sha256()
+    for name in sorted(SOURCES + HEADERS):
+        with open(os.path.join(HERE, name), "rb") as f:
+            digest.update(name.encode() + b"\0" + f.read())
+    return digest.hexdigest()
+
+
 def is_stale() -> bool:
     if not os.path.exists(LIBRARY):
         return True

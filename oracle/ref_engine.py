@@ -1,10 +1,13 @@
-"""Bridge to the upstream Torch engine, used ONLY to generate golden vectors.
+"""Bridge to the upstream Torch engine (TEST INFRASTRUCTURE, never on the product path).
 
-The upstream package lives outside this repository and is importable only on
-the machine where the fixtures are generated; nothing in the test-suite or the
-product imports this module at run time.  ``make_golden.py`` uses it to run the
-upstream CPU renderer on seeded synthetic scenes and to store its inputs and
-outputs as ``.npz`` fixtures.
+Two users: ``tests/golden/make_golden.py`` runs the upstream CPU renderer on seeded
+synthetic scenes to record the golden fixtures, and the reference arm of ``bench.py``
+times the upstream engine on the host cores.  The upstream package is pure Python;
+``install()`` puts an unmodified copy of its ``src/gradoom`` package under
+``oracle/_ref/`` (git-ignored, so it never enters the history, but it travels with the
+working tree to the machine that runs the benchmark), the way ``pip install --target``
+would.  ``load()`` imports the engine module from there, or from the directory named by
+``GRADOOM_REFERENCE_SRC``.
 """
 
 from __future__ import annotations
@@ -16,7 +19,30 @@ import types
 
 import numpy as np
 
-REFERENCE_SRC = os.environ.get("GRADOOM_REFERENCE_SRC", "")   # <upstream checkout>/src/gradoom
+HERE = os.path.dirname(os.path.abspath(__file__))
+INSTALLED = os.path.join(HERE, "_ref", "gradoom")
+
+
+def install(upstream_checkout: str) -> str | None:
+    """Copy the upstream package, unmodified, to ``oracle/_ref/gradoom``.  Returns the
+    directory, or None when the checkout is not on this machine."""
+
+    import shutil
+
+    src = os.path.join(upstream_checkout, "src", "gradoom")
+    if not os.path.isdir(src):
+        return INSTALLED if os.path.isdir(INSTALLED) else None
+    if os.path.isdir(INSTALLED):
+        shutil.rmtree(INSTALLED)
+    shutil.copytree(src, INSTALLED, ignore=shutil.ignore_patterns("__pycache__", "*.pyc"))
+    return INSTALLED
+
+
+def source_dir() -> str | None:
+    env = os.environ.get("GRADOOM_REFERENCE_SRC", "")   # <upstream checkout>/src/gradoom
+    if os.path.isdir(env):
+        return env
+    return INSTALLED if os.path.isdir(INSTALLED) else None
 
 
 def load_reference():
@@ -26,11 +52,13 @@ def load_reference():
     engine module itself only needs numpy and torch.
     """
 
-    if not os.path.isdir(REFERENCE_SRC):
-        raise SystemExit("set GRADOOM_REFERENCE_SRC to the upstream checkout's src/gradoom directory")
+    src = source_dir()
+    if src is None:
+        raise SystemExit("the upstream package is neither installed under oracle/_ref nor named by "
+                         "GRADOOM_REFERENCE_SRC (<upstream checkout>/src/gradoom)")
     if "gradoom" not in sys.modules:
         pkg = types.ModuleType("gradoom")
-        pkg.__path__ = [REFERENCE_SRC]
+        pkg.__path__ = [src]
         sys.modules["gradoom"] = pkg
     engine = importlib.import_module("gradoom.engine")
     scenario = importlib.import_module("gradoom.scenario")

@@ -35,7 +35,8 @@ from __graft_entry__ import load_oracle, load_package  # noqa: E402
 load_package()
 oracle = load_oracle()
 from gradoom_b200 import scene as gdscene, state as gdstate  # noqa: E402
-import refbridge  # noqa: E402
+sys.path.insert(0, os.path.join(ROOT, "oracle"))
+import ref_engine as refbridge  # noqa: E402
 
 PLANS = {
     # name: (config, lanes, monsters per lane, checkpoints (agent steps))
