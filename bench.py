@@ -337,6 +337,7 @@ def run_ours(args):
     # that the ranks' times measure the machine and not the seeds
     producer = stepper.LaneStepper(sc, n, device=device, k_things=THINGS, max_things=THINGS, seed=1000)
     renderer = native.Renderer(blob, device, THINGS)
+    producer.bind_renderer(renderer)          # the players' kinematics run in the renderer's library
     stack = torch.zeros((n, 4, 84, 84), dtype=torch.uint8, device=device)
     rgb = torch.empty((n, 240, 320, 3), dtype=torch.uint8, device=device) if spec["rgb"] else None
     # timed leg: the reference's contiguous rolled stack (what GraDoomVecEnv hands out by default);
@@ -523,7 +524,7 @@ def run_ours(args):
                     "d2h_bytes_per_step": int(host_obs.numel()), "steps": e2e_steps},
             "whole_step": {"value": api_value, "unit": UNIT, "steps": api_steps,
                            "api": "GraDoomVecEnv.step_and_reset_device, device tensors, no host sync",
-                           "producer": "synthetic lane stepper (torch elementwise ops)"},
+                           "producer": "player kinematics kernel (gd_player_tics) + synthetic things"},
             "per_rank_ms_per_step": per_rank_ms, "sum_of_rank_rates": sum_of_rank_rates,
             "host_cores": len(os.sched_getaffinity(0)),
             "gpu_launches": launches,

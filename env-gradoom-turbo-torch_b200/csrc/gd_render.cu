@@ -433,3 +433,4 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
 #include "gd_abi.cuh"
 #include "gd_state.cuh"
 #include "gd_state_abi.cuh"
+#include "gd_move.cuh"

@@ -23,7 +23,7 @@ EXPORTS = (
     "gd_error_string", "gd_renderer_create", "gd_renderer_destroy", "gd_renderer_scratch_bytes",
     "gd_renderer_ctas", "gd_renderer_shared_bytes", "gd_render_step", "gd_render_reset", "gd_render_frames",
     "gd_render_step_frames", "gd_render_step_host", "gd_render_step_ring", "gd_render_reset_ring", "gd_static_scratch_bytes", "gd_static_max_walls", "gd_render_step_static",
-    "gd_pack_state_scratch_bytes", "gd_pack_state",
+    "gd_pack_state_scratch_bytes", "gd_pack_state", "gd_player_tics",
 )
 
 _lib = None
@@ -80,6 +80,8 @@ def load() -> ctypes.CDLL:
         lib.gd_pack_state_scratch_bytes.argtypes = []
         lib.gd_pack_state.restype = ci
         lib.gd_pack_state.argtypes = [vp, vp, vp, vp, vp, sz, vp, vp]
+        lib.gd_player_tics.restype = ci
+        lib.gd_player_tics.argtypes = [vp, vp, vp, vp, ci, ci, ci, vp, vp, vp]
         _lib = lib
     return _lib
 
@@ -167,6 +169,28 @@ class Renderer:
                                           self.flags_scratch.numel(), self.status.data_ptr(), self._stream()),
                    "gd_pack_state")
         self.launches += 2
+
+    def player_tics(self, players, buttons, tics, episode_timeout, *, lanes=None, actors=None):
+        """Advance the player kinematics records ``players (N,24) int32`` in place by ``tics``
+        game tics under ``buttons (N,) int32`` button masks; with ``lanes`` the new pose is
+        also written into the lane records.  ``actors``: a ``state.SolidActors`` or None."""
+
+        n = players.shape[0]
+        if players.dtype != torch.int32 or players.dim() != 2 or players.shape[1] != 24 or not players.is_contiguous():
+            raise ValueError("players must be a contiguous (N,24) int32 tensor")
+        if buttons.dtype != torch.int32 or tuple(buttons.shape) != (n,) or not buttons.is_contiguous():
+            raise ValueError("buttons must be a contiguous (N,) int32 tensor of button masks")
+        if lanes is not None and (lanes.dtype != torch.int32 or tuple(lanes.shape) != (n, 32) or not lanes.is_contiguous()):
+            raise ValueError("lanes must be a contiguous (N,32) int32 tensor")
+        for t in (players, buttons, lanes):
+            if t is not None and t.device != self.device:
+                raise TypeError("the kinematics buffers must live on the renderer's device")
+        with torch.cuda.device(self.device):
+            _check(self.lib.gd_player_tics(self.handle, players.data_ptr(), buttons.data_ptr(),
+                                           None if actors is None else ctypes.byref(actors.struct), n, int(tics),
+                                           int(episode_timeout), _ptr(lanes), self.status.data_ptr(), self._stream()),
+                   "gd_player_tics")
+        self.launches += 1
 
     def step(self, lanes, things, stack, mask_hud=True):
         n = self._inputs(lanes, things)

@@ -36,6 +36,14 @@ BAM_TO_RADIANS = 2.0 * math.pi / float(1 << 32)
  L_AMMO0, L_AMMO1, L_AMMO2, L_AMMO3, L_WEAPONS_OWNED, L_FACE_INDEX, L_PAIN_DIRECTION,
  L_PAIN_TICS, L_GRIN_TICS, L_ATTACK_HELD) = range(32)
 
+# word indices of the player kinematics record (enum gd_player_word)
+PLAYER_WORDS = 24
+(P_X_FIXED, P_Y_FIXED, P_MOMENTUM_X, P_MOMENTUM_Y, P_ANGLE_BAM, P_PITCH_BAM, P_BOB, P_Z, P_VIEW_Z, P_VIEW_HEIGHT,
+ P_DELTA_VIEW_HEIGHT, P_VELOCITY_Z, P_FLOOR_Z, P_CEILING_Z, P_PREV_FLOOR_Z, P_REACTION_TIME, P_TURN_HELD,
+ P_EPISODE_TIME, P_FLAGS, P_RESERVED) = range(20)
+PLAYER_DEAD = 1
+PLAYER_CHAINSAW_PULL = 2
+
 THING_ALIVE = 1
 THING_BRIGHT = 2
 FLAG_SCREEN_FLASHES = 4
@@ -152,6 +160,63 @@ class EngineState:
     @property
     def n(self) -> int:
         return int(self.struct.n)
+
+
+SOLID_ACTOR_POINTERS = (
+    ("enemy_x", _F32), ("enemy_y", _F32), ("enemy_z", _F32), ("enemy_type", _I64), ("enemy_death_type", _I64),
+    ("enemy_death_tics", _I32), ("enemy_death_elapsed", _I32), ("enemy_alive", _U8), ("enemy_death_extreme", _U8),
+)
+
+
+class SolidActorsStruct(ctypes.Structure):
+    """ctypes mirror of ``struct gd_solid_actors``."""
+
+    _fields_ = [("enemy_slots", ctypes.c_int32), ("reserved", ctypes.c_int32)] + \
+               [(name, ctypes.c_void_p) for name, _d in SOLID_ACTOR_POINTERS]
+
+
+class SolidActors:
+    """Pointer table of the monsters that block the player (``gd_solid_actors``)."""
+
+    def __init__(self, src):
+        self.src = src
+        self.struct = SolidActorsStruct()
+        self.refresh()
+
+    def refresh(self) -> "SolidActors":
+        self.keep = []
+        self.device = self.src.enemy_x.device
+        self.struct.enemy_slots = int(self.src.enemy_x.shape[1])
+        for name, dtype in SOLID_ACTOR_POINTERS:
+            c = _as_dtype(getattr(self.src, name), dtype)
+            self.keep.append(c)
+            setattr(self.struct, name, c.data_ptr())
+        return self
+
+
+def player_records(src) -> torch.Tensor:
+    """``(N,24) int32`` player kinematics records from an object that carries the reference
+    engine's player tensors (src/gradoom/engine.py:1658-1744)."""
+
+    n = src.x.shape[0]
+    out = torch.zeros((n, PLAYER_WORDS), dtype=torch.int32, device=src.x.device)
+    out[:, P_X_FIXED] = src._x_fixed.to(torch.int32)
+    out[:, P_Y_FIXED] = src._y_fixed.to(torch.int32)
+    out[:, P_MOMENTUM_X] = src._momentum_x_fixed.to(torch.int32)
+    out[:, P_MOMENTUM_Y] = src._momentum_y_fixed.to(torch.int32)
+    out[:, P_ANGLE_BAM] = _u32_as_i32(src._angle_bam)
+    out[:, P_PITCH_BAM] = src._pitch_bam.to(torch.int32)
+    out[:, P_BOB] = src._player_bob_fixed.to(torch.int32)
+    for word, name in ((P_Z, "z"), (P_VIEW_Z, "view_z"), (P_VIEW_HEIGHT, "view_height"),
+                       (P_DELTA_VIEW_HEIGHT, "delta_view_height"), (P_VELOCITY_Z, "velocity_z"),
+                       (P_FLOOR_Z, "player_floor_z"), (P_CEILING_Z, "player_ceiling_z"),
+                       (P_PREV_FLOOR_Z, "previous_player_floor_z")):
+        out[:, word] = _f32_bits(getattr(src, name))
+    out[:, P_REACTION_TIME] = src.reaction_time.to(torch.int32)
+    out[:, P_TURN_HELD] = src.turn_held_tics.to(torch.int32)
+    out[:, P_EPISODE_TIME] = src.episode_time.to(torch.int32)
+    out[:, P_FLAGS] = src.player_dead.to(torch.int32) * PLAYER_DEAD + src.chainsaw_pull.to(torch.int32) * PLAYER_CHAINSAW_PULL
+    return out
 
 
 def _f32_bits(t: torch.Tensor) -> torch.Tensor:

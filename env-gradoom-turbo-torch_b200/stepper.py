@@ -122,14 +122,18 @@ def advance(sc: gdscene.Scene, lanes: np.ndarray, seed: int, turn_bam: int = 640
 
 
 class LaneStepper:
-    """Device-resident state producer for throughput runs (no parity claim).
+    """Device-resident state producer of the environment.
 
-    Keeps packed lane / thing records on the device and evolves them with a few
-    elementwise torch ops per step: players turn and move inside the map, the
-    view height follows the floor of the room they stand in, an ATTACK press
-    kills a thing now and then (which feeds the per-lane statistics), episodes
-    time out.  It exposes what ``GraDoomVecEnv`` needs from a producer:
-    ``reset``, ``step``, ``render_inputs``, ``signal_buffer``, ``pending_reset``.
+    The players move with the reference's own per-tic kinematics, computed by the CUDA
+    library (``gd_player_tics``: keyboard turn ramp, thrust, wall slide, step-up, view-height
+    easing, gravity; src/gradoom/engine.py:4344-4671, 3207-3498) on player records kept on the
+    device.  Everything else is synthetic and makes no parity claim: reset places the
+    players at seeded positions inside the rooms (the reference draws them from its own
+    random streams), the things stand still, an ATTACK press kills one now and then (which
+    feeds the per-lane statistics), episodes time out.  It exposes what ``GraDoomVecEnv``
+    needs from a producer: ``reset``, ``step``, ``render_inputs``, ``signal_buffer``,
+    ``pending_reset``, and ``bind_renderer`` (the kinematics kernel lives in the renderer's
+    library; there is no fallback without it).
     """
 
     SIGNALS = 27  # width of the reference's signal buffer (src/gradoom/engine.py:509-539)
@@ -154,7 +158,39 @@ class LaneStepper:
         self.signal_buffer = torch.zeros((num_envs, self.SIGNALS), dtype=torch.float32, device=self.device)
         self.pending_reset = torch.zeros(num_envs, dtype=torch.bool, device=self.device)
         self.lanes[:, gdstate.L_EPISODE_TIME] = 1
+        self.ceilings = torch.as_tensor(sc.sector_heights[:, 1].astype(np.float32), device=self.device)
+        self.players = torch.zeros((num_envs, gdstate.PLAYER_WORDS), dtype=torch.int32, device=self.device)
+        self.button_weights = None
+        self.renderer = None
         self._tick = 0
+        self._players_from_lanes(torch.ones(num_envs, dtype=torch.bool, device=self.device))
+
+    def bind_renderer(self, renderer):
+        self.renderer = renderer
+
+    def _players_from_lanes(self, mask):
+        """Player records of freshly placed lanes: standing on the floor of their room."""
+
+        torch = self.torch
+        lanes, players = self.lanes, self.players
+        room = float(self.spec.room)
+        xf = lanes[:, gdstate.L_X_FIXED].to(torch.float32) / FIXED_UNIT
+        yf = lanes[:, gdstate.L_Y_FIXED].to(torch.float32) / FIXED_UNIT
+        col = torch.clamp((xf / room).to(torch.int64), 0, self.spec.cols - 1)
+        row = torch.clamp((yf / room).to(torch.int64), 0, self.spec.rows - 1)
+        sector = row * self.spec.cols + col
+        floor, ceiling = self.floors[sector], self.ceilings[sector]
+        fresh = torch.zeros_like(players)
+        fresh[:, gdstate.P_X_FIXED] = lanes[:, gdstate.L_X_FIXED]
+        fresh[:, gdstate.P_Y_FIXED] = lanes[:, gdstate.L_Y_FIXED]
+        fresh[:, gdstate.P_ANGLE_BAM] = lanes[:, gdstate.L_ANGLE_BAM]
+        for word, value in ((gdstate.P_Z, floor), (gdstate.P_VIEW_Z, floor + VIEW_HEIGHT),
+                            (gdstate.P_VIEW_HEIGHT, torch.full_like(floor, VIEW_HEIGHT)), (gdstate.P_FLOOR_Z, floor),
+                            (gdstate.P_CEILING_Z, ceiling), (gdstate.P_PREV_FLOOR_Z, floor)):
+            fresh[:, word] = value.contiguous().view(torch.int32)
+        fresh[:, gdstate.P_REACTION_TIME] = 7       # the input freeze after a spawn (src/gradoom/engine.py:81, 2407)
+        fresh[:, gdstate.P_EPISODE_TIME] = lanes[:, gdstate.L_EPISODE_TIME]
+        players.copy_(torch.where(mask[:, None], fresh, players))
 
     # deterministic per-lane pseudo random numbers in [0, 1)
     def _uniform(self, seeds, salt):
@@ -218,6 +254,9 @@ class LaneStepper:
         if self.k > 0:
             word = self.things[:, :, 3]
             self.things[:, :, 3] = torch.where(mask[:, None], word | (THING_ALIVE_BIT), word)
+        self.lanes[:, gdstate.L_BOB_FIXED] = torch.where(mask, torch.zeros_like(self.lanes[:, 0]),
+                                                         self.lanes[:, gdstate.L_BOB_FIXED])
+        self._players_from_lanes(mask)
         self.signal_buffer[mask] = 0
         self.signal_buffer[:, 1] = torch.where(mask, torch.full_like(self.signal_buffer[:, 1], 100.0),
                                                self.signal_buffer[:, 1])
@@ -226,28 +265,16 @@ class LaneStepper:
     def step(self, buttons):
         torch = self.torch
         lanes = self.lanes
-        everyone = torch.ones(self.num_envs, dtype=torch.bool, device=self.device)
+        if self.renderer is None:
+            raise RuntimeError("the lane stepper moves its players with the renderer's library: "
+                               "bind_renderer() first (GraDoomVecEnv does it)")
         self._tick += 1
         b = buttons.to(torch.int64)
-        speed = 1 + b[:, 1]
-        forward = (b[:, 6] - b[:, 5]) * speed
-        strafe = b[:, 3] - b[:, 4]
-        turn = b[:, 8] - b[:, 7]
-        bam = lanes[:, gdstate.L_ANGLE_BAM].to(torch.int64) & 0xFFFFFFFF
-        bam = (bam + turn * (640 << 16) * self.frame_skip) & 0xFFFFFFFF
-        ang = bam.to(torch.float64) * (2.0 * np.pi / (1 << 32))
-        step_units = 6.0 * self.frame_skip * FIXED_UNIT
-        dx = (torch.cos(ang) * forward + torch.sin(ang) * strafe) * step_units
-        dy = (torch.sin(ang) * forward - torch.cos(ang) * strafe) * step_units
-        x_fixed = lanes[:, gdstate.L_X_FIXED].to(torch.int64) + dx.to(torch.int64)
-        y_fixed = lanes[:, gdstate.L_Y_FIXED].to(torch.int64) + dy.to(torch.int64)
-        lo = 20 * FIXED_UNIT
-        x_fixed = torch.clamp(x_fixed, lo, int(self.spec.cols * self.spec.room * FIXED_UNIT) - lo)
-        y_fixed = torch.clamp(y_fixed, lo, int(self.spec.rows * self.spec.room * FIXED_UNIT) - lo)
-        self._refresh_pose(x_fixed, y_fixed, bam, everyone)
-        lanes[:, gdstate.L_EPISODE_TIME] += self.frame_skip
-        moving = ((forward != 0) | (strafe != 0)).to(torch.int32)
-        lanes[:, gdstate.L_BOB_FIXED] = moving * (8 * FIXED_UNIT)
+        if self.button_weights is None or self.button_weights.shape[0] != b.shape[1]:
+            self.button_weights = 1 << torch.arange(b.shape[1], device=self.device, dtype=torch.int64)
+        masks = (b * self.button_weights).sum(dim=1).to(torch.int32)
+        # frame_skip game tics under the same buttons; the kernel also refreshes the pose words of the lane records
+        self.renderer.player_tics(self.players, masks, self.frame_skip, self.episode_timeout, lanes=lanes)
         # an attack kills the first living thing once in a while
         rewards = torch.zeros(self.num_envs, dtype=torch.float32, device=self.device)
         if self.k > 0:

@@ -247,6 +247,35 @@ int gd_pack_state(const gd_renderer *r, const gd_engine_state *state, int32_t *l
                   void *flags_scratch, size_t flags_scratch_bytes, int *status, void *stream);
 
 /*
+ * Per-tic player kinematics on the device, one thread per lane: turning with the
+ * keyboard ramp, thrust, bob, the wall slide with step-up over the openings under
+ * the player's box, solid actors in the way, friction, view-height easing, gravity
+ * and landing.  Advances every lane by `tics` game tics under the lane's button mask
+ * (bit i = button i of the reference's button list, src/gradoom/actions.py:10-31) and,
+ * when `lanes` is not NULL, writes the new pose into the lane records the render
+ * calls read (x, y, angle, view_z, the fixed-point pose, pitch, bob, episode time).
+ * Replaces, for the player's pose: _move_player, _doom_axis_slide_move and
+ * _vertical_player_tick inside the tic loop of TorchDeathmatchEngine.step
+ * (src/gradoom/engine.py:4344-4575, 3207-3498, 4577-4671, 9558-9573).  Weapons,
+ * attacks, monsters' thinking and pickups are not part of it.
+ * players: n x GD_PLAYER_WORDS i32 (gradoom_b200_layout.h); buttons: n u32;
+ * `actors` (may be NULL): the solid monsters of every lane, under the reference
+ * engine's names and dtypes, which block the player like the voodoo dolls of the
+ * scene do.
+ */
+typedef struct gd_solid_actors {
+  int32_t enemy_slots;
+  int32_t reserved;
+  const float *enemy_x, *enemy_y, *enemy_z;
+  const int64_t *enemy_type, *enemy_death_type;
+  const int32_t *enemy_death_tics, *enemy_death_elapsed;
+  const uint8_t *enemy_alive, *enemy_death_extreme;
+} gd_solid_actors;
+
+int gd_player_tics(const gd_renderer *r, int32_t *players, const uint32_t *buttons, const gd_solid_actors *actors,
+                   int n, int tics, int episode_timeout, int32_t *lanes, int *status, void *stream);
+
+/*
  * No counterpart in the reference.  gd_render_step for callers that may not
  * allocate device memory -- a plugin inside a host process whose GPU memory
  * pool is owned and budgeted by the embedding application, or code running

@@ -183,6 +183,37 @@ enum gd_lane_word {
 };
 
 /*
+ * Player kinematics record: 24 words (96 bytes) per lane, the state the per-tic
+ * player movement reads and writes (src/gradoom/engine.py:1658-1744, narrowed to
+ * 32 bits: every fixed-point value of a map fits).
+ */
+#define GD_PLAYER_WORDS 24
+enum gd_player_word {
+  GD_P_X_FIXED = 0,        /* i32 16.16 (_x_fixed) */
+  GD_P_Y_FIXED,
+  GD_P_MOMENTUM_X,         /* i32 16.16 (_momentum_x_fixed) */
+  GD_P_MOMENTUM_Y,
+  GD_P_ANGLE_BAM,          /* u32 (_angle_bam) */
+  GD_P_PITCH_BAM,          /* i32 (_pitch_bam) */
+  GD_P_BOB,                /* i32 16.16 (_player_bob_fixed) */
+  GD_P_Z,                  /* f32 feet height */
+  GD_P_VIEW_Z,             /* f32 camera height */
+  GD_P_VIEW_HEIGHT,        /* f32 */
+  GD_P_DELTA_VIEW_HEIGHT,  /* f32 */
+  GD_P_VELOCITY_Z,         /* f32 */
+  GD_P_FLOOR_Z,            /* f32 player_floor_z */
+  GD_P_CEILING_Z,          /* f32 player_ceiling_z */
+  GD_P_PREV_FLOOR_Z,       /* f32 previous_player_floor_z */
+  GD_P_REACTION_TIME,      /* i32 tics of input freeze left */
+  GD_P_TURN_HELD,          /* i32 turn_held_tics */
+  GD_P_EPISODE_TIME,       /* i32 */
+  GD_P_FLAGS,              /* GD_PLAYER_* */
+  GD_P_RESERVED
+};
+#define GD_PLAYER_DEAD 1
+#define GD_PLAYER_CHAINSAW_PULL 2
+
+/*
  * Thing record: 16 bytes.  One per drawable actor of a lane, in the order the
  * reference concatenates them (src/gradoom/engine.py:14328-14682).
  */

@@ -16,6 +16,7 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 SOURCE = os.path.join(HERE, "gd_oracle.c")
 STATE_SOURCE = os.path.join(HERE, "gd_oracle_state.c")
+MOVE_SOURCE = os.path.join(HERE, "gd_oracle_move.c")
 LIBRARY = os.path.join(HERE, "_gd_oracle.so")
 
 STAGE_WALLS, STAGE_SPRITES, STAGE_WEAPON, STAGE_HUD = 1, 2, 4, 8
@@ -27,11 +28,11 @@ _lib = None
 def build(force: bool = False) -> str:
     headers = [os.path.join(HERE, "..", "include", h) for h in ("gradoom_b200_layout.h", "gradoom_b200.h")]
     stale = (not os.path.exists(LIBRARY)) or os.path.getmtime(LIBRARY) < max(
-        os.path.getmtime(f) for f in (SOURCE, STATE_SOURCE, *headers))
+        os.path.getmtime(f) for f in (SOURCE, STATE_SOURCE, MOVE_SOURCE, *headers))
     if force or stale:
         subprocess.check_call(
             ["gcc", "-O2", "-ffp-contract=off", "-fno-fast-math", "-fPIC", "-shared",
-             "-o", LIBRARY, SOURCE, STATE_SOURCE, "-lm"])
+             "-o", LIBRARY, SOURCE, STATE_SOURCE, MOVE_SOURCE, "-lm"])
     return LIBRARY
 
 
@@ -45,6 +46,7 @@ def lib():
         _lib.gd_oracle_rgb.restype = ctypes.c_int
         _lib.gd_oracle_stack.restype = ctypes.c_int
         _lib.gd_oracle_pack_state.restype = ctypes.c_int
+        _lib.gd_oracle_player_tics.restype = ctypes.c_int
     return _lib
 
 
@@ -149,3 +151,26 @@ def pack_state(blob, src, max_things, *, render_screen_flashes=None):
     if k < 0:
         raise RuntimeError(f"oracle rejected the state or the blob (code {k})")
     return lanes, things, int(k)
+
+
+def player_tics(blob, players, buttons, tics, episode_timeout, actors=None):
+    """Advance ``players (N,24) i32`` in place by ``tics`` game tics under ``buttons (N,) u32``
+    (the checker of the CUDA library's ``gd_player_tics``).  ``actors``: an object with the
+    reference engine's monster tensors on the CPU, or None."""
+
+    from gradoom_b200 import state as gdstate
+
+    blob = np.ascontiguousarray(blob, dtype=np.uint8)
+    assert players.dtype == np.int32 and players.flags.c_contiguous and players.shape[1] == gdstate.PLAYER_WORDS
+    buttons = np.ascontiguousarray(buttons, dtype=np.uint32)
+    solid = None
+    if actors is not None:
+        solid = gdstate.SolidActors(actors)
+        if solid.device.type != "cpu":
+            raise TypeError("the oracle reads CPU tensors")
+    rc = lib().gd_oracle_player_tics(_ptr(blob), _ptr(players), _ptr(buttons),
+                                     None if solid is None else ctypes.byref(solid.struct),
+                                     ctypes.c_int(players.shape[0]), ctypes.c_int(tics), ctypes.c_int(episode_timeout))
+    if rc != 0:
+        raise RuntimeError(f"oracle rejected the blob (code {rc})")
+    return players

@@ -3,7 +3,7 @@
 Run once on a machine that has the upstream sources:
 
     GRADOOM_REFERENCE_SRC=<upstream checkout>/src/gradoom python tests/golden/make_golden.py \
-        [c1 c2 c3 c4 c1m stack flashes pitch fallback c2d c4d c1k state]
+        [c1 c2 c3 c4 c1m stack flashes pitch fallback c2d c4d c1k state move_c1 move_c2]
 
 For each seeded synthetic scene it resets the upstream engine, injects K
 monsters per lane, replays a seeded uniform action stream and, at a few
@@ -337,6 +337,57 @@ def generate_state(eng, scn, act):
     print("state fixture done; records per lane:", used, flush=True)
 
 
+def generate_move(eng, scn, act, config):
+    """Per-step player kinematics of the upstream engine (engine.py:4344-4671, 3207-3498):
+    4 lanes, 300 agent steps of the uniform action stream with frame skip 2, monster spawning
+    switched off so that nothing but the map and the voodoo doll acts on the player.  Stored:
+    the player record after the reset and after every step, and the button masks."""
+
+    n, steps = 4, 300
+    sc = gdscene.make_grid_scene(gdscene.GRID_CONFIGS[config])
+    e, g = make_engine(eng, scn, sc, n, 0, seed=31)
+    del e.render_frame
+    e.next_spawn_check.fill_(2_000_000_000)
+    # two lanes start beside the outer walls, looking at them at a slant, so that the run
+    # contains wall contacts, slides along both axes and corner stalls
+    spec = sc.meta["spec"]
+    size_x, size_y = spec.cols * spec.room, spec.rows * spec.room
+    for lane, (x, y, degrees) in ((2, (40.0, float(round(size_y * 0.4)), 205.0)), (3, (size_x - 60.0, 36.0, 300.0))):
+        sector = int(e._sector_at(torch.tensor([x]), torch.tensor([y]))[0])
+        floor, ceiling = float(e.map.sector_heights[sector, 0]), float(e.map.sector_heights[sector, 1])
+        bam = int(round(degrees / 360.0 * (1 << 32))) & 0xFFFFFFFF
+        e._x_fixed[lane], e._y_fixed[lane] = int(x * 65536), int(y * 65536)
+        e.x[lane], e.y[lane] = x, y
+        e._angle_bam[lane] = bam
+        e.angle[lane] = torch.tensor(bam, dtype=torch.int64).to(torch.float32) * gdstate.BAM_TO_RADIANS
+        e.z[lane], e.view_z[lane] = floor, floor + 41.0
+        e.player_floor_z[lane] = e.previous_player_floor_z[lane] = floor
+        e.player_ceiling_z[lane] = ceiling
+    am = action_matrix(act)
+    weights = (1 << torch.arange(am.shape[1], dtype=torch.int64))
+    ag = torch.Generator().manual_seed(ACTION_SEED + 11)
+    out = {"config": np.asarray(config), "frame_skip": np.asarray(e.frame_skip),
+           "episode_timeout": np.asarray(int(e.episode_timeout)),
+           "players_reset": gdstate.player_records(e).numpy()}
+    players, masks = [], []
+    for step in range(steps):
+        a = torch.randint(0, 17, (n,), generator=ag)
+        # long runs of one action exercise the turn ramp and wall slides better than white noise
+        if step % 40 >= 20:
+            a = torch.full((n,), int(a[0]))
+        buttons = am[a]
+        _f, _r, term, trunc = e.step(buttons)
+        assert not bool((term | trunc).any()), "the kinematics fixture expects no episode end"
+        assert not bool(e.enemy_alive.any())
+        assert torch.equal(e.x, e._x_fixed.to(torch.float32) / 65536) and torch.equal(e.y, e._y_fixed.to(torch.float32) / 65536)
+        players.append(gdstate.player_records(e).numpy())
+        masks.append((buttons.to(torch.int64) * weights).sum(dim=1).numpy().astype(np.uint32))
+    out["players"] = np.stack(players)
+    out["buttons"] = np.stack(masks)
+    np.savez_compressed(os.path.join(OUT, f"golden_move_{config}.npz"), **out)
+    print("move fixture done:", config, flush=True)
+
+
 def generate_pitch(eng, scn, act):
     """c1 with the view pitched up and down (engine.py:9622-9631 and every use of the
     pitched view centre): inputs, indexed frames and observations."""
@@ -407,6 +458,8 @@ def main(argv):
             generate_flashes(eng, scn, act)
         elif name == "pitch":
             generate_pitch(eng, scn, act)
+        elif name in ("move_c1", "move_c2"):
+            generate_move(eng, scn, act, name[len("move_"):])
         elif name == "state":
             generate_state(eng, scn, act)
         elif name == "fallback":

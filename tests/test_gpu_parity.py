@@ -254,6 +254,63 @@ def test_state_packer_reports_more_records_than_the_stride(pkg, scenes):
         r.check_status()
 
 
+@pytest.mark.parametrize("config", ["c1", "c2"])
+def test_kinematics_kernel_follows_the_upstream_trajectories(config, pkg, scenes):
+    """gd_player_tics against the per-step player records of the upstream engine (300 steps x
+    4 lanes, frame skip 2): bit-equal after every step, and the lane records carry the pose."""
+
+    from gradoom_b200 import state as gdstate
+
+    data = load_golden(f"move_{config}")
+    _sc, blob = scenes(config)
+    r = _renderer(blob, 4)
+    players = _dev(data["players_reset"])
+    lanes = torch.zeros((players.shape[0], 32), dtype=torch.int32, device=DEV)
+    tics, timeout = int(data["frame_skip"]), int(data["episode_timeout"])
+    buttons = _dev(data["buttons"].astype(np.int64)).to(torch.int32)
+    for step in range(data["players"].shape[0]):
+        r.player_tics(players, buttons[step].contiguous(), tics, timeout, lanes=lanes)
+        if step % 25 == 24 or step < 8:
+            assert np.array_equal(players.cpu().numpy(), data["players"][step]), f"step {step}"
+    final = data["players"][-1]
+    assert np.array_equal(players.cpu().numpy(), final)
+    got = lanes.cpu().numpy()
+    assert np.array_equal(got[:, gdstate.L_X_FIXED], final[:, gdstate.P_X_FIXED])
+    assert np.array_equal(got[:, gdstate.L_ANGLE_BAM], final[:, gdstate.P_ANGLE_BAM])
+    assert np.array_equal(got[:, gdstate.L_VIEW_Z], final[:, gdstate.P_VIEW_Z])
+    assert np.array_equal(got[:, gdstate.L_X].view(np.float32), (final[:, gdstate.P_X_FIXED] / 65536.0).astype(np.float32))
+
+
+def test_kinematics_kernel_matches_the_oracle_on_a_seeded_batch(pkg, oracle, scenes):
+    """2048 lanes of c2 walking for 30 steps under random buttons with solid monsters
+    around: the kernel's player records equal the CPU restatement's."""
+
+    from conftest import fake_engine
+    from gradoom_b200 import state as gdstate, stepper
+
+    sc, blob = scenes("c2")
+    n = 2048
+    r = _renderer(blob, 12)
+    producer = stepper.LaneStepper(sc, n, device=DEV, k_things=12, max_things=12, seed=3)
+    producer.bind_renderer(r)
+    producer.reset(torch.ones(n, dtype=torch.bool, device=DEV), torch.arange(n, device=DEV) + 1)
+    players = producer.players.clone()
+    want = players.cpu().numpy().copy()
+    monsters = fake_engine(n, seed=77, span=1900.0)
+    monsters.enemy_z = torch.zeros_like(monsters.enemy_z) + 8.0
+    dev_monsters = fake_engine(n, seed=77, span=1900.0, device=DEV)
+    dev_monsters.enemy_z = torch.zeros_like(dev_monsters.enemy_z) + 8.0
+    solid_dev = gdstate.SolidActors(dev_monsters)
+    rng = np.random.default_rng(5)
+    for step in range(30):
+        masks = rng.integers(0, 1 << 9, size=n).astype(np.uint32) & np.uint32(0b111111110)
+        r.player_tics(players, _dev(masks.astype(np.int64)).to(torch.int32), 2, 4200, actors=solid_dev)
+        oracle.player_tics(blob, want, masks, 2, 4200, actors=monsters)
+    assert np.array_equal(players.cpu().numpy(), want)
+    moved = (want[:, gdstate.P_X_FIXED] != producer.players.cpu().numpy()[:, gdstate.P_X_FIXED]).mean()
+    assert moved > 0.9
+
+
 def test_full_size_batch_properties(pkg, oracle, scenes):
     """4096 lanes on the 64-sector map: size-independent properties plus an
     oracle check of a lane sample."""
@@ -372,21 +429,18 @@ def test_flat_fallback_after_free_movement(pkg, oracle, scenes):
     """Players that have walked freely stand on or next to portal lines now and
     then; their frames need the fallback's vertical and horizontal repairs."""
 
-    import torch
-
-    from gradoom_b200 import stepper
-    from gradoom_b200.env import action_matrix
+    from gradoom_b200 import state as gdstate, stepper
 
     sc, blob = scenes("c2")
     n = 512
-    producer = stepper.LaneStepper(sc, n, device="cpu", k_things=12, max_things=12, seed=1000)
-    producer.reset(torch.ones(n, dtype=torch.bool), torch.arange(n) + 1)
-    table = action_matrix("cpu")
-    g = torch.Generator().manual_seed(20260813)
-    for _ in range(8):
-        producer.step(table[torch.randint(0, table.shape[0], (n,), generator=g)])
-    lanes_t, things_t = producer.render_inputs()
-    lanes, things = lanes_t.numpy().copy(), things_t.numpy().copy()
+    lanes, things = stepper.random_lanes(sc, n, 12, seed=1000)
+    # every eighth player is moved onto a portal line of the grid or a hair beside it
+    rng = np.random.default_rng(7)
+    moved = np.arange(0, n, 8)
+    offsets = rng.choice(np.asarray([0.0, 1.0 / 65536, -1.0 / 65536, 0.25, -0.25, 1.0]), size=len(moved))
+    x = (rng.integers(1, 8, size=len(moved)) * 256 + offsets).astype(np.float32)
+    lanes[moved, gdstate.L_X] = x.view(np.int32)
+    lanes[moved, gdstate.L_X_FIXED] = np.round(x.astype(np.float64) * 65536).astype(np.int32)
     expected = oracle.render(blob, lanes, things)
     chosen = np.flatnonzero(expected["unowned"] > 0)
     assert len(chosen) >= 4, "the seeded batch is expected to contain such lanes"

@@ -100,6 +100,64 @@ def test_state_packer_feeds_the_upstream_frame(pkg, oracle, scenes):
     assert np.array_equal(out["indexed"], data["indexed_0"])
 
 
+@pytest.mark.parametrize("config", ["c1", "c2"])
+def test_player_kinematics_follow_the_upstream_trajectories(config, pkg, oracle, scenes):
+    """300 agent steps x 4 lanes of the upstream engine's player movement (engine.py:4344-4671,
+    3207-3498; frame skip 2): turn ramp, thrust, bob, wall slides, step-ups, view-height
+    easing, falls -- every word of the player record equal after every step."""
+
+    from gradoom_b200 import state as gdstate
+
+    data = load_golden(f"move_{config}")
+    _sc, blob = scenes(config)
+    players = data["players_reset"].copy()
+    tics, timeout = int(data["frame_skip"]), int(data["episode_timeout"])
+    for step in range(data["players"].shape[0]):
+        oracle.player_tics(blob, players, data["buttons"][step], tics, timeout)
+        assert np.array_equal(players, data["players"][step]), f"step {step}"
+    recorded = data["players"]
+    floors = recorded[:, :, gdstate.P_FLOOR_Z].view(np.float32)
+    assert (np.diff(floors, axis=0) != 0).sum() >= 5                       # floors change under the player
+    assert (recorded[:, :, gdstate.P_VIEW_HEIGHT].view(np.float32) < 41.0).any()   # step-up easing happened
+    x = recorded[:, :, gdstate.P_X_FIXED] / 65536.0
+    assert (x < 16.6).sum() >= 10                                           # a lane slid along the outer wall
+
+
+def test_solid_monsters_block_the_player(pkg, oracle, scenes):
+    """A living monster in the way stops the move (engine.py:2933-2975, 3244-3262); the same
+    run without it walks through the spot."""
+
+    import types
+
+    import torch
+
+    from gradoom_b200 import state as gdstate
+
+    sc, blob = scenes("c1")
+    floor = float(sc.sector_heights[0, 0])
+
+    def run(with_monster):
+        p = np.zeros((1, gdstate.PLAYER_WORDS), dtype=np.int32)
+        p[0, gdstate.P_X_FIXED], p[0, gdstate.P_Y_FIXED] = 60 << 16, 128 << 16
+        for word, value in ((gdstate.P_Z, floor), (gdstate.P_VIEW_Z, floor + 41), (gdstate.P_VIEW_HEIGHT, 41.0),
+                            (gdstate.P_FLOOR_Z, floor), (gdstate.P_CEILING_Z, float(sc.sector_heights[0, 1])),
+                            (gdstate.P_PREV_FLOOR_Z, floor)):
+            p[0, word] = np.float32(value).view(np.int32)
+        actors = types.SimpleNamespace(
+            enemy_x=torch.tensor([[130.0]]), enemy_y=torch.tensor([[128.0]]), enemy_z=torch.tensor([[floor]]),
+            enemy_type=torch.tensor([[0]]), enemy_death_type=torch.tensor([[-1]]),
+            enemy_death_tics=torch.zeros((1, 1), dtype=torch.int32),
+            enemy_death_elapsed=torch.zeros((1, 1), dtype=torch.int32),
+            enemy_alive=torch.tensor([[with_monster]]), enemy_death_extreme=torch.tensor([[False]]))
+        forward = np.asarray([1 << 6 | 1 << 1], dtype=np.uint32)            # run forward, facing +x
+        for _ in range(40):
+            oracle.player_tics(blob, p, forward, 1, 4200, actors=actors)
+        return p[0, gdstate.P_X_FIXED] / 65536.0
+
+    assert run(False) > 160.0
+    assert run(True) < 130.0 - 36.0 + 1.0
+
+
 def _area_axis(source, output):
     w = np.zeros((output, source), dtype=np.float32)
     for o in range(output):
