@@ -461,7 +461,8 @@ def run_ours(args):
     # reset launch of the auto-reset), no host synchronisation between steps
     from gradoom_b200.env import GraDoomVecEnv
 
-    env = GraDoomVecEnv(sc, n, device=device, max_things=THINGS, producer_seed=2000 + rank)
+    env = GraDoomVecEnv(compiled_scenario=sc, num_envs=n, device=device, frame_skip=2, obs_crop=(0, 32, 0, 0),
+                        obs_crop_mode="mask", max_things=THINGS, producer_seed=2000)
     env.reset_device(everyone, lane_ids + 1)
     api_steps = max(args.steps, 3)
     for k in range(3):
@@ -557,7 +558,8 @@ def run_rollout(args):
     torch.cuda.set_device(device)
     lanes, horizon, things = args.lanes or 256, 16, 12
     sc = gdscene.make_grid_scene(gdscene.GRID_CONFIGS["c2"])
-    env = GraDoomVecEnv(sc, lanes, device=device, max_things=things, producer_seed=5)
+    env = GraDoomVecEnv(compiled_scenario=sc, num_envs=lanes, device=device, frame_skip=2, obs_crop=(0, 32, 0, 0),
+                        obs_crop_mode="mask", max_things=things, producer_seed=5)
     torch.manual_seed(5)
     trunk = nn.Sequential(nn.Conv2d(4, 32, 8, 4), nn.ReLU(), nn.Conv2d(32, 64, 4, 2), nn.ReLU(),
                           nn.Conv2d(64, 64, 3, 1), nn.ReLU(), nn.Flatten(), nn.Linear(64 * 7 * 7, 512), nn.ReLU()).to(device)

@@ -45,6 +45,27 @@ DEATHMATCH_ACTIONS = (
     ("SELECT_NEXT_WEAPON",), ("SELECT_PREV_WEAPON",),
 )
 _ACTION_DTYPES = (torch.int8, torch.int16, torch.int32, torch.int64, torch.uint8)
+# columns of the signal buffer (src/gradoom/engine.py:509-539)
+DEVICE_SIGNAL_NAMES = (
+    "killcount", "health", "armor", "selected_weapon", "selected_weapon_ammo", "weapon1", "weapon2", "weapon3",
+    "weapon4", "weapon5", "weapon6", "ammo1", "ammo2", "ammo3", "ammo4", "ammo5", "ammo6", "episode_time",
+    "episode_return", "player_dead", "pending_reset", "deathcount", "hitcount", "damagecount", "hits_taken",
+    "damage_taken", "player_killcount",
+)
+
+
+def _normalize_seed(seed, num_envs: int):
+    """One seed per lane from None, an int (lane i gets seed + i) or a sequence
+    (src/gradoom/env.py:101-113)."""
+
+    if seed is None:
+        return [None] * num_envs
+    if isinstance(seed, (list, tuple, np.ndarray)):
+        result = [None if value is None else int(value) for value in seed]
+        if len(result) != num_envs:
+            raise ValueError("seed sequence length must match num_envs")
+        return result
+    return [int(seed) + lane for lane in range(num_envs)]
 
 
 @dataclass(frozen=True)
@@ -172,20 +193,120 @@ class GraDoomVecEnv:
         "gradoom_device_api_version": 1,
     }
 
-    def __init__(self, sc: gdscene.Scene, num_envs: int, *, device, producer=None, max_things: int = 16,
-                 frame_skip: int = 2, render_mode: str | None = None, obs_crop=(0, 32, 0, 0),
-                 obs_crop_mode: str = "mask", obs_layout: str = "chw", episode_timeout: int = 4200,
-                 producer_seed: int = 0, stack_policy: str = "roll"):
-        if num_envs <= 0:
-            raise ValueError("num_envs must be positive")
+    def __init__(self, game=None, state=None, scenario=None, info=None, use_restricted_actions="default",
+                 record: bool = False, players: int = 1, inttype="stable", obs_type="image",
+                 render_mode: str | None = None, *, num_envs: int = 1, num_threads: int | None = None,
+                 rom_path: str | None = None, transport: str = "default", obs_copy: str = "safe_view",
+                 obs_resize=(84, 84), obs_crop=None, obs_crop_mode: str = "remove", obs_crop_fill: int = 0,
+                 obs_grayscale: bool = True, obs_resize_algorithm: str = "area", obs_layout: str = "chw",
+                 frame_skip: int = 4, frame_stack: int = 4, maxpool_last_two: bool = False,
+                 noop_reset_max: int = 0, use_fire_reset: bool = False, sticky_action_prob: float = 0.0,
+                 reward_clip=False, info_filter="all", info_frame_stack_keys=None, state_catalog=None,
+                 device=None, doom_map=None, doom_skill=None, wall_contact_damage_scale: float = 1.0,
+                 observation_renderer: str = "reference", game_args=None, game_variables=None,
+                 enemy_variants=None, surface_variants=None, treat_episode_timeout_as_truncation: bool = True,
+                 vizdoom_config=None, compiled_scenario=None, require_pinned_scenario: bool = True,
+                 compile_engine: bool = False,
+                 # beyond the reference's keyword set: the state producer and the renderer's options
+                 producer=None, max_things: int = 16, producer_seed: int = 0, stack_policy: str = "roll"):
+        """Keyword-compatible with the reference's constructor (src/gradoom/env.py:228-350): the
+        same names, defaults and refusals for what the deathmatch profile does not support.
+        Differences, all refusals or additions: the scene must be handed over compiled
+        (``compiled_scenario=``: a ``scene.Scene`` of this package, or the reference's
+        ``CompiledScenario``; WAD compilation is not part of this library);
+        ``observation_renderer`` must be ``"reference"`` -- the native pipeline is the one
+        renderer behind this class, and it is also the default here; ``info_frame_stack_keys``
+        is not supported."""
+
+        if transport == "default":
+            transport = "torch"
+        if info not in (None, "data"):
+            raise ValueError("info must be None or 'data'")
+        if record:
+            raise ValueError("record=True is not supported on the device path")
+        if players != 1:
+            raise ValueError("the deathmatch-p1-v1 profile supports players=1")
+        if str(obs_type).split(".")[-1].casefold() != "image":
+            raise ValueError("GraDoomVecEnv supports image observations only")
         if render_mode not in (None, "rgb_array"):
             raise ValueError("render_mode must be None or 'rgb_array'")
+        if state is not None and state_catalog is not None:
+            raise ValueError("state and state_catalog are mutually exclusive")
+        catalog = ("default",) if state_catalog is None else tuple(state_catalog)
+        if state not in (None, "default") or catalog != ("default",):
+            raise ValueError("the first device profile supports only the default initial state")
+        if any(value is not None for value in (doom_map, game_args, enemy_variants, surface_variants)):
+            raise ValueError("custom maps, game args, and variants are not yet supported")
+        if doom_skill not in (None, 1, 3):
+            raise ValueError("deathmatch-p1-v1 supports Doom skill 1 or 3")
+        if observation_renderer not in ("approximate", "native-fused", "reference"):
+            raise ValueError("observation_renderer must be 'approximate', 'native-fused', or 'reference'")
+        if observation_renderer != "reference":
+            raise ValueError("this library draws observation_renderer='reference' (the native pipeline) only")
+        if use_fire_reset or noop_reset_max or sticky_action_prob:
+            raise ValueError("fire reset, no-op reset, and sticky actions are not in deathmatch-p1-v1")
+        if maxpool_last_two:
+            raise ValueError("deathmatch-p1-v1 does not max-pool consecutive frames")
+        if tuple(obs_resize or ()) != (84, 84) or not obs_grayscale or frame_stack != 4:
+            raise ValueError("deathmatch-p1-v1 requires 84x84 grayscale frame-stack 4")
+        if obs_crop is not None:
+            obs_crop = tuple(obs_crop)
+        if obs_crop not in (None, (0, 32, 0, 0)):
+            raise ValueError("deathmatch-p1-v1 supports no crop or the pinned bottom-32 mask")
+        if obs_crop is not None and (obs_crop_mode != "mask" or obs_crop_fill != 0):
+            raise ValueError("the pinned deathmatch crop is a zero-filled mask")
+        if obs_crop is None and obs_crop_mode not in ("remove", "mask"):
+            raise ValueError("obs_crop_mode must be 'remove' or 'mask'")
+        if obs_crop_fill != 0:
+            raise ValueError("deathmatch-p1-v1 requires obs_crop_fill=0")
         if obs_layout not in ("chw", "hwc"):
             raise ValueError("obs_layout must be 'chw' or 'hwc'")
+        if obs_resize_algorithm != "area":
+            raise ValueError("deathmatch-p1-v1 supports obs_resize_algorithm='area' only")
+        if transport != "torch":
+            raise ValueError("transport must be 'torch'; NumPy transition transport is unsupported")
+        if obs_copy not in ("copy", "safe_view", "unsafe_view"):
+            raise ValueError("obs_copy must be copy, safe_view, or unsafe_view")
+        if str(getattr(inttype, "name", inttype)).split(".")[-1].casefold() != "stable":
+            raise ValueError("inttype must select the Stable integration")
+        if num_threads is not None:
+            raise ValueError("num_threads is unsupported and must be None on the device path")
+        if isinstance(num_envs, bool) or not isinstance(num_envs, (int, np.integer)) or num_envs <= 0:
+            raise ValueError("num_envs must be a positive integer")
+        if isinstance(frame_skip, bool) or not isinstance(frame_skip, (int, np.integer)) or frame_skip <= 0:
+            raise ValueError("frame_skip must be a positive integer")
+        if info_frame_stack_keys:
+            raise ValueError("info_frame_stack_keys are not supported by this library")
+        if not treat_episode_timeout_as_truncation:
+            raise ValueError("deathmatch-p1-v1 treats its native timeout as truncation")
         if stack_policy not in ("roll", "ring"):
             raise ValueError("stack_policy must be 'roll' or 'ring'")
-        if obs_crop not in (None, (0, 32, 0, 0)) or (obs_crop is not None and obs_crop_mode != "mask"):
-            raise ValueError("only obs_crop=None or obs_crop=(0, 32, 0, 0) with obs_crop_mode='mask' is supported")
+        options = dict(vizdoom_config or {})
+        unknown = set(options) - {"episode_timeout", "render_screen_flashes"}
+        if unknown:
+            raise ValueError(f"unsupported vizdoom_config keys: {sorted(unknown)}")
+        episode_timeout = options.get("episode_timeout", 4200)
+        if isinstance(episode_timeout, bool) or not isinstance(episode_timeout, (int, np.integer)) or episode_timeout <= 0:
+            raise ValueError("episode_timeout must be a positive integer")
+        self.render_screen_flashes = options.get("render_screen_flashes", False)
+        if not isinstance(self.render_screen_flashes, bool):
+            raise ValueError("render_screen_flashes must be a boolean")
+        if compiled_scenario is None:
+            raise FileNotFoundError("pass compiled_scenario=...: this library does not compile WAD files")
+        sc = compiled_scenario if isinstance(compiled_scenario, gdscene.Scene) \
+            else gdscene.from_compiled_scenario(compiled_scenario)
+        if device is None:
+            device = "cuda"
+        self.game = str(game or "VizdoomDeathmatch-v1")
+        self.obs_copy = obs_copy
+        self.observation_renderer = observation_renderer
+        self.transport = transport
+        self.compiled_scenario = compiled_scenario
+        self._safe_obs_index = 0
+        self._pending_actions = None
+        self._seed_values = [None] * int(num_envs)
+        self._reset_rngs = [np.random.default_rng(lane) for lane in range(int(num_envs))]
+        self._reward_clip = self._normalize_reward_clip(reward_clip)
         self.device = torch.device(device)
         if self.device.type == "cuda" and self.device.index is None:
             self.device = torch.device("cuda", torch.cuda.current_device())
@@ -217,6 +338,9 @@ class GraDoomVecEnv:
         self._frames = torch.zeros((self.num_envs, slots, 84, 84), dtype=torch.uint8, device=self.device)
         self._initialized = torch.zeros(self.num_envs, dtype=torch.bool, device=self.device)
         self._action_matrix = action_matrix(self.device)
+        shape = (4, 84, 84) if obs_layout == "chw" else (84, 84, 4)
+        self._safe_obs_buffers = tuple(torch.empty((self.num_envs, *shape), dtype=torch.uint8, device=self.device)
+                                       for _ in range(2)) if obs_copy == "safe_view" else ()
         self._info_history = torch.zeros((self.num_envs, 0, 4), dtype=torch.float32, device=self.device)
         self._state_indices = torch.zeros(self.num_envs, dtype=torch.int32, device=self.device)
         self.action_table = DEATHMATCH_ACTIONS
@@ -263,6 +387,81 @@ class GraDoomVecEnv:
         return DeviceTransition(self._device_observations(), rewards, terminated, truncated,
                                 self._producer.signal_buffer, self._info_history)
 
+    @staticmethod
+    def _normalize_reward_clip(value):
+        if value is False:
+            return None
+        if value is True:
+            return (-1.0, 1.0)
+        try:
+            low, high = (float(item) for item in value)
+        except (TypeError, ValueError) as exc:
+            raise ValueError("reward_clip must be a bool or a (low, high) pair") from exc
+        if not np.isfinite(low) or not np.isfinite(high) or low > high:
+            raise ValueError("reward_clip bounds must be finite with low <= high")
+        return low, high
+
+    # -- gym-level API (src/gradoom/env.py:678-688, 746-848) ------------------
+    def _observations(self, values: torch.Tensor) -> torch.Tensor:
+        """Ownership of the observations a gym-level call returns: ``copy`` clones, ``safe_view``
+        alternates two buffers (a returned tensor stays intact for one more call), ``unsafe_view``
+        hands out the live stack."""
+
+        if self.obs_copy == "copy":
+            return values.clone()
+        if self.obs_copy == "safe_view":
+            buffer = self._safe_obs_buffers[self._safe_obs_index]
+            self._safe_obs_index = (self._safe_obs_index + 1) % len(self._safe_obs_buffers)
+            buffer.copy_(values)
+            return buffer
+        return values
+
+    def _infos(self, availability=None) -> dict:
+        if availability is None:
+            availability = torch.ones(self.num_envs, dtype=torch.bool, device=self.device)
+        signals = self._producer.signal_buffer
+        result = {}
+        for index, name in enumerate(DEVICE_SIGNAL_NAMES):
+            result[name] = signals[:, index].to(torch.float64)
+            result[f"_{name}"] = availability.clone()
+        return result
+
+    def seed(self, seed=None):
+        self._seed_values = _normalize_seed(seed, self.num_envs)
+        return list(self._seed_values)
+
+    def reset(self, *, seed=None, options=None):
+        self._require_open("reset")
+        reset_options = dict(options or {})
+        raw_mask = reset_options.pop("reset_mask", None)
+        if raw_mask is None:
+            mask = torch.ones(self.num_envs, dtype=torch.bool, device=self.device)
+        else:
+            mask = require_device_tensor(raw_mask, "options['reset_mask']", device=self.device,
+                                         shape=(self.num_envs,), dtypes=(torch.bool,))
+        if not bool(torch.any(mask)):
+            raise ValueError("options['reset_mask'] must select at least one lane")
+        state_indices = reset_options.pop("state_indices", None)
+        if state_indices is not None:
+            selected = require_device_tensor(state_indices, "options['state_indices']", device=self.device,
+                                             shape=(self.num_envs,), dtypes=(torch.int32,))
+            if bool(torch.any(selected[mask] != 0)):
+                raise ValueError("deathmatch-p1-v1 has only state index 0")
+        if reset_options:
+            raise ValueError(f"unsupported reset options: {sorted(reset_options)}")
+        seed_values = _normalize_seed(seed, self.num_envs) if seed is not None else self._seed_values
+        game_seeds = [0] * self.num_envs
+        for lane in torch.nonzero(mask, as_tuple=False).flatten().to("cpu").tolist():
+            if seed_values[lane] is not None:
+                self._reset_rngs[lane] = np.random.default_rng(seed_values[lane])
+            game_seeds[lane] = int(self._reset_rngs[lane].integers(0, np.iinfo(np.uint32).max + 1, dtype=np.uint32))
+        self._seed_values = [None] * self.num_envs
+        observations, _signals = self.reset_device(mask, torch.tensor(game_seeds, dtype=torch.int64, device=self.device))
+        infos = self._infos(mask)
+        infos["state_index"] = self._state_indices.clone()
+        infos["_state_index"] = mask.clone()
+        return self._observations(observations), infos
+
     def step(self, actions: torch.Tensor):
         """Validated step (host synchronising, like the reference's gym ``step``)."""
 
@@ -278,7 +477,19 @@ class GraDoomVecEnv:
         if bool(torch.any((indices < 0) | (indices >= len(self.action_table)))):
             raise ValueError("actions fall outside the declared action space")
         t = self.step_device(indices)
-        return t.observations, t.rewards, t.terminated, t.truncated, {}
+        rewards = t.rewards if self._reward_clip is None else t.rewards.clamp(*self._reward_clip)
+        return self._observations(t.observations), rewards, t.terminated, t.truncated, self._infos()
+
+    def step_async(self, actions: torch.Tensor) -> None:
+        if self._pending_actions is not None:
+            raise RuntimeError("an asynchronous step is already pending")
+        self._pending_actions = actions
+
+    def step_wait(self):
+        if self._pending_actions is None:
+            raise RuntimeError("no asynchronous step is pending")
+        actions, self._pending_actions = self._pending_actions, None
+        return self.step(actions)
 
     def step_and_reset_device(self, actions: torch.Tensor, reset_seeds: torch.Tensor) -> DeviceAutoResetTransition:
         t = self.step_device(actions)

@@ -435,6 +435,85 @@ def make_grid_scene(spec: GridSpec) -> Scene:
     )
 
 
+def from_compiled_scenario(cs) -> Scene:
+    """A Scene from the reference's ``CompiledScenario`` (src/gradoom/scenario.py:302-410), field
+    by field; the defaults for absent optional fields are the ones the reference's device scene
+    applies (src/gradoom/engine.py:869-1100).  Scenarios without the native renderer's assets
+    (palette-indexed textures, raw sprites, status-bar patches) are refused."""
+
+    def need(name):
+        value = getattr(cs, name, None)
+        if value is None:
+            raise ValueError(f"the compiled scenario lacks {name!r}, which the native render path needs")
+        return np.asarray(value)
+
+    def maybe(name, default):
+        value = getattr(cs, name, None)
+        return np.asarray(default if value is None else value)
+
+    if getattr(cs, "wall_projection_fragments_fixed", None) is not None:
+        raise ValueError("scenarios with node-builder wall fragments are not supported by this render path")
+    spr_atlas = need("raw_sprite_atlas")
+    last_sprite = max(len(spr_atlas) - 1, 0)
+    wpn_atlas = getattr(cs, "native_weapon_patch_atlas", None)
+    if wpn_atlas is None:
+        wpn = {"atlas": np.zeros((1, 1, 1), np.uint8), "opaque": np.zeros((1, 1, 1), bool),
+               "widths": np.zeros(1, np.int32), "heights": np.zeros(1, np.int32), "left": np.zeros(1, np.int32),
+               "top": np.zeros(1, np.int32)}
+    else:
+        wpn = {"atlas": np.asarray(wpn_atlas), "opaque": need("native_weapon_patch_opaque"),
+               "widths": need("native_weapon_patch_widths"), "heights": need("native_weapon_patch_heights"),
+               "left": need("native_weapon_patch_left_offsets"), "top": need("native_weapon_patch_top_offsets")}
+    meta = {}
+    item_types = np.asarray(getattr(cs, "item_types", np.empty(0, np.int32)))
+    if len(item_types):
+        meta["items"] = {"spawns": np.asarray(cs.item_spawns, dtype=np.float32), "types": item_types.astype(np.int32),
+                         "anim_ids": maybe("raw_item_animation_sprite_ids", np.zeros(8, np.int32)).astype(np.int32)}
+    return Scene(
+        walls=need("wall_segments").astype(np.float32), wall_sectors=need("wall_sectors").astype(np.int32),
+        side_textures=need("wall_side_texture_ids").astype(np.int32),
+        side_offsets=need("wall_side_texture_offsets").astype(np.float32),
+        sector_edge_mask=need("sector_edge_mask").astype(np.bool_),
+        sector_heights=need("sector_heights").astype(np.float32), sector_lights=need("sector_lights").astype(np.int16),
+        sector_floor_tex=need("sector_floor_texture_ids").astype(np.int32),
+        sector_ceil_tex=need("sector_ceiling_texture_ids").astype(np.int32),
+        player_starts=need("player_starts").astype(np.float32),
+        tex_atlas=need("texture_index_atlas").astype(np.uint8), tex_widths=need("texture_widths").astype(np.int32),
+        tex_heights=need("texture_heights").astype(np.int32), playpal=need("playpal").astype(np.uint8),
+        colormap=maybe("colormap", np.broadcast_to(np.arange(256, dtype=np.uint8), (34, 256))).astype(np.uint8),
+        spr_atlas=spr_atlas.astype(np.uint8), spr_opaque=need("raw_sprite_opaque").astype(np.bool_),
+        spr_widths=need("raw_sprite_widths").astype(np.int32), spr_heights=need("raw_sprite_heights").astype(np.int32),
+        spr_left=need("raw_sprite_left_offsets").astype(np.int32), spr_top=need("raw_sprite_top_offsets").astype(np.int32),
+        enemy_walk_ids=need("enemy_walk_sprite_ids").astype(np.int32),
+        enemy_attack_ids=need("enemy_attack_sprite_ids").astype(np.int32),
+        enemy_pain_ids=need("enemy_pain_sprite_ids").astype(np.int32),
+        enemy_death_ids=need("enemy_death_sprite_ids").astype(np.int32),
+        enemy_death_counts=need("enemy_death_frame_counts").astype(np.int32),
+        enemy_death_durations=need("enemy_death_frame_durations").astype(np.int32),
+        enemy_xdeath_ids=need("enemy_xdeath_sprite_ids").astype(np.int32),
+        enemy_xdeath_counts=need("enemy_xdeath_frame_counts").astype(np.int32),
+        enemy_xdeath_durations=need("enemy_xdeath_frame_durations").astype(np.int32),
+        proj_flight_ids=need("raw_projectile_flight_sprite_ids").astype(np.int32),
+        proj_explosion_ids=need("raw_projectile_explosion_sprite_ids").astype(np.int32),
+        proj_explosion_counts=need("projectile_explosion_frame_counts").astype(np.int32),
+        proj_explosion_durations=need("projectile_explosion_frame_durations").astype(np.int32),
+        fog_ids=need("raw_teleport_fog_sprite_ids").astype(np.int32), puff_ids=need("raw_bullet_puff_sprite_ids").astype(np.int32),
+        static_ids=maybe("raw_static_sprite_ids", [min(i, last_sprite) for i in range(6, 26)]).astype(np.int32),
+        additive_luts=need("projectile_additive_luts").astype(np.uint8),
+        translucent_lut=need("sprite_translucent_lut").astype(np.uint8),
+        wpn_atlas=wpn["atlas"].astype(np.uint8), wpn_opaque=wpn["opaque"].astype(np.bool_),
+        wpn_widths=wpn["widths"].astype(np.int32), wpn_heights=wpn["heights"].astype(np.int32),
+        wpn_left=wpn["left"].astype(np.int32), wpn_top=wpn["top"].astype(np.int32),
+        wpn_frame_ids=need("native_weapon_frame_ids").astype(np.int32),
+        wpn_flash_ids=need("native_weapon_flash_ids").astype(np.int32),
+        wpn_flash_lights=need("native_weapon_flash_lights").astype(np.int32),
+        hud_atlas=need("hud_patch_atlas").astype(np.uint8), hud_opaque=need("hud_patch_opaque").astype(np.bool_),
+        hud_widths=need("hud_patch_widths").astype(np.int32), hud_heights=need("hud_patch_heights").astype(np.int32),
+        hud_left=need("hud_patch_left_offsets").astype(np.int32), hud_top=need("hud_patch_top_offsets").astype(np.int32),
+        meta=meta,
+    )
+
+
 # ---------------------------------------------------------------------------
 # Packing a Scene into the device blob (layout: include/gradoom_b200_layout.h)
 # ---------------------------------------------------------------------------

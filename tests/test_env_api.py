@@ -14,7 +14,11 @@ def _env(scenes, n=6, **kw):
     from gradoom_b200 import env as gdenv
 
     sc, _ = scenes("c1")
-    return gdenv.GraDoomVecEnv(sc, n, device=DEV, max_things=8, **kw)
+    timeout = kw.pop("episode_timeout", None)
+    if timeout is not None:
+        kw["vizdoom_config"] = {"episode_timeout": timeout}
+    return gdenv.GraDoomVecEnv(compiled_scenario=sc, num_envs=n, device=DEV, max_things=8, frame_skip=2,
+                               obs_crop=(0, 32, 0, 0), obs_crop_mode="mask", **kw)
 
 
 def test_reset_and_step_contracts(pkg, oracle, scenes):
@@ -125,7 +129,9 @@ def test_ring_stack_policy_shows_the_same_windows_as_the_rolled_stack(pkg, scene
 
     sc, _ = scenes("c1")
     n = 96
-    envs = [GraDoomVecEnv(sc, n, device="cuda", max_things=8, episode_timeout=10, producer_seed=3, stack_policy=p)
+    envs = [GraDoomVecEnv(compiled_scenario=sc, num_envs=n, device="cuda", max_things=8, frame_skip=2,
+                          obs_crop=(0, 32, 0, 0), obs_crop_mode="mask", vizdoom_config={"episode_timeout": 10},
+                          producer_seed=3, stack_policy=p)
             for p in ("roll", "ring")]
     everyone = torch.ones(n, dtype=torch.bool, device="cuda")
     seeds = torch.arange(n, device="cuda") + 1
@@ -141,7 +147,8 @@ def test_ring_stack_policy_shows_the_same_windows_as_the_rolled_stack(pkg, scene
         out = [e.step_and_reset_device(actions, seeds + 1000 * (step + 1)) for e in envs]
         assert torch.equal(out[0].observations, out[1].observations), step
         assert torch.equal(out[0].final_observations, out[1].final_observations), step
-    hwc = GraDoomVecEnv(sc, 4, device="cuda", max_things=8, obs_layout="hwc", stack_policy="ring")
+    hwc = GraDoomVecEnv(compiled_scenario=sc, num_envs=4, device="cuda", max_things=8, frame_skip=2,
+                        obs_crop=(0, 32, 0, 0), obs_crop_mode="mask", obs_layout="hwc", stack_policy="ring")
     assert tuple(hwc.reset_device(torch.ones(4, dtype=torch.bool, device="cuda"), seeds[:4])[0].shape) == (4, 84, 84, 4)
     for e in envs + [hwc]:
         e.check_status()
@@ -182,7 +189,8 @@ def test_engine_state_producer_packs_on_the_device(pkg, oracle, scenes):
 
     engine = Engine()
     producer = gdenv.EngineStateProducer(engine, sc, 64)
-    e = gdenv.GraDoomVecEnv(sc, n, device="cuda:0", producer=producer, max_things=64)
+    e = gdenv.GraDoomVecEnv(compiled_scenario=sc, num_envs=n, device="cuda:0", producer=producer, max_things=64,
+                            frame_skip=2, obs_crop=(0, 32, 0, 0), obs_crop_mode="mask")
     obs, _signals = e.reset_device(torch.ones(n, dtype=torch.bool, device="cuda:0"),
                                    torch.arange(n, device="cuda:0"))
     lanes, things, _k = oracle.pack_state(blob, fake_engine(n, seed=21), 64)
@@ -193,3 +201,108 @@ def test_engine_state_producer_packs_on_the_device(pkg, oracle, scenes):
     assert np.array_equal(t.observations[:, 3].cpu().numpy(), oracle.render(blob, lanes, things)["obs"])
     assert np.array_equal(t.observations[:, 2].cpu().numpy(), want)
     e.close()
+
+
+@pytest.mark.gpu
+def test_gym_level_reset_step_and_observation_ownership(pkg, scenes):
+    """reset()/step() with the three obs_copy modes (src/gradoom/env.py:678-688; upstream
+    tests/test_turbo_api_contract.py:454-465: safe_view alternates two buffers)."""
+
+    n = 4
+    actions = torch.full((n,), 2, device=DEV, dtype=torch.int64)
+    safe = _env(scenes, n=n, obs_copy="safe_view")
+    first, infos = safe.reset(seed=7)
+    assert first.shape == (n, 4, 84, 84) and set(("killcount", "_killcount", "state_index")) <= set(infos)
+    second = safe.step(actions)[0]
+    after_one_step = second.clone()
+    third = safe.step(actions)[0]
+    assert first.data_ptr() != second.data_ptr() and third.data_ptr() == first.data_ptr()
+    assert second.data_ptr() != safe._frames.data_ptr()
+    kept = third.clone()
+    safe.step(actions)                                   # lands in `second`'s buffer; `third` is still intact
+    assert torch.equal(third, kept)
+    owned = _env(scenes, n=n, obs_copy="copy")
+    a, _ = owned.reset(seed=7)
+    b = owned.step(actions)[0]
+    assert a.data_ptr() != b.data_ptr() and b.data_ptr() != owned._frames.data_ptr()
+    live = _env(scenes, n=n, obs_copy="unsafe_view")
+    c, _ = live.reset(seed=7)
+    d, rewards, terminated, truncated, info = live.step(actions)
+    assert c.data_ptr() == d.data_ptr() == live._frames.data_ptr()
+    assert rewards.shape == (n,) and terminated.dtype == torch.bool and "episode_time" in info
+    # the same seeds give the same episode in every mode
+    assert torch.equal(b, d) and torch.equal(after_one_step, b)
+    # masked reset through options, seeds per lane, the asynchronous pair
+    mask = torch.tensor([True, False, False, True], device=DEV)
+    obs, infos = live.reset(seed=[3, None, None, 9], options={"reset_mask": mask})
+    assert torch.equal(infos["_state_index"], mask) and torch.equal(obs[0, 0], obs[0, 3])
+    live.step_async(actions)
+    with pytest.raises(RuntimeError):
+        live.step_async(actions)
+    assert live.step_wait()[0].shape == (n, 4, 84, 84)
+    with pytest.raises(ValueError):
+        live.reset(options={"reset_mask": torch.zeros(n, dtype=torch.bool, device=DEV)})
+    with pytest.raises(ValueError):
+        live.reset(options={"bogus": 1})
+    for e in (safe, owned, live):
+        e.close()
+
+
+@pytest.mark.gpu
+def test_constructor_follows_the_reference_keyword_set(pkg, scenes):
+    """Names and refusals of src/gradoom/env.py:228-350."""
+
+    from gradoom_b200 import env as gdenv
+
+    sc, _ = scenes("c1")
+    base = dict(compiled_scenario=sc, num_envs=2, device=DEV)
+    for bad in (dict(players=2), dict(record=True), dict(render_mode="human"), dict(num_threads=4),
+                dict(obs_resize=(64, 64)), dict(frame_stack=2), dict(obs_crop=(1, 2, 3, 4)),
+                dict(obs_crop=(0, 32, 0, 0), obs_crop_mode="remove"), dict(obs_layout="nhwc"),
+                dict(transport="numpy"), dict(obs_copy="view"), dict(observation_renderer="approximate"),
+                dict(observation_renderer="bogus"), dict(doom_skill=2), dict(sticky_action_prob=0.25),
+                dict(maxpool_last_two=True), dict(vizdoom_config={"fps": 35}), dict(num_envs=0),
+                dict(state="other"), dict(doom_map="MAP01"), dict(stack_policy="stack")):
+        with pytest.raises(ValueError):
+            gdenv.GraDoomVecEnv(**{**base, **bad})
+    with pytest.raises(FileNotFoundError):
+        gdenv.GraDoomVecEnv(num_envs=2, device=DEV)
+    e = gdenv.GraDoomVecEnv("VizdoomDeathmatch-v1", **base)      # the reference's defaults: HUD visible, frame skip 4
+    assert e.frame_skip == 4 and e.mask_hud is False and e.obs_copy == "safe_view" and e.observation_renderer == "reference"
+    obs, _ = e.reset(seed=1)
+    assert obs[:, :, 74:].any()                                   # status-bar rows are drawn when nothing is masked
+    e.close()
+
+
+@pytest.mark.gpu
+def test_operator_seam_traces_under_torch_compile(pkg, oracle, scenes):
+    """The entry points as torch.library operators (the reference's second plugin
+    mechanism, src/gradoom/_triton_kernels.py:180-212): eager and compiled with
+    fullgraph=True give the oracle's frames."""
+
+    from gradoom_b200 import native, ops, stepper
+
+    sc, blob = scenes("c1")
+    n, k = 6, 4
+    r = native.Renderer(blob, DEV, k)
+    lanes_np, things_np = stepper.random_lanes(sc, n, k, seed=4)
+    expected = oracle.render(blob, lanes_np, things_np)
+    lanes, things = torch.from_numpy(lanes_np).to(DEV), torch.from_numpy(things_np).to(DEV)
+    handle = r.handle.value
+    assert set(ops.NAMES) <= set(dir(torch.ops.gradoom_b200))
+
+    def step(lanes, things, stack, scratch, status):
+        torch.ops.gradoom_b200.render_step_(handle, lanes, things, stack, scratch, status, True)
+        obs = torch.ops.gradoom_b200.render_observation(handle, lanes, things, scratch, status, True)
+        return obs, stack.to(torch.float32).mean()
+
+    stack = torch.zeros((n, 4, 84, 84), dtype=torch.uint8, device=DEV)
+    obs, mean = step(lanes, things, stack, r.scratch, r.status)
+    assert np.array_equal(obs.cpu().numpy(), expected["obs"]) and np.array_equal(stack[:, 3].cpu().numpy(), expected["obs"])
+    compiled = torch.compile(step, fullgraph=True)
+    stack2 = torch.zeros_like(stack)
+    obs2, mean2 = compiled(lanes, things, stack2, r.scratch, r.status)
+    assert torch.equal(obs2, obs) and torch.equal(stack2, stack) and torch.allclose(mean2, mean)
+    rgb = torch.ops.gradoom_b200.render_rgb(handle, lanes, things, r.scratch, r.status, True)
+    assert np.array_equal(rgb.cpu().numpy(), oracle.rgb(blob, expected["indexed"]))
+    r.check_status()

@@ -145,6 +145,25 @@ def test_engine_state_struct_matches_the_header(pkg):
     assert names == mirror
 
 
+def test_scene_from_the_reference_scenario_container(pkg, scenes):
+    """A ``CompiledScenario``-shaped object (src/gradoom/scenario.py:302-410) converts into the
+    same blob as the Scene it was made from; one without the native assets is refused."""
+
+    import sys
+
+    sys.path.insert(0, os.path.join(entry.ROOT, "oracle"))
+    import ref_engine
+    from gradoom_b200 import scene as gdscene
+
+    sc, blob = scenes("c1i")
+    container = ref_engine.scene_to_compiled(sc, types.SimpleNamespace(CompiledScenario=types.SimpleNamespace))
+    back = gdscene.from_compiled_scenario(container)
+    assert np.array_equal(gdscene.pack_scene(back), blob)
+    container.texture_index_atlas = None
+    with pytest.raises(ValueError):
+        gdscene.from_compiled_scenario(container)
+
+
 def test_pack_things_roundtrip(pkg):
     from gradoom_b200 import state as gdstate
 
