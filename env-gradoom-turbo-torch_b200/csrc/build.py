@@ -10,6 +10,8 @@ SOURCES = ["gd_render.cu"]
 HEADERS = ["gd_device.cuh", "gd_geometry.cuh", "gd_walk.cuh", "gd_flats.cuh", "gd_sprites.cuh", "gd_output.cuh", "gd_abi.cuh", "gd_state.cuh", "gd_state_abi.cuh", "gd_move.cuh",
            "../../include/gradoom_b200.h", "../../include/gradoom_b200_layout.h"]
 LIBRARY = os.path.join(HERE, "libgradoom_b200.so")
+# the same sources with -DGD_CHECKED: every index taken from the blob or a record is range-tested
+CHECKED_LIBRARY = os.path.join(HERE, "libgradoom_b200_checked.so")
 
 # -fmad=false: the reference rounds every float32 multiply and add separately;
 # a fused multiply-add would change texel and ownership decisions.
@@ -32,18 +34,19 @@ def sources_hash() -> str:
     return digest.hexdigest()
 
 
-def is_stale() -> bool:
-    if not os.path.exists(LIBRARY):
+def is_stale(library: str = LIBRARY) -> bool:
+    if not os.path.exists(library):
         return True
-    built = os.path.getmtime(LIBRARY)
+    built = os.path.getmtime(library)
     return any(os.path.getmtime(os.path.join(HERE, f)) > built for f in SOURCES + HEADERS)
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
-    if force or is_stale():
-        cmd = ["nvcc", *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-o", LIBRARY,
-               *[os.path.join(HERE, s) for s in SOURCES]]
-        subprocess.check_call(cmd, cwd=HERE)
+    for library, extra in ((LIBRARY, []), (CHECKED_LIBRARY, ["-DGD_CHECKED"])):
+        if force or is_stale(library):
+            cmd = ["nvcc", *NVCC_FLAGS, *extra, *(["-Xptxas", "-v"] if verbose else []), "-o", library,
+                   *[os.path.join(HERE, s) for s in SOURCES]]
+            subprocess.check_call(cmd, cwd=HERE)
     return LIBRARY
 
 

@@ -86,7 +86,7 @@ extern "C" int gd_renderer_create(const void *blob_header_host, const void *blob
   sc.P = h[GD_H_SPRITES]; sc.sprH = h[GD_H_SPR_H]; sc.sprW = h[GD_H_SPR_W];
   sc.Q = h[GD_H_WPN_PATCHES]; sc.wpnH = h[GD_H_WPN_H]; sc.wpnW = h[GD_H_WPN_W]; sc.wpnTics = h[GD_H_WPN_TICS];
   sc.nStarts = h[GD_H_STARTS]; sc.B = h[GD_H_BLOCKING]; sc.nbDirect = h[GD_H_NB_DIRECT];
-  sc.wpnAvailable = h[GD_H_WPN_AVAILABLE];
+  sc.wpnAvailable = h[GD_H_WPN_AVAILABLE]; sc.hudPatches = h[GD_H_HUD_PATCHES];
 #define SECP(type, name) (const type *)gd_section(d, h, name)
   sc.walls = SECP(float, GD_S_WALLS); sc.wsec = SECP(int32_t, GD_S_WALL_SECTORS); sc.wlen = SECP(float, GD_S_WALL_LEN);
   sc.sideTex = SECP(int32_t, GD_S_SIDE_TEX); sc.sideOff = SECP(float, GD_S_SIDE_OFF);

@@ -30,10 +30,12 @@ typedef long long i64;
 /* status bits written to the device status word */
 #define GD_STATUS_EVENT_OVERFLOW 1   /* a column produced more clip events than the scratch holds */
 #define GD_STATUS_THINGS_OVERFLOW 2  /* a lane lists more things than the configured maximum */
-#define GD_STATUS_BAD_SECTOR 4       /* a state record points outside the scene */
+#define GD_STATUS_BAD_SECTOR 4       /* checked build: a sector index outside the scene */
+#define GD_STATUS_BAD_INDEX 8        /* checked build: a wall, texture, sprite or patch index outside its table */
+#define GD_STATUS_BAD_STATE 16       /* checked build: a lane or thing record with a value outside its range */
 
 struct GdScene {
-  int W, S, T, texH, texW, P, sprH, sprW, Q, wpnH, wpnW, wpnTics, nStarts, B, nbDirect, wpnAvailable;
+  int W, S, T, texH, texW, P, sprH, sprW, Q, wpnH, wpnW, wpnTics, nStarts, B, nbDirect, wpnAvailable, hudPatches;
   const float *walls;
   const int32_t *wsec;
   const float *wlen;
@@ -66,6 +68,38 @@ struct GdScene {
   int groups[2];
   int M;
 };
+
+/*
+ * Checked build (-DGD_CHECKED, libgradoom_b200_checked.so): every index taken from
+ * the scene blob, a lane record or a thing record is range-tested where it is about
+ * to address memory; an index out of range is replaced by 0 (the access it would
+ * have made is skipped) and a bit is set in the caller's status word.  Nothing
+ * traps.  The regular build compiles the tests away.
+ */
+#ifdef GD_CHECKED
+__device__ int *gdCheckedStatus;     /* the status word of the launch in flight (one launch at a time) */
+__device__ __forceinline__ int gd_checked(int i, int n, int bit) {
+  if ((unsigned)i < (unsigned)n) return i;
+  atomicOr(gdCheckedStatus, bit);
+  return 0;
+}
+#define GD_CHECK_INDEX(i, n) gd_checked((int)(i), (int)(n), GD_STATUS_BAD_INDEX)
+#define GD_CHECK_SECTOR(i, n) gd_checked((int)(i), (int)(n), GD_STATUS_BAD_SECTOR)
+#define GD_FLAG_STATE(bad) do { if (bad) atomicOr(gdCheckedStatus, GD_STATUS_BAD_STATE); } while (0)
+#else
+#define GD_CHECK_INDEX(i, n) (i)
+#define GD_CHECK_SECTOR(i, n) (i)
+#define GD_FLAG_STATE(bad) do { } while (0)
+#endif
+
+/* sector on one side of a wall: entry `i` of the wall-sector table, -1 = none */
+__device__ __forceinline__ int gd_wsec(const GdScene &sc, int i) {
+  const int s = sc.wsec[i];
+#ifdef GD_CHECKED
+  if (s < -1 || s >= sc.S) { atomicOr(gdCheckedStatus, GD_STATUS_BAD_SECTOR); return -1; }
+#endif
+  return s;
+}
 
 __device__ __forceinline__ i64 gd_min(i64 a, i64 b) { return a < b ? a : b; }
 __device__ __forceinline__ i64 gd_max(i64 a, i64 b) { return a > b ? a : b; }

@@ -7,6 +7,7 @@
 /* Crossing parity of a +x ray over the sector's edges.  The bounding box only
  * skips sectors whose parity is provably even. */
 __device__ __forceinline__ bool gd_point_in_sector(const GdScene &sc, int s, float px, float py) {
+  s = GD_CHECK_SECTOR(s, sc.S);
   const float4 bb = *reinterpret_cast<const float4 *>(&sc.secBBox[s * 4]);
   if (py >= bb.w || py < bb.z) return false;           /* no edge straddles the ray's row */
   if (px > bb.y + 1.0f) return false;                  /* every crossing lies left of the point */
@@ -14,7 +15,7 @@ __device__ __forceinline__ bool gd_point_in_sector(const GdScene &sc, int s, flo
   int crossings = 0;
 #pragma unroll 1
   for (int k = sc.edgeOff[s]; k < sc.edgeOff[s + 1]; ++k) {
-    const float4 e = *reinterpret_cast<const float4 *>(&sc.walls[sc.edgeWalls[k] * 4]);
+    const float4 e = *reinterpret_cast<const float4 *>(&sc.walls[GD_CHECK_INDEX(sc.edgeWalls[k], sc.W) * 4]);
     bool crosses = (e.y > py) != (e.w > py);
     float dy = e.w - e.y;
     float safe = fabsf(dy) < 1e-6f ? 1.0f : dy;

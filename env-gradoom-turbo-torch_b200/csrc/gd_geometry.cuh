@@ -101,7 +101,7 @@ __device__ __noinline__ void gd_project_wall(const GdScene &sc, const GdView &v,
   out.sl = sl; out.sr = sr; out.dl = dl; out.dr = dr;
   gd_wall_visibility(tx[0], ty[0], tx[1], ty[1], out.visL[0], out.visStep[0], out.visSl[0]);
   gd_wall_visibility(tx[1], ty[1], tx[0], ty[0], out.visL[1], out.visStep[1], out.visSl[1]);
-  out.oneSided = sc.wsec[w * 2 + 1] < 0;
+  out.oneSided = gd_wsec(sc, w * 2 + 1) < 0;
   float sx = wl[0], sy = wl[1];
   float segx = wl[2] - sx, segy = wl[3] - sy;
   float vfsx = v.x - sx, vfsy = v.y - sy;
@@ -157,6 +157,7 @@ __device__ __forceinline__ GdHit gd_hit(const GdScene &sc, const GdView &v, cons
   GdHit h;
   float distance, along;
   bool geo, positive;
+  w = GD_CHECK_INDEX(w, sc.W);
   gd_ray_test(sc, v, w, rx, ry, distance, along, geo, positive);
   const GdWall &wv = walls[w];
   bool screenValid = wv.hasColumns && x >= wv.isl && x < wv.isr;
@@ -193,7 +194,7 @@ __device__ __noinline__ void gd_endpoint_owner(const GdScene &sc, const GdView &
   bool ownerValid = false;
   if (sc.nbDirect) {
     const int32_t *nd = &sc.nbDirectTab[w * 4];
-    int sIdx = nd[0] >= 0 ? nd[0] : w, eIdx = nd[1] >= 0 ? nd[1] : w;
+    int sIdx = nd[0] >= 0 ? GD_CHECK_INDEX(nd[0], sc.W) : w, eIdx = nd[1] >= 0 ? GD_CHECK_INDEX(nd[1], sc.W) : w;
     bool hasS = nd[0] >= 0, hasE = nd[1] >= 0;
     int rIdx = usesStart ? sIdx : eIdx, rSlot = usesStart ? nd[2] : nd[3];
     bool rHas = usesStart ? hasS : hasE;
@@ -213,7 +214,7 @@ __device__ __noinline__ void gd_endpoint_owner(const GdScene &sc, const GdView &
     int n0 = sc.nbOff[w], n1 = sc.nbOff[w + 1];
 #pragma unroll 1
     for (int k = n0; k < n1; ++k) {
-      int nb = sc.nbIdx[k], fl = sc.nbFlags[k];
+      int nb = GD_CHECK_INDEX(sc.nbIdx[k], sc.W), fl = sc.nbFlags[k];
       GdHit hn = gd_hit(sc, v, walls, nb, x, rx, ry);
       bool rayNb = usesStart ? (fl & 1) : ((fl >> 1) & 1);
       bool sel = rayNb || (subpixel && (fabsf(hn.d - d) <= tol));
@@ -221,7 +222,7 @@ __device__ __noinline__ void gd_endpoint_owner(const GdScene &sc, const GdView &
       if (cand < best) { best = cand; bestSlot = k - n0; }
     }
     od = best;
-    oi = (n1 > n0) ? sc.nbIdx[n0 + bestSlot] : w;
+    oi = (n1 > n0) ? GD_CHECK_INDEX(sc.nbIdx[n0 + bestSlot], sc.W) : w;
     ownerValid = isfinite(best);
   }
   bool has = !hw.proj && ownerValid;
@@ -373,7 +374,7 @@ __device__ __forceinline__ int gd_wall_shade(i64 light, i64 vis) {
 }
 
 /* ---- static topology predicates (engine.py:399-484, 1596-1612) ---------- */
-__device__ __forceinline__ int gd_secidx(const GdScene &sc, int s) { return s < 0 ? s + sc.S : s; }
+__device__ __forceinline__ int gd_secidx(const GdScene &sc, int s) { return GD_CHECK_SECTOR(s < 0 ? s + sc.S : s, sc.S); }
 __device__ __forceinline__ float gd_sec_floor(const GdScene &sc, int s) { return sc.secF[gd_secidx(sc, s) * 2]; }
 __device__ __forceinline__ float gd_sec_ceil(const GdScene &sc, int s) { return sc.secF[gd_secidx(sc, s) * 2 + 1]; }
 __device__ __forceinline__ int4 gd_sec_info(const GdScene &sc, int s) {
@@ -381,7 +382,7 @@ __device__ __forceinline__ int4 gd_sec_info(const GdScene &sc, int s) {
 }
 
 __device__ __forceinline__ bool gd_same_pair(const GdScene &sc, int a, int b) {
-  int a0 = sc.wsec[a * 2], a1 = sc.wsec[a * 2 + 1], b0 = sc.wsec[b * 2], b1 = sc.wsec[b * 2 + 1];
+  int a0 = gd_wsec(sc, a * 2), a1 = gd_wsec(sc, a * 2 + 1), b0 = gd_wsec(sc, b * 2), b1 = gd_wsec(sc, b * 2 + 1);
   return (a0 == b0 && a1 == b1) || (a0 == b1 && a1 == b0);
 }
 __device__ __forceinline__ bool gd_shares_endpoint(const GdScene &sc, int a, int b) {
@@ -390,7 +391,7 @@ __device__ __forceinline__ bool gd_shares_endpoint(const GdScene &sc, int a, int
 }
 __device__ __noinline__ bool gd_opposing_pair(const GdScene &sc, int a, int b) {
   if (!gd_same_pair(sc, a, b)) return false;
-  if (sc.wsec[a * 2 + 1] < 0 || sc.wsec[b * 2 + 1] < 0) return false;
+  if (gd_wsec(sc, a * 2 + 1) < 0 || gd_wsec(sc, b * 2 + 1) < 0) return false;
   if (gd_shares_endpoint(sc, a, b)) return false;
   const float *A = &sc.walls[a * 4], *B = &sc.walls[b * 4];
   float adx = A[2] - A[0], ady = A[3] - A[1], bdx = B[2] - B[0], bdy = B[3] - B[1];
@@ -399,10 +400,10 @@ __device__ __noinline__ bool gd_opposing_pair(const GdScene &sc, int a, int b) {
   return dot < 0 && fabsf(cross) < 1e-6f;
 }
 __device__ __forceinline__ bool gd_two_distinct(const GdScene &sc, int w) {
-  return sc.wsec[w * 2 + 1] >= 0 && sc.wsec[w * 2] != sc.wsec[w * 2 + 1];
+  return gd_wsec(sc, w * 2 + 1) >= 0 && gd_wsec(sc, w * 2) != gd_wsec(sc, w * 2 + 1);
 }
 __device__ bool gd_bridge_pair_of(const GdScene &sc, int a, int b, int &p0, int &p1) {
-  int a0 = sc.wsec[a * 2], a1 = sc.wsec[a * 2 + 1], b0 = sc.wsec[b * 2], b1 = sc.wsec[b * 2 + 1];
+  int a0 = gd_wsec(sc, a * 2), a1 = gd_wsec(sc, a * 2 + 1), b0 = gd_wsec(sc, b * 2), b1 = gd_wsec(sc, b * 2 + 1);
   int shared = 0, sv = -2;
   if (a0 == b0 || a0 == b1) { shared++; sv = a0; }
   if (a1 == b0 || a1 == b1) { shared++; sv = a1; }
@@ -412,7 +413,7 @@ __device__ bool gd_bridge_pair_of(const GdScene &sc, int a, int b, int &p0, int 
   return true;
 }
 __device__ __forceinline__ bool gd_set_equals(const GdScene &sc, int w, int p0, int p1) {
-  int s0 = sc.wsec[w * 2], s1 = sc.wsec[w * 2 + 1];
+  int s0 = gd_wsec(sc, w * 2), s1 = gd_wsec(sc, w * 2 + 1);
   if (p0 == p1) return s0 == p0 && s1 == p0;
   return (s0 == p0 && s1 == p1) || (s0 == p1 && s1 == p0);
 }
@@ -420,7 +421,7 @@ __device__ bool gd_unique_at_vertex(const GdScene &sc, int v, int skipA, int ski
   int count = 0, found = 0;
 #pragma unroll 1
   for (int k = sc.vtxOff[v]; k < sc.vtxOff[v + 1]; ++k) {
-    int c = sc.vtxWalls[k];
+    int c = GD_CHECK_INDEX(sc.vtxWalls[k], sc.W);
     if (c == skipA || c == skipB) continue;
     if (gd_set_equals(sc, c, p0, p1)) { count++; found = c; }
   }
@@ -540,7 +541,7 @@ __device__ void gd_wall_spans(const GdScene &sc, const GdView &v, const GdShared
 __device__ void gd_blocking_raycast(const GdScene &sc, const GdView &v, const GdShared &sh, const short *list, int listed,
                                     float rx, float ry, float &wallDistance, int &blockingWall) {
   float best = GD_INF;
-  int bestWall = sc.blocking[0];
+  int bestWall = GD_CHECK_INDEX(sc.blocking[0], sc.W);
 #pragma unroll 1
   for (int i = 0; i < listed; ++i) {
     const int w = list[i];

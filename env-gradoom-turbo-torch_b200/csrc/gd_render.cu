@@ -200,6 +200,10 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
   __syncthreads();
   const GdScene &sc = sScene;
   const GdShared &sh = sShared;
+#ifdef GD_CHECKED
+  if (tid == 0) gdCheckedStatus = p.status;
+  __syncthreads();
+#endif
   /* tables shared by every lane this CTA draws */
   for (int i = tid; i < 32 * 256 / 4; i += GD_THREADS)
     ((unsigned *)sh.colormap)[i] = ((const unsigned *)sc.colormap)[i];
@@ -248,6 +252,26 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
       nThings = min(p.maxThings, 64);
     }
     if (nThings < 0) nThings = 0;
+#ifdef GD_CHECKED
+    {
+      /* a lane whose pose is not a number, or lies far outside any map, is drawn from the map's origin instead */
+      const float lx = __int_as_float(sh.lane[GD_L_X]), ly = __int_as_float(sh.lane[GD_L_Y]);
+      const float lz = __int_as_float(sh.lane[GD_L_VIEW_Z]), la = __int_as_float(sh.lane[GD_L_ANGLE]);
+      const bool badPose = !isfinite(lx) || !isfinite(ly) || !isfinite(lz) || !isfinite(la) || fabsf(lx) > 32768.0f ||
+                           fabsf(ly) > 32768.0f;
+      const int weapon = sh.lane[GD_L_WEAPON];
+      __syncthreads();
+      if (tid == 0) {
+        GD_FLAG_STATE(badPose || weapon < 0 || weapon > 7 || sh.lane[GD_L_THINGS] < 0);
+        if (badPose) {
+          sh.lane[GD_L_X] = sh.lane[GD_L_Y] = sh.lane[GD_L_ANGLE] = 0;
+          sh.lane[GD_L_X_FIXED] = sh.lane[GD_L_Y_FIXED] = sh.lane[GD_L_ANGLE_BAM] = 0;
+          sh.lane[GD_L_VIEW_Z] = __float_as_int(41.0f);
+        }
+      }
+      __syncthreads();
+    }
+#endif
     if (tid == 0) {
       gd_view_setup(sc, sh.lane, sView);
     } else if (tid >= 32) {
@@ -290,7 +314,7 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
      * walk selects no other wall) */
     for (int idx = tid; idx < sh.misc[2] * 4; idx += GD_THREADS) {
       int w = ((const short *)sh.hitD)[idx >> 2], slot = idx & 3;
-      int sector = sc.wsec[w * 2 + (slot >> 1)];
+      int sector = gd_wsec(sc, w * 2 + (slot >> 1));
       if (sector >= 0) gd_rowproj_setup(v, sh.walls[w], sc.secF[sector * 2 + (slot & 1)], rowproj[w * 4 + slot]);
     }
     __syncthreads();

@@ -13,6 +13,16 @@ __device__ __noinline__ void gd_actor_setup(const GdScene &sc, const GdView &v, 
   ac.sprite = sprite;
   const int4 si = *reinterpret_cast<const int4 *>(&sc.sprInfo[sprite * 4]);
   ac.w = si.x; ac.h = si.y;
+#ifdef GD_CHECKED
+  {
+    /* a record that names no patch of the scene, or lies nowhere, is not drawn */
+    const bool badIndex = t.sprite >= sc.P || si.x > sc.sprW || si.y > sc.sprH || si.x < 0 || si.y < 0;
+    const bool badState = !isfinite(t.x) || !isfinite(t.y) || !isfinite(t.z) || sector < 0 || sector >= sc.S;
+    if (badIndex) atomicOr(gdCheckedStatus, GD_STATUS_BAD_INDEX);
+    if (badState) atomicOr(gdCheckedStatus, GD_STATUS_BAD_STATE);
+    if (badIndex || badState) { ac.alive = 0; ac.w = ac.h = 0; if (badState) sector = 0; }
+  }
+#endif
   float dx = t.x - v.x, dy = t.y - v.y;
   float dist = sqrtf(dx * dx + dy * dy);
   if (dist < 1.0f) dist = 1.0f;
@@ -171,6 +181,9 @@ __device__ void gd_sprites(const GdScene &sc, const GdView &v, const GdShared &s
 
 /* ---- phase: weapon (engine.py:14994-15121) ------------------------------ */
 __device__ __noinline__ void gd_weapon_patch(const GdScene &sc, uint8_t *frame, int id, i64 hoff, i64 voff) {
+#ifdef GD_CHECKED
+  if (id >= sc.Q || id < -1) { if (threadIdx.x == 0) atomicOr(gdCheckedStatus, GD_STATUS_BAD_INDEX); }
+#endif
   if (id < 0 || id >= sc.Q) return;
   const int4 wi = *reinterpret_cast<const int4 *>(&sc.wpnInfo[id * 4]);
   int w = wi.x, h = wi.y;
@@ -227,10 +240,13 @@ __device__ void gd_weapon(const GdScene &sc, const int32_t *lane, uint8_t *frame
  * per entry clips it against the canvas, and then every column thread resolves
  * its 32 pixels from the entries that cross its column, topmost first. */
 
-struct GdHudList { int4 *entries; int *count; };
+struct GdHudList { int4 *entries; int *count; int patches; };
 
 __device__ __forceinline__ void gd_hud_push(const GdHudList &hl, int patch, int x, int y) {
   int n = *hl.count;
+#ifdef GD_CHECKED
+  if (patch < 0 || patch >= hl.patches) { atomicOr(gdCheckedStatus, GD_STATUS_BAD_INDEX); return; }
+#endif
   if (n < GD_HUD_MAX_PATCHES) { hl.entries[n] = make_int4(patch, x, y, 0); *hl.count = n + 1; }
 }
 
@@ -256,6 +272,7 @@ __device__ __noinline__ void gd_hud(const GdScene &sc, const GdShared &sh, const
   GdHudList hl;
   hl.entries = (int4 *)sh.obs;                       /* free until the resize */
   hl.count = (int *)(sh.obs + GD_HUD_MAX_PATCHES * sizeof(int4));
+  hl.patches = sc.hudPatches;
   if (threadIdx.x == 0) {
     *hl.count = 0;
     gd_hud_push(hl, 0, 0, 0);

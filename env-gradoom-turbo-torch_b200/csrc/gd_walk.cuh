@@ -25,7 +25,7 @@ __device__ __noinline__ void gd_plane_entry_setup(const GdScene &sc, const GdVie
                                                   GdPlaneEntry &e) {
   float ph = isFloor ? (v.viewZ - gd_sec_floor(sc, sector)) : (gd_sec_ceil(sc, sector) - v.viewZ);
   int4 si = gd_sec_info(sc, sector);
-  int tex = isFloor ? si.y : si.z;
+  int tex = GD_CHECK_INDEX(isFloor ? si.y : si.z, sc.T);
   const int4 ti = *reinterpret_cast<const int4 *>(&sc.texInfo[tex * 4]);
   e.wbits = ti.z; e.hbits = ti.w;
   e.tex = sc.texAtlas + (size_t)tex * sc.texH * sc.texW;
@@ -130,7 +130,7 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
                                  const GdRowProj *rowproj, float *hitD, float *hitA, uint8_t *hitF, int x, float rx,
                                  float ry, const GdColState &c, GdIter &it) {
   const int curSector = c.cur;
-  const int current = curSector < 0 ? 0 : curSector;
+  const int current = GD_CHECK_SECTOR(curSector < 0 ? 0 : curSector, sc.S);
   const float prev = c.prev;
   const int i0 = sc.secOff[current], i1 = sc.secOff[current + 1];
   /* every rule below looks at the walls of the current sector: test each once
@@ -139,7 +139,7 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
   const int nCache = min(i1 - i0, kCache);
 #pragma unroll 1
   for (int k = 0; k < nCache; ++k) {
-    GdHit h = gd_hit(sc, v, walls, sc.secWalls[i0 + k], x, rx, ry);
+    GdHit h = gd_hit(sc, v, walls, GD_CHECK_INDEX(sc.secWalls[i0 + k], sc.W), x, rx, ry);
     hitD[k * GD_SW + x] = h.d;
     hitA[k * GD_SW + x] = h.along;
     hitF[k * GD_SW + x] = (uint8_t)((h.geo ? 1 : 0) | (h.proj ? 2 : 0) | (h.left ? 4 : 0));
@@ -160,13 +160,13 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
     return gd_hit_slow(sc, v, walls, w, x, rx, ry);
   };
 #define HIT(w) cachedHit(w)
-#define HITK(k) (((k) - i0) < nCache ? loadHit((k) - i0) : gd_hit_slow(sc, v, walls, sc.secWalls[k], x, rx, ry))
+#define HITK(k) (((k) - i0) < nCache ? loadHit((k) - i0) : gd_hit_slow(sc, v, walls, GD_CHECK_INDEX(sc.secWalls[k], sc.W), x, rx, ry))
   float distance = GD_INF;
   int wallIndex = 0;
   if (curSector >= 0) {
 #pragma unroll 1
     for (int k = i0; k < i1; ++k) {
-      int w = sc.secWalls[k];
+      int w = GD_CHECK_INDEX(sc.secWalls[k], sc.W);
       GdHit h = HITK(k);
       if (h.d > prev && h.d < distance) { distance = h.d; wallIndex = w; }
     }
@@ -174,7 +174,7 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
     int sw = 0;
 #pragma unroll 1
     for (int k = i0; k < i1; ++k) {
-      int w = sc.secWalls[k];
+      int w = GD_CHECK_INDEX(sc.secWalls[k], sc.W);
       if (!walls[w].oneSided) continue;
       GdHit h = HITK(k);
       if (!(h.d > prev) || !isfinite(h.d)) continue;
@@ -207,7 +207,7 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
   if (!selIsProjected) {
 #pragma unroll 1
     for (int k = i0; k < i1; ++k) {
-      int w = sc.secWalls[k];
+      int w = GD_CHECK_INDEX(sc.secWalls[k], sc.W);
       if (!walls[w].oneSided || !SHARES_SEL(w)) continue;
       GdHit h = HITK(k);
       if (h.proj && h.left && (h.d > prev + 1e-3f) && h.d < psd) { psd = h.d; psi = w; }
@@ -219,8 +219,8 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
       int sbi = wallIndex;
 #pragma unroll 1
       for (int k = off[wallIndex]; k < off[wallIndex + 1]; ++k) {
-        int b = idx[k];
-        bool inc = sc.wsec[b * 2] == current || sc.wsec[b * 2 + 1] == current;
+        int b = GD_CHECK_INDEX(idx[k], sc.W);
+        bool inc = gd_wsec(sc, b * 2) == current || gd_wsec(sc, b * 2 + 1) == current;
         if (!inc || !walls[b].oneSided) continue;
         GdHit h = HIT(b);
         if (h.proj && h.left && (h.d > prev + 1e-3f) && h.d < sbd) { sbd = h.d; sbi = b; }
@@ -240,8 +240,8 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
   int nopIndex = wallIndex;
   float nopDist = distance;
   bool nopIsGeo = replaceEo ? eoPathIsGeo : hW.geo;
-  bool nopFromFront = curSector == sc.wsec[nopIndex * 2];
-  int nopOther = nopFromFront ? sc.wsec[nopIndex * 2 + 1] : sc.wsec[nopIndex * 2];
+  bool nopFromFront = curSector == gd_wsec(sc, nopIndex * 2);
+  int nopOther = nopFromFront ? gd_wsec(sc, nopIndex * 2 + 1) : gd_wsec(sc, nopIndex * 2);
   bool selOwnerIsProjected = hW.proj;
   bool selOwnerExclRight = walls[wallIndex].sr == x;
   i64 selOwnerSpan = walls[wallIndex].sr - walls[wallIndex].sl;
@@ -251,7 +251,7 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
   if (!selOwnerIsProjected) {
 #pragma unroll 1
     for (int k = i0; k < i1; ++k) {
-      int w = sc.secWalls[k];
+      int w = GD_CHECK_INDEX(sc.secWalls[k], sc.W);
       if (walls[w].oneSided) continue;
       GdHit h = HITK(k);
       if (!h.proj || !(h.d > prev + 1e-3f)) continue;
@@ -268,17 +268,17 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
   }
   /* projected sector bridge (engine.py:12073-12164) */
   const int pew = c.pendEpWall;
-  bool peFromCur = curSector == sc.wsec[pew * 2];
-  int peOther = peFromCur ? sc.wsec[pew * 2 + 1] : sc.wsec[pew * 2];
+  bool peFromCur = curSector == gd_wsec(sc, pew * 2);
+  int peOther = peFromCur ? gd_wsec(sc, pew * 2 + 1) : gd_wsec(sc, pew * 2);
   bool usePsb = false;
   if (c.pendEpBoundary && !selOwnerIsProjected && selOwnerExclRight && nopIsGeo) {
-    bool peIncident = peFromCur || curSector == sc.wsec[pew * 2 + 1];
+    bool peIncident = peFromCur || curSector == gd_wsec(sc, pew * 2 + 1);
     const float *peWall = &sc.walls[pew * 4];
     int peSlot = (c.pendEpEpX == peWall[2] && c.pendEpEpY == peWall[3]) ? 1 : 0;
     int psbIndex;
     bool psbExists = gd_sector_bridge(sc, peSlot, pew, nopIndex, psbIndex);
     if (psbExists && peIncident && peOther >= 0 && nopOther >= 0 && (walls[pew].sr - walls[pew].sl <= 1)) {
-      int b0 = sc.wsec[psbIndex * 2], b1 = sc.wsec[psbIndex * 2 + 1];
+      int b0 = gd_wsec(sc, psbIndex * 2), b1 = gd_wsec(sc, psbIndex * 2 + 1);
       bool matches = (b0 == peOther && b1 == nopOther) || (b1 == peOther && b0 == nopOther);
       GdHit hb = HIT(psbIndex);
       GdHit hp = HIT(pew);
@@ -299,7 +299,7 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
                      !((pendEpHasFwd || completesPendEpBridge) && !selIsProjected && selExclRight && !replaceNp);
   bool geometric = replaceNp ? nopIsGeo : (replaceEo ? eoPathIsGeo : hW.geo);
   bool nokpp = replaceNp && nopIsGeo && nopOther >= 0;
-  int front = sc.wsec[wallIndex * 2], back = sc.wsec[wallIndex * 2 + 1];
+  int front = gd_wsec(sc, wallIndex * 2), back = gd_wsec(sc, wallIndex * 2 + 1);
   bool fromFront = curSector == front;
   int otherSector = fromFront ? back : front;
   int renderCurrent = usePsb ? peOther : (completesOpposing ? otherSector : current);
@@ -308,8 +308,8 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
   int side = renderFromFront ? 0 : 1;
   const GdWall &wv = walls[wallIndex];
   i64 vis = wv.visL[side] + ((i64)x - wv.visSl[side]) * wv.visStep[side];
-  bool psFromFront = curSector == sc.wsec[psPathIndex * 2];
-  int psOther = psFromFront ? sc.wsec[psPathIndex * 2 + 1] : sc.wsec[psPathIndex * 2];
+  bool psFromFront = curSector == gd_wsec(sc, psPathIndex * 2);
+  int psOther = psFromFront ? gd_wsec(sc, psPathIndex * 2 + 1) : gd_wsec(sc, psPathIndex * 2);
   bool pskpp = hasProjectedSolidOwner && hSel.geo && psOther >= 0;
   int safeOther = renderOther < 0 ? 0 : renderOther;
   float viewFloor = gd_sec_floor(sc, renderCurrent), viewCeil = gd_sec_ceil(sc, renderCurrent);
@@ -367,7 +367,7 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
   if (endpointOnly) {
 #pragma unroll 1
     for (int k = i0; k < i1; ++k) {
-      int w = sc.secWalls[k];
+      int w = GD_CHECK_INDEX(sc.secWalls[k], sc.W);
       GdHit h = HITK(k);
       bool os = walls[w].oneSided;
       bool fut = (h.geo || (os && isfinite(h.d))) && (h.d > distance + 1e-3f);
@@ -382,7 +382,7 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
     /* endpointOnly implies otherSector >= 0 */
 #pragma unroll 1
     for (int k = sc.secOff[otherSector]; k < sc.secOff[otherSector + 1]; ++k) {
-      int w = sc.secWalls[k];
+      int w = GD_CHECK_INDEX(sc.secWalls[k], sc.W);
       GdHit h = HIT(w);
       bool os = walls[w].oneSided;
       bool fut = (h.geo || (os && isfinite(h.d))) && (h.d > distance + 1e-3f);
@@ -396,8 +396,8 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
   bool tied = endpointOnly && isfinite(cnd) && cni == oni && gd_opposing_pair(sc, wallIndex, cni);
   bool entersOther = endpointOnly && otherSector >= 0 && ((ond < cnd) || tied);
   bool entersShared = endpointOnly && otherSector >= 0 && (osd < csd);
-  bool gpFromFront = curSector == sc.wsec[gpi * 2];
-  int gpOther = gpFromFront ? sc.wsec[gpi * 2 + 1] : sc.wsec[gpi * 2];
+  bool gpFromFront = curSector == gd_wsec(sc, gpi * 2);
+  int gpOther = gpFromFront ? gd_wsec(sc, gpi * 2 + 1) : gd_wsec(sc, gpi * 2);
   bool usesGeo = endpointOnly && isfinite(gpd) && gpOther >= 0;
   int ppbIdx = 0;
   bool epb = false;
@@ -442,6 +442,9 @@ __device__ __noinline__ void gd_draw_tier(const GdScene &sc, const GdView &v, co
                              bool tailValid, int tailBottom, int oa, int ob, bool oTailValid, int oTailBottom,
                              unsigned *filled) {
   if (texId < 0 || ya >= yb) return;
+#ifdef GD_CHECKED
+  if (texId >= sc.T) { atomicOr(gdCheckedStatus, GD_STATUS_BAD_INDEX); return; }   /* the tier stays undrawn */
+#endif
   const int4 ti = *reinterpret_cast<const int4 *>(&sc.texInfo[texId * 4]);
   int tw = ti.x, hbits = ti.w;
   int u = gd_pymod_width((t.hoff + t.tox) >> 16, tw);
@@ -536,16 +539,19 @@ __device__ __noinline__ void gd_masked_pass(const GdScene &sc, const GdView &v, 
   bool leftEdge = false;
 #pragma unroll 1
   for (int i = 0; i < sc.M; ++i) {
-    const int k = sc.maskedWalls[i];
+    const int k = GD_CHECK_INDEX(sc.maskedWalls[i], sc.W);
     const int sd = sh.walls[k].frontF ? 0 : 1;
     const int t = sc.sideTex[(k * 2 + sd) * 3];
     if (t < 0) continue;
+#ifdef GD_CHECKED
+    if (t >= sc.T) { atomicOr(gdCheckedStatus, GD_STATUS_BAD_INDEX); continue; }
+#endif
     GdHit h = gd_hit_slow(sc, v, sh.walls, k, x, rx, ry);
     if (h.proj && h.d < best) { best = h.d; w = k; side = sd; texId = t; leftEdge = h.left; }
   }
   if (!isfinite(best)) return;
   const GdWall &wv = sh.walls[w];
-  const int front = sc.wsec[w * 2], back = sc.wsec[w * 2 + 1] < 0 ? 0 : sc.wsec[w * 2 + 1];
+  const int front = gd_wsec(sc, w * 2), back = gd_wsec(sc, w * 2 + 1) < 0 ? 0 : gd_wsec(sc, w * 2 + 1);
   const int lightSector = side == 0 ? front : back;
   const float worldTop = fminf(gd_sec_ceil(sc, front), gd_sec_ceil(sc, back));
   const int4 ti = *reinterpret_cast<const int4 *>(&sc.texInfo[texId * 4]);

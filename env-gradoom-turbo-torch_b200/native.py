@@ -14,10 +14,15 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIBRARY = os.path.join(HERE, "csrc", "libgradoom_b200.so")
+# the same sources compiled with -DGD_CHECKED: range tests on every index, for debugging state producers
+CHECKED_LIBRARY = os.path.join(HERE, "csrc", "libgradoom_b200_checked.so")
 
 GD_OK = 0
 STATUS_EVENT_OVERFLOW = 1
 STATUS_THINGS_OVERFLOW = 2
+STATUS_BAD_SECTOR = 4
+STATUS_BAD_INDEX = 8
+STATUS_BAD_STATE = 16
 
 EXPORTS = (
     "gd_error_string", "gd_renderer_create", "gd_renderer_destroy", "gd_renderer_scratch_bytes",
@@ -26,23 +31,23 @@ EXPORTS = (
     "gd_pack_state_scratch_bytes", "gd_pack_state", "gd_player_tics",
 )
 
-_lib = None
+_libs = {}
 
 
 class NativeError(RuntimeError):
     pass
 
 
-def load() -> ctypes.CDLL:
-    """Load libgradoom_b200.so; raise if it has not been built."""
+def load(checked: bool = False) -> ctypes.CDLL:
+    """Load libgradoom_b200.so (or its checked build); raise if it has not been built."""
 
-    global _lib
-    if _lib is None:
-        if not os.path.exists(LIBRARY):
+    path = CHECKED_LIBRARY if checked else LIBRARY
+    if path not in _libs:
+        if not os.path.exists(path):
             raise NativeError(
-                f"{LIBRARY} is missing: build it with __graft_entry__.build() "
+                f"{path} is missing: build it with __graft_entry__.build() "
                 "(nvcc, sm_100a). This package has no CPU or PyTorch fallback.")
-        lib = ctypes.CDLL(LIBRARY)
+        lib = ctypes.CDLL(path)
         vp, ci, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
         lib.gd_error_string.restype = ctypes.c_char_p
         lib.gd_error_string.argtypes = [ci]
@@ -82,8 +87,8 @@ def load() -> ctypes.CDLL:
         lib.gd_pack_state.argtypes = [vp, vp, vp, vp, vp, sz, vp, vp]
         lib.gd_player_tics.restype = ci
         lib.gd_player_tics.argtypes = [vp, vp, vp, vp, ci, ci, ci, vp, vp, vp]
-        _lib = lib
-    return _lib
+        _libs[path] = lib
+    return _libs[path]
 
 
 def _check(code: int, what: str) -> None:
@@ -102,8 +107,9 @@ class Renderer:
     the same device (layout: include/gradoom_b200_layout.h).
     """
 
-    def __init__(self, blob: np.ndarray, device: torch.device | str, max_things: int):
-        self.lib = load()
+    def __init__(self, blob: np.ndarray, device: torch.device | str, max_things: int, *, checked: bool = False):
+        self.lib = load(checked)
+        self.checked = checked
         self.device = torch.device(device)
         if self.device.type != "cuda":
             raise NativeError("the renderer needs a CUDA device; there is no CPU path")
@@ -322,4 +328,10 @@ class Renderer:
                 names.append("clip-event overflow (a column crossed more segs than the scratch holds)")
             if bits & STATUS_THINGS_OVERFLOW:
                 names.append("a lane listed more things than max_things")
+            if bits & STATUS_BAD_SECTOR:
+                names.append("a sector index outside the scene (checked build)")
+            if bits & STATUS_BAD_INDEX:
+                names.append("a wall, texture, sprite or patch index outside its table (checked build)")
+            if bits & STATUS_BAD_STATE:
+                names.append("a lane or thing record with a value outside its range (checked build)")
             raise NativeError("renderer status: " + "; ".join(names or [hex(bits)]))

@@ -46,7 +46,12 @@ enum gd_error {
 /* device status bits */
 #define GD_STATUS_EVENT_OVERFLOW 1
 #define GD_STATUS_THINGS_OVERFLOW 2
-#define GD_STATUS_BAD_SECTOR 4
+/* set only by the checked build of the library (libgradoom_b200_checked.so, compiled with
+ * -DGD_CHECKED), which range-tests every index taken from the blob and the records, skips the
+ * access an index out of range would have made, and reports it here: */
+#define GD_STATUS_BAD_SECTOR 4     /* a sector index outside the scene */
+#define GD_STATUS_BAD_INDEX 8      /* a wall, texture, sprite or patch index outside its table */
+#define GD_STATUS_BAD_STATE 16     /* a lane or thing record with a value outside its range */
 
 typedef struct gd_renderer gd_renderer;
 
