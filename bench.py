@@ -541,17 +541,17 @@ def run_ours(args):
 
 
 def run_rollout(args):
-    """Rollout loop of the benchmark definition's last configuration (src/gradoom/train.py:1500-1521,
-    1645-1672, 2888-2901 in shape): 256 lanes x 16-step rollouts on the 64-sector map, a random-init
-    Nature-CNN policy under bf16 autocast picking the actions, +1 reward per kill, GAE(0.99, 0.95) at the
-    end of every rollout.  The policy is plain PyTorch (context, not part of the render path); what is
-    measured is env-frames/s with the render in the loop.  ``--steps`` counts rollouts."""
+    """The rollout workload of the benchmark definition (256 lanes x 16-step rollouts on the
+    64-sector map, a random-init Nature-CNN under bf16 autocast picking the actions, +1 per kill,
+    GAE(0.99, 0.95)): ``gradoom_b200.rollout.RolloutLoop`` around ``GraDoomVecEnv``.  The policy is
+    plain PyTorch (context, not part of the render path); what is measured is env-frames/s with
+    the render in the loop.  ``--steps`` counts rollouts; ``--update`` adds the clipped
+    policy-gradient pass after every rollout."""
 
     import torch
-    import torch.nn as nn
 
     entry.load_package()
-    from gradoom_b200 import scene as gdscene
+    from gradoom_b200 import rollout, scene as gdscene
     from gradoom_b200.env import GraDoomVecEnv
 
     device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
@@ -561,60 +561,28 @@ def run_rollout(args):
     env = GraDoomVecEnv(compiled_scenario=sc, num_envs=lanes, device=device, frame_skip=2, obs_crop=(0, 32, 0, 0),
                         obs_crop_mode="mask", max_things=things, producer_seed=5)
     torch.manual_seed(5)
-    trunk = nn.Sequential(nn.Conv2d(4, 32, 8, 4), nn.ReLU(), nn.Conv2d(32, 64, 4, 2), nn.ReLU(),
-                          nn.Conv2d(64, 64, 3, 1), nn.ReLU(), nn.Flatten(), nn.Linear(64 * 7 * 7, 512), nn.ReLU()).to(device)
-    heads = nn.Linear(512, 17 + 1).to(device)
-    everyone = torch.ones(lanes, dtype=torch.bool, device=device)
-    lane_ids = torch.arange(lanes, device=device, dtype=torch.int64)
-    obs, _ = env.reset_device(everyone, lane_ids + 1)
-    rewards = torch.zeros((horizon, lanes), device=device)
-    values = torch.zeros((horizon + 1, lanes), device=device)
-    dones = torch.zeros((horizon, lanes), device=device)
-
-    @torch.no_grad()
-    def act(observation):
-        with torch.autocast("cuda", dtype=torch.bfloat16):
-            out = heads(trunk(observation.float() / 255.0)).float()
-        logits = out[:, :17]
-        gumbel = -torch.log(-torch.log(torch.rand_like(logits).clamp_min(1e-20)))   # categorical sample, no host check
-        return torch.argmax(logits + gumbel, dim=1), out[:, 17]
-
-    counter = torch.zeros((), dtype=torch.int64, device=device)        # reseed counter, advanced on the device
-
-    def rollout():
-        nonlocal obs
-        for t in range(horizon):
-            action, values[t] = act(obs)
-            counter.add_(1)
-            tr = env.step_and_reset_device(action, lane_ids + counter * lanes)
-            obs = tr.observations
-            rewards[t] = tr.rewards
-            dones[t] = (tr.terminated | tr.truncated).float()
-        _, values[horizon] = act(obs)
-        advantage = torch.zeros(lanes, device=device)
-        returns = torch.zeros_like(rewards)
-        for t in reversed(range(horizon)):                  # GAE(gamma 0.99, lambda 0.95)
-            alive = 1.0 - dones[t]
-            delta = rewards[t] + 0.99 * values[t + 1] * alive - values[t]
-            advantage = delta + 0.99 * 0.95 * alive * advantage
-            returns[t] = advantage + values[t]
-        return returns
+    policy = rollout.NatureCnnPolicy().to(device)
+    loop = rollout.RolloutLoop(env, policy, horizon=horizon, gamma=0.99, gae_lambda=0.95, seed=5)
+    launches_before = env._renderer.launches
 
     for w in range(args.warmup):
-        rollout()
+        loop.collect()
+        if args.update:
+            loop.update()
     torch.cuda.synchronize(device)
-    # The loop is launch-bound at 256 lanes (about 60 small launches per env step), so one whole rollout
-    # is captured into a CUDA graph: the render entry points allocate nothing and never synchronise.
+    launches_per_rollout = (env._renderer.launches - launches_before) // max(args.warmup, 1)
+    # The loop is launch-bound at 256 lanes (dozens of small launches per env step), so one whole rollout
+    # is captured into a CUDA graph: the environment's calls allocate nothing and never synchronise.
     graph = None
     if not args.no_graph:
         side = torch.cuda.Stream(device)
         side.wait_stream(torch.cuda.current_stream(device))
         with torch.cuda.stream(side):
-            rollout()
+            loop.collect()
         torch.cuda.current_stream(device).wait_stream(side)
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            graph_returns = rollout()
+            loop.collect()
         torch.cuda.synchronize(device)
     sampler = ClockSampler(device.index)
     sampler.start()
@@ -626,9 +594,11 @@ def run_rollout(args):
     for k in range(args.steps):
         if graph is not None:
             graph.replay()
-            mean_return = float(graph_returns.mean())               # the learner reads a scalar per rollout
         else:
-            mean_return = float(rollout().mean())
+            loop.collect()
+        if args.update:
+            loop.update()
+        mean_return = float(loop.store.returns.mean())              # the learner reads a scalar per rollout
     e1.record()
     torch.cuda.synchronize(device)
     wall1 = time.time()
@@ -642,12 +612,13 @@ def run_rollout(args):
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "i64+f32 render, bf16 policy",
         "data": "synthetic",
         "config": {"workload": f"c5: {lanes} lanes x {horizon}-step rollouts, 64-sector 8x8 map, {things} things/lane, "
-                               "Nature-CNN policy (PyTorch) in the loop, GAE(0.99, 0.95)",
-                   "producer": "synthetic lane stepper", "l2": "not flushed: the loop's own working set",
+                               "Nature-CNN policy (PyTorch) in the loop, GAE(0.99, 0.95)"
+                               + (", one clipped policy-gradient pass per rollout" if args.update else ""),
+                   "producer": "player kinematics kernel + synthetic things", "l2": "not flushed: the loop's own working set",
                    "cuda_graph": graph is not None},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 4,
                 "note": "one scalar per rollout read by the host; observations stay on the device"},
-        "gpu_launches": 2 * horizon * args.steps, "mean_return": mean_return,
+        "gpu_launches": launches_per_rollout * args.steps, "mean_return": mean_return,
         "clocks": sampler.stop(wall0, wall1),
     }
     print(json.dumps(line), flush=True)
@@ -670,6 +641,7 @@ def main():
     ap.add_argument("--skip-upstream", action="store_true",
                     help="reference arm: time only the C restatement, not the upstream Torch engine")
     ap.add_argument("--no-graph", action="store_true", help="c5 only: launch the rollout eagerly instead of as a CUDA graph")
+    ap.add_argument("--update", action="store_true", help="c5 only: a clipped policy-gradient pass after every rollout")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.workload == "c5":
