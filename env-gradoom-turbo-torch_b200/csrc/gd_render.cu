@@ -89,7 +89,7 @@ struct GdShared {
   int32_t *lane;        /* 32 */
   float *wallDistance;  /* 320 */
   short *blockingWall;  /* 320 */
-  unsigned *ownerMask;  /* 10 words: boundary_has_projected_owner */
+  unsigned *ownerMask;  /* 10 words: boundary_has_projected_owner; words 16..25: columns whose walk goes on after leaving the map */
   GdWall *walls;        /* W */
   GdActor *actors;      /* maxThings */
   unsigned long long *pal64;  /* 256: R | G<<20 | B<<40 */
@@ -114,7 +114,7 @@ __host__ __device__ inline size_t gd_shared_bytes(int W, int maxThings) {
   b += gd_align16(GD_LANE_WORDS * 4);
   b += gd_align16(GD_SW * 4);
   b += gd_align16(GD_SW * 2);
-  b += gd_align16(16 * 4);
+  b += gd_align16(32 * 4);
   b += gd_align16(256 * 8);
   b += gd_align16(64);
   b += gd_align16(14 * GD_SW * 4);
@@ -135,7 +135,7 @@ __device__ inline void gd_carve(uint8_t *base, int W, int maxThings, GdShared &s
   s.lane = (int32_t *)(base + o); o += gd_align16(GD_LANE_WORDS * 4);
   s.wallDistance = (float *)(base + o); o += gd_align16(GD_SW * 4);
   s.blockingWall = (short *)(base + o); o += gd_align16(GD_SW * 2);
-  s.ownerMask = (unsigned *)(base + o); o += gd_align16(16 * 4);
+  s.ownerMask = (unsigned *)(base + o); o += gd_align16(32 * 4);
   s.pal64 = (unsigned long long *)(base + o); o += gd_align16(256 * 8);
   s.misc = (int *)(base + o); o += gd_align16(64);
   s.masks = (unsigned *)(base + o); o += gd_align16(14 * GD_SW * 4);
@@ -232,7 +232,7 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
       if (p.resetMask && !p.resetMask[l]) continue;  /* uniform across the CTA */
     }
     if (tid < GD_LANE_WORDS) sh.lane[tid] = p.lanes[(size_t)l * GD_LANE_WORDS + tid];
-    if (tid < 10) sh.ownerMask[tid] = 0;
+    if (tid < 10) { sh.ownerMask[tid] = 0; sh.ownerMask[16 + tid] = 0; }
     if (tid == 0) sh.misc[1] = 0;
     /* sector of every thing and of the player (slot 64): lowest index that
      * contains the point (engine.py:9598-9617), found by all threads together
@@ -330,6 +330,7 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
         if (isfinite(h.d)) atomicOr(&sh.ownerMask[xl >> 5], 1u << (xl & 31));
       }
     }
+    gd_mark_afterlife_columns(sc, sh);
     {
       float rx, ry, wd;
       int bw;

@@ -607,6 +607,36 @@ __device__ __noinline__ void gd_masked_pass(const GdScene &sc, const GdView &v, 
 
 #define GD_FALLBACK_MAX (8 * GD_SW)
 
+/* A column that has left the map (current sector -1) still takes part in the reference's
+ * vectorised iterations: its decision is made against sector 0 with wall 0 selected at an
+ * infinite distance (engine.py:11561-11588 clamp the sector index).  That decision can only
+ * become a valid crossing through a projected left-edge owner: a wall of sector 0, or a
+ * neighbour of wall 0 at one of its endpoints, whose ray-owned span starts at this very
+ * column (engine.py:11589-11730, 11905-11990, 12005-12072), or through the rules that need
+ * wall 0's projected span to end at this column (engine.py:11930-11962, 12073-12164).  Every
+ * other column draws nothing, records nothing and changes nothing the frame depends on once
+ * it is outside, so its walk can stop there.  This marks the columns that must go on. */
+__device__ void gd_mark_afterlife_columns(const GdScene &sc, const GdShared &sh) {
+  unsigned *busy = sh.ownerMask + 16;
+  const int n0 = sc.secOff[1] - sc.secOff[0];
+  const int nb0 = sc.nbDirect ? 0 : sc.nbOff[0], nb1 = sc.nbDirect ? 2 : sc.nbOff[1];
+  const int total = n0 + (nb1 - nb0) + 1;
+  for (int i = threadIdx.x; i < total; i += GD_THREADS) {
+    int xl;
+    if (i == total - 1) {
+      const i64 sr = sh.walls[0].sr;
+      xl = (sr >= 0 && sr < GD_SW) ? (int)sr : -1;
+    } else {
+      int w = i < n0 ? sc.secWalls[sc.secOff[0] + i]
+                     : (sc.nbDirect ? sc.nbDirectTab[i - n0] : sc.nbIdx[nb0 + (i - n0)]);
+      if (w < 0) continue;                            /* no neighbour at that endpoint */
+      w = GD_CHECK_INDEX(w, sc.W);
+      xl = sh.walls[w].isl;
+    }
+    if (xl >= 0 && xl < GD_SW) atomicOr(&busy[xl >> 5], 1u << (xl & 31));
+  }
+}
+
 __device__ void gd_walk(const GdScene &sc, const GdView &v, const GdShared &sh, GdEvent *events, int *eventCount,
                         const GdRowProj *rowproj, int *status, int startSector) {
   const int x = threadIdx.x;
@@ -626,6 +656,7 @@ __device__ void gd_walk(const GdScene &sc, const GdView &v, const GdShared &sh, 
   c.pendPortalBridgeSector = -1;
   c.pendPortalBridgeExit = 0.0f;
   bool settled = false;
+  const bool stopsOutside = !((sh.ownerMask[16 + (x >> 5)] >> (x & 31)) & 1u);
   int nEvents = 0;
   bool overflow = false;
 
@@ -830,6 +861,7 @@ __device__ void gd_walk(const GdScene &sc, const GdView &v, const GdShared &sh, 
      * state forever; once an iteration changes nothing and draws nothing it can
      * stop. */
     if (before.cur < 0 && !it.rasterValid && !it.pskpp && gd_state_equal(before, c)) settled = true;
+    if (c.cur < 0 && stopsOutside) settled = true;
   }
   eventCount[x] = nEvents < GD_MAX_EVENTS ? nEvents : GD_MAX_EVENTS;
   if (overflow) atomicOr(status, GD_STATUS_EVENT_OVERFLOW);
