@@ -7,7 +7,7 @@ import subprocess
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 SOURCES = ["gd_render.cu"]
-HEADERS = ["gd_device.cuh", "gd_geometry.cuh", "gd_walk.cuh", "gd_flats.cuh", "gd_sprites.cuh", "gd_output.cuh", "gd_abi.cuh", "gd_state.cuh", "gd_state_abi.cuh", "gd_move.cuh",
+HEADERS = ["gd_device.cuh", "gd_geometry.cuh", "gd_walk.cuh", "gd_flats.cuh", "gd_sprites.cuh", "gd_decals.cuh", "gd_output.cuh", "gd_abi.cuh", "gd_state.cuh", "gd_state_abi.cuh", "gd_move.cuh",
            "../../include/gradoom_b200.h", "../../include/gradoom_b200_layout.h"]
 LIBRARY = os.path.join(HERE, "libgradoom_b200.so")
 # the same sources with -DGD_CHECKED: every index taken from the blob or a record is range-tested

@@ -25,6 +25,11 @@ struct gd_renderer {
    * the drawing of the next on this side stream */
   cudaStream_t copyStream;
   cudaEvent_t chunkDone[GD_HOST_CHUNKS], copiesDone;
+  /* gd_renderer_bind_decals: the lanes' decal rings and the renderer's own scratch for them */
+  const gd_decal *decals;
+  int decalSlots;
+  uint8_t *decalScratch;
+  size_t decalScratchBytes;
 };
 
 static const void *gd_section(const uint8_t *dev, const int32_t *h, int s) { return dev + h[GD_HDR_SECTION0 + s]; }
@@ -118,6 +123,11 @@ extern "C" int gd_renderer_create(const void *blob_header_host, const void *blob
   sc.groupH[0] = SECP(float, GD_S_CEIL_GROUP_H); sc.groupOff[0] = SECP(int32_t, GD_S_CEIL_GROUP_OFF);
   sc.groupSec[0] = SECP(int32_t, GD_S_CEIL_GROUP_SEC); sc.groups[0] = h[GD_H_CEIL_GROUPS];
   sc.M = h[GD_H_MASKED_WALLS_N];
+  sc.decals = h[GD_H_DECALS]; sc.decalH = h[GD_H_DECAL_H]; sc.decalW = h[GD_H_DECAL_W];
+  sc.decalInfo = SECP(int32_t, GD_S_DECAL_INFO); sc.wallFine = SECP(int32_t, GD_S_WALL_FINE);
+  sc.decalAtlas = SECP(uint8_t, GD_S_DECAL_ATLAS); sc.decalOpacity = SECP(uint8_t, GD_S_DECAL_OPACITY);
+  sc.decalBlack = SECP(uint8_t, GD_S_DECAL_BLACK);
+  r->decals = nullptr; r->decalSlots = 0; r->decalScratch = nullptr; r->decalScratchBytes = 0;
 #undef SECP
   r->smemBytes = gd_shared_bytes(sc.W, max_things);
   r->secWallsN = h[GD_H_SEC_WALLS_N]; r->vtxWallsN = h[GD_H_VTX_WALLS_N]; r->V = h[GD_H_VERTICES];
@@ -170,8 +180,30 @@ extern "C" void gd_renderer_destroy(gd_renderer *r) {
     if (r->chunkDone[c]) cudaEventDestroy(r->chunkDone[c]);
   if (r->copiesDone) cudaEventDestroy(r->copiesDone);
   if (r->copyStream) cudaStreamDestroy(r->copyStream);
+  if (r->decalScratch) cudaFree(r->decalScratch);
   if (switched) cudaSetDevice(prev);
   delete r;
+}
+
+extern "C" int gd_renderer_bind_decals(gd_renderer *r, const void *decals, int slots) {
+  if (!r) return GD_ERR_NULL;
+  if (!decals) { r->decals = nullptr; r->decalSlots = 0; return GD_OK; }
+  if (slots < 1 || slots > GD_MAX_DECAL_SLOTS) return GD_ERR_SIZE;
+  if ((uintptr_t)decals & 15) return GD_ERR_ALIGN;
+  int current = -1;
+  if (cudaGetDevice(&current) != cudaSuccess) return GD_ERR_CUDA;
+  if (current != r->device) return GD_ERR_DEVICE;
+  const size_t need = (size_t)r->ctas * gd_decal_scratch_per_cta(slots);
+  if (need > r->decalScratchBytes) {
+    if (r->decalScratch) cudaFree(r->decalScratch);      /* waits for work that still uses it */
+    r->decalScratch = nullptr; r->decalScratchBytes = 0;
+    r->decals = nullptr; r->decalSlots = 0;
+    void *mem = nullptr;
+    if (cudaMalloc(&mem, need) != cudaSuccess) { cudaGetLastError(); return GD_ERR_CUDA; }
+    r->decalScratch = (uint8_t *)mem; r->decalScratchBytes = need;
+  }
+  r->decals = (const gd_decal *)decals; r->decalSlots = slots;
+  return GD_OK;
 }
 
 extern "C" size_t gd_renderer_scratch_bytes(const gd_renderer *r) {
@@ -203,6 +235,7 @@ static int gd_launch(const gd_renderer *r, const int32_t *lanes, const gd_thing 
   p.scratch = (uint8_t *)scratch; p.status = status;
   p.queueOffset = (size_t)r->ctas * gd_scratch_per_cta(r->sc.W, r->sc.S);
   p.stageMask = r->stageMask; p.secWallsN = r->secWallsN; p.vtxWallsN = r->vtxWallsN; p.V = r->V;
+  p.decals = r->decals; p.decalSlots = r->decalSlots; p.decalScratch = r->decalScratch;
   int grid = n < r->ctas ? n : r->ctas;
   gd_render_kernel<<<grid, GD_THREADS, r->smemBytes, (cudaStream_t)stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? GD_OK : GD_ERR_CUDA;
@@ -406,6 +439,7 @@ extern "C" int gd_render_step_static(const gd_renderer *r, const int32_t *lanes,
    * loaded and left at zero by every launch */
   p.queueOffset = (size_t)GD_STATIC_MAX_CTAS * GD_STATIC_PER_CTA;
   p.stageMask = r->stageMask; p.secWallsN = r->secWallsN; p.vtxWallsN = r->vtxWallsN; p.V = r->V;
+  p.decals = r->decals; p.decalSlots = r->decalSlots; p.decalScratch = r->decalScratch;
   int grid = n < r->ctas ? n : r->ctas;
   if (grid > GD_STATIC_MAX_CTAS) grid = GD_STATIC_MAX_CTAS;
   gd_render_kernel<<<grid, GD_THREADS, r->smemBytes, (cudaStream_t)stream>>>(p);

@@ -67,6 +67,10 @@ struct GdScene {
   const int32_t *groupOff[2], *groupSec[2];
   int groups[2];
   int M;
+  /* bullet-chip decals: variants (0 = none), atlas slice height / width */
+  int decals, decalH, decalW;
+  const int32_t *decalInfo, *wallFine;
+  const uint8_t *decalAtlas, *decalOpacity, *decalBlack;
 };
 
 /*

@@ -56,6 +56,9 @@ struct GdParams {
   int stageMask;             /* which scene tables each CTA copies into shared memory */
   int secWallsN, vtxWallsN, V;
   int *status;
+  const gd_decal *decals;    /* n x decalSlots rings of bullet chips, or null */
+  int decalSlots;
+  uint8_t *decalScratch;     /* ctas x gd_decal_scratch_per_cta(decalSlots) */
 };
 
 #define GD_SCRATCH_EVENTS_BYTES (GD_MAX_EVENTS * GD_SW * (int)sizeof(GdEvent))
@@ -155,6 +158,7 @@ __device__ inline void gd_carve(uint8_t *base, int W, int maxThings, GdShared &s
 #include "gd_walk.cuh"
 #include "gd_flats.cuh"
 #include "gd_sprites.cuh"
+#include "gd_decals.cuh"
 #include "gd_output.cuh"
 
 /* ---- the kernel ----------------------------------------------------------- */
@@ -370,6 +374,9 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
       gd_masked_pass(sc, v, sh);
       __syncthreads();
     }
+    if (p.decals != nullptr && sc.decals > 0)
+      gd_decals(sc, v, sh, events, eventCount, p.decals + (size_t)l * p.decalSlots, p.decalSlots,
+                p.decalScratch + (size_t)blockIdx.x * gd_decal_scratch_per_cta(p.decalSlots));
     gd_sprites(sc, v, sh, events, eventCount, nThings);
     __syncthreads();
     gd_weapon(sc, sh.lane, sh.frame);

@@ -549,7 +549,9 @@ __device__ __noinline__ void gd_masked_pass(const GdScene &sc, const GdView &v, 
     GdHit h = gd_hit_slow(sc, v, sh.walls, k, x, rx, ry);
     if (h.proj && h.d < best) { best = h.d; w = k; side = sd; texId = t; leftEdge = h.left; }
   }
-  if (!isfinite(best)) return;
+  /* what this column drew, for the decal layer's depth test: the crossing's distance in
+   * maskedDist (infinite: nothing), first row | end row << 8 in maskedInfo */
+  if (!isfinite(best)) { sh.maskedDist[x] = GD_INF; return; }
   const GdWall &wv = sh.walls[w];
   const int front = gd_wsec(sc, w * 2), back = gd_wsec(sc, w * 2 + 1) < 0 ? 0 : gd_wsec(sc, w * 2 + 1);
   const int lightSector = side == 0 ? front : back;
@@ -591,7 +593,7 @@ __device__ __noinline__ void gd_masked_pass(const GdScene &sc, const GdView &v, 
   const i64 fracEnd = fracStart + gd_wmul(clippedBottom - clippedTop - 1, dcIscale);
   if (clippedTop < clippedBottom && clippedBottom < floorClip && fracEnd < (i64)th * GD_FU - dcIscale)
     clippedBottom += 1;
-  if (!(hasSaved || leftEdge)) return;
+  if (!(hasSaved || leftEdge)) { sh.maskedDist[x] = GD_INF; return; }
   const float *wl = &sc.walls[w * 4];
   const bool horizontal = fabsf(wl[3] - wl[1]) < 1e-6f, vertical = fabsf(wl[2] - wl[0]) < 1e-6f;
   const i64 light = gd_sec_info(sc, lightSector).x + v.flashLight * 16 + (vertical ? 16 : (horizontal ? -16 : 0));
@@ -600,9 +602,12 @@ __device__ __noinline__ void gd_masked_pass(const GdScene &sc, const GdView &v, 
   const uint8_t *col = sc.texAtlasCol + ((size_t)texId * sc.texW + u) * sc.texH;
   const unsigned base = (unsigned)(gd_shl(texMid, 16 - hbits) + (gd_wmul(vstep, GD_FU - v.center) >> 16));
   const unsigned step = (unsigned)vstep;
+  const int rowA = (int)gd_max(clippedTop, 0), rowB = (int)gd_min(clippedBottom, GD_VH);
 #pragma unroll 1
-  for (int y = (int)gd_max(clippedTop, 0); y < (int)gd_min(clippedBottom, GD_VH); ++y)
+  for (int y = rowA; y < rowB; ++y)
     sh.frame[y * GD_SW + x] = cm[col[(base + (unsigned)y * step) >> (32 - hbits)]];
+  sh.maskedDist[x] = rowA < rowB ? best : GD_INF;
+  sh.maskedInfo[x] = (unsigned)max(rowA, 0) | ((unsigned)max(rowB, 0) << 8);
 }
 
 #define GD_FALLBACK_MAX (8 * GD_SW)

@@ -171,6 +171,11 @@ class EngineStateProducer:
         dev = renderer.device
         self._lanes = torch.zeros((self.num_envs, gdstate.LANE_WORDS), dtype=torch.int32, device=dev)
         self._things = torch.zeros((self.num_envs, max(self.max_things, 1), 4), dtype=torch.int32, device=dev)
+        # the engine's bullet-chip rings (src/gradoom/engine.py:1870-1884), when it keeps any
+        self._decals = None
+        if hasattr(self.engine, "hitscan_decal_serial"):
+            self._decals = gdstate.decal_records(self.engine).to(dev).contiguous()
+            renderer.bind_decals(self._decals)
 
     def render_inputs(self):
         """Lane and thing records of the engine's present state, packed on the
@@ -179,6 +184,8 @@ class EngineStateProducer:
         if self.renderer is None:
             raise RuntimeError("bind_renderer() must be called before render_inputs()")
         self.renderer.pack_state(self.state.refresh(), self._lanes, self._things)
+        if self._decals is not None:
+            gdstate.decal_records(self.engine, out=self._decals)
         return self._lanes, self._things
 
 

@@ -28,7 +28,7 @@ EXPORTS = (
     "gd_error_string", "gd_renderer_create", "gd_renderer_destroy", "gd_renderer_scratch_bytes",
     "gd_renderer_ctas", "gd_renderer_shared_bytes", "gd_render_step", "gd_render_reset", "gd_render_frames",
     "gd_render_step_frames", "gd_render_step_host", "gd_render_step_ring", "gd_render_reset_ring", "gd_static_scratch_bytes", "gd_static_max_walls", "gd_render_step_static",
-    "gd_pack_state_scratch_bytes", "gd_pack_state", "gd_player_tics",
+    "gd_pack_state_scratch_bytes", "gd_pack_state", "gd_player_tics", "gd_renderer_bind_decals",
 )
 
 _libs = {}
@@ -87,6 +87,8 @@ def load(checked: bool = False) -> ctypes.CDLL:
         lib.gd_pack_state.argtypes = [vp, vp, vp, vp, vp, sz, vp, vp]
         lib.gd_player_tics.restype = ci
         lib.gd_player_tics.argtypes = [vp, vp, vp, vp, ci, ci, ci, vp, vp, vp]
+        lib.gd_renderer_bind_decals.restype = ci
+        lib.gd_renderer_bind_decals.argtypes = [vp, vp, ci]
         _libs[path] = lib
     return _libs[path]
 
@@ -133,6 +135,26 @@ class Renderer:
         self.ctas = int(self.lib.gd_renderer_ctas(handle))
         self.shared_bytes = int(self.lib.gd_renderer_shared_bytes(handle))
         self.launches = 0
+        self._decals = None
+
+    def bind_decals(self, decals: torch.Tensor | None) -> None:
+        """The lanes' bullet-chip rings for every later render call: ``(N, slots, 4) int32`` on the
+        renderer's device, each record a ``gd_decal`` (serial, wall | style << 16, along and z as
+        float bits; ``state.decal_records`` builds it), or None to unbind.  The tensor is kept alive
+        by the renderer; lane ``l`` of a render call reads ring ``l``."""
+
+        if decals is None:
+            _check(self.lib.gd_renderer_bind_decals(self.handle, None, 0), "gd_renderer_bind_decals")
+            self._decals = None
+            return
+        if decals.dtype != torch.int32 or decals.dim() != 3 or decals.shape[2] != 4 or not decals.is_contiguous():
+            raise ValueError("decals must be a contiguous (N, slots, 4) int32 tensor of gd_decal records")
+        if decals.device != self.device:
+            raise TypeError("the decal rings must live on the renderer's device")
+        with torch.cuda.device(self.device):
+            _check(self.lib.gd_renderer_bind_decals(self.handle, decals.data_ptr(), int(decals.shape[1])),
+                   "gd_renderer_bind_decals")
+        self._decals = decals
 
     def close(self) -> None:
         if getattr(self, "handle", None):

@@ -124,6 +124,7 @@ class GridSpec:
     hud: bool = True
     weapon: bool = True
     items: int = 0               # map items (pickups) at seeded positions, cycling through the animated kinds
+    decals: bool = False         # carry bullet-chip decal bitmaps and their blend tables
 
 
 # The five workloads of the benchmark definition, by name.
@@ -143,6 +144,12 @@ GRID_CONFIGS = {
     # c1 with twelve map items, for the parity tests of the state packer
     "c1i": GridSpec(rows=4, cols=4, room=256.0, seed=1, wall_textures=8, flats=4,
                     floor_max=64, items=12),
+    # c1 and a quarter-size c4 (diagonal lines) with bullet-chip decal bitmaps, for the parity tests
+    # of the decal layer
+    "c1d": GridSpec(rows=4, cols=4, room=256.0, seed=1, wall_textures=8, flats=4,
+                    floor_max=64, decals=True),
+    "c4d": GridSpec(rows=8, cols=8, room=128.0, seed=4, wall_textures=16,
+                    tex_w=128, tex_h=128, flats=8, floor_max=128, diagonals=True, decals=True),
 }
 
 
@@ -167,6 +174,34 @@ def _sprite_patches(rng, count, w, h):
 
 
 _ITEM_KINDS = (2014, 2015, 2018, 2019, 2011, 2012, 2007, 2001)   # both bonuses, both armours, four still pickups
+
+
+def decal_opacity_lut() -> np.ndarray:
+    """(32, 256) opacity of a chip texel under each wall shade: ZDoom's shaded-decal table for a
+    `translucent 0.85` decal, alpha level 13 of 16 (definition: src/gradoom/scenario.py:260-268)."""
+
+    texel = np.arange(256, dtype=np.int64)
+    shade = np.arange(32, dtype=np.int64)[:, None]
+    alpha = (32 - shade) * 256 // 32 * 13
+    return np.minimum(((texel + 2) * alpha + 256) >> 14, 64).astype(np.uint8)
+
+
+def _synthetic_decals(spec: GridSpec, colormap: np.ndarray) -> dict:
+    """Five seeded grayscale chips, seven texels wide and five to nine tall, with holes, and the two
+    blend tables: the opacity table by its definition, the darkening table from the scene's own
+    colormap (opacity 0 leaves a colour alone, 64 takes it to the darkest row)."""
+
+    rng = np.random.default_rng(spec.seed + 3000)
+    heights = np.asarray((9, 7, 8, 5, 6), dtype=np.int32)
+    atlas = np.zeros((5, 9, 7), dtype=np.uint8)
+    for i, h in enumerate(heights):
+        chip = rng.integers(1, 256, size=(h, 7)).astype(np.uint8)
+        chip[rng.random((h, 7)) < 0.25] = 0
+        atlas[i, :h] = chip
+    rows = (np.arange(65) * 31) // 64
+    return {"atlas": atlas, "heights": heights, "left": np.asarray((3, 4, 3, 2, 3), dtype=np.int32),
+            "top": np.asarray((4, 3, 4, 2, 3), dtype=np.int32), "opacity_lut": decal_opacity_lut(),
+            "black_lut": np.ascontiguousarray(colormap[rows]).astype(np.uint8)}
 
 
 def _scene_meta(spec: GridSpec, static_ids, patches) -> dict:
@@ -431,7 +466,7 @@ def make_grid_scene(spec: GridSpec) -> Scene:
         hud_heights=hud_heights,
         hud_left=hud_left,
         hud_top=hud_top,
-        meta=_scene_meta(spec, None, P),
+        meta=dict(_scene_meta(spec, None, P), **({"decals": _synthetic_decals(spec, colormap)} if spec.decals else {})),
     )
 
 
@@ -469,6 +504,13 @@ def from_compiled_scenario(cs) -> Scene:
     if len(item_types):
         meta["items"] = {"spawns": np.asarray(cs.item_spawns, dtype=np.float32), "types": item_types.astype(np.int32),
                          "anim_ids": maybe("raw_item_animation_sprite_ids", np.zeros(8, np.int32)).astype(np.int32)}
+    if getattr(cs, "bullet_decal_atlas", None) is not None:
+        meta["decals"] = {"atlas": need("bullet_decal_atlas").astype(np.uint8),
+                          "heights": need("bullet_decal_heights").astype(np.int32),
+                          "left": need("bullet_decal_left_offsets").astype(np.int32),
+                          "top": need("bullet_decal_top_offsets").astype(np.int32),
+                          "opacity_lut": need("bullet_decal_opacity_lut").astype(np.uint8),
+                          "black_lut": need("bullet_decal_black_lut").astype(np.uint8)}
     return Scene(
         walls=need("wall_segments").astype(np.float32), wall_sectors=need("wall_sectors").astype(np.int32),
         side_textures=need("wall_side_texture_ids").astype(np.int32),
@@ -519,14 +561,15 @@ def from_compiled_scenario(cs) -> Scene:
 # ---------------------------------------------------------------------------
 
 GD_MAGIC = 0x4744424C
-GD_VERSION = 10
-GD_HDR_WORDS = 128
+GD_VERSION = 11
+GD_HDR_WORDS = 160
 GD_HDR_SECTION0 = 48
 
 _HEADER_WORDS = (
     "MAGIC VERSION BYTES WALLS SECTORS VERTICES TEXTURES TEX_H TEX_W SPRITES SPR_H SPR_W "
     "WPN_PATCHES WPN_H WPN_W WPN_TICS STARTS DEATH_FRAMES XDEATH_FRAMES BLOCKING NB_DIRECT "
-    "WPN_AVAILABLE HUD_PATCHES UNSUPPORTED SEC_WALLS_N VTX_WALLS_N MASKED_WALLS_N FLOOR_GROUPS CEIL_GROUPS ITEMS"
+    "WPN_AVAILABLE HUD_PATCHES UNSUPPORTED SEC_WALLS_N VTX_WALLS_N MASKED_WALLS_N FLOOR_GROUPS CEIL_GROUPS ITEMS "
+    "DECALS DECAL_H DECAL_W"
 ).split()
 H = {name: i for i, name in enumerate(_HEADER_WORDS)}
 
@@ -540,12 +583,33 @@ _SECTIONS = (
     "WPN_ATLAS WPN_OPAQUE WPN_FRAME_IDS WPN_FLASH_IDS WPN_FLASH_LIGHTS HUD_INFO HUD_ATLAS "
     "HUD_OPAQUE FINESINE FINETAN STARTS RAY_OFFSETS RAY_COSCORR TEX_ATLAS_COL SECTOR_BBOX "
     "MASKED_WALLS DAMAGE_ALPHA FLOOR_GROUP_H FLOOR_GROUP_OFF FLOOR_GROUP_SEC CEIL_GROUP_H CEIL_GROUP_OFF "
-    "CEIL_GROUP_SEC ITEM_POS ITEM_INFO ITEM_ANIM"
+    "CEIL_GROUP_SEC ITEM_POS ITEM_INFO ITEM_ANIM DECAL_INFO DECAL_ATLAS DECAL_OPACITY DECAL_BLACK WALL_FINE"
 ).split()
 SEC = {name: i for i, name in enumerate(_SECTIONS)}
 
 FIXED_UNIT = 1 << 16
 FINE_ANGLES = 8192
+
+
+def wall_fine_angles(walls: np.ndarray) -> np.ndarray:
+    """(W, 2) fine-angle index of each wall's direction as seen from side 0 and from side 1
+    (the direction reversed): atan2 of the float32 wall vector, wrapped to [0, 2 pi) and quantised
+    to 8192 steps (src/gradoom/engine.py:2153-2165, 13818-13830).  Evaluated with torch's float32
+    kernels, the arithmetic the reference itself runs, so that a direction on a step boundary
+    (every multiple of 45 degrees is one) lands on the same side."""
+
+    import math
+    import torch
+
+    w = torch.from_numpy(np.ascontiguousarray(walls, dtype=np.float32))
+    vec = w[:, 2:] - w[:, :2]
+    out = np.zeros((len(walls), 2), dtype=np.int32)
+    for side in (0, 1):
+        oriented = vec if side == 0 else -vec
+        angle = torch.atan2(oriented[:, 1], oriented[:, 0])
+        index = torch.floor(torch.remainder(angle, 2.0 * math.pi) * (FINE_ANGLES / (2.0 * math.pi))).to(torch.int64)
+        out[:, side] = (index & (FINE_ANGLES - 1)).numpy()
+    return out
 
 
 def fine_sine_table() -> np.ndarray:
@@ -761,6 +825,24 @@ def pack_scene(scene: Scene, ray_table_override=None) -> np.ndarray:
     def info4(a, b, c, d):
         return np.stack((a, b, c, d), axis=1).astype(np.int32)
 
+    # Bullet-chip decals (src/gradoom/scenario.py:280-300, engine.py:1038-1068): an optional
+    # meta["decals"] = {"atlas": (V,h,w) u8, "heights", "left", "top": (V,), "opacity_lut": (32,256),
+    # "black_lut": (65,256)}.  Without it the decal layer draws nothing, as the reference's zero atlas.
+    decals = scene.meta.get("decals")
+    n_decals = 0 if decals is None else len(decals["heights"])
+    decal_atlas = np.zeros((1, 1, 1), dtype=np.uint8) if decals is None else np.asarray(decals["atlas"], dtype=np.uint8)
+    decal_info = np.zeros((max(n_decals, 1), 4), dtype=np.int32)
+    decal_opacity = np.zeros((32, 256), dtype=np.uint8)
+    decal_black = np.broadcast_to(np.arange(256, dtype=np.uint8), (65, 256)).copy()
+    if n_decals:
+        if decal_atlas.ndim != 3 or len(decal_atlas) != n_decals:
+            raise ValueError("the decal atlas must hold one (h, w) slice per chip variant")
+        decal_info[:, 0] = decals["heights"]
+        decal_info[:, 1] = decals["left"]
+        decal_info[:, 2] = decals["top"]
+        decal_opacity = np.asarray(decals["opacity_lut"], dtype=np.uint8).reshape(32, 256)
+        decal_black = np.asarray(decals["black_lut"], dtype=np.uint8).reshape(65, 256)
+
     # Map items (pickups placed by the map; src/gradoom/engine.py:1084-1088, 2077-2081): an optional
     # meta["items"] = {"spawns": (I,3) x y z-above-floor, "types": (I,) editor ids, "anim_ids": (8,)}.
     items = scene.meta.get("items")
@@ -851,6 +933,8 @@ def pack_scene(scene: Scene, ray_table_override=None) -> np.ndarray:
         "FLOOR_GROUP_H": floor_groups[0], "FLOOR_GROUP_OFF": floor_groups[1], "FLOOR_GROUP_SEC": floor_groups[2],
         "CEIL_GROUP_H": ceil_groups[0], "CEIL_GROUP_OFF": ceil_groups[1], "CEIL_GROUP_SEC": ceil_groups[2],
         "ITEM_POS": item_pos, "ITEM_INFO": item_info, "ITEM_ANIM": item_anim,
+        "DECAL_INFO": decal_info, "DECAL_ATLAS": decal_atlas, "DECAL_OPACITY": decal_opacity,
+        "DECAL_BLACK": decal_black, "WALL_FINE": wall_fine_angles(walls),
     }
     assert set(sections) == set(SEC), set(SEC) ^ set(sections)
 
@@ -901,6 +985,9 @@ def pack_scene(scene: Scene, ray_table_override=None) -> np.ndarray:
     header[H["FLOOR_GROUPS"]] = int(floor_groups[0].size)
     header[H["CEIL_GROUPS"]] = int(ceil_groups[0].size)
     header[H["ITEMS"]] = n_items
+    header[H["DECALS"]] = n_decals
+    header[H["DECAL_H"]] = decal_atlas.shape[1]
+    header[H["DECAL_W"]] = decal_atlas.shape[2]
     blob = np.concatenate([header.view(np.uint8)] + chunks)
     assert blob.size == cursor
     return blob

@@ -219,6 +219,23 @@ def player_records(src) -> torch.Tensor:
     return out
 
 
+def decal_records(src, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``(N, slots, 4) int32`` decal rings (``gd_decal``: serial, wall | style << 16, along, z) from an
+    object that carries the reference engine's ``hitscan_decal_*`` tensors
+    (src/gradoom/engine.py:1870-1884).  With ``out`` the records are written in place (five
+    elementwise launches, no host synchronisation), so a bound ring buffer follows the engine."""
+
+    serial = src.hitscan_decal_serial
+    if out is None:
+        out = torch.empty((*serial.shape, 4), dtype=torch.int32, device=serial.device)
+    out[..., 0] = serial.to(torch.int32)
+    wall = src.hitscan_decal_wall.to(torch.int32) & 0xFFFF
+    out[..., 1] = wall | (src.hitscan_decal_style.to(torch.int32) << 16)
+    out[..., 2] = _f32_bits(src.hitscan_decal_along)
+    out[..., 3] = _f32_bits(src.hitscan_decal_z)
+    return out
+
+
 def _f32_bits(t: torch.Tensor) -> torch.Tensor:
     return t.to(torch.float32).contiguous().view(torch.int32)
 

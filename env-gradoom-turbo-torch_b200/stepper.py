@@ -96,6 +96,51 @@ def random_lanes(sc: gdscene.Scene, n: int, k_things: int, seed: int, max_things
     return lanes, things
 
 
+def random_decals(sc: gdscene.Scene, lanes: np.ndarray, per_lane: int, slots: int, seed: int) -> np.ndarray:
+    """Seeded bullet chips for every lane: ``(n, slots, 4) int32`` ``gd_decal`` rings.  Most chips sit
+    where a ray through the lane's view meets the nearest line, on the viewer's side of it (what a
+    hitscan impact leaves, src/gradoom/engine.py:6257-6340); a few are on the far side or on lines
+    elsewhere.  Serials ascend in shuffled slot order; the other slots are free."""
+
+    rng = np.random.default_rng(seed)
+    n = lanes.shape[0]
+    lf = lanes.view(np.float32)
+    walls = sc.walls.astype(np.float64)
+    sx, sy = walls[:, 0], walls[:, 1]
+    ex, ey = walls[:, 2] - sx, walls[:, 3] - sy
+    out = np.zeros((n, slots, 4), dtype=np.int32)
+    out[:, :, 0] = -1
+    of = out.view(np.float32)
+    for lane in range(n):
+        px, py, ang = float(lf[lane, gdstate.L_X]), float(lf[lane, gdstate.L_Y]), float(lf[lane, gdstate.L_ANGLE])
+        where = rng.permutation(slots)[:per_lane]
+        for i, slot in enumerate(where):
+            if rng.random() < 0.85:
+                a = ang + rng.uniform(-0.75, 0.75)
+                rx, ry = np.cos(a), np.sin(a)
+                den = rx * ey - ry * ex
+                ok = np.abs(den) > 1e-9
+                den = np.where(ok, den, 1.0)
+                dist = ((sx - px) * ey - (sy - py) * ex) / den
+                t = ((sx - px) * ry - (sy - py) * rx) / den
+                dist = np.where(ok & (dist > 1e-3) & (t >= 0) & (t <= 1), dist, np.inf)
+                w = int(np.argmin(dist))
+                if not np.isfinite(dist[w]):
+                    continue
+                along = float(t[w])
+            else:
+                w, along = int(rng.integers(0, len(walls))), float(rng.random())
+            side = int(ex[w] * (py - sy[w]) - ey[w] * (px - sx[w]) > 0)
+            if rng.random() < 0.1:
+                side = 1 - side
+            style = int(rng.integers(0, 5)) + 5 * int(rng.integers(0, 2)) + 10 * int(rng.integers(0, 2)) + 20 * side
+            out[lane, slot, 0] = 1000 + i
+            out[lane, slot, 1] = (w & 0xFFFF) | (style << 16)
+            of[lane, slot, 2] = np.float32(along)
+            of[lane, slot, 3] = np.float32(rng.uniform(-8.0, 200.0))
+    return out
+
+
 def advance(sc: gdscene.Scene, lanes: np.ndarray, seed: int, turn_bam: int = 640 << 16, move: float = 6.0):
     """Turn every player a little and move it forward inside its room (numpy, in place)."""
 

@@ -69,6 +69,23 @@ int gd_renderer_create(const void *blob_header_host, const void *blob_dev, size_
                        int max_things, gd_renderer **out);
 void gd_renderer_destroy(gd_renderer *r);
 
+/*
+ * Bullet-chip decals.  Replaces: _native_render_hitscan_decals
+ * (src/gradoom/engine.py:13747-13991), the layer between the walls and the sprites.
+ * `decals` is a device array of n x slots gd_decal records (16-byte aligned,
+ * 1 <= slots <= GD_MAX_DECAL_SLOTS): lane l of every later render call reads
+ * records [l * slots, (l + 1) * slots), the engine's per-lane ring
+ * (hitscan_decal_serial / _wall / _along / _z / _style, engine.py:1870-1884) packed
+ * as gd_decal.  The array must stay alive and hold at least as many lanes as the
+ * calls draw.  NULL unbinds.  The layer draws only when the scene blob carries
+ * decal bitmaps (GD_H_DECALS > 0).  The call may allocate (the renderer keeps its
+ * own projection scratch, slots * 34 bytes per CTA) and must not overlap with
+ * render calls of the same renderer; the render calls themselves stay allocation
+ * free.  Pixels the flat fallback layer alone filled (rows no seg and no visplane
+ * claimed) are never shaded by a chip.
+ */
+int gd_renderer_bind_decals(gd_renderer *r, const void *decals, int slots);
+
 /* Scratch the caller must provide to every render call: clip events of the
  * lanes being drawn plus, in its last 16 bytes, the kernel's lane queue.  Zero
  * the buffer once after allocating it; every launch leaves the queue at zero.

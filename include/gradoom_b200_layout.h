@@ -14,8 +14,8 @@
 #include <stdint.h>
 
 #define GD_MAGIC 0x4744424C /* "GDBL" */
-#define GD_VERSION 10
-#define GD_HDR_WORDS 128
+#define GD_VERSION 11
+#define GD_HDR_WORDS 160
 #define GD_HDR_SECTION0 48
 
 /* view constants (src/gradoom/engine.py:1484-1487) */
@@ -57,6 +57,9 @@ enum gd_header_word {
   GD_H_FLOOR_GROUPS, /* distinct floor heights */
   GD_H_CEIL_GROUPS,  /* distinct ceiling heights */
   GD_H_ITEMS,        /* map items (pickups placed by the map) */
+  GD_H_DECALS,       /* bullet-chip variants (0: the scene carries no decal bitmaps) */
+  GD_H_DECAL_H,      /* atlas slice height */
+  GD_H_DECAL_W,      /* atlas slice width = the width of every chip */
   GD_H_COUNT
 };
 
@@ -137,6 +140,12 @@ enum gd_section {
   GD_S_ITEM_POS,        /* items x 4 f32: x y z (floor of its sector + spawn height) 0 */
   GD_S_ITEM_INFO,       /* items x 2 i32: editor type id, sprite patch of its resting frame */
   GD_S_ITEM_ANIM,       /* 8 i32: bonus / armour animation frames (src/gradoom/engine.py:14258-14317) */
+  GD_S_DECAL_INFO,      /* variants x 4 i32: height, left offset, top offset, 0 (src/gradoom/scenario.py:280-300) */
+  GD_S_DECAL_ATLAS,     /* variants x h x w u8 grayscale chips, 0 = transparent */
+  GD_S_DECAL_OPACITY,   /* 32 x 256 u8 [wall shade][chip texel] -> opacity 0..64 (src/gradoom/scenario.py:260-268) */
+  GD_S_DECAL_BLACK,     /* 65 x 256 u8 [opacity][palette index] -> darkened palette index (scenario.py:269-272) */
+  GD_S_WALL_FINE,       /* W x 2 i32: fine angle (0..8191) of the wall's direction seen from side 0 / side 1,
+                           the tangent a chip on that side is laid out along (src/gradoom/engine.py:13818-13830) */
   GD_S_COUNT
 };
 
@@ -226,5 +235,20 @@ typedef struct gd_thing {
 
 #define GD_THING_ALIVE 1
 #define GD_THING_BRIGHT 2
+
+/*
+ * Decal record: 16 bytes.  One per slot of a lane's ring of bullet-chip decals
+ * (src/gradoom/engine.py:1870-1884, written by 6257-6340).  A slot is in use when
+ * serial >= 0; the chips of a lane are painted in ascending serial order.
+ */
+typedef struct gd_decal {
+  int32_t serial;   /* hitscan_decal_serial, -1 = free slot */
+  int16_t wall;     /* hitscan_decal_wall (clamped to the wall table when read) */
+  uint16_t style;   /* hitscan_decal_style: variant + 5 * flip_x + 10 * flip_y + 20 * side */
+  float along;      /* hitscan_decal_along: position of the impact on the wall, 0..1 */
+  float z;          /* hitscan_decal_z: height of the impact */
+} gd_decal;
+#define GD_DECAL_SCALE 0.5f        /* map units per chip texel (src/gradoom/engine.py:133) */
+#define GD_MAX_DECAL_SLOTS 1024    /* slots per lane the renderer accepts (src/gradoom/engine.py:132) */
 
 #endif

@@ -83,6 +83,9 @@ typedef struct {
   const int32_t *fineSine, *fineTan;
   const float *starts;
   const float *rayOffsets, *rayCosCorr;
+  int decals, decalH, decalW;
+  const int32_t *decalInfo, *wallFine;
+  const uint8_t *decalAtlas, *decalOpacity, *decalBlack;
 } Scene;
 
 static const void *sec_ptr(const uint8_t *blob, int s) {
@@ -177,6 +180,14 @@ static int scene_open(Scene *sc, const uint8_t *blob) {
   sc->starts = sec_ptr(blob, GD_S_STARTS);
   sc->rayOffsets = sec_ptr(blob, GD_S_RAY_OFFSETS);
   sc->rayCosCorr = sec_ptr(blob, GD_S_RAY_COSCORR);
+  sc->decals = h[GD_H_DECALS];
+  sc->decalH = h[GD_H_DECAL_H];
+  sc->decalW = h[GD_H_DECAL_W];
+  sc->decalInfo = sec_ptr(blob, GD_S_DECAL_INFO);
+  sc->decalAtlas = sec_ptr(blob, GD_S_DECAL_ATLAS);
+  sc->decalOpacity = sec_ptr(blob, GD_S_DECAL_OPACITY);
+  sc->decalBlack = sec_ptr(blob, GD_S_DECAL_BLACK);
+  sc->wallFine = sec_ptr(blob, GD_S_WALL_FINE);
   return 0;
 }
 
@@ -661,6 +672,9 @@ typedef struct {
   uint8_t filled[VH * SW];
   int16_t planeSector[VH * SW];
   uint8_t planeIsFloor[VH * SW];
+  /* depth of the surface every pixel shows (engine.py:11551-11553, 12872, 13412, 13740): what a
+   * decal is tested against */
+  float sceneDepth[VH * SW];
   SpriteClip clip;
   /* nearest raster-valid two-sided crossing with a middle texture, per column
    * (engine.py:11573-11579, 12914-12939) */
@@ -1016,6 +1030,7 @@ static void wall_pass(const Scene *sc, const View *v, const LaneGeom *g, LaneBuf
             int shade = wall_shade(light, tail ? firstVis : it->vis);
             lb->frame[y * SW + x] = sc->colormap[shade * 256 + texel];
             lb->filled[y * SW + x] = 1;
+            lb->sceneDepth[y * SW + x] = it->distance;
             if (it->distance < lb->clip.depth[y * SW + x]) {
               lb->clip.depth[y * SW + x] = it->distance;
               lb->clip.wall[y * SW + x] = wallIndex;
@@ -1170,6 +1185,7 @@ static int sector_at(const Scene *sc, float px, float py);
 typedef struct {
   uint8_t resolved[VH * SW];
   int16_t sector[VH * SW];
+  float depth[VH * SW];     /* engine.py:11136-11170: ray depth, or the repaired span's plane depth */
 } FlatLayer;
 
 static void flat_layer(const Scene *sc, const View *v, int currentSector, FlatLayer *fl) {
@@ -1208,6 +1224,7 @@ static void flat_layer(const Scene *sc, const View *v, int currentSector, FlatLa
       unresolved[i] = !isfinite(best);
       floorPx[i] = (uint8_t)isFloor;
       fl->sector[i] = (int16_t)bestSector;
+      fl->depth[i] = isfinite(best) ? best * cc : INFINITY;
     }
   }
   /* vertical repair: the next resolved row below of the same orientation */
@@ -1246,13 +1263,21 @@ static void flat_layer(const Scene *sc, const View *v, int currentSector, FlatLa
       int i = y * SW + x;
       if (!unresolved[i] || left[x] < 0 || right[x] >= SW) continue;
       int ls = fl->sector[y * SW + left[x]], rs = fl->sector[y * SW + right[x]];
-      if (ls == rs) repaired[i] = (int16_t)ls;
+      if (ls == rs) { repaired[i] = (int16_t)ls; vspan[i] = 1; }
     }
   }
   memcpy(fl->sector, repaired, sizeof(int16_t) * VH * SW);
+  for (int i = 0; i < VH * SW; ++i) {
+    if (!vspan[i]) continue;               /* a vertically or horizontally repaired pixel */
+    int y = i / SW, sector = fl->sector[i];
+    float ph = floorPx[i] ? (v->viewZ - sc->secF[sector * 2]) : (sc->secF[sector * 2 + 1] - v->viewZ);
+    fl->depth[i] = ph * 192.0f / fmaxf(fabsf((float)y - center), 0.5f);
+  }
   for (int i = 0; i < VH * SW; ++i) fl->resolved[i] = floorPx[i];  /* reused: 1 = floor pixel */
   free(repaired); free(unresolved); free(floorPx); free(vspan); free(anchor);
 }
+
+static float plane_depth(const Scene *sc, const View *v, int sector, int isFloor, int y);
 
 static void plane_pass(const Scene *sc, const View *v, LaneBuffers *lb, int *unownedPixels) {
   int unowned = 0;
@@ -1260,8 +1285,10 @@ static void plane_pass(const Scene *sc, const View *v, LaneBuffers *lb, int *uno
     for (int x = 0; x < SW; ++x) {
       int i = y * SW + x;
       if (lb->filled[i]) continue;
-      if (lb->planeSector[i] >= 0) lb->frame[i] = plane_pixel(sc, v, lb->planeSector[i], lb->planeIsFloor[i], x, y);
-      else { lb->frame[i] = 0; unowned++; }
+      if (lb->planeSector[i] >= 0) {
+        lb->frame[i] = plane_pixel(sc, v, lb->planeSector[i], lb->planeIsFloor[i], x, y);
+        lb->sceneDepth[i] = plane_depth(sc, v, lb->planeSector[i], lb->planeIsFloor[i], y);
+      } else { lb->frame[i] = 0; lb->sceneDepth[i] = INFINITY; unowned++; }
     }
   if (unowned) {
     /* pixels no seg claimed show the per-pixel fallback layer */
@@ -1270,8 +1297,10 @@ static void plane_pass(const Scene *sc, const View *v, LaneBuffers *lb, int *uno
     for (int y = 0; y < VH; ++y)
       for (int x = 0; x < SW; ++x) {
         int i = y * SW + x;
-        if (!lb->filled[i] && lb->planeSector[i] < 0)
+        if (!lb->filled[i] && lb->planeSector[i] < 0) {
           lb->frame[i] = plane_pixel(sc, v, fl->sector[i], fl->resolved[i], x, y);
+          lb->sceneDepth[i] = fl->depth[i];
+        }
       }
     free(fl);
   }
@@ -1356,6 +1385,7 @@ static void masked_pass(const Scene *sc, const View *v, const LaneGeom *g, LaneB
       i64 tv = (frac & U32MASK) >> (32 - hbits);
       uint8_t texel = sc->texAtlas[((size_t)texId * sc->texH + tv) * sc->texW + u];
       lb->frame[y * SW + x] = sc->colormap[shade * 256 + texel];
+      lb->sceneDepth[y * SW + x] = best;
     }
   }
 }
@@ -1434,6 +1464,112 @@ static float plane_depth(const Scene *sc, const View *v, int sector, int isFloor
   float ph = isFloor ? (v->viewZ - sec_floor(sc, sector)) : (sec_ceil(sc, sector) - v->viewZ);
   float den = fmaxf(fabsf((float)y - flatCenter), 0.5f);
   return ph * 192.0f / den;
+}
+
+
+/* ---- bullet-chip decals (engine.py:13747-13991) --------------------------------
+ * The chips of a lane, oldest first, are shaded onto the wall pixels whose surface
+ * depth equals the chip's own ray depth.  `decals` is the lane's ring of `slots`
+ * records; a slot with serial < 0 is free. */
+static void decal_pass(const Scene *sc, const View *v, const LaneGeom *g, LaneBuffers *lb, const gd_decal *decals,
+                       int slots) {
+  if (!decals || slots <= 0 || sc->decals <= 0) return;
+  int *order = malloc(sizeof(int) * (size_t)slots);
+  int n = 0;
+  for (int s = 0; s < slots; ++s)
+    if (decals[s].serial >= 0) order[n++] = s;
+  /* ascending serial (engine.py:13763-13775); serials of a lane are distinct */
+  for (int i = 1; i < n; ++i) {
+    int s = order[i], j = i - 1;
+    while (j >= 0 && decals[order[j]].serial > decals[s].serial) { order[j + 1] = order[j]; --j; }
+    order[j + 1] = s;
+  }
+  const i64 ti = iclamp((ANG90 - v->pitchBam) >> 19, 0, 4095);
+  const i64 offFixed = ((i64)sc->fineTan[ti] * 12582912LL) >> 16;   /* round(192 * 65536) */
+  const float center = 104.0f + (float)offFixed / 65536.0f;        /* engine.py:13785-13789 */
+  const float width = (float)sc->decalW;
+  for (int k = 0; k < n; ++k) {
+    const gd_decal *d = &decals[order[k]];
+    int w = (int)iclamp(d->wall, 0, sc->W - 1);
+    int style = d->style;
+    int variant = style % 5, flipX = (style / 5) % 2, flipY = (style / 10) % 2, side = style / 20;
+    if (variant >= sc->decals || side > 1) continue;   /* the engine writes sides 0 and 1 only (engine.py:6280-6306) */
+    const float *wl = &sc->walls[w * 4];
+    float vecx = wl[2] - wl[0], vecy = wl[3] - wl[1];
+    float impx = wl[0] + d->along * vecx, impy = wl[1] + d->along * vecy;
+    /* tangent: the fine-angle direction of the wall as seen from the chip's side */
+    int fine = sc->wallFine[w * 2 + side] & 8191;
+    float tanx = (float)sc->fineSine[(fine + 2048) & 8191] / 65536.0f, tany = (float)sc->fineSine[fine] / 65536.0f;
+    float leftOff = (float)sc->decalInfo[variant * 4 + 1], topOff = (float)sc->decalInfo[variant * 4 + 2];
+    int height = sc->decalInfo[variant * 4 + 0];
+    float a = leftOff * GD_DECAL_SCALE, b = (width - leftOff) * GD_DECAL_SCALE;
+    float lx = impx - tanx * a, ly = impy - tany * a;
+    float rx_ = impx + tanx * b, ry_ = impy + tany * b;
+    float segx = rx_ - lx, segy = ry_ - ly;
+    /* FWallCoords on the chip's two fixed-point endpoints (engine.py:13837-13883) */
+    i64 ex[2] = {rint_f(lx * 65536.0f), rint_f(rx_ * 65536.0f)}, ey[2] = {rint_f(ly * 65536.0f), rint_f(ry_ * 65536.0f)};
+    i64 tx[2], ty[2];
+    for (int e = 0; e < 2; ++e) {
+      i64 relx = ex[e] - v->vx, rely = ey[e] - v->vy;
+      tx[e] = (relx * v->vsin - rely * v->vcos) >> 20;
+      ty[e] = (relx * v->vcos + rely * v->vsin) >> 20;
+    }
+    const i64 cf = 160 * FU;
+    i64 sty1 = ty[0] == 0 ? 1 : ty[0], sty2 = ty[1] == 0 ? 1 : ty[1];
+    i64 pl = ((cf + (tx[0] * cf) / sty1) >> 16) + (tx[0] >= 0);
+    i64 pr = ((cf + (tx[1] * cf) / sty2) >> 16) + (tx[1] >= 0);
+    i64 lden = tx[0] - tx[1] - ty[1] + ty[0], rden = ty[1] - ty[0] - tx[1] + tx[0];
+    int leftInside = tx[0] >= -ty[0] && tx[0] <= ty[0] && ty[0] != 0;
+    int rightInside = tx[1] <= ty[1] && tx[1] >= -ty[1] && ty[1] != 0;
+    int leftClipped = tx[0] < -ty[0] && tx[1] >= -ty[1] && lden != 0;
+    int rightClipped = tx[1] > ty[1] && tx[0] <= ty[0] && rden != 0;
+    i64 screenL = leftInside ? iclamp(pl, 0, SW) : 0, screenR = rightInside ? iclamp(pr, 0, SW) : SW;
+    if (!((leftInside || leftClipped) && (rightInside || rightClipped) && screenR > screenL)) continue;
+    float cross = vecx * (v->y - wl[1]) - vecy * (v->x - wl[0]);
+    if ((cross > 0 ? 1 : 0) != side) continue;
+    int sector = sc->wsec[w * 2 + side];
+    if (sector < 0) sector = 0;
+    int horizontal = fabsf(vecy) < 1e-6f, vertical = fabsf(vecx) < 1e-6f;
+    i64 light = (i64)sec_light(sc, sector) + (vertical ? 16 : (horizontal ? -16 : 0)) + v->flashLight * 16;
+    float offx = lx - v->x, offy = ly - v->y;
+    for (int x = (int)screenL; x < (int)screenR; ++x) {
+      float rx = g->dirx[x], ry = g->diry[x];
+      float den = rx * segy - ry * segx;
+      if (fabsf(den) < 1e-6f) continue;
+      float distance = (offx * segy - offy * segx) / den;
+      float along = (offx * ry - offy * rx) / den;
+      if (!(distance > 0)) continue;
+      i64 u = (i64)floorf(along * width);
+      u = iclamp(u, 0, sc->decalW - 1);
+      if (flipX) u = sc->decalW - 1 - u;
+      float safeDist = fmaxf(distance, 1e-6f);
+      float vscale = 96.0f / safeDist;
+      float top = center - ((d->z + topOff * GD_DECAL_SCALE) - v->viewZ) * 192.0f / safeDist;
+      i64 depthFixed = rint_f(safeDist * 4096.0f);
+      i64 vis = (WALL_VIS << 12) / imax(depthFixed, 1);
+      int shade = wall_shade(light, vis);
+      for (int y = 0; y < VH; ++y) {
+        i64 tv = (i64)floorf(((float)y - top) / vscale);
+        if (tv < 0 || tv >= height) continue;
+        if (flipY) tv = height - 1 - tv;
+        uint8_t src = sc->decalAtlas[((size_t)variant * sc->decalH + tv) * sc->decalW + u];
+        if (!src) continue;
+        int i = y * SW + x;
+        if (!(fabsf(lb->sceneDepth[i] - distance) <= 1e-3f)) continue;
+        uint8_t opacity = sc->decalOpacity[shade * 256 + src];
+        lb->frame[i] = sc->decalBlack[opacity * 256 + lb->frame[i]];
+      }
+    }
+  }
+  free(order);
+}
+
+static const gd_decal *gBoundDecals;
+static int gBoundDecalSlots;
+/* Decal rings of the lanes of the next gd_oracle_render calls: n x slots records, or NULL. */
+void gd_oracle_bind_decals(const gd_decal *decals, int slots) {
+  gBoundDecals = decals;
+  gBoundDecalSlots = slots;
 }
 
 typedef struct {
@@ -1793,6 +1929,8 @@ int gd_oracle_render(const uint8_t *blob, const int32_t *lanes, const gd_thing *
       wall_pass(&c->sc, &v, &c->g, c->lb);
       plane_pass(&c->sc, &v, c->lb, &un);
       masked_pass(&c->sc, &v, &c->g, c->lb);
+      if (gBoundDecals)
+        decal_pass(&c->sc, &v, &c->g, c->lb, &gBoundDecals[(size_t)l * gBoundDecalSlots], gBoundDecalSlots);
     } else {
       for (int i = 0; i < VH * SW; ++i) { c->lb->clip.depth[i] = INFINITY; c->lb->clip.wall[i] = -1; }
     }

@@ -54,9 +54,14 @@ def _ptr(a):
     return None if a is None else a.ctypes.data_as(ctypes.c_void_p)
 
 
+DECAL_DTYPE = np.dtype([("serial", "<i4"), ("wall", "<i2"), ("style", "<u2"), ("along", "<f4"), ("z", "<f4")])
+
+
 def render(blob, lanes, things, *, mask_hud=True, stage_mask=STAGE_ALL, depth_override=None,
-           want_stages=False):
+           want_stages=False, decals=None):
     """Render every lane on the CPU.
+
+    ``decals``: optional ``(N, slots)`` array of ``DECAL_DTYPE`` records (the lanes' bullet-chip rings).
 
     Returns a dict with ``indexed (N,240,320) u8``, ``obs (N,84,84) u8``,
     ``unowned (N,) i32`` and, on request, ``stages (N,3,208,320) u8`` (the view
@@ -74,10 +79,18 @@ def render(blob, lanes, things, *, mask_hud=True, stage_mask=STAGE_ALL, depth_ov
     stages = np.zeros((n, 3, 208, 320), dtype=np.uint8) if want_stages else None
     if depth_override is not None:
         depth_override = np.ascontiguousarray(depth_override, dtype=np.float32)
-    rc = lib().gd_oracle_render(_ptr(blob), _ptr(lanes), _ptr(things), ctypes.c_int(k),
-                                _ptr(depth_override), ctypes.c_int(n), ctypes.c_int(int(mask_hud)),
-                                ctypes.c_int(stage_mask), _ptr(indexed), _ptr(obs), _ptr(stages),
-                                _ptr(unowned))
+    if decals is not None:
+        decals = np.ascontiguousarray(decals, dtype=DECAL_DTYPE)
+        assert decals.ndim == 2 and decals.shape[0] == n
+        lib().gd_oracle_bind_decals(_ptr(decals), ctypes.c_int(decals.shape[1]))
+    try:
+        rc = lib().gd_oracle_render(_ptr(blob), _ptr(lanes), _ptr(things), ctypes.c_int(k),
+                                    _ptr(depth_override), ctypes.c_int(n), ctypes.c_int(int(mask_hud)),
+                                    ctypes.c_int(stage_mask), _ptr(indexed), _ptr(obs), _ptr(stages),
+                                    _ptr(unowned))
+    finally:
+        if decals is not None:
+            lib().gd_oracle_bind_decals(None, ctypes.c_int(0))
     if rc != 0:
         raise RuntimeError(f"oracle rejected the scene blob (code {rc})")
     out = {"indexed": indexed, "obs": obs, "unowned": unowned}

@@ -82,7 +82,14 @@ def scene_to_compiled(scene, scenario_module):
     W = len(walls)
     middle = scene.side_textures[:, 0, 0]
     items = scene.meta.get("items")
+    decals = scene.meta.get("decals") or {}
     return scenario_module.CompiledScenario(
+        bullet_decal_atlas=decals.get("atlas"),
+        bullet_decal_heights=decals.get("heights"),
+        bullet_decal_left_offsets=decals.get("left"),
+        bullet_decal_top_offsets=decals.get("top"),
+        bullet_decal_opacity_lut=decals.get("opacity_lut"),
+        bullet_decal_black_lut=decals.get("black_lut"),
         scenario_sha256="0" * 64,
         iwad_sha256="1" * 64,
         namespace="zdoom",

@@ -50,6 +50,17 @@ def load_golden(name):
     return np.load(path)
 
 
+def decal_rings(data):
+    """``(N, slots, 4) int32`` gd_decal rings from the engine's ``hitscan_decal_*`` arrays of a fixture."""
+
+    out = np.zeros((*data["decal_serial"].shape, 4), dtype=np.int32)
+    out[..., 0] = data["decal_serial"]
+    out[..., 1] = (data["decal_wall"].astype(np.int32) & 0xFFFF) | (data["decal_style"].astype(np.int32) << 16)
+    out[..., 2] = data["decal_along"].astype(np.float32).view(np.int32)
+    out[..., 3] = data["decal_z"].astype(np.float32).view(np.int32)
+    return out
+
+
 def pad_things(things, k):
     out = np.zeros((things.shape[0], k, 4), dtype=np.int32)
     out[:, : things.shape[1]] = things

@@ -3,7 +3,7 @@
 Run once on a machine that has the upstream sources:
 
     GRADOOM_REFERENCE_SRC=<upstream checkout>/src/gradoom python tests/golden/make_golden.py \
-        [c1 c2 c3 c4 c1m stack flashes pitch fallback c2d c4d c1k state move_c1 move_c2]
+        [c1 c2 c3 c4 c1m stack flashes pitch fallback c2d c4d c1k state move_c1 move_c2 decals_c1 decals_c4]
 
 For each seeded synthetic scene it resets the upstream engine, injects K
 monsters per lane, replays a seeded uniform action stream and, at a few
@@ -202,6 +202,86 @@ def generate_fallback(eng, scn, act):
     out["indexed_0"], out["obs_float_0"] = indexed, obs_float
     np.savez_compressed(os.path.join(OUT, "golden_fallback.npz"), **out)
     print("fallback fixture done", flush=True)
+
+
+def generate_decals(cfg, eng, scn, act):
+    """Bullet chips on the walls in view (engine.py:13747-13991): the scene carries decal bitmaps,
+    the engine's decal rings are written directly (the way the upstream tests set state): per lane
+    some forty chips where rays through the view meet the nearest line, at seeded heights, on the
+    viewer's side of the line mostly, a few on the far side, a few on lines elsewhere, serials in
+    shuffled slot order, free slots in between."""
+
+    n, k = 4, 4
+    sc = gdscene.make_grid_scene(gdscene.GRID_CONFIGS[cfg])
+    blob = gdscene.pack_scene(sc)
+    e, g = make_engine(eng, scn, sc, n, k, seed=4242)
+    am = action_matrix(act)
+    ag = torch.Generator().manual_seed(ACTION_SEED + 11)
+    del e.render_frame
+    for step in range(12):
+        _f, _r, term, trunc = e.step(am[torch.randint(0, 17, (n,), generator=ag)])
+        done = term | trunc
+        if bool(done.any()):
+            e.reset(done, torch.arange(n) + 1000 * (step + 1))
+    rng = np.random.default_rng(99)
+    walls = sc.walls.astype(np.float64)
+    slots = e.hitscan_decal_serial.shape[1]
+    serial = np.full((n, slots), -1, dtype=np.int32)
+    wall = np.zeros((n, slots), dtype=np.int32)
+    along = np.zeros((n, slots), dtype=np.float32)
+    zs = np.zeros((n, slots), dtype=np.float32)
+    style = np.zeros((n, slots), dtype=np.uint8)
+    for lane in range(n):
+        px, py, ang = float(e.x[lane]), float(e.y[lane]), float(e.angle[lane])
+        chips = []
+        for _ in range(44):
+            if rng.random() < 0.85:
+                a = ang + rng.uniform(-0.75, 0.75)
+                rx, ry = np.cos(a), np.sin(a)
+                sx, sy = walls[:, 0], walls[:, 1]
+                ex, ey = walls[:, 2] - sx, walls[:, 3] - sy
+                den = rx * ey - ry * ex
+                ok = np.abs(den) > 1e-9
+                den = np.where(ok, den, 1.0)
+                dist = ((sx - px) * ey - (sy - py) * ex) / den
+                t = ((sx - px) * ry - (sy - py) * rx) / den
+                dist = np.where(ok & (dist > 1e-3) & (t >= 0) & (t <= 1), dist, np.inf)
+                w = int(np.argmin(dist))
+                if not np.isfinite(dist[w]):
+                    continue
+                tt = float(t[w])
+            else:
+                w, tt = int(rng.integers(0, len(walls))), float(rng.random())
+            cross = (walls[w, 2] - walls[w, 0]) * (py - walls[w, 1]) - (walls[w, 3] - walls[w, 1]) * (px - walls[w, 0])
+            side = int(cross > 0)
+            if rng.random() < 0.1:
+                side = 1 - side
+            chips.append((w, tt, float(rng.uniform(-8.0, 200.0)), int(rng.integers(0, 5)) + 5 * int(rng.integers(0, 2))
+                          + 10 * int(rng.integers(0, 2)) + 20 * side))
+        where = rng.permutation(slots)[: len(chips)]
+        for i, (slot, chip) in enumerate(zip(where, chips)):
+            serial[lane, slot] = 1000 + i
+            wall[lane, slot], along[lane, slot], zs[lane, slot], style[lane, slot] = chip
+    e.hitscan_decal_serial.copy_(torch.from_numpy(serial))
+    e.hitscan_decal_wall.copy_(torch.from_numpy(wall))
+    e.hitscan_decal_along.copy_(torch.from_numpy(along))
+    e.hitscan_decal_z.copy_(torch.from_numpy(zs))
+    e.hitscan_decal_style.copy_(torch.from_numpy(style))
+    e.hitscan_decal_count.copy_(torch.full((n,), 1000 + 44, dtype=torch.int64))
+    offsets, coscorr = gdscene.ray_tables()
+    out = {"config": np.asarray(cfg), "ray_offsets": offsets, "ray_coscorr": coscorr, "checkpoints": np.asarray([0]),
+           "decal_serial": serial, "decal_wall": wall, "decal_along": along, "decal_z": zs, "decal_style": style}
+    lanes, things, indexed, obs_float = snapshot(e, blob, 64)
+    used = max(int(lanes[:, gdstate.L_THINGS].max()), 1)
+    out["lanes_0"], out["things_0"] = lanes, things[:, :used].copy()
+    out["indexed_0"], out["obs_float_0"] = indexed, obs_float
+    # the same state with the rings emptied, to count what the chips changed
+    e.hitscan_decal_serial.fill_(-1)
+    bare = e._render_native_indexed_frame(include_hud=True).numpy()
+    out["changed_pixels"] = np.asarray(int((bare != indexed).sum()))
+    np.savez_compressed(os.path.join(OUT, f"golden_decals_{cfg}.npz"), **out)
+    print("decal fixture", cfg, "done; pixels the chips changed:", int(out["changed_pixels"]), flush=True)
+
 
 
 def generate_c1k(eng, scn, act):
@@ -466,6 +546,8 @@ def main(argv):
             generate_fallback(eng, scn, act)
         elif name == "c1k":
             generate_c1k(eng, scn, act)
+        elif name in ("decals_c1", "decals_c4"):
+            generate_decals({"decals_c1": "c1d", "decals_c4": "c4d"}[name], eng, scn, act)
         else:
             generate(name, eng, scn, act)
 

@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 import torch
 
-from conftest import load_golden, pad_things
+from conftest import decal_rings, load_golden, pad_things
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -123,3 +123,43 @@ def test_corrupted_blobs_are_reported_not_followed(pkg, scenes):
             bits |= _bits(r)
         assert bits & bit, section
         r.close()
+
+
+def test_decal_rings_under_the_checked_build(pkg, oracle, scenes):
+    """The decal fixtures are clean and equal; records with a wall index beyond the table (clamped,
+    as the reference clamps it, engine.py:13799-13806), a variant beyond the atlas, a side that does
+    not exist, and positions that are not numbers draw without a fault and leave the other lanes'
+    frames equal to the oracle's."""
+
+    from gradoom_b200 import stepper
+
+    for name in ("decals_c1d", "decals_c4d"):
+        data = load_golden(name)
+        _sc, blob = scenes(str(data["config"]), (data["ray_offsets"], data["ray_coscorr"]))
+        r = _checked(blob, 64)
+        r.bind_decals(_dev(decal_rings(data)))
+        _, indexed, _ = r.frames(_dev(data["lanes_0"]), _dev(pad_things(data["things_0"], 64)), indexed=True)
+        assert np.array_equal(indexed.cpu().numpy(), data["indexed_0"]) and _bits(r) == 0
+    sc, blob = scenes("c1d")
+    lanes, things = stepper.random_lanes(sc, 4, 4, seed=14)
+    rings = stepper.random_decals(sc, lanes, 50, 64, seed=15)
+    clean = oracle.render(blob, lanes, things, decals=rings.view(oracle.DECAL_DTYPE)[..., 0])["indexed"]
+    odd = rings.copy()
+    used = np.flatnonzero(odd[0, :, 0] >= 0)
+    odd[0, used[0], 1] = 30000 | (3 << 16)                      # wall 30000
+    odd[0, used[1], 1] = (odd[0, used[1], 1] & 0xFFFF) | (255 << 16)   # variant 0, side 12
+    r = _checked(blob, 4)
+    r.bind_decals(_dev(odd))
+    _, indexed, _ = r.frames(_dev(lanes), _dev(things), indexed=True)
+    assert _bits(r) == 0
+    assert np.array_equal(indexed.cpu().numpy(),
+                          oracle.render(blob, lanes, things, decals=odd.view(oracle.DECAL_DTYPE)[..., 0])["indexed"])
+    # positions that are not numbers: whatever lane 0 shows, nothing faults and lanes 1..3 are untouched
+    bad = rings.copy()
+    bad[0, used[2], 2] = np.float32(np.nan).view(np.int32)      # along
+    bad[0, used[3], 3] = np.float32(np.inf).view(np.int32)      # height
+    bad[0, used[4], 2] = np.float32(3.0e38).view(np.int32)
+    r.bind_decals(_dev(bad))
+    _, indexed, _ = r.frames(_dev(lanes), _dev(things), indexed=True)
+    assert _bits(r) == 0
+    assert np.array_equal(indexed.cpu().numpy()[1:], clean[1:])

@@ -204,6 +204,66 @@ def test_engine_state_producer_packs_on_the_device(pkg, oracle, scenes):
 
 
 @pytest.mark.gpu
+def test_engine_state_producer_follows_the_engines_decal_rings(pkg, oracle, scenes):
+    """An engine that keeps ``hitscan_decal_*`` rings (src/gradoom/engine.py:1870-1884): the producer
+    binds them to the renderer and refreshes them with the state, so chips added between two
+    steps show up in the next observation."""
+
+    from conftest import fake_engine
+    from gradoom_b200 import env as gdenv, state as gdstate, stepper
+
+    sc, blob = scenes("c1d")
+    n, slots = 4, 128
+    base = fake_engine(n, seed=31)
+    lanes, things, _k = oracle.pack_state(blob, base, 64)
+    rings = [stepper.random_decals(sc, lanes, count, slots, seed=40 + count) for count in (0, 90)]
+
+    def ring_tensors(engine, rec):
+        engine.hitscan_decal_serial = torch.from_numpy(rec[..., 0].copy()).to(DEV)
+        engine.hitscan_decal_wall = torch.from_numpy((rec[..., 1] & 0xFFFF).astype(np.int32)).to(DEV)
+        engine.hitscan_decal_style = torch.from_numpy((rec[..., 1] >> 16).astype(np.uint8)).to(DEV)
+        engine.hitscan_decal_along = torch.from_numpy(rec[..., 2].copy().view(np.float32)).to(DEV)
+        engine.hitscan_decal_z = torch.from_numpy(rec[..., 3].copy().view(np.float32)).to(DEV)
+
+    class Engine:
+        def __init__(self):
+            self.__dict__.update(vars(fake_engine(n, seed=31, device=DEV)))
+            self.signal_buffer = torch.zeros((n, 27), device=DEV)
+            self.pending_reset = torch.zeros(n, dtype=torch.bool, device=DEV)
+            self.render_frame = None
+            ring_tensors(self, rings[0])
+
+        def reset(self, mask, seeds):
+            self.render_frame(mask)
+
+        def step(self, buttons):
+            self.render_frame()
+            ring_tensors_in_place(self, rings[1])
+            zeros = torch.zeros(n, device=DEV)
+            return None, zeros, zeros.bool(), zeros.bool()
+
+    def ring_tensors_in_place(engine, rec):
+        fresh = Engine.__new__(Engine)
+        ring_tensors(fresh, rec)
+        for name in ("serial", "wall", "style", "along", "z"):
+            getattr(engine, f"hitscan_decal_{name}").copy_(getattr(fresh, f"hitscan_decal_{name}"))
+
+    engine = Engine()
+    assert torch.equal(gdstate.decal_records(engine).cpu(), torch.from_numpy(rings[0]))
+    producer = gdenv.EngineStateProducer(engine, sc, 64)
+    e = gdenv.GraDoomVecEnv(compiled_scenario=sc, num_envs=n, device=DEV, producer=producer, max_things=64,
+                            frame_skip=2, obs_crop=(0, 32, 0, 0), obs_crop_mode="mask")
+    obs, _signals = e.reset_device(torch.ones(n, dtype=torch.bool, device=DEV), torch.arange(n, device=DEV))
+    bare = oracle.render(blob, lanes, things)["obs"]
+    assert np.array_equal(obs[:, 3].cpu().numpy(), bare)
+    t = e.step_device(torch.zeros(n, dtype=torch.int64, device=DEV))
+    chipped = oracle.render(blob, lanes, things, decals=rings[1].view(oracle.DECAL_DTYPE)[..., 0])["obs"]
+    assert not np.array_equal(chipped, bare)
+    assert np.array_equal(t.observations[:, 3].cpu().numpy(), chipped)
+    e.close()
+
+
+@pytest.mark.gpu
 def test_gym_level_reset_step_and_observation_ownership(pkg, scenes):
     """reset()/step() with the three obs_copy modes (src/gradoom/env.py:678-688; upstream
     tests/test_turbo_api_contract.py:454-465: safe_view alternates two buffers)."""

@@ -619,3 +619,59 @@ def test_render_step_captures_into_a_cuda_graph(pkg, scenes):
     r.check_status()
     assert torch.equal(stack, expect)
     assert not torch.equal(stack[:, 3], stack[:, 2])
+
+
+@pytest.mark.parametrize("name", ["decals_c1d", "decals_c4d"])
+def test_cuda_draws_the_upstream_bullet_chips(name, pkg, oracle, scenes):
+    """The decal layer (engine.py:13747-13991) against the frames recorded from the upstream engine."""
+
+    from conftest import decal_rings
+
+    data = load_golden(name)
+    _sc, blob = scenes(str(data["config"]), (data["ray_offsets"], data["ray_coscorr"]))
+    r = _renderer(blob, 64)
+    lanes, things = _dev(data["lanes_0"]), _dev(pad_things(data["things_0"], 64))
+    r.bind_decals(_dev(decal_rings(data)))
+    _, indexed, _ = r.frames(lanes, things, indexed=True)
+    r.check_status()
+    assert np.array_equal(indexed.cpu().numpy(), data["indexed_0"])
+    r.bind_decals(None)
+    _, bare, _ = r.frames(lanes, things, indexed=True)
+    assert int((bare.cpu().numpy() != data["indexed_0"]).sum()) == int(data["changed_pixels"])
+
+
+@pytest.mark.parametrize("name,n,k,per_lane,slots,seed", [("c4d", 96, 8, 60, 1024, 1), ("c1d", 64, 4, 200, 256, 2),
+                                                          ("c1d", 5, 0, 1, 1, 3)])
+def test_cuda_decals_match_the_oracle_on_seeded_lanes(name, n, k, per_lane, slots, seed, pkg, oracle, scenes):
+    from gradoom_b200 import stepper
+
+    sc, blob = scenes(name)
+    lanes, things = stepper.random_lanes(sc, n, k, seed=seed)
+    rings = stepper.random_decals(sc, lanes, per_lane, slots, seed=seed + 100)
+    expected = oracle.render(blob, lanes, things, decals=rings.view(oracle.DECAL_DTYPE)[..., 0])
+    bare = oracle.render(blob, lanes, things)
+    if per_lane > 1:
+        assert int((expected["indexed"] != bare["indexed"]).sum()) > 1000
+    r = _renderer(blob, k)
+    r.bind_decals(_dev(rings))
+    obs, indexed, _ = r.frames(_dev(lanes), _dev(things), obs=True, indexed=True)
+    r.check_status()
+    assert np.array_equal(indexed.cpu().numpy(), expected["indexed"])
+    assert np.array_equal(obs.cpu().numpy(), expected["obs"])
+
+
+def test_decal_rings_are_ignored_by_a_scene_without_chip_bitmaps(pkg, oracle, scenes):
+    from gradoom_b200 import native, stepper
+
+    sc, blob = scenes("c1")
+    lanes, things = stepper.random_lanes(sc, 8, 4, seed=5)
+    rings = stepper.random_decals(sc, lanes, 30, 64, seed=6)
+    r = _renderer(blob, 4)
+    _, bare, _ = r.frames(_dev(lanes), _dev(things), indexed=True)
+    r.bind_decals(_dev(rings))
+    _, bound, _ = r.frames(_dev(lanes), _dev(things), indexed=True)
+    assert torch.equal(bare, bound)
+    with pytest.raises(native.NativeError):
+        r.bind_decals(torch.zeros((8, 2048, 4), dtype=torch.int32, device=DEV))     # more slots than the renderer accepts
+    with pytest.raises(ValueError):
+        r.bind_decals(torch.zeros((8, 64, 3), dtype=torch.int32, device=DEV))

@@ -248,3 +248,41 @@ def test_random_lanes_are_valid_and_deterministic(pkg, scenes):
     x = lanes[:, gdstate.L_X].view(np.float32)
     assert ((x > 0) & (x < 2048)).all()
     assert (lanes[:, gdstate.L_THINGS] == 12).all()
+
+
+def test_decal_records_follow_the_record_layout(pkg, oracle):
+    """gd_decal (include/gradoom_b200_layout.h): serial, wall | style << 16, along, z in 16 bytes; the
+    torch packer, the test helper and the oracle's record type agree."""
+
+    import types
+
+    import torch
+
+    from conftest import decal_rings
+    from gradoom_b200 import state as gdstate
+
+    rng = np.random.default_rng(3)
+    data = {"decal_serial": rng.integers(-1, 500, size=(3, 16)).astype(np.int32),
+            "decal_wall": rng.integers(0, 800, size=(3, 16)).astype(np.int32),
+            "decal_style": rng.integers(0, 40, size=(3, 16)).astype(np.uint8),
+            "decal_along": rng.random((3, 16)).astype(np.float32),
+            "decal_z": rng.uniform(-8, 200, size=(3, 16)).astype(np.float32)}
+    src = types.SimpleNamespace(**{f"hitscan_{k}": torch.from_numpy(v) for k, v in data.items()})
+    rec = gdstate.decal_records(src).numpy()
+    assert np.array_equal(rec, decal_rings(data))
+    assert oracle.DECAL_DTYPE.itemsize == 16
+    typed = rec.view(oracle.DECAL_DTYPE)[..., 0]
+    assert np.array_equal(typed["serial"], data["decal_serial"]) and np.array_equal(typed["wall"], data["decal_wall"])
+    assert np.array_equal(typed["style"], data["decal_style"]) and np.array_equal(typed["z"], data["decal_z"])
+    again = torch.zeros((3, 16, 4), dtype=torch.int32)
+    assert gdstate.decal_records(src, out=again) is again and np.array_equal(again.numpy(), rec)
+
+
+def test_wall_fine_angles_of_axis_aligned_and_diagonal_lines(pkg):
+    from gradoom_b200 import scene as gdscene
+
+    walls = np.asarray([[0, 0, 64, 0], [0, 0, 0, 64], [64, 0, 0, 0], [0, 64, 0, 0], [0, 0, 64, 64], [64, 64, 0, 0],
+                        [0, 64, 64, 0]], dtype=np.float32)
+    fine = gdscene.wall_fine_angles(walls)
+    assert fine[:, 0].tolist() == [0, 2048, 4096, 6144, 1024, 5120, 7168]
+    assert fine[:, 1].tolist() == [4096, 6144, 0, 2048, 5120, 1024, 3072]

@@ -254,3 +254,21 @@ def test_oracle_screen_flashes_match_upstream_rgb(pkg, oracle):
         assert np.abs(out["obs"].astype(int) - data[f"obs_float_{ci}"].astype(int)).max() <= 1
     plain = oracle.rgb(blob, out["indexed"])
     assert not np.array_equal(plain, data["rgb_2"]), "the last case blends every lane"
+
+
+@pytest.mark.parametrize("name,floor", [("decals_c1d", 250), ("decals_c4d", 3000)])
+def test_oracle_draws_the_upstream_bullet_chips(name, floor, pkg, oracle, scenes):
+    """engine.py:13747-13991: the decal layer of the indexed frame, recorded from the upstream
+    engine with its decal rings written directly; the fixture counts the pixels the chips changed."""
+
+    from conftest import decal_rings
+
+    data = load_golden(name)
+    assert int(data["changed_pixels"]) > floor
+    _sc, blob = scenes(str(data["config"]), (data["ray_offsets"], data["ray_coscorr"]))
+    rings = decal_rings(data)
+    with_chips = oracle.render(blob, data["lanes_0"], data["things_0"], mask_hud=False,
+                               decals=rings.view(oracle.DECAL_DTYPE)[..., 0])
+    assert np.array_equal(with_chips["indexed"], data["indexed_0"])
+    bare = oracle.render(blob, data["lanes_0"], data["things_0"], mask_hud=False)
+    assert int((bare["indexed"] != data["indexed_0"]).sum()) == int(data["changed_pixels"])
