@@ -486,7 +486,13 @@ def from_compiled_scenario(cs) -> Scene:
         value = getattr(cs, name, None)
         return np.asarray(default if value is None else value)
 
-    if getattr(cs, "wall_projection_fragments_fixed", None) is not None:
+    # every line is one fragment unless a node builder split it (src/gradoom/scenario.py:420-455);
+    # split lines are outside this render path
+    fragment_mask = getattr(cs, "wall_projection_fragment_mask", None)
+    fragments = getattr(cs, "wall_projection_fragments_fixed", None)
+    split = (fragment_mask is not None and np.asarray(fragment_mask)[:, 1:].any()) or \
+            (fragment_mask is None and fragments is not None and np.asarray(fragments).shape[1] > 1)
+    if split:
         raise ValueError("scenarios with node-builder wall fragments are not supported by this render path")
     spr_atlas = need("raw_sprite_atlas")
     last_sprite = max(len(spr_atlas) - 1, 0)

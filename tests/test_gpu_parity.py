@@ -675,3 +675,36 @@ def test_decal_rings_are_ignored_by_a_scene_without_chip_bitmaps(pkg, oracle, sc
         r.bind_decals(torch.zeros((8, 2048, 4), dtype=torch.int32, device=DEV))     # more slots than the renderer accepts
     with pytest.raises(ValueError):
         r.bind_decals(torch.zeros((8, 64, 3), dtype=torch.int32, device=DEV))
+
+
+def test_cuda_draws_a_scene_compiled_from_wad_files(pkg, oracle):
+    """WAD + UDMF in (src/gradoom/scenario.py:457-1064), frames out: textures composed from patches,
+    sprites with mirrored rotations, weapon and status-bar pictures, all through the blob."""
+
+    import wadgen
+    from gradoom_b200 import scene as gdscene, state as gdstate, wad as gdwad
+
+    sc = gdscene.from_compiled_scenario(gdwad.compile_scenario(*wadgen.synthetic_pair(gdscene, gdwad)))
+    blob = gdscene.pack_scene(sc)
+    rng = np.random.default_rng(8)
+    poses = [(float(rng.uniform(40, 980)), float(rng.uniform(40, 980)), float(rng.uniform(0, 6.28))) for _ in range(24)]
+    poses = [(x + (20 if x % 256 < 20 else 0) - (20 if x % 256 > 236 else 0),
+              y + (20 if y % 256 < 20 else 0) - (20 if y % 256 > 236 else 0), a) for x, y, a in poses]
+    lanes = wadgen.view_lanes(gdscene, gdstate, sc, poses)
+    k = 6
+    things = np.zeros((len(poses), k, 4), dtype=np.int32)
+    tf = things.view(np.float32)
+    for i in range(len(poses)):
+        for j in range(k):
+            x, y = float(rng.uniform(40, 980)), float(rng.uniform(40, 980))
+            sector = gdscene.sector_at(sc, np.float32([x]), np.float32([y]))[0]
+            tf[i, j, 0], tf[i, j, 1], tf[i, j, 2] = x, y, sc.sector_heights[sector, 0]
+            word = int(rng.integers(0, len(sc.spr_atlas))) | (gdstate.THING_ALIVE << 16) | (0xFF << 24)   # style -1
+            things[i, j, 3] = np.uint32(word).view(np.int32)
+    lanes[:, gdstate.L_THINGS] = k
+    expected = oracle.render(blob, lanes, things, mask_hud=False)
+    r = _renderer(blob, k)
+    obs, indexed, _ = r.frames(_dev(lanes), _dev(things), obs=True, indexed=True, mask_hud=False)
+    r.check_status()
+    assert np.array_equal(indexed.cpu().numpy(), expected["indexed"])
+    assert np.array_equal(obs.cpu().numpy(), expected["obs"])

@@ -159,6 +159,17 @@ def test_scene_from_the_reference_scenario_container(pkg, scenes):
     container = ref_engine.scene_to_compiled(sc, types.SimpleNamespace(CompiledScenario=types.SimpleNamespace))
     back = gdscene.from_compiled_scenario(container)
     assert np.array_equal(gdscene.pack_scene(back), blob)
+    # one fragment per line (what the upstream compiler writes for any map but its pinned one) is
+    # accepted; a line split by the node builder is refused
+    W = len(sc.walls)
+    container.wall_projection_fragments_fixed = np.zeros((W, 2, 4), dtype=np.int64)
+    container.wall_projection_fragment_mask = np.zeros((W, 2), dtype=bool)
+    container.wall_projection_fragment_mask[:, 0] = True
+    assert np.array_equal(gdscene.pack_scene(gdscene.from_compiled_scenario(container)), blob)
+    container.wall_projection_fragment_mask[3, 1] = True
+    with pytest.raises(ValueError):
+        gdscene.from_compiled_scenario(container)
+    container.wall_projection_fragment_mask[3, 1] = False
     container.texture_index_atlas = None
     with pytest.raises(ValueError):
         gdscene.from_compiled_scenario(container)
