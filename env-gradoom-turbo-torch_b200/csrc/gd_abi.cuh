@@ -30,6 +30,7 @@ struct gd_renderer {
   int decalSlots;
   uint8_t *decalScratch;
   size_t decalScratchBytes;
+  GdWall *fragScratch;       /* ctas x F records, allocated with the renderer when the scene has split lines */
 };
 
 static const void *gd_section(const uint8_t *dev, const int32_t *h, int s) { return dev + h[GD_HDR_SECTION0 + s]; }
@@ -55,11 +56,20 @@ extern "C" const char *gd_error_string(int code) {
  * renderer: every renderer raises it to the most the device allows beside the
  * kernel's static shared memory, so renderers of different scenes can live side
  * by side.  Returns that limit, or -1. */
+typedef void (*gd_kernel_fn)(const GdParams);
+/* the instantiation that draws a scene: with or without the code for split lines */
+static gd_kernel_fn gd_kernel_for(const GdScene &sc) { return sc.F > 0 ? gd_render_kernel<true> : gd_render_kernel<false>; }
+
 static int gd_raise_shared_limit(int maxOptin) {
-  cudaFuncAttributes fa;
-  if (cudaFuncGetAttributes(&fa, gd_render_kernel) != cudaSuccess) return -1;
-  const int limit = maxOptin - (int)fa.sharedSizeBytes;
-  if (cudaFuncSetAttribute(gd_render_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, limit) != cudaSuccess) return -1;
+  int limit = maxOptin;
+  const gd_kernel_fn kernels[2] = {gd_render_kernel<false>, gd_render_kernel<true>};
+  for (int k = 0; k < 2; ++k) {
+    cudaFuncAttributes fa;
+    if (cudaFuncGetAttributes(&fa, kernels[k]) != cudaSuccess) return -1;
+    if (maxOptin - (int)fa.sharedSizeBytes < limit) limit = maxOptin - (int)fa.sharedSizeBytes;
+  }
+  for (int k = 0; k < 2; ++k)
+    if (cudaFuncSetAttribute(kernels[k], cudaFuncAttributeMaxDynamicSharedMemorySize, limit) != cudaSuccess) return -1;
   return limit;
 }
 
@@ -79,6 +89,8 @@ extern "C" int gd_renderer_create(const void *blob_header_host, const void *blob
   if (!r) return GD_ERR_CUDA;
   r->copyStream = nullptr;
   r->copiesDone = nullptr;
+  r->decalScratch = nullptr;
+  r->fragScratch = nullptr;
   for (int c = 0; c < GD_HOST_CHUNKS; ++c) r->chunkDone[c] = nullptr;
   memcpy(r->header, h, sizeof r->header);
   r->device = device;
@@ -127,7 +139,9 @@ extern "C" int gd_renderer_create(const void *blob_header_host, const void *blob
   sc.decalInfo = SECP(int32_t, GD_S_DECAL_INFO); sc.wallFine = SECP(int32_t, GD_S_WALL_FINE);
   sc.decalAtlas = SECP(uint8_t, GD_S_DECAL_ATLAS); sc.decalOpacity = SECP(uint8_t, GD_S_DECAL_OPACITY);
   sc.decalBlack = SECP(uint8_t, GD_S_DECAL_BLACK);
+  sc.F = h[GD_H_FRAGMENTS]; sc.fragOff = SECP(int32_t, GD_S_FRAG_OFF); sc.fragFixed = SECP(int32_t, GD_S_FRAG_FIXED);
   r->decals = nullptr; r->decalSlots = 0; r->decalScratch = nullptr; r->decalScratchBytes = 0;
+  r->fragScratch = nullptr;
 #undef SECP
   r->smemBytes = gd_shared_bytes(sc.W, max_things);
   r->secWallsN = h[GD_H_SEC_WALLS_N]; r->vtxWallsN = h[GD_H_VTX_WALLS_N]; r->V = h[GD_H_VERTICES];
@@ -150,11 +164,16 @@ extern "C" int gd_renderer_create(const void *blob_header_host, const void *blob
       if (r->smemBytes + extra <= (size_t)limit) { r->smemBytes += extra; r->stageMask |= bit; }
     }
     int perSm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, gd_render_kernel, GD_THREADS, r->smemBytes) != cudaSuccess ||
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, gd_kernel_for(sc), GD_THREADS, r->smemBytes) != cudaSuccess ||
         perSm < 1)
       rc = GD_ERR_CUDA;
     else
       r->ctas = sms * perSm;  /* one persistent CTA per resident slot */
+  }
+  if (rc == GD_OK && sc.F > 0) {
+    void *mem = nullptr;
+    if (cudaMalloc(&mem, (size_t)r->ctas * sc.F * sizeof(GdWall)) != cudaSuccess) rc = GD_ERR_CUDA;
+    r->fragScratch = (GdWall *)mem;
   }
   r->copyStream = nullptr;
   r->copiesDone = nullptr;
@@ -181,6 +200,7 @@ extern "C" void gd_renderer_destroy(gd_renderer *r) {
   if (r->copiesDone) cudaEventDestroy(r->copiesDone);
   if (r->copyStream) cudaStreamDestroy(r->copyStream);
   if (r->decalScratch) cudaFree(r->decalScratch);
+  if (r->fragScratch) cudaFree(r->fragScratch);
   if (switched) cudaSetDevice(prev);
   delete r;
 }
@@ -236,8 +256,9 @@ static int gd_launch(const gd_renderer *r, const int32_t *lanes, const gd_thing 
   p.queueOffset = (size_t)r->ctas * gd_scratch_per_cta(r->sc.W, r->sc.S);
   p.stageMask = r->stageMask; p.secWallsN = r->secWallsN; p.vtxWallsN = r->vtxWallsN; p.V = r->V;
   p.decals = r->decals; p.decalSlots = r->decalSlots; p.decalScratch = r->decalScratch;
+  p.fragScratch = r->fragScratch;
   int grid = n < r->ctas ? n : r->ctas;
-  gd_render_kernel<<<grid, GD_THREADS, r->smemBytes, (cudaStream_t)stream>>>(p);
+  gd_kernel_for(r->sc)<<<grid, GD_THREADS, r->smemBytes, (cudaStream_t)stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? GD_OK : GD_ERR_CUDA;
 }
 
@@ -440,9 +461,10 @@ extern "C" int gd_render_step_static(const gd_renderer *r, const int32_t *lanes,
   p.queueOffset = (size_t)GD_STATIC_MAX_CTAS * GD_STATIC_PER_CTA;
   p.stageMask = r->stageMask; p.secWallsN = r->secWallsN; p.vtxWallsN = r->vtxWallsN; p.V = r->V;
   p.decals = r->decals; p.decalSlots = r->decalSlots; p.decalScratch = r->decalScratch;
+  p.fragScratch = r->fragScratch;
   int grid = n < r->ctas ? n : r->ctas;
   if (grid > GD_STATIC_MAX_CTAS) grid = GD_STATIC_MAX_CTAS;
-  gd_render_kernel<<<grid, GD_THREADS, r->smemBytes, (cudaStream_t)stream>>>(p);
+  gd_kernel_for(r->sc)<<<grid, GD_THREADS, r->smemBytes, (cudaStream_t)stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? GD_OK : GD_ERR_CUDA;
 }
 

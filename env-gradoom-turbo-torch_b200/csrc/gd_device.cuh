@@ -67,6 +67,9 @@ struct GdScene {
   const int32_t *groupOff[2], *groupSec[2];
   int groups[2];
   int M;
+  /* projection fragments of the lines a node builder split: total count, CSR per line, 16.16 endpoints */
+  int F;
+  const int32_t *fragOff, *fragFixed;
   /* bullet-chip decals: variants (0 = none), atlas slice height / width */
   int decals, decalH, decalW;
   const int32_t *decalInfo, *wallFine;

@@ -77,12 +77,9 @@ __device__ void gd_wall_visibility(i64 tx1, i64 ty1, i64 tx2, i64 ty2, i64 &visL
   visSl = wsl;
 }
 
-/* Project wall w of the map for this lane (engine.py:10747-10869, 11207-11302,
- * 11359-11427).  The ray-owned span is completed by gd_wall_span below. */
-__device__ __noinline__ void gd_project_wall(const GdScene &sc, const GdView &v, int w, GdWall &out) {
-  const float *wl = &sc.walls[w * 4];
-  i64 fx[2] = {gd_rint(wl[0] * 65536.0f), gd_rint(wl[2] * 65536.0f)};
-  i64 fy[2] = {gd_rint(wl[1] * 65536.0f), gd_rint(wl[3] * 65536.0f)};
+/* View coordinates, FWallCoords and wallscan light of a segment given by its 16.16 endpoints
+ * (engine.py:10747-10869, 11207-11302). */
+__device__ __noinline__ void gd_project_fixed(const GdView &v, const i64 fx[2], const i64 fy[2], GdWall &out) {
   i64 tx[2], ty[2];
 #pragma unroll
   for (int e = 0; e < 2; ++e) {
@@ -101,11 +98,29 @@ __device__ __noinline__ void gd_project_wall(const GdScene &sc, const GdView &v,
   out.sl = sl; out.sr = sr; out.dl = dl; out.dr = dr;
   gd_wall_visibility(tx[0], ty[0], tx[1], ty[1], out.visL[0], out.visStep[0], out.visSl[0]);
   gd_wall_visibility(tx[1], ty[1], tx[0], ty[0], out.visL[1], out.visStep[1], out.visSl[1]);
+}
+
+/* Project wall w of the map for this lane (engine.py:10747-10869, 11207-11302,
+ * 11359-11427).  The ray-owned span is completed by gd_wall_span below. */
+__device__ __forceinline__ void gd_project_wall(const GdScene &sc, const GdView &v, int w, GdWall &out) {
+  const float *wl = &sc.walls[w * 4];
+  const i64 fx[2] = {gd_rint(wl[0] * 65536.0f), gd_rint(wl[2] * 65536.0f)};
+  const i64 fy[2] = {gd_rint(wl[1] * 65536.0f), gd_rint(wl[3] * 65536.0f)};
+  gd_project_fixed(v, fx, fy, out);
   out.oneSided = gd_wsec(sc, w * 2 + 1) < 0;
   float sx = wl[0], sy = wl[1];
   float segx = wl[2] - sx, segy = wl[3] - sy;
   float vfsx = v.x - sx, vfsy = v.y - sy;
   out.frontF = (segx * vfsy - segy * vfsx) < 0;
+}
+
+/* One piece of a line a node builder split (engine.py:11478-11500): projected like a line, from its
+ * own fixed-point endpoints.  Only its FWallCoords and its wallscan light are ever read. */
+__device__ __forceinline__ void gd_project_fragment(const GdScene &sc, const GdView &v, int f, GdWall &out) {
+  const int4 q = *reinterpret_cast<const int4 *>(&sc.fragFixed[f * 4]);
+  const i64 fx[2] = {q.x, q.z}, fy[2] = {q.y, q.w};
+  gd_project_fixed(v, fx, fy, out);
+  out.oneSided = 0; out.frontF = 0; out.hasColumns = 0; out.isl = 0; out.isr = 0; out.pad = 0;
 }
 
 /* Column-ray test of wall w at column x (engine.py:11317-11331).  Returns the
@@ -303,6 +318,46 @@ __device__ __noinline__ int gd_project_rows(const GdView &v, const GdWall &wv, f
   i64 span = gd_max(cr - cl, 1);
   i64 pstep = gd_div(pr - pl, span);
   return (int)gd_clamp((center + pl + (x - cl) * pstep) >> 16, 0, GD_VH);
+}
+
+/* The unclipped whole-line projection: what a column of a split line falls back to when none of
+ * the line's fragments owns it (engine.py:12393-12410, 12596-12604). */
+__device__ __noinline__ int gd_project_rows_whole(const GdView &v, const GdWall &wv, float worldZ, int x) {
+  const i64 wdl = gd_max(wv.dl, 1), wdr = gd_max(wv.dr, 1);
+  const i64 relZ = gd_rint((worldZ - v.viewZ) * 65536.0f);
+  const i64 num = -(relZ >> 4) * GD_FOCAL_Y;
+  const i64 opl = gd_div(num, wdl), opr = gd_div(num, wdr);
+  const i64 ostep = gd_div(opr - opl, gd_max(wv.sr - wv.sl, 1));
+  return (int)gd_clamp((v.center + opl + (x - wv.sl) * ostep) >> 16, 0, GD_VH);
+}
+
+/* Is line w split, and if so which of its fragments owns column x: the first whose half-open
+ * span holds it (engine.py:12310-12376, 11511-11545), or null. */
+__device__ __forceinline__ bool gd_line_is_split(const GdScene &sc, int w) {
+  return sc.F > 0 && sc.fragOff[w + 1] > sc.fragOff[w];
+}
+__device__ __noinline__ const GdWall *gd_fragment_at(const GdScene &sc, const GdWall *frags, int w, int x) {
+#pragma unroll 1
+  for (int f = sc.fragOff[w]; f < sc.fragOff[w + 1]; ++f) {
+    const GdWall &q = frags[f];
+    if (q.sr > q.sl && x >= q.sl && x < q.sr) return &q;
+  }
+  return nullptr;
+}
+/* Row projection and wallscan light of line w at column x, fragments considered. */
+__device__ __noinline__ int gd_line_rows(const GdScene &sc, const GdView &v, const GdWall *walls, const GdWall *frags, int w,
+                                         float worldZ, int x) {
+  if (!gd_line_is_split(sc, w)) return gd_project_rows(v, walls[w], worldZ, x);
+  const GdWall *q = gd_fragment_at(sc, frags, w, x);
+  return q ? gd_project_rows(v, *q, worldZ, x) : gd_project_rows_whole(v, walls[w], worldZ, x);
+}
+__device__ __forceinline__ i64 gd_line_vis(const GdScene &sc, const GdWall *walls, const GdWall *frags, int w, int side, int x) {
+  const GdWall *q = &walls[w];
+  if (gd_line_is_split(sc, w)) {
+    const GdWall *f = gd_fragment_at(sc, frags, w, x);
+    if (f) q = f;
+  }
+  return q->visL[side] + ((i64)x - q->visSl[side]) * q->visStep[side];
 }
 
 /* Column-independent part of gd_project_rows for one (wall, height). */

@@ -59,6 +59,7 @@ struct GdParams {
   const gd_decal *decals;    /* n x decalSlots rings of bullet chips, or null */
   int decalSlots;
   uint8_t *decalScratch;     /* ctas x gd_decal_scratch_per_cta(decalSlots) */
+  GdWall *fragScratch;       /* ctas x F fragment records, when the scene has split lines */
 };
 
 #define GD_SCRATCH_EVENTS_BYTES (GD_MAX_EVENTS * GD_SW * (int)sizeof(GdEvent))
@@ -94,6 +95,7 @@ struct GdShared {
   short *blockingWall;  /* 320 */
   unsigned *ownerMask;  /* 10 words: boundary_has_projected_owner; words 16..25: columns whose walk goes on after leaving the map */
   GdWall *walls;        /* W */
+  GdWall *frags;        /* scratch: F projection fragments of split lines (only their spans, depths and light) */
   GdActor *actors;      /* maxThings */
   unsigned long long *pal64;  /* 256: R | G<<20 | B<<40 */
   uint8_t *obs;         /* 84 x 84; shares the memory of hitD, which is free once the sprites are drawn */
@@ -164,6 +166,8 @@ __device__ inline void gd_carve(uint8_t *base, int W, int maxThings, GdShared &s
 /* ---- the kernel ----------------------------------------------------------- */
 extern __shared__ __align__(16) uint8_t gd_smem[];
 
+/* Two instantiations: kSplit = the scene carries projection fragments of split lines. */
+template <bool kSplit>
 __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams p) {
   /* The scene descriptor, the shared-memory map and the lane's view are read by
    * every helper through references; keeping them in shared memory (one copy
@@ -199,6 +203,8 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
     }
     if (m & GD_STAGE_ROWPROJ) { stagedRowproj = (GdRowProj *)cursor; cursor += gd_align16((size_t)sc.W * 4 * sizeof(GdRowProj)); }
     sh.planeTab = (GdPlaneEntry *)(p.scratch + (size_t)blockIdx.x * gd_scratch_per_cta(sc.W, sc.S) + GD_SCRATCH_FIXED);
+    sh.frags = p.fragScratch ? p.fragScratch + (size_t)blockIdx.x * sc.F : nullptr;
+    if (!sh.frags) sc.F = 0;
     if (tid == 0) { sScene = sc; sShared = sh; }
   }
   __syncthreads();
@@ -305,6 +311,8 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
       sh.yslope[tid] = (unsigned)ys;
     }
     for (int w = tid; w < sc.W; w += GD_THREADS) gd_project_wall(sc, v, w, sh.walls[w]);
+    if (kSplit)
+      for (int f = tid; f < sc.F; f += GD_THREADS) gd_project_fragment(sc, v, f, sh.frags[f]);
     for (int idx = GD_THREADS - 1 - tid; idx < sc.S * 2; idx += GD_THREADS)   /* the threads the walls leave idle */
       gd_plane_entry_setup(sc, v, idx >> 1, (idx & 1) != 0, sh.planeTab[idx]);
     for (int a = tid; a < nThings; a += GD_THREADS) {
@@ -344,7 +352,7 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
       sh.blockingWall[tid] = (short)bw;
     }
     __syncthreads();
-    gd_walk(sc, v, sh, events, eventCount, rowproj, p.status, sh.misc[0]);
+    gd_walk<kSplit>(sc, v, sh, events, eventCount, rowproj, p.status, sh.misc[0]);
     __syncthreads();
     /* Rows no seg ever claimed show the per-pixel flat fallback.  They are
      * queued (the hit cache is free once every column has finished its walk)
@@ -371,12 +379,14 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
       __syncthreads();
     }
     if (sc.M > 0) {
-      gd_masked_pass(sc, v, sh);
+      gd_masked_pass<kSplit>(sc, v, sh);
       __syncthreads();
     }
+#ifndef GD_NO_DECALS
     if (p.decals != nullptr && sc.decals > 0)
       gd_decals(sc, v, sh, events, eventCount, p.decals + (size_t)l * p.decalSlots, p.decalSlots,
                 p.decalScratch + (size_t)blockIdx.x * gd_decal_scratch_per_cta(p.decalSlots));
+#endif
     gd_sprites(sc, v, sh, events, eventCount, nThings);
     __syncthreads();
     gd_weapon(sc, sh.lane, sh.frame);

@@ -82,6 +82,13 @@ __device__ __forceinline__ unsigned gd_range_word(int k, int a, int b) {
   return upto & ~((1u << lo) - 1u);
 }
 
+/* rows of line w at column x: fragment aware in the instantiation for scenes with split lines */
+template <bool kSplit>
+__device__ __forceinline__ int gd_rows(const GdScene &sc, const GdView &v, const GdShared &sh, int w, float worldZ, int x) {
+  if (kSplit) return gd_line_rows(sc, v, sh.walls, sh.frags, w, worldZ, x);
+  return gd_project_rows(v, sh.walls[w], worldZ, x);
+}
+
 /* ---- phase: per-column portal walk (engine.py:11561-13371) -------------- */
 struct GdColState {
   int cur;
@@ -126,8 +133,10 @@ struct GdIter {
   bool psFromFront;
 };
 
-__device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWall *walls, const unsigned *ownerMask,
-                                 const GdRowProj *rowproj, float *hitD, float *hitA, uint8_t *hitF, int x, float rx,
+/* kSplit: the scene has lines a node builder split; the other instantiation carries none of that code */
+template <bool kSplit>
+__device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWall *walls, const GdWall *frags,
+                                 const unsigned *ownerMask, const GdRowProj *rowproj, float *hitD, float *hitA, uint8_t *hitF, int x, float rx,
                                  float ry, const GdColState &c, GdIter &it) {
   const int curSector = c.cur;
   const int current = GD_CHECK_SECTOR(curSector < 0 ? 0 : curSector, sc.S);
@@ -307,7 +316,9 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
   int renderOther = renderFromFront ? back : front;
   int side = renderFromFront ? 0 : 1;
   const GdWall &wv = walls[wallIndex];
-  i64 vis = wv.visL[side] + ((i64)x - wv.visSl[side]) * wv.visStep[side];
+  const bool splitLine = kSplit && gd_line_is_split(sc, wallIndex);      /* a node builder cut this line: the slow way */
+  i64 vis = splitLine ? gd_line_vis(sc, walls, frags, wallIndex, side, x)
+                      : wv.visL[side] + ((i64)x - wv.visSl[side]) * wv.visStep[side];
   bool psFromFront = curSector == gd_wsec(sc, psPathIndex * 2);
   int psOther = psFromFront ? gd_wsec(sc, psPathIndex * 2 + 1) : gd_wsec(sc, psPathIndex * 2);
   bool pskpp = hasProjectedSolidOwner && hSel.geo && psOther >= 0;
@@ -324,6 +335,9 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
   /* the row bounds feed tiers, marks, clips and events, all of which need a
    * raster-valid crossing */
   if (!rasterValid) {
+  } else if (splitLine) {
+    oneTop = gd_line_rows(sc, v, walls, frags, wallIndex, viewCeil, x);
+    oneBottom = gd_line_rows(sc, v, walls, frags, wallIndex, viewFloor, x);
   } else if (slotCur >= 0) {
     oneBottom = gd_rowproj_eval(v, wv, rp[slotCur], x);
     oneTop = gd_rowproj_eval(v, wv, rp[slotCur + 1], x);
@@ -334,7 +348,10 @@ __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWal
   int lowerTop = 0, upperBottom = 0;
   if (!oneSided && rasterValid) {  /* the tiers and clips below use them only for two-sided lines */
     int slotOther = (renderOther >= 0 && renderOther == back) ? 2 : ((renderOther >= 0 && renderOther == front) ? 0 : -1);
-    if (slotOther >= 0) {
+    if (splitLine) {
+      lowerTop = gd_line_rows(sc, v, walls, frags, wallIndex, otherFloor, x);
+      upperBottom = gd_line_rows(sc, v, walls, frags, wallIndex, otherCeil, x);
+    } else if (slotOther >= 0) {
       lowerTop = gd_rowproj_eval(v, wv, rp[slotOther], x);
       upperBottom = gd_rowproj_eval(v, wv, rp[slotOther + 1], x);
     } else {
@@ -530,6 +547,7 @@ __device__ __forceinline__ i64 gd_masked_iscale(i64 swall) {
   return s;
 }
 
+template <bool kSplit>
 __device__ __noinline__ void gd_masked_pass(const GdScene &sc, const GdView &v, const GdShared &sh) {
   const int x = threadIdx.x;
   float rx, ry;
@@ -558,8 +576,8 @@ __device__ __noinline__ void gd_masked_pass(const GdScene &sc, const GdView &v, 
   const float worldTop = fminf(gd_sec_ceil(sc, front), gd_sec_ceil(sc, back));
   const int4 ti = *reinterpret_cast<const int4 *>(&sc.texInfo[texId * 4]);
   const int tw = ti.x, th = ti.y, hbits = ti.w;
-  const i64 owallTop = gd_project_rows(v, wv, worldTop, x);
-  const i64 owallBottom = gd_project_rows(v, wv, worldTop - (float)th, x);
+  const i64 owallTop = gd_rows<kSplit>(sc, v, sh, w, worldTop, x);
+  const i64 owallBottom = gd_rows<kSplit>(sc, v, sh, w, worldTop - (float)th, x);
   const unsigned info = sh.maskedInfo[x];
   const bool hasSaved = (int)(info >> 16) == w;
   const i64 ceilClip = gd_max(owallTop, hasSaved ? (i64)((info >> 8) & 0xFF) : 0);
@@ -597,7 +615,8 @@ __device__ __noinline__ void gd_masked_pass(const GdScene &sc, const GdView &v, 
   const float *wl = &sc.walls[w * 4];
   const bool horizontal = fabsf(wl[3] - wl[1]) < 1e-6f, vertical = fabsf(wl[2] - wl[0]) < 1e-6f;
   const i64 light = gd_sec_info(sc, lightSector).x + v.flashLight * 16 + (vertical ? 16 : (horizontal ? -16 : 0));
-  const i64 vis = wv.visL[side] + ((i64)x - wv.visSl[side]) * wv.visStep[side];
+  const i64 vis = kSplit ? gd_line_vis(sc, sh.walls, sh.frags, w, side, x)
+                         : wv.visL[side] + ((i64)x - wv.visSl[side]) * wv.visStep[side];
   const uint8_t *cm = sh.colormap + gd_wall_shade(light, vis) * 256;
   const uint8_t *col = sc.texAtlasCol + ((size_t)texId * sc.texW + u) * sc.texH;
   const unsigned base = (unsigned)(gd_shl(texMid, 16 - hbits) + (gd_wmul(vstep, GD_FU - v.center) >> 16));
@@ -642,6 +661,7 @@ __device__ void gd_mark_afterlife_columns(const GdScene &sc, const GdShared &sh)
   }
 }
 
+template <bool kSplit>
 __device__ void gd_walk(const GdScene &sc, const GdView &v, const GdShared &sh, GdEvent *events, int *eventCount,
                         const GdRowProj *rowproj, int *status, int startSector) {
   const int x = threadIdx.x;
@@ -669,7 +689,7 @@ __device__ void gd_walk(const GdScene &sc, const GdView &v, const GdShared &sh, 
     if (__all_sync(0xffffffffu, settled)) break;
     GdIter it;
     if (!settled) {
-      gd_column_decide(sc, v, sh.walls, sh.ownerMask, rowproj, sh.hitD, sh.hitA, sh.hitF, x, rx, ry, c, it);
+      gd_column_decide<kSplit>(sc, v, sh.walls, sh.frags, sh.ownerMask, rowproj, sh.hitD, sh.hitA, sh.hitF, x, rx, ry, c, it);
     } else {
       it.wall = -1 - x; it.side = 0; it.tier[0] = it.tier[1] = it.tier[2] = false;
       it.ctop = it.clowtop = 0; it.cbot = it.cupbot = 0; it.vis = 0;
@@ -795,13 +815,13 @@ __device__ void gd_walk(const GdScene &sc, const GdView &v, const GdShared &sh, 
      * (engine.py:12965-13069) */
     if (it.pskpp) {
       int pIdx = it.psPathIndex;
-      const GdWall &pw = sh.walls[pIdx];
       int pSafeOther = it.psOther < 0 ? 0 : it.psOther;
       float pOtherFloor = gd_sec_floor(sc, pSafeOther), pOtherCeil = gd_sec_ceil(sc, pSafeOther);
       int pSide = it.psFromFront ? 0 : 1;
       const int32_t *ptex = &sc.sideTex[(pIdx * 2 + pSide) * 3];
-      int pTop = gd_project_rows(v, pw, it.viewCeil, x), pBottom = gd_project_rows(v, pw, it.viewFloor, x);
-      int pLowerTop = gd_project_rows(v, pw, pOtherFloor, x), pUpperBottom = gd_project_rows(v, pw, pOtherCeil, x);
+      int pTop = gd_rows<kSplit>(sc, v, sh, pIdx, it.viewCeil, x), pBottom = gd_rows<kSplit>(sc, v, sh, pIdx, it.viewFloor, x);
+      int pLowerTop = gd_rows<kSplit>(sc, v, sh, pIdx, pOtherFloor, x);
+      int pUpperBottom = gd_rows<kSplit>(sc, v, sh, pIdx, pOtherCeil, x);
       int pct = max(pTop, c.ceilClip), pcb = min(pBottom, c.floorClip);
       int pcub = max(min(pUpperBottom, c.floorClip), pct);
       int pclt = min(max(pLowerTop, c.ceilClip), pcb);

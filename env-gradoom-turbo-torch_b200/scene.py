@@ -125,6 +125,7 @@ class GridSpec:
     weapon: bool = True
     items: int = 0               # map items (pickups) at seeded positions, cycling through the animated kinds
     decals: bool = False         # carry bullet-chip decal bitmaps and their blend tables
+    splits: float = 0.0          # share of lines a node builder "split" into two or three projection fragments
 
 
 # The five workloads of the benchmark definition, by name.
@@ -150,6 +151,11 @@ GRID_CONFIGS = {
                     floor_max=64, decals=True),
     "c4d": GridSpec(rows=8, cols=8, room=128.0, seed=4, wall_textures=16,
                     tex_w=128, tex_h=128, flats=8, floor_max=128, diagonals=True, decals=True),
+    # c1 and the quarter-size diagonal map with 40 % of their lines split into projection fragments
+    "c1s": GridSpec(rows=4, cols=4, room=256.0, seed=1, wall_textures=8, flats=4,
+                    floor_max=64, splits=0.4),
+    "c4s": GridSpec(rows=8, cols=8, room=128.0, seed=4, wall_textures=16,
+                    tex_w=128, tex_h=128, flats=8, floor_max=128, diagonals=True, splits=0.4),
 }
 
 
@@ -202,6 +208,27 @@ def _synthetic_decals(spec: GridSpec, colormap: np.ndarray) -> dict:
     return {"atlas": atlas, "heights": heights, "left": np.asarray((3, 4, 3, 2, 3), dtype=np.int32),
             "top": np.asarray((4, 3, 4, 2, 3), dtype=np.int32), "opacity_lut": decal_opacity_lut(),
             "black_lut": np.ascontiguousarray(colormap[rows]).astype(np.uint8)}
+
+
+def synthetic_fragments(walls: np.ndarray, share: float, seed: int) -> dict:
+    """Split a seeded share of the lines into two or three fragments at interior points, some of
+    them a few fixed-point units off the line, as a node builder's rounded intersections are."""
+
+    rng = np.random.default_rng(seed)
+    fixed = np.rint(walls.astype(np.float64) * FIXED_UNIT).astype(np.int64)
+    out = {}
+    for w in np.flatnonzero(rng.random(len(walls)) < share):
+        a, b = fixed[w, :2], fixed[w, 2:]
+        cuts = (0.5,) if rng.random() < 0.6 else (float(rng.choice((0.25, 0.375))), 0.75)
+        points = [a]
+        for t in cuts:
+            point = a + np.rint((b - a) * t).astype(np.int64)
+            if rng.random() < 0.5:
+                point = point + rng.integers(-3, 4, size=2)
+            points.append(point)
+        points.append(b)
+        out[int(w)] = np.asarray([(*points[i], *points[i + 1]) for i in range(len(points) - 1)], dtype=np.int64)
+    return out
 
 
 def _scene_meta(spec: GridSpec, static_ids, patches) -> dict:
@@ -466,7 +493,8 @@ def make_grid_scene(spec: GridSpec) -> Scene:
         hud_heights=hud_heights,
         hud_left=hud_left,
         hud_top=hud_top,
-        meta=dict(_scene_meta(spec, None, P), **({"decals": _synthetic_decals(spec, colormap)} if spec.decals else {})),
+        meta=dict(_scene_meta(spec, None, P), **({"decals": _synthetic_decals(spec, colormap)} if spec.decals else {}),
+                  **({"fragments": synthetic_fragments(walls, spec.splits, spec.seed + 4000)} if spec.splits > 0 else {})),
     )
 
 
@@ -486,14 +514,18 @@ def from_compiled_scenario(cs) -> Scene:
         value = getattr(cs, name, None)
         return np.asarray(default if value is None else value)
 
-    # every line is one fragment unless a node builder split it (src/gradoom/scenario.py:420-455);
-    # split lines are outside this render path
+    # every line is one fragment unless a node builder split it (src/gradoom/scenario.py:420-455)
     fragment_mask = getattr(cs, "wall_projection_fragment_mask", None)
     fragments = getattr(cs, "wall_projection_fragments_fixed", None)
-    split = (fragment_mask is not None and np.asarray(fragment_mask)[:, 1:].any()) or \
-            (fragment_mask is None and fragments is not None and np.asarray(fragments).shape[1] > 1)
-    if split:
-        raise ValueError("scenarios with node-builder wall fragments are not supported by this render path")
+    if (fragment_mask is None) != (fragments is None):
+        raise ValueError("wall projection fragments and their mask must be provided together")
+    split_lines = {}
+    if fragments is not None:
+        fragments, fragment_mask = np.asarray(fragments), np.asarray(fragment_mask).astype(bool)
+        if fragments.shape[:2] != fragment_mask.shape or fragments.shape[2:] != (4,):
+            raise ValueError("invalid wall projection fragment arrays")
+        for line in np.flatnonzero(fragment_mask.sum(axis=1) > 1):
+            split_lines[int(line)] = fragments[line][fragment_mask[line]].astype(np.int64)
     spr_atlas = need("raw_sprite_atlas")
     last_sprite = max(len(spr_atlas) - 1, 0)
     wpn_atlas = getattr(cs, "native_weapon_patch_atlas", None)
@@ -510,6 +542,8 @@ def from_compiled_scenario(cs) -> Scene:
     if len(item_types):
         meta["items"] = {"spawns": np.asarray(cs.item_spawns, dtype=np.float32), "types": item_types.astype(np.int32),
                          "anim_ids": maybe("raw_item_animation_sprite_ids", np.zeros(8, np.int32)).astype(np.int32)}
+    if split_lines:
+        meta["fragments"] = split_lines
     if getattr(cs, "bullet_decal_atlas", None) is not None:
         meta["decals"] = {"atlas": need("bullet_decal_atlas").astype(np.uint8),
                           "heights": need("bullet_decal_heights").astype(np.int32),
@@ -575,7 +609,7 @@ _HEADER_WORDS = (
     "MAGIC VERSION BYTES WALLS SECTORS VERTICES TEXTURES TEX_H TEX_W SPRITES SPR_H SPR_W "
     "WPN_PATCHES WPN_H WPN_W WPN_TICS STARTS DEATH_FRAMES XDEATH_FRAMES BLOCKING NB_DIRECT "
     "WPN_AVAILABLE HUD_PATCHES UNSUPPORTED SEC_WALLS_N VTX_WALLS_N MASKED_WALLS_N FLOOR_GROUPS CEIL_GROUPS ITEMS "
-    "DECALS DECAL_H DECAL_W"
+    "DECALS DECAL_H DECAL_W FRAGMENTS"
 ).split()
 H = {name: i for i, name in enumerate(_HEADER_WORDS)}
 
@@ -589,7 +623,8 @@ _SECTIONS = (
     "WPN_ATLAS WPN_OPAQUE WPN_FRAME_IDS WPN_FLASH_IDS WPN_FLASH_LIGHTS HUD_INFO HUD_ATLAS "
     "HUD_OPAQUE FINESINE FINETAN STARTS RAY_OFFSETS RAY_COSCORR TEX_ATLAS_COL SECTOR_BBOX "
     "MASKED_WALLS DAMAGE_ALPHA FLOOR_GROUP_H FLOOR_GROUP_OFF FLOOR_GROUP_SEC CEIL_GROUP_H CEIL_GROUP_OFF "
-    "CEIL_GROUP_SEC ITEM_POS ITEM_INFO ITEM_ANIM DECAL_INFO DECAL_ATLAS DECAL_OPACITY DECAL_BLACK WALL_FINE"
+    "CEIL_GROUP_SEC ITEM_POS ITEM_INFO ITEM_ANIM DECAL_INFO DECAL_ATLAS DECAL_OPACITY DECAL_BLACK WALL_FINE "
+    "FRAG_OFF FRAG_FIXED"
 ).split()
 SEC = {name: i for i, name in enumerate(_SECTIONS)}
 
@@ -831,6 +866,22 @@ def pack_scene(scene: Scene, ray_table_override=None) -> np.ndarray:
     def info4(a, b, c, d):
         return np.stack((a, b, c, d), axis=1).astype(np.int32)
 
+    # Projection fragments of lines a node builder split (src/gradoom/scenario.py:420-455,
+    # engine.py:745-767): an optional meta["fragments"] = {wall index: (F,4) int64 16.16 endpoints,
+    # in order}.  Lines absent from it, or with a single fragment, project as a whole.
+    frag_off = np.zeros(W + 1, dtype=np.int32)
+    frag_rows = []
+    for w_, pieces in sorted((scene.meta.get("fragments") or {}).items()):
+        pieces = np.asarray(pieces, dtype=np.int64).reshape(-1, 4)
+        if not 0 <= w_ < W:
+            raise ValueError(f"fragments given for line {w_}, the scene has {W}")
+        if len(pieces) > 1:
+            frag_off[w_ + 1] = len(pieces)
+            frag_rows.append(pieces)
+    frag_off = np.cumsum(frag_off).astype(np.int32)
+    n_fragments = int(frag_off[-1])
+    frag_fixed = (np.concatenate(frag_rows) if frag_rows else np.zeros((1, 4), dtype=np.int64)).astype(np.int32)
+
     # Bullet-chip decals (src/gradoom/scenario.py:280-300, engine.py:1038-1068): an optional
     # meta["decals"] = {"atlas": (V,h,w) u8, "heights", "left", "top": (V,), "opacity_lut": (32,256),
     # "black_lut": (65,256)}.  Without it the decal layer draws nothing, as the reference's zero atlas.
@@ -941,6 +992,7 @@ def pack_scene(scene: Scene, ray_table_override=None) -> np.ndarray:
         "ITEM_POS": item_pos, "ITEM_INFO": item_info, "ITEM_ANIM": item_anim,
         "DECAL_INFO": decal_info, "DECAL_ATLAS": decal_atlas, "DECAL_OPACITY": decal_opacity,
         "DECAL_BLACK": decal_black, "WALL_FINE": wall_fine_angles(walls),
+        "FRAG_OFF": frag_off, "FRAG_FIXED": frag_fixed,
     }
     assert set(sections) == set(SEC), set(SEC) ^ set(sections)
 
@@ -949,7 +1001,7 @@ def pack_scene(scene: Scene, ray_table_override=None) -> np.ndarray:
     cursor = GD_HDR_WORDS * 4
     for name in _SECTIONS:
         data = np.ascontiguousarray(sections[name]).view(np.uint8).reshape(-1)
-        pad = (-cursor) % 16
+        pad = (-cursor) % 128        # a texture column of 128 texels then lies in one 128-byte line
         if pad:
             chunks.append(np.zeros(pad, dtype=np.uint8))
             cursor += pad
@@ -992,6 +1044,7 @@ def pack_scene(scene: Scene, ray_table_override=None) -> np.ndarray:
     header[H["CEIL_GROUPS"]] = int(ceil_groups[0].size)
     header[H["ITEMS"]] = n_items
     header[H["DECALS"]] = n_decals
+    header[H["FRAGMENTS"]] = n_fragments
     header[H["DECAL_H"]] = decal_atlas.shape[1]
     header[H["DECAL_W"]] = decal_atlas.shape[2]
     blob = np.concatenate([header.view(np.uint8)] + chunks)

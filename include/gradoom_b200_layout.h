@@ -3,7 +3,7 @@
  * blob (one per device) and the per-lane state records.  Plain C so that the
  * CUDA library, the CPU oracle and any foreign-function binding agree on it.
  *
- * Scene blob: `GD_HDR_WORDS` int32 words, then 16-byte aligned sections.  Word
+ * Scene blob: `GD_HDR_WORDS` int32 words, then 128-byte aligned sections.  Word
  * GD_H_* holds a count; word GD_HDR_SECTION0 + GD_S_* holds the byte offset of
  * a section from the start of the blob.  The field meanings follow the
  * reference's device scene (src/gradoom/engine.py:607-1476, DeviceScenario).
@@ -60,6 +60,7 @@ enum gd_header_word {
   GD_H_DECALS,       /* bullet-chip variants (0: the scene carries no decal bitmaps) */
   GD_H_DECAL_H,      /* atlas slice height */
   GD_H_DECAL_W,      /* atlas slice width = the width of every chip */
+  GD_H_FRAGMENTS,    /* entries of GD_S_FRAG_FIXED: projection fragments of the lines a node builder split */
   GD_H_COUNT
 };
 
@@ -146,6 +147,9 @@ enum gd_section {
   GD_S_DECAL_BLACK,     /* 65 x 256 u8 [opacity][palette index] -> darkened palette index (scenario.py:269-272) */
   GD_S_WALL_FINE,       /* W x 2 i32: fine angle (0..8191) of the wall's direction seen from side 0 / side 1,
                            the tangent a chip on that side is laid out along (src/gradoom/engine.py:13818-13830) */
+  GD_S_FRAG_OFF,        /* W+1 i32 CSR into GD_S_FRAG_FIXED; a line that was not split has an empty range */
+  GD_S_FRAG_FIXED,      /* fragments x 4 i32: x1 y1 x2 y2 in 16.16, the pieces of a split line in the node
+                           builder's order (src/gradoom/scenario.py:420-455, engine.py:745-767) */
   GD_S_COUNT
 };
 

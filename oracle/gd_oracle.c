@@ -84,6 +84,8 @@ typedef struct {
   const float *starts;
   const float *rayOffsets, *rayCosCorr;
   int decals, decalH, decalW;
+  int F;                               /* projection fragments of split lines */
+  const int32_t *fragOff, *fragFixed;
   const int32_t *decalInfo, *wallFine;
   const uint8_t *decalAtlas, *decalOpacity, *decalBlack;
 } Scene;
@@ -188,6 +190,9 @@ static int scene_open(Scene *sc, const uint8_t *blob) {
   sc->decalOpacity = sec_ptr(blob, GD_S_DECAL_OPACITY);
   sc->decalBlack = sec_ptr(blob, GD_S_DECAL_BLACK);
   sc->wallFine = sec_ptr(blob, GD_S_WALL_FINE);
+  sc->F = h[GD_H_FRAGMENTS];
+  sc->fragOff = sec_ptr(blob, GD_S_FRAG_OFF);
+  sc->fragFixed = sec_ptr(blob, GD_S_FRAG_FIXED);
   return 0;
 }
 
@@ -229,6 +234,7 @@ typedef struct {
 typedef struct {
   int W;
   WallView *wv;
+  WallView *frag;  /* [F] FWallCoords and wallscan light of every projection fragment */
   float *dist;     /* [SW][W] inf when invalid */
   float *along;    /* clamped to [0,1] */
   uint8_t *geo, *proj, *left;
@@ -309,6 +315,22 @@ static void wall_visibility(i64 tx1, i64 ty1, i64 tx2, i64 ty2, i64 *visL, i64 *
   *visSl = wsl;
 }
 
+/* View coordinates, FWallCoords and wallscan light of a segment given by its 16.16 endpoints. */
+static void project_fixed(const View *v, const i64 fx[2], const i64 fy[2], WallView *wv) {
+  for (int e = 0; e < 2; ++e) {
+    i64 rx = fx[e] - v->vx, ry = fy[e] - v->vy;
+    wv->tx[e] = (rx * v->vsin - ry * v->vcos) >> 20;
+    wv->ty[e] = (rx * v->vcos + ry * v->vsin) >> 20;
+  }
+  i64 wvx = fx[1] - fx[0], wvy = fy[1] - fy[0];
+  i64 fsx = v->vx - fx[0], fsy = v->vy - fy[0];
+  int ff = (wvx * fsy - wvy * fsx) < 0;
+  int a = ff ? 0 : 1, b = ff ? 1 : 0;
+  fwall_coords(wv->tx[a], wv->ty[a], wv->tx[b], wv->ty[b], &wv->sl, &wv->sr, &wv->dl, &wv->dr);
+  wall_visibility(wv->tx[0], wv->ty[0], wv->tx[1], wv->ty[1], &wv->visL[0], &wv->visStep[0], &wv->visSl[0]);
+  wall_visibility(wv->tx[1], wv->ty[1], wv->tx[0], wv->ty[0], &wv->visL[1], &wv->visStep[1], &wv->visSl[1]);
+}
+
 static void lane_geometry(const Scene *sc, const View *v, LaneGeom *g) {
   int W = sc->W;
   g->W = W;
@@ -317,22 +339,18 @@ static void lane_geometry(const Scene *sc, const View *v, LaneGeom *g) {
     g->dirx[x] = v->fcos + v->fsin * c;
     g->diry[x] = v->fsin - v->fcos * c;
   }
+  /* the pieces of the lines a node builder split: the same projection, from their own
+   * fixed-point endpoints (engine.py:11478-11500, 10747-10869) */
+  for (int f = 0; f < sc->F; ++f) {
+    const int32_t *q = &sc->fragFixed[f * 4];
+    i64 fx[2] = {q[0], q[2]}, fy[2] = {q[1], q[3]};
+    project_fixed(v, fx, fy, &g->frag[f]);
+  }
   for (int w = 0; w < W; ++w) {
     WallView *wv = &g->wv[w];
     i64 fx[2] = {wall_fixed(sc, w, 0), wall_fixed(sc, w, 2)};
     i64 fy[2] = {wall_fixed(sc, w, 1), wall_fixed(sc, w, 3)};
-    for (int e = 0; e < 2; ++e) {
-      i64 rx = fx[e] - v->vx, ry = fy[e] - v->vy;
-      wv->tx[e] = (rx * v->vsin - ry * v->vcos) >> 20;
-      wv->ty[e] = (rx * v->vcos + ry * v->vsin) >> 20;
-    }
-    i64 wvx = fx[1] - fx[0], wvy = fy[1] - fy[0];
-    i64 fsx = v->vx - fx[0], fsy = v->vy - fy[0];
-    int ff = (wvx * fsy - wvy * fsx) < 0;
-    int a = ff ? 0 : 1, b = ff ? 1 : 0;
-    fwall_coords(wv->tx[a], wv->ty[a], wv->tx[b], wv->ty[b], &wv->sl, &wv->sr, &wv->dl, &wv->dr);
-    wall_visibility(wv->tx[0], wv->ty[0], wv->tx[1], wv->ty[1], &wv->visL[0], &wv->visStep[0], &wv->visSl[0]);
-    wall_visibility(wv->tx[1], wv->ty[1], wv->tx[0], wv->ty[0], &wv->visL[1], &wv->visStep[1], &wv->visSl[1]);
+    project_fixed(v, fx, fy, wv);
     wv->oneSided = sc->wsec[w * 2 + 1] < 0;
 
     /* float ray tests for every column (engine.py:11317-11331) */
@@ -494,6 +512,45 @@ static void prep_wall(const Scene *sc, const WallView *wv, int w, int x, i64 *ho
 }
 
 /* OWallMost row projection (engine.py:12294-12605), single-fragment walls. */
+/* The unclipped whole-line projection: what a column of a split line falls back to when none of
+ * the line's fragments owns it (engine.py:12393-12410, 12596-12604). */
+static i64 project_rows_whole(const View *v, const WallView *wv, float worldZ, int x) {
+  i64 wsl = wv->sl, wsr = wv->sr;
+  i64 wdl = imax(wv->dl, 1), wdr = imax(wv->dr, 1);
+  i64 relZ = rint_f((worldZ - v->viewZ) * 65536.0f);
+  i64 pz = -(relZ >> 4);
+  i64 ospan = imax(wsr - wsl, 1);
+  i64 opl = (pz * FOCAL_Y) / wdl, opr = (pz * FOCAL_Y) / wdr;
+  i64 ostep = (opr - opl) / ospan;
+  return iclamp((v->center + opl + (x - wsl) * ostep) >> 16, 0, VH);
+}
+
+static i64 project_rows(const View *v, const WallView *wv, float worldZ, int x);
+
+/* Which FWallCoords the row projection and the wallscan light of line w use at column x: the
+ * line itself, or, for a split line, the first of its fragments whose span holds the column
+ * (engine.py:12310-12376, 11511-11545); NULL when the line is split and no fragment does. */
+static const WallView *projection_fragment(const Scene *sc, const LaneGeom *g, int w, int x) {
+  int f0 = sc->fragOff[w], f1 = sc->fragOff[w + 1];
+  if (sc->F <= 0 || f1 <= f0) return &g->wv[w];
+  for (int f = f0; f < f1; ++f) {
+    const WallView *q = &g->frag[f];
+    if (q->sr > q->sl && x >= q->sl && x < q->sr) return q;
+  }
+  return NULL;
+}
+
+static i64 line_rows(const Scene *sc, const View *v, const LaneGeom *g, int w, float worldZ, int x) {
+  const WallView *q = projection_fragment(sc, g, w, x);
+  return q ? project_rows(v, q, worldZ, x) : project_rows_whole(v, &g->wv[w], worldZ, x);
+}
+
+static i64 line_vis(const Scene *sc, const LaneGeom *g, int w, int side, int x) {
+  const WallView *q = projection_fragment(sc, g, w, x);
+  if (!q) q = &g->wv[w];
+  return q->visL[side] + ((i64)x - q->visSl[side]) * q->visStep[side];
+}
+
 static i64 project_rows(const View *v, const WallView *wv, float worldZ, int x) {
   i64 wsl = wv->sl, wsr = wv->sr;
   i64 wdl = imax(wv->dl, 1), wdr = imax(wv->dr, 1);
@@ -874,7 +931,7 @@ static void wall_pass(const Scene *sc, const View *v, const LaneGeom *g, LaneBuf
       int renderOther = renderFromFront ? back : front;
       int side = !renderFromFront;
       const WallView *wv = &g->wv[wallIndex];
-      i64 vis = wv->visL[side] + ((i64)x - wv->visSl[side]) * wv->visStep[side];
+      i64 vis = line_vis(sc, g, wallIndex, side, x);
       int psFromFront = curSector == sc->wsec[psPathIndex * 2];
       int psOther = psFromFront ? sc->wsec[psPathIndex * 2 + 1] : sc->wsec[psPathIndex * 2];
       int psIsGeo = G[psPathIndex];
@@ -884,8 +941,8 @@ static void wall_pass(const Scene *sc, const View *v, const LaneGeom *g, LaneBuf
       float otherFloor = sec_floor(sc, safeOther), otherCeil = sec_ceil(sc, safeOther);
       int oneSided = otherSector < 0;
       const int32_t *stex = &sc->sideTex[(wallIndex * 2 + side) * 3];
-      i64 oneTop = project_rows(v, wv, viewCeil, x), oneBottom = project_rows(v, wv, viewFloor, x);
-      i64 lowerTop = project_rows(v, wv, otherFloor, x), upperBottom = project_rows(v, wv, otherCeil, x);
+      i64 oneTop = line_rows(sc, v, g, wallIndex, viewCeil, x), oneBottom = line_rows(sc, v, g, wallIndex, viewFloor, x);
+      i64 lowerTop = line_rows(sc, v, g, wallIndex, otherFloor, x), upperBottom = line_rows(sc, v, g, wallIndex, otherCeil, x);
       i64 ctop = imax(oneTop, c->ceilClip), cbot = imin(oneBottom, c->floorClip);
       i64 cupbot = imax(imin(upperBottom, c->floorClip), ctop);
       i64 clowtop = imin(imax(lowerTop, c->ceilClip), cbot);
@@ -1072,8 +1129,8 @@ static void wall_pass(const Scene *sc, const View *v, const LaneGeom *g, LaneBuf
           float pOtherFloor = sec_floor(sc, pSafeOther), pOtherCeil = sec_ceil(sc, pSafeOther);
           int pSide = !t->psFromFront;
           const int32_t *ptex = &sc->sideTex[(pIdx * 2 + pSide) * 3];
-          i64 pTop = project_rows(v, pw, it->viewCeil, x), pBottom = project_rows(v, pw, it->viewFloor, x);
-          i64 pLowerTop = project_rows(v, pw, pOtherFloor, x), pUpperBottom = project_rows(v, pw, pOtherCeil, x);
+          i64 pTop = line_rows(sc, v, g, pIdx, it->viewCeil, x), pBottom = line_rows(sc, v, g, pIdx, it->viewFloor, x);
+          i64 pLowerTop = line_rows(sc, v, g, pIdx, pOtherFloor, x), pUpperBottom = line_rows(sc, v, g, pIdx, pOtherCeil, x);
           i64 pct = imax(pTop, c->ceilClip), pcb = imin(pBottom, c->floorClip);
           i64 pcub = imax(imin(pUpperBottom, c->floorClip), pct);
           i64 pclt = imin(imax(pLowerTop, c->ceilClip), pcb);
@@ -1339,8 +1396,8 @@ static void masked_pass(const Scene *sc, const View *v, const LaneGeom *g, LaneB
     float worldTop = fminf(sec_ceil(sc, front), sec_ceil(sc, back));
     const int32_t *ti = &sc->texInfo[texId * 4];
     int tw = ti[0], th = ti[1], hbits = ti[3];
-    i64 owallTop = project_rows(v, wv, worldTop, x);
-    i64 owallBottom = project_rows(v, wv, worldTop - (float)th, x);
+    i64 owallTop = line_rows(sc, v, g, w, worldTop, x);
+    i64 owallBottom = line_rows(sc, v, g, w, worldTop - (float)th, x);
     int hasSaved = lb->maskedWall[x] == w;
     i64 ceilClip = imax(owallTop, hasSaved ? lb->maskedCeil[x] : 0);
     i64 floorClip = imin(owallBottom, hasSaved ? lb->maskedFloor[x] : VH);
@@ -1377,7 +1434,7 @@ static void masked_pass(const Scene *sc, const View *v, const LaneGeom *g, LaneB
     const float *wl = &sc->walls[w * 4];
     int horizontal = fabsf(wl[3] - wl[1]) < 1e-6f, vertical = fabsf(wl[2] - wl[0]) < 1e-6f;
     i64 light = sec_light(sc, lightSector) + v->flashLight * 16 + (vertical ? 16 : (horizontal ? -16 : 0));
-    i64 vis = wv->visL[side] + ((i64)x - wv->visSl[side]) * wv->visStep[side];
+    i64 vis = line_vis(sc, g, w, side, x);
     int shade = wall_shade(light, vis);
     for (i64 y = imax(clippedTop, 0); y < imin(clippedBottom, VH); ++y) {
       i64 screenDelta = y * FU - v->center + FU;
@@ -1895,11 +1952,12 @@ static Ctx *ctx_new(const uint8_t *blob) {
   c->g.left = malloc((size_t)SW * W);
   c->g.eoIdx = malloc(sizeof(int32_t) * SW * (size_t)W);
   c->g.eoDist = malloc(sizeof(float) * SW * (size_t)W);
+  c->g.frag = calloc((size_t)(c->sc.F > 0 ? c->sc.F : 1), sizeof(WallView));
   c->lb = malloc(sizeof(LaneBuffers));
   return c;
 }
 static void ctx_free(Ctx *c) {
-  free(c->g.wv); free(c->g.dist); free(c->g.along); free(c->g.geo); free(c->g.proj); free(c->g.left);
+  free(c->g.frag); free(c->g.wv); free(c->g.dist); free(c->g.along); free(c->g.geo); free(c->g.proj); free(c->g.left);
   free(c->g.eoIdx); free(c->g.eoDist); free(c->lb); free(c);
 }
 

@@ -83,7 +83,20 @@ def scene_to_compiled(scene, scenario_module):
     middle = scene.side_textures[:, 0, 0]
     items = scene.meta.get("items")
     decals = scene.meta.get("decals") or {}
+    fragments = fragment_mask = None
+    split = scene.meta.get("fragments")
+    if split:
+        most = max(len(pieces) for pieces in split.values())
+        fragments = np.zeros((W, most, 4), dtype=np.int64)
+        fragment_mask = np.zeros((W, most), dtype=np.bool_)
+        fragments[:, 0] = np.rint(walls.astype(np.float64) * 65536.0).astype(np.int64)
+        fragment_mask[:, 0] = True
+        for line, pieces in split.items():
+            fragments[line, : len(pieces)] = pieces
+            fragment_mask[line, : len(pieces)] = True
     return scenario_module.CompiledScenario(
+        wall_projection_fragments_fixed=fragments,
+        wall_projection_fragment_mask=fragment_mask,
         bullet_decal_atlas=decals.get("atlas"),
         bullet_decal_heights=decals.get("heights"),
         bullet_decal_left_offsets=decals.get("left"),

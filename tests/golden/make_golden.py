@@ -3,7 +3,7 @@
 Run once on a machine that has the upstream sources:
 
     GRADOOM_REFERENCE_SRC=<upstream checkout>/src/gradoom python tests/golden/make_golden.py \
-        [c1 c2 c3 c4 c1m stack flashes pitch fallback c2d c4d c1k state move_c1 move_c2 decals_c1 decals_c4]
+        [c1 c2 c3 c4 c1m stack flashes pitch fallback c2d c4d c1k state move_c1 move_c2 decals_c1 decals_c4 c1s c4s]
 
 For each seeded synthetic scene it resets the upstream engine, injects K
 monsters per lane, replays a seeded uniform action stream and, at a few
@@ -48,6 +48,9 @@ PLANS = {
     # deeper action streams on the two benchmark maps
     "c2d": ("c2", 8, 12, (0, 50, 150)),
     "c4d": ("c4", 4, 32, (0, 20, 60)),
+    # lines split into projection fragments (engine.py:745-767, 11478-11545, 12310-12376)
+    "c1s": ("c1s", 4, 4, (0, 12, 30)),
+    "c4s": ("c4s", 4, 8, (0, 10, 25)),
 }
 # Plans whose skipped steps run with the upstream default (fast) observation renderer: the
 # game dynamics never read a rendered frame, so the state at a checkpoint is the same

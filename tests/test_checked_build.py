@@ -30,7 +30,7 @@ def _bits(r):
     return bits
 
 
-@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4", "c1m", "pitch", "fallback", "c2d", "c4d", "c1k", "state"])
+@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4", "c1m", "pitch", "fallback", "c2d", "c4d", "c1k", "state", "c1s", "c4s"])
 def test_fixtures_are_clean_and_equal_under_the_checked_build(name, pkg, scenes):
     data = load_golden(name)
     _sc, blob = scenes(str(data["config"]), (data["ray_offsets"], data["ray_coscorr"]))

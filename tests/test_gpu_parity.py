@@ -30,7 +30,7 @@ def _dev(a):
     return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
 
 
-@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4", "c1m", "pitch", "fallback", "c2d", "c4d", "c1k"])
+@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4", "c1m", "pitch", "fallback", "c2d", "c4d", "c1k", "c1s", "c4s"])
 def test_cuda_matches_upstream_fixtures(name, pkg, oracle, scenes):
     data = load_golden(name)
     _sc, blob = scenes(str(data["config"]), (data["ray_offsets"], data["ray_coscorr"]))
@@ -49,7 +49,7 @@ def test_cuda_matches_upstream_fixtures(name, pkg, oracle, scenes):
 
 @pytest.mark.parametrize("name,n,k,seed", [("c1", 64, 4, 1), ("c2", 96, 12, 2), ("c3", 48, 12, 3),
                                            ("c4", 12, 32, 4), ("c2", 1, 0, 5), ("c1", 3, 1, 6),
-                                           ("c1m", 48, 4, 7)])
+                                           ("c1m", 48, 4, 7), ("c1s", 64, 4, 8), ("c4s", 48, 8, 9)])
 def test_cuda_matches_oracle_on_seeded_lanes(name, n, k, seed, pkg, oracle, scenes):
     from gradoom_b200 import stepper
 

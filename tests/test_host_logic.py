@@ -159,17 +159,26 @@ def test_scene_from_the_reference_scenario_container(pkg, scenes):
     container = ref_engine.scene_to_compiled(sc, types.SimpleNamespace(CompiledScenario=types.SimpleNamespace))
     back = gdscene.from_compiled_scenario(container)
     assert np.array_equal(gdscene.pack_scene(back), blob)
-    # one fragment per line (what the upstream compiler writes for any map but its pinned one) is
-    # accepted; a line split by the node builder is refused
+    # one fragment per line (what the upstream compiler writes for any map but its pinned one) changes
+    # nothing; a line the node builder split arrives as projection fragments in the blob
     W = len(sc.walls)
     container.wall_projection_fragments_fixed = np.zeros((W, 2, 4), dtype=np.int64)
     container.wall_projection_fragment_mask = np.zeros((W, 2), dtype=bool)
     container.wall_projection_fragment_mask[:, 0] = True
     assert np.array_equal(gdscene.pack_scene(gdscene.from_compiled_scenario(container)), blob)
     container.wall_projection_fragment_mask[3, 1] = True
+    container.wall_projection_fragments_fixed[3] = ((0, 0, 65536, 0), (65536, 0, 131072, 3))
+    split = gdscene.pack_scene(gdscene.from_compiled_scenario(container))
+    header = split[: gdscene.GD_HDR_WORDS * 4].view(np.int32)
+    assert header[gdscene.H["FRAGMENTS"]] == 2
+    off = split[header[gdscene.GD_HDR_SECTION0 + gdscene.SEC["FRAG_OFF"]]:].view(np.int32)[: W + 1]
+    assert off[3] == 0 and off[4] == 2 and off[-1] == 2
+    fixed = split[header[gdscene.GD_HDR_SECTION0 + gdscene.SEC["FRAG_FIXED"]]:].view(np.int32)[:8]
+    assert fixed.tolist() == [0, 0, 65536, 0, 65536, 0, 131072, 3]
+    container.wall_projection_fragment_mask = None
     with pytest.raises(ValueError):
         gdscene.from_compiled_scenario(container)
-    container.wall_projection_fragment_mask[3, 1] = False
+    container.wall_projection_fragments_fixed = None
     container.texture_index_atlas = None
     with pytest.raises(ValueError):
         gdscene.from_compiled_scenario(container)

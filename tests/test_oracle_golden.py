@@ -12,7 +12,7 @@ import pytest
 from conftest import engine_from_fixture, load_golden
 
 
-@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4", "c1m", "pitch", "fallback", "c2d", "c4d", "c1k"])
+@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4", "c1m", "pitch", "fallback", "c2d", "c4d", "c1k", "c1s", "c4s"])
 def test_oracle_matches_upstream_indexed_frames(name, pkg, oracle, scenes):
     data = load_golden(name)
     _sc, blob = scenes(str(data["config"]), (data["ray_offsets"], data["ray_coscorr"]))
@@ -272,3 +272,24 @@ def test_oracle_draws_the_upstream_bullet_chips(name, floor, pkg, oracle, scenes
     assert np.array_equal(with_chips["indexed"], data["indexed_0"])
     bare = oracle.render(blob, data["lanes_0"], data["things_0"], mask_hud=False)
     assert int((bare["indexed"] != data["indexed_0"]).sum()) == int(data["changed_pixels"])
+
+
+def test_split_lines_change_what_the_fixtures_show(pkg, oracle, scenes):
+    """The fragment fixtures are not vacuous: the same lanes drawn from the scene without its
+    projection fragments differ from the upstream frames (engine.py:11511-11545, 12310-12376)."""
+
+    import dataclasses
+
+    from gradoom_b200 import scene as gdscene
+
+    for name in ("c1s", "c4s"):
+        data = load_golden(name)
+        sc, blob = scenes(str(data["config"]), (data["ray_offsets"], data["ray_coscorr"]))
+        assert gdscene.pack_scene(sc)[: gdscene.GD_HDR_WORDS * 4].view(np.int32)[gdscene.H["FRAGMENTS"]] > 30
+        whole = dataclasses.replace(sc, meta={k: v for k, v in sc.meta.items() if k != "fragments"})
+        whole_blob = gdscene.pack_scene(whole, ray_table_override=(data["ray_offsets"], data["ray_coscorr"]))
+        changed = 0
+        for ci in range(len(data["checkpoints"])):
+            frames = oracle.render(whole_blob, data[f"lanes_{ci}"], data[f"things_{ci}"], mask_hud=False)["indexed"]
+            changed += int((frames != data[f"indexed_{ci}"]).sum())
+        assert changed > 400
