@@ -330,7 +330,10 @@ def run_ours(args):
     workload = args.workload
     spec = WORKLOADS[workload]
     THINGS = spec["things"]
-    sc = gdscene.make_grid_scene(gdscene.GRID_CONFIGS[workload])
+    import dataclasses
+
+    grid = gdscene.GRID_CONFIGS[workload]
+    sc = gdscene.make_grid_scene(dataclasses.replace(grid, decals=True) if args.decals > 0 else grid)
     blob = gdscene.pack_scene(sc)
     n = args.lanes if args.lanes else spec["lanes"]
     # every rank draws the same seeded lane population (its lanes differ only in their global ids), so
@@ -360,6 +363,9 @@ def run_ours(args):
     lane_ids = torch.arange(n, device=device, dtype=torch.int64) + rank * n
     producer.reset(everyone, lane_ids + 1)
     lanes, things = producer.render_inputs()
+    if args.decals > 0:
+        rings = stepper.random_decals(sc, lanes.cpu().numpy(), min(args.decals, 64), 64, seed=5)
+        renderer.bind_decals(torch.from_numpy(rings).to(device))
     renderer.reset(lanes, things, everyone, stack)
     if use_ring:
         renderer.reset_ring(lanes, things, everyone, ring)
@@ -524,13 +530,14 @@ def run_ours(args):
             "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "i64+f32", "data": "synthetic",
             "config": {"workload": f"{workload}: {n} lanes/GPU, {spec['map']}, {THINGS} things/lane, "
-                                   + ("obs and RGB24 frame every step" if rgb is not None else "obs only"),
+                                   + ("obs and RGB24 frame every step" if rgb is not None else "obs only")
+                                   + (f", {min(args.decals, 64)} bullet chips/lane" if args.decals > 0 else ""),
                        "lanes_per_gpu": n, "l2": "flushed with a 256 MiB write between timed steps",
                        "ctas": renderer.ctas, "shared_bytes_per_cta": renderer.shared_bytes,
                        "stack_policy": "mirrored ring (write 2 of 8 slots per lane, no reads)" if use_ring
                        else "roll (read 3 + write 4 slots per lane)"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": traffic if (workload, n, rgb) == (WORKLOAD, 4096, None) else None,
+                         "traffic": traffic if (workload, n, rgb, args.decals) == (WORKLOAD, 4096, None, 0) else None,
                          "traffic_source": counters_source + " (ncu capture of this command, recorded; not "
                          "measured by this run)", "peak_source": peak_kind,
                          "algorithmic_bytes_per_launch": bytes_per_frame * n,
@@ -666,6 +673,8 @@ def main():
                     help="reference arm: time only the C restatement, not the upstream Torch engine")
     ap.add_argument("--no-graph", action="store_true", help="c5 only: launch the rollout eagerly instead of as a CUDA graph")
     ap.add_argument("--update", action="store_true", help="c5 only: a clipped policy-gradient pass after every rollout")
+    ap.add_argument("--decals", type=int, default=0,
+                    help="bullet chips per lane (rings of 64 slots, bitmaps added to the scene); 0 = the contract workload")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.workload == "c5":

@@ -44,7 +44,6 @@ __device__ __noinline__ void gd_decals(const GdScene &sc, const GdView &v, const
   const int tid = threadIdx.x;
   int *count = &sh.misc[12];
   GdDecalProj *proj = (GdDecalProj *)scratch;
-  short *order = (short *)(scratch + gd_align16((size_t)slots * sizeof(GdDecalProj)));
   if (tid == 0) *count = 0;
   __syncthreads();
   const float width = (float)sc.decalW;
@@ -105,7 +104,11 @@ __device__ __noinline__ void gd_decals(const GdScene &sc, const GdView &v, const
   __syncthreads();
   const int n = *count;
   if (n == 0) return;                                /* block-uniform */
-  /* ---- oldest first (engine.py:13763-13775) ---- */
+  /* ---- oldest first (engine.py:13763-13775); the ranked list and every chip's column span go to
+   * shared memory (the hit cache is idle here), so a column rejects the chips beside it cheaply ---- */
+  short *ranked = (short *)sh.hitD;                  /* GD_MAX_DECAL_SLOTS x 2 bytes */
+  unsigned *spans = (unsigned *)sh.hitA;             /* GD_MAX_DECAL_SLOTS x 4 bytes: first column | end column << 16 */
+  static_assert(GD_MAX_DECAL_SLOTS * 4 <= 8 * GD_SW * 4, "the chip list fits the hit cache");
   for (int i = tid; i < n; i += GD_THREADS) {
     const int si = proj[i].serial, li = proj[i].slotStyle & 1023;
     int rank = 0;
@@ -113,7 +116,8 @@ __device__ __noinline__ void gd_decals(const GdScene &sc, const GdView &v, const
       const int sj = proj[j].serial;
       rank += (sj < si) || (sj == si && (proj[j].slotStyle & 1023) < li);
     }
-    order[rank] = (short)i;
+    ranked[rank] = (short)i;
+    spans[rank] = (unsigned)proj[i].sl | ((unsigned)proj[i].sr << 16);
   }
   __syncthreads();
   /* ---- column x of every listed chip ---- */
@@ -129,8 +133,9 @@ __device__ __noinline__ void gd_decals(const GdScene &sc, const GdView &v, const
   const float maskedDepth = haveMasked ? sh.maskedDist[x] : GD_INF;
 #pragma unroll 1
   for (int k = 0; k < n; ++k) {
-    const GdDecalProj &d = proj[order[k]];
-    if (x < d.sl || x >= d.sr) continue;
+    const unsigned span = spans[k];
+    if (x < (int)(span & 0xFFFFu) || x >= (int)(span >> 16)) continue;
+    const GdDecalProj &d = proj[ranked[k]];
     const int variant = (d.slotStyle >> 10) & 7;
     const bool mirrored = (d.slotStyle >> 13) & 1, upsideDown = (d.slotStyle >> 14) & 1;
     const float den = rx * d.segy - ry * d.segx;
@@ -204,6 +209,7 @@ __device__ __noinline__ void gd_decals(const GdScene &sc, const GdView &v, const
       *px = sc.decalBlack[min((int)opacityRow[src], 64) * 256 + *px];   /* the table has 65 rows */
     }
   }
+  __syncthreads();                                   /* the chip list leaves the hit cache to the sprite pass */
 }
 
 #endif
