@@ -412,12 +412,17 @@ def run_ours(args):
         render_step()
         ends[k].record()
         if (k + 1) % gather_every == 0:
-            g0.record()
             gathered = stats.gather_lane_stats(producer.signal_buffer)
-            g1.record()
     barrier()
     wall1 = time.time()
     if gathered is not None:
+        # the collective alone: inside the loop its duration would mostly be the wait for the slowest
+        # rank (the ranks drift apart by a fraction of a millisecond per step), so it is timed once
+        # more here, right after a barrier
+        g0.record()
+        stats.gather_lane_stats(producer.signal_buffer)
+        g1.record()
+        torch.cuda.synchronize(device)
         gather_us = 1000.0 * g0.elapsed_time(g1)
     kernel_ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
     launches = renderer.launches - launches0

@@ -179,6 +179,8 @@ class Renderer:
             raise ValueError(f"things must be a contiguous (N,{max(self.max_things, 1)},4) int32 tensor")
         if lanes.device != self.device or things.device != self.device:
             raise TypeError("lanes and things must live on the renderer's device")
+        if self._decals is not None and self._decals.shape[0] < n:
+            raise ValueError(f"the bound decal rings cover {self._decals.shape[0]} lanes, the call draws {n}")
         return n
 
     def pack_state(self, engine_state, lanes, things):

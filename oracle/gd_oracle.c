@@ -1621,8 +1621,9 @@ static void decal_pass(const Scene *sc, const View *v, const LaneGeom *g, LaneBu
   free(order);
 }
 
-static const gd_decal *gBoundDecals;
-static int gBoundDecalSlots;
+/* per calling thread: the tests render chunks of lanes from several threads at once */
+static __thread const gd_decal *gBoundDecals;
+static __thread int gBoundDecalSlots;
 /* Decal rings of the lanes of the next gd_oracle_render calls: n x slots records, or NULL. */
 void gd_oracle_bind_decals(const gd_decal *decals, int slots) {
   gBoundDecals = decals;

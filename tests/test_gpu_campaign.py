@@ -1,9 +1,10 @@
 """CUDA path against the CPU oracle on seeded random scene specifications: grid shape, room
-size, texture sizes, floor range, diagonal lines, masked middle textures, thing count and the
-status bar all vary; the players walk with the kinematics kernel before the comparison, so
-some stand in doorways.  Every indexed frame and observation must be equal.  With
+size, texture sizes, floor range, diagonal lines, masked middle textures, split lines, bullet
+chips, thing count and the status bar all vary; the players walk with the kinematics kernel
+before the comparison, so some stand in doorways.  Every indexed frame and observation must be equal.  With
 GD_CAMPAIGN_LOG set, one line per specification is appended to that file."""
 
+import dataclasses
 import json
 import os
 from concurrent.futures import ThreadPoolExecutor
@@ -33,6 +34,10 @@ def test_random_scene_specification(trial, pkg, oracle):
     from gradoom_b200.env import action_matrix
 
     spec, rng = _spec(gdscene, trial)
+    extra = np.random.default_rng(9500 + trial)       # a generator of its own: the older draws stay as they were
+    splits = 0.3 if extra.random() < 0.4 else 0.0
+    chips = 24 if extra.random() < 0.5 else 0
+    spec = dataclasses.replace(spec, splits=splits, decals=chips > 0)
     sc = gdscene.make_grid_scene(spec)
     blob = gdscene.pack_scene(sc)
     k = int(rng.choice([0, 4, 12, 32]))
@@ -46,14 +51,22 @@ def test_random_scene_specification(trial, pkg, oracle):
     for _ in range(steps):
         producer.step(table[torch.randint(0, 17, (LANES,), device=DEV, generator=g)])
     lanes, things = producer.render_inputs()
+    host_lanes, host_things = lanes.cpu().numpy(), things.cpu().numpy()
+    rings = None
+    if chips:
+        rings = stepper.random_decals(sc, host_lanes, chips, 64, seed=9700 + trial)
+        r.bind_decals(torch.from_numpy(rings).to(DEV))
     hud = bool(trial % 2)
     obs, indexed, _ = r.frames(lanes, things, obs=True, indexed=True, mask_hud=not hud)
     r.check_status()
-    host_lanes, host_things = lanes.cpu().numpy(), things.cpu().numpy()
     chunk = 32
+
+    def draw(i):
+        part = None if rings is None else rings[i:i + chunk].view(oracle.DECAL_DTYPE)[..., 0]
+        return oracle.render(blob, host_lanes[i:i + chunk], host_things[i:i + chunk], mask_hud=not hud, decals=part)
+
     with ThreadPoolExecutor(max_workers=min(len(os.sched_getaffinity(0)), 8)) as pool:
-        parts = list(pool.map(lambda i: oracle.render(blob, host_lanes[i:i + chunk], host_things[i:i + chunk],
-                                                      mask_hud=not hud), range(0, LANES, chunk)))
+        parts = list(pool.map(draw, range(0, LANES, chunk)))
     want_indexed = np.concatenate([p["indexed"] for p in parts])
     want_obs = np.concatenate([p["obs"] for p in parts])
     unowned = np.concatenate([p["unowned"] for p in parts])
@@ -64,6 +77,7 @@ def test_random_scene_specification(trial, pkg, oracle):
         with open(log, "a") as f:
             f.write(json.dumps({"trial": trial, "rows": spec.rows, "cols": spec.cols, "room": spec.room,
                                 "diagonals": spec.diagonals, "mid_textures": spec.mid_textures, "things": k,
+                                "split_lines": len(sc.meta.get("fragments", {})), "chips_per_lane": chips,
                                 "walls": sc.num_walls, "steps_walked": steps, "status_bar": hud, "lanes": LANES,
                                 "lanes_with_fallback_pixels": int((unowned > 0).sum()),
                                 "mismatching_lanes": int(wrong.sum())}) + "\n")

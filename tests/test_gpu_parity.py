@@ -675,6 +675,9 @@ def test_decal_rings_are_ignored_by_a_scene_without_chip_bitmaps(pkg, oracle, sc
         r.bind_decals(torch.zeros((8, 2048, 4), dtype=torch.int32, device=DEV))     # more slots than the renderer accepts
     with pytest.raises(ValueError):
         r.bind_decals(torch.zeros((8, 64, 3), dtype=torch.int32, device=DEV))
+    r.bind_decals(_dev(rings[:4]))                     # rings for four lanes, a call that draws eight
+    with pytest.raises(ValueError):
+        r.frames(_dev(lanes), _dev(things), indexed=True)
 
 
 def test_cuda_draws_a_scene_compiled_from_wad_files(pkg, oracle):
