@@ -151,6 +151,12 @@ GRID_CONFIGS = {
                     floor_max=64, decals=True),
     "c4d": GridSpec(rows=8, cols=8, room=128.0, seed=4, wall_textures=16,
                     tex_w=128, tex_h=128, flats=8, floor_max=128, diagonals=True, decals=True),
+    # masked middle textures with chips on them, and the 64-sector map with chips (drawn from the poses
+    # that leave most of the view to the flat fallback)
+    "c1md": GridSpec(rows=4, cols=4, room=256.0, seed=5, wall_textures=8, flats=4,
+                     floor_max=64, mid_textures=0.5, decals=True),
+    "c2dec": GridSpec(rows=8, cols=8, room=256.0, seed=2, wall_textures=16, flats=8,
+                      floor_max=128, decals=True),
     # c1 and the quarter-size diagonal map with 40 % of their lines split into projection fragments
     "c1s": GridSpec(rows=4, cols=4, room=256.0, seed=1, wall_textures=8, flats=4,
                     floor_max=64, splits=0.4),

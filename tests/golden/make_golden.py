@@ -3,7 +3,7 @@
 Run once on a machine that has the upstream sources:
 
     GRADOOM_REFERENCE_SRC=<upstream checkout>/src/gradoom python tests/golden/make_golden.py \
-        [c1 c2 c3 c4 c1m stack flashes pitch fallback c2d c4d c1k state move_c1 move_c2 decals_c1 decals_c4 c1s c4s]
+        [c1 c2 c3 c4 c1m stack flashes pitch fallback c2d c4d c1k state move_c1 move_c2 decals_c1 decals_c4 decals_c1m decals_fallback c1s c4s]
 
 For each seeded synthetic scene it resets the upstream engine, injects K
 monsters per lane, replays a seeded uniform action stream and, at a few
@@ -207,14 +207,20 @@ def generate_fallback(eng, scn, act):
     print("fallback fixture done", flush=True)
 
 
-def generate_decals(cfg, eng, scn, act):
+FALLBACK_POSES = [  # x, y, angle (degrees): see generate_fallback
+    (512.0, 600.0, 170.0), (768.0, 1024.0, 200.0), (1280.0 + 2.0 ** -15, 700.0, 95.0),
+    (900.0, 1536.0, 0.0), (600.0, 512.0, 200.0), (512.0, 600.0, 100.0),
+]
+
+
+def generate_decals(cfg, eng, scn, act, poses=None, name=None):
     """Bullet chips on the walls in view (engine.py:13747-13991): the scene carries decal bitmaps,
     the engine's decal rings are written directly (the way the upstream tests set state): per lane
     some forty chips where rays through the view meet the nearest line, at seeded heights, on the
     viewer's side of the line mostly, a few on the far side, a few on lines elsewhere, serials in
     shuffled slot order, free slots in between."""
 
-    n, k = 4, 4
+    n, k = (4 if poses is None else len(poses)), 4
     sc = gdscene.make_grid_scene(gdscene.GRID_CONFIGS[cfg])
     blob = gdscene.pack_scene(sc)
     e, g = make_engine(eng, scn, sc, n, k, seed=4242)
@@ -226,6 +232,16 @@ def generate_decals(cfg, eng, scn, act):
         done = term | trunc
         if bool(done.any()):
             e.reset(done, torch.arange(n) + 1000 * (step + 1))
+    if poses is not None:          # stand on lines and vertices, as the fallback fixture does
+        x = torch.tensor([p[0] for p in poses], dtype=torch.float32)
+        y = torch.tensor([p[1] for p in poses], dtype=torch.float32)
+        bam = torch.tensor([int(round(p[2] / 360.0 * (1 << 32))) & 0xFFFFFFFF for p in poses], dtype=torch.int64)
+        e.x.copy_(x)
+        e.y.copy_(y)
+        e._x_fixed.copy_(torch.round(x.to(torch.float64) * 65536.0).to(torch.int64))
+        e._y_fixed.copy_(torch.round(y.to(torch.float64) * 65536.0).to(torch.int64))
+        e._angle_bam.copy_(bam)
+        e.angle.copy_(bam.to(torch.float32) * gdstate.BAM_TO_RADIANS)
     rng = np.random.default_rng(99)
     walls = sc.walls.astype(np.float64)
     slots = e.hitscan_decal_serial.shape[1]
@@ -282,8 +298,8 @@ def generate_decals(cfg, eng, scn, act):
     e.hitscan_decal_serial.fill_(-1)
     bare = e._render_native_indexed_frame(include_hud=True).numpy()
     out["changed_pixels"] = np.asarray(int((bare != indexed).sum()))
-    np.savez_compressed(os.path.join(OUT, f"golden_decals_{cfg}.npz"), **out)
-    print("decal fixture", cfg, "done; pixels the chips changed:", int(out["changed_pixels"]), flush=True)
+    np.savez_compressed(os.path.join(OUT, f"golden_decals_{name or cfg}.npz"), **out)
+    print("decal fixture", name or cfg, "done; pixels the chips changed:", int(out["changed_pixels"]), flush=True)
 
 
 
@@ -549,8 +565,10 @@ def main(argv):
             generate_fallback(eng, scn, act)
         elif name == "c1k":
             generate_c1k(eng, scn, act)
-        elif name in ("decals_c1", "decals_c4"):
-            generate_decals({"decals_c1": "c1d", "decals_c4": "c4d"}[name], eng, scn, act)
+        elif name in ("decals_c1", "decals_c4", "decals_c1m"):
+            generate_decals({"decals_c1": "c1d", "decals_c4": "c4d", "decals_c1m": "c1md"}[name], eng, scn, act)
+        elif name == "decals_fallback":
+            generate_decals("c2dec", eng, scn, act, poses=FALLBACK_POSES, name="fallback")
         else:
             generate(name, eng, scn, act)
 

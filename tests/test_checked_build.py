@@ -133,7 +133,7 @@ def test_decal_rings_under_the_checked_build(pkg, oracle, scenes):
 
     from gradoom_b200 import stepper
 
-    for name in ("decals_c1d", "decals_c4d"):
+    for name in ("decals_c1d", "decals_c4d", "decals_c1md", "decals_fallback"):
         data = load_golden(name)
         _sc, blob = scenes(str(data["config"]), (data["ray_offsets"], data["ray_coscorr"]))
         r = _checked(blob, 64)

@@ -621,7 +621,7 @@ def test_render_step_captures_into_a_cuda_graph(pkg, scenes):
     assert not torch.equal(stack[:, 3], stack[:, 2])
 
 
-@pytest.mark.parametrize("name", ["decals_c1d", "decals_c4d"])
+@pytest.mark.parametrize("name", ["decals_c1d", "decals_c4d", "decals_c1md", "decals_fallback"])
 def test_cuda_draws_the_upstream_bullet_chips(name, pkg, oracle, scenes):
     """The decal layer (engine.py:13747-13991) against the frames recorded from the upstream engine."""
 

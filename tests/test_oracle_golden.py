@@ -256,7 +256,8 @@ def test_oracle_screen_flashes_match_upstream_rgb(pkg, oracle):
     assert not np.array_equal(plain, data["rgb_2"]), "the last case blends every lane"
 
 
-@pytest.mark.parametrize("name,floor", [("decals_c1d", 250), ("decals_c4d", 3000)])
+@pytest.mark.parametrize("name,floor", [("decals_c1d", 250), ("decals_c4d", 3000), ("decals_c1md", 500),
+                                        ("decals_fallback", 50)])
 def test_oracle_draws_the_upstream_bullet_chips(name, floor, pkg, oracle, scenes):
     """engine.py:13747-13991: the decal layer of the indexed frame, recorded from the upstream
     engine with its decal rings written directly; the fixture counts the pixels the chips changed."""
