@@ -468,4 +468,26 @@ extern "C" int gd_render_step_static(const gd_renderer *r, const int32_t *lanes,
   return cudaGetLastError() == cudaSuccess ? GD_OK : GD_ERR_CUDA;
 }
 
+/* ---- diagnostic: the device's float32 libm on caller-given arguments -------------------- */
+__global__ void gd_probe_libm_kernel(int function, const float *a, const float *b, float *out, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float r;
+  switch (function) {
+    case GD_PROBE_ATAN2F: r = atan2f(a[i], b[i]); break;
+    case GD_PROBE_COSF: r = cosf(a[i]); break;
+    case GD_PROBE_SINF: r = sinf(a[i]); break;
+    default: r = sqrtf(a[i] * a[i] + b[i] * b[i]); break;      /* GD_PROBE_HYPOT: the sprite distance as the kernel forms it */
+  }
+  out[i] = r;
+}
+
+extern "C" int gd_probe_libm(int function, const float *a, const float *b, float *out, int n, void *stream) {
+  if (!a || !out || ((function == GD_PROBE_ATAN2F || function == GD_PROBE_HYPOT) && !b)) return GD_ERR_NULL;
+  if (function < GD_PROBE_ATAN2F || function > GD_PROBE_HYPOT || n < 0) return GD_ERR_SIZE;
+  if (n == 0) return GD_OK;
+  gd_probe_libm_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>(function, a, b, out, n);
+  return cudaGetLastError() == cudaSuccess ? GD_OK : GD_ERR_CUDA;
+}
+
 #endif

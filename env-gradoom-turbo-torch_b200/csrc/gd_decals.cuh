@@ -33,12 +33,6 @@ __host__ __device__ inline size_t gd_decal_scratch_per_cta(int slots) {
   return gd_align16((size_t)slots * sizeof(GdDecalProj)) + gd_align16((size_t)slots * 2);
 }
 
-/* rows [a,b) as bits of the 7-word row mask */
-__device__ __forceinline__ void gd_rows_or(unsigned *m, int a, int b) {
-#pragma unroll
-  for (int k = 0; k < 7; ++k) m[k] |= gd_range_word(k, a, b);
-}
-
 __device__ __noinline__ void gd_decals(const GdScene &sc, const GdView &v, const GdShared &sh, const GdEvent *events,
                                        const int *eventCount, const gd_decal *ring, int slots, uint8_t *scratch) {
   const int tid = threadIdx.x;
@@ -158,21 +152,21 @@ __device__ __noinline__ void gd_decals(const GdScene &sc, const GdView &v, const
     const int shade = gd_wall_shade(d.light, gd_div(GD_WALL_VIS << 12, gd_max(depthFixed, 1)));
     const uint8_t *opacityRow = sc.decalOpacity + shade * 256;
     const uint8_t *chip = sc.decalAtlas + (size_t)variant * sc.decalH * sc.decalW + u;
-    /* rows of this column drawn by a wall tier, and those of them drawn at the chip's depth */
+    /* rows of this column drawn by a wall tier, and those of them drawn at the chip's depth; only the
+     * 32-row words the chip reaches are replayed */
     unsigned tierRows[7] = {0, 0, 0, 0, 0, 0, 0}, chipRows[7] = {0, 0, 0, 0, 0, 0, 0};
+    const int word0 = (int)firstRow >> 5, word1 = (int)lastRow >> 5;
 #pragma unroll 1
     for (int e = 0; e < nEvents; ++e) {
       const GdEvent ev = events[e * GD_SW + x];
-      unsigned rows[7] = {0, 0, 0, 0, 0, 0, 0};
-      if ((ev.pad0 & 2) && ev.t1a < ev.t1b) gd_rows_or(rows, ev.t1a, ev.t1b);
-      if ((ev.pad0 & 1) && ev.t0a < ev.t0b) {
-#pragma unroll
-        for (int q = 0; q < 7; ++q) rows[q] |= gd_range_word(q, ev.t0a, ev.t0b) & ~gd_range_word(q, ev.t1a, ev.t1b);
-      }
+      const bool lower = (ev.pad0 & 2) && ev.t1a < ev.t1b, upper = (ev.pad0 & 1) && ev.t0a < ev.t0b;
+      if (!lower && !upper) continue;
       const bool atDepth = fabsf(ev.dist - distance) <= 1e-3f;
-#pragma unroll
-      for (int q = 0; q < 7; ++q) {
-        const unsigned fresh = rows[q] & ~tierRows[q];
+#pragma unroll 1
+      for (int q = word0; q <= word1; ++q) {
+        const unsigned under = gd_range_word(q, ev.t1a, ev.t1b);          /* the lower tier has the row first */
+        const unsigned rows = (lower ? under : 0u) | (upper ? gd_range_word(q, ev.t0a, ev.t0b) & ~under : 0u);
+        const unsigned fresh = rows & ~tierRows[q];
         tierRows[q] |= fresh;
         if (atDepth) chipRows[q] |= fresh;
       }

@@ -28,7 +28,7 @@ EXPORTS = (
     "gd_error_string", "gd_renderer_create", "gd_renderer_destroy", "gd_renderer_scratch_bytes",
     "gd_renderer_ctas", "gd_renderer_shared_bytes", "gd_render_step", "gd_render_reset", "gd_render_frames",
     "gd_render_step_frames", "gd_render_step_host", "gd_render_step_ring", "gd_render_reset_ring", "gd_static_scratch_bytes", "gd_static_max_walls", "gd_render_step_static",
-    "gd_pack_state_scratch_bytes", "gd_pack_state", "gd_player_tics", "gd_renderer_bind_decals",
+    "gd_pack_state_scratch_bytes", "gd_pack_state", "gd_player_tics", "gd_renderer_bind_decals", "gd_probe_libm",
 )
 
 _libs = {}
@@ -89,6 +89,8 @@ def load(checked: bool = False) -> ctypes.CDLL:
         lib.gd_player_tics.argtypes = [vp, vp, vp, vp, ci, ci, ci, vp, vp, vp]
         lib.gd_renderer_bind_decals.restype = ci
         lib.gd_renderer_bind_decals.argtypes = [vp, vp, ci]
+        lib.gd_probe_libm.restype = ci
+        lib.gd_probe_libm.argtypes = [ci, vp, vp, vp, ci, vp]
         _libs[path] = lib
     return _libs[path]
 
@@ -100,6 +102,24 @@ def _check(code: int, what: str) -> None:
 
 def _ptr(t: torch.Tensor | None) -> int | None:
     return None if t is None else t.data_ptr()
+
+
+PROBE_ATAN2F, PROBE_COSF, PROBE_SINF, PROBE_HYPOT = 0, 1, 2, 3
+
+
+def probe_libm(function: int, a: torch.Tensor, b: torch.Tensor | None = None) -> torch.Tensor:
+    """The device's float32 ``atan2f(a, b)`` / ``cosf(a)`` / ``sinf(a)`` / ``sqrtf(a*a + b*b)`` as the
+    kernels call them (diagnostic; see ``gd_probe_libm`` in the header)."""
+
+    if a.dtype != torch.float32 or not a.is_cuda or not a.is_contiguous():
+        raise ValueError("a must be a contiguous float32 CUDA tensor")
+    if b is not None and (b.dtype != torch.float32 or b.shape != a.shape or b.device != a.device or not b.is_contiguous()):
+        raise ValueError("b must match a")
+    out = torch.empty_like(a)
+    with torch.cuda.device(a.device):
+        _check(load().gd_probe_libm(int(function), a.data_ptr(), _ptr(b), out.data_ptr(), a.numel(),
+                                    torch.cuda.current_stream(a.device).cuda_stream), "gd_probe_libm")
+    return out
 
 
 class Renderer:

@@ -318,6 +318,18 @@ int gd_static_max_walls(void);
 int gd_render_step_static(const gd_renderer *r, const int32_t *lanes, const void *things, int n, int mask_hud,
                           uint8_t *stack, int *status, void *stream);
 
+/*
+ * Diagnostic, no counterpart in the reference.  The few float32 transcendentals of the path
+ * (sprite bearing and depth, engine.py:14684-14688; sprite rotation, 13994-14009; the flat
+ * fallback's ray direction, 10966-10974) are evaluated by the device's libm, the reference's by
+ * ATen's CPU kernels; they may differ in the last place.  This evaluates `function` on n device
+ * floats with exactly the calls the kernels make, so that a test can count how often, on the
+ * arguments the renderer forms, the two disagree.  `b` is read by GD_PROBE_ATAN2F (a = y, b = x)
+ * and GD_PROBE_HYPOT (sqrtf(a*a + b*b)) only.
+ */
+enum gd_probe_function { GD_PROBE_ATAN2F = 0, GD_PROBE_COSF = 1, GD_PROBE_SINF = 2, GD_PROBE_HYPOT = 3 };
+int gd_probe_libm(int function, const float *a, const float *b, float *out, int n, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

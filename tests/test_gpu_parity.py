@@ -711,3 +711,75 @@ def test_cuda_draws_a_scene_compiled_from_wad_files(pkg, oracle):
     r.check_status()
     assert np.array_equal(indexed.cpu().numpy(), expected["indexed"])
     assert np.array_equal(obs.cpu().numpy(), expected["obs"])
+
+
+def test_device_libm_against_the_hosts_on_the_renderers_arguments(pkg):
+    """The float32 transcendentals of the path (engine.py:14684-14688, 13994-14009, 10966-10974) run in
+    the device's libm here; the reference runs them in ATen: its CUDA kernels on a GPU, its CPU kernels
+    (which recorded the fixtures) on the host.  On arguments formed the way the renderer forms them
+    this counts how often the library's calls differ from either, bounds the distance, and checks that
+    the quantities derived from them (sprite depth, rotation step) agree.  With GD_LIBM_LOG set the
+    counts are appended to that file."""
+
+    import json
+    import math
+
+    from gradoom_b200 import native
+
+    g = torch.Generator().manual_seed(77)
+    n = 1 << 20
+    # positions on the 16.16 grid of a 2048-unit map: thing minus player
+    px = torch.randint(0, 2048 << 16, (n,), generator=g).to(torch.float32) / 65536.0
+    py = torch.randint(0, 2048 << 16, (n,), generator=g).to(torch.float32) / 65536.0
+    tx = torch.randint(0, 2048 << 16, (n,), generator=g).to(torch.float32) / 65536.0
+    ty = torch.randint(0, 2048 << 16, (n,), generator=g).to(torch.float32) / 65536.0
+    dx, dy = tx - px, ty - py
+    view = torch.randint(0, 1 << 32, (n,), generator=g).to(torch.float32) * (2.0 * math.pi / float(1 << 32))
+
+    def ulps(a, b):
+        ia, ib = a.view(torch.int32).to(torch.int64), b.view(torch.int32).to(torch.int64)
+        ia = torch.where(ia < 0, -(ia & 0x7FFFFFFF), ia)
+        ib = torch.where(ib < 0, -(ib & 0x7FFFFFFF), ib)
+        return (ia - ib).abs()
+
+    def compare(ours, aten_cpu, aten_cuda):
+        d = ulps(aten_cpu, ours)
+        return {"n": n, "differ_from_aten_cpu": int((d > 0).sum()), "max_ulp_from_aten_cpu": int(d.max()),
+                "differ_from_aten_cuda": int((ulps(aten_cuda.cpu(), ours) > 0).sum())}
+
+    report = {}
+    host_bearing = torch.atan2(dy, dx)
+    dev_bearing = native.probe_libm(native.PROBE_ATAN2F, dy.to(DEV), dx.to(DEV)).cpu()
+    report["atan2f"] = compare(dev_bearing, host_bearing, torch.atan2(dy.to(DEV), dx.to(DEV)))
+    rel = torch.remainder(host_bearing - view + math.pi, 2 * math.pi) - math.pi
+    for name, fn, op in (("cosf", native.PROBE_COSF, torch.cos), ("sinf", native.PROBE_SINF, torch.sin)):
+        report[name] = compare(native.probe_libm(fn, rel.to(DEV)).cpu(), op(rel), op(rel.to(DEV)))
+    squares = dx * dx + dy * dy
+    dev_dist = native.probe_libm(native.PROBE_HYPOT, dx.to(DEV), dy.to(DEV)).cpu()
+    report["sqrtf"] = compare(dev_dist, torch.sqrt(squares), torch.sqrt(squares.to(DEV)))
+    exact = torch.sqrt(squares.to(torch.float64)).to(torch.float32)       # the correctly rounded root
+    report["sqrtf"]["differ_from_correctly_rounded"] = int((dev_dist != exact).sum())
+    report["sqrtf"]["aten_cpu_differs_from_correctly_rounded"] = int((torch.sqrt(squares) != exact).sum())
+    # derived quantities: sprite depth (dist * cos(rel)) and the sprite rotation step of eight
+    dev_rel = torch.remainder(dev_bearing - view + math.pi, 2 * math.pi) - math.pi
+    host_depth = torch.sqrt(squares) * torch.cos(rel)
+    dev_depth = dev_dist * native.probe_libm(native.PROBE_COSF, dev_rel.to(DEV)).cpu()
+    close = (host_depth - dev_depth).abs() <= 1e-4 * dev_dist.clamp_min(1.0)
+    report["sprite_depth"] = {"n": n, "differ_from_aten_cpu": int((host_depth != dev_depth).sum()),
+                              "beyond_1e-4_relative": int((~close).sum())}
+    facing = torch.rand(n, generator=g) * 2 * math.pi
+
+    def rotation(bearing):
+        relative = torch.remainder(bearing + math.pi - facing + math.pi / 8, 2 * math.pi)
+        return torch.remainder(torch.floor(relative / (math.pi / 4)), 8)
+
+    report["sprite_rotation_step"] = {"n": n, "differ_from_aten_cpu": int((rotation(host_bearing) != rotation(dev_bearing)).sum())}
+    log = os.environ.get("GD_LIBM_LOG")
+    if log:
+        with open(log, "a") as f:
+            f.write(json.dumps(report) + "\n")
+    for name in ("atan2f", "cosf", "sinf", "sqrtf"):
+        assert report[name]["max_ulp_from_aten_cpu"] <= 4
+    assert report["sqrtf"]["differ_from_correctly_rounded"] == 0     # IEEE square root, products and sum rounded separately
+    assert report["sprite_depth"]["beyond_1e-4_relative"] == 0
+    assert report["sprite_rotation_step"]["differ_from_aten_cpu"] <= n // 10000
