@@ -30,7 +30,7 @@ struct __align__(16) GdDecalProj {
 static_assert(sizeof(GdDecalProj) == 32, "scratch layout");
 
 __host__ __device__ inline size_t gd_decal_scratch_per_cta(int slots) {
-  return gd_align16((size_t)slots * sizeof(GdDecalProj)) + gd_align16((size_t)slots * 2);
+  return gd_align16((size_t)slots * sizeof(GdDecalProj));
 }
 
 __device__ __noinline__ void gd_decals(const GdScene &sc, const GdView &v, const GdShared &sh, const GdEvent *events,

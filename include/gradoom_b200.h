@@ -79,7 +79,7 @@ void gd_renderer_destroy(gd_renderer *r);
  * as gd_decal.  The array must stay alive and hold at least as many lanes as the
  * calls draw.  NULL unbinds.  The layer draws only when the scene blob carries
  * decal bitmaps (GD_H_DECALS > 0).  The call may allocate (the renderer keeps its
- * own projection scratch, slots * 34 bytes per CTA) and must not overlap with
+ * own projection scratch, slots * 32 bytes per CTA) and must not overlap with
  * render calls of the same renderer; the render calls themselves stay allocation
  * free.  Pixels the flat fallback layer alone filled (rows no seg and no visplane
  * claimed) are never shaded by a chip.
