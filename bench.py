@@ -538,7 +538,8 @@ def run_ours(args):
                                    + ("obs and RGB24 frame every step" if rgb is not None else "obs only")
                                    + (f", {min(args.decals, 64)} bullet chips/lane" if args.decals > 0 else ""),
                        "lanes_per_gpu": n, "l2": "flushed with a 256 MiB write between timed steps",
-                       "ctas": renderer.ctas, "shared_bytes_per_cta": renderer.shared_bytes,
+                       "ctas": renderer.ctas,
+                       "shared_bytes_per_cta": renderer.shared_bytes if rgb is not None else renderer.shared_bytes_view,
                        "stack_policy": "mirrored ring (write 2 of 8 slots per lane, no reads)" if use_ring
                        else "roll (read 3 + write 4 slots per lane)"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,

@@ -18,8 +18,11 @@ struct gd_renderer {
   int device;
   int maxThings;
   int ctas;
-  size_t smemBytes;
+  size_t smemBytes;          /* dynamic shared memory and staged tables with the whole 240-row frame on chip ... */
   int stageMask;
+  size_t smemBytesView;      /* ... and with the 208 view rows only (calls that draw no status bar and want no full
+                                frame): the 10 KB go to more staged tables */
+  int stageMaskView;
   int secWallsN, vtxWallsN, V;
   /* gd_render_step_host overlaps the device->host copy of one lane chunk with
    * the drawing of the next on this side stream */
@@ -143,9 +146,10 @@ extern "C" int gd_renderer_create(const void *blob_header_host, const void *blob
   r->decals = nullptr; r->decalSlots = 0; r->decalScratch = nullptr; r->decalScratchBytes = 0;
   r->fragScratch = nullptr;
 #undef SECP
-  r->smemBytes = gd_shared_bytes(sc.W, max_things);
+  r->smemBytes = gd_shared_bytes(sc.W, max_things, GD_SCREEN_H);
+  r->smemBytesView = gd_shared_bytes(sc.W, max_things, GD_VH);
   r->secWallsN = h[GD_H_SEC_WALLS_N]; r->vtxWallsN = h[GD_H_VTX_WALLS_N]; r->V = h[GD_H_VERTICES];
-  r->stageMask = 0;
+  r->stageMask = r->stageMaskView = 0;
   int prev = 0;
   if (cudaGetDevice(&prev) != cudaSuccess || cudaSetDevice(device) != cudaSuccess) { delete r; return GD_ERR_CUDA; }
   int maxOptin = 0, sms = 0;
@@ -162,6 +166,7 @@ extern "C" int gd_renderer_create(const void *blob_header_host, const void *blob
     for (int bit = 1; bit <= GD_STAGE_ROWPROJ; bit <<= 1) {
       size_t extra = gd_stage_bytes(bit, sc.W, sc.S, r->V, r->secWallsN, r->vtxWallsN);
       if (r->smemBytes + extra <= (size_t)limit) { r->smemBytes += extra; r->stageMask |= bit; }
+      if (r->smemBytesView + extra <= (size_t)limit) { r->smemBytesView += extra; r->stageMaskView |= bit; }
     }
     int perSm = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, gd_kernel_for(sc), GD_THREADS, r->smemBytes) != cudaSuccess ||
@@ -232,6 +237,7 @@ extern "C" size_t gd_renderer_scratch_bytes(const gd_renderer *r) {
 
 extern "C" int gd_renderer_ctas(const gd_renderer *r) { return r ? r->ctas : 0; }
 extern "C" size_t gd_renderer_shared_bytes(const gd_renderer *r) { return r ? r->smemBytes : 0; }
+extern "C" size_t gd_renderer_shared_bytes_view(const gd_renderer *r) { return r ? r->smemBytesView : 0; }
 
 static int gd_launch(const gd_renderer *r, const int32_t *lanes, const gd_thing *things, int n, int flags,
                      uint8_t *stack, const uint8_t *reset_mask, uint8_t *obs_out, uint8_t *indexed_out,
@@ -254,11 +260,15 @@ static int gd_launch(const gd_renderer *r, const int32_t *lanes, const gd_thing 
   p.stack = stack; p.ringHead = ring_head; p.resetMask = reset_mask; p.obsOut = obs_out; p.indexedOut = indexed_out; p.rgbOut = rgb_out;
   p.scratch = (uint8_t *)scratch; p.status = status;
   p.queueOffset = (size_t)r->ctas * gd_scratch_per_cta(r->sc.W, r->sc.S);
-  p.stageMask = r->stageMask; p.secWallsN = r->secWallsN; p.vtxWallsN = r->vtxWallsN; p.V = r->V;
+  /* the status-bar rows of the frame stay off chip when nothing of this call shows them */
+  const bool viewOnly = (flags & GD_F_MASK_HUD) && !(flags & GD_F_DRAW_HUD) && !indexed_out && !rgb_out;
+  p.frameRows = viewOnly ? GD_VH : GD_SCREEN_H;
+  p.stageMask = viewOnly ? r->stageMaskView : r->stageMask;
+  p.secWallsN = r->secWallsN; p.vtxWallsN = r->vtxWallsN; p.V = r->V;
   p.decals = r->decals; p.decalSlots = r->decalSlots; p.decalScratch = r->decalScratch;
   p.fragScratch = r->fragScratch;
   int grid = n < r->ctas ? n : r->ctas;
-  gd_kernel_for(r->sc)<<<grid, GD_THREADS, r->smemBytes, (cudaStream_t)stream>>>(p);
+  gd_kernel_for(r->sc)<<<grid, GD_THREADS, viewOnly ? r->smemBytesView : r->smemBytes, (cudaStream_t)stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? GD_OK : GD_ERR_CUDA;
 }
 
@@ -459,7 +469,8 @@ extern "C" int gd_render_step_static(const gd_renderer *r, const int32_t *lanes,
   /* lane queue: the last 16 bytes of the array; zero when the library is
    * loaded and left at zero by every launch */
   p.queueOffset = (size_t)GD_STATIC_MAX_CTAS * GD_STATIC_PER_CTA;
-  p.stageMask = r->stageMask; p.secWallsN = r->secWallsN; p.vtxWallsN = r->vtxWallsN; p.V = r->V;
+  p.frameRows = GD_SCREEN_H; p.stageMask = r->stageMask;
+  p.secWallsN = r->secWallsN; p.vtxWallsN = r->vtxWallsN; p.V = r->V;
   p.decals = r->decals; p.decalSlots = r->decalSlots; p.decalScratch = r->decalScratch;
   p.fragScratch = r->fragScratch;
   int grid = n < r->ctas ? n : r->ctas;

@@ -30,7 +30,7 @@ __device__ void gd_resize(const uint8_t *frame, const unsigned long long *pal64,
       int sy = sy0 + i;
       int yo = min(ye, (sy + 1) * 84) - max(ys, sy * 84);
       unsigned wy = (yo > 0 && sy < srcRows) ? (unsigned)yo / 12u : 0u;
-      const uint8_t *row = frame + min(sy, GD_SCREEN_H - 1) * GD_SW;
+      const uint8_t *row = frame + min(sy, srcRows - 1) * GD_SW;      /* rows beyond srcRows weigh nothing */
       unsigned long long racc = 0;
 #pragma unroll
       for (int j = 0; j < 5; ++j) racc += (unsigned long long)wx[j] * pal64[row[cx[j]]];

@@ -54,6 +54,8 @@ struct GdParams {
   uint8_t *scratch;          /* ctas x gd_scratch_per_cta(W), then the lane queue (2 words, zero between launches) */
   size_t queueOffset;
   int stageMask;             /* which scene tables each CTA copies into shared memory */
+  int frameRows;             /* rows of the frame kept in shared memory: GD_VIEW_H when neither the status bar
+                                nor a full frame is wanted (the 32 rows make room for more tables), else GD_SCREEN_H */
   int secWallsN, vtxWallsN, V;
   int *status;
   const gd_decal *decals;    /* n x decalSlots rings of bullet chips, or null */
@@ -110,9 +112,9 @@ struct GdShared {
 
 __host__ __device__ inline size_t gd_align16(size_t v) { return (v + 15) & ~(size_t)15; }
 
-__host__ __device__ inline size_t gd_shared_bytes(int W, int maxThings) {
+__host__ __device__ inline size_t gd_shared_bytes(int W, int maxThings, int frameRows) {
   size_t b = 0;
-  b += gd_align16((size_t)GD_SCREEN_H * GD_SW);
+  b += gd_align16((size_t)frameRows * GD_SW);
   b += gd_align16(32 * 256);
   b += gd_align16(768);
   b += gd_align16(GD_VH * 4);
@@ -131,9 +133,9 @@ __host__ __device__ inline size_t gd_shared_bytes(int W, int maxThings) {
   return b;
 }
 
-__device__ inline void gd_carve(uint8_t *base, int W, int maxThings, GdShared &s) {
+__device__ inline void gd_carve(uint8_t *base, int W, int maxThings, int frameRows, GdShared &s) {
   size_t o = 0;
-  s.frame = base + o; o += gd_align16((size_t)GD_SCREEN_H * GD_SW);
+  s.frame = base + o; o += gd_align16((size_t)frameRows * GD_SW);
   s.colormap = base + o; o += gd_align16(32 * 256);
   s.playpal = base + o; o += gd_align16(768);
   s.yslope = (unsigned *)(base + o); o += gd_align16(GD_VH * 4);
@@ -180,8 +182,8 @@ __global__ void __launch_bounds__(GD_THREADS, 1) gd_render_kernel(const GdParams
   {
     GdScene sc = p.sc;
     GdShared sh;
-    gd_carve(gd_smem, sc.W, p.maxThings, sh);
-    uint8_t *cursor = gd_smem + gd_shared_bytes(sc.W, p.maxThings);
+    gd_carve(gd_smem, sc.W, p.maxThings, p.frameRows, sh);
+    uint8_t *cursor = gd_smem + gd_shared_bytes(sc.W, p.maxThings, p.frameRows);
     const int m = p.stageMask;
     if (m & GD_STAGE_WALLS) sc.walls = (const float *)gd_stage_copy(cursor, sc.walls, (size_t)sc.W * 16);
     if (m & GD_STAGE_WSEC) sc.wsec = (const int32_t *)gd_stage_copy(cursor, sc.wsec, (size_t)sc.W * 8);

@@ -26,7 +26,7 @@ STATUS_BAD_STATE = 16
 
 EXPORTS = (
     "gd_error_string", "gd_renderer_create", "gd_renderer_destroy", "gd_renderer_scratch_bytes",
-    "gd_renderer_ctas", "gd_renderer_shared_bytes", "gd_render_step", "gd_render_reset", "gd_render_frames",
+    "gd_renderer_ctas", "gd_renderer_shared_bytes", "gd_renderer_shared_bytes_view", "gd_render_step", "gd_render_reset", "gd_render_frames",
     "gd_render_step_frames", "gd_render_step_host", "gd_render_step_ring", "gd_render_reset_ring", "gd_static_scratch_bytes", "gd_static_max_walls", "gd_render_step_static",
     "gd_pack_state_scratch_bytes", "gd_pack_state", "gd_player_tics", "gd_renderer_bind_decals", "gd_probe_libm",
 )
@@ -61,6 +61,8 @@ def load(checked: bool = False) -> ctypes.CDLL:
         lib.gd_renderer_ctas.argtypes = [vp]
         lib.gd_renderer_shared_bytes.restype = sz
         lib.gd_renderer_shared_bytes.argtypes = [vp]
+        lib.gd_renderer_shared_bytes_view.restype = sz
+        lib.gd_renderer_shared_bytes_view.argtypes = [vp]
         lib.gd_render_step.restype = ci
         lib.gd_render_step.argtypes = [vp, vp, vp, ci, ci, vp, vp, sz, vp, vp]
         lib.gd_render_reset.restype = ci
@@ -154,6 +156,7 @@ class Renderer:
                                          device=self.device)
         self.ctas = int(self.lib.gd_renderer_ctas(handle))
         self.shared_bytes = int(self.lib.gd_renderer_shared_bytes(handle))
+        self.shared_bytes_view = int(self.lib.gd_renderer_shared_bytes_view(handle))   # observation-only calls
         self.launches = 0
         self._decals = None
 

@@ -94,6 +94,10 @@ size_t gd_renderer_scratch_bytes(const gd_renderer *r);
 /* Launch shape, for reports: persistent CTAs and dynamic shared memory per CTA. */
 int gd_renderer_ctas(const gd_renderer *r);
 size_t gd_renderer_shared_bytes(const gd_renderer *r);
+/* The same for calls that neither draw the status bar nor return a full frame (gd_render_step and
+ * gd_render_reset with mask_hud, and their ring / host variants): the frame's 32 status-bar rows stay
+ * off chip and their 10 KB hold more of the scene's tables (or leave the SM a larger L1). */
+size_t gd_renderer_shared_bytes_view(const gd_renderer *r);
 
 /*
  * One agent step: render every lane and push the frame onto its stack
