@@ -783,3 +783,26 @@ def test_device_libm_against_the_hosts_on_the_renderers_arguments(pkg):
     assert report["sqrtf"]["differ_from_correctly_rounded"] == 0     # IEEE square root, products and sum rounded separately
     assert report["sprite_depth"]["beyond_1e-4_relative"] == 0
     assert report["sprite_rotation_step"]["differ_from_aten_cpu"] <= n // 10000
+
+
+@pytest.mark.parametrize("name,n,k", [("c2", 300, 12), ("c4", 160, 32), ("c1m", 64, 4)])
+def test_observation_only_calls_equal_full_frame_calls(name, n, k, pkg, oracle, scenes):
+    """A call that draws no status bar and returns no full frame keeps only the view rows of the frame
+    on chip and stages other tables than a full-frame call does; the observations must not differ."""
+
+    from gradoom_b200 import stepper
+
+    sc, blob = scenes(name)
+    lanes, things = stepper.random_lanes(sc, n, k, seed=31)
+    r = _renderer(blob, k)
+    assert r.shared_bytes - 32 * 320 <= r.shared_bytes_view <= r.shared_bytes + 16384   # 10 KB of frame out, tables in
+    view_only, _, _ = r.frames(_dev(lanes), _dev(things), obs=True, mask_hud=True)
+    full, indexed, _ = r.frames(_dev(lanes), _dev(things), obs=True, indexed=True, mask_hud=True)
+    r.check_status()
+    assert torch.equal(view_only, full)
+    expected = oracle.render(blob, lanes[:32], things[:32], mask_hud=True)
+    assert np.array_equal(view_only[:32].cpu().numpy(), expected["obs"])
+    assert np.array_equal(indexed[:32, :208].cpu().numpy(), expected["indexed"][:, :208])
+    stack = torch.zeros((n, 4, 84, 84), dtype=torch.uint8, device=DEV)
+    r.step(_dev(lanes), _dev(things), stack)
+    assert torch.equal(stack[:, 3], full)
