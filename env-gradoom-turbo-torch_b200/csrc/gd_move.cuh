@@ -1,4 +1,8 @@
-/* Per-tic player kinematics (gd_player_tics): one thread per lane.
+/* Per-tic player kinematics (gd_player_tics): one warp per lane.  The 32 threads of a warp
+ * carry the same player record through the same control flow; only the loops over the map's
+ * walls and sectors are split between them (thread t takes walls t, t + 32, ...) and joined
+ * with exact warp reductions (any, float min / max, minimum of (fraction, wall index)), so
+ * the result is the serial one.
  * Part of gd_render.cu (one translation unit); not meant to be included elsewhere.
  *
  * Restates src/gradoom/engine.py: _move_player (4344-4575), _doom_axis_slide_move
@@ -36,20 +40,26 @@ __device__ static float gdm_fixed_to_float(i64 v) { return (float)v / 65536.0f; 
 /* torch.round of a float64: half to even */
 __device__ static i64 gdm_round_ratio(i64 numerator, i64 denominator) { return (i64)rint(__ddiv_rn(__dmul_rn((double)numerator, 65536.0), (double)denominator)); }
 
-/* engine.py:9598-9617 */
+#define GDM_ALL 0xffffffffu
+#define GDM_T ((int)(threadIdx.x & 31))
+
+/* engine.py:9598-9617: the first sector with an odd crossing count; 32 sectors per round */
 __device__ static int gdm_sector_at(const GdMoveMap *m, float px, float py) {
-  for (int s = 0; s < m->S; ++s) {
+  for (int base = 0; base < m->S; base += 32) {
+    const int s = base + GDM_T;
     int crossings = 0;
-    for (int k = m->edgeOff[s]; k < m->edgeOff[s + 1]; ++k) {
-      const float *e = &m->walls[m->edgeWalls[k] * 4];
-      float x1 = e[0], y1 = e[1], x2 = e[2], y2 = e[3];
-      int crosses = (y1 > py) != (y2 > py);
-      float dy = y2 - y1;
-      float safe = fabsf(dy) < 1e-6f ? 1.0f : dy;
-      float cx = x1 + (py - y1) * (x2 - x1) / safe;
-      crossings += crosses && (px < cx);
-    }
-    if (crossings & 1) return s;
+    if (s < m->S)
+      for (int k = m->edgeOff[s]; k < m->edgeOff[s + 1]; ++k) {
+        const float *e = &m->walls[m->edgeWalls[k] * 4];
+        float x1 = e[0], y1 = e[1], x2 = e[2], y2 = e[3];
+        int crosses = (y1 > py) != (y2 > py);
+        float dy = y2 - y1;
+        float safe = fabsf(dy) < 1e-6f ? 1.0f : dy;
+        float cx = x1 + (py - y1) * (x2 - x1) / safe;
+        crossings += crosses && (px < cx);
+      }
+    const unsigned odd = __ballot_sync(GDM_ALL, crossings & 1);
+    if (odd) return base + __ffs(odd) - 1;
   }
   return 0;
 }
@@ -70,16 +80,17 @@ __device__ static int gdm_box_touches(const float *w, float x, float y, float ra
 
 /* engine.py:2555-2598: any one-sided wall crosses the player's box */
 __device__ static int gdm_points_collide(const GdMoveMap *m, float x, float y) {
-  for (int w = 0; w < m->W; ++w)
-    if (m->wsec[w * 2 + 1] < 0 && gdm_box_touches(&m->walls[w * 4], x, y, RADIUS)) return 1;
-  return 0;
+  int hit = 0;
+  for (int w = GDM_T; w < m->W; w += 32)
+    hit |= m->wsec[w * 2 + 1] < 0 && gdm_box_touches(&m->walls[w * 4], x, y, RADIUS);
+  return __any_sync(GDM_ALL, hit);
 }
 
 /* engine.py:2600-2711: floor and ceiling under the player's box */
 __device__ static void gdm_opening_at(const GdMoveMap *m, float x, float y, float *floorOut, float *ceilOut) {
   int c = gdm_sector_at(m, x, y);
   float floor = m->secF[c * 2], ceiling = m->secF[c * 2 + 1];
-  for (int w = 0; w < m->W; ++w) {
+  for (int w = GDM_T; w < m->W; w += 32) {
     if (!gdm_box_touches(&m->walls[w * 4], x, y, RADIUS)) continue;
     for (int side = 0; side < 2; ++side) {
       int s = m->wsec[w * 2 + side];
@@ -87,6 +98,10 @@ __device__ static void gdm_opening_at(const GdMoveMap *m, float x, float y, floa
       floor = fmaxf(floor, m->secF[s * 2]);
       ceiling = fminf(ceiling, m->secF[s * 2 + 1]);
     }
+  }
+  for (int d = 16; d; d >>= 1) {
+    floor = fmaxf(floor, __shfl_xor_sync(GDM_ALL, floor, d));
+    ceiling = fminf(ceiling, __shfl_xor_sync(GDM_ALL, ceiling, d));
   }
   *floorOut = floor; *ceilOut = ceiling;
 }
@@ -139,12 +154,26 @@ __device__ static int gdm_player_collides(const GdMoveMap *m, const GdmSolids *s
 
 typedef struct { i64 fraction; int hitHorizontal, contact; i64 axis; } GdmContact;
 
+/* The serial rule keeps the first blocking wall that reaches the smallest fraction (and the first
+ * blocking wall of all when none is valid): the minimum of (fraction, wall index) over the warp. */
+__device__ static void gdm_first_smallest(i64 &best, i64 &axis, int &wall) {
+  unsigned long long key = ((unsigned long long)best << 32) | (unsigned)wall;
+  for (int d = 16; d; d >>= 1) {
+    const unsigned long long other = __shfl_xor_sync(GDM_ALL, key, d);
+    key = other < key ? other : key;
+  }
+  wall = (int)(unsigned)key;
+  best = (i64)(key >> 32);
+  axis = __shfl_sync(GDM_ALL, axis, wall & 31);
+  if (wall == 0x7fffffff) { best = FU + 1; axis = 0; }      /* no blocking wall at all */
+}
+
 /* engine.py:3120-3205 */
 __device__ static GdmContact gdm_axis_contact(const GdMoveMap *m, i64 px, i64 py, i64 mx, i64 my) {
-  i64 hBest = FU + 1, vBest = FU + 1, hAxis = 0, vAxis = 0;
-  int hFirst = 1, vFirst = 1;
+  i64 hBest = FU + 2, vBest = FU + 2, hAxis = 0, vAxis = 0;
+  int hWall = 0x7fffffff, vWall = 0x7fffffff;
   i64 safeY = my == 0 ? 1 : my, safeX = mx == 0 ? 1 : mx;
-  for (int w = 0; w < m->W; ++w) {
+  for (int w = GDM_T; w < m->W; w += 32) {
     if (m->wsec[w * 2 + 1] >= 0) continue;                    /* blocking (one-sided) walls only */
     const float *f = &m->walls[w * 4];
     i64 x1 = (i64)rintf(f[0] * 65536.0f), y1 = (i64)rintf(f[1] * 65536.0f);
@@ -156,7 +185,7 @@ __device__ static GdmContact gdm_axis_contact(const GdMoveMap *m, i64 px, i64 py
       int valid = (y1 == y2) && my != 0 && fraction >= 0 && fraction <= FU && hx >= gdm_imin(x1, x2) - RADIUS_FIXED &&
                   hx <= gdm_imax(x1, x2) + RADIUS_FIXED;
       i64 cand = valid ? fraction : FU + 1;
-      if (hFirst || cand < hBest) { hBest = cand; hAxis = target; hFirst = 0; }
+      if (cand < hBest) { hBest = cand; hAxis = target; hWall = w; }
     }
     {
       i64 target = x1 - gdm_isign(mx) * RADIUS_FIXED;
@@ -165,9 +194,11 @@ __device__ static GdmContact gdm_axis_contact(const GdMoveMap *m, i64 px, i64 py
       int valid = (x1 == x2) && mx != 0 && fraction >= 0 && fraction <= FU && vy >= gdm_imin(y1, y2) - RADIUS_FIXED &&
                   vy <= gdm_imax(y1, y2) + RADIUS_FIXED;
       i64 cand = valid ? fraction : FU + 1;
-      if (vFirst || cand < vBest) { vBest = cand; vAxis = target; vFirst = 0; }
+      if (cand < vBest) { vBest = cand; vAxis = target; vWall = w; }
     }
   }
+  gdm_first_smallest(hBest, hAxis, hWall);
+  gdm_first_smallest(vBest, vAxis, vWall);
   GdmContact c;
   c.fraction = gdm_imin(hBest, vBest);
   c.hitHorizontal = hBest <= vBest;
@@ -371,15 +402,18 @@ struct GdMoveParams {
   int32_t *lanes;
 };
 
-__global__ void __launch_bounds__(128) gd_player_tics_kernel(const GdMoveParams q) {
-  const int l = blockIdx.x * blockDim.x + threadIdx.x;
-  if (l >= q.n) return;
+#define GDM_BLOCK 128      /* four lanes per block */
+
+__global__ void __launch_bounds__(GDM_BLOCK) gd_player_tics_kernel(const GdMoveParams q) {
+  const int l = (int)(((size_t)blockIdx.x * GDM_BLOCK + threadIdx.x) >> 5);
+  if (l >= q.n) return;                                        /* whole warps leave */
   int32_t p[GD_PLAYER_WORDS];
 #pragma unroll
   for (int k = 0; k < GD_PLAYER_WORDS; ++k) p[k] = q.players[(size_t)l * GD_PLAYER_WORDS + k];
   GdmSolids so = {q.hasActors ? &q.actors : nullptr, l};
   const uint32_t buttons = q.buttons[l];
   for (int t = 0; t < q.tics; ++t) gdm_player_tic(&q.map, &so, p, buttons, q.episodeTimeout);
+  if (GDM_T != 0) return;                                      /* every thread holds the same record */
 #pragma unroll
   for (int k = 0; k < GD_PLAYER_WORDS; ++k) q.players[(size_t)l * GD_PLAYER_WORDS + k] = p[k];
   if (q.lanes) {
@@ -406,6 +440,8 @@ __global__ void __launch_bounds__(128) gd_player_tics_kernel(const GdMoveParams 
 #undef PLAYER_HEIGHT
 #undef VIEW_HEIGHT
 #undef U32MASK
+#undef GDM_ALL
+#undef GDM_T
 
 extern "C" int gd_player_tics(const gd_renderer *r, int32_t *players, const uint32_t *buttons, const gd_solid_actors *actors,
                               int n, int tics, int episode_timeout, int32_t *lanes, int *status, void *stream) {
@@ -431,7 +467,8 @@ extern "C" int gd_player_tics(const gd_renderer *r, int32_t *players, const uint
   q.hasActors = actors && actors->enemy_slots > 0;
   if (q.hasActors) q.actors = *actors; else memset(&q.actors, 0, sizeof q.actors);
   q.players = players; q.buttons = buttons; q.n = n; q.tics = tics; q.episodeTimeout = episode_timeout; q.lanes = lanes;
-  gd_player_tics_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t)stream>>>(q);
+  const int lanesPerBlock = GDM_BLOCK / 32;
+  gd_player_tics_kernel<<<(n + lanesPerBlock - 1) / lanesPerBlock, GDM_BLOCK, 0, (cudaStream_t)stream>>>(q);
   return cudaGetLastError() == cudaSuccess ? GD_OK : GD_ERR_CUDA;
 }
 
