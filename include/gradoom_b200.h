@@ -273,7 +273,7 @@ int gd_pack_state(const gd_renderer *r, const gd_engine_state *state, int32_t *l
                   void *flags_scratch, size_t flags_scratch_bytes, int *status, void *stream);
 
 /*
- * Per-tic player kinematics on the device, one thread per lane: turning with the
+ * Per-tic player kinematics on the device, one warp per lane: turning with the
  * keyboard ramp, thrust, bob, the wall slide with step-up over the openings under
  * the player's box, solid actors in the way, friction, view-height easing, gravity
  * and landing.  Advances every lane by `tics` game tics under the lane's button mask
