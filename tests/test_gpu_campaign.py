@@ -2,7 +2,8 @@
 size, texture sizes, floor range, diagonal lines, masked middle textures, split lines, bullet
 chips, thing count and the status bar all vary; the players walk with the kinematics kernel
 before the comparison, so some stand in doorways.  Every indexed frame and observation must be equal.  With
-GD_CAMPAIGN_LOG set, one line per specification is appended to that file."""
+GD_CAMPAIGN_LOG set, one line per specification is appended to that file; GD_CAMPAIGN_SPECS and
+GD_CAMPAIGN_FIRST widen or move the range of specification numbers (default: the first 24)."""
 
 import dataclasses
 import json
@@ -15,7 +16,8 @@ import torch
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
-SPECS = 24
+SPECS = int(os.environ.get("GD_CAMPAIGN_SPECS", "24"))
+FIRST = int(os.environ.get("GD_CAMPAIGN_FIRST", "0"))
 LANES = 256
 
 
@@ -28,7 +30,7 @@ def _spec(gdscene, trial):
         diagonals=bool(rng.random() < 0.4), mid_textures=float(rng.choice([0.0, 0.0, 0.3, 0.8]))), rng
 
 
-@pytest.mark.parametrize("trial", range(SPECS))
+@pytest.mark.parametrize("trial", range(FIRST, FIRST + SPECS))
 def test_random_scene_specification(trial, pkg, oracle):
     from gradoom_b200 import native, scene as gdscene, stepper
     from gradoom_b200.env import action_matrix
