@@ -3,7 +3,9 @@ size, texture sizes, floor range, diagonal lines, masked middle textures, split 
 chips, thing count and the status bar all vary; the players walk with the kinematics kernel
 before the comparison, so some stand in doorways.  Every indexed frame and observation must be equal.  With
 GD_CAMPAIGN_LOG set, one line per specification is appended to that file; GD_CAMPAIGN_SPECS and
-GD_CAMPAIGN_FIRST widen or move the range of specification numbers (default: the first 24)."""
+GD_CAMPAIGN_FIRST widen or move the range of specification numbers (default: the first 24);
+GD_CAMPAIGN_MAX_GRID raises the largest grid side (default 8; 16 reaches 800-wall maps, which keep fewer
+tables in shared memory)."""
 
 import dataclasses
 import json
@@ -18,13 +20,14 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 SPECS = int(os.environ.get("GD_CAMPAIGN_SPECS", "24"))
 FIRST = int(os.environ.get("GD_CAMPAIGN_FIRST", "0"))
+MAX_GRID = int(os.environ.get("GD_CAMPAIGN_MAX_GRID", "8"))
 LANES = 256
 
 
 def _spec(gdscene, trial):
     rng = np.random.default_rng(9000 + trial)
     return gdscene.GridSpec(
-        rows=int(rng.integers(2, 9)), cols=int(rng.integers(2, 9)), room=float(rng.choice([96.0, 128.0, 192.0, 256.0, 320.0])),
+        rows=int(rng.integers(2, MAX_GRID + 1)), cols=int(rng.integers(2, MAX_GRID + 1)), room=float(rng.choice([96.0, 128.0, 192.0, 256.0, 320.0])),
         seed=300 + trial, wall_textures=int(rng.choice([4, 8, 16])), tex_w=int(rng.choice([64, 128])), tex_h=128,
         flats=int(rng.choice([2, 4, 8])), floor_max=int(rng.choice([0, 32, 64, 128])),
         diagonals=bool(rng.random() < 0.4), mid_textures=float(rng.choice([0.0, 0.0, 0.3, 0.8]))), rng
