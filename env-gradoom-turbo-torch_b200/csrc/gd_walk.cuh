@@ -8,6 +8,7 @@ struct GdPlaneSpan {
   i64 basex, basey, pviewx, pviewy, phf, gv, shadeBase;
   const uint8_t *tex;
   int wbits, hbits, texW;
+  bool narrow;   /* the row's light term fits 32-bit arithmetic (see gd_plane_pixel) */
 };
 
 /* Column-independent part of a span setup, one entry per (sector, floor or
@@ -41,13 +42,18 @@ __device__ __noinline__ void gd_plane_entry_setup(const GdScene &sc, const GdVie
   e.gv = gd_min(gd_div(GD_FLOOR_VIS << 16, gd_max(e.phf, 1)), (1LL << 31) - 1);
   i64 light = si.x + v.flashLight * 16;
   e.shadeBase = 64 * GD_FU - (light + 12) * (GD_FU / 4);
+  /* gv lies in [0, 2^31) by construction; with the screen centre within +-2^30 (any pitch short of
+   * +-89.5 degrees) and a shade base that fits an int, the light term of a pixel needs one 32 x 32 -> 64
+   * multiply; the flag travels in the spare bits of hbits */
+  const bool narrow = v.center > -(1LL << 30) && v.center < (1LL << 30) && e.shadeBase > -(1LL << 31) && e.shadeBase < (1LL << 31);
+  e.hbits |= narrow ? 256 : 0;
 }
 
 __device__ __forceinline__ void gd_plane_setup(const GdScene &sc, const GdPlaneEntry *table, int sector, bool isFloor,
                                                int x, GdPlaneSpan &p) {
   const GdPlaneEntry &e = table[gd_secidx(sc, sector) * 2 + (isFloor ? 1 : 0)];
   i64 col = (i64)x - 159;
-  p.wbits = e.wbits; p.hbits = e.hbits; p.texW = sc.texW;
+  p.wbits = e.wbits; p.hbits = e.hbits & 255; p.narrow = (e.hbits & 256) != 0; p.texW = sc.texW;
   p.tex = e.tex;
   p.basex = e.bx0 + col * e.xstep;
   p.basey = e.by0 + col * e.ystep;
@@ -58,17 +64,29 @@ __device__ __forceinline__ void gd_plane_setup(const GdScene &sc, const GdPlaneE
   p.shadeBase = e.shadeBase;
 }
 
-__device__ __forceinline__ uint8_t gd_plane_pixel(const GdPlaneSpan &p, const GdView &v, const unsigned *yslope,
+/* One visplane pixel (R_DrawSpan, engine.py:10879-10954).  kNarrow: the span's `narrow` flag holds, so
+ * |center - y * 65536| < 2^31 and the light term is exact in 32-bit arithmetic: vis = min(gv * rowDist >> 16,
+ * 24 * 65536) is 24 * 65536 exactly when the 64-bit product is at least 0x18 << 32. */
+template <bool kNarrow>
+__device__ __forceinline__ uint8_t gd_plane_pixel(const GdPlaneSpan &p, i64 center, const unsigned *yslope,
                                                   const uint8_t *colormap, int y) {
   i64 distance = gd_wmul(p.phf, (i64)yslope[y]) >> 16;
   i64 xfrac = ((gd_wmul(distance, p.basex) >> 16) + p.pviewx) & GD_U32MASK;
   i64 yfrac = ((gd_wmul(distance, p.basey) >> 16) + p.pviewy) & GD_U32MASK;
   int u = (int)(xfrac >> (32 - p.wbits)), tv = (int)(yfrac >> (32 - p.hbits));
   uint8_t texel = p.tex[tv * p.texW + u];
-  i64 rowDist = v.center - (i64)y * GD_FU;
-  if (rowDist < 0) rowDist = -rowDist;
-  i64 vis = gd_min(gd_wmul(p.gv, rowDist) >> 16, 24 * GD_FU);
-  int shade = (int)gd_clamp((p.shadeBase - vis) >> 16, 0, 31);
+  int shade;
+  if (kNarrow) {
+    const int rowDist = abs((int)center - (y << 16));
+    const i64 vis64 = (i64)(int)p.gv * (i64)rowDist;
+    const int vis = (unsigned)(vis64 >> 32) >= 0x18u ? 24 * 65536 : (int)(unsigned)(vis64 >> 16);
+    shade = min(max(((int)p.shadeBase - vis) >> 16, 0), 31);
+  } else {
+    i64 rowDist = center - (i64)y * GD_FU;
+    if (rowDist < 0) rowDist = -rowDist;
+    i64 vis = gd_min(gd_wmul(p.gv, rowDist) >> 16, 24 * GD_FU);
+    shade = (int)gd_clamp((p.shadeBase - vis) >> 16, 0, 31);
+  }
   return colormap[shade * 256 + texel];
 }
 
@@ -503,19 +521,17 @@ __device__ __noinline__ void gd_draw_tier(const GdScene &sc, const GdView &v, co
   }
 }
 
-__device__ __noinline__ void gd_mark_plane(const GdScene &sc, const GdView &v, const GdShared &sh, int x, int ya, int yb,
-                              int sector, bool isFloor, unsigned *owned, const unsigned *filled) {
-  if (ya >= yb) return;
-  const int k0 = ya >> 5, k1 = (yb - 1) >> 5;
-  unsigned any = 0;
-#pragma unroll 1
-  for (int k = k0; k <= k1; ++k) any |= gd_range_word(k, ya, yb) & ~owned[k * GD_SW];
-  if (!any) return;
-  GdPlaneSpan p;
-  gd_plane_setup(sc, sh.planeTab, sector, isFloor, x, p);
+/* Rows [ya,yb) of column x that no plane owns yet become the span's; those no wall tier filled are drawn.
+ * The pointers and the centre are taken into registers first: the byte stores into the frame would make the
+ * compiler read them again from the shared structures on every trip. */
+template <bool kNarrow>
+__device__ __forceinline__ void gd_plane_rows(const GdPlaneSpan &p, i64 center, const GdShared &sh, int x, int ya, int yb,
+                                              unsigned *owned, const unsigned *filled) {
   uint8_t *dst = sh.frame + x;
+  const unsigned *yslope = sh.yslope;
+  const uint8_t *colormap = sh.colormap;
 #pragma unroll 1
-  for (int k = k0; k <= k1; ++k) {
+  for (int k = ya >> 5; k <= (yb - 1) >> 5; ++k) {
     unsigned have = owned[k * GD_SW];
     unsigned fresh = gd_range_word(k, ya, yb) & ~have;
     if (!fresh) continue;
@@ -528,12 +544,26 @@ __device__ __noinline__ void gd_mark_plane(const GdScene &sc, const GdView &v, c
       m &= m - 1;
       int b1 = m ? __ffs(m) - 1 : b0;
       m &= m - 1;
-      uint8_t p0 = gd_plane_pixel(p, v, sh.yslope, sh.colormap, y0 + b0);
-      uint8_t p1 = gd_plane_pixel(p, v, sh.yslope, sh.colormap, y0 + b1);
+      uint8_t p0 = gd_plane_pixel<kNarrow>(p, center, yslope, colormap, y0 + b0);
+      uint8_t p1 = gd_plane_pixel<kNarrow>(p, center, yslope, colormap, y0 + b1);
       dst[(y0 + b0) * GD_SW] = p0;
       dst[(y0 + b1) * GD_SW] = p1;
     }
   }
+}
+
+__device__ __noinline__ void gd_mark_plane(const GdScene &sc, const GdView &v, const GdShared &sh, int x, int ya, int yb,
+                              int sector, bool isFloor, unsigned *owned, const unsigned *filled) {
+  if (ya >= yb) return;
+  const int k0 = ya >> 5, k1 = (yb - 1) >> 5;
+  unsigned any = 0;
+#pragma unroll 1
+  for (int k = k0; k <= k1; ++k) any |= gd_range_word(k, ya, yb) & ~owned[k * GD_SW];
+  if (!any) return;
+  GdPlaneSpan p;
+  gd_plane_setup(sc, sh.planeTab, sector, isFloor, x, p);
+  if (p.narrow) gd_plane_rows<true>(p, v.center, sh, x, ya, yb, owned, filled);
+  else gd_plane_rows<false>(p, v.center, sh, x, ya, yb, owned, filled);
 }
 
 /* ---- two-sided middle textures (engine.py:13424-13745) -----------------------
