@@ -108,6 +108,23 @@ __device__ __forceinline__ int gd_wsec(const GdScene &sc, int i) {
   return s;
 }
 
+/* Shared-memory accesses of the pixel loops by 32-bit shared-space address: the pointers of the shared-memory
+ * map are generic (they are read from a structure), so the compiler would otherwise carry 64-bit addresses
+ * and issue generic loads and stores.  The loads are for tables nothing writes while a lane is drawn. */
+__device__ __forceinline__ unsigned gd_shared_addr(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ unsigned gd_lds8(unsigned addr) {
+  unsigned v;
+  asm("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ unsigned gd_lds32(unsigned addr) {
+  unsigned v;
+  asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void gd_sts8(unsigned addr, unsigned v) {
+  asm volatile("st.shared.u8 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
 __device__ __forceinline__ i64 gd_min(i64 a, i64 b) { return a < b ? a : b; }
 __device__ __forceinline__ i64 gd_max(i64 a, i64 b) { return a > b ? a : b; }
 __device__ __forceinline__ i64 gd_clamp(i64 v, i64 lo, i64 hi) { return v < lo ? lo : (v > hi ? hi : v); }

@@ -232,7 +232,7 @@ __device__ void gd_fallback_pass(const GdScene &sc, const GdView &v, const GdSha
     if (!own.unresolved) {
       GdPlaneSpan p;
       gd_plane_setup(sc, sh.planeTab, own.sector, own.isFloor, px, p);
-      sh.frame[py * GD_SW + px] = gd_plane_pixel<false>(p, v.center, sh.yslope, sh.colormap, py);
+      sh.frame[py * GD_SW + px] = (uint8_t)gd_plane_pixel<false>(p, v.center, gd_shared_addr(sh.yslope), gd_shared_addr(sh.colormap), py);
       atomicOr(&owned[(py >> 5) * GD_SW + px], 1u << (py & 31));
       queue[i] = -1;
     } else {
@@ -313,7 +313,7 @@ __device__ void gd_fallback_pass(const GdScene &sc, const GdView &v, const GdSha
     const bool isFloor = ((float)py - gd_flat_ray(sc, v, px).center) > 0;
     GdPlaneSpan p;
     gd_plane_setup(sc, sh.planeTab, sector, isFloor, px, p);
-    sh.frame[py * GD_SW + px] = gd_plane_pixel<false>(p, v.center, sh.yslope, sh.colormap, py);
+    sh.frame[py * GD_SW + px] = (uint8_t)gd_plane_pixel<false>(p, v.center, gd_shared_addr(sh.yslope), gd_shared_addr(sh.colormap), py);
     atomicOr(&owned[(py >> 5) * GD_SW + px], 1u << (py & 31));
   }
   __syncthreads();

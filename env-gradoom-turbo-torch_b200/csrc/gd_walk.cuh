@@ -68,9 +68,8 @@ __device__ __forceinline__ void gd_plane_setup(const GdScene &sc, const GdPlaneE
  * |center - y * 65536| < 2^31 and the light term is exact in 32-bit arithmetic: vis = min(gv * rowDist >> 16,
  * 24 * 65536) is 24 * 65536 exactly when the 64-bit product is at least 0x18 << 32. */
 template <bool kNarrow>
-__device__ __forceinline__ uint8_t gd_plane_pixel(const GdPlaneSpan &p, i64 center, const unsigned *yslope,
-                                                  const uint8_t *colormap, int y) {
-  i64 distance = gd_wmul(p.phf, (i64)yslope[y]) >> 16;
+__device__ __forceinline__ unsigned gd_plane_pixel(const GdPlaneSpan &p, i64 center, unsigned yslope, unsigned colormap, int y) {
+  i64 distance = gd_wmul(p.phf, (i64)gd_lds32(yslope + y * 4)) >> 16;
   i64 xfrac = ((gd_wmul(distance, p.basex) >> 16) + p.pviewx) & GD_U32MASK;
   i64 yfrac = ((gd_wmul(distance, p.basey) >> 16) + p.pviewy) & GD_U32MASK;
   int u = (int)(xfrac >> (32 - p.wbits)), tv = (int)(yfrac >> (32 - p.hbits));
@@ -87,7 +86,7 @@ __device__ __forceinline__ uint8_t gd_plane_pixel(const GdPlaneSpan &p, i64 cent
     i64 vis = gd_min(gd_wmul(p.gv, rowDist) >> 16, 24 * GD_FU);
     shade = (int)gd_clamp((p.shadeBase - vis) >> 16, 0, 31);
   }
-  return colormap[shade * 256 + texel];
+  return gd_lds8(colormap + shade * 256 + texel);
 }
 
 /* The 208-row column masks live in shared memory, one word column per screen
@@ -491,12 +490,12 @@ __device__ __noinline__ void gd_draw_tier(const GdScene &sc, const GdView &v, co
   unsigned step = (unsigned)vstep;
   const uint8_t *col = sc.texAtlasCol + ((size_t)texId * sc.texW + u) * sc.texH;
   int shadeN = gd_wall_shade(t.light, vis), shadeT = gd_wall_shade(t.light, firstVis);
-  const uint8_t *cmN = sh.colormap + shadeN * 256, *cmT = sh.colormap + shadeT * 256;
+  const unsigned cmN = gd_shared_addr(sh.colormap + shadeN * 256), cmT = gd_shared_addr(sh.colormap + shadeT * 256);
   /* rows lit with the group's first-column light */
   const int tailA = tailValid ? tailBottom : GD_VH, oTailA = oTailValid ? max(oa, oTailBottom) : 0,
             oTailB = oTailValid ? ob : 0;
   const int shift = 32 - hbits;
-  uint8_t *dst = sh.frame + x;
+  const unsigned dst = gd_shared_addr(sh.frame + x);
 #pragma unroll 1
   for (int k = ya >> 5; k <= (yb - 1) >> 5; ++k) {
     unsigned have = filled[k * GD_SW];
@@ -513,10 +512,10 @@ __device__ __noinline__ void gd_draw_tier(const GdScene &sc, const GdView &v, co
       int b1 = m ? __ffs(m) - 1 : b0;
       m &= m - 1;
       unsigned f0 = base + (unsigned)(y0 + b0) * step, f1 = base + (unsigned)(y0 + b1) * step;
-      uint8_t t0 = col[f0 >> shift], t1 = col[f1 >> shift];
-      uint8_t p0 = ((tailM >> b0) & 1u ? cmT : cmN)[t0], p1 = ((tailM >> b1) & 1u ? cmT : cmN)[t1];
-      dst[(y0 + b0) * GD_SW] = p0;
-      dst[(y0 + b1) * GD_SW] = p1;
+      const unsigned t0 = col[f0 >> shift], t1 = col[f1 >> shift];
+      const unsigned p0 = gd_lds8(((tailM >> b0) & 1u ? cmT : cmN) + t0), p1 = gd_lds8(((tailM >> b1) & 1u ? cmT : cmN) + t1);
+      gd_sts8(dst + (y0 + b0) * GD_SW, p0);
+      gd_sts8(dst + (y0 + b1) * GD_SW, p1);
     }
   }
 }
@@ -527,9 +526,8 @@ __device__ __noinline__ void gd_draw_tier(const GdScene &sc, const GdView &v, co
 template <bool kNarrow>
 __device__ __forceinline__ void gd_plane_rows(const GdPlaneSpan &p, i64 center, const GdShared &sh, int x, int ya, int yb,
                                               unsigned *owned, const unsigned *filled) {
-  uint8_t *dst = sh.frame + x;
-  const unsigned *yslope = sh.yslope;
-  const uint8_t *colormap = sh.colormap;
+  const unsigned dst = gd_shared_addr(sh.frame + x);
+  const unsigned yslope = gd_shared_addr(sh.yslope), colormap = gd_shared_addr(sh.colormap);
 #pragma unroll 1
   for (int k = ya >> 5; k <= (yb - 1) >> 5; ++k) {
     unsigned have = owned[k * GD_SW];
@@ -544,10 +542,10 @@ __device__ __forceinline__ void gd_plane_rows(const GdPlaneSpan &p, i64 center, 
       m &= m - 1;
       int b1 = m ? __ffs(m) - 1 : b0;
       m &= m - 1;
-      uint8_t p0 = gd_plane_pixel<kNarrow>(p, center, yslope, colormap, y0 + b0);
-      uint8_t p1 = gd_plane_pixel<kNarrow>(p, center, yslope, colormap, y0 + b1);
-      dst[(y0 + b0) * GD_SW] = p0;
-      dst[(y0 + b1) * GD_SW] = p1;
+      const unsigned p0 = gd_plane_pixel<kNarrow>(p, center, yslope, colormap, y0 + b0);
+      const unsigned p1 = gd_plane_pixel<kNarrow>(p, center, yslope, colormap, y0 + b1);
+      gd_sts8(dst + (y0 + b0) * GD_SW, p0);
+      gd_sts8(dst + (y0 + b1) * GD_SW, p1);
     }
   }
 }
