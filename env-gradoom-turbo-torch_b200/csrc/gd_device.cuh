@@ -108,10 +108,19 @@ __device__ __forceinline__ int gd_wsec(const GdScene &sc, int i) {
   return s;
 }
 
+/* The CTA's dynamic shared memory. */
+extern __shared__ __align__(16) uint8_t gd_smem[];
+
 /* Shared-memory accesses of the pixel loops by 32-bit shared-space address: the pointers of the shared-memory
  * map are generic (they are read from a structure), so the compiler would otherwise carry 64-bit addresses
  * and issue generic loads and stores.  The loads are for tables nothing writes while a lane is drawn. */
 __device__ __forceinline__ unsigned gd_shared_addr(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
+/* The same pointer, re-derived from the shared array itself: the compiler then knows its address space and
+ * addresses everything reached through it with 32 bits and shared-space instructions. */
+template <class T>
+__device__ __forceinline__ T *gd_as_shared(T *p) {
+  return (T *)(gd_smem + (gd_shared_addr(p) - gd_shared_addr(gd_smem)));
+}
 __device__ __forceinline__ unsigned gd_lds8(unsigned addr) {
   unsigned v;
   asm("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));

@@ -166,7 +166,6 @@ __device__ inline void gd_carve(uint8_t *base, int W, int maxThings, int frameRo
 #include "gd_output.cuh"
 
 /* ---- the kernel ----------------------------------------------------------- */
-extern __shared__ __align__(16) uint8_t gd_smem[];
 
 /* Two instantiations: kSplit = the scene carries projection fragments of split lines. */
 template <bool kSplit>

@@ -155,6 +155,8 @@ template <bool kSplit>
 __device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWall *walls, const GdWall *frags,
                                  const unsigned *ownerMask, const GdRowProj *rowproj, float *hitD, float *hitA, uint8_t *hitF, int x, float rx,
                                  float ry, const GdColState &c, GdIter &it) {
+  walls = gd_as_shared(walls); ownerMask = gd_as_shared(ownerMask);
+  hitD = gd_as_shared(hitD); hitA = gd_as_shared(hitA); hitF = gd_as_shared(hitF);
   const int curSector = c.cur;
   const int current = GD_CHECK_SECTOR(curSector < 0 ? 0 : curSector, sc.S);
   const float prev = c.prev;
@@ -479,6 +481,7 @@ __device__ __noinline__ void gd_draw_tier(const GdScene &sc, const GdView &v, co
 #ifdef GD_CHECKED
   if (texId >= sc.T) { atomicOr(gdCheckedStatus, GD_STATUS_BAD_INDEX); return; }   /* the tier stays undrawn */
 #endif
+  filled = gd_as_shared(filled);
   const int4 ti = *reinterpret_cast<const int4 *>(&sc.texInfo[texId * 4]);
   int tw = ti.x, hbits = ti.w;
   int u = gd_pymod_width((t.hoff + t.tox) >> 16, tw);
@@ -528,6 +531,7 @@ __device__ __forceinline__ void gd_plane_rows(const GdPlaneSpan &p, i64 center, 
                                               unsigned *owned, const unsigned *filled) {
   const unsigned dst = gd_shared_addr(sh.frame + x);
   const unsigned yslope = gd_shared_addr(sh.yslope), colormap = gd_shared_addr(sh.colormap);
+  owned = gd_as_shared(owned); filled = gd_as_shared(filled);
 #pragma unroll 1
   for (int k = ya >> 5; k <= (yb - 1) >> 5; ++k) {
     unsigned have = owned[k * GD_SW];
@@ -697,7 +701,7 @@ __device__ void gd_walk(const GdScene &sc, const GdView &v, const GdShared &sh, 
   const unsigned quadBase = lane & ~3u;
   float rx, ry;
   gd_ray(v, x, rx, ry);
-  unsigned *filled = sh.masks + x, *owned = sh.masks + 7 * GD_SW + x;
+  unsigned *filled = gd_as_shared(sh.masks) + x, *owned = filled + 7 * GD_SW;
 #pragma unroll
   for (int k = 0; k < 7; ++k) { filled[k * GD_SW] = 0; owned[k * GD_SW] = 0; }
   if (sc.M > 0) { sh.maskedDist[x] = GD_INF; sh.maskedInfo[x] = 0xFFFF0000u | GD_VH; }
