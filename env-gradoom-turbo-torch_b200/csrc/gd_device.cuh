@@ -119,7 +119,7 @@ __device__ __forceinline__ unsigned gd_shared_addr(const void *p) { return (unsi
  * addresses everything reached through it with 32 bits and shared-space instructions. */
 template <class T>
 __device__ __forceinline__ T *gd_as_shared(T *p) {
-  return (T *)(gd_smem + (gd_shared_addr(p) - gd_shared_addr(gd_smem)));
+  return (T *)(gd_smem + (int)(gd_shared_addr(p) - gd_shared_addr(gd_smem)));   /* static shared variables lie below */
 }
 __device__ __forceinline__ unsigned gd_lds8(unsigned addr) {
   unsigned v;

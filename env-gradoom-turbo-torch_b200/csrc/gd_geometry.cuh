@@ -189,16 +189,20 @@ __device__ __forceinline__ GdHit gd_hit(const GdScene &sc, const GdView &v, cons
   return h;
 }
 
-__device__ __noinline__ GdHit gd_hit_slow(const GdScene &sc, const GdView &v, const GdWall *walls, int w, int x,
+__device__ __noinline__ GdHit gd_hit_slow(const GdScene &sc_, const GdView &v_, const GdWall *walls, int w, int x,
                                           float rx, float ry) {
+  const GdScene &sc = *gd_as_shared(&sc_);
+  const GdView &v = *gd_as_shared(&v_);
   return gd_hit(sc, v, walls, w, x, rx, ry);
 }
 
 __device__ __forceinline__ float gd_tol(float d) { return fmaxf(fabsf(d) / 128.0f, 4.0f); }
 
 /* Endpoint owner of wall w at column x (engine.py:11589-11730). */
-__device__ __noinline__ void gd_endpoint_owner(const GdScene &sc, const GdView &v, const GdWall *walls, int w, int x, float rx,
+__device__ __noinline__ void gd_endpoint_owner(const GdScene &sc_, const GdView &v_, const GdWall *walls, int w, int x, float rx,
                                   float ry, const GdHit &hw, int &ownerIdx, float &ownerDist) {
+  const GdScene &sc = *gd_as_shared(&sc_);
+  const GdView &v = *gd_as_shared(&v_);
   const GdWall &wv = walls[w];
   float d = hw.d;
   float tol = gd_tol(d);
@@ -246,7 +250,8 @@ __device__ __noinline__ void gd_endpoint_owner(const GdScene &sc, const GdView &
 }
 
 /* PrepWall for one (column, wall) (engine.py:10672-10739). */
-__device__ __noinline__ void gd_prep_wall(const GdScene &sc, const GdWall &wv, int w, int x, i64 &hoff, i64 &vstep) {
+__device__ __noinline__ void gd_prep_wall(const GdScene &sc_, const GdWall &wv, int w, int x, i64 &hoff, i64 &vstep) {
+  const GdScene &sc = *gd_as_shared(&sc_);
   i64 tx1 = wv.tx[0], tx2 = wv.tx[1], ty1 = wv.ty[0], ty2 = wv.ty[1];
   double uozOrigin = (double)((float)tx1 * 160.0f);
   double uozStep = (double)(-(float)ty1);
@@ -267,7 +272,8 @@ __device__ __noinline__ void gd_prep_wall(const GdScene &sc, const GdWall &wv, i
 }
 
 /* OWallMost row projection (engine.py:12294-12605), one fragment per wall. */
-__device__ __noinline__ int gd_project_rows(const GdView &v, const GdWall &wv, float worldZ, int x) {
+__device__ __noinline__ int gd_project_rows(const GdView &v_, const GdWall &wv, float worldZ, int x) {
+  const GdView &v = *gd_as_shared(&v_);
   i64 wsl = wv.sl, wsr = wv.sr;
   i64 wdl = gd_max(wv.dl, 1), wdr = gd_max(wv.dr, 1);
   bool owns = (wsr > wsl) && x >= wsl && x < wsr;
@@ -444,7 +450,8 @@ __device__ __forceinline__ bool gd_shares_endpoint(const GdScene &sc, int a, int
   int a0 = sc.wvtx[a * 2], a1 = sc.wvtx[a * 2 + 1], b0 = sc.wvtx[b * 2], b1 = sc.wvtx[b * 2 + 1];
   return a0 == b0 || a0 == b1 || a1 == b0 || a1 == b1;
 }
-__device__ __noinline__ bool gd_opposing_pair(const GdScene &sc, int a, int b) {
+__device__ __noinline__ bool gd_opposing_pair(const GdScene &sc_, int a, int b) {
+  const GdScene &sc = *gd_as_shared(&sc_);
   if (!gd_same_pair(sc, a, b)) return false;
   if (gd_wsec(sc, a * 2 + 1) < 0 || gd_wsec(sc, b * 2 + 1) < 0) return false;
   if (gd_shares_endpoint(sc, a, b)) return false;
@@ -483,7 +490,8 @@ __device__ bool gd_unique_at_vertex(const GdScene &sc, int v, int skipA, int ski
   index = (count == 1) ? found : 0;
   return count == 1;
 }
-__device__ __noinline__ bool gd_portal_bridge(const GdScene &sc, int slot, int path, int owner, int &index) {
+__device__ __noinline__ bool gd_portal_bridge(const GdScene &sc_, int slot, int path, int owner, int &index) {
+  const GdScene &sc = *gd_as_shared(&sc_);
   index = 0;
   if (!gd_two_distinct(sc, path) || owner == path) return false;
   int v = sc.wvtx[path * 2 + slot];
@@ -493,7 +501,8 @@ __device__ __noinline__ bool gd_portal_bridge(const GdScene &sc, int slot, int p
   if (!gd_bridge_pair_of(sc, path, owner, p0, p1)) return false;
   return gd_unique_at_vertex(sc, v, path, owner, p0, p1, index);
 }
-__device__ __noinline__ bool gd_sector_bridge(const GdScene &sc, int slot, int pending, int path, int &index) {
+__device__ __noinline__ bool gd_sector_bridge(const GdScene &sc_, int slot, int pending, int path, int &index) {
+  const GdScene &sc = *gd_as_shared(&sc_);
   index = 0;
   if (!gd_two_distinct(sc, pending) || path == pending || !gd_two_distinct(sc, path)) return false;
   int p0, p1;

@@ -152,9 +152,11 @@ struct GdIter {
 
 /* kSplit: the scene has lines a node builder split; the other instantiation carries none of that code */
 template <bool kSplit>
-__device__ void gd_column_decide(const GdScene &sc, const GdView &v, const GdWall *walls, const GdWall *frags,
+__device__ void gd_column_decide(const GdScene &sc_, const GdView &v_, const GdWall *walls, const GdWall *frags,
                                  const unsigned *ownerMask, const GdRowProj *rowproj, float *hitD, float *hitA, uint8_t *hitF, int x, float rx,
                                  float ry, const GdColState &c, GdIter &it) {
+  const GdScene &sc = *gd_as_shared(&sc_);
+  const GdView &v = *gd_as_shared(&v_);
   walls = gd_as_shared(walls); ownerMask = gd_as_shared(ownerMask);
   hitD = gd_as_shared(hitD); hitA = gd_as_shared(hitA); hitF = gd_as_shared(hitF);
   const int curSector = c.cur;
@@ -473,10 +475,13 @@ struct GdTierCtx {
   int tailBottom;   /* rows >= tailBottom use the group's first-column light; 255+ = never */
 };
 
-__device__ __noinline__ void gd_draw_tier(const GdScene &sc, const GdView &v, const GdShared &sh, int x, int ya, int yb, int ea,
+__device__ __noinline__ void gd_draw_tier(const GdScene &sc_, const GdView &v_, const GdShared &sh_, int x, int ya, int yb, int ea,
                              int eb, int texId, float originZ, const GdTierCtx &t, i64 vis, i64 firstVis,
                              bool tailValid, int tailBottom, int oa, int ob, bool oTailValid, int oTailBottom,
                              unsigned *filled) {
+  const GdScene &sc = *gd_as_shared(&sc_);
+  const GdView &v = *gd_as_shared(&v_);
+  const GdShared &sh = *gd_as_shared(&sh_);
   if (texId < 0 || ya >= yb) return;
 #ifdef GD_CHECKED
   if (texId >= sc.T) { atomicOr(gdCheckedStatus, GD_STATUS_BAD_INDEX); return; }   /* the tier stays undrawn */
@@ -554,8 +559,11 @@ __device__ __forceinline__ void gd_plane_rows(const GdPlaneSpan &p, i64 center, 
   }
 }
 
-__device__ __noinline__ void gd_mark_plane(const GdScene &sc, const GdView &v, const GdShared &sh, int x, int ya, int yb,
+__device__ __noinline__ void gd_mark_plane(const GdScene &sc_, const GdView &v_, const GdShared &sh_, int x, int ya, int yb,
                               int sector, bool isFloor, unsigned *owned, const unsigned *filled) {
+  const GdScene &sc = *gd_as_shared(&sc_);
+  const GdView &v = *gd_as_shared(&v_);
+  const GdShared &sh = *gd_as_shared(&sh_);
   if (ya >= yb) return;
   const int k0 = ya >> 5, k1 = (yb - 1) >> 5;
   unsigned any = 0;
@@ -694,8 +702,11 @@ __device__ void gd_mark_afterlife_columns(const GdScene &sc, const GdShared &sh)
 }
 
 template <bool kSplit>
-__device__ void gd_walk(const GdScene &sc, const GdView &v, const GdShared &sh, GdEvent *events, int *eventCount,
+__device__ void gd_walk(const GdScene &sc_, const GdView &v_, const GdShared &sh_, GdEvent *events, int *eventCount,
                         const GdRowProj *rowproj, int *status, int startSector) {
+  const GdScene &sc = *gd_as_shared(&sc_);
+  const GdView &v = *gd_as_shared(&v_);
+  const GdShared &sh = *gd_as_shared(&sh_);
   const int x = threadIdx.x;
   const int lane = x & 31;
   const unsigned quadBase = lane & ~3u;
