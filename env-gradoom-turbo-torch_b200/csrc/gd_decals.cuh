@@ -33,8 +33,11 @@ __host__ __device__ inline size_t gd_decal_scratch_per_cta(int slots) {
   return gd_align16((size_t)slots * sizeof(GdDecalProj));
 }
 
-__device__ __noinline__ void gd_decals(const GdScene &sc, const GdView &v, const GdShared &sh, const GdEvent *events,
+__device__ __noinline__ void gd_decals(const GdScene &sc_, const GdView &v_, const GdShared &sh_, const GdEvent *events,
                                        const int *eventCount, const gd_decal *ring, int slots, uint8_t *scratch) {
+  const GdScene &sc = *gd_as_shared(&sc_);
+  const GdView &v = *gd_as_shared(&v_);
+  const GdShared &sh = *gd_as_shared(&sh_);
   const int tid = threadIdx.x;
   int *count = &sh.misc[12];
   GdDecalProj *proj = (GdDecalProj *)scratch;

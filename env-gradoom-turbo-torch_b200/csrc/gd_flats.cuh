@@ -27,8 +27,10 @@ __device__ __forceinline__ bool gd_point_in_sector(const GdScene &sc, int s, flo
 
 /* Flat-fallback resolution of a pixel (engine.py:10961-11026): true when the
  * column ray meets no sector's plane inside that sector's polygon. */
-__device__ __noinline__ bool gd_pixel_unresolved(const GdScene &sc, const GdView &v, int x, int y, float rc, float rs,
+__device__ __noinline__ bool gd_pixel_unresolved(const GdScene &sc_, const GdView &v_, int x, int y, float rc, float rs,
                                                  int hint) {
+  const GdScene &sc = *gd_as_shared(&sc_);
+  const GdView &v = *gd_as_shared(&v_);
   i64 ti = gd_clamp((GD_ANG90 - v.pitchBam) >> 19, 0, 4095);
   i64 offFixed = ((i64)sc.fineTan[ti] * 12582912LL) >> 16;
   float center = 103.5f + (float)offFixed / 65536.0f;
@@ -61,7 +63,9 @@ __device__ __noinline__ bool gd_pixel_unresolved(const GdScene &sc, const GdView
   return true;
 }
 
-__device__ float gd_plane_depth(const GdScene &sc, const GdView &v, int sector, bool isFloor, int y) {
+__device__ float gd_plane_depth(const GdScene &sc_, const GdView &v_, int sector, bool isFloor, int y) {
+  const GdScene &sc = *gd_as_shared(&sc_);
+  const GdView &v = *gd_as_shared(&v_);
   i64 ti = gd_clamp((GD_ANG90 - v.pitchBam) >> 19, 0, 4095);
   i64 offFixed = ((i64)sc.fineTan[ti] * 12582912LL) >> 16;
   float flatCenter = (103.0f + (float)offFixed / 65536.0f) + 0.5f;
@@ -139,7 +143,9 @@ __device__ void gd_flat_bounds_setup(const GdScene &sc, const GdView &v, int *mi
   }
 }
 
-__device__ __noinline__ GdFlatRay gd_flat_ray(const GdScene &sc, const GdView &v, int x) {
+__device__ __noinline__ GdFlatRay gd_flat_ray(const GdScene &sc_, const GdView &v_, int x) {
+  const GdScene &sc = *gd_as_shared(&sc_);
+  const GdView &v = *gd_as_shared(&v_);
   i64 ti = gd_clamp((GD_ANG90 - v.pitchBam) >> 19, 0, 4095);
   i64 offFixed = ((i64)sc.fineTan[ti] * 12582912LL) >> 16;
   GdFlatRay r;
@@ -151,8 +157,10 @@ __device__ __noinline__ GdFlatRay gd_flat_ray(const GdScene &sc, const GdView &v
   return r;
 }
 
-__device__ __noinline__ GdFlatProbe gd_flat_probe(const GdScene &sc, const GdView &v, const GdFlatRay &r,
+__device__ __noinline__ GdFlatProbe gd_flat_probe(const GdScene &sc_, const GdView &v_, const GdFlatRay &r,
                                                   const GdFlatBounds &b, int y, int currentSector) {
+  const GdScene &sc = *gd_as_shared(&sc_);
+  const GdView &v = *gd_as_shared(&v_);
   float delta = (float)y - r.center;
   GdFlatProbe out;
   out.isFloor = delta > 0;
@@ -214,8 +222,11 @@ __device__ __noinline__ GdFlatProbe gd_flat_probe(const GdScene &sc, const GdVie
  *      and one bit per pixel telling whether it anchors horizontal spans.
  *   C  one thread per remaining queued pixel: its own repaired sector, or the
  *      one its nearest anchors left and right agree on. */
-__device__ void gd_fallback_pass(const GdScene &sc, const GdView &v, const GdShared &sh, int currentSector,
+__device__ void gd_fallback_pass(const GdScene &sc_, const GdView &v_, const GdShared &sh_, int currentSector,
                                  unsigned short *vsec, bool &sweepDone) {
+  const GdScene &sc = *gd_as_shared(&sc_);
+  const GdView &v = *gd_as_shared(&v_);
+  const GdShared &sh = *gd_as_shared(&sh_);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int count = min(sh.misc[1], GD_FALLBACK_MAX);
   int *queue = (int *)sh.hitD;

@@ -367,7 +367,8 @@ __device__ __forceinline__ i64 gd_line_vis(const GdScene &sc, const GdWall *wall
 }
 
 /* Column-independent part of gd_project_rows for one (wall, height). */
-__device__ __noinline__ void gd_rowproj_setup(const GdView &v, const GdWall &wv, float worldZ, GdRowProj &o) {
+__device__ __noinline__ void gd_rowproj_setup(const GdView &v_, const GdWall &wv, float worldZ, GdRowProj &o) {
+  const GdView &v = *gd_as_shared(&v_);
   i64 wsl = wv.sl, wsr = wv.sr;
   i64 wdl = gd_max(wv.dl, 1), wdr = gd_max(wv.dr, 1);
   i64 relZ = gd_rint((worldZ - v.viewZ) * 65536.0f);
@@ -527,7 +528,10 @@ __device__ __forceinline__ bool gd_wall_in_frustum(const float4 wl, const GdView
   return true;
 }
 
-__device__ void gd_wall_spans(const GdScene &sc, const GdView &v, const GdShared &sh) {
+__device__ void gd_wall_spans(const GdScene &sc_, const GdView &v_, const GdShared &sh_) {
+  const GdScene &sc = *gd_as_shared(&sc_);
+  const GdView &v = *gd_as_shared(&v_);
+  const GdShared &sh = *gd_as_shared(&sh_);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   GdWall *walls = sh.walls;
   short *list = (short *)sh.hitD;           /* walls that need the sweep */
@@ -602,8 +606,11 @@ __device__ void gd_wall_spans(const GdScene &sc, const GdView &v, const GdShared
  * lowest wall index, as the reference's first-minimum over its ascending
  * blocking list.  Only walls that passed the frustum test can be crossed, and
  * the division is spent only on walls the sign test says are crossed. */
-__device__ void gd_blocking_raycast(const GdScene &sc, const GdView &v, const GdShared &sh, const short *list, int listed,
+__device__ void gd_blocking_raycast(const GdScene &sc_, const GdView &v_, const GdShared &sh_, const short *list, int listed,
                                     float rx, float ry, float &wallDistance, int &blockingWall) {
+  const GdScene &sc = *gd_as_shared(&sc_);
+  const GdView &v = *gd_as_shared(&v_);
+  const GdShared &sh = *gd_as_shared(&sh_);
   float best = GD_INF;
   int bestWall = GD_CHECK_INDEX(sc.blocking[0], sc.W);
 #pragma unroll 1

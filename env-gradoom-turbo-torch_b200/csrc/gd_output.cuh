@@ -7,6 +7,7 @@
  * Integer definition: src/gradoom/_triton_kernels.py:120-177.  The weights
  * (y_overlap*x_overlap)/48 factor exactly into (y_overlap/12)*(x_overlap/4). */
 __device__ void gd_resize(const uint8_t *frame, const unsigned long long *pal64, int srcRows, uint8_t *out) {
+  frame = gd_as_shared(frame); pal64 = gd_as_shared(pal64); out = gd_as_shared(out);
   for (int o = threadIdx.x; o < GD_OBS * GD_OBS; o += GD_THREADS) {
     int oy = o / GD_OBS, ox = o - oy * GD_OBS;
     int ys = oy * 240, ye = ys + 240, xs = ox * 320, xe = xs + 320;

@@ -4,8 +4,10 @@
 #define GD_SPRITES_CUH
 
 /* ---- phase: sprites (engine.py:14138-14228, 14684-14947) ----------------- */
-__device__ __noinline__ void gd_actor_setup(const GdScene &sc, const GdView &v, const gd_thing &t, int sector,
+__device__ __noinline__ void gd_actor_setup(const GdScene &sc_, const GdView &v_, const gd_thing &t, int sector,
                                             GdActor &ac) {
+  const GdScene &sc = *gd_as_shared(&sc_);
+  const GdView &v = *gd_as_shared(&v_);
   ac.alive = (t.flags & GD_THING_ALIVE) != 0;
   ac.style = t.style;
   ac.x = t.x; ac.y = t.y;
@@ -64,8 +66,11 @@ __device__ __forceinline__ bool gd_behind(const GdScene &sc, const GdWall &wv, i
  * every column thread first lists its visible candidates; then the warps take
  * the listed columns from a counter and draw each candidate's rows 32 at a
  * time, far to near. */
-__device__ void gd_sprites(const GdScene &sc, const GdView &v, const GdShared &sh, const GdEvent *events,
+__device__ void gd_sprites(const GdScene &sc_, const GdView &v_, const GdShared &sh_, const GdEvent *events,
                            const int *eventCount, int nThings) {
+  const GdScene &sc = *gd_as_shared(&sc_);
+  const GdView &v = *gd_as_shared(&v_);
+  const GdShared &sh = *gd_as_shared(&sh_);
   const int x0 = threadIdx.x, lane = threadIdx.x & 31;
   if (nThings <= 0) return;                          /* block-uniform */
   unsigned long long *candOf = (unsigned long long *)sh.hitD;       /* per column */
@@ -180,7 +185,9 @@ __device__ void gd_sprites(const GdScene &sc, const GdView &v, const GdShared &s
 }
 
 /* ---- phase: weapon (engine.py:14994-15121) ------------------------------ */
-__device__ __noinline__ void gd_weapon_patch(const GdScene &sc, uint8_t *frame, int id, i64 hoff, i64 voff) {
+__device__ __noinline__ void gd_weapon_patch(const GdScene &sc_, uint8_t *frame, int id, i64 hoff, i64 voff) {
+  frame = gd_as_shared(frame);
+  const GdScene &sc = *gd_as_shared(&sc_);
 #ifdef GD_CHECKED
   if (id >= sc.Q || id < -1) { if (threadIdx.x == 0) atomicOr(gdCheckedStatus, GD_STATUS_BAD_INDEX); }
 #endif
@@ -209,7 +216,8 @@ __device__ __noinline__ void gd_weapon_patch(const GdScene &sc, uint8_t *frame, 
   }
 }
 
-__device__ void gd_weapon(const GdScene &sc, const int32_t *lane, uint8_t *frame) {
+__device__ void gd_weapon(const GdScene &sc_, const int32_t *lane, uint8_t *frame) {
+  const GdScene &sc = *gd_as_shared(&sc_);
   if (!sc.wpnAvailable) return;
   if (lane[GD_L_FLAGS] & 1) return;
   int weapon = (int)gd_clamp(lane[GD_L_WEAPON], 0, 7);
@@ -268,7 +276,9 @@ __device__ void gd_hud_number(const GdScene &sc, const GdHudList &hl, int value,
   }
 }
 
-__device__ __noinline__ void gd_hud(const GdScene &sc, const GdShared &sh, const int32_t *lane, uint8_t *canvas) {
+__device__ __noinline__ void gd_hud(const GdScene &sc_, const GdShared &sh_, const int32_t *lane, uint8_t *canvas) {
+  const GdScene &sc = *gd_as_shared(&sc_);
+  const GdShared &sh = *gd_as_shared(&sh_);
   GdHudList hl;
   hl.entries = (int4 *)sh.obs;                       /* free until the resize */
   hl.count = (int *)(sh.obs + GD_HUD_MAX_PATCHES * sizeof(int4));

@@ -22,8 +22,10 @@ struct GdPlaneEntry {
 
 static_assert(sizeof(GdPlaneEntry) == GD_PLANE_ENTRY_BYTES, "scratch layout");
 
-__device__ __noinline__ void gd_plane_entry_setup(const GdScene &sc, const GdView &v, int sector, bool isFloor,
+__device__ __noinline__ void gd_plane_entry_setup(const GdScene &sc_, const GdView &v_, int sector, bool isFloor,
                                                   GdPlaneEntry &e) {
+  const GdScene &sc = *gd_as_shared(&sc_);
+  const GdView &v = *gd_as_shared(&v_);
   float ph = isFloor ? (v.viewZ - gd_sec_floor(sc, sector)) : (gd_sec_ceil(sc, sector) - v.viewZ);
   int4 si = gd_sec_info(sc, sector);
   int tex = GD_CHECK_INDEX(isFloor ? si.y : si.z, sc.T);
@@ -588,7 +590,10 @@ __device__ __forceinline__ i64 gd_masked_iscale(i64 swall) {
 }
 
 template <bool kSplit>
-__device__ __noinline__ void gd_masked_pass(const GdScene &sc, const GdView &v, const GdShared &sh) {
+__device__ __noinline__ void gd_masked_pass(const GdScene &sc_, const GdView &v_, const GdShared &sh_) {
+  const GdScene &sc = *gd_as_shared(&sc_);
+  const GdView &v = *gd_as_shared(&v_);
+  const GdShared &sh = *gd_as_shared(&sh_);
   const int x = threadIdx.x;
   float rx, ry;
   gd_ray(v, x, rx, ry);
