@@ -63,6 +63,27 @@ def test_cuda_matches_oracle_on_seeded_lanes(name, n, k, seed, pkg, oracle, scen
     assert np.array_equal(obs.cpu().numpy(), expected["obs"])
 
 
+def test_views_pitched_to_the_ends_of_the_tangent_table_match_the_oracle(pkg, oracle, scenes):
+    """Pitch values that index the first and last entries of the fine-tangent table put the screen centre
+    tens of thousands of rows off screen: the visplane pixels then take the 64-bit form of their light
+    term (the 32-bit form serves every pitch short of +-89.5 degrees), and everything else must hold too."""
+
+    from gradoom_b200 import state as gdstate, stepper
+
+    sc, blob = scenes("c1")
+    lanes, things = stepper.random_lanes(sc, 12, 4, seed=21)
+    for lane, index in enumerate([0, 1, 2, 3, 8, 40, 4095, 4094, 4093, 4088, 4050, 2048]):
+        lanes[lane, gdstate.L_PITCH_BAM] = 0x40000000 - (index << 19)
+    expected = oracle.render(blob, lanes, things, mask_hud=True)
+    r = _renderer(blob, 4)
+    obs, indexed, _ = r.frames(_dev(lanes), _dev(things), obs=True, indexed=True)
+    r.check_status()
+    assert np.array_equal(indexed.cpu().numpy(), expected["indexed"])
+    assert np.array_equal(obs.cpu().numpy(), expected["obs"])
+    only, _, _ = r.frames(_dev(lanes), _dev(things), obs=True)          # the observation-only configuration
+    assert np.array_equal(only.cpu().numpy(), expected["obs"])
+
+
 def test_unmasked_observation_includes_the_status_bar(pkg, oracle, scenes):
     from gradoom_b200 import stepper
 
